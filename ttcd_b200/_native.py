@@ -1,0 +1,127 @@
+"""ctypes binding to the in-tree sm_100a library ``ttcd_b200/_lib/libttcd_b200.so``.
+
+Every kernel is exported with C linkage and takes raw device pointers, sizes and
+a ``cudaStream_t``; Python passes ``tensor.data_ptr()`` and the current torch
+stream, so launches are ordered with the surrounding torch work and no torch C++
+headers are needed at build time.  Entry points return 0 on success or a
+non-zero ``cudaError_t`` / negative framework error code.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+
+import torch
+
+_LIB_DIR = Path(__file__).resolve().parent / "_lib"
+_LIB_PATH = _LIB_DIR / "libttcd_b200.so"
+_lib: ctypes.CDLL | None = None
+_load_error: str | None = None
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def load(required: bool = False) -> ctypes.CDLL | None:
+    """Load the shared library once.  ``required`` raises if it is missing."""
+    global _lib, _load_error
+    if _lib is None and _load_error is None:
+        if _LIB_PATH.exists():
+            try:
+                _lib = ctypes.CDLL(str(_LIB_PATH), mode=ctypes.RTLD_GLOBAL)
+            except OSError as exc:  # pragma: no cover - depends on the machine
+                _load_error = f"{exc}"
+        else:
+            _load_error = f"{_LIB_PATH} not built (run `python -m ttcd_b200._build`)"
+    if _lib is None and required:
+        raise NativeError(f"ttcd_b200 native library unavailable: {_load_error}")
+    return _lib
+
+
+def available() -> bool:
+    return load() is not None
+
+
+def torch_fallback_allowed() -> bool:
+    """Bring-up switch: let CUDA tensors run the PyTorch statement of an op."""
+    return os.environ.get("TTCD_TORCH_FALLBACK", "0") == "1"
+
+
+def use_native(*tensors: torch.Tensor) -> bool:
+    """True when the op must run on the hand-written kernels.
+
+    CUDA bf16 tensors always take the native path; a missing library is an error
+    (never a silent fallback) unless TTCD_TORCH_FALLBACK=1.  CPU tensors and fp32
+    CUDA tensors take the PyTorch statement.
+    """
+    t = tensors[0]
+    if not t.is_cuda or t.dtype != torch.bfloat16:
+        return False
+    if load() is None:
+        if torch_fallback_allowed():
+            return False
+        raise NativeError(
+            "CUDA bf16 tensors require the ttcd_b200 native library: " + str(_load_error)
+        )
+    return True
+
+
+def has(symbol: str) -> bool:
+    lib = load()
+    return lib is not None and hasattr(lib, symbol)
+
+
+def stream_ptr() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+_ERRORS = {
+    -1: "invalid argument (shape/stride/alignment)",
+    -2: "device wait ran out (bounded spin expired)",
+    -3: "size exceeds the built-in maximum",
+    -4: "tensor-map encode failed",
+}
+
+
+def call(symbol: str, *args) -> None:
+    """Invoke ``int symbol(args...)`` and raise on a non-zero status."""
+    lib = load(required=True)
+    fn = getattr(lib, symbol, None)
+    if fn is None:
+        raise NativeError(f"native symbol {symbol} missing from {_LIB_PATH}")
+    fn.restype = ctypes.c_int
+    rc = fn(*args)
+    if rc != 0:
+        detail = _ERRORS.get(rc, f"cudaError {rc}")
+        raise NativeError(f"{symbol} failed: {detail}")
+
+
+def i32(v) -> ctypes.c_int:
+    return ctypes.c_int(int(v))
+
+
+def i64(v) -> ctypes.c_longlong:
+    return ctypes.c_longlong(int(v))
+
+
+def f32(v) -> ctypes.c_float:
+    return ctypes.c_float(float(v))
+
+
+def device_status(reset: bool = True) -> int:
+    """Read (and clear) the device-side error word written by bounded waits."""
+    if not has("ttcd_read_status"):
+        return 0
+    lib = load(required=True)
+    lib.ttcd_read_status.restype = ctypes.c_int
+    return int(lib.ttcd_read_status(ctypes.c_int(1 if reset else 0)))

@@ -1,0 +1,39 @@
+"""Model families and their HF Auto* registration.
+
+Importing this package registers ``transformer``, ``ipttt`` and ``ipttcdv9`` with
+``AutoConfig`` / ``AutoModel`` / ``AutoModelForCausalLM`` (the reference does the same on
+``import custom_models``: custom_models/ipttcd/__init__.py:17-24, custom_models/ipttt/__init__.py).
+"""
+from transformers import AutoConfig, AutoModel, AutoModelForCausalLM
+
+from .configuration import (IPTTCDConfig, IPTTCDv8Config, IPTTCDv9Config, IPTTCDv9LowCopyConfig, IPTTTConfig,
+                            TransformerConfig)
+from .layers import Attention, GatedMLP, RMSNorm, RotaryEmbedding, WindowKVCache
+from .modeling_ipttcdv9 import IPTTCDBlock, IPTTCDForCausalLM, IPTTCDMLP, IPTTCDModel
+from .modeling_ipttt import IPTTTBlock, IPTTTForCausalLM, IPTTTMLP, IPTTTModel
+from .modeling_transformer import TransformerBlock, TransformerForCausalLM, TransformerModel
+
+IPTTCDv9Model = IPTTCDModel
+IPTTCDv9ForCausalLM = IPTTCDForCausalLM
+
+
+def register_all() -> None:
+    for cfg, model, causal in (
+        (TransformerConfig, TransformerModel, TransformerForCausalLM),
+        (IPTTTConfig, IPTTTModel, IPTTTForCausalLM),
+        (IPTTCDv9Config, IPTTCDModel, IPTTCDForCausalLM),
+    ):
+        AutoConfig.register(cfg.model_type, cfg, exist_ok=True)
+        AutoModel.register(cfg, model, exist_ok=True)
+        AutoModelForCausalLM.register(cfg, causal, exist_ok=True)
+
+
+register_all()
+
+__all__ = [
+    "TransformerConfig", "IPTTTConfig", "IPTTCDConfig", "IPTTCDv8Config", "IPTTCDv9Config", "IPTTCDv9LowCopyConfig",
+    "TransformerModel", "TransformerForCausalLM", "TransformerBlock",
+    "IPTTTModel", "IPTTTForCausalLM", "IPTTTBlock", "IPTTTMLP",
+    "IPTTCDModel", "IPTTCDForCausalLM", "IPTTCDBlock", "IPTTCDMLP", "IPTTCDv9Model", "IPTTCDv9ForCausalLM",
+    "Attention", "GatedMLP", "RMSNorm", "RotaryEmbedding", "WindowKVCache", "register_all",
+]

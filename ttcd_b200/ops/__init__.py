@@ -1,0 +1,168 @@
+"""Functional op layer.
+
+Each function routes CUDA bf16 tensors to the hand-written sm_100a kernels
+(``ttcd_b200.ops.cuda``; autograd Functions with native forward and backward)
+and everything else (CPU tensors, fp32) to the PyTorch statements in
+``ttcd_b200.ops.reference``.  A CUDA bf16 call with the native library missing
+raises instead of silently falling back.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from .. import _native
+from . import reference
+
+__all__ = [
+    "rmsnorm", "rmsnorm_dual", "qkv_norm_rope", "rope", "swiglu", "swiglu_packed", "linear", "matmul",
+    "attention", "dual_window_attention", "lse_merge", "dwconv_chunked", "dwconv_sequence",
+    "ttt_scan", "cross_entropy", "linear_cross_entropy", "newton_schulz", "reference",
+]
+
+
+def _cuda():
+    from . import cuda  # noqa: WPS433 (lazy: keeps CPU-only imports light)
+    return cuda
+
+
+# -- normalisation -----------------------------------------------------------------
+
+def rmsnorm(x, weight, eps: float, residual=None, prenorm: bool = False):
+    if _native.use_native(x):
+        return _cuda().rmsnorm(x, weight, eps, residual, prenorm)
+    return reference.rmsnorm(x, weight, eps, residual, prenorm)
+
+
+def rmsnorm_dual(attn_teacher, attn_student, residual, weight, eps: float):
+    if _native.use_native(attn_teacher):
+        return _cuda().rmsnorm_dual(attn_teacher, attn_student, residual, weight, eps)
+    return reference.rmsnorm_dual(attn_teacher, attn_student, residual, weight, eps)
+
+
+# -- rotary --------------------------------------------------------------------------
+
+def rope(x, cos, sin, offset=0, positions=None):
+    if _native.use_native(x):
+        return _cuda().rope(x, cos, sin, offset, positions)
+    return reference.rope(x, cos, sin, offset, positions)
+
+
+def qkv_norm_rope(q, k, q_weight, k_weight, eps: float, cos, sin, offset=0, positions=None):
+    """Per-head RMSNorm (when weights are given) followed by RoPE on q[B,T,H,D], k[B,T,HK,D]."""
+    if _native.use_native(q):
+        return _cuda().qk_norm_rope(q, k, q_weight, k_weight, eps, cos, sin, offset, positions)
+    if q_weight is not None:
+        q = reference.rmsnorm(q, q_weight, eps)
+        k = reference.rmsnorm(k, k_weight, eps)
+    if cos is not None:
+        q = reference.rope(q, cos, sin, offset, positions)
+        k = reference.rope(k, cos, sin, offset, positions)
+    return q, k
+
+
+# -- MLP pieces ------------------------------------------------------------------------
+
+def swiglu(gate, up):
+    if _native.use_native(gate):
+        return _cuda().swiglu(gate, up)
+    return reference.swiglu(gate, up)
+
+
+def swiglu_packed(gate_up):
+    """swiglu on a [*, 2*d_i] tensor holding gate then up columns."""
+    d = gate_up.shape[-1] // 2
+    if _native.use_native(gate_up):
+        return _cuda().swiglu_packed(gate_up)
+    return reference.swiglu(gate_up[..., :d], gate_up[..., d:])
+
+
+def linear(x, weight, bias=None):
+    if _native.use_native(x):
+        return _cuda().linear(x, weight, bias)
+    return F.linear(x, weight, bias)
+
+
+def matmul(a, b):
+    """Batched a @ b; transposed views select the operand major mode of the tensor-core kernel."""
+    if _native.use_native(a) and b.dtype == torch.bfloat16:
+        return _cuda().matmul(a, b)
+    return torch.matmul(a, b)
+
+
+def dwconv_chunked(x, weight, causal: bool = True):
+    """x[b,T,C,D], weight [D,K] (or Conv1d layout [D,1,K])."""
+    w2 = weight.reshape(weight.shape[0], weight.shape[-1])
+    if _native.use_native(x):
+        return _cuda().dwconv_chunked(x, w2, causal)
+    return reference.dwconv_chunked(x, w2, causal)
+
+
+def dwconv_sequence(x, weight, bias=None, activation=None, residual=None, cu_seqlens=None):
+    w2 = weight.reshape(weight.shape[0], weight.shape[-1])
+    if _native.use_native(x) and cu_seqlens is None:
+        y = _cuda().dwconv_chunked(x.unsqueeze(1), w2, True).squeeze(1)
+        if bias is not None:
+            y = y + bias
+        if activation in ("silu", "swish"):
+            y = F.silu(y)
+        if residual is not None:
+            y = y + residual
+        return y
+    return reference.dwconv_sequence(x, w2, bias, activation, residual, cu_seqlens)
+
+
+# -- attention ---------------------------------------------------------------------------
+
+def attention(q, k, v, window=None, scale=None, cu_seqlens=None, return_lse: bool = False):
+    if _native.use_native(q):
+        return _cuda().attention(q, k, v, window, scale, cu_seqlens, return_lse)
+    return reference.attention(q, k, v, window, scale, cu_seqlens, return_lse)
+
+
+def dual_window_attention(q, k, v, window_teacher, window_student, scale=None, cu_seqlens=None):
+    """Teacher and student sliding-window outputs in one pass over K/V."""
+    if _native.use_native(q):
+        return _cuda().dual_window_attention(q, k, v, window_teacher, window_student, scale, cu_seqlens)
+    return reference.dual_window_attention(q, k, v, window_teacher, window_student, scale, cu_seqlens)
+
+
+def lse_merge(o_a, lse_a, o_b, lse_b):
+    if _native.use_native(o_a):
+        return _cuda().lse_merge(o_a, lse_a, o_b, lse_b)
+    return reference.lse_merge(o_a, lse_a, o_b, lse_b)
+
+
+# -- fast-weight scan ----------------------------------------------------------------------
+
+def ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, *, lr, update_every, state_dtype=None,
+             normalize_student=False, norm_proj_diff=False, post_proj=None, return_last_dw_norm=False):
+    plain = not normalize_student and not norm_proj_diff and post_proj is None
+    if _native.use_native(z_out) and plain and (state_dtype in (None, torch.bfloat16)):
+        return reference.ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, lr=lr,
+                                  update_every=update_every, state_dtype=torch.float32,
+                                  return_last_dw_norm=return_last_dw_norm, matmul=_cuda().matmul)
+    return reference.ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, lr=lr,
+                              update_every=update_every, state_dtype=state_dtype,
+                              normalize_student=normalize_student, norm_proj_diff=norm_proj_diff,
+                              post_proj=post_proj, return_last_dw_norm=return_last_dw_norm)
+
+
+# -- losses ------------------------------------------------------------------------------------
+
+def cross_entropy(logits, labels, ignore_index: int = -100, label_smoothing: float = 0.0, z_loss: float = 0.0):
+    if _native.use_native(logits) and label_smoothing == 0.0 and z_loss == 0.0:
+        return _cuda().cross_entropy(logits, labels, ignore_index)
+    return reference.cross_entropy(logits, labels, ignore_index, label_smoothing, z_loss)
+
+
+def linear_cross_entropy(hidden, labels, weight, bias=None, ignore_index: int = -100, num_chunks: int = 8):
+    if _native.use_native(hidden) and bias is None:
+        return _cuda().linear_cross_entropy(hidden, labels, weight, ignore_index, num_chunks)
+    return reference.linear_cross_entropy(hidden, labels, weight, bias, ignore_index)
+
+
+def newton_schulz(g, coeffs=reference.NS_COEFFS):
+    if g.is_cuda and _native.available():
+        return _cuda().newton_schulz(g, coeffs)
+    return reference.newton_schulz(g, coeffs)

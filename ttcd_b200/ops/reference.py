@@ -1,0 +1,373 @@
+"""Plain-PyTorch statements of every op in the framework.
+
+These are the numerical oracles for the CUDA kernels (tests compare a kernel
+against the function here evaluated in fp32) and the execution path for CPU
+tensors.  Nothing in this file launches a hand-written kernel.
+
+Semantics follow the reference's layers: RMSNorm with fp32 statistics and an
+optional fused residual add (fla/modules/layernorm.py:254-320), NeoX-style RoPE
+(fla/modules/rotary.py:27-32), flash-attn window semantics
+``window_size=(W-1, 0)`` with bottom-right alignment when ``Tq < Tk``
+(test/test_fused_dual_attn.py:88-110), the per-chunk causal depthwise conv
+(custom_models/ipttcd/modeling_ipttcdv9.py:203-211) and the grouped fast-weight
+scan (custom_models/ipttcd/modeling_ipttcdv9_lowcopy_scanfuse.py:117-204).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+# ----------------------------------------------------------------------------
+# normalisation / rotary / activation
+# ----------------------------------------------------------------------------
+
+
+def rmsnorm(x, weight, eps: float, residual=None, prenorm: bool = False):
+    """y = rmsnorm(x + residual) * weight; optionally also return the summed residual."""
+    out_dtype = x.dtype
+    xf = x.float()
+    if residual is not None:
+        xf = xf + residual.float()
+    res_out = xf.to(residual.dtype if residual is not None else out_dtype)
+    rstd = torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + eps)
+    y = xf * rstd
+    if weight is not None:
+        y = y * weight.float()
+    y = y.to(out_dtype)
+    return (y, res_out) if prenorm else y
+
+
+def rmsnorm_dual(attn_teacher, attn_student, residual, weight, eps: float):
+    """The TTT block's two mlp_norm calls sharing one residual.
+
+    Returns (teacher_normed, student_normed, new_residual) with
+    new_residual = residual + attn_teacher (the student sum is not kept).
+    """
+    x, res_out = rmsnorm(attn_teacher, weight, eps, residual=residual, prenorm=True)
+    t = rmsnorm(attn_student, weight, eps, residual=residual, prenorm=False)
+    return x, t, res_out
+
+
+def rope_tables(head_dim: int, base: float, seqlen: int, device=None, dtype=torch.float32,
+                inv_freq: torch.Tensor | None = None, attn_scale: float = 1.0):
+    """cos/sin tables [seqlen, head_dim/2]: fp32 math, stored in ``dtype``."""
+    if inv_freq is None:
+        inv_freq = 1.0 / (base ** (torch.arange(0, head_dim, 2, device=device, dtype=torch.float32) / head_dim))
+    t = torch.arange(seqlen, device=device, dtype=torch.float32)
+    freqs = torch.outer(t, inv_freq.to(device=device, dtype=torch.float32))
+    cos, sin = torch.cos(freqs), torch.sin(freqs)
+    if attn_scale != 1.0:
+        cos, sin = cos * attn_scale, sin * attn_scale
+    return cos.to(dtype), sin.to(dtype)
+
+
+def yarn_inv_freq(head_dim: int, base: float, factor: float, original_max_position: int,
+                  beta_fast: float = 32.0, beta_slow: float = 1.0, device=None) -> torch.Tensor:
+    """YaRN inverse frequencies: blend of extrapolation and interpolation by a per-pair ramp."""
+    inv_freq = 1.0 / (base ** (torch.arange(0, head_dim, 2, device=device, dtype=torch.float32) / head_dim))
+    if factor <= 1.0:
+        return inv_freq
+
+    def correction_dim(n_rot: float) -> float:
+        return head_dim * math.log(original_max_position / (2.0 * math.pi * n_rot)) / (2.0 * math.log(base))
+
+    low = max(math.floor(correction_dim(beta_fast)), 0)
+    high = min(math.ceil(correction_dim(beta_slow)), head_dim - 1)
+    lo, hi = low / 2.0, high / 2.0
+    if lo == hi:
+        hi += 0.001
+    idx = torch.arange(inv_freq.shape[0], device=device, dtype=torch.float32)
+    ramp = ((idx - lo) / (hi - lo)).clamp(0.0, 1.0)
+    return inv_freq * (1.0 - ramp) + (inv_freq / factor) * ramp
+
+
+def yarn_mscale(factor: float, mscale: float = 1.0) -> float:
+    if factor <= 1.0:
+        return 1.0
+    return float(mscale) if mscale != 1.0 else 0.1 * math.log(factor) + 1.0
+
+
+def rope(x, cos, sin, offset=0, positions=None, conjugate: bool = False):
+    """NeoX (half-split) rotary on x[B,T,H,D] with tables [*, D/2].
+
+    ``offset`` is an int or a per-batch tensor; ``positions`` (shape [B,T] or [T])
+    overrides it (varlen packing, context-parallel shards).
+    """
+    B, T, H, D = x.shape
+    half = cos.shape[-1]
+    if positions is None:
+        base = torch.arange(T, device=x.device)
+        if isinstance(offset, torch.Tensor):
+            positions = base[None, :] + offset.to(x.device).view(-1, 1)
+        else:
+            positions = (base + int(offset))[None, :]
+    elif positions.dim() == 1:
+        positions = positions[None, :]
+    c = cos[positions].float().unsqueeze(2)  # [B|1, T, 1, half]
+    s = sin[positions].float().unsqueeze(2)
+    if conjugate:
+        s = -s
+    xf = x.float()
+    x1, x2 = xf[..., :half], xf[..., half:2 * half]
+    out = torch.cat([x1 * c - x2 * s, x1 * s + x2 * c, xf[..., 2 * half:]], dim=-1)
+    return out.to(x.dtype)
+
+
+def swiglu(gate, up):
+    gf = gate.float()
+    return (gf * torch.sigmoid(gf) * up.float()).to(gate.dtype)
+
+
+# ----------------------------------------------------------------------------
+# attention
+# ----------------------------------------------------------------------------
+
+
+def window_mask(tq: int, tk: int, window: int | None, device=None) -> torch.Tensor:
+    """Boolean [tq, tk] visibility mask, causal, bottom-right aligned, W keys incl. self."""
+    qi = torch.arange(tq, device=device)[:, None] + (tk - tq)
+    kj = torch.arange(tk, device=device)[None, :]
+    mask = kj <= qi
+    if window is not None and window > 0:
+        mask &= kj > qi - window
+    return mask
+
+
+def _segment_mask(cu_seqlens: torch.Tensor, total: int, device) -> torch.Tensor:
+    seg = torch.zeros(total, dtype=torch.long, device=device)
+    bounds = cu_seqlens.to(device=device, dtype=torch.long)
+    seg[bounds[1:-1]] = 1
+    seg = seg.cumsum(0)
+    return seg[:, None] == seg[None, :]
+
+
+def attention(q, k, v, window: int | None = None, scale: float | None = None,
+              cu_seqlens: torch.Tensor | None = None, return_lse: bool = False):
+    """Causal (sliding-window) attention on q[B,Tq,H,D], k/v[B,Tk,HK,D]; fp32 softmax."""
+    B, Tq, H, D = q.shape
+    Tk, HK = k.shape[1], k.shape[2]
+    scale = D ** -0.5 if scale is None else scale
+    rep = H // HK
+    qf = q.float().permute(0, 2, 1, 3)
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(rep, dim=1)
+    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(rep, dim=1)
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    mask = window_mask(Tq, Tk, window, device=q.device)
+    if cu_seqlens is not None:
+        mask = mask & _segment_mask(cu_seqlens, Tk, q.device)[Tk - Tq:]
+    s = s.masked_fill(~mask, float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    p = torch.exp(s - lse.unsqueeze(-1))
+    p = torch.nan_to_num(p, nan=0.0)
+    o = torch.matmul(p, vf).permute(0, 2, 1, 3).to(q.dtype)
+    return (o, lse) if return_lse else o
+
+
+def dual_window_attention(q, k, v, window_teacher: int | None, window_student: int,
+                          scale: float | None = None, cu_seqlens=None):
+    """Teacher (w_T) and student (w_S) outputs over shared Q/K/V."""
+    o_t = attention(q, k, v, window_teacher, scale, cu_seqlens)
+    o_s = attention(q, k, v, window_student, scale, cu_seqlens)
+    return o_t, o_s
+
+
+def lse_merge(o_a, lse_a, o_b, lse_b):
+    """Merge two partial softmax results (o[B,T,H,D], lse[B,H,T]) over disjoint key sets."""
+    m = torch.maximum(lse_a, lse_b)
+    m = torch.where(torch.isinf(m), torch.zeros_like(m), m)
+    wa = torch.exp(lse_a - m)
+    wb = torch.exp(lse_b - m)
+    denom = (wa + wb).clamp_min(1e-38)
+    wa = (wa / denom).transpose(1, 2).unsqueeze(-1)
+    wb = (wb / denom).transpose(1, 2).unsqueeze(-1)
+    return (o_a.float() * wa + o_b.float() * wb).to(o_a.dtype)
+
+
+# ----------------------------------------------------------------------------
+# depthwise conv
+# ----------------------------------------------------------------------------
+
+
+def dwconv_chunked(x, weight, causal: bool = True):
+    """Depthwise conv over the C axis of x[b,T,C,D] with zero context per chunk.
+
+    weight: [D, K].  causal: y[c] = sum_j w[:, j] * x[c - (K-1) + j]; otherwise
+    centred ('same' padding K//2).
+    """
+    b, T, C, D = x.shape
+    K = weight.shape[-1]
+    xf = x.float()
+    wf = weight.float().reshape(D, K)
+    left = K - 1 if causal else K // 2
+    right = 0 if causal else K - 1 - left
+    xp = F.pad(xf, (0, 0, left, right))
+    y = torch.zeros_like(xf)
+    for j in range(K):
+        y = y + xp[:, :, j:j + C, :] * wf[:, j]
+    return y.to(x.dtype)
+
+
+def dwconv_sequence(x, weight, bias=None, activation: str | None = None, residual=None,
+                    cu_seqlens=None):
+    """Sequence-level causal depthwise conv on x[B,T,D] (no per-chunk reset), weight [D,K]."""
+    B, T, D = x.shape
+    if cu_seqlens is not None:
+        outs = []
+        bounds = cu_seqlens.tolist()
+        for s, e in zip(bounds[:-1], bounds[1:]):
+            outs.append(dwconv_chunked(x[:, s:e].unsqueeze(1), weight, True).squeeze(1))
+        y = torch.cat(outs, dim=1)
+    else:
+        y = dwconv_chunked(x.unsqueeze(1), weight, True).squeeze(1)
+    y = y.float()
+    if bias is not None:
+        y = y + bias.float()
+    if activation in ("silu", "swish"):
+        y = F.silu(y)
+    if residual is not None:
+        y = y + residual.float()
+    return y.to(x.dtype)
+
+
+# ----------------------------------------------------------------------------
+# TTT fast-weight scan
+# ----------------------------------------------------------------------------
+
+
+def ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, *, lr: float, update_every: int,
+             state_dtype: torch.dtype | None = None, normalize_student: bool = False,
+             norm_proj_diff: bool = False, post_proj: torch.Tensor | None = None,
+             return_last_dw_norm: bool = False, matmul=torch.matmul):
+    """Grouped fast-weight scan.
+
+    ``matmul`` is the batched-matmul primitive (torch.matmul, or the tensor-core
+    kernel wrapper for CUDA bf16 inputs).
+
+    z_out, z_tgt, z_hat: [b, T, C, d_i]; beta: [b, T, C, 1] or None;
+    w_down: [d_h, d_i]; w_update_t: [d_i, d_h] (= W_down^T @ W_p when the
+    projection is folded in, else W_down^T); post_proj: optional [d_h, d_h]
+    applied after beta when the projection is not folded.
+
+        P_j  = beta_j * ((z_tgt_j - z_hat_j) @ w_update_t)
+        dW_j = P_j^T @ z_hat_j                      (j = 0..T-2)
+        W_i  = w_down + lr * sum_{j<i} dW_j          (prefix kept in state_dtype, grouped)
+        Y_i  = z_out_i @ W_i^T
+    """
+    b, T, C, d_i = z_out.shape
+    compute_dtype = z_out.dtype
+    state_dtype = compute_dtype if state_dtype is None else state_dtype
+    w_cur = w_down.to(state_dtype).unsqueeze(0).expand(b, -1, -1)
+    lr_t = w_cur.new_tensor(lr)
+    group = max(1, min(T, update_every))
+    outs = []
+    last_norm = None
+    for gs in range(0, T, group):
+        ge = min(gs + group, T)
+        upd_end = min(ge, T - 1)
+        k_upd = upd_end - gs
+        cs = None
+        if k_upd > 0:
+            diff = z_tgt[:, gs:upd_end] - z_hat[:, gs:upd_end]
+            proj = matmul(diff, w_update_t.to(compute_dtype))
+            if norm_proj_diff:
+                proj = F.normalize(proj, p=2, dim=-1, eps=1e-6)
+            zh = z_hat[:, gs:upd_end]
+            if normalize_student:
+                zh = F.normalize(zh, p=2, dim=-1, eps=1e-6)
+            if beta is not None:
+                proj = proj * beta[:, gs:upd_end]
+            if post_proj is not None:
+                proj = matmul(proj, post_proj.to(compute_dtype))
+            d_w = matmul(proj.transpose(-1, -2), zh)
+            if return_last_dw_norm:
+                last_norm = d_w[:, -1].detach().float().norm()
+            cs = lr_t * torch.cumsum(d_w.to(state_dtype), dim=1)
+        for local in range(ge - gs):
+            if local == 0 or k_upd == 0:
+                w_step = w_cur
+            else:
+                w_step = w_cur + cs[:, min(local - 1, k_upd - 1)]
+            outs.append(matmul(z_out[:, gs + local], w_step.to(compute_dtype).transpose(-1, -2)))
+        if k_upd > 0:
+            w_cur = w_cur + cs[:, -1]
+    y = torch.stack(outs, dim=1)
+    return (y, last_norm) if return_last_dw_norm else y
+
+
+# ----------------------------------------------------------------------------
+# losses
+# ----------------------------------------------------------------------------
+
+
+def cross_entropy(logits, labels, ignore_index: int = -100, label_smoothing: float = 0.0,
+                  z_loss: float = 0.0):
+    """Mean CE over non-ignored rows; fp32 math."""
+    lf = logits.float()
+    loss = F.cross_entropy(lf, labels, ignore_index=ignore_index, label_smoothing=label_smoothing,
+                           reduction="sum")
+    valid = labels.ne(ignore_index)
+    if z_loss:
+        lse = torch.logsumexp(lf, dim=-1)
+        loss = loss + z_loss * (lse.pow(2) * valid).sum()
+    return loss / valid.sum().clamp_min(1)
+
+
+def linear_cross_entropy(hidden, labels, weight, bias=None, ignore_index: int = -100):
+    """CE(hidden @ weight^T + bias, labels) with the logits GEMM in the activation dtype."""
+    logits = F.linear(hidden, weight.to(hidden.dtype), None if bias is None else bias.to(hidden.dtype))
+    return cross_entropy(logits.view(-1, logits.shape[-1]), labels.reshape(-1), ignore_index)
+
+
+def l2_warp_grad(logits, loss_scale: float = 1e-4):
+    """Gradient term of l2-warp: 1e-4/(B*T) * max logit at the argmax position."""
+    B, T, V = logits.shape
+    mx, idx = logits.max(-1, keepdim=True)
+    g = torch.zeros_like(logits)
+    g.scatter_(-1, idx, mx * (loss_scale / (B * T)))
+    return g
+
+
+# ----------------------------------------------------------------------------
+# optimiser math
+# ----------------------------------------------------------------------------
+
+NS_COEFFS = (
+    (4.0848, -6.8946, 2.9270),
+    (3.9505, -6.3029, 2.6377),
+    (3.7418, -5.5913, 2.3037),
+    (2.8769, -3.1427, 1.2046),
+    (2.8366, -3.0525, 1.2012),
+)
+
+
+def newton_schulz(g: torch.Tensor, coeffs=NS_COEFFS, dtype=torch.bfloat16) -> torch.Tensor:
+    """Quintic Newton-Schulz orthogonalisation of a matrix or batch of matrices."""
+    squeeze = g.dim() == 2
+    x = (g.unsqueeze(0) if squeeze else g).to(dtype)
+    transposed = x.size(1) > x.size(2)
+    if transposed:
+        x = x.transpose(1, 2)
+    x = x / (x.float().norm(dim=(1, 2), keepdim=True).to(dtype) + 1e-7)
+    for a, b, c in coeffs:
+        A = x @ x.transpose(1, 2)
+        Bm = b * A + c * (A @ A)
+        x = a * x + Bm @ x
+    if transposed:
+        x = x.transpose(1, 2)
+    return x.squeeze(0) if squeeze else x
+
+
+def adamw_step(param, grad, exp_avg, exp_avg_sq, *, lr, beta1, beta2, eps, weight_decay, step,
+               grad_scale: float = 1.0):
+    """One decoupled-weight-decay Adam update in fp32 (in place on param and moments)."""
+    g = grad.float() * grad_scale
+    param.mul_(1.0 - lr * weight_decay)
+    exp_avg.mul_(beta1).add_(g, alpha=1.0 - beta1)
+    exp_avg_sq.mul_(beta2).addcmul_(g, g, value=1.0 - beta2)
+    bc1 = 1.0 - beta1 ** step
+    bc2 = 1.0 - beta2 ** step
+    denom = (exp_avg_sq.sqrt() / math.sqrt(bc2)).add_(eps)
+    param.addcdiv_(exp_avg, denom, value=-lr / bc1)
+    return param
