@@ -1,0 +1,452 @@
+// Fused add+RMSNorm (forward/backward) and per-head q/k RMSNorm fused with NeoX rotary embedding
+// (forward/backward) for sm_100a: 16-byte vector accesses, fp32 math on bf16 storage, one warp per
+// row (or per head).  They replace the Triton kernels of the reference
+// (fla/modules/layernorm.py:254-526, fla/modules/rotary.py:35-135).
+
+#include "common.cuh"
+
+#include <algorithm>
+
+namespace ttcd {
+
+struct alignas(16) Vec8 {
+  uint4 raw;
+  __device__ __forceinline__ void load(const bf16* p) { raw = *reinterpret_cast<const uint4*>(p); }
+  __device__ __forceinline__ void store(bf16* p) const { *reinterpret_cast<uint4*>(p) = raw; }
+  __device__ __forceinline__ void to_float(float (&f)[8]) const {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 t = unpack_bf16(w[i]);
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  }
+  __device__ __forceinline__ void from_float(const float (&f)[8]) {
+    raw.x = pack_bf16(f[0], f[1]);
+    raw.y = pack_bf16(f[2], f[3]);
+    raw.z = pack_bf16(f[4], f[5]);
+    raw.w = pack_bf16(f[6], f[7]);
+  }
+};
+
+// ------------------------------------------------------------------------------------------------
+// RMSNorm forward: s = x (+ res); y = s * rsqrt(mean(s^2) + eps) * w.  One warp per row.
+// ------------------------------------------------------------------------------------------------
+template <int CHUNKS>
+__global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res,
+                                                          const bf16* __restrict__ w, bf16* __restrict__ y,
+                                                          bf16* __restrict__ sum_out, float* __restrict__ rstd_out,
+                                                          int64_t rows, int D, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const bf16* xr = x + row * D;
+  float v[CHUNKS][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int col = (c * 32 + lane) * 8;
+    if (col < D) {
+      Vec8 a;
+      a.load(xr + col);
+      a.to_float(v[c]);
+      if (res != nullptr) {
+        Vec8 b;
+        float r[8];
+        b.load(res + row * D + col);
+        b.to_float(r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[c][i] += r[i];
+      }
+      if (sum_out != nullptr) {
+        Vec8 o;
+        o.from_float(v[c]);
+        o.store(sum_out + row * D + col);
+        // statistics use the stored (rounded) residual so forward and backward see the same input
+        o.to_float(v[c]);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += v[c][i] * v[c][i];
+    }
+  }
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss / D + eps);
+  if (lane == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int col = (c * 32 + lane) * 8;
+    if (col < D) {
+      float wv[8];
+      if (w != nullptr) {
+        Vec8 ww;
+        ww.load(w + col);
+        ww.to_float(wv);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) wv[i] = 1.f;
+      }
+      float o[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = v[c][i] * rstd * wv[i];
+      Vec8 ov;
+      ov.from_float(o);
+      ov.store(y + row * D + col);
+    }
+  }
+}
+
+// RMSNorm backward.  s: the (summed) pre-norm input saved by the forward.  dx = dnorm(dy) (+ dres).
+// dw partial sums are written per block to dw_partial[gridDim.x][D].
+template <int CHUNKS>
+__global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ s,
+                                                          const bf16* __restrict__ w, const float* __restrict__ rstd_in,
+                                                          const bf16* __restrict__ dres, bf16* __restrict__ dx,
+                                                          float* __restrict__ dw_partial, int64_t rows, int D) {
+  extern __shared__ float red[];  // [warps][D]
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int warps = blockDim.x >> 5;
+  float wv[CHUNKS][8];
+  float dwacc[CHUNKS][8];
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int col = (c * 32 + lane) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { dwacc[c][i] = 0.f; wv[c][i] = 1.f; }
+    if (col < D && w != nullptr) {
+      Vec8 ww;
+      ww.load(w + col);
+      ww.to_float(wv[c]);
+    }
+  }
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * warps + warp; row < rows;
+       row += static_cast<int64_t>(gridDim.x) * warps) {
+    const float rstd = rstd_in[row];
+    float g[CHUNKS][8], xh[CHUNKS][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int col = (c * 32 + lane) * 8;
+      if (col < D) {
+        Vec8 a, b;
+        a.load(dy + row * D + col);
+        b.load(s + row * D + col);
+        a.to_float(g[c]);
+        b.to_float(xh[c]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xh[c][i] *= rstd;
+          dwacc[c][i] += g[c][i] * xh[c][i];
+          g[c][i] *= wv[c][i];
+          dot += g[c][i] * xh[c][i];
+        }
+      }
+    }
+    dot = warp_sum(dot) / D;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int col = (c * 32 + lane) * 8;
+      if (col < D) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = rstd * (g[c][i] - xh[c][i] * dot);
+        if (dres != nullptr) {
+          Vec8 r;
+          float rf[8];
+          r.load(dres + row * D + col);
+          r.to_float(rf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += rf[i];
+        }
+        Vec8 ov;
+        ov.from_float(o);
+        ov.store(dx + row * D + col);
+      }
+    }
+  }
+  if (dw_partial == nullptr) return;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int col = (c * 32 + lane) * 8;
+    if (col < D) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) red[warp * D + col + i] = dwacc[c][i];
+    }
+  }
+  __syncthreads();
+  for (int col = threadIdx.x; col < D; col += blockDim.x) {
+    float acc = 0.f;
+    for (int wi = 0; wi < warps; ++wi) acc += red[wi * D + col];
+    dw_partial[static_cast<int64_t>(blockIdx.x) * D + col] = acc;
+  }
+}
+
+
+// ------------------------------------------------------------------------------------------------
+// Per-head RMSNorm (optional) + NeoX rotary.  One warp per (token, head); q heads then k heads.
+// Lane l handles the rotary pairs (l + 32 i, l + 32 i + half).
+// ------------------------------------------------------------------------------------------------
+struct QKRopeParams {
+  const bf16* q_in; const bf16* k_in; int64_t ldq, ldk;     // pre-norm inputs (strided rows)
+  bf16* q_out; bf16* k_out; int64_t ldqo, ldko;              // forward: outputs; backward: dx
+  const bf16* dq; const bf16* dk; int64_t lddq, lddk;        // backward: incoming gradients
+  const bf16* qw; const bf16* kw;                             // norm weights [D] or null
+  const bf16* cos; const bf16* sin;                           // [max_pos, half] or null
+  const int* positions;                                       // [rows] or null
+  int64_t rows; int T; int pos_offset; int H, HK, D, half; float eps;
+  float* dqw_partial; float* dkw_partial;                     // backward: [gridDim.x][D] or null
+};
+
+template <int MAXP>
+__global__ void __launch_bounds__(256) qk_norm_rope_fwd_kernel(const QKRopeParams p) {
+  const int lane = threadIdx.x & 31;
+  const int warps = blockDim.x >> 5;
+  const int heads = p.H + p.HK;
+  const int64_t total = p.rows * heads;
+  for (int64_t item = static_cast<int64_t>(blockIdx.x) * warps + (threadIdx.x >> 5); item < total;
+       item += static_cast<int64_t>(gridDim.x) * warps) {
+    const int64_t row = item / heads;
+    const int h = static_cast<int>(item % heads);
+    const bool is_q = h < p.H;
+    const int hh = is_q ? h : h - p.H;
+    const bf16* in = (is_q ? p.q_in + row * p.ldq : p.k_in + row * p.ldk) + hh * p.D;
+    bf16* out = (is_q ? p.q_out + row * p.ldqo : p.k_out + row * p.ldko) + hh * p.D;
+    const bf16* w = is_q ? p.qw : p.kw;
+    const int pos = p.positions != nullptr ? p.positions[row] : static_cast<int>(row % p.T) + p.pos_offset;
+    float x1[MAXP], x2[MAXP];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXP; ++i) {
+      const int idx = lane + 32 * i;
+      x1[i] = x2[i] = 0.f;
+      if (idx < p.half) {
+        x1[i] = __bfloat162float(in[idx]);
+        x2[i] = __bfloat162float(in[idx + p.half]);
+        ss += x1[i] * x1[i] + x2[i] * x2[i];
+      }
+    }
+    float rstd = 1.f;
+    if (w != nullptr) rstd = rsqrtf(warp_sum(ss) / p.D + p.eps);
+#pragma unroll
+    for (int i = 0; i < MAXP; ++i) {
+      const int idx = lane + 32 * i;
+      if (idx < p.half) {
+        float y1 = x1[i] * rstd, y2 = x2[i] * rstd;
+        if (w != nullptr) {
+          y1 *= __bfloat162float(w[idx]);
+          y2 *= __bfloat162float(w[idx + p.half]);
+        }
+        float c = 1.f, s = 0.f;
+        if (p.cos != nullptr) {
+          c = __bfloat162float(p.cos[static_cast<int64_t>(pos) * p.half + idx]);
+          s = __bfloat162float(p.sin[static_cast<int64_t>(pos) * p.half + idx]);
+        }
+        out[idx] = __float2bfloat16(y1 * c - y2 * s);
+        out[idx + p.half] = __float2bfloat16(y1 * s + y2 * c);
+      }
+    }
+  }
+}
+
+template <int MAXP>
+__global__ void __launch_bounds__(256) qk_norm_rope_bwd_kernel(const QKRopeParams p) {
+  __shared__ float red[2][8][256];  // [q|k][warp][D <= 256]
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int warps = blockDim.x >> 5;
+  const int heads = p.H + p.HK;
+  const int64_t total = p.rows * heads;
+  float dwq1[MAXP], dwq2[MAXP], dwk1[MAXP], dwk2[MAXP];
+#pragma unroll
+  for (int i = 0; i < MAXP; ++i) dwq1[i] = dwq2[i] = dwk1[i] = dwk2[i] = 0.f;
+
+  for (int64_t item = static_cast<int64_t>(blockIdx.x) * warps + warp; item < total;
+       item += static_cast<int64_t>(gridDim.x) * warps) {
+    const int64_t row = item / heads;
+    const int h = static_cast<int>(item % heads);
+    const bool is_q = h < p.H;
+    const int hh = is_q ? h : h - p.H;
+    const bf16* in = (is_q ? p.q_in + row * p.ldq : p.k_in + row * p.ldk) + hh * p.D;
+    const bf16* gin = (is_q ? p.dq + row * p.lddq : p.dk + row * p.lddk) + hh * p.D;
+    bf16* out = (is_q ? p.q_out + row * p.ldqo : p.k_out + row * p.ldko) + hh * p.D;
+    const bf16* w = is_q ? p.qw : p.kw;
+    const int pos = p.positions != nullptr ? p.positions[row] : static_cast<int>(row % p.T) + p.pos_offset;
+    float x1[MAXP], x2[MAXP], g1[MAXP], g2[MAXP];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXP; ++i) {
+      const int idx = lane + 32 * i;
+      x1[i] = x2[i] = g1[i] = g2[i] = 0.f;
+      if (idx < p.half) {
+        x1[i] = __bfloat162float(in[idx]);
+        x2[i] = __bfloat162float(in[idx + p.half]);
+        ss += x1[i] * x1[i] + x2[i] * x2[i];
+        const float d1 = __bfloat162float(gin[idx]);
+        const float d2 = __bfloat162float(gin[idx + p.half]);
+        float c = 1.f, s = 0.f;
+        if (p.cos != nullptr) {
+          c = __bfloat162float(p.cos[static_cast<int64_t>(pos) * p.half + idx]);
+          s = __bfloat162float(p.sin[static_cast<int64_t>(pos) * p.half + idx]);
+        }
+        g1[i] = d1 * c + d2 * s;   // transpose of the rotation
+        g2[i] = -d1 * s + d2 * c;
+      }
+    }
+    if (w == nullptr) {
+#pragma unroll
+      for (int i = 0; i < MAXP; ++i) {
+        const int idx = lane + 32 * i;
+        if (idx < p.half) {
+          out[idx] = __float2bfloat16(g1[i]);
+          out[idx + p.half] = __float2bfloat16(g2[i]);
+        }
+      }
+      continue;
+    }
+    const float rstd = rsqrtf(warp_sum(ss) / p.D + p.eps);
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXP; ++i) {
+      const int idx = lane + 32 * i;
+      if (idx < p.half) {
+        x1[i] *= rstd;
+        x2[i] *= rstd;
+        if (is_q) { dwq1[i] += g1[i] * x1[i]; dwq2[i] += g2[i] * x2[i]; }
+        else      { dwk1[i] += g1[i] * x1[i]; dwk2[i] += g2[i] * x2[i]; }
+        g1[i] *= __bfloat162float(w[idx]);
+        g2[i] *= __bfloat162float(w[idx + p.half]);
+        dot += g1[i] * x1[i] + g2[i] * x2[i];
+      }
+    }
+    dot = warp_sum(dot) / p.D;
+#pragma unroll
+    for (int i = 0; i < MAXP; ++i) {
+      const int idx = lane + 32 * i;
+      if (idx < p.half) {
+        out[idx] = __float2bfloat16(rstd * (g1[i] - x1[i] * dot));
+        out[idx + p.half] = __float2bfloat16(rstd * (g2[i] - x2[i] * dot));
+      }
+    }
+  }
+  if (p.dqw_partial == nullptr) return;
+#pragma unroll
+  for (int i = 0; i < MAXP; ++i) {
+    const int idx = lane + 32 * i;
+    if (idx < p.half) {
+      red[0][warp][idx] = dwq1[i];
+      red[0][warp][idx + p.half] = dwq2[i];
+      red[1][warp][idx] = dwk1[i];
+      red[1][warp][idx + p.half] = dwk2[i];
+    }
+  }
+  __syncthreads();
+  for (int col = threadIdx.x; col < 2 * p.half; col += blockDim.x) {
+    float aq = 0.f, ak = 0.f;
+    for (int wi = 0; wi < warps; ++wi) { aq += red[0][wi][col]; ak += red[1][wi][col]; }
+    p.dqw_partial[static_cast<int64_t>(blockIdx.x) * p.D + col] = aq;
+    p.dkw_partial[static_cast<int64_t>(blockIdx.x) * p.D + col] = ak;
+  }
+}
+
+}  // namespace ttcd
+
+using namespace ttcd;
+
+// y = rmsnorm(x + res) * w.  res, w, sum_out, rstd may be null.  D % 8 == 0, D <= 2048.
+TTCD_EXPORT int ttcd_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* sum_out, float* rstd,
+                                 long long rows, int D, float eps, void* stream_ptr) {
+  if (D % 8 != 0 || D > 2048 || rows <= 0) return TTCD_ERR_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream_ptr);
+  const int warps = 8;
+  const unsigned grid = static_cast<unsigned>((rows + warps - 1) / warps);
+  const int chunks = (D + 255) / 256;
+#define LAUNCH(C)                                                                                          \
+  rmsnorm_fwd_kernel<C><<<grid, warps * 32, 0, st>>>(static_cast<const bf16*>(x), static_cast<const bf16*>(res), \
+                                                     static_cast<const bf16*>(w), static_cast<bf16*>(y),       \
+                                                     static_cast<bf16*>(sum_out), rstd, rows, D, eps)
+  switch (chunks) {
+    case 1: LAUNCH(1); break;
+    case 2: LAUNCH(2); break;
+    case 3: LAUNCH(3); break;
+    case 4: LAUNCH(4); break;
+    case 5: case 6: LAUNCH(6); break;
+    default: LAUNCH(8); break;
+  }
+#undef LAUNCH
+  return static_cast<int>(cudaGetLastError());
+}
+
+// dx = rmsnorm_backward(dy; s, w, rstd) (+ dres).  dw_partial: [nblocks][D] fp32 or null.
+TTCD_EXPORT int ttcd_rmsnorm_bwd(const void* dy, const void* s, const void* w, const float* rstd, const void* dres,
+                                 void* dx, float* dw_partial, long long rows, int D, int nblocks, void* stream_ptr) {
+  if (D % 8 != 0 || D > 2048 || rows <= 0 || nblocks <= 0) return TTCD_ERR_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream_ptr);
+  const int warps = 8;
+  const size_t smem = static_cast<size_t>(warps) * D * sizeof(float);
+  const int chunks = (D + 255) / 256;
+#define LAUNCH(C)                                                                                           \
+  rmsnorm_bwd_kernel<C><<<nblocks, warps * 32, smem, st>>>(                                                 \
+      static_cast<const bf16*>(dy), static_cast<const bf16*>(s), static_cast<const bf16*>(w), rstd,          \
+      static_cast<const bf16*>(dres), static_cast<bf16*>(dx), dw_partial, rows, D)
+  if (smem > 48 * 1024) {
+    if (chunks <= 6) cudaFuncSetAttribute(rmsnorm_bwd_kernel<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    else cudaFuncSetAttribute(rmsnorm_bwd_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+  }
+  switch (chunks) {
+    case 1: LAUNCH(1); break;
+    case 2: LAUNCH(2); break;
+    case 3: LAUNCH(3); break;
+    case 4: LAUNCH(4); break;
+    case 5: case 6: LAUNCH(6); break;
+    default: LAUNCH(8); break;
+  }
+#undef LAUNCH
+  return static_cast<int>(cudaGetLastError());
+}
+
+static int qk_check(int D, int half) { return (D > 256 || half * 2 > D || half <= 0) ? TTCD_ERR_ARG : TTCD_OK; }
+
+// Forward: q_out/k_out = rope(headnorm(q_in/k_in)).  Row strides in elements.
+TTCD_EXPORT int ttcd_qk_norm_rope_fwd(const void* q_in, long long ldq, const void* k_in, long long ldk, void* q_out,
+                                      long long ldqo, void* k_out, long long ldko, const void* qw, const void* kw,
+                                      const void* cos, const void* sin, const int* positions, long long rows, int T,
+                                      int pos_offset, int H, int HK, int D, int half, float eps, void* stream_ptr) {
+  if (qk_check(D, half) != TTCD_OK || rows <= 0) return TTCD_ERR_ARG;
+  QKRopeParams p{};
+  p.q_in = static_cast<const bf16*>(q_in); p.k_in = static_cast<const bf16*>(k_in); p.ldq = ldq; p.ldk = ldk;
+  p.q_out = static_cast<bf16*>(q_out); p.k_out = static_cast<bf16*>(k_out); p.ldqo = ldqo; p.ldko = ldko;
+  p.qw = static_cast<const bf16*>(qw); p.kw = static_cast<const bf16*>(kw);
+  p.cos = static_cast<const bf16*>(cos); p.sin = static_cast<const bf16*>(sin); p.positions = positions;
+  p.rows = rows; p.T = T; p.pos_offset = pos_offset; p.H = H; p.HK = HK; p.D = D; p.half = half; p.eps = eps;
+  cudaStream_t st = static_cast<cudaStream_t>(stream_ptr);
+  const long long items = rows * (H + HK);
+  const unsigned grid = static_cast<unsigned>(std::min<long long>((items + 7) / 8, 148LL * 16));
+  if (half <= 32) qk_norm_rope_fwd_kernel<1><<<grid, 256, 0, st>>>(p);
+  else if (half <= 64) qk_norm_rope_fwd_kernel<2><<<grid, 256, 0, st>>>(p);
+  else qk_norm_rope_fwd_kernel<4><<<grid, 256, 0, st>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Backward: dq_in/dk_in (written to q_out/k_out slots) from gradients w.r.t. the rotated outputs.
+TTCD_EXPORT int ttcd_qk_norm_rope_bwd(const void* dq, long long lddq, const void* dk, long long lddk, const void* q_in,
+                                      long long ldq, const void* k_in, long long ldk, void* dq_in, long long ldqo,
+                                      void* dk_in, long long ldko, const void* qw, const void* kw, const void* cos,
+                                      const void* sin, const int* positions, float* dqw_partial, float* dkw_partial,
+                                      int nblocks, long long rows, int T, int pos_offset, int H, int HK, int D,
+                                      int half, float eps, void* stream_ptr) {
+  if (qk_check(D, half) != TTCD_OK || rows <= 0 || nblocks <= 0) return TTCD_ERR_ARG;
+  QKRopeParams p{};
+  p.q_in = static_cast<const bf16*>(q_in); p.k_in = static_cast<const bf16*>(k_in); p.ldq = ldq; p.ldk = ldk;
+  p.q_out = static_cast<bf16*>(dq_in); p.k_out = static_cast<bf16*>(dk_in); p.ldqo = ldqo; p.ldko = ldko;
+  p.dq = static_cast<const bf16*>(dq); p.dk = static_cast<const bf16*>(dk); p.lddq = lddq; p.lddk = lddk;
+  p.qw = static_cast<const bf16*>(qw); p.kw = static_cast<const bf16*>(kw);
+  p.cos = static_cast<const bf16*>(cos); p.sin = static_cast<const bf16*>(sin); p.positions = positions;
+  p.rows = rows; p.T = T; p.pos_offset = pos_offset; p.H = H; p.HK = HK; p.D = D; p.half = half; p.eps = eps;
+  p.dqw_partial = dqw_partial; p.dkw_partial = dkw_partial;
+  cudaStream_t st = static_cast<cudaStream_t>(stream_ptr);
+  if (half <= 32) qk_norm_rope_bwd_kernel<1><<<nblocks, 256, 0, st>>>(p);
+  else if (half <= 64) qk_norm_rope_bwd_kernel<2><<<nblocks, 256, 0, st>>>(p);
+  else qk_norm_rope_bwd_kernel<4><<<nblocks, 256, 0, st>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -1,0 +1,302 @@
+"""Numerics of every hand-written kernel against the fp32 PyTorch statement of the same op."""
+import math
+
+import pytest
+import torch
+
+from ttcd_b200 import _native, ops
+from ttcd_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+BF = torch.bfloat16
+
+
+@pytest.fixture(autouse=True)
+def _native_required():
+    _native.load(required=True)
+    yield
+    torch.cuda.synchronize()
+    assert _native.device_status() == 0, "a bounded device wait expired"
+
+
+def _close(got, want, atol, rtol, name=""):
+    got, want = got.float(), want.float()
+    err = (got - want).abs()
+    tol = atol + rtol * want.abs()
+    bad = (err > tol).float().mean().item()
+    assert bad == 0.0, f"{name}: max err {err.max().item():.4g}, {bad * 100:.3f}% outside tol, ref max {want.abs().max().item():.4g}"
+
+
+# ------------------------------------------------------------------------------------------- GEMM
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 256, 128), (384, 320, 192), (1000, 1160, 1032), (4096, 1024, 1024)])
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+def test_gemm_layouts(M, N, K, ta, tb):
+    from ttcd_b200.ops import cuda
+    a = torch.randn((K, M) if ta else (M, K), device=DEV, dtype=BF)
+    b = torch.randn((N, K) if tb else (K, N), device=DEV, dtype=BF)
+    a_l = a.t() if ta else a
+    b_l = b.t() if tb else b
+    got = cuda.gemm(a_l, b_l).view(M, N)
+    want = a_l.float() @ b_l.float()
+    _close(got, want, atol=0.02 * math.sqrt(K), rtol=1.6e-2, name=f"gemm {M}x{N}x{K} ta={ta} tb={tb}")
+
+
+def test_gemm_batched_fp32_accumulate_rowscale():
+    from ttcd_b200.ops import cuda
+    Bt, M, N, K = 3, 256, 384, 512
+    a = torch.randn(Bt, K, M, device=DEV, dtype=BF)
+    b = torch.randn(Bt, K, N, device=DEV, dtype=BF)
+    c = torch.randn(Bt, M, N, device=DEV, dtype=torch.float32)
+    rs = torch.rand(Bt * M, device=DEV, dtype=BF)
+    want = 0.5 * rs.float().view(Bt, M, 1) * (a.float().transpose(1, 2) @ b.float()) + 2.0 * c
+    got = cuda.gemm(a.transpose(1, 2), b, alpha=0.5, beta=2.0, c_in=c, row_scale=rs, out=c.clone())
+    _close(got, want, atol=0.3, rtol=1e-2, name="batched gemm")
+
+
+def test_matmul_autograd():
+    a = torch.randn(2, 3, 256, 192, device=DEV, dtype=BF, requires_grad=True)
+    b = torch.randn(192, 320, device=DEV, dtype=BF, requires_grad=True)
+    out = ops.matmul(a, b)
+    g = torch.randn_like(out)
+    out.backward(g)
+    af, bf_ = a.detach().float().requires_grad_(), b.detach().float().requires_grad_()
+    (af @ bf_).backward(g.float())
+    _close(out, af @ bf_, 0.3, 1.6e-2, "matmul fwd")
+    _close(a.grad, af.grad, 0.4, 1.6e-2, "matmul da")
+    _close(b.grad, bf_.grad, 1.5, 1.6e-2, "matmul db")
+
+
+def test_linear_and_fused_linear_autograd():
+    from ttcd_b200.models.layers import _slab_view
+    x = torch.randn(2, 200, 256, device=DEV, dtype=BF, requires_grad=True)
+    flat = torch.randn((384 + 128 + 128) * 256, device=DEV, dtype=BF) * 0.05
+    ws = [flat[: 384 * 256].view(384, 256), flat[384 * 256: 512 * 256].view(128, 256), flat[512 * 256:].view(128, 256)]
+    ws = [w.detach().requires_grad_() for w in ws]
+    from ttcd_b200.ops import cuda
+    outs = cuda.fused_linear(x, ws, _slab_view(ws))
+    loss = sum((o.float() * (i + 1)).sum() for i, o in enumerate(outs))
+    loss.backward()
+    xf = x.detach().float().requires_grad_()
+    wf = [w.detach().float().requires_grad_() for w in ws]
+    ref_outs = [xf @ w.t() for w in wf]
+    sum((o * (i + 1)).sum() for i, o in enumerate(ref_outs)).backward()
+    for o, r in zip(outs, ref_outs):
+        _close(o, r, 0.05, 1.6e-2, "fused linear fwd")
+    _close(x.grad, xf.grad, 0.3, 2e-2, "fused linear dx")
+    for w, r in zip(ws, wf):
+        _close(w.grad, r.grad, 1.0, 2e-2, "fused linear dw")
+
+
+# ----------------------------------------------------------------------------------- elementwise
+
+@pytest.mark.parametrize("D", [128, 960, 1024, 2048])
+def test_rmsnorm_fwd_bwd(D):
+    x = torch.randn(3, 77, D, device=DEV, dtype=BF, requires_grad=True)
+    r = torch.randn(3, 77, D, device=DEV, dtype=BF, requires_grad=True)
+    w = (torch.randn(D, device=DEV) * 0.1 + 1).to(BF).requires_grad_()
+    y, s = ops.rmsnorm(x, w, 1e-6, residual=r, prenorm=True)
+    gy, gs = torch.randn_like(y), torch.randn_like(s)
+    torch.autograd.backward([y, s], [gy, gs])
+    xf, rf, wf = (t.detach().float().requires_grad_() for t in (x, r, w))
+    yr, sr = ref.rmsnorm(xf, wf, 1e-6, residual=rf, prenorm=True)
+    torch.autograd.backward([yr, sr], [gy.float(), gs.float()])
+    _close(y, yr, 2e-2, 1e-2, "rmsnorm y")
+    _close(s, sr, 2e-2, 1e-2, "rmsnorm sum")
+    _close(x.grad, xf.grad, 4e-2, 2e-2, "rmsnorm dx")
+    _close(r.grad, rf.grad, 4e-2, 2e-2, "rmsnorm dres")
+    _close(w.grad, wf.grad, 0.3, 3e-2, "rmsnorm dw")
+
+
+def test_rmsnorm_dual():
+    D = 1024
+    a_t, a_s, r = (torch.randn(2, 50, D, device=DEV, dtype=BF, requires_grad=True) for _ in range(3))
+    w = torch.ones(D, device=DEV, dtype=BF, requires_grad=True)
+    outs = ops.rmsnorm_dual(a_t, a_s, r, w, 1e-6)
+    gs = [torch.randn_like(o) for o in outs]
+    torch.autograd.backward(outs, gs)
+    f = [t.detach().float().requires_grad_() for t in (a_t, a_s, r, w)]
+    outs_r = ref.rmsnorm_dual(f[0], f[1], f[2], f[3], 1e-6)
+    torch.autograd.backward(outs_r, [g.float() for g in gs])
+    for o, o_r in zip(outs, outs_r):
+        _close(o, o_r, 3e-2, 1e-2, "dual fwd")
+    for t, t_r, n in zip((a_t, a_s, r), f[:3], ("da_t", "da_s", "dres")):
+        _close(t.grad, t_r.grad, 6e-2, 2e-2, n)
+    _close(w.grad, f[3].grad, 0.5, 3e-2, "dual dw")
+
+
+@pytest.mark.parametrize("H,HK,D,norm", [(4, 2, 128, True), (15, 5, 64, False), (2, 2, 128, False)])
+def test_qk_norm_rope(H, HK, D, norm):
+    B, T = 2, 130
+    qkv = torch.randn(B, T, (H + 2 * HK) * D, device=DEV, dtype=BF, requires_grad=True)
+    q = qkv[..., : H * D].view(B, T, H, D)
+    k = qkv[..., H * D: (H + HK) * D].view(B, T, HK, D)
+    qw = (torch.rand(D, device=DEV) + 0.5).to(BF).requires_grad_() if norm else None
+    kw = (torch.rand(D, device=DEV) + 0.5).to(BF).requires_grad_() if norm else None
+    cos, sin = ref.rope_tables(D, 10000.0, 512, device=DEV, dtype=BF)
+    qo, ko = ops.qkv_norm_rope(q, k, qw, kw, 1e-5, cos, sin, offset=7)
+    gq, gk = torch.randn_like(qo), torch.randn_like(ko)
+    torch.autograd.backward([qo, ko], [gq, gk])
+    qkv_f = qkv.detach().float().requires_grad_()
+    qf = qkv_f[..., : H * D].view(B, T, H, D)
+    kf = qkv_f[..., H * D: (H + HK) * D].view(B, T, HK, D)
+    qwf = qw.detach().float().requires_grad_() if norm else None
+    kwf = kw.detach().float().requires_grad_() if norm else None
+    if norm:
+        qf, kf = ref.rmsnorm(qf, qwf, 1e-5), ref.rmsnorm(kf, kwf, 1e-5)
+    qr, kr = ref.rope(qf, cos, sin, 7), ref.rope(kf, cos, sin, 7)
+    torch.autograd.backward([qr, kr], [gq.float(), gk.float()])
+    _close(qo, qr, 3e-2, 1.5e-2, "q rope")
+    _close(ko, kr, 3e-2, 1.5e-2, "k rope")
+    _close(qkv.grad, qkv_f.grad, 6e-2, 3e-2, "dqkv")
+    if norm:
+        _close(qw.grad, qwf.grad, 1.0, 5e-2, "dqw")
+        _close(kw.grad, kwf.grad, 1.0, 5e-2, "dkw")
+
+
+def test_swiglu():
+    gu = torch.randn(300, 2 * 768, device=DEV, dtype=BF, requires_grad=True)
+    z = ops.swiglu_packed(gu)
+    g = torch.randn_like(z)
+    z.backward(g)
+    guf = gu.detach().float().requires_grad_()
+    zr = ref.swiglu(guf[:, :768], guf[:, 768:])
+    zr.backward(g.float())
+    _close(z, zr, 2e-2, 1e-2, "swiglu")
+    _close(gu.grad, guf.grad, 4e-2, 2e-2, "swiglu grad")
+
+
+@pytest.mark.parametrize("K,causal,C", [(5, True, 96), (4, True, 64), (5, False, 130), (3, True, 17)])
+def test_dwconv(K, causal, C):
+    x = torch.randn(2, 3, C, 384, device=DEV, dtype=BF, requires_grad=True)
+    w = (torch.randn(384, K, device=DEV) * 0.5).to(BF).requires_grad_()
+    y = ops.dwconv_chunked(x, w, causal)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = ref.dwconv_chunked(xf, wf, causal)
+    yr.backward(g.float())
+    _close(y, yr, 3e-2, 1e-2, "dwconv y")
+    _close(x.grad, xf.grad, 5e-2, 2e-2, "dwconv dx")
+    _close(w.grad, wf.grad, 0.8, 3e-2, "dwconv dw")
+
+
+def test_cross_entropy_rows():
+    V = 5000 * 8
+    logits = (torch.randn(300, V, device=DEV) * 3).to(BF).requires_grad_()
+    labels = torch.randint(0, V, (300,), device=DEV)
+    labels[::7] = -100
+    loss = ops.cross_entropy(logits, labels)
+    loss.backward()
+    lf = logits.detach().float().requires_grad_()
+    lr = ref.cross_entropy(lf, labels)
+    lr.backward()
+    assert abs(loss.item() - lr.item()) < 2e-3 * max(1.0, abs(lr.item()))
+    _close(logits.grad, lf.grad, 2e-5, 2e-2, "dlogits")
+
+
+def test_linear_cross_entropy():
+    N, Hd, V = 700, 256, 4096
+    h = (torch.randn(N, Hd, device=DEV) * 0.5).to(BF).requires_grad_()
+    w = (torch.randn(V, Hd, device=DEV) * 0.1).to(BF).requires_grad_()
+    labels = torch.randint(0, V, (N,), device=DEV)
+    labels[-1] = -100
+    loss = ops.linear_cross_entropy(h, labels, w, num_chunks=3)
+    loss.backward()
+    hf, wf = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    lr = ref.cross_entropy(hf @ wf.t(), labels)
+    lr.backward()
+    assert abs(loss.item() - lr.item()) < 5e-3 * abs(lr.item())
+    _close(h.grad, hf.grad, 3e-5, 5e-2, "lce dh")
+    _close(w.grad, wf.grad, 3e-5, 5e-2, "lce dw")
+
+
+def test_adamw_and_sumsq():
+    from ttcd_b200.ops import cuda
+    n = 100_003
+    p = torch.randn(n, device=DEV)
+    g = torch.randn(n, device=DEV).to(BF)
+    m, v = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    pr, mr, vr = p.clone(), m.clone(), v.clone()
+    pb = torch.empty(n, device=DEV, dtype=BF)
+    coef = torch.tensor([0.5], device=DEV)
+    for step in (1, 2, 3):
+        cuda.adamw_step(p, g, m, v, pb, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-15, weight_decay=0.1, step=step, coef=coef)
+        ref.adamw_step(pr, g, mr, vr, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-15, weight_decay=0.1, step=step, grad_scale=0.5)
+    _close(p, pr, 1e-5, 1e-4, "adamw p")
+    _close(pb, pr, 1e-2, 1e-2, "adamw bf16 copy")
+    out = torch.zeros(1, device=DEV)
+    cuda.sumsq(g, out)
+    assert abs(out.item() - g.float().pow(2).sum().item()) < 1e-3 * out.item()
+
+
+def test_newton_schulz():
+    g = torch.randn(2, 256, 512, device=DEV, dtype=BF)
+    got = ops.newton_schulz(g)
+    want = ref.newton_schulz(g.float(), dtype=torch.float32)
+    _close(got, want, 0.06, 0.1, "newton-schulz")
+
+
+# ------------------------------------------------------------------------------------- attention fwd
+
+def _attn_inputs(B, T, H, HK, D, scale=1.0, Tk=None):
+    Tk = T if Tk is None else Tk
+    q = (torch.randn(B, T, H, D, device=DEV) * scale).to(BF)
+    k = (torch.randn(B, Tk, HK, D, device=DEV) * scale).to(BF)
+    v = torch.randn(B, Tk, HK, D, device=DEV).to(BF)
+    return q, k, v
+
+
+ATTN_TOL = dict(atol=8e-3, rtol=1e-2)
+
+
+@pytest.mark.parametrize("T,H,HK,D,W", [(128, 2, 1, 128, None), (257, 4, 2, 128, 100), (513, 2, 2, 64, 192),
+                                         (769, 3, 1, 128, 64), (1024, 4, 4, 128, 1024), (2000, 2, 1, 64, None)])
+def test_attention_single_window_fwd(T, H, HK, D, W):
+    from ttcd_b200.ops import cuda
+    q, k, v = _attn_inputs(2, T, H, HK, D)
+    with torch.no_grad():
+        _, o, _, lse, _ = cuda.attn_forward(q, k, v, W, W, D ** -0.5, False)
+    o_r, lse_r = ref.attention(q, k, v, W, return_lse=True)
+    _close(o, o_r, name="attn o", **ATTN_TOL)
+    _close(lse, lse_r, 2e-2, 1e-3, "attn lse")
+
+
+@pytest.mark.parametrize("T,H,HK,D,WT,WS", [(512, 2, 1, 128, 256, 128), (1000, 4, 2, 128, 400, 200),
+                                             (769, 3, 3, 64, 300, 150), (1536, 2, 1, 128, None, 256),
+                                             (700, 2, 2, 128, 256, 256), (900, 2, 1, 128, 320, 288),
+                                             (4097, 2, 1, 128, 2048, 1024)])
+def test_attention_dual_window_fwd(T, H, HK, D, WT, WS):
+    from ttcd_b200.ops import cuda
+    q, k, v = _attn_inputs(1, T, H, HK, D)
+    with torch.no_grad():
+        _, o_t, o_s, lse_t, lse_s = cuda.attn_forward(q, k, v, WT, WS, D ** -0.5, True)
+    r_t, l_t = ref.attention(q, k, v, WT, return_lse=True)
+    r_s, l_s = ref.attention(q, k, v, WS, return_lse=True)
+    _close(o_s, r_s, name="student o", **ATTN_TOL)
+    _close(o_t, r_t, name="teacher o", **ATTN_TOL)
+    _close(lse_t, l_t, 2e-2, 1e-3, "teacher lse")
+    _close(lse_s, l_s, 2e-2, 1e-3, "student lse")
+
+
+@pytest.mark.parametrize("qk_scale", [0.0, 0.5, 4.0, 16.0])
+def test_attention_scale_stress(qk_scale):
+    from ttcd_b200.ops import cuda
+    q, k, v = _attn_inputs(1, 640, 2, 1, 128, scale=qk_scale)
+    with torch.no_grad():
+        _, o_t, o_s, _, _ = cuda.attn_forward(q, k, v, 256, 128, 128 ** -0.5, True)
+    r_t, r_s = ref.dual_window_attention(q, k, v, 256, 128)
+    _close(o_t, r_t, name="teacher", **ATTN_TOL)
+    _close(o_s, r_s, name="student", **ATTN_TOL)
+
+
+def test_attention_cached_prefill_tq_lt_tk():
+    from ttcd_b200.ops import cuda
+    q, k, v = _attn_inputs(1, 200, 2, 1, 128, Tk=712)
+    with torch.no_grad():
+        _, o_t, o_s, _, _ = cuda.attn_forward(q, k, v, 512, 256, 128 ** -0.5, True)
+    r_t, r_s = ref.dual_window_attention(q, k, v, 512, 256)
+    _close(o_t, r_t, name="teacher", **ATTN_TOL)
+    _close(o_s, r_s, name="student", **ATTN_TOL)

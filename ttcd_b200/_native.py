@@ -120,8 +120,15 @@ def f32(v) -> ctypes.c_float:
 
 def device_status(reset: bool = True) -> int:
     """Read (and clear) the device-side error word written by bounded waits."""
-    if not has("ttcd_read_status"):
+    lib = load()
+    if lib is None:
         return 0
-    lib = load(required=True)
-    lib.ttcd_read_status.restype = ctypes.c_int
-    return int(lib.ttcd_read_status(ctypes.c_int(1 if reset else 0)))
+    status = 0
+    for unit in ("gemm", "attn", "comm"):
+        fn = getattr(lib, f"ttcd_read_status_{unit}", None)
+        if fn is None:
+            continue
+        fn.restype = ctypes.c_int
+        v = int(fn(ctypes.c_int(1 if reset else 0)))
+        status = status or v
+    return status

@@ -1,0 +1,742 @@
+"""Autograd Functions and launch wrappers for the hand-written sm_100a kernels.
+
+Every function here takes CUDA bf16 tensors and calls ``libttcd_b200.so`` through
+``ttcd_b200._native``; forward and backward both run on the native kernels.  Shapes are
+validated on the host before a launch (the kernels do no bounds recovery).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import _native as nv
+from . import reference
+
+_BF16 = torch.bfloat16
+_SM_BLOCKS = 148 * 2
+
+
+def _check(t: torch.Tensor, name: str):
+    if not (t.is_cuda and t.dtype == _BF16):
+        raise TypeError(f"{name} must be a CUDA bf16 tensor, got {t.dtype} on {t.device}")
+
+
+def _rows2d(x: torch.Tensor) -> torch.Tensor:
+    return x.reshape(-1, x.shape[-1])
+
+
+def _dense_rows(x: torch.Tensor) -> torch.Tensor:
+    """2-D view with unit inner stride and a 16-byte aligned row stride (copy only if needed)."""
+    x2 = _rows2d(x)
+    if x2.stride(-1) != 1 or (x2.stride(0) % 8) or (x2.data_ptr() % 16):
+        x2 = x2.contiguous()
+    return x2
+
+
+# =============================================================================================
+# GEMM
+# =============================================================================================
+
+def _operand(t: torch.Tensor):
+    """Describe a [.., R, C] matrix for the kernel: (tensor, is_row_major, ld, batch_stride)."""
+    if t.dim() == 2:
+        t = t.unsqueeze(0)
+    if t.dim() > 3:
+        t = t.reshape(-1, t.shape[-2], t.shape[-1]) if t.is_contiguous() else t.contiguous().view(-1, *t.shape[-2:])
+    ok_row = t.stride(-1) == 1 and t.stride(-2) % 8 == 0 and t.stride(-2) >= t.shape[-1]
+    ok_col = t.stride(-2) == 1 and t.stride(-1) % 8 == 0 and t.stride(-1) >= t.shape[-2]
+    if t.shape[-1] == 1 and t.shape[-2] == 1:
+        ok_row, ok_col = False, False
+    if not (ok_row or ok_col) or t.data_ptr() % 16 or (t.shape[0] > 1 and t.stride(0) % 8):
+        t = t.contiguous()
+        ok_row, ok_col = True, False
+    row_major = ok_row
+    ld = t.stride(-2) if row_major else t.stride(-1)
+    return t, row_major, ld, (t.stride(0) if t.shape[0] > 1 else 0)
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, out_dtype=_BF16, alpha: float = 1.0, beta: float = 0.0,
+         c_in: torch.Tensor | None = None, row_scale: torch.Tensor | None = None,
+         out: torch.Tensor | None = None) -> torch.Tensor:
+    """C[.., M, N] = alpha * rowscale * (a[.., M, K] @ b[.., K, N]) + beta * c_in.
+
+    ``a`` / ``b`` may be transposed views: a row-major a is a K-major A operand, a column-major a
+    (i.e. ``x.transpose(-1, -2)`` of a row-major tensor) is MN-major; b row-major [K, N] is an
+    MN-major B operand, b = w.transpose(-1, -2) of row-major w [N, K] is K-major.
+    """
+    _check(a, "a"), _check(b, "b")
+    a3, a_row, lda, sa = _operand(a)
+    b3, b_row, ldb, sb = _operand(b)
+    batch = max(a3.shape[0], b3.shape[0])
+    M, K = a3.shape[-2], a3.shape[-1]
+    K2, N = b3.shape[-2], b3.shape[-1]
+    if K != K2:
+        raise ValueError(f"gemm shape mismatch: {tuple(a.shape)} @ {tuple(b.shape)}")
+    if a3.shape[0] not in (1, batch) or b3.shape[0] not in (1, batch):
+        raise ValueError("gemm batch mismatch")
+    if a3.shape[0] == 1:
+        sa = 0
+    if b3.shape[0] == 1:
+        sb = 0
+    if out is None:
+        out = torch.empty((batch, M, N), dtype=out_dtype, device=a.device)
+    c3 = out.view(batch, M, N) if out.dim() != 3 else out
+    if c3.stride(-1) != 1:
+        raise ValueError("gemm output must be row-major")
+    if c_in is not None:
+        c_in3 = c_in.view(batch, M, N) if c_in.dim() != 3 else c_in
+        if c_in3.stride() != c3.stride() or c_in3.dtype != c3.dtype:
+            raise ValueError("c_in must match the output layout and dtype")
+    a_mn = 0 if a_row else 1           # A logical [M, K]: row-major => K-major
+    b_mn = 1 if b_row else 0           # B given as [K, N]: row-major => N contiguous => MN-major
+    nv.call(
+        "ttcd_gemm_bf16", nv.ptr(a3), nv.ptr(b3), nv.ptr(c3), nv.ptr(c_in if c_in is not None else None),
+        nv.ptr(row_scale), nv.i64(M), nv.i64(N), nv.i64(K), nv.i64(batch), nv.i64(lda), nv.i64(ldb),
+        nv.i64(c3.stride(-2)), nv.i64(sa), nv.i64(sb), nv.i64(c3.stride(0) if batch > 1 else M * c3.stride(-2)),
+        nv.i32(a_mn), nv.i32(b_mn), nv.i32(1 if c3.dtype == torch.float32 else 0), nv.f32(alpha), nv.f32(beta),
+        nv.stream_ptr())
+    return out
+
+
+class _MatMul(torch.autograd.Function):
+    """Batched a @ b with native forward and backward."""
+
+    @staticmethod
+    def forward(ctx, a, b):
+        ctx.save_for_backward(a, b)
+        out_shape = torch.broadcast_shapes(a.shape[:-2], b.shape[:-2]) + (a.shape[-2], b.shape[-1])
+        return gemm(a, b).view(out_shape)
+
+    @staticmethod
+    def backward(ctx, g):
+        a, b = ctx.saved_tensors
+        ga = gb = None
+        g = g if g.dtype == _BF16 else g.to(_BF16)
+        if ctx.needs_input_grad[0]:
+            ga = gemm(g, b.transpose(-1, -2))
+            ga = _reduce_to(ga.view(torch.broadcast_shapes(g.shape[:-2], b.shape[:-2]) + ga.shape[-2:]), a.shape)
+        if ctx.needs_input_grad[1]:
+            gb = gemm(a.transpose(-1, -2), g)
+            gb = _reduce_to(gb.view(torch.broadcast_shapes(g.shape[:-2], a.shape[:-2]) + gb.shape[-2:]), b.shape)
+        return ga, gb
+
+
+def _reduce_to(t: torch.Tensor, shape) -> torch.Tensor:
+    """Sum broadcast batch dims so that t matches ``shape``."""
+    if tuple(t.shape) == tuple(shape):
+        return t
+    while t.dim() > len(shape):
+        t = t.sum(0)
+    for i, (ts, s) in enumerate(zip(t.shape, shape)):
+        if s == 1 and ts != 1:
+            t = t.sum(i, keepdim=True)
+    return t.reshape(shape)
+
+
+def matmul(a, b):
+    if a.dtype != _BF16:
+        a = a.to(_BF16)
+    if b.dtype != _BF16:
+        b = b.to(_BF16)
+    return _MatMul.apply(a, b)
+
+
+class _Linear(torch.autograd.Function):
+    """y = x @ W^T for one or several weights that share x (one GEMM when they form a slab)."""
+
+    @staticmethod
+    def forward(ctx, x, slab, *weights):
+        x2 = _dense_rows(x)
+        w = slab if slab is not None else (weights[0] if len(weights) == 1 else torch.cat(weights, dim=0))
+        ctx.save_for_backward(x2, w)
+        ctx.x_shape = x.shape
+        ctx.splits = [wi.shape[0] for wi in weights]
+        y = gemm(x2, w.transpose(0, 1)).view(x2.shape[0], w.shape[0])
+        if len(weights) == 1:
+            return y.view(*x.shape[:-1], w.shape[0])
+        outs, col = [], 0
+        for n in ctx.splits:
+            outs.append(y[:, col:col + n].view(*x.shape[:-1], n))
+            col += n
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        x2, w = ctx.saved_tensors
+        n_total = w.shape[0]
+        if len(grads) == 1:
+            g = _dense_rows(grads[0].to(_BF16))
+        elif (g := _adjacent_columns(grads, ctx.splits, n_total)) is not None:
+            pass  # the incoming gradients already sit side by side in one buffer
+        else:
+            # the outputs are column slices of one buffer; rebuild the packed gradient
+            g = torch.empty(x2.shape[0], n_total, dtype=_BF16, device=x2.device)
+            col = 0
+            for gi, n in zip(grads, ctx.splits):
+                if gi is None:
+                    g[:, col:col + n].zero_()
+                else:
+                    g[:, col:col + n].copy_(gi.reshape(-1, n))
+                col += n
+        gx = None
+        if ctx.needs_input_grad[0]:
+            gx = gemm(g, w).view(ctx.x_shape)
+        gw_all = gemm(g.transpose(0, 1), x2).view(n_total, x2.shape[1])
+        gws, row = [], 0
+        for n in ctx.splits:
+            gws.append(gw_all[row:row + n])
+            row += n
+        return (gx, None, *gws)
+
+
+def _adjacent_columns(grads, splits, n_total):
+    """If the gradients are consecutive column slices of one [rows, n_total] buffer, return it."""
+    if any(g is None or g.dtype != _BF16 for g in grads):
+        return None
+    try:
+        views = [g.view(-1, n) for g, n in zip(grads, splits)]
+    except RuntimeError:
+        return None
+    base = views[0]
+    expect = base.data_ptr()
+    for v, n in zip(views, splits):
+        if v.stride() != (n_total, 1) or v.data_ptr() != expect:
+            return None
+        expect += n * 2
+    if base.data_ptr() % 16:
+        return None
+    return torch.as_strided(base, (base.shape[0], n_total), (n_total, 1))
+
+
+def linear(x, weight, bias=None):
+    _check(x, "x")
+    w = weight if weight.dtype == _BF16 else weight.to(_BF16)
+    y = _Linear.apply(x, None, w)
+    return y if bias is None else y + bias.to(y.dtype)
+
+
+def fused_linear(x, weights, slab):
+    """Several projections of the same input; returns a tuple of column views of one output."""
+    ws = [w if w.dtype == _BF16 else w.to(_BF16) for w in weights]
+    if any(w.dtype != weights[i].dtype for i, w in enumerate(ws)):
+        slab = None
+    return _Linear.apply(x, slab, *ws)
+
+
+# =============================================================================================
+# RMSNorm
+# =============================================================================================
+
+def _rmsnorm_fwd(x2, res2, w, eps, want_sum):
+    rows, D = x2.shape
+    y = torch.empty_like(x2)
+    s = torch.empty_like(x2) if want_sum else None
+    rstd = torch.empty(rows, dtype=torch.float32, device=x2.device)
+    nv.call("ttcd_rmsnorm_fwd", nv.ptr(x2), nv.ptr(res2), nv.ptr(w), nv.ptr(y), nv.ptr(s), nv.ptr(rstd),
+            nv.i64(rows), nv.i32(D), nv.f32(eps), nv.stream_ptr())
+    return y, s, rstd
+
+
+def _rmsnorm_bwd(dy2, s2, w, rstd, dres2):
+    rows, D = dy2.shape
+    dx = torch.empty_like(dy2)
+    nblk = min(_SM_BLOCKS, (rows + 7) // 8)
+    dwp = torch.empty(nblk, D, dtype=torch.float32, device=dy2.device) if w is not None else None
+    nv.call("ttcd_rmsnorm_bwd", nv.ptr(dy2), nv.ptr(s2), nv.ptr(w), nv.ptr(rstd), nv.ptr(dres2), nv.ptr(dx),
+            nv.ptr(dwp), nv.i64(rows), nv.i32(D), nv.i32(nblk), nv.stream_ptr())
+    dw = dwp.sum(0) if dwp is not None else None
+    return dx, dw
+
+
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, residual, weight, eps, prenorm):
+        x2 = _rows2d(x).contiguous()
+        r2 = _rows2d(residual).contiguous() if residual is not None else None
+        w = None if weight is None else weight.to(_BF16).contiguous()
+        y, s, rstd = _rmsnorm_fwd(x2, r2, w, eps, want_sum=r2 is not None)
+        ctx.save_for_backward(s if s is not None else x2, w, rstd)
+        ctx.has_res = r2 is not None
+        ctx.prenorm = prenorm
+        ctx.wdtype = None if weight is None else weight.dtype
+        y = y.view(x.shape)
+        if prenorm:
+            return y, (s.view(x.shape) if s is not None else x)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy, dres_out=None):
+        s, w, rstd = ctx.saved_tensors
+        dy2 = _rows2d(dy).contiguous().to(_BF16)
+        dres2 = None
+        if ctx.prenorm and dres_out is not None:
+            dres2 = _rows2d(dres_out).contiguous().to(_BF16)
+        dx, dw = _rmsnorm_bwd(dy2, s, w, rstd, dres2)
+        dx = dx.view(dy.shape)
+        if dw is not None:
+            dw = dw.to(ctx.wdtype)
+        return dx, (dx if ctx.has_res else None), dw, None, None
+
+
+def rmsnorm(x, weight, eps, residual=None, prenorm=False):
+    _check(x, "x")
+    return _RMSNorm.apply(x, residual, weight, float(eps), bool(prenorm))
+
+
+class _RMSNormDual(torch.autograd.Function):
+    """x = norm(r + a_T), t = norm(r + a_S), r_out = r + a_T with one shared weight."""
+
+    @staticmethod
+    def forward(ctx, a_t, a_s, residual, weight, eps):
+        at2, as2, r2 = (_rows2d(v).contiguous() for v in (a_t, a_s, residual))
+        w = weight.to(_BF16).contiguous()
+        x, s_t, rstd_t = _rmsnorm_fwd(at2, r2, w, eps, True)
+        t, s_s, rstd_s = _rmsnorm_fwd(as2, r2, w, eps, True)
+        ctx.save_for_backward(s_t, s_s, w, rstd_t, rstd_s)
+        ctx.wdtype = weight.dtype
+        shp = a_t.shape
+        return x.view(shp), t.view(shp), s_t.view(shp)
+
+    @staticmethod
+    def backward(ctx, dx, dt, dres):
+        s_t, s_s, w, rstd_t, rstd_s = ctx.saved_tensors
+        shp = dx.shape
+        d_at, dw_t = _rmsnorm_bwd(_rows2d(dx).contiguous(), s_t, w, rstd_t,
+                                  None if dres is None else _rows2d(dres).contiguous())
+        d_as, dw_s = _rmsnorm_bwd(_rows2d(dt).contiguous(), s_s, w, rstd_s, None)
+        d_res = d_at + d_as
+        return d_at.view(shp), d_as.view(shp), d_res.view(shp), (dw_t + dw_s).to(ctx.wdtype), None
+
+
+def rmsnorm_dual(a_t, a_s, residual, weight, eps):
+    _check(a_t, "a_t")
+    return _RMSNormDual.apply(a_t, a_s, residual, weight, float(eps))
+
+
+# =============================================================================================
+# per-head q/k norm + rotary
+# =============================================================================================
+
+def _pos_arg(positions, rows, device):
+    if positions is None:
+        return None
+    pos = positions.to(device=device, dtype=torch.int32).reshape(-1)
+    if pos.numel() != rows:
+        pos = pos.expand(rows // pos.numel(), pos.numel()).reshape(-1)
+    return pos.contiguous()
+
+
+class _QKNormRope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, qw, kw, eps, cos, sin, offset, positions):
+        B, T, H, D = q.shape
+        HK = k.shape[2]
+        rows = B * T
+        if q.stride(-1) != 1 or q.stride(2) != D or k.stride(-1) != 1 or k.stride(2) != D:
+            q, k = q.contiguous(), k.contiguous()
+        ldq, ldk = q.stride(1), k.stride(1)
+        if (B > 1 and (q.stride(0) != T * ldq or k.stride(0) != T * ldk)):
+            q, k = q.contiguous(), k.contiguous()
+            ldq, ldk = q.stride(1), k.stride(1)
+        q_out = torch.empty(B, T, H, D, dtype=_BF16, device=q.device)
+        k_out = torch.empty(B, T, HK, D, dtype=_BF16, device=q.device)
+        qwb = None if qw is None else qw.to(_BF16).contiguous()
+        kwb = None if kw is None else kw.to(_BF16).contiguous()
+        half = D // 2 if cos is None else cos.shape[-1]
+        pos = _pos_arg(positions, rows, q.device)
+        off = 0 if isinstance(offset, torch.Tensor) else int(offset)
+        if isinstance(offset, torch.Tensor):
+            pos = (torch.arange(T, device=q.device)[None, :] + offset.to(q.device).view(-1, 1)).to(torch.int32).reshape(-1)
+        if cos is not None:
+            need = (int(pos.max()) if pos is not None else T - 1 + off) + 1
+            if cos.shape[0] < need:
+                raise ValueError(f"rotary table has {cos.shape[0]} positions, need {need}")
+            cos, sin = cos.contiguous(), sin.contiguous()
+        nv.call("ttcd_qk_norm_rope_fwd", nv.ptr(q), nv.i64(ldq), nv.ptr(k), nv.i64(ldk), nv.ptr(q_out), nv.i64(H * D),
+                nv.ptr(k_out), nv.i64(HK * D), nv.ptr(qwb), nv.ptr(kwb), nv.ptr(cos), nv.ptr(sin), nv.ptr(pos),
+                nv.i64(rows), nv.i32(T), nv.i32(off), nv.i32(H), nv.i32(HK), nv.i32(D), nv.i32(half), nv.f32(eps),
+                nv.stream_ptr())
+        ctx.save_for_backward(q, k, qwb, kwb, cos, sin, pos)
+        ctx.meta = (B, T, H, HK, D, half, off, eps, ldq, ldk,
+                    None if qw is None else qw.dtype, None if kw is None else kw.dtype)
+        return q_out, k_out
+
+    @staticmethod
+    def backward(ctx, dq, dk):
+        q, k, qwb, kwb, cos, sin, pos = ctx.saved_tensors
+        B, T, H, HK, D, half, off, eps, ldq, ldk, qdt, kdt = ctx.meta
+        rows = B * T
+        dq, dk = dq.contiguous(), dk.contiguous()
+        dq_in = torch.empty(B, T, H, D, dtype=_BF16, device=q.device)
+        dk_in = torch.empty(B, T, HK, D, dtype=_BF16, device=q.device)
+        nblk = min(_SM_BLOCKS, (rows * (H + HK) + 7) // 8)
+        has_w = qwb is not None
+        dqw = torch.empty(nblk, D, dtype=torch.float32, device=q.device) if has_w else None
+        dkw = torch.empty(nblk, D, dtype=torch.float32, device=q.device) if has_w else None
+        nv.call("ttcd_qk_norm_rope_bwd", nv.ptr(dq), nv.i64(H * D), nv.ptr(dk), nv.i64(HK * D), nv.ptr(q), nv.i64(ldq),
+                nv.ptr(k), nv.i64(ldk), nv.ptr(dq_in), nv.i64(H * D), nv.ptr(dk_in), nv.i64(HK * D), nv.ptr(qwb),
+                nv.ptr(kwb), nv.ptr(cos), nv.ptr(sin), nv.ptr(pos), nv.ptr(dqw), nv.ptr(dkw), nv.i32(nblk),
+                nv.i64(rows), nv.i32(T), nv.i32(off), nv.i32(H), nv.i32(HK), nv.i32(D), nv.i32(half), nv.f32(eps),
+                nv.stream_ptr())
+        gqw = dqw.sum(0).to(qdt) if has_w else None
+        gkw = dkw.sum(0).to(kdt) if has_w else None
+        return dq_in, dk_in, gqw, gkw, None, None, None, None, None
+
+
+def qk_norm_rope(q, k, q_weight, k_weight, eps, cos, sin, offset=0, positions=None):
+    _check(q, "q"), _check(k, "k")
+    return _QKNormRope.apply(q, k, q_weight, k_weight, float(eps), cos, sin, offset, positions)
+
+
+def rope(x, cos, sin, offset=0, positions=None):
+    """Rotary on one tensor (runs the fused kernel with a zero-head partner)."""
+    k_dummy = x[:, :, :0]
+    out, _ = _QKNormRope.apply(x, k_dummy.reshape(x.shape[0], x.shape[1], 0, x.shape[3]), None, None, 0.0, cos, sin,
+                               offset, positions)
+    return out
+
+
+# =============================================================================================
+# SwiGLU
+# =============================================================================================
+
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate, up):
+        d = gate.shape[-1]
+        g2, u2 = _rows2d(gate), _rows2d(up)
+        if g2.stride(-1) != 1 or g2.stride(0) % 8:
+            g2 = g2.contiguous()
+        if u2.stride(-1) != 1 or u2.stride(0) % 8:
+            u2 = u2.contiguous()
+        rows = g2.shape[0]
+        z = torch.empty(rows, d, dtype=_BF16, device=gate.device)
+        nv.call("ttcd_swiglu_fwd", nv.ptr(g2), nv.ptr(u2), nv.ptr(z), nv.i64(rows), nv.i32(d), nv.i64(g2.stride(0)),
+                nv.i64(u2.stride(0)), nv.i64(d), nv.stream_ptr())
+        ctx.save_for_backward(g2, u2)
+        ctx.shape = gate.shape
+        return z.view(gate.shape)
+
+    @staticmethod
+    def backward(ctx, dz):
+        g2, u2 = ctx.saved_tensors
+        rows, d = g2.shape
+        dz2 = _rows2d(dz).contiguous()
+        # gradients are written side by side so a fused gate/up GEMM backward can consume one buffer
+        packed = torch.empty(rows, 2 * d, dtype=_BF16, device=dz.device)
+        dg, du = packed[:, :d], packed[:, d:]
+        nv.call("ttcd_swiglu_bwd", nv.ptr(dz2), nv.ptr(g2), nv.ptr(u2), nv.ptr(dg), nv.ptr(du), nv.i64(rows), nv.i32(d),
+                nv.i64(d), nv.i64(g2.stride(0)), nv.i64(u2.stride(0)), nv.i64(2 * d), nv.i64(2 * d), nv.stream_ptr())
+        return dg.view(ctx.shape), du.view(ctx.shape)
+
+
+def swiglu(gate, up):
+    _check(gate, "gate")
+    return _SwiGLU.apply(gate, up)
+
+
+def swiglu_packed(gate_up):
+    d = gate_up.shape[-1] // 2
+    return _SwiGLU.apply(gate_up[..., :d], gate_up[..., d:])
+
+
+# =============================================================================================
+# depthwise conv
+# =============================================================================================
+
+class _DWConv(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, causal):
+        b, T, C, D = x.shape
+        K = w.shape[-1]
+        xc = x.contiguous()
+        wb = w.to(_BF16).contiguous()
+        y = torch.empty_like(xc)
+        nv.call("ttcd_dwconv_fwd", nv.ptr(xc), nv.ptr(wb), nv.ptr(y), nv.i64(b * T), nv.i32(C), nv.i32(D), nv.i32(K),
+                nv.i32(1 if causal else 0), nv.stream_ptr())
+        ctx.save_for_backward(xc, wb)
+        ctx.causal = causal
+        ctx.wdtype = w.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xc, wb = ctx.saved_tensors
+        b, T, C, D = xc.shape
+        K = wb.shape[-1]
+        dyc = dy.contiguous()
+        dx = torch.empty_like(xc)
+        rows_per_block = 64
+        nparts = b * T * ((C + rows_per_block - 1) // rows_per_block)
+        dwp = torch.empty(nparts, D, K, dtype=torch.float32, device=xc.device) if ctx.needs_input_grad[1] else None
+        nv.call("ttcd_dwconv_bwd", nv.ptr(dyc), nv.ptr(xc), nv.ptr(wb), nv.ptr(dx), nv.ptr(dwp), nv.i64(b * T),
+                nv.i32(C), nv.i32(D), nv.i32(K), nv.i32(1 if ctx.causal else 0), nv.stream_ptr())
+        dw = dwp.sum(0).to(ctx.wdtype) if dwp is not None else None
+        return dx, dw, None
+
+
+def dwconv_chunked(x, w2, causal=True):
+    _check(x, "x")
+    K = w2.shape[-1]
+    if K < 2 or K > 8 or x.shape[-1] % 8:
+        return reference.dwconv_chunked(x, w2, causal)
+    return _DWConv.apply(x, w2, bool(causal))
+
+
+# =============================================================================================
+# attention
+# =============================================================================================
+
+def _attn_layout(t: torch.Tensor):
+    """[B, T, H, D] view requirements of the kernel: unit stride on D, heads D apart."""
+    B, T, H, D = t.shape
+    if t.stride(-1) != 1 or (H > 1 and t.stride(2) != D) or t.stride(1) % 8 or t.data_ptr() % 16 or (
+            B > 1 and t.stride(0) % 8):
+        t = t.contiguous()
+    return t, t.stride(1), (t.stride(0) if B > 1 else T * t.stride(1))
+
+
+def attn_forward(q, k, v, window_t, window_s, scale, dual):
+    B, Tq, H, D = q.shape
+    Tk, HK = k.shape[1], k.shape[2]
+    if D not in (64, 128):
+        raise ValueError(f"head_dim {D} not supported by the attention kernel (64 or 128)")
+    q, ldq, sq = _attn_layout(q)
+    k, ldk, sk = _attn_layout(k)
+    v, ldv, sv = _attn_layout(v)
+    o_t = torch.empty(B, Tq, H, D, dtype=_BF16, device=q.device)
+    lse_t = torch.empty(B, H, Tq, dtype=torch.float32, device=q.device)
+    o_s = torch.empty_like(o_t) if dual else None
+    lse_s = torch.empty_like(lse_t) if dual else None
+    nv.call("ttcd_attn_fwd", nv.ptr(q), nv.ptr(k), nv.ptr(v), nv.ptr(o_t), nv.ptr(o_s), nv.ptr(lse_t), nv.ptr(lse_s),
+            nv.i32(B), nv.i32(Tq), nv.i32(Tk), nv.i32(H), nv.i32(HK), nv.i32(D), nv.i64(ldq), nv.i64(ldk), nv.i64(ldv),
+            nv.i64(sq), nv.i64(sk), nv.i64(sv), nv.i32(window_t or 0), nv.i32(window_s or 0), nv.f32(scale),
+            nv.stream_ptr())
+    return (q, k, v), o_t, o_s, lse_t, lse_s
+
+
+def attn_backward(q, k, v, o_t, o_s, lse_t, lse_s, do_t, do_s, window_t, window_s, scale):
+    """dq, dk, dv of the (dual-window) attention; both outputs' gradients are summed in-kernel."""
+    B, Tq, H, D = q.shape
+    Tk, HK = k.shape[1], k.shape[2]
+    if not nv.has("ttcd_attn_bwd"):
+        raise nv.NativeError("ttcd_attn_bwd missing from the native library")
+    dual = o_s is not None
+    q, ldq, sq = _attn_layout(q)
+    k, ldk, sk = _attn_layout(k)
+    v, ldv, sv = _attn_layout(v)
+    do_t = do_t.contiguous()
+    do_s = do_s.contiguous() if dual else None
+    def _delta(o, d_o):
+        out = torch.empty(B, H, Tq, dtype=torch.float32, device=q.device)
+        nv.call("ttcd_attn_delta", nv.ptr(o), nv.ptr(d_o), nv.ptr(out), nv.i64(B), nv.i32(Tq), nv.i32(H), nv.i32(D),
+                nv.stream_ptr())
+        return out
+
+    delta_t = _delta(o_t, do_t)
+    delta_s = _delta(o_s, do_s) if dual else None
+    dq = torch.empty(B, Tq, H, D, dtype=_BF16, device=q.device)
+    dk = torch.empty(B, Tk, HK, D, dtype=_BF16, device=q.device)
+    dv = torch.empty(B, Tk, HK, D, dtype=_BF16, device=q.device)
+    nv.call("ttcd_attn_bwd", nv.ptr(q), nv.ptr(k), nv.ptr(v), nv.ptr(do_t), nv.ptr(do_s), nv.ptr(lse_t), nv.ptr(lse_s),
+            nv.ptr(delta_t), nv.ptr(delta_s), nv.ptr(dq), nv.ptr(dk), nv.ptr(dv), nv.i32(B), nv.i32(Tq), nv.i32(Tk),
+            nv.i32(H), nv.i32(HK), nv.i32(D), nv.i64(ldq), nv.i64(ldk), nv.i64(ldv), nv.i64(sq), nv.i64(sk), nv.i64(sv),
+            nv.i32(window_t or 0), nv.i32(window_s or 0), nv.f32(scale), nv.stream_ptr())
+    return dq, dk, dv
+
+
+class _Attention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, window_t, window_s, scale, dual):
+        (qc, kc, vc), o_t, o_s, lse_t, lse_s = attn_forward(q, k, v, window_t, window_s, scale, dual)
+        ctx.save_for_backward(qc, kc, vc, o_t, o_s, lse_t, lse_s)
+        ctx.cfg = (window_t, window_s, scale, dual)
+        ctx.mark_non_differentiable(lse_t)
+        if dual:
+            ctx.mark_non_differentiable(lse_s)
+            return o_t, o_s, lse_t, lse_s
+        return o_t, lse_t
+
+    @staticmethod
+    def backward(ctx, *grads):
+        qc, kc, vc, o_t, o_s, lse_t, lse_s = ctx.saved_tensors
+        window_t, window_s, scale, dual = ctx.cfg
+        do_t = grads[0]
+        do_s = grads[1] if dual else None
+        if do_t is None:
+            do_t = torch.zeros_like(o_t)
+        if dual and do_s is None:
+            do_s = torch.zeros_like(o_s)
+        dq, dk, dv = attn_backward(qc, kc, vc, o_t, o_s, lse_t, lse_s, do_t, do_s, window_t, window_s, scale)
+        return dq, dk, dv, None, None, None, None
+
+
+def _per_segment(fn, q, k, v, cu_seqlens):
+    """Packed (varlen) batches: run each sequence separately and concatenate."""
+    bounds = cu_seqlens.tolist()
+    outs = [fn(q[:, s:e], k[:, s:e], v[:, s:e]) for s, e in zip(bounds[:-1], bounds[1:])]
+    if isinstance(outs[0], tuple):
+        return tuple(torch.cat([o[i] for o in outs], dim=1 if outs[0][i].dim() == 4 else 2) for i in range(len(outs[0])))
+    return torch.cat(outs, dim=1)
+
+
+def attention(q, k, v, window=None, scale=None, cu_seqlens=None, return_lse=False):
+    _check(q, "q")
+    scale = q.shape[-1] ** -0.5 if scale is None else scale
+    if cu_seqlens is not None:
+        out = _per_segment(lambda a, b, c: _Attention.apply(a, b, c, window, window, scale, False), q, k, v, cu_seqlens)
+        return out if return_lse else out[0]
+    o, lse = _Attention.apply(q, k, v, window, window, scale, False)
+    return (o, lse) if return_lse else o
+
+
+def dual_window_attention(q, k, v, window_teacher, window_student, scale=None, cu_seqlens=None):
+    _check(q, "q")
+    scale = q.shape[-1] ** -0.5 if scale is None else scale
+    if cu_seqlens is not None:
+        out = _per_segment(lambda a, b, c: _Attention.apply(a, b, c, window_teacher, window_student, scale, True),
+                           q, k, v, cu_seqlens)
+        return out[0], out[1]
+    o_t, o_s, _, _ = _Attention.apply(q, k, v, window_teacher, window_student, scale, True)
+    return o_t, o_s
+
+
+def lse_merge(o_a, lse_a, o_b, lse_b):
+    B, T, H, D = o_a.shape
+    out = torch.empty_like(o_a)
+    nv.call("ttcd_lse_merge", nv.ptr(o_a.contiguous()), nv.ptr(lse_a.contiguous()), nv.ptr(o_b.contiguous()),
+            nv.ptr(lse_b.contiguous()), nv.ptr(out), nv.ptr(None), nv.i64(B), nv.i32(T), nv.i32(H), nv.i32(D),
+            nv.stream_ptr())
+    return out
+
+
+# =============================================================================================
+# losses
+# =============================================================================================
+
+def _ce_rows(logits2, labels, inv_total, ignore_index, write_grad):
+    rows, V = logits2.shape
+    loss_rows = torch.empty(rows, dtype=torch.float32, device=logits2.device)
+    nv.call("ttcd_ce_rows", nv.ptr(logits2), nv.ptr(labels), nv.ptr(loss_rows), nv.ptr(None), nv.ptr(inv_total),
+            nv.i64(rows), nv.i32(V), nv.i64(logits2.stride(0)), nv.i32(ignore_index), nv.i32(1 if write_grad else 0),
+            nv.stream_ptr())
+    return loss_rows
+
+
+class _CrossEntropy(torch.autograd.Function):
+    """Mean CE over valid rows; the gradient is computed in the forward, in place on a copy."""
+
+    @staticmethod
+    def forward(ctx, logits, labels, ignore_index):
+        lg = logits.contiguous().clone() if logits.requires_grad else logits.contiguous()
+        if lg.stride(0) % 8:
+            raise ValueError("vocab size must be a multiple of 8 for the CE kernel")
+        labels = labels.contiguous().to(torch.int64)
+        total = labels.ne(ignore_index).sum().clamp_min(1).to(torch.float32)
+        inv_total = (1.0 / total).reshape(1)
+        loss_rows = _ce_rows(lg, labels, inv_total, ignore_index, logits.requires_grad)
+        if logits.requires_grad:
+            ctx.save_for_backward(lg)
+        return (loss_rows.sum() * inv_total).reshape(())
+
+    @staticmethod
+    def backward(ctx, g):
+        (dlogits,) = ctx.saved_tensors
+        return dlogits * g.to(dlogits.dtype), None, None
+
+
+def cross_entropy(logits, labels, ignore_index=-100):
+    return _CrossEntropy.apply(logits, labels, int(ignore_index))
+
+
+class _LinearCrossEntropy(torch.autograd.Function):
+    """CE(hidden @ W^T) in token chunks: logits GEMM -> row kernel (LSE + in-place dlogits) ->
+    dx and dW GEMMs, so the [tokens, vocab] logits never exist at once and there is no host sync."""
+
+    @staticmethod
+    def forward(ctx, hidden, labels, weight, ignore_index, num_chunks):
+        N, Hd = hidden.shape
+        V = weight.shape[0]
+        hidden = hidden.contiguous()
+        w = weight if weight.dtype == _BF16 else weight.to(_BF16)
+        labels = labels.contiguous().to(torch.int64)
+        total = labels.ne(ignore_index).sum().clamp_min(1).to(torch.float32)
+        inv_total = (1.0 / total).reshape(1)
+        need_grad = hidden.requires_grad or weight.requires_grad
+        chunk = max(128, -(-N // max(1, num_chunks)))
+        chunk = ((chunk + 127) // 128) * 128
+        dx = torch.empty_like(hidden) if need_grad else None
+        dw = torch.zeros(V, Hd, dtype=torch.float32, device=hidden.device) if need_grad else None
+        loss = torch.zeros((), dtype=torch.float32, device=hidden.device)
+        logits = torch.empty(min(chunk, N), V, dtype=_BF16, device=hidden.device)
+        for s in range(0, N, chunk):
+            e = min(s + chunk, N)
+            lg = logits[: e - s]
+            gemm(hidden[s:e], w.transpose(0, 1), out=lg.view(1, e - s, V))
+            loss_rows = _ce_rows(lg, labels[s:e], inv_total, ignore_index, need_grad)
+            loss = loss + loss_rows.sum()
+            if need_grad:
+                gemm(lg, w, out=dx[s:e].view(1, e - s, Hd))
+                gemm(lg.transpose(0, 1), hidden[s:e], out=dw.view(1, V, Hd), out_dtype=torch.float32, beta=1.0,
+                     c_in=dw.view(1, V, Hd))
+        if need_grad:
+            ctx.save_for_backward(dx, dw.to(weight.dtype))
+        return (loss * inv_total).reshape(())
+
+    @staticmethod
+    def backward(ctx, g):
+        dx, dw = ctx.saved_tensors
+        return dx * g.to(dx.dtype), None, dw * g.to(dw.dtype), None, None
+
+
+def linear_cross_entropy(hidden, labels, weight, ignore_index=-100, num_chunks=8):
+    _check(hidden, "hidden")
+    return _LinearCrossEntropy.apply(hidden, labels, weight, int(ignore_index), int(num_chunks))
+
+
+# =============================================================================================
+# Newton-Schulz (Muon) on the tensor-core GEMM
+# =============================================================================================
+
+def newton_schulz(g: torch.Tensor, coeffs=reference.NS_COEFFS) -> torch.Tensor:
+    """X <- aX + (bA + cA^2)X with A = XX^T, five fixed coefficient triples, bf16 on tcgen05."""
+    squeeze = g.dim() == 2
+    x = (g.unsqueeze(0) if squeeze else g).to(_BF16)
+    transposed = x.size(1) > x.size(2)
+    if transposed:
+        x = x.transpose(1, 2).contiguous()
+    x = (x / (x.float().norm(dim=(1, 2), keepdim=True) + 1e-7).to(_BF16)).contiguous()
+    for a, b, c in coeffs:
+        A = gemm(x, x.transpose(1, 2))                                   # X X^T
+        Bm = gemm(A, A.transpose(1, 2), alpha=c, beta=b, c_in=A)         # c A^2 + b A   (A symmetric)
+        x = gemm(Bm, x, alpha=1.0, beta=a, c_in=x)                        # B X + a X
+    if transposed:
+        x = x.transpose(1, 2)
+    return x.squeeze(0) if squeeze else x
+
+
+# =============================================================================================
+# optimiser helpers
+# =============================================================================================
+
+def adamw_step(p32, grad, m, v, p_bf16, *, lr, beta1, beta2, eps, weight_decay, step, coef=None, skip=None):
+    """Fused AdamW on a flat fp32 shard; optionally refreshes the bf16 compute copy."""
+    n = p32.numel()
+    bc1 = 1.0 - beta1 ** step
+    bc2_sqrt = math.sqrt(1.0 - beta2 ** step)
+    nv.call("ttcd_adamw", nv.ptr(p32), nv.ptr(grad), nv.i32(1 if grad.dtype == _BF16 else 0), nv.ptr(m), nv.ptr(v),
+            nv.ptr(p_bf16), nv.i64(n), nv.f32(lr), nv.f32(beta1), nv.f32(beta2), nv.f32(eps), nv.f32(weight_decay),
+            nv.f32(bc1), nv.f32(bc2_sqrt), nv.ptr(coef), nv.ptr(skip), nv.stream_ptr())
+
+
+def sumsq(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out[0] += sum(x^2); ``out`` is a 1-element fp32 CUDA tensor."""
+    nv.call("ttcd_sumsq", nv.ptr(x), nv.i32(1 if x.dtype == _BF16 else 0), nv.i64(x.numel()), nv.ptr(out),
+            nv.stream_ptr())
+
+
+def cast_scale(x: torch.Tensor, y: torch.Tensor, scale: float = 1.0, accumulate: bool = False) -> None:
+    kinds = {(_BF16, torch.float32): 0, (torch.float32, _BF16): 1, (torch.float32, torch.float32): 2, (_BF16, _BF16): 3}
+    nv.call("ttcd_cast_scale", nv.ptr(x), nv.ptr(y), nv.i64(x.numel()), nv.f32(scale), nv.i32(kinds[(x.dtype, y.dtype)]),
+            nv.i32(1 if accumulate else 0), nv.stream_ptr())
