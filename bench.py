@@ -1,0 +1,235 @@
+"""Headline benchmark: IP-TTCD training throughput (tokens/s over the whole job).
+
+Default config = the continued-training recipe on the Qwen3-0.6B shape: 28 layers, hidden 1024, 16 Q / 8 KV
+heads, head_dim 128, SwiGLU 3072, vocab 151936, tied embeddings, window 8192, student window 4096, TTT layers
+[0, 7, 14, 21]; bf16 compute, one 65536-token sequence per GPU, full activation checkpointing, AdamW
+(eps 1e-15, clip 1.0), synthetic uniform-random tokens, random-init weights.
+
+    python bench.py --gpus 1 --steps 3 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus 8 --steps 3 --warmup 3
+    python bench.py --impl reference ...      # the unmodified upstream model from baseline/_ref under FSDP2
+
+Two timed regions of K steps each, both bracketed by barrier + synchronize and timed with CUDA events
+(max over ranks): (1) inputs already on the device -> ``value``; (2) end to end through the public API
+(``Trainer.train_step`` on pinned host tensors: H2D copy of the step's tokens, step, D2H read of the loss)
+-> ``e2e``.  One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+import warnings
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+warnings.filterwarnings("ignore")
+
+METRIC = "train_tokens_per_second"
+DEFAULT_CONFIG = ROOT / "configs" / "ipttcd" / "ipttcdv9_qwen3_0.6B_ct_64k_v2_swa8k.json"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default=str(DEFAULT_CONFIG))
+    ap.add_argument("--seq-len", type=int, default=65536)
+    ap.add_argument("--batch-per-gpu", type=int, default=1)
+    ap.add_argument("--layers", type=int, default=None, help="debug only: override num_hidden_layers (invalidates the number)")
+    ap.add_argument("--no-ac", action="store_true", help="disable activation checkpointing")
+    return ap.parse_args()
+
+
+# ----------------------------------------------------------------------------------------------------
+# clocks
+# ----------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """nvidia-smi sampling of SM clocks and throttle reasons during the timed region (read-only)."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu_index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        clocks, reasons, mx = [], set(), None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    clocks.append(float(parts[1])); mx = float(parts[2])
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if clocks:
+            out["sm_mhz"] = statistics.median(clocks)
+            out["sm_max_mhz"] = mx
+            out["reasons"] = sorted(reasons)
+            out["samples"] = len(clocks)
+        return out
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    return rank, local, world
+
+
+def timed_region(torch, dist, world, fn, steps):
+    """K calls of fn between barrier+sync brackets; device time via CUDA events, max over ranks."""
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for i in range(steps):
+        fn(i)
+    e.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = torch.tensor([s.elapsed_time(e)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return float(ms.item())
+
+
+# ----------------------------------------------------------------------------------------------------
+# this framework
+# ----------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank, local, world = dist_env()
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from ttcd_b200 import _native
+    from ttcd_b200.train.engine import EngineConfig, TrainEngine, load_model_config
+
+    _native.load(required=True)
+    overrides = {}
+    if args.layers is not None:
+        overrides["num_hidden_layers"] = args.layers
+    cfg = load_model_config(args.config, **overrides)
+    engine = TrainEngine(cfg, EngineConfig(activation_checkpoint="none" if args.no_ac else "full"), device=f"cuda:{local}")
+    B, S, V = args.batch_per_gpu, args.seq_len, cfg.vocab_size
+    n_total = args.warmup + 2 * args.steps
+    gen = torch.Generator().manual_seed(1234 + rank)
+    host = [torch.randint(0, V, (B, S), generator=gen, dtype=torch.int64).pin_memory() for _ in range(n_total)]
+    dev = [t.cuda(non_blocking=True) for t in host[args.warmup:args.warmup + args.steps]]
+
+    for i in range(args.warmup):
+        engine.train_step(host[i], return_loss_on_host=False)
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    launches0 = _native.launch_count
+    ms_dev = timed_region(torch, dist, world, lambda i: engine.train_step(dev[i], return_loss_on_host=False), args.steps)
+    launches = _native.launch_count - launches0
+    losses = []
+    e2e_host = host[args.warmup + args.steps:]
+    ms_e2e = timed_region(torch, dist, world, lambda i: losses.append(engine.train_step(e2e_host[i])), args.steps)
+    clocks = sampler.stop() if sampler else {}
+    status = _native.device_status()
+
+    tokens = B * S * world * args.steps
+    value = tokens / (ms_dev / 1e3)
+    e2e = tokens / (ms_e2e / 1e3)
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms_dev / args.steps, 2), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
+            "impl": "ours",
+            "config": {"model": Path(args.config).stem, "global_batch": B * world, "seq_len": S,
+                       "parallelism": f"sharded-dp{world}", "activation_checkpointing": "none" if args.no_ac else "full",
+                       "optimizer": "AdamW", "l2": "per-step working set (several GB) exceeds the 126 MB L2",
+                       "layers": cfg.num_hidden_layers},
+            "clocks": clocks,
+            "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e / args.steps, 2),
+                    "h2d_bytes_per_step": B * S * 8, "d2h_bytes_per_step": 4},
+            "gpu_launches": launches, "final_loss": losses[-1] if losses else None, "device_status": status,
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ----------------------------------------------------------------------------------------------------
+# reference arm: the unmodified upstream model classes from baseline/_ref under PyTorch FSDP2
+# ----------------------------------------------------------------------------------------------------
+def run_reference(args):
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "custom_models").is_dir():
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed (pip install --target baseline/_ref /root/reference)"}))
+        return
+    sys.path.insert(0, str(ref_root))
+    for k in [k for k in sys.modules if k.split(".")[0] in ("custom_models", "flame", "fla")]:
+        del sys.modules[k]
+    try:
+        from baseline.reference_arm import run
+    except Exception as exc:  # pragma: no cover
+        print(json.dumps({"impl": "reference", "unavailable": f"reference arm import failed: {type(exc).__name__}: {exc}"[:300]}))
+        return
+    run(args, METRIC, ClockSampler, timed_region, dist_env)
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        try:
+            run_reference(args)
+        except Exception as exc:
+            rank = int(os.environ.get("RANK", "0"))
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": f"{type(exc).__name__}: {exc}"[:400]}), flush=True)
+        return
+    run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

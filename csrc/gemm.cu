@@ -319,7 +319,9 @@ TTCD_EXPORT int ttcd_gemm_bf16(const void* a, const void* b, void* c, const void
     return TTCD_ERR_ARG;
   if (c_in != nullptr && (reinterpret_cast<uintptr_t>(c_in) & 15u)) return TTCD_ERR_ARG;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
-  const int BN = N > 128 ? 256 : 128;
+  // every TMA box must fit inside its tensor: the caller pads tiny problems up to these minima
+  if (M < GEMM_BM || N < 128 || K < GEMM_BK) return TTCD_ERR_ARG;
+  const int BN = N >= 256 ? 256 : 128;
   CUtensorMap ta, tb;
   int rc;
   const int a_bcast = (batch > 1 && stride_a == 0) ? 1 : 0;

@@ -93,8 +93,14 @@ _ERRORS = {
 }
 
 
+launch_count = 0  # kernels launched through this binding (entry points that launch two count twice)
+_MULTI_KERNEL = {"ttcd_attn_bwd": 2}
+
+
 def call(symbol: str, *args) -> None:
     """Invoke ``int symbol(args...)`` and raise on a non-zero status."""
+    global launch_count
+    launch_count += _MULTI_KERNEL.get(symbol, 1)
     lib = load(required=True)
     fn = getattr(lib, symbol, None)
     if fn is None:

@@ -66,6 +66,16 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, out_dtype=_BF16, alpha: float = 1.
     MN-major B operand, b = w.transpose(-1, -2) of row-major w [N, K] is K-major.
     """
     _check(a, "a"), _check(b, "b")
+    M0, K0, N0 = a.shape[-2], a.shape[-1], b.shape[-1]
+    if M0 < 128 or N0 < 128 or K0 < 64:
+        # tiny problem: zero-pad up to one tile (TMA boxes must fit inside their tensors)
+        if out is not None or c_in is not None or row_scale is not None:
+            raise ValueError("gemm with M < 128, N < 128 or K < 64 does not support out/c_in/row_scale")
+        Mp, Kp, Np = max(M0, 128), max(K0, 64), max(N0, 128)
+        ap = torch.nn.functional.pad(a, (0, Kp - K0, 0, Mp - M0))
+        bp = torch.nn.functional.pad(b, (0, Np - N0, 0, Kp - K0))
+        full = gemm(ap, bp, out_dtype=out_dtype, alpha=alpha)
+        return full[..., :M0, :N0].contiguous()
     a3, a_row, lda, sa = _operand(a)
     b3, b_row, ldb, sb = _operand(b)
     batch = max(a3.shape[0], b3.shape[0])

@@ -1,0 +1,261 @@
+"""Flat-buffer sharded data-parallel runtime (the FSDP role of the reference).
+
+The reference wraps every block and the root in PyTorch FSDP2 (flame/models/parallelize_fla.py:436-497):
+bf16 parameters are all-gathered before each use and freed after, gradients are reduce-scattered in
+fp32, and AdamW runs on fp32 DTensor shards.  On a 180 GB B200 a 0.6 B-parameter model does not need
+to free its bf16 weights between uses, so this runtime is organised around that:
+
+* per group (one per block + one root group) a **flat bf16 parameter buffer** stays resident and the
+  module parameters are views into it, laid out in registration order so that q/k/v and gate/up
+  weights are contiguous slabs (one GEMM each);
+* a **flat bf16 gradient buffer** per group receives autograd's accumulation in place;
+* each rank owns a contiguous 1/world **fp32 master shard** with its Adam moments; after backward the
+  group's gradient is cast/scaled to fp32 and reduce-scattered (overlapped with the remaining
+  backward on a side stream), the fused AdamW kernel updates the shard and writes the new bf16
+  values straight into the owner's slice of the flat parameter buffer, and an all-gather publishes
+  them (overlapped with the next group's update);
+* gradient clipping uses device-side squared norms and a device-side coefficient: no host sync.
+
+``world_size == 1`` degenerates to flat buffers + fused AdamW with no communication.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .. import _native
+from ..ops import reference as ref_ops
+
+
+def _align(n: int, a: int) -> int:
+    return (n + a - 1) // a * a
+
+
+@dataclass
+class ParamGroup:
+    """One flat buffer: its parameters, their offsets, and this rank's optimizer shard."""
+
+    name: str
+    params: list[nn.Parameter]
+    names: list[str]
+    offsets: list[int] = field(default_factory=list)
+    numel: int = 0             # padded to a multiple of 8 * world
+    flat_param: torch.Tensor | None = None   # bf16 [numel]
+    flat_grad: torch.Tensor | None = None    # bf16 [numel]
+    master: torch.Tensor | None = None       # fp32 [numel / world]
+    exp_avg: torch.Tensor | None = None
+    exp_avg_sq: torch.Tensor | None = None
+    grad_shard: torch.Tensor | None = None   # fp32 [numel / world] (world > 1)
+    grad_full32: torch.Tensor | None = None  # fp32 [numel] staging for the reduce-scatter (world > 1)
+    reduce_event: torch.cuda.Event | None = None
+    pending_hooks: int = 0
+
+
+class ShardedDataParallel:
+    """Owns the flat buffers of ``model`` and performs the sharded optimizer step."""
+
+    def __init__(self, model: nn.Module, blocks: list[nn.Module] | None = None,
+                 process_group: dist.ProcessGroup | None = None, *, lr: float = 1e-4, betas=(0.9, 0.95),
+                 eps: float = 1e-8, weight_decay: float = 0.1, max_norm: float | None = 1.0,
+                 param_dtype: torch.dtype = torch.bfloat16, overlap: bool = True):
+        self.model = model
+        self.pg = process_group
+        self.world = dist.get_world_size(process_group) if (dist.is_initialized() and process_group is not False) else 1
+        self.rank = dist.get_rank(process_group) if self.world > 1 else 0
+        self.lr, self.betas, self.eps, self.weight_decay, self.max_norm = lr, betas, eps, weight_decay, max_norm
+        self.param_dtype = param_dtype
+        self.step_count = 0
+        self.overlap = overlap
+        first = next(model.parameters())
+        self.device = first.device
+        self.use_native = self.device.type == "cuda" and param_dtype == torch.bfloat16 and _native.available()
+        if self.device.type == "cuda" and param_dtype == torch.bfloat16 and not self.use_native:
+            _native.load(required=not _native.torch_fallback_allowed())
+        self.groups: list[ParamGroup] = []
+        self._build_groups(blocks)
+        self.comm_stream = torch.cuda.Stream() if (self.device.type == "cuda" and self.world > 1) else None
+        self._norm_sq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._coef = torch.ones(1, dtype=torch.float32, device=self.device)
+        self._skip = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.last_grad_norm: torch.Tensor | None = None
+        self.skip_nan_inf = False
+        if self.world > 1:
+            self._install_hooks()
+
+    # ---------------------------------------------------------------------------------- layout
+    def _build_groups(self, blocks):
+        seen: set[int] = set()
+        groups: list[ParamGroup] = []
+        blocks = list(blocks) if blocks is not None else []
+        for i, blk in enumerate(blocks):
+            ps, ns = [], []
+            for n, p in blk.named_parameters():
+                if id(p) not in seen:
+                    seen.add(id(p)); ps.append(p); ns.append(n)
+            if ps:
+                groups.append(ParamGroup(f"block{i}", ps, ns))
+        ps, ns = [], []
+        for n, p in self.model.named_parameters():
+            if id(p) not in seen:
+                seen.add(id(p)); ps.append(p); ns.append(n)
+        if ps:
+            groups.append(ParamGroup("root", ps, ns))
+        for g in groups:
+            off = 0
+            for p in g.params:
+                g.offsets.append(off)
+                off += _align(p.numel(), 8)          # 16-byte aligned starts (TMA / vector loads)
+            g.numel = _align(off, 8 * self.world)
+            g.flat_param = torch.zeros(g.numel, dtype=self.param_dtype, device=self.device)
+            g.flat_grad = torch.zeros(g.numel, dtype=self.param_dtype, device=self.device)
+            for p, o in zip(g.params, g.offsets):
+                view = g.flat_param[o:o + p.numel()].view(p.shape)
+                view.copy_(p.data)
+                p.data = view
+                p.grad = g.flat_grad[o:o + p.numel()].view(p.shape)
+            shard = g.numel // self.world
+            lo = self.rank * shard
+            g.master = g.flat_param[lo:lo + shard].float()
+            g.exp_avg = torch.zeros(shard, dtype=torch.float32, device=self.device)
+            g.exp_avg_sq = torch.zeros(shard, dtype=torch.float32, device=self.device)
+            if self.world > 1:
+                g.grad_shard = torch.zeros(shard, dtype=torch.float32, device=self.device)
+                g.grad_full32 = torch.empty(g.numel, dtype=torch.float32, device=self.device)
+        self.groups = groups
+
+    def resync_master(self) -> None:
+        """Re-derive the fp32 master shards from the current bf16 parameters (after a weight load)."""
+        for g in self.groups:
+            shard = g.numel // self.world
+            g.master.copy_(g.flat_param[self.rank * shard:(self.rank + 1) * shard].float())
+
+    # ---------------------------------------------------------------------------------- reduce-scatter
+    def _install_hooks(self):
+        """Launch a group's gradient reduce-scatter as soon as its last parameter gradient is ready."""
+        for g in self.groups:
+            for p in g.params:
+                if p.requires_grad:
+                    p.register_post_accumulate_grad_hook(self._make_hook(g))
+
+    def _make_hook(self, g: ParamGroup):
+        n_params = sum(1 for p in g.params if p.requires_grad)
+
+        def hook(_param):
+            g.pending_hooks += 1
+            if g.pending_hooks == n_params:
+                g.pending_hooks = 0
+                if self.overlap:
+                    self._reduce_group(g)
+        return hook
+
+    def _reduce_group(self, g: ParamGroup):
+        """bf16 grads -> fp32 (scaled by 1/world) -> reduce-scatter into this rank's fp32 shard."""
+        cur = torch.cuda.current_stream()
+        self.comm_stream.wait_stream(cur)
+        with torch.cuda.stream(self.comm_stream):
+            if self.use_native:
+                from ..ops import cuda
+                cuda.cast_scale(g.flat_grad, g.grad_full32, 1.0 / self.world)
+            else:
+                g.grad_full32.copy_(g.flat_grad)
+                g.grad_full32.mul_(1.0 / self.world)
+            dist.reduce_scatter_tensor(g.grad_shard, g.grad_full32, group=self.pg)
+            g.reduce_event = torch.cuda.Event()
+            g.reduce_event.record(self.comm_stream)
+
+    # ---------------------------------------------------------------------------------- step
+    def zero_grad(self):
+        for g in self.groups:
+            g.flat_grad.zero_()
+            g.reduce_event = None
+            g.pending_hooks = 0
+            for p, o in zip(g.params, g.offsets):
+                if p.grad is None or p.grad.data_ptr() != g.flat_grad.data_ptr() + o * g.flat_grad.element_size():
+                    p.grad = g.flat_grad[o:o + p.numel()].view(p.shape)
+
+    def _local_grad(self, g: ParamGroup) -> torch.Tensor:
+        return g.grad_shard if self.world > 1 else g.flat_grad
+
+    @torch.no_grad()
+    def step(self, lr: float | None = None) -> torch.Tensor:
+        """Clip (global norm), AdamW on the local shards, publish bf16 params.  Returns the grad norm
+        as a device scalar (read it lazily; nothing here synchronises with the host)."""
+        lr = self.lr if lr is None else lr
+        self.step_count += 1
+        cur = torch.cuda.current_stream() if self.device.type == "cuda" else None
+        if self.world > 1:
+            for g in self.groups:
+                if g.reduce_event is None:
+                    self._reduce_group(g)
+            cur.wait_stream(self.comm_stream)
+        # ---- global grad norm (device side)
+        self._norm_sq.zero_()
+        if self.use_native:
+            from ..ops import cuda
+            for g in self.groups:
+                cuda.sumsq(self._local_grad(g), self._norm_sq)
+        else:
+            for g in self.groups:
+                self._norm_sq += self._local_grad(g).float().pow(2).sum()
+        if self.world > 1:
+            dist.all_reduce(self._norm_sq, group=self.pg)
+        norm = self._norm_sq.sqrt()
+        self.last_grad_norm = norm
+        if self.max_norm is not None:
+            torch.clamp(self.max_norm / (norm + 1e-6), max=1.0, out=self._coef)
+        else:
+            self._coef.fill_(1.0)
+        if self.skip_nan_inf:
+            self._skip.copy_((~torch.isfinite(norm)).to(torch.int32))
+        b1, b2 = self.betas
+        for g in self.groups:
+            shard = g.numel // self.world
+            lo = self.rank * shard
+            out_slice = g.flat_param[lo:lo + shard]
+            if self.use_native:
+                from ..ops import cuda
+                cuda.adamw_step(g.master, self._local_grad(g) if self.world > 1 else g.flat_grad[lo:lo + shard],
+                                g.exp_avg, g.exp_avg_sq, out_slice, lr=lr, beta1=b1, beta2=b2, eps=self.eps,
+                                weight_decay=self.weight_decay, step=self.step_count, coef=self._coef,
+                                skip=self._skip if self.skip_nan_inf else None)
+            else:
+                grad = (self._local_grad(g) if self.world > 1 else g.flat_grad[lo:lo + shard]).float() * self._coef
+                ref_ops.adamw_step(g.master, grad, g.exp_avg, g.exp_avg_sq, lr=lr, beta1=b1, beta2=b2, eps=self.eps,
+                                   weight_decay=self.weight_decay, step=self.step_count)
+                out_slice.copy_(g.master)
+            if self.world > 1:
+                # publish: every rank contributes its updated slice; overlaps the next group's AdamW
+                self.comm_stream.wait_stream(cur)
+                with torch.cuda.stream(self.comm_stream):
+                    dist.all_gather_into_tensor(g.flat_param, out_slice, group=self.pg)
+        if self.world > 1:
+            cur.wait_stream(self.comm_stream)
+        return norm
+
+    # ---------------------------------------------------------------------------------- state
+    def optimizer_state_dict(self) -> dict:
+        return {
+            "step": self.step_count,
+            "groups": {g.name: {"master": g.master, "exp_avg": g.exp_avg, "exp_avg_sq": g.exp_avg_sq} for g in self.groups},
+            "world": self.world, "rank": self.rank,
+        }
+
+    def load_optimizer_state_dict(self, state: dict) -> None:
+        self.step_count = int(state["step"])
+        for g in self.groups:
+            s = state["groups"][g.name]
+            g.master.copy_(s["master"]); g.exp_avg.copy_(s["exp_avg"]); g.exp_avg_sq.copy_(s["exp_avg_sq"])
+            shard = g.numel // self.world
+            g.flat_param[self.rank * shard:(self.rank + 1) * shard].copy_(g.master)
+        if self.world > 1:
+            for g in self.groups:
+                shard = g.numel // self.world
+                dist.all_gather_into_tensor(g.flat_param, g.flat_param[self.rank * shard:(self.rank + 1) * shard].clone(),
+                                            group=self.pg)
+
+    def num_params(self) -> int:
+        return sum(p.numel() for g in self.groups for p in g.params)

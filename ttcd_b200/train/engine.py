@@ -1,0 +1,118 @@
+"""Training engine: model + sharded runtime + one-call train step.
+
+This is the object the trainer entry point (``python -m flame.train``) and ``bench.py`` drive; it
+plays the role of the reference's model-build / parallelize / optimizer section of
+flame/train.py:299-470 and its hot loop body (563-700): forward, backward, gradient clipping,
+optimizer step, with full or no activation checkpointing.
+"""
+from __future__ import annotations
+
+import json
+from dataclasses import dataclass
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+from ..models import IPTTCDv9Config, IPTTTConfig, TransformerConfig  # noqa: F401  (registers Auto classes)
+from ..parallel.sharded import ShardedDataParallel
+
+
+@dataclass
+class EngineConfig:
+    lr: float = 1e-4
+    betas: tuple = (0.9, 0.95)
+    eps: float = 1e-15
+    weight_decay: float = 0.1
+    max_norm: float | None = 1.0
+    activation_checkpoint: str = "full"       # full | none
+    dtype: torch.dtype = torch.bfloat16
+    skip_nan_inf: bool = False
+    seed: int = 42
+
+
+def load_model_config(path_or_cfg, **overrides):
+    from transformers import AutoConfig
+    if isinstance(path_or_cfg, (str, Path)):
+        data = json.loads(Path(path_or_cfg).read_text())
+        data.update(overrides)
+        if "num_hidden_layers" in overrides and "ttt_layers" in data:
+            data["ttt_layers"] = [i for i in data["ttt_layers"] if i < overrides["num_hidden_layers"]]
+        model_type = data.pop("model_type")
+        return AutoConfig.for_model(model_type, **data)
+    for k, v in overrides.items():
+        setattr(path_or_cfg, k, v)
+    return path_or_cfg
+
+
+def build_model(config, device, dtype, seed: int = 42):
+    """Random-init model built directly on ``device`` in ``dtype`` (same seed on every rank)."""
+    from transformers import AutoModelForCausalLM
+    torch.manual_seed(seed)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(dtype)
+    try:
+        with torch.device(device):
+            model = AutoModelForCausalLM.from_config(config)
+    finally:
+        torch.set_default_dtype(prev)
+    model.to(device=device, dtype=dtype)
+    model.tie_weights()
+    return model
+
+
+class TrainEngine:
+    """``engine.train_step(input_ids, labels)`` runs one optimizer step and returns the loss."""
+
+    def __init__(self, model_config, engine_config: EngineConfig | None = None, device=None,
+                 process_group=None, model=None):
+        self.cfg = engine_config or EngineConfig()
+        self.device = torch.device(device if device is not None else ("cuda" if torch.cuda.is_available() else "cpu"))
+        self.model_config = model_config
+        self.model = model if model is not None else build_model(model_config, self.device, self.cfg.dtype, self.cfg.seed)
+        self.model.train()
+        if self.cfg.activation_checkpoint == "full":
+            self.model.model.gradient_checkpointing = True
+        multi = dist.is_initialized() and dist.get_world_size(process_group) > 1
+        self.sdp = ShardedDataParallel(
+            self.model, blocks=list(self.model.model.layers), process_group=process_group if multi else False,
+            lr=self.cfg.lr, betas=self.cfg.betas, eps=self.cfg.eps, weight_decay=self.cfg.weight_decay,
+            max_norm=self.cfg.max_norm, param_dtype=self.cfg.dtype)
+        self.sdp.skip_nan_inf = self.cfg.skip_nan_inf
+        self.world = self.sdp.world
+        self._dev_ids = None
+        self.last_loss: torch.Tensor | None = None
+        self.tokens_seen = 0
+
+    # ------------------------------------------------------------------------------------------
+    def _to_device(self, t: torch.Tensor) -> torch.Tensor:
+        if t.device == self.device:
+            return t
+        return t.to(self.device, non_blocking=True)
+
+    def forward_backward(self, input_ids: torch.Tensor, labels: torch.Tensor | None = None, scale: float = 1.0,
+                         **model_kwargs) -> torch.Tensor:
+        ids = self._to_device(input_ids)
+        lab = ids if labels is None else self._to_device(labels)
+        out = self.model(input_ids=ids, labels=lab, **model_kwargs)
+        loss = out.loss
+        (loss * scale if scale != 1.0 else loss).backward()
+        self.tokens_seen += ids.numel()
+        return loss.detach()
+
+    def train_step(self, input_ids: torch.Tensor, labels: torch.Tensor | None = None, lr: float | None = None,
+                   return_loss_on_host: bool = True, **model_kwargs):
+        """One full step: (H2D copy if the tensors live on the host) forward, backward, clip, AdamW.
+
+        Returns the loss as a Python float (device->host read) or, with ``return_loss_on_host=False``,
+        as a device scalar so that nothing synchronises.
+        """
+        self.sdp.zero_grad()
+        loss = self.forward_backward(input_ids, labels, **model_kwargs)
+        self.sdp.step(lr)
+        self.last_loss = loss
+        return float(loss.item()) if return_loss_on_host else loss
+
+    @property
+    def grad_norm(self):
+        return self.sdp.last_grad_norm
