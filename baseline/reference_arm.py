@@ -43,6 +43,16 @@ def run(args, metric, ClockSampler, timed_region, dist_env):
         data["ttt_layers"] = [l for l in data.get("ttt_layers", []) if l < args.layers]
     model_type = data.pop("model_type")
     cfg = AutoConfig.for_model(model_type, **data)
+    # transformers >= 5 wants `_tied_weights_keys` as a {target: source} dict; upstream (pinned to 4.57)
+    # declares the same tie as a list.  Setting the attribute changes no computation and is needed
+    # to construct the tied-embedding recipe config at all on this image.
+    compat = []
+    if getattr(cfg, "tie_word_embeddings", False):
+        cls = AutoModelForCausalLM._model_mapping[type(cfg)]
+        for klass in cls.__mro__:
+            if isinstance(klass.__dict__.get("_tied_weights_keys"), (list, tuple)):
+                klass._tied_weights_keys = {"lm_head.weight": "model.embeddings.weight"}
+                compat.append(f"{klass.__name__}._tied_weights_keys list->dict (transformers 5.x)")
     torch.manual_seed(42)
     with torch.device("cuda"):
         model = AutoModelForCausalLM.from_config(cfg)
@@ -101,6 +111,6 @@ def run(args, metric, ClockSampler, timed_region, dist_env):
             "clocks": clocks,
             "e2e": {"value": round(tokens / (ms_e2e / 1e3), 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e / args.steps, 2),
                     "h2d_bytes_per_step": B * S * 8, "d2h_bytes_per_step": 4},
-            "final_loss": losses[-1] if losses else None,
+            "final_loss": losses[-1] if losses else None, "compat": compat,
         }), flush=True)
     dist.destroy_process_group()
