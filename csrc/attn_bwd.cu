@@ -9,12 +9,17 @@
 //   attn_bwd_dq   : one CTA per (128-query block, head, batch); loops over the key blocks (64 keys) of
 //                   the teacher window, recomputes S / dP and accumulates dQ += dS K in TMEM.
 //
-// Both stream operand tiles with TMA (128-byte swizzle, no multicast) through 2-slot rings and reuse
-// one swizzled tile as a K-major operand of one MMA and an MN-major operand of another (Q and dO in
-// dkdv, K in dq), so nothing is transposed in memory.  The reference has no fused dual-window
-// backward at all: training there runs two flash-attn backward passes whose dq/dk/dv are summed by
-// autograd (custom_models/ipttcd/modeling_ipttcdv9.py:686-690; profiling/FUSED_ATTENTION_DESIGN.md:68-69).
+// Software pipeline: the S / dP accumulators are double-buffered in TMEM wherever the 512 columns
+// allow it (always in dq; in dkdv for the single-window case), so the tensor core computes the
+// S / dP of step i+1 while the eight warps do the element-wise work of step i; operand tiles come
+// through a 3-slot (2-slot for dual dkdv) TMA ring (128-byte swizzle, no multicast).  One swizzled
+// tile serves as a K-major operand of one MMA and an MN-major operand of another (Q and dO in dkdv,
+// K in dq), so nothing is transposed in memory.  The reference has no fused dual-window backward:
+// training there runs two flash-attn backward passes whose dq/dk/dv are summed by autograd
+// (custom_models/ipttcd/modeling_ipttcdv9.py:686-690; profiling/FUSED_ATTENTION_DESIGN.md:68-69).
 #include "common.cuh"
+
+#include <algorithm>
 
 namespace ttcd {
 
@@ -52,27 +57,130 @@ __device__ __forceinline__ void store_half_row(uint8_t* tile, int row, int half,
   }
 }
 
+// 16 packed bf16 pairs (32 values) -> one 64-byte half row of a K-major SW128 tile
+__device__ __forceinline__ void store_half_row_packed(uint8_t* tile, int row, int half, const uint32_t (&v)[16]) {
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+    *reinterpret_cast<uint4*>(tile + sw128_offset(row, half * 4 + c)) =
+        make_uint4(v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
+}
+
+// 32 fp32 accumulator columns (times `scale`) -> 32 bf16 written to global memory (64 contiguous bytes)
+__device__ __forceinline__ void store_out32(bf16* dst, const uint32_t (&a)[32], float scale = 1.f) {
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    uint4 o;
+    o.x = pack_bf16(__uint_as_float(a[j]) * scale, __uint_as_float(a[j + 1]) * scale);
+    o.y = pack_bf16(__uint_as_float(a[j + 2]) * scale, __uint_as_float(a[j + 3]) * scale);
+    o.z = pack_bf16(__uint_as_float(a[j + 4]) * scale, __uint_as_float(a[j + 5]) * scale);
+    o.w = pack_bf16(__uint_as_float(a[j + 6]) * scale, __uint_as_float(a[j + 7]) * scale);
+    *reinterpret_cast<uint4*>(dst + j) = o;
+  }
+}
+
+// Element-wise core of the dK/dV step for one thread: 32 query columns of one key row.
+//   stats: shared-memory block [-lse_t*log2e | delta_t | -lse_s*log2e | delta_s] (64 floats each),
+//          already offset to this thread's first column.
+//   p_t = 2^(s*c - lse_t),  dS (unscaled) = p_t (dP_t - delta_t) [+ p_s (dP_s - delta_s)]
+// MASKED = false is the common case of a block that is fully inside every window.
+template <bool MASKED, bool STUDENT>
+__device__ __forceinline__ void dkdv_elementwise(const uint32_t (&sv)[32], const uint32_t (&dpt)[32],
+                                                 const uint32_t (&dps)[32], const float* stats, float scale_log2,
+                                                 int key, int qpos0, int w_t, int w_s, bool key_ok,
+                                                 uint32_t (&ptp)[16], uint32_t (&psp)[16], uint32_t (&dsp)[16]) {
+#pragma unroll
+  for (int c = 0; c < 32; c += 4) {
+    const float4 nl = *reinterpret_cast<const float4*>(stats + c);
+    const float4 dl = *reinterpret_cast<const float4*>(stats + 64 + c);
+    const float nls[4] = {nl.x, nl.y, nl.z, nl.w};
+    const float dls[4] = {dl.x, dl.y, dl.z, dl.w};
+    float nss[4] = {0.f, 0.f, 0.f, 0.f}, dss[4] = {0.f, 0.f, 0.f, 0.f};
+    if (STUDENT) {
+      const float4 ns = *reinterpret_cast<const float4*>(stats + 128 + c);
+      const float4 dsv = *reinterpret_cast<const float4*>(stats + 192 + c);
+      nss[0] = ns.x; nss[1] = ns.y; nss[2] = ns.z; nss[3] = ns.w;
+      dss[0] = dsv.x; dss[1] = dsv.y; dss[2] = dsv.z; dss[3] = dsv.w;
+    }
+    float pt[4], ps[4], d[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float s = __uint_as_float(sv[c + j]);
+      pt[j] = ex2(fmaf(s, scale_log2, nls[j]));
+      if (MASKED) {
+        const int qpos = qpos0 + c + j;
+        if (!(key_ok && key <= qpos && key > qpos - w_t)) pt[j] = 0.f;
+      }
+      d[j] = pt[j] * (__uint_as_float(dpt[c + j]) - dls[j]);
+      if (STUDENT) {
+        ps[j] = ex2(fmaf(s, scale_log2, nss[j]));
+        if (MASKED) {
+          const int qpos = qpos0 + c + j;
+          if (!(key_ok && key <= qpos && key > qpos - w_s)) ps[j] = 0.f;
+        }
+        d[j] = fmaf(ps[j], __uint_as_float(dps[c + j]) - dss[j], d[j]);
+      }
+    }
+    ptp[c / 2] = pack_bf16(pt[0], pt[1]);
+    ptp[c / 2 + 1] = pack_bf16(pt[2], pt[3]);
+    dsp[c / 2] = pack_bf16(d[0], d[1]);
+    dsp[c / 2 + 1] = pack_bf16(d[2], d[3]);
+    if (STUDENT) {
+      psp[c / 2] = pack_bf16(ps[0], ps[1]);
+      psp[c / 2 + 1] = pack_bf16(ps[2], ps[3]);
+    }
+  }
+}
+
+// Element-wise core of the dQ step: 32 key columns of one query row (statistics live in registers).
+template <bool MASKED, bool STUDENT>
+__device__ __forceinline__ void dq_elementwise(const uint32_t (&sv)[32], const uint32_t (&dpt)[32],
+                                               const uint32_t (&dps)[32], float scale_log2, float nlse_t, float del_t,
+                                               float nlse_s, float del_s, int qpos, int key0, int w_t, int w_s,
+                                               uint32_t (&dsp)[16]) {
+#pragma unroll
+  for (int c = 0; c < 32; c += 2) {
+    float d[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const float s = __uint_as_float(sv[c + j]);
+      const int key = key0 + c + j;
+      float pt = ex2(fmaf(s, scale_log2, nlse_t));
+      if (MASKED && !(key <= qpos && key > qpos - w_t)) pt = 0.f;
+      d[j] = pt * (__uint_as_float(dpt[c + j]) - del_t);
+      if (STUDENT) {
+        float ps = ex2(fmaf(s, scale_log2, nlse_s));
+        if (MASKED && !(key <= qpos && key > qpos - w_s)) ps = 0.f;
+        d[j] = fmaf(ps, __uint_as_float(dps[c + j]) - del_s, d[j]);
+      }
+    }
+    dsp[c / 2] = pack_bf16(d[0], d[1]);
+  }
+}
+
 // =================================================================================================
 // dK / dV
 // =================================================================================================
-template <int D>
-struct DkdvSmem {
+template <int D, bool DUAL>
+struct DkdvCfg {
   static constexpr int DB = D / 64;
+  static constexpr int NSETS = DUAL ? 1 : 2;    // S/dP accumulator sets in TMEM
+  static constexpr int NSLOTS = DUAL ? 2 : 3;   // Q/dO tile ring
+  static constexpr int SET_COLS = DUAL ? 192 : 128;
   static constexpr int KEY_REGION = 128 * 128;  // [128 keys x 64 d] swizzled
   static constexpr int ROW_REGION = 64 * 128;   // [64 rows x 64 d] swizzled
+  static constexpr int TILE_BYTES = DB * ROW_REGION;
+  static constexpr int NTILES = DUAL ? 3 : 2;   // Q, dO_T (, dO_S) per slot
   static constexpr int K_OFF = 0;
   static constexpr int V_OFF = K_OFF + DB * KEY_REGION;
-  static constexpr int Q_OFF = V_OFF + DB * KEY_REGION;          // 2 slots
-  static constexpr int DOT_OFF = Q_OFF + 2 * DB * ROW_REGION;    // 2 slots
-  static constexpr int DOS_OFF = DOT_OFF + 2 * DB * ROW_REGION;  // 2 slots
-  static constexpr int PT_OFF = DOS_OFF + 2 * DB * ROW_REGION;   // [128 x 64] bf16
-  static constexpr int PS_OFF = PT_OFF + KEY_REGION;
-  static constexpr int DS_OFF = PS_OFF + KEY_REGION;
-  static constexpr int VEC_OFF = DS_OFF + KEY_REGION;            // 2 slots x 4 vectors x 64 floats
+  static constexpr int RING_OFF = V_OFF + DB * KEY_REGION;            // NSLOTS x NTILES x TILE_BYTES
+  static constexpr int PT_OFF = RING_OFF + NSLOTS * NTILES * TILE_BYTES;
+  static constexpr int PS_OFF = PT_OFF + KEY_REGION;                  // only used when DUAL
+  static constexpr int DS_OFF = PS_OFF + (DUAL ? KEY_REGION : 0);
+  static constexpr int VEC_OFF = DS_OFF + KEY_REGION;                 // 2 slots x 4 vectors x 64 floats
   static constexpr int BAR_OFF = VEC_OFF + 2 * 4 * 64 * 4;
-  static constexpr int NBARS = 6;  // kv_full, tiles_full[2], sdp_full, ew_done, acc_done
+  // kv_full, tiles_full[NSLOTS], sdp_full[NSETS], ew_done, acc_done
+  static constexpr int NBARS = 1 + NSLOTS + NSETS + 2;
   static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16;
-  static constexpr int TILE_BYTES = DB * ROW_REGION;
 };
 
 template <int D, bool DUAL>
@@ -80,18 +188,18 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                      const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ CUtensorMap tma_dot,
                      const __grid_constant__ CUtensorMap tma_dos, const AttnBwdParams p) {
-  using S = DkdvSmem<D>;
+  using C = DkdvCfg<D, DUAL>;
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sbase = smem_u32(smem);
-  const uint32_t bars = sbase + S::BAR_OFF;
+  const uint32_t bars = sbase + C::BAR_OFF;
   const uint32_t kv_full = bars;
   auto tiles_full = [&](int s) { return bars + 8u * (1 + s); };
-  const uint32_t sdp_full = bars + 8u * 3;
-  const uint32_t ew_done = bars + 8u * 4;
-  const uint32_t acc_done = bars + 8u * 5;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + S::BAR_OFF + S::NBARS * 8);
+  auto sdp_full = [&](int s) { return bars + 8u * (1 + C::NSLOTS + s); };
+  const uint32_t ew_done = bars + 8u * (1 + C::NSLOTS + C::NSETS);
+  const uint32_t acc_done = ew_done + 8u;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::BAR_OFF + C::NBARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* vecs = reinterpret_cast<float*>(smem + S::VEC_OFF);
+  float* vecs = reinterpret_cast<float*>(smem + C::VEC_OFF);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * 128;
@@ -111,9 +219,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
     *abort_flag = ((sbase & 1023u) != 0) ? 1 : 0;
     if (*abort_flag) atomicCAS(&g_status, 0, 399);
     mbar_init(kv_full, 1);
-    mbar_init(tiles_full(0), 1);
-    mbar_init(tiles_full(1), 1);
-    mbar_init(sdp_full, 1);
+    for (int s = 0; s < C::NSLOTS; ++s) mbar_init(tiles_full(s), 1);
+    for (int s = 0; s < C::NSETS; ++s) mbar_init(sdp_full(s), 1);
     mbar_init(ew_done, 8);
     mbar_init(acc_done, 1);
     mbar_fence_init();
@@ -126,109 +233,119 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t t_dk = tmem_base, t_dv = tmem_base + 128, t_s = tmem_base + 256, t_dpt = tmem_base + 320,
-                 t_dps = tmem_base + 384;
+  const uint32_t t_dk = tmem_base, t_dv = tmem_base + 128;
+  auto t_set = [&](int it) { return tmem_base + 256 + (it % C::NSETS) * C::SET_COLS; };  // S | dP_T | dP_S
   const bool healthy = (*abort_flag == 0);
 
   auto iter_head = [&](int it) { return kvh * G + it / nqb; };
   auto iter_row0 = [&](int it) { return (jb_lo + it % nqb) * 64; };
-  auto iter_student = [&](int it) {
-    const int qlo_b = iter_row0(it) + off;
-    return DUAL && (qlo_b < n0 + 127 + p.w_s);
-  };
+  auto iter_student = [&](int it) { return DUAL && (iter_row0(it) + off < n0 + 127 + p.w_s); };
+  auto slot_base = [&](int it) { return sbase + C::RING_OFF + (it % C::NSLOTS) * C::NTILES * C::TILE_BYTES; };
 
   if (warp == 8 && healthy && n_iters > 0) {
     if (elect_one()) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, false, false);  // [keys x q] = A(K-major) B(K-major)
       constexpr uint32_t idesc_acc = umma_idesc_bf16(128, D, false, true);   // [keys x D] = A(K-major) B(MN-major)
       auto load_tiles = [&](int it) {
-        const int slot = it & 1;
+        const int slot = it % C::NSLOTS;
         const int h = iter_head(it), r0 = iter_row0(it);
         const bool st = iter_student(it);
-        mbar_expect_tx(tiles_full(slot), S::TILE_BYTES * (st ? 3 : 2));
+        const uint32_t base = slot_base(it);
+        mbar_expect_tx(tiles_full(slot), C::TILE_BYTES * (st ? 3 : 2));
 #pragma unroll
-        for (int d = 0; d < S::DB; ++d) {
-          tma_load_3d(sbase + S::Q_OFF + slot * S::TILE_BYTES + d * S::ROW_REGION, &tma_q, tiles_full(slot),
-                      h * D + d * 64, r0, b);
-          tma_load_3d(sbase + S::DOT_OFF + slot * S::TILE_BYTES + d * S::ROW_REGION, &tma_dot, tiles_full(slot),
-                      h * D + d * 64, r0, b);
-          if (st)
-            tma_load_3d(sbase + S::DOS_OFF + slot * S::TILE_BYTES + d * S::ROW_REGION, &tma_dos, tiles_full(slot),
-                        h * D + d * 64, r0, b);
+        for (int d = 0; d < C::DB; ++d) {
+          tma_load_3d(base + d * C::ROW_REGION, &tma_q, tiles_full(slot), h * D + d * 64, r0, b);
+          tma_load_3d(base + C::TILE_BYTES + d * C::ROW_REGION, &tma_dot, tiles_full(slot), h * D + d * 64, r0, b);
+          if (DUAL && st)
+            tma_load_3d(base + 2 * C::TILE_BYTES + d * C::ROW_REGION, &tma_dos, tiles_full(slot), h * D + d * 64, r0, b);
         }
       };
-      bool ok = true;
-      mbar_expect_tx(kv_full, 2 * S::DB * S::KEY_REGION);
-#pragma unroll
-      for (int d = 0; d < S::DB; ++d) {
-        tma_load_3d(sbase + S::K_OFF + d * S::KEY_REGION, &tma_k, kv_full, kvh * D + d * 64, n0, b);
-        tma_load_3d(sbase + S::V_OFF + d * S::KEY_REGION, &tma_v, kv_full, kvh * D + d * 64, n0, b);
-      }
-      load_tiles(0);
-      ok = mbar_wait(kv_full, 0, abort_flag, 301);
-      for (int it = 0; it < n_iters && ok; ++it) {
-        const int slot = it & 1;
+      auto issue_sdp = [&](int it) {
         const bool st = iter_student(it);
-        ok = mbar_wait(tiles_full(slot), (it >> 1) & 1, abort_flag, 302);
-        if (!ok) break;
-        tc_fence_after_sync();
-        const uint32_t sq = sbase + S::Q_OFF + slot * S::TILE_BYTES;
-        const uint32_t sdot = sbase + S::DOT_OFF + slot * S::TILE_BYTES;
-        const uint32_t sdos = sbase + S::DOS_OFF + slot * S::TILE_BYTES;
+        const uint32_t sq = slot_base(it), sdot = sq + C::TILE_BYTES, sdos = sq + 2 * C::TILE_BYTES;
+        const uint32_t ts = t_set(it);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t ko = (k / 4) * S::KEY_REGION + (k % 4) * 32;
-          const uint32_t ro = (k / 4) * S::ROW_REGION + (k % 4) * 32;
-          umma_ss(t_s, umma_desc_sw128(sbase + S::K_OFF + ko, 16, 1024), umma_desc_sw128(sq + ro, 16, 1024), idesc_s,
+          const uint32_t ko = (k / 4) * C::KEY_REGION + (k % 4) * 32;
+          const uint32_t ro = (k / 4) * C::ROW_REGION + (k % 4) * 32;
+          umma_ss(ts, umma_desc_sw128(sbase + C::K_OFF + ko, 16, 1024), umma_desc_sw128(sq + ro, 16, 1024), idesc_s,
                   k != 0);
         }
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t ko = (k / 4) * S::KEY_REGION + (k % 4) * 32;
-          const uint32_t ro = (k / 4) * S::ROW_REGION + (k % 4) * 32;
-          umma_ss(t_dpt, umma_desc_sw128(sbase + S::V_OFF + ko, 16, 1024), umma_desc_sw128(sdot + ro, 16, 1024),
+          const uint32_t ko = (k / 4) * C::KEY_REGION + (k % 4) * 32;
+          const uint32_t ro = (k / 4) * C::ROW_REGION + (k % 4) * 32;
+          umma_ss(ts + 64, umma_desc_sw128(sbase + C::V_OFF + ko, 16, 1024), umma_desc_sw128(sdot + ro, 16, 1024),
                   idesc_s, k != 0);
         }
-        if (st) {
+        if (DUAL && st) {
 #pragma unroll
           for (int k = 0; k < D / 16; ++k) {
-            const uint32_t ko = (k / 4) * S::KEY_REGION + (k % 4) * 32;
-            const uint32_t ro = (k / 4) * S::ROW_REGION + (k % 4) * 32;
-            umma_ss(t_dps, umma_desc_sw128(sbase + S::V_OFF + ko, 16, 1024), umma_desc_sw128(sdos + ro, 16, 1024),
+            const uint32_t ko = (k / 4) * C::KEY_REGION + (k % 4) * 32;
+            const uint32_t ro = (k / 4) * C::ROW_REGION + (k % 4) * 32;
+            umma_ss(ts + 128, umma_desc_sw128(sbase + C::V_OFF + ko, 16, 1024), umma_desc_sw128(sdos + ro, 16, 1024),
                     idesc_s, k != 0);
           }
         }
-        umma_commit(sdp_full);
-        if (it + 1 < n_iters) {
-          // slot (it+1)&1 was last read by the accumulate MMAs of iteration it-1
-          if (it >= 1) ok = mbar_wait(acc_done, (it - 1) & 1, abort_flag, 303);
-          if (!ok) break;
-          load_tiles(it + 1);
-        }
-        ok = mbar_wait(ew_done, it & 1, abort_flag, 304);
-        if (!ok) break;
-        tc_fence_after_sync();
+        umma_commit(sdp_full(it % C::NSETS));
+      };
+      auto issue_acc = [&](int it) {
+        const bool st = iter_student(it);
+        const uint32_t sq = slot_base(it), sdot = sq + C::TILE_BYTES, sdos = sq + 2 * C::TILE_BYTES;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {  // contraction over the 64 query rows
-          umma_ss(t_dv, umma_desc_sw128(sbase + S::PT_OFF + k * 32, 16, 1024),
-                  umma_desc_sw128(sdot + k * 2048, S::ROW_REGION, 1024), idesc_acc, (it | k) != 0);
-        }
-        if (st) {
+        for (int k = 0; k < 4; ++k)  // contraction over the 64 query rows
+          umma_ss(t_dv, umma_desc_sw128(sbase + C::PT_OFF + k * 32, 16, 1024),
+                  umma_desc_sw128(sdot + k * 2048, C::ROW_REGION, 1024), idesc_acc, (it | k) != 0);
+        if (DUAL && st) {
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_ss(t_dv, umma_desc_sw128(sbase + S::PS_OFF + k * 32, 16, 1024),
-                    umma_desc_sw128(sdos + k * 2048, S::ROW_REGION, 1024), idesc_acc, 1u);
+            umma_ss(t_dv, umma_desc_sw128(sbase + C::PS_OFF + k * 32, 16, 1024),
+                    umma_desc_sw128(sdos + k * 2048, C::ROW_REGION, 1024), idesc_acc, 1u);
         }
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          umma_ss(t_dk, umma_desc_sw128(sbase + S::DS_OFF + k * 32, 16, 1024),
-                  umma_desc_sw128(sq + k * 2048, S::ROW_REGION, 1024), idesc_acc, (it | k) != 0);
-        }
+        for (int k = 0; k < 4; ++k)
+          umma_ss(t_dk, umma_desc_sw128(sbase + C::DS_OFF + k * 32, 16, 1024),
+                  umma_desc_sw128(sq + k * 2048, C::ROW_REGION, 1024), idesc_acc, (it | k) != 0);
         umma_commit(acc_done);
+      };
+
+      bool ok = true;
+      mbar_expect_tx(kv_full, 2 * C::DB * C::KEY_REGION);
+#pragma unroll
+      for (int d = 0; d < C::DB; ++d) {
+        tma_load_3d(sbase + C::K_OFF + d * C::KEY_REGION, &tma_k, kv_full, kvh * D + d * 64, n0, b);
+        tma_load_3d(sbase + C::V_OFF + d * C::KEY_REGION, &tma_v, kv_full, kvh * D + d * 64, n0, b);
+      }
+      for (int it = 0; it < C::NSLOTS - 1 && it < n_iters; ++it) load_tiles(it);
+      ok = mbar_wait(kv_full, 0, abort_flag, 301);
+      if (ok && C::NSETS == 2) {
+        ok = mbar_wait(tiles_full(0), 0, abort_flag, 302);
+        if (ok) { tc_fence_after_sync(); issue_sdp(0); }
+      }
+      for (int it = 0; it < n_iters && ok; ++it) {
+        // S/dP for the step the compute warps will need next
+        const int nxt = C::NSETS == 2 ? it + 1 : it;
+        if (nxt < n_iters) {
+          ok = mbar_wait(tiles_full(nxt % C::NSLOTS), (nxt / C::NSLOTS) & 1, abort_flag, 303);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_sdp(nxt);  // its TMEM set was last read before ew_done(nxt - NSETS), already observed
+        }
+        // refill the ring: the slot of step it-1 is free once its accumulate MMAs have completed
+        const int pre = it + C::NSLOTS - 1;
+        if (pre < n_iters) {
+          if (it >= 1) ok = mbar_wait(acc_done, (it - 1) & 1, abort_flag, 304);
+          if (!ok) break;
+          load_tiles(pre);
+        }
+        ok = mbar_wait(ew_done, it & 1, abort_flag, 305);
+        if (!ok) break;
+        tc_fence_after_sync();
+        issue_acc(it);
       }
       if (!ok) {
         mbar_drain(kv_full, 0);
-        for (int s = 0; s < 2; ++s) { mbar_drain(tiles_full(s), 0); mbar_drain(tiles_full(s), 1); }
+        for (int s = 0; s < C::NSLOTS; ++s) { mbar_drain(tiles_full(s), 0); mbar_drain(tiles_full(s), 1); }
       }
     }
   } else if (warp < 8 && healthy) {
@@ -242,73 +359,76 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       const bool r = mbar_wait(bar, parity, abort_flag, code);
       return __all_sync(0xffffffffu, r) != 0;
     };
+    // per-row statistics of a query block: [-lse_t*log2e | delta_t | -lse_s*log2e | delta_s], 64 each;
+    // this thread fetches element (which, r) of the block used by step `it`
+    auto fetch_stat = [&](int it) -> float {
+      const int which = ctid >> 6, r = ctid & 63;
+      const int row = iter_row0(it) + r;
+      const int64_t idx = (static_cast<int64_t>(b) * p.H + iter_head(it)) * p.Tq + row;
+      if (row >= p.Tq) return (which == 0 || which == 2) ? -INFINITY : 0.f;  // p = 0 past the end
+      if (which == 0) return -p.lse_t[idx] * LOG2E;
+      if (which == 1) return p.delta_t[idx];
+      if (!DUAL || !iter_student(it)) return 0.f;
+      return which == 2 ? -p.lse_s[idx] * LOG2E : p.delta_s[idx];
+    };
+    if (n_iters > 0) vecs[ctid] = fetch_stat(0);
     for (int it = 0; it < n_iters && ok; ++it) {
-      const int h = iter_head(it), r0 = iter_row0(it);
+      const int r0 = iter_row0(it);
       const bool st = iter_student(it);
-      float* vslot = vecs + (it & 1) * 256;
-      {
-        // per-row statistics of this query block: [lse_t*log2e | delta_t | lse_s*log2e | delta_s]
-        const int which = ctid >> 6, r = ctid & 63;
-        const int row = r0 + r;
-        const int64_t idx = (static_cast<int64_t>(b) * p.H + h) * p.Tq + row;
-        float val = 0.f;
-        if (row < p.Tq) {
-          if (which == 0) val = p.lse_t[idx] * LOG2E;
-          else if (which == 1) val = p.delta_t[idx];
-          else if (DUAL && st && which == 2) val = p.lse_s[idx] * LOG2E;
-          else if (DUAL && st && which == 3) val = p.delta_s[idx];
-        } else if (which == 0 || which == 2) {
-          val = INFINITY;  // rows past the end contribute p = 0
-        }
-        vslot[which * 64 + r] = val;
-      }
+      const float* vslot = vecs + (it & 1) * 256;
+      const float next_stat = (it + 1 < n_iters) ? fetch_stat(it + 1) : 0.f;  // in flight during this step
       named_barrier_sync(1, 256);
-      ok = wait_all(sdp_full, it & 1, 311);
+      ok = wait_all(sdp_full(it % C::NSETS), (it / C::NSETS) & 1, 311);
       if (!ok) break;
       tc_fence_after_sync();
+      const uint32_t ts = t_set(it) + lane_addr + half * 32;
       uint32_t sv[32], dpt[32], dps[32];
-      tmem_ld32(t_s + lane_addr + half * 32, sv);
-      tmem_ld32(t_dpt + lane_addr + half * 32, dpt);
-      if (st) tmem_ld32(t_dps + lane_addr + half * 32, dps);
+      tmem_ld32(ts, sv);
+      tmem_ld32(ts + 64, dpt);
+      if (DUAL && st) tmem_ld32(ts + 128, dps);
       tmem_ld_wait();
+      uint32_t ptp[16], psp[16], dsp[16];
+      {
+        const int qlo_b = r0 + off, qhi_b = r0 + 63 + off;
+        // fully visible block: every (key, query) pair is inside the teacher (and student) window
+        const bool full_t = (n0 + 127 <= qlo_b) && (n0 > qhi_b - p.w_t) && (n0 + 127 < p.Tk);
+        const bool full_s = (n0 > qhi_b - p.w_s);
+        const float* stats = vslot + half * 32;
+        const int qpos0 = r0 + half * 32 + off;
+        const bool key_ok = key < p.Tk;
+        if (DUAL && st) {
+          if (full_t && full_s)
+            dkdv_elementwise<false, true>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, p.w_t, p.w_s, key_ok, ptp, psp, dsp);
+          else
+            dkdv_elementwise<true, true>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, p.w_t, p.w_s, key_ok, ptp, psp, dsp);
+        } else {
+          if (full_t)
+            dkdv_elementwise<false, false>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, p.w_t, p.w_s, key_ok, ptp, psp, dsp);
+          else
+            dkdv_elementwise<true, false>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, p.w_t, p.w_s, key_ok, ptp, psp, dsp);
+        }
+      }
       if (it >= 1) {
-        ok = wait_all(acc_done, (it - 1) & 1, 312);  // P / dS tiles free again
+        ok = wait_all(acc_done, (it - 1) & 1, 312);  // P / dS tiles are free again
         if (!ok) break;
       }
-      float pt[32], ps[32], ds[32];
-#pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        const int col = half * 32 + c;
-        const int qpos = r0 + col + off;
-        const float s2 = __uint_as_float(sv[c]) * p.scale_log2;
-        const bool vis_t = key <= qpos && key > qpos - p.w_t && key < p.Tk;
-        const float p_t = vis_t ? ex2(s2 - vslot[col]) : 0.f;
-        float d = p_t * (__uint_as_float(dpt[c]) - vslot[64 + col]);
-        pt[c] = p_t;
-        if (DUAL && st) {
-          const bool vis_s = key <= qpos && key > qpos - p.w_s && key < p.Tk;
-          const float p_s = vis_s ? ex2(s2 - vslot[128 + col]) : 0.f;
-          d += p_s * (__uint_as_float(dps[c]) - vslot[192 + col]);
-          ps[c] = p_s;
-        }
-        ds[c] = d * p.scale;
-      }
-      store_half_row(smem + S::PT_OFF, krow, half, pt);
-      if (DUAL && st) store_half_row(smem + S::PS_OFF, krow, half, ps);
-      store_half_row(smem + S::DS_OFF, krow, half, ds);
+      store_half_row_packed(smem + C::PT_OFF, krow, half, ptp);
+      if (DUAL && st) store_half_row_packed(smem + C::PS_OFF, krow, half, psp);
+      store_half_row_packed(smem + C::DS_OFF, krow, half, dsp);
+      vecs[((it + 1) & 1) * 256 + ctid] = next_stat;
       fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(ew_done);
     }
-    // epilogue: dK, dV -> global (this thread: key row `krow`, column half of D)
+    // epilogue: dK, dV -> global (this thread: key row `krow`, one half of the D columns)
     if (ok) {
       if (n_iters > 0) ok = wait_all(acc_done, (n_iters - 1) & 1, 313);
       if (ok) {
         tc_fence_after_sync();
         const bool store = key < p.Tk;
         const int64_t rowoff = ((static_cast<int64_t>(b) * p.Tk + key) * p.HK + kvh) * D;
-        constexpr int COLS = D / 2;  // per thread
+        constexpr int COLS = D / 2;
 #pragma unroll
         for (int c = 0; c < COLS; c += 32) {
           uint32_t a[32], v[32];
@@ -321,20 +441,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
             for (int j = 0; j < 32; ++j) a[j] = v[j] = 0u;
           }
           if (store) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 o;
-              o.x = pack_bf16(__uint_as_float(a[j]), __uint_as_float(a[j + 1]));
-              o.y = pack_bf16(__uint_as_float(a[j + 2]), __uint_as_float(a[j + 3]));
-              o.z = pack_bf16(__uint_as_float(a[j + 4]), __uint_as_float(a[j + 5]));
-              o.w = pack_bf16(__uint_as_float(a[j + 6]), __uint_as_float(a[j + 7]));
-              *reinterpret_cast<uint4*>(p.dk + rowoff + half * COLS + c + j) = o;
-              o.x = pack_bf16(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
-              o.y = pack_bf16(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-              o.z = pack_bf16(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
-              o.w = pack_bf16(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
-              *reinterpret_cast<uint4*>(p.dv + rowoff + half * COLS + c + j) = o;
-            }
+            store_out32(p.dk + rowoff + half * COLS + c, a, p.scale);  // dS was kept unscaled
+            store_out32(p.dv + rowoff + half * COLS + c, v);
           }
         }
       }
@@ -351,21 +459,23 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
 // =================================================================================================
 // dQ
 // =================================================================================================
-template <int D>
-struct DqSmem {
+template <int D, bool DUAL>
+struct DqCfg {
   static constexpr int DB = D / 64;
+  static constexpr int NSLOTS = 3;
+  static constexpr int SET_COLS = DUAL ? 192 : 128;
   static constexpr int Q_REGION = 128 * 128;
   static constexpr int KV_REGION = 64 * 128;
+  static constexpr int KV_BYTES = DB * KV_REGION;
   static constexpr int Q_OFF = 0;
   static constexpr int DOT_OFF = Q_OFF + DB * Q_REGION;
-  static constexpr int DOS_OFF = DOT_OFF + DB * Q_REGION;
-  static constexpr int K_OFF = DOS_OFF + DB * Q_REGION;      // 2 slots
-  static constexpr int V_OFF = K_OFF + 2 * DB * KV_REGION;   // 2 slots
-  static constexpr int DS_OFF = V_OFF + 2 * DB * KV_REGION;  // [128 x 64] bf16
+  static constexpr int DOS_OFF = DOT_OFF + DB * Q_REGION;                 // only used when DUAL
+  static constexpr int RING_OFF = DOS_OFF + (DUAL ? DB * Q_REGION : 0);   // NSLOTS x (K, V)
+  static constexpr int DS_OFF = RING_OFF + NSLOTS * 2 * KV_BYTES;         // [128 x 64] bf16
   static constexpr int BAR_OFF = DS_OFF + Q_REGION;
-  static constexpr int NBARS = 6;  // q_full, kv_full[2], sdp_full, ew_done, acc_done
+  // q_full, kv_full[NSLOTS], sdp_full[2], ew_done, acc_done
+  static constexpr int NBARS = 1 + NSLOTS + 2 + 2;
   static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16;
-  static constexpr int KV_BYTES = DB * KV_REGION;
 };
 
 template <int D, bool DUAL>
@@ -373,16 +483,16 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                    const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ CUtensorMap tma_dot,
                    const __grid_constant__ CUtensorMap tma_dos, const AttnBwdParams p) {
-  using S = DqSmem<D>;
+  using C = DqCfg<D, DUAL>;
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sbase = smem_u32(smem);
-  const uint32_t bars = sbase + S::BAR_OFF;
+  const uint32_t bars = sbase + C::BAR_OFF;
   const uint32_t q_full = bars;
   auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
-  const uint32_t sdp_full = bars + 8u * 3;
-  const uint32_t ew_done = bars + 8u * 4;
-  const uint32_t acc_done = bars + 8u * 5;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + S::BAR_OFF + S::NBARS * 8);
+  auto sdp_full = [&](int s) { return bars + 8u * (1 + C::NSLOTS + s); };
+  const uint32_t ew_done = bars + 8u * (3 + C::NSLOTS);
+  const uint32_t acc_done = ew_done + 8u;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::BAR_OFF + C::NBARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -398,14 +508,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   const int n_iters = key_hi / 64 - blk_lo + 1;
   auto iter_key0 = [&](int it) { return (blk_lo + it) * 64; };
   auto iter_student = [&](int it) { return DUAL && (iter_key0(it) + 63 > qlo - p.w_s); };
+  auto slot_base = [&](int it) { return sbase + C::RING_OFF + (it % C::NSLOTS) * 2 * C::KV_BYTES; };
 
   if (threadIdx.x == 0) {
     *abort_flag = ((sbase & 1023u) != 0) ? 1 : 0;
     if (*abort_flag) atomicCAS(&g_status, 0, 398);
     mbar_init(q_full, 1);
-    mbar_init(kv_full(0), 1);
-    mbar_init(kv_full(1), 1);
-    mbar_init(sdp_full, 1);
+    for (int s = 0; s < C::NSLOTS; ++s) mbar_init(kv_full(s), 1);
+    mbar_init(sdp_full(0), 1);
+    mbar_init(sdp_full(1), 1);
     mbar_init(ew_done, 8);
     mbar_init(acc_done, 1);
     mbar_fence_init();
@@ -418,7 +529,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t t_dq = tmem_base, t_s = tmem_base + 128, t_dpt = tmem_base + 192, t_dps = tmem_base + 256;
+  const uint32_t t_dq = tmem_base;
+  auto t_set = [&](int it) { return tmem_base + 128 + (it & 1) * C::SET_COLS; };  // S | dP_T | dP_S
   const bool healthy = (*abort_flag == 0);
 
   if (warp == 8 && healthy) {
@@ -426,75 +538,81 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, false, false);
       constexpr uint32_t idesc_acc = umma_idesc_bf16(128, D, false, true);
       auto load_kv = [&](int it) {
-        const int slot = it & 1;
-        mbar_expect_tx(kv_full(slot), 2 * S::KV_BYTES);
+        const int slot = it % C::NSLOTS;
+        const uint32_t base = slot_base(it);
+        mbar_expect_tx(kv_full(slot), 2 * C::KV_BYTES);
 #pragma unroll
-        for (int d = 0; d < S::DB; ++d) {
-          tma_load_3d(sbase + S::K_OFF + slot * S::KV_BYTES + d * S::KV_REGION, &tma_k, kv_full(slot),
-                      kvh * D + d * 64, iter_key0(it), b);
-          tma_load_3d(sbase + S::V_OFF + slot * S::KV_BYTES + d * S::KV_REGION, &tma_v, kv_full(slot),
-                      kvh * D + d * 64, iter_key0(it), b);
+        for (int d = 0; d < C::DB; ++d) {
+          tma_load_3d(base + d * C::KV_REGION, &tma_k, kv_full(slot), kvh * D + d * 64, iter_key0(it), b);
+          tma_load_3d(base + C::KV_BYTES + d * C::KV_REGION, &tma_v, kv_full(slot), kvh * D + d * 64, iter_key0(it), b);
         }
       };
-      bool ok = true;
-      mbar_expect_tx(q_full, S::DB * S::Q_REGION * (DUAL ? 3 : 2));
-#pragma unroll
-      for (int d = 0; d < S::DB; ++d) {
-        tma_load_3d(sbase + S::Q_OFF + d * S::Q_REGION, &tma_q, q_full, h * D + d * 64, m0, b);
-        tma_load_3d(sbase + S::DOT_OFF + d * S::Q_REGION, &tma_dot, q_full, h * D + d * 64, m0, b);
-        if (DUAL) tma_load_3d(sbase + S::DOS_OFF + d * S::Q_REGION, &tma_dos, q_full, h * D + d * 64, m0, b);
-      }
-      load_kv(0);
-      ok = mbar_wait(q_full, 0, abort_flag, 321);
-      for (int it = 0; it < n_iters && ok; ++it) {
-        const int slot = it & 1;
+      auto issue_sdp = [&](int it) {
         const bool st = iter_student(it);
-        ok = mbar_wait(kv_full(slot), (it >> 1) & 1, abort_flag, 322);
-        if (!ok) break;
-        tc_fence_after_sync();
-        const uint32_t sk = sbase + S::K_OFF + slot * S::KV_BYTES;
-        const uint32_t sv = sbase + S::V_OFF + slot * S::KV_BYTES;
+        const uint32_t sk = slot_base(it), sv = sk + C::KV_BYTES;
+        const uint32_t ts = t_set(it);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t qo = (k / 4) * S::Q_REGION + (k % 4) * 32;
-          const uint32_t ko = (k / 4) * S::KV_REGION + (k % 4) * 32;
-          umma_ss(t_s, umma_desc_sw128(sbase + S::Q_OFF + qo, 16, 1024), umma_desc_sw128(sk + ko, 16, 1024), idesc_s,
+          const uint32_t qo = (k / 4) * C::Q_REGION + (k % 4) * 32;
+          const uint32_t ko = (k / 4) * C::KV_REGION + (k % 4) * 32;
+          umma_ss(ts, umma_desc_sw128(sbase + C::Q_OFF + qo, 16, 1024), umma_desc_sw128(sk + ko, 16, 1024), idesc_s,
                   k != 0);
         }
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t qo = (k / 4) * S::Q_REGION + (k % 4) * 32;
-          const uint32_t ko = (k / 4) * S::KV_REGION + (k % 4) * 32;
-          umma_ss(t_dpt, umma_desc_sw128(sbase + S::DOT_OFF + qo, 16, 1024), umma_desc_sw128(sv + ko, 16, 1024),
+          const uint32_t qo = (k / 4) * C::Q_REGION + (k % 4) * 32;
+          const uint32_t ko = (k / 4) * C::KV_REGION + (k % 4) * 32;
+          umma_ss(ts + 64, umma_desc_sw128(sbase + C::DOT_OFF + qo, 16, 1024), umma_desc_sw128(sv + ko, 16, 1024),
                   idesc_s, k != 0);
         }
-        if (st) {
+        if (DUAL && st) {
 #pragma unroll
           for (int k = 0; k < D / 16; ++k) {
-            const uint32_t qo = (k / 4) * S::Q_REGION + (k % 4) * 32;
-            const uint32_t ko = (k / 4) * S::KV_REGION + (k % 4) * 32;
-            umma_ss(t_dps, umma_desc_sw128(sbase + S::DOS_OFF + qo, 16, 1024), umma_desc_sw128(sv + ko, 16, 1024),
+            const uint32_t qo = (k / 4) * C::Q_REGION + (k % 4) * 32;
+            const uint32_t ko = (k / 4) * C::KV_REGION + (k % 4) * 32;
+            umma_ss(ts + 128, umma_desc_sw128(sbase + C::DOS_OFF + qo, 16, 1024), umma_desc_sw128(sv + ko, 16, 1024),
                     idesc_s, k != 0);
           }
         }
-        umma_commit(sdp_full);
+        umma_commit(sdp_full(it & 1));
+      };
+      bool ok = true;
+      mbar_expect_tx(q_full, C::DB * C::Q_REGION * (DUAL ? 3 : 2));
+#pragma unroll
+      for (int d = 0; d < C::DB; ++d) {
+        tma_load_3d(sbase + C::Q_OFF + d * C::Q_REGION, &tma_q, q_full, h * D + d * 64, m0, b);
+        tma_load_3d(sbase + C::DOT_OFF + d * C::Q_REGION, &tma_dot, q_full, h * D + d * 64, m0, b);
+        if (DUAL) tma_load_3d(sbase + C::DOS_OFF + d * C::Q_REGION, &tma_dos, q_full, h * D + d * 64, m0, b);
+      }
+      for (int it = 0; it < C::NSLOTS - 1 && it < n_iters; ++it) load_kv(it);
+      ok = mbar_wait(q_full, 0, abort_flag, 321) && mbar_wait(kv_full(0), 0, abort_flag, 322);
+      if (ok) { tc_fence_after_sync(); issue_sdp(0); }
+      for (int it = 0; it < n_iters && ok; ++it) {
         if (it + 1 < n_iters) {
-          if (it >= 1) ok = mbar_wait(acc_done, (it - 1) & 1, abort_flag, 323);
+          ok = mbar_wait(kv_full((it + 1) % C::NSLOTS), ((it + 1) / C::NSLOTS) & 1, abort_flag, 323);
           if (!ok) break;
-          load_kv(it + 1);
+          tc_fence_after_sync();
+          issue_sdp(it + 1);  // its TMEM set was last read before ew_done(it-1), already observed
         }
-        ok = mbar_wait(ew_done, it & 1, abort_flag, 324);
+        const int pre = it + C::NSLOTS - 1;
+        if (pre < n_iters) {
+          if (it >= 1) ok = mbar_wait(acc_done, (it - 1) & 1, abort_flag, 324);  // slot of step it-1 is free
+          if (!ok) break;
+          load_kv(pre);
+        }
+        ok = mbar_wait(ew_done, it & 1, abort_flag, 325);
         if (!ok) break;
         tc_fence_after_sync();
+        const uint32_t sk = slot_base(it);
 #pragma unroll
         for (int k = 0; k < 4; ++k)  // contraction over the 64 keys of the block
-          umma_ss(t_dq, umma_desc_sw128(sbase + S::DS_OFF + k * 32, 16, 1024),
-                  umma_desc_sw128(sk + k * 2048, S::KV_REGION, 1024), idesc_acc, (it | k) != 0);
+          umma_ss(t_dq, umma_desc_sw128(sbase + C::DS_OFF + k * 32, 16, 1024),
+                  umma_desc_sw128(sk + k * 2048, C::KV_REGION, 1024), idesc_acc, (it | k) != 0);
         umma_commit(acc_done);
       }
       if (!ok) {
         mbar_drain(q_full, 0);
-        for (int s = 0; s < 2; ++s) { mbar_drain(kv_full(s), 0); mbar_drain(kv_full(s), 1); }
+        for (int s = 0; s < C::NSLOTS; ++s) { mbar_drain(kv_full(s), 0); mbar_drain(kv_full(s), 1); }
       }
     }
   } else if (warp < 8 && healthy) {
@@ -505,9 +623,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const bool row_ok = row < p.Tq;
     const int64_t sidx = (static_cast<int64_t>(b) * p.H + h) * p.Tq + row;
-    const float lse_t2 = row_ok ? p.lse_t[sidx] * LOG2E : INFINITY;
+    const float nlse_t = row_ok ? -p.lse_t[sidx] * LOG2E : -INFINITY;
     const float del_t = row_ok ? p.delta_t[sidx] : 0.f;
-    const float lse_s2 = (DUAL && row_ok) ? p.lse_s[sidx] * LOG2E : INFINITY;
+    const float nlse_s = (DUAL && row_ok) ? -p.lse_s[sidx] * LOG2E : -INFINITY;
     const float del_s = (DUAL && row_ok) ? p.delta_s[sidx] : 0.f;
     bool ok = true;
     auto wait_all = [&](uint32_t bar, uint32_t parity, int code) {
@@ -517,32 +635,37 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     for (int it = 0; it < n_iters && ok; ++it) {
       const bool st = iter_student(it);
       const int key0 = iter_key0(it) + half * 32;
-      ok = wait_all(sdp_full, it & 1, 331);
+      ok = wait_all(sdp_full(it & 1), (it >> 1) & 1, 331);
       if (!ok) break;
       tc_fence_after_sync();
+      const uint32_t ts = t_set(it) + lane_addr + half * 32;
       uint32_t sv[32], dpt[32], dps[32];
-      tmem_ld32(t_s + lane_addr + half * 32, sv);
-      tmem_ld32(t_dpt + lane_addr + half * 32, dpt);
-      if (st) tmem_ld32(t_dps + lane_addr + half * 32, dps);
+      tmem_ld32(ts, sv);
+      tmem_ld32(ts + 64, dpt);
+      if (DUAL && st) tmem_ld32(ts + 128, dps);
       tmem_ld_wait();
+      uint32_t dsp[16];
+      {
+        const int kb0 = iter_key0(it);
+        const bool full_t = (kb0 + 63 <= qlo) && (kb0 > qhi - p.w_t);
+        const bool full_s = (kb0 > qhi - p.w_s);
+        if (DUAL && st) {
+          if (full_t && full_s)
+            dq_elementwise<false, true>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, key0, p.w_t, p.w_s, dsp);
+          else
+            dq_elementwise<true, true>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, key0, p.w_t, p.w_s, dsp);
+        } else {
+          if (full_t)
+            dq_elementwise<false, false>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, key0, p.w_t, p.w_s, dsp);
+          else
+            dq_elementwise<true, false>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, key0, p.w_t, p.w_s, dsp);
+        }
+      }
       if (it >= 1) {
-        ok = wait_all(acc_done, (it - 1) & 1, 332);
+        ok = wait_all(acc_done, (it - 1) & 1, 332);  // dS tile is free again
         if (!ok) break;
       }
-      float ds[32];
-#pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        const int key = key0 + c;
-        const float s2 = __uint_as_float(sv[c]) * p.scale_log2;
-        const bool vis_t = key <= qpos && key > qpos - p.w_t;
-        float d = vis_t ? ex2(s2 - lse_t2) * (__uint_as_float(dpt[c]) - del_t) : 0.f;
-        if (DUAL && st) {
-          const bool vis_s = key <= qpos && key > qpos - p.w_s;
-          d += vis_s ? ex2(s2 - lse_s2) * (__uint_as_float(dps[c]) - del_s) : 0.f;
-        }
-        ds[c] = d * p.scale;
-      }
-      store_half_row(smem + S::DS_OFF, qrow, half, ds);
+      store_half_row_packed(smem + C::DS_OFF, qrow, half, dsp);
       fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncwarp();
@@ -559,17 +682,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
           uint32_t a[32];
           tmem_ld32(t_dq + lane_addr + half * COLS + c, a);
           tmem_ld_wait();
-          if (row_ok) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 o;
-              o.x = pack_bf16(__uint_as_float(a[j]), __uint_as_float(a[j + 1]));
-              o.y = pack_bf16(__uint_as_float(a[j + 2]), __uint_as_float(a[j + 3]));
-              o.z = pack_bf16(__uint_as_float(a[j + 4]), __uint_as_float(a[j + 5]));
-              o.w = pack_bf16(__uint_as_float(a[j + 6]), __uint_as_float(a[j + 7]));
-              *reinterpret_cast<uint4*>(p.dq + rowoff + half * COLS + c + j) = o;
-            }
-          }
+          if (row_ok) store_out32(p.dq + rowoff + half * COLS + c, a, p.scale);  // dS was kept unscaled
         }
       }
     }
@@ -600,24 +713,27 @@ __global__ void __launch_bounds__(256) attn_delta_kernel(const bf16* __restrict_
   if (lane == 0) delta[((bt / T) * H + h) * T + (bt % T)] = acc;
 }
 
+struct BwdMaps {
+  CUtensorMap q64, q128, k64, k128, v64, v128, dot64, dot128, dos64, dos128;
+};
+
 template <int D, bool DUAL>
-static int launch_bwd(const CUtensorMap& tq64, const CUtensorMap& tq128, const CUtensorMap& tk64,
-                      const CUtensorMap& tk128, const CUtensorMap& tv64, const CUtensorMap& tv128,
-                      const CUtensorMap& tdot64, const CUtensorMap& tdot128, const CUtensorMap& tdos64,
-                      const CUtensorMap& tdos128, const AttnBwdParams& p, int B, cudaStream_t stream) {
+static int launch_bwd(const BwdMaps& m, const AttnBwdParams& p, int B, cudaStream_t stream) {
   auto k1 = attn_bwd_dkdv_kernel<D, DUAL>;
   auto k2 = attn_bwd_dq_kernel<D, DUAL>;
+  constexpr int smem1 = DkdvCfg<D, DUAL>::TOTAL, smem2 = DqCfg<D, DUAL>::TOTAL;
+  static_assert(smem1 <= 232448 && smem2 <= 232448, "shared memory budget exceeded");
   static bool configured = false;
   if (!configured) {
-    TTCD_CUDA_CHECK(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, DkdvSmem<D>::TOTAL));
-    TTCD_CUDA_CHECK(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, DqSmem<D>::TOTAL));
+    TTCD_CUDA_CHECK(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1));
+    TTCD_CUDA_CHECK(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2));
     configured = true;
   }
   dim3 g1((p.Tk + 127) / 128, p.HK, B);
-  k1<<<g1, BWD_THREADS, DkdvSmem<D>::TOTAL, stream>>>(tq64, tk128, tv128, tdot64, tdos64, p);
+  k1<<<g1, BWD_THREADS, smem1, stream>>>(m.q64, m.k128, m.v128, m.dot64, m.dos64, p);
   TTCD_CUDA_CHECK(cudaGetLastError());
   dim3 g2(p.H, (p.Tq + 127) / 128, B);
-  k2<<<g2, BWD_THREADS, DqSmem<D>::TOTAL, stream>>>(tq128, tk64, tv64, tdot128, tdos128, p);
+  k2<<<g2, BWD_THREADS, smem2, stream>>>(m.q128, m.k64, m.v64, m.dot128, m.dos128, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -644,19 +760,20 @@ TTCD_EXPORT int ttcd_attn_bwd(const void* q, const void* k, const void* v, const
   using namespace ttcd;
   if (B <= 0 || Tq <= 0 || Tk < Tq || H <= 0 || HK <= 0 || H % HK != 0 || (D != 64 && D != 128)) return TTCD_ERR_ARG;
   const bool dual = do_s != nullptr;
-  CUtensorMap tq64, tq128, tk64, tk128, tv64, tv128, tdot64, tdot128, tdos64, tdos128;
+  BwdMaps m;
   const uint64_t qi = static_cast<uint64_t>(H) * D, ki = static_cast<uint64_t>(HK) * D;
   int rc = TTCD_OK;
-  auto mk = [&](CUtensorMap* m, const void* ptr, uint64_t inner, int rows, long long ld, long long sb, int box) {
-    if (rc == TTCD_OK) rc = make_tmap_bf16_3d(m, ptr, inner, rows, B, ld, sb, 64, box);
+  auto mk = [&](CUtensorMap* map, const void* ptr, uint64_t inner, int rows, long long ld, long long sb, int box) {
+    if (rc == TTCD_OK) rc = make_tmap_bf16_3d(map, ptr, inner, rows, B, ld, sb, 64, std::min(box, rows));
   };
-  mk(&tq64, q, qi, Tq, ldq, sq, 64);   mk(&tq128, q, qi, Tq, ldq, sq, 128);
-  mk(&tk64, k, ki, Tk, ldk, sk, 64);   mk(&tk128, k, ki, Tk, ldk, sk, 128);
-  mk(&tv64, v, ki, Tk, ldv, sv, 64);   mk(&tv128, v, ki, Tk, ldv, sv, 128);
-  mk(&tdot64, do_t, qi, Tq, qi, qi * Tq, 64);   mk(&tdot128, do_t, qi, Tq, qi, qi * Tq, 128);
+  mk(&m.q64, q, qi, Tq, ldq, sq, 64);   mk(&m.q128, q, qi, Tq, ldq, sq, 128);
+  mk(&m.k64, k, ki, Tk, ldk, sk, 64);   mk(&m.k128, k, ki, Tk, ldk, sk, 128);
+  mk(&m.v64, v, ki, Tk, ldv, sv, 64);   mk(&m.v128, v, ki, Tk, ldv, sv, 128);
+  mk(&m.dot64, do_t, qi, Tq, qi, qi * Tq, 64);   mk(&m.dot128, do_t, qi, Tq, qi, qi * Tq, 128);
   const void* dos = dual ? do_s : do_t;
-  mk(&tdos64, dos, qi, Tq, qi, qi * Tq, 64);    mk(&tdos128, dos, qi, Tq, qi, qi * Tq, 128);
+  mk(&m.dos64, dos, qi, Tq, qi, qi * Tq, 64);    mk(&m.dos128, dos, qi, Tq, qi, qi * Tq, 128);
   if (rc != TTCD_OK) return rc;
+  if (Tq < 128 || Tk < 128) return TTCD_ERR_ARG;  // every TMA box must fit inside its tensor
   const int big = 1 << 30;
   AttnBwdParams p;
   p.lse_t = lse_t; p.lse_s = lse_s; p.delta_t = delta_t; p.delta_s = delta_s;
@@ -667,9 +784,6 @@ TTCD_EXPORT int ttcd_attn_bwd(const void* q, const void* k, const void* v, const
   if (!dual) p.w_s = p.w_t;
   p.scale = scale; p.scale_log2 = scale * LOG2E;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
-  if (D == 128)
-    return dual ? launch_bwd<128, true>(tq64, tq128, tk64, tk128, tv64, tv128, tdot64, tdot128, tdos64, tdos128, p, B, stream)
-                : launch_bwd<128, false>(tq64, tq128, tk64, tk128, tv64, tv128, tdot64, tdot128, tdos64, tdos128, p, B, stream);
-  return dual ? launch_bwd<64, true>(tq64, tq128, tk64, tk128, tv64, tv128, tdot64, tdot128, tdos64, tdos128, p, B, stream)
-              : launch_bwd<64, false>(tq64, tq128, tk64, tk128, tv64, tv128, tdot64, tdot128, tdos64, tdos128, p, B, stream);
+  if (D == 128) return dual ? launch_bwd<128, true>(m, p, B, stream) : launch_bwd<128, false>(m, p, B, stream);
+  return dual ? launch_bwd<64, true>(m, p, B, stream) : launch_bwd<64, false>(m, p, B, stream);
 }

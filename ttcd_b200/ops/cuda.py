@@ -591,11 +591,18 @@ def _per_segment(fn, q, k, v, cu_seqlens):
     return torch.cat(outs, dim=1)
 
 
+def _too_short(q, k) -> bool:
+    """Single-token decode and other tiny problems (< one 128-row tile) use the PyTorch statement."""
+    return q.shape[1] < 128 or k.shape[1] < 128
+
+
 def attention(q, k, v, window=None, scale=None, cu_seqlens=None, return_lse=False):
     _check(q, "q")
+    if _too_short(q, k) and cu_seqlens is None:
+        return reference.attention(q, k, v, window, scale, None, return_lse)
     scale = q.shape[-1] ** -0.5 if scale is None else scale
     if cu_seqlens is not None:
-        out = _per_segment(lambda a, b, c: _Attention.apply(a, b, c, window, window, scale, False), q, k, v, cu_seqlens)
+        out = _per_segment(lambda a, b, c: attention(a, b, c, window, scale, None, True), q, k, v, cu_seqlens)
         return out if return_lse else out[0]
     o, lse = _Attention.apply(q, k, v, window, window, scale, False)
     return (o, lse) if return_lse else o
@@ -603,9 +610,11 @@ def attention(q, k, v, window=None, scale=None, cu_seqlens=None, return_lse=Fals
 
 def dual_window_attention(q, k, v, window_teacher, window_student, scale=None, cu_seqlens=None):
     _check(q, "q")
+    if _too_short(q, k) and cu_seqlens is None:
+        return reference.dual_window_attention(q, k, v, window_teacher, window_student, scale)
     scale = q.shape[-1] ** -0.5 if scale is None else scale
     if cu_seqlens is not None:
-        out = _per_segment(lambda a, b, c: _Attention.apply(a, b, c, window_teacher, window_student, scale, True),
+        out = _per_segment(lambda a, b, c: dual_window_attention(a, b, c, window_teacher, window_student, scale),
                            q, k, v, cu_seqlens)
         return out[0], out[1]
     o_t, o_s, _, _ = _Attention.apply(q, k, v, window_teacher, window_student, scale, True)
