@@ -126,8 +126,13 @@ def bench_attn(seqs, batches, wt=8192, ws=4096, bwd=False):
                 o_t, o_s, _, _ = cuda._Attention.apply(q, k, v, wt, ws, sc, True)
                 g_t, g_s = torch.randn_like(o_t), torch.randn_like(o_s)
                 ms = timeit(lambda: torch.autograd.grad([o_t, o_s], [q, k, v], [g_t, g_s], retain_graph=True), iters=5)
-                fl = 2.5 * attn_flops(B, T, H, D, wt) + 1.0 * attn_flops(B, T, H, D, ws)
+                fl = 2.5 * attn_flops(B, T, H, D, wt) + 2.5 * attn_flops(B, T, H, D, ws)  # two separate backward passes
                 row.update(fused_dual_bwd_ms=round(ms, 3), tflops=round(fl / ms / 1e9, 1))
+                o1, _ = cuda._Attention.apply(q, k, v, wt, wt, sc, False)
+                ms1 = timeit(lambda: torch.autograd.grad([o1], [q, k, v], [g_t], retain_graph=True), iters=5)
+                fl1 = 2.5 * attn_flops(B, T, H, D, wt)  # algorithmic: 5 GEMMs
+                row.update(single_window_bwd_ms=round(ms1, 3), single_tflops=round(fl1 / ms1 / 1e9, 1),
+                           single_frac_of_peak=round(fl1 / ms1 / 1e9 / tf_peak, 3))
                 if fa is not None:
                     ft = fa(q, k, v, causal=True, window_size=(wt - 1, 0))
                     fs = fa(q, k, v, causal=True, window_size=(ws - 1, 0))

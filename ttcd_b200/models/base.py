@@ -125,6 +125,20 @@ class DecoderModel(DecoderPreTrainedModel):
     def _block_kwargs(self, input_ids, inputs_embeds, kwargs) -> dict[str, Any]:
         return kwargs
 
+    # which blocks are recomputed in backward: "full" (all), "everyN", "ttt" (fast-weight blocks only)
+    checkpoint_policy: str = "full"
+
+    def _checkpoint_layer(self, layer) -> bool:
+        policy = self.checkpoint_policy
+        if policy == "full":
+            return True
+        if policy == "ttt":
+            return bool(getattr(layer, "is_ttt_layer", False))
+        if policy.startswith("every"):
+            n = max(1, int(policy[5:] or 1))
+            return getattr(layer, "layer_idx", 0) % n == 0
+        return False
+
     def forward(self, input_ids=None, attention_mask=None, past_key_values=None, inputs_embeds=None,
                 use_cache=None, output_attentions=None, output_hidden_states=None, return_dict=None,
                 **kwargs):
@@ -148,7 +162,7 @@ class DecoderModel(DecoderPreTrainedModel):
         for layer in self.layers:
             if output_hidden_states:
                 all_hidden += (hidden_states,)
-            if self.gradient_checkpointing and self.training:
+            if self.gradient_checkpointing and self.training and self._checkpoint_layer(layer):
                 hidden_states = torch.utils.checkpoint.checkpoint(
                     layer, hidden_states, attention_mask, None, False, use_reentrant=False, **kwargs)
             else:

@@ -257,5 +257,57 @@ class ShardedDataParallel:
                 dist.all_gather_into_tensor(g.flat_param, g.flat_param[self.rank * shard:(self.rank + 1) * shard].clone(),
                                             group=self.pg)
 
+    # ---------------------------------------------------------------------------------- full (unsharded) views
+    def _gather_flat(self, g: ParamGroup, which: str) -> torch.Tensor:
+        shard = getattr(g, which)
+        if self.world == 1:
+            return shard
+        full = torch.empty(g.numel, dtype=shard.dtype, device=shard.device)
+        dist.all_gather_into_tensor(full, shard.contiguous(), group=self.pg)
+        return full
+
+    def _global_names(self) -> dict[int, str]:
+        return {id(p): n for n, p in self.model.named_parameters()}
+
+    def gather_full(self, which: str = "master") -> dict[int, torch.Tensor]:
+        """{param.data_ptr(): full fp32 tensor} rebuilt from every rank's shard of ``which``."""
+        out = {}
+        for g in self.groups:
+            flat = self._gather_flat(g, which)
+            for p, o in zip(g.params, g.offsets):
+                out[p.data_ptr()] = flat[o:o + p.numel()].view(p.shape)
+        return out
+
+    def full_optimizer_state(self, template: bool = False) -> dict[str, torch.Tensor]:
+        """Per-parameter fp32 Adam moments (gathered), keyed by the global parameter name."""
+        names = self._global_names()
+        sd: dict[str, torch.Tensor] = {"step": torch.tensor(self.step_count, dtype=torch.int64)}
+        for g in self.groups:
+            flats = {}
+            for which in ("exp_avg", "exp_avg_sq"):
+                flats[which] = None if template else self._gather_flat(g, which)
+            for p, o in zip(g.params, g.offsets):
+                for which in ("exp_avg", "exp_avg_sq"):
+                    key = f"{names[id(p)]}.{which}"
+                    if template:
+                        sd[key] = torch.empty(p.shape, dtype=torch.float32, device="cpu")
+                    else:
+                        sd[key] = flats[which][o:o + p.numel()].view(p.shape)
+        return sd
+
+    def load_full_optimizer_state(self, sd: dict[str, torch.Tensor]) -> None:
+        names = self._global_names()
+        self.step_count = int(sd["step"])
+        for g in self.groups:
+            shard = g.numel // self.world
+            lo, hi = self.rank * shard, (self.rank + 1) * shard
+            for which in ("exp_avg", "exp_avg_sq"):
+                dst = getattr(g, which)
+                for p, o in zip(g.params, g.offsets):
+                    src = sd[f"{names[id(p)]}.{which}"].reshape(-1)
+                    a, b = max(o, lo), min(o + p.numel(), hi)
+                    if a < b:
+                        dst[a - lo:b - lo].copy_(src[a - o:b - o])
+
     def num_params(self) -> int:
         return sum(p.numel() for g in self.groups for p in g.params)

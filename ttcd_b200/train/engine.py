@@ -25,10 +25,14 @@ class EngineConfig:
     eps: float = 1e-15
     weight_decay: float = 0.1
     max_norm: float | None = 1.0
-    activation_checkpoint: str = "full"       # full | none
+    activation_checkpoint: str = "full"       # full | none | everyN (checkpoint every Nth block) | ttt (TTT blocks only)
     dtype: torch.dtype = torch.bfloat16
     skip_nan_inf: bool = False
     seed: int = 42
+    enable_muon: bool = False
+    muon_momentum: float = 0.95
+    tensor_parallel: int = 1
+    context_parallel: int = 1
 
 
 def load_model_config(path_or_cfg, **overrides):
@@ -71,8 +75,10 @@ class TrainEngine:
         self.model_config = model_config
         self.model = model if model is not None else build_model(model_config, self.device, self.cfg.dtype, self.cfg.seed)
         self.model.train()
-        if self.cfg.activation_checkpoint == "full":
-            self.model.model.gradient_checkpointing = True
+        self.set_activation_checkpointing(self.cfg.activation_checkpoint)
+        if self.cfg.tensor_parallel > 1 or self.cfg.context_parallel > 1:
+            from ..parallel import context as _ctx
+            _ctx.configure(self, tensor_parallel=self.cfg.tensor_parallel, context_parallel=self.cfg.context_parallel)
         multi = dist.is_initialized() and dist.get_world_size(process_group) > 1
         self.sdp = ShardedDataParallel(
             self.model, blocks=list(self.model.model.layers), process_group=process_group if multi else False,
@@ -85,6 +91,15 @@ class TrainEngine:
         self.tokens_seen = 0
 
     # ------------------------------------------------------------------------------------------
+    def set_activation_checkpointing(self, mode: str) -> None:
+        """'full' recomputes every block in backward (the reference recipe, sized for 80 GB GPUs);
+        'ttt' recomputes only the fast-weight blocks; 'everyN' every Nth block; 'none' keeps all
+        activations resident (fits at 64K tokens on a 180 GB B200)."""
+        inner = self.model.model
+        inner.gradient_checkpointing = mode != "none"
+        inner.checkpoint_policy = mode if mode != "none" else "full"
+        self.cfg.activation_checkpoint = mode
+
     def _to_device(self, t: torch.Tensor) -> torch.Tensor:
         if t.device == self.device:
             return t
