@@ -1,0 +1,46 @@
+"""Multi-GPU checks (symmetric memory, flag barrier, fused reduce-scatter / AdamW-push vs the NCCL baseline).
+
+Each test launches one process per GPU with torch.distributed.run and is skipped on machines with fewer
+than two GPUs.  Host-side protocol logic is covered on CPU in tests/test_comm_protocol.py.
+"""
+import os
+import socket
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _launch(what: str, nproc: int, timeout: int = 600) -> str:
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), str(ROOT / "tests" / "multi_gpu_worker.py"), what]
+    env = dict(os.environ, PYTHONPATH=str(ROOT))
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=str(ROOT))
+    out = res.stdout + res.stderr
+    assert res.returncode == 0 and "MULTI_GPU_OK" in out, out[-4000:]
+    return out
+
+
+def _ngpu() -> int:
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
+def test_symmetric_memory_and_barrier():
+    _launch("symmetric", min(_ngpu(), 8))
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
+def test_fused_sharded_step_matches_nccl_baseline():
+    _launch("sharded", 2)

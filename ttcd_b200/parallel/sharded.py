@@ -44,6 +44,7 @@ class ParamGroup:
     names: list[str]
     offsets: list[int] = field(default_factory=list)
     numel: int = 0             # padded to a multiple of 8 * world
+    base: int = 0              # element offset of this group inside the symmetric buffers
     flat_param: torch.Tensor | None = None   # bf16 [numel]
     flat_grad: torch.Tensor | None = None    # bf16 [numel]
     master: torch.Tensor | None = None       # fp32 [numel / world]
@@ -61,8 +62,12 @@ class ShardedDataParallel:
     def __init__(self, model: nn.Module, blocks: list[nn.Module] | None = None,
                  process_group: dist.ProcessGroup | None = None, *, lr: float = 1e-4, betas=(0.9, 0.95),
                  eps: float = 1e-8, weight_decay: float = 0.1, max_norm: float | None = 1.0,
-                 param_dtype: torch.dtype = torch.bfloat16, overlap: bool = True):
+                 param_dtype: torch.dtype = torch.bfloat16, overlap: bool = True, comm: str | None = None):
+        """``comm``: 'peer' = fused peer-memory kernels over NVLink (default on CUDA with the native
+        library), 'nccl' = the NCCL reduce-scatter / all-gather baseline (also TTCD_COMM=nccl)."""
+        import os
         self.model = model
+        self.comm = comm or os.environ.get("TTCD_COMM", "peer")
         self.pg = process_group
         self.world = dist.get_world_size(process_group) if (dist.is_initialized() and process_group is not False) else 1
         self.rank = dist.get_rank(process_group) if self.world > 1 else 0
@@ -75,6 +80,8 @@ class ShardedDataParallel:
         self.use_native = self.device.type == "cuda" and param_dtype == torch.bfloat16 and _native.available()
         if self.device.type == "cuda" and param_dtype == torch.bfloat16 and not self.use_native:
             _native.load(required=not _native.torch_fallback_allowed())
+        self.peer = self.world > 1 and self.use_native and self.comm == "peer"
+        self.sym_params = self.sym_grads = self.barrier = None
         self.groups: list[ParamGroup] = []
         self._build_groups(blocks)
         self.comm_stream = torch.cuda.Stream() if (self.device.type == "cuda" and self.world > 1) else None
@@ -110,8 +117,25 @@ class ShardedDataParallel:
                 g.offsets.append(off)
                 off += _align(p.numel(), 8)          # 16-byte aligned starts (TMA / vector loads)
             g.numel = _align(off, 8 * self.world)
-            g.flat_param = torch.zeros(g.numel, dtype=self.param_dtype, device=self.device)
-            g.flat_grad = torch.zeros(g.numel, dtype=self.param_dtype, device=self.device)
+        total = sum(g.numel for g in groups)
+        if self.peer:
+            # flat parameters and gradients live in peer-addressable memory: the fused kernels read every
+            # rank's gradients and write every rank's parameters directly over NVLink
+            from ..comm.symmetric import PeerBarrier, SymmetricBuffer
+            esize = torch.empty((), dtype=self.param_dtype).element_size()
+            self.sym_params = SymmetricBuffer(total * esize, self.pg, self.device)
+            self.sym_grads = SymmetricBuffer(total * esize, self.pg, self.device)
+            self.barrier = PeerBarrier(self.pg, slots=4)
+        base = 0
+        for g in groups:
+            g.base = base
+            if self.peer:
+                g.flat_param = self.sym_params.view(self.param_dtype, g.numel, base * esize)
+                g.flat_grad = self.sym_grads.view(self.param_dtype, g.numel, base * esize)
+            else:
+                g.flat_param = torch.zeros(g.numel, dtype=self.param_dtype, device=self.device)
+                g.flat_grad = torch.zeros(g.numel, dtype=self.param_dtype, device=self.device)
+            base += g.numel
             for p, o in zip(g.params, g.offsets):
                 view = g.flat_param[o:o + p.numel()].view(p.shape)
                 view.copy_(p.data)
@@ -124,7 +148,8 @@ class ShardedDataParallel:
             g.exp_avg_sq = torch.zeros(shard, dtype=torch.float32, device=self.device)
             if self.world > 1:
                 g.grad_shard = torch.zeros(shard, dtype=torch.float32, device=self.device)
-                g.grad_full32 = torch.empty(g.numel, dtype=torch.float32, device=self.device)
+                if not self.peer:
+                    g.grad_full32 = torch.empty(g.numel, dtype=torch.float32, device=self.device)
         self.groups = groups
 
     def resync_master(self) -> None:
@@ -153,22 +178,36 @@ class ShardedDataParallel:
         return hook
 
     def _reduce_group(self, g: ParamGroup):
-        """bf16 grads -> fp32 (scaled by 1/world) -> reduce-scatter into this rank's fp32 shard."""
+        """Gradient reduce-scatter of one group into this rank's fp32 shard, on the side stream.
+
+        peer mode: flag barrier (every rank's gradients of this group are complete), then ONE kernel pulls
+        this rank's shard from every peer over NVLink and fuses the bf16->fp32 cast, the 1/world scale and
+        the squared-norm partial.  nccl mode: cast/scale kernel + ``reduce_scatter_tensor``."""
         cur = torch.cuda.current_stream()
         self.comm_stream.wait_stream(cur)
         with torch.cuda.stream(self.comm_stream):
-            if self.use_native:
-                from ..ops import cuda
-                cuda.cast_scale(g.flat_grad, g.grad_full32, 1.0 / self.world)
+            if self.peer:
+                from ..ops import cuda  # noqa: F401
+                shard = g.numel // self.world
+                self.barrier.sync(slot=0, stream=self.comm_stream)
+                _native.call("ttcd_rs_cast_scale_norm", self.sym_grads.ptr_array(), _native.i32(self.world),
+                             _native.i64(g.base + self.rank * shard), _native.i64(shard), _native.f32(1.0 / self.world),
+                             _native.ptr(g.grad_shard), _native.ptr(self._norm_sq), _native.stream_ptr())
             else:
-                g.grad_full32.copy_(g.flat_grad)
-                g.grad_full32.mul_(1.0 / self.world)
-            dist.reduce_scatter_tensor(g.grad_shard, g.grad_full32, group=self.pg)
+                if self.use_native:
+                    from ..ops import cuda
+                    cuda.cast_scale(g.flat_grad, g.grad_full32, 1.0 / self.world)
+                else:
+                    g.grad_full32.copy_(g.flat_grad)
+                    g.grad_full32.mul_(1.0 / self.world)
+                dist.reduce_scatter_tensor(g.grad_shard, g.grad_full32, group=self.pg)
             g.reduce_event = torch.cuda.Event()
             g.reduce_event.record(self.comm_stream)
 
     # ---------------------------------------------------------------------------------- step
     def zero_grad(self):
+        if self.peer:
+            self._norm_sq.zero_()
         for g in self.groups:
             g.flat_grad.zero_()
             g.reduce_event = None
@@ -192,13 +231,16 @@ class ShardedDataParallel:
                 if g.reduce_event is None:
                     self._reduce_group(g)
             cur.wait_stream(self.comm_stream)
-        # ---- global grad norm (device side)
-        self._norm_sq.zero_()
-        if self.use_native:
+        # ---- global grad norm (device side); in peer mode the reduce kernels already accumulated it
+        if self.peer:
+            pass
+        elif self.use_native:
+            self._norm_sq.zero_()
             from ..ops import cuda
             for g in self.groups:
                 cuda.sumsq(self._local_grad(g), self._norm_sq)
         else:
+            self._norm_sq.zero_()
             for g in self.groups:
                 self._norm_sq += self._local_grad(g).float().pow(2).sum()
         if self.world > 1:
@@ -216,6 +258,16 @@ class ShardedDataParallel:
             shard = g.numel // self.world
             lo = self.rank * shard
             out_slice = g.flat_param[lo:lo + shard]
+            if self.peer:
+                bc1 = 1.0 - b1 ** self.step_count
+                bc2_sqrt = math.sqrt(1.0 - b2 ** self.step_count)
+                _native.call("ttcd_adamw_push", _native.ptr(g.master), _native.ptr(g.grad_shard), _native.ptr(g.exp_avg),
+                             _native.ptr(g.exp_avg_sq), self.sym_params.ptr_array(), _native.i32(self.world),
+                             _native.i64(g.base + lo), _native.i64(shard), _native.f32(lr), _native.f32(b1), _native.f32(b2),
+                             _native.f32(self.eps), _native.f32(self.weight_decay), _native.f32(bc1), _native.f32(bc2_sqrt),
+                             _native.ptr(self._coef), _native.ptr(self._skip if self.skip_nan_inf else None),
+                             _native.stream_ptr())
+                continue
             if self.use_native:
                 from ..ops import cuda
                 cuda.adamw_step(g.master, self._local_grad(g) if self.world > 1 else g.flat_grad[lo:lo + shard],
@@ -232,7 +284,10 @@ class ShardedDataParallel:
                 self.comm_stream.wait_stream(cur)
                 with torch.cuda.stream(self.comm_stream):
                     dist.all_gather_into_tensor(g.flat_param, out_slice, group=self.pg)
-        if self.world > 1:
+        if self.peer:
+            # every rank's pushes have landed everywhere (and nobody still reads this rank's gradients)
+            self.barrier.sync(slot=1)
+        elif self.world > 1:
             cur.wait_stream(self.comm_stream)
         return norm
 
