@@ -42,6 +42,8 @@ struct AttnBwdParams {
   int Tq, Tk, H, HK;
   int w_t, w_s;
   float scale, scale_log2;
+  // context parallel: keys [0, halo_len) live in the previous rank's K/V buffers (rows halo_row0..)
+  int halo_len, halo_row0;
 };
 
 // 32 accumulator columns of one TMEM lane -> 32 bf16 (one 64-byte half row) of a K-major SW128 tile
@@ -187,7 +189,8 @@ template <int D, bool DUAL>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                      const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ CUtensorMap tma_dot,
-                     const __grid_constant__ CUtensorMap tma_dos, const AttnBwdParams p) {
+                     const __grid_constant__ CUtensorMap tma_dos, const __grid_constant__ CUtensorMap tma_kh,
+                     const __grid_constant__ CUtensorMap tma_vh, const AttnBwdParams p) {
   using C = DkdvCfg<D, DUAL>;
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sbase = smem_u32(smem);
@@ -313,8 +316,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       mbar_expect_tx(kv_full, 2 * C::DB * C::KEY_REGION);
 #pragma unroll
       for (int d = 0; d < C::DB; ++d) {
-        tma_load_3d(sbase + C::K_OFF + d * C::KEY_REGION, &tma_k, kv_full, kvh * D + d * 64, n0, b);
-        tma_load_3d(sbase + C::V_OFF + d * C::KEY_REGION, &tma_v, kv_full, kvh * D + d * 64, n0, b);
+        const bool halo = n0 < p.halo_len;  // plain TMA loads from the previous rank's memory
+        const int krow = halo ? p.halo_row0 + n0 : n0 - p.halo_len;
+        tma_load_3d(sbase + C::K_OFF + d * C::KEY_REGION, halo ? &tma_kh : &tma_k, kv_full, kvh * D + d * 64, krow, b);
+        tma_load_3d(sbase + C::V_OFF + d * C::KEY_REGION, halo ? &tma_vh : &tma_v, kv_full, kvh * D + d * 64, krow, b);
       }
       for (int it = 0; it < C::NSLOTS - 1 && it < n_iters; ++it) load_tiles(it);
       ok = mbar_wait(kv_full, 0, abort_flag, 301);
@@ -482,7 +487,8 @@ template <int D, bool DUAL>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                    const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ CUtensorMap tma_dot,
-                   const __grid_constant__ CUtensorMap tma_dos, const AttnBwdParams p) {
+                   const __grid_constant__ CUtensorMap tma_dos, const __grid_constant__ CUtensorMap tma_kh,
+                   const __grid_constant__ CUtensorMap tma_vh, const AttnBwdParams p) {
   using C = DqCfg<D, DUAL>;
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sbase = smem_u32(smem);
@@ -541,10 +547,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         const int slot = it % C::NSLOTS;
         const uint32_t base = slot_base(it);
         mbar_expect_tx(kv_full(slot), 2 * C::KV_BYTES);
-#pragma unroll
+        const int key0 = iter_key0(it);
+        const bool halo = key0 < p.halo_len;
+        const int krow = halo ? p.halo_row0 + key0 : key0 - p.halo_len;
         for (int d = 0; d < C::DB; ++d) {
-          tma_load_3d(base + d * C::KV_REGION, &tma_k, kv_full(slot), kvh * D + d * 64, iter_key0(it), b);
-          tma_load_3d(base + C::KV_BYTES + d * C::KV_REGION, &tma_v, kv_full(slot), kvh * D + d * 64, iter_key0(it), b);
+          tma_load_3d(base + d * C::KV_REGION, halo ? &tma_kh : &tma_k, kv_full(slot), kvh * D + d * 64, krow, b);
+          tma_load_3d(base + C::KV_BYTES + d * C::KV_REGION, halo ? &tma_vh : &tma_v, kv_full(slot), kvh * D + d * 64, krow, b);
         }
       };
       auto issue_sdp = [&](int it) {
@@ -714,7 +722,7 @@ __global__ void __launch_bounds__(256) attn_delta_kernel(const bf16* __restrict_
 }
 
 struct BwdMaps {
-  CUtensorMap q64, q128, k64, k128, v64, v128, dot64, dot128, dos64, dos128;
+  CUtensorMap q64, q128, k64, k128, v64, v128, dot64, dot128, dos64, dos128, kh64, kh128, vh64, vh128;
 };
 
 template <int D, bool DUAL>
@@ -730,10 +738,10 @@ static int launch_bwd(const BwdMaps& m, const AttnBwdParams& p, int B, cudaStrea
     configured = true;
   }
   dim3 g1((p.Tk + 127) / 128, p.HK, B);
-  k1<<<g1, BWD_THREADS, smem1, stream>>>(m.q64, m.k128, m.v128, m.dot64, m.dos64, p);
+  k1<<<g1, BWD_THREADS, smem1, stream>>>(m.q64, m.k128, m.v128, m.dot64, m.dos64, m.kh128, m.vh128, p);
   TTCD_CUDA_CHECK(cudaGetLastError());
   dim3 g2(p.H, (p.Tq + 127) / 128, B);
-  k2<<<g2, BWD_THREADS, smem2, stream>>>(m.q128, m.k64, m.v64, m.dot128, m.dos128, p);
+  k2<<<g2, BWD_THREADS, smem2, stream>>>(m.q128, m.k64, m.v64, m.dot128, m.dos128, m.kh64, m.vh64, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -750,40 +758,58 @@ TTCD_EXPORT int ttcd_attn_delta(const void* o, const void* d_o, float* delta, lo
   return static_cast<int>(cudaGetLastError());
 }
 
-// Gradients of (dual-window) attention.  q/k/v strided as in ttcd_attn_fwd; do_t/do_s contiguous
-// [B, Tq, H, D] (do_s null => single window); dq [B,Tq,H,D], dk/dv [B,Tk,HK,D] bf16 contiguous.
-TTCD_EXPORT int ttcd_attn_bwd(const void* q, const void* k, const void* v, const void* do_t, const void* do_s,
-                              const float* lse_t, const float* lse_s, const float* delta_t, const float* delta_s,
-                              void* dq, void* dk, void* dv, int B, int Tq, int Tk, int H, int HK, int D,
-                              long long ldq, long long ldk, long long ldv, long long sq, long long sk, long long sv,
-                              int window_t, int window_s, float scale, void* stream_ptr) {
+// Gradients of (dual-window) attention.  q/k/v strided as in ttcd_attn_fwd_cp; do_t/do_s contiguous
+// [B, Tq, H, D] (do_s null => single window); dq [B,Tq,H,D], dk/dv [B, halo_len + Tk_local, HK, D] bf16
+// contiguous: their first halo_len rows are the gradients of the previous rank's keys.
+TTCD_EXPORT int ttcd_attn_bwd_cp(const void* q, const void* k, const void* v, const void* k_halo, const void* v_halo,
+                                 const void* do_t, const void* do_s, const float* lse_t, const float* lse_s,
+                                 const float* delta_t, const float* delta_s, void* dq, void* dk, void* dv, int B, int Tq,
+                                 int Tk_local, int H, int HK, int D, long long ldq, long long ldk, long long ldv,
+                                 long long sq, long long sk, long long sv, int halo_len, int halo_rows, int window_t,
+                                 int window_s, float scale, void* stream_ptr) {
   using namespace ttcd;
-  if (B <= 0 || Tq <= 0 || Tk < Tq || H <= 0 || HK <= 0 || H % HK != 0 || (D != 64 && D != 128)) return TTCD_ERR_ARG;
+  if (B <= 0 || Tq < 128 || Tk_local < Tq || H <= 0 || HK <= 0 || H % HK != 0 || (D != 64 && D != 128)) return TTCD_ERR_ARG;
+  if (halo_len < 0 || halo_len % 128 != 0 || (halo_len > 0 && (k_halo == nullptr || v_halo == nullptr || halo_rows < halo_len)))
+    return TTCD_ERR_ARG;
   const bool dual = do_s != nullptr;
   BwdMaps m;
   const uint64_t qi = static_cast<uint64_t>(H) * D, ki = static_cast<uint64_t>(HK) * D;
   int rc = TTCD_OK;
   auto mk = [&](CUtensorMap* map, const void* ptr, uint64_t inner, int rows, long long ld, long long sb, int box) {
-    if (rc == TTCD_OK) rc = make_tmap_bf16_3d(map, ptr, inner, rows, B, ld, sb, 64, std::min(box, rows));
+    if (rc == TTCD_OK) rc = make_tmap_bf16_3d(map, ptr, inner, rows, B, ld, sb, 64, box);
   };
-  mk(&m.q64, q, qi, Tq, ldq, sq, 64);   mk(&m.q128, q, qi, Tq, ldq, sq, 128);
-  mk(&m.k64, k, ki, Tk, ldk, sk, 64);   mk(&m.k128, k, ki, Tk, ldk, sk, 128);
-  mk(&m.v64, v, ki, Tk, ldv, sv, 64);   mk(&m.v128, v, ki, Tk, ldv, sv, 128);
+  mk(&m.q64, q, qi, Tq, ldq, sq, 64);         mk(&m.q128, q, qi, Tq, ldq, sq, 128);
+  mk(&m.k64, k, ki, Tk_local, ldk, sk, 64);   mk(&m.k128, k, ki, Tk_local, ldk, sk, 128);
+  mk(&m.v64, v, ki, Tk_local, ldv, sv, 64);   mk(&m.v128, v, ki, Tk_local, ldv, sv, 128);
   mk(&m.dot64, do_t, qi, Tq, qi, qi * Tq, 64);   mk(&m.dot128, do_t, qi, Tq, qi, qi * Tq, 128);
   const void* dos = dual ? do_s : do_t;
   mk(&m.dos64, dos, qi, Tq, qi, qi * Tq, 64);    mk(&m.dos128, dos, qi, Tq, qi, qi * Tq, 128);
+  m.kh64 = m.k64; m.kh128 = m.k128; m.vh64 = m.v64; m.vh128 = m.v128;
+  if (halo_len > 0) {
+    mk(&m.kh64, k_halo, ki, halo_rows, ldk, sk, 64);   mk(&m.kh128, k_halo, ki, halo_rows, ldk, sk, 128);
+    mk(&m.vh64, v_halo, ki, halo_rows, ldv, sv, 64);   mk(&m.vh128, v_halo, ki, halo_rows, ldv, sv, 128);
+  }
   if (rc != TTCD_OK) return rc;
-  if (Tq < 128 || Tk < 128) return TTCD_ERR_ARG;  // every TMA box must fit inside its tensor
   const int big = 1 << 30;
   AttnBwdParams p;
   p.lse_t = lse_t; p.lse_s = lse_s; p.delta_t = delta_t; p.delta_s = delta_s;
   p.dq = static_cast<bf16*>(dq); p.dk = static_cast<bf16*>(dk); p.dv = static_cast<bf16*>(dv);
-  p.Tq = Tq; p.Tk = Tk; p.H = H; p.HK = HK;
+  p.Tq = Tq; p.Tk = Tk_local + halo_len; p.H = H; p.HK = HK;
   p.w_t = window_t > 0 ? window_t : big;
   p.w_s = window_s > 0 ? window_s : big;
   if (!dual) p.w_s = p.w_t;
   p.scale = scale; p.scale_log2 = scale * LOG2E;
+  p.halo_len = halo_len; p.halo_row0 = halo_rows - halo_len;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   if (D == 128) return dual ? launch_bwd<128, true>(m, p, B, stream) : launch_bwd<128, false>(m, p, B, stream);
   return dual ? launch_bwd<64, true>(m, p, B, stream) : launch_bwd<64, false>(m, p, B, stream);
+}
+
+TTCD_EXPORT int ttcd_attn_bwd(const void* q, const void* k, const void* v, const void* do_t, const void* do_s,
+                              const float* lse_t, const float* lse_s, const float* delta_t, const float* delta_s,
+                              void* dq, void* dk, void* dv, int B, int Tq, int Tk, int H, int HK, int D,
+                              long long ldq, long long ldk, long long ldv, long long sq, long long sk, long long sv,
+                              int window_t, int window_s, float scale, void* stream_ptr) {
+  return ttcd_attn_bwd_cp(q, k, v, nullptr, nullptr, do_t, do_s, lse_t, lse_s, delta_t, delta_s, dq, dk, dv, B, Tq, Tk, H,
+                          HK, D, ldq, ldk, ldv, sq, sk, sv, 0, 0, window_t, window_s, scale, stream_ptr);
 }

@@ -30,6 +30,9 @@ struct AttnFwdParams {
   int Tq, Tk, H, HK;
   int w_t, w_s;                  // window sizes in keys (w_s is the only window in single mode)
   float scale_log2;              // softmax scale * log2(e)
+  // context parallel: keys [0, halo_len) are the tail of the PREVIOUS rank's sequence shard and are read
+  // straight from that rank's memory (rows halo_row0.. of its K/V buffers); keys >= halo_len are local
+  int halo_len, halo_row0;
 };
 
 template <int D>
@@ -58,7 +61,8 @@ __device__ __forceinline__ float fast_exp2(float x) {
 template <int D, bool DUAL>
 __global__ void __launch_bounds__(ATT_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
-                const __grid_constant__ CUtensorMap tma_v, const AttnFwdParams p) {
+                const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ CUtensorMap tma_kh,
+                const __grid_constant__ CUtensorMap tma_vh, const AttnFwdParams p) {
   using S = AttnSmem<D>;
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sbase = smem_u32(smem);
@@ -138,18 +142,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       auto load_k = [&](int i) {
         const int slot = i & 1;
         mbar_expect_tx(k_full(slot), S::KV_BYTES);
-#pragma unroll
+        const int key0 = block_key0(i);
+        const bool halo = key0 < p.halo_len;   // plain (non-multicast) TMA load from the peer's memory
+        const CUtensorMap* map = halo ? &tma_kh : &tma_k;
+        const int row = halo ? p.halo_row0 + key0 : key0 - p.halo_len;
         for (int d = 0; d < S::DB; ++d)
-          tma_load_3d(sbase + S::K_OFF + slot * S::KV_BYTES + d * S::KV_REGION, &tma_k, k_full(slot),
-                      kvh * D + d * 64, block_key0(i), b);
+          tma_load_3d(sbase + S::K_OFF + slot * S::KV_BYTES + d * S::KV_REGION, map, k_full(slot),
+                      kvh * D + d * 64, row, b);
       };
       auto load_v = [&](int i) {
         const int slot = i & 1;
         mbar_expect_tx(v_full(slot), S::KV_BYTES);
-#pragma unroll
+        const int key0 = block_key0(i);
+        const bool halo = key0 < p.halo_len;
+        const CUtensorMap* map = halo ? &tma_vh : &tma_v;
+        const int row = halo ? p.halo_row0 + key0 : key0 - p.halo_len;
         for (int d = 0; d < S::DB; ++d)
-          tma_load_3d(sbase + S::V_OFF + slot * S::KV_BYTES + d * S::KV_REGION, &tma_v, v_full(slot),
-                      kvh * D + d * 64, block_key0(i), b);
+          tma_load_3d(sbase + S::V_OFF + slot * S::KV_BYTES + d * S::KV_REGION, map, v_full(slot),
+                      kvh * D + d * 64, row, b);
       };
       auto issue_s = [&](int i) {
         const uint32_t kslot = sbase + S::K_OFF + (i & 1) * S::KV_BYTES;
@@ -377,7 +387,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
 
 template <int D, bool DUAL>
 static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                           const AttnFwdParams& p, int B, cudaStream_t stream) {
+                           const CUtensorMap& tkh, const CUtensorMap& tvh, const AttnFwdParams& p, int B,
+                           cudaStream_t stream) {
   using S = AttnSmem<D>;
   auto kern = attn_fwd_kernel<D, DUAL>;
   static bool configured = false;
@@ -386,7 +397,7 @@ static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const C
     configured = true;
   }
   dim3 grid(p.H, (p.Tq + ATT_BM - 1) / ATT_BM, B);
-  kern<<<grid, ATT_THREADS, S::TOTAL, stream>>>(tq, tk, tv, p);
+  kern<<<grid, ATT_THREADS, S::TOTAL, stream>>>(tq, tk, tv, tkh, tvh, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -395,22 +406,37 @@ static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const C
 TTCD_DEFINE_STATUS_READER(attn)
 
 // q: [B, Tq, *] with token stride ldq and batch stride sq (elements), head h at column h*D.
-// k, v: [B, Tk, *] likewise with HK heads.  o_t (and o_s, lse_s when dual) are contiguous
+// k, v: [B, Tk_local, *] likewise with HK heads.  o_t (and o_s, lse_s when dual) are contiguous
 // [B, Tq, H, D] / [B, H, Tq].  window <= 0 means unlimited (full causal).
-TTCD_EXPORT int ttcd_attn_fwd(const void* q, const void* k, const void* v, void* o_t, void* o_s, float* lse_t,
-                              float* lse_s, int B, int Tq, int Tk, int H, int HK, int D, long long ldq,
-                              long long ldk, long long ldv, long long sq, long long sk, long long sv,
-                              int window_t, int window_s, float scale, void* stream_ptr) {
+// Context parallel: k_halo / v_halo point at the previous rank's K / V buffers (same layout and strides,
+// halo_rows rows); its last halo_len rows are prepended to the local keys.  halo_len % 128 == 0.
+TTCD_EXPORT int ttcd_attn_fwd_cp(const void* q, const void* k, const void* v, const void* k_halo, const void* v_halo,
+                                 void* o_t, void* o_s, float* lse_t, float* lse_s, int B, int Tq, int Tk_local, int H,
+                                 int HK, int D, long long ldq, long long ldk, long long ldv, long long sq, long long sk,
+                                 long long sv, int halo_len, int halo_rows, int window_t, int window_s, float scale,
+                                 void* stream_ptr) {
   using namespace ttcd;
-  if (B <= 0 || Tq <= 0 || Tk < Tq || H <= 0 || HK <= 0 || H % HK != 0 || (D != 64 && D != 128)) return TTCD_ERR_ARG;
+  const int Tk = Tk_local + halo_len;
+  if (B <= 0 || Tq < ATT_BM || Tk_local < Tq || H <= 0 || HK <= 0 || H % HK != 0 || (D != 64 && D != 128))
+    return TTCD_ERR_ARG;
+  if (halo_len < 0 || halo_len % 128 != 0 || (halo_len > 0 && (k_halo == nullptr || v_halo == nullptr || halo_rows < halo_len)))
+    return TTCD_ERR_ARG;
   const bool dual = o_s != nullptr;
-  CUtensorMap tq, tk, tv;
+  CUtensorMap tq, tk, tv, tkh, tvh;
   int rc = make_tmap_bf16_3d(&tq, q, static_cast<uint64_t>(H) * D, Tq, B, ldq, sq, 64, ATT_BM);
   if (rc != TTCD_OK) return rc;
-  rc = make_tmap_bf16_3d(&tk, k, static_cast<uint64_t>(HK) * D, Tk, B, ldk, sk, 64, ATT_BN);
+  rc = make_tmap_bf16_3d(&tk, k, static_cast<uint64_t>(HK) * D, Tk_local, B, ldk, sk, 64, ATT_BN);
   if (rc != TTCD_OK) return rc;
-  rc = make_tmap_bf16_3d(&tv, v, static_cast<uint64_t>(HK) * D, Tk, B, ldv, sv, 64, ATT_BN);
+  rc = make_tmap_bf16_3d(&tv, v, static_cast<uint64_t>(HK) * D, Tk_local, B, ldv, sv, 64, ATT_BN);
   if (rc != TTCD_OK) return rc;
+  tkh = tk;
+  tvh = tv;
+  if (halo_len > 0) {
+    rc = make_tmap_bf16_3d(&tkh, k_halo, static_cast<uint64_t>(HK) * D, halo_rows, B, ldk, sk, 64, ATT_BN);
+    if (rc != TTCD_OK) return rc;
+    rc = make_tmap_bf16_3d(&tvh, v_halo, static_cast<uint64_t>(HK) * D, halo_rows, B, ldv, sv, 64, ATT_BN);
+    if (rc != TTCD_OK) return rc;
+  }
   const int big = 1 << 30;
   AttnFwdParams p;
   p.o_t = static_cast<bf16*>(o_t); p.o_s = static_cast<bf16*>(o_s);
@@ -420,9 +446,19 @@ TTCD_EXPORT int ttcd_attn_fwd(const void* q, const void* k, const void* v, void*
   p.w_s = window_s > 0 ? window_s : big;
   if (!dual) p.w_s = p.w_t;  // single-window mode runs phase A only, with the one window
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.halo_len = halo_len;
+  p.halo_row0 = halo_rows - halo_len;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
-  if (D == 128) return dual ? launch_attn_fwd<128, true>(tq, tk, tv, p, B, stream)
-                            : launch_attn_fwd<128, false>(tq, tk, tv, p, B, stream);
-  return dual ? launch_attn_fwd<64, true>(tq, tk, tv, p, B, stream)
-              : launch_attn_fwd<64, false>(tq, tk, tv, p, B, stream);
+  if (D == 128) return dual ? launch_attn_fwd<128, true>(tq, tk, tv, tkh, tvh, p, B, stream)
+                            : launch_attn_fwd<128, false>(tq, tk, tv, tkh, tvh, p, B, stream);
+  return dual ? launch_attn_fwd<64, true>(tq, tk, tv, tkh, tvh, p, B, stream)
+              : launch_attn_fwd<64, false>(tq, tk, tv, tkh, tvh, p, B, stream);
+}
+
+TTCD_EXPORT int ttcd_attn_fwd(const void* q, const void* k, const void* v, void* o_t, void* o_s, float* lse_t,
+                              float* lse_s, int B, int Tq, int Tk, int H, int HK, int D, long long ldq,
+                              long long ldk, long long ldv, long long sq, long long sk, long long sv,
+                              int window_t, int window_s, float scale, void* stream_ptr) {
+  return ttcd_attn_fwd_cp(q, k, v, nullptr, nullptr, o_t, o_s, lse_t, lse_s, B, Tq, Tk, H, HK, D, ldq, ldk, ldv, sq, sk,
+                          sv, 0, 0, window_t, window_s, scale, stream_ptr);
 }

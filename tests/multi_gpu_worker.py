@@ -75,7 +75,7 @@ def main():
         check_symmetric()
     if what in ("all", "sharded"):
         check_sharded_modes()
-    if what in ("all", "cp") and "cp" in sys.argv[1:]:
+    if what in ("all", "cp"):
         from tests.multi_gpu_cp import check_context_parallel
         check_context_parallel()
     torch.cuda.synchronize()

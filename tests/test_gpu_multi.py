@@ -44,3 +44,8 @@ def test_symmetric_memory_and_barrier():
 @pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
 def test_fused_sharded_step_matches_nccl_baseline():
     _launch("sharded", 2)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
+def test_context_parallel_halo_attention_matches_single_gpu():
+    _launch("cp", 2)

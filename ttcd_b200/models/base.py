@@ -228,6 +228,7 @@ class DecoderForCausalLM(DecoderPreTrainedModel):
                 return_dict=None, logits_to_keep: int | None = 0, **kwargs):
         return_dict = True if return_dict is None else return_dict
         kwargs.pop("num_logits_to_keep", None)
+        shift_labels = kwargs.pop("shift_labels", True)   # False: the caller already aligned labels to positions
         outputs = self.model(input_ids=input_ids, attention_mask=attention_mask, past_key_values=past_key_values,
                              inputs_embeds=inputs_embeds, use_cache=use_cache,
                              output_hidden_states=output_hidden_states, return_dict=True, **kwargs)
@@ -243,7 +244,8 @@ class DecoderForCausalLM(DecoderPreTrainedModel):
             criterion = self.criterion if getattr(self, "criterion", None) is not None else self._default_criterion()
             ignore = getattr(criterion, "ignore_index", IGNORE_INDEX)
             labels = labels.to(hidden_states.device)
-            labels = torch.cat((labels[..., 1:], torch.full_like(labels[:, :1], ignore)), dim=1)
+            if shift_labels:
+                labels = torch.cat((labels[..., 1:], torch.full_like(labels[:, :1], ignore)), dim=1)
             if fuse_lce:
                 loss = criterion(hidden_states, labels, self.lm_head.weight, self.lm_head.bias)
             else:

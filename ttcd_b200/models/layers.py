@@ -196,6 +196,9 @@ class Attention(nn.Module):
                 use_cache: bool = False, cu_seqlens=None, positions=None, **_):
         B, T, _ = hidden_states.shape
         offset = 0
+        cp = _cp_state() if past_key_values is None else None
+        if cp is not None:
+            offset = cp.position_offset(T)
         if past_key_values is not None:
             offset = past_key_values.get_seq_length(self.layer_idx)
             if attention_mask is not None:
@@ -209,11 +212,21 @@ class Attention(nn.Module):
             k_all, v_all = past_key_values.update(k, v, self.layer_idx, self.window_size)
             if had_content:
                 k, v = k_all, v_all
-        if attention_mask is not None and not bool(attention_mask.all()):
+        if cp is not None:
+            from ..parallel import context as _context
+            o = _context.attention(q, k, v, self.window_size, None, self.layer_idx)
+        elif attention_mask is not None and not bool(attention_mask.all()):
             o = _padded_attention(q, k, v, attention_mask, self.window_size)
         else:
             o = ops.attention(q, k, v, window=self.window_size, cu_seqlens=cu_seqlens)
         return self.finish(o, hidden_states), past_key_values
+
+
+def _cp_state():
+    """The active context-parallel state, if any (sequence shards + K/V halo from the previous rank)."""
+    import sys
+    mod = sys.modules.get("ttcd_b200.parallel.context")
+    return mod.active() if mod is not None else None
 
 
 def positions_from_cu_seqlens(cu_seqlens: torch.Tensor, total: int, device) -> torch.Tensor:

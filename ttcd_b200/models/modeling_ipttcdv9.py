@@ -30,7 +30,7 @@ from torch.profiler import record_function
 from .. import ops
 from .base import DecoderForCausalLM, DecoderModel
 from .configuration import IPTTCDv9Config
-from .layers import GatedMLP, RMSNorm, WindowKVCache
+from .layers import GatedMLP, RMSNorm, WindowKVCache, _cp_state
 from .modeling_ipttt import make_depthwise_conv, pad_to_chunks
 from .modeling_transformer import build_attention
 
@@ -128,7 +128,7 @@ class IPTTCDMLP(GatedMLP):
                     z_out, z_tgt, z_hat_p, beta, w_down, w_update_t, lr=self.ttt_lr,
                     update_every=min(T, self.ttt_update_every), state_dtype=self._state_dtype(compute_dtype),
                     normalize_student=self.ttt_normalize_student_features, norm_proj_diff=self.ttt_norm_proj_diff,
-                    post_proj=post, return_last_dw_norm=True)
+                    post_proj=post, return_last_dw_norm=True, cp=_cp_state() if self.training else None)
             if self.training and last is not None:
                 self._last_delta_w_norm_t = last  # device scalar; read lazily, no host sync here
         return y.reshape(b, T * C, -1)[:, :seq_len]
@@ -220,6 +220,9 @@ class IPTTCDBlock(nn.Module):
         """Shared-QKV teacher+student attention; returns (teacher_attn_out, student_attn_out)."""
         attn = self.attn
         offset = 0
+        cp = _cp_state() if past_key_values is None else None
+        if cp is not None:
+            offset = cp.position_offset(hidden_states.shape[1])
         if past_key_values is not None:
             offset = past_key_values.get_seq_length(attn.layer_idx)
         cu = kwargs.get("cu_seqlens")
@@ -230,7 +233,11 @@ class IPTTCDBlock(nn.Module):
             k_all, v_all = past_key_values.update(k, v, attn.layer_idx, attn.window_size)
             if had_content:
                 k, v = k_all, v_all
-        o_t, o_s = ops.dual_window_attention(q, k, v, attn.window_size, self.student_window, cu_seqlens=cu)
+        if cp is not None:
+            from ..parallel import context as _context
+            o_t, o_s = _context.dual_window_attention(q, k, v, attn.window_size, self.student_window, None, attn.layer_idx)
+        else:
+            o_t, o_s = ops.dual_window_attention(q, k, v, attn.window_size, self.student_window, cu_seqlens=cu)
         b = hidden_states.shape[0]
         both = attn.finish(torch.cat([o_t, o_s], dim=0), torch.cat([hidden_states, hidden_states], dim=0)
                            if attn.use_output_gate else hidden_states)

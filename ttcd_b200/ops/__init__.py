@@ -136,16 +136,16 @@ def lse_merge(o_a, lse_a, o_b, lse_b):
 # -- fast-weight scan ----------------------------------------------------------------------
 
 def ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, *, lr, update_every, state_dtype=None,
-             normalize_student=False, norm_proj_diff=False, post_proj=None, return_last_dw_norm=False):
+             normalize_student=False, norm_proj_diff=False, post_proj=None, return_last_dw_norm=False, cp=None):
     plain = not normalize_student and not norm_proj_diff and post_proj is None
     if _native.use_native(z_out) and plain and (state_dtype in (None, torch.bfloat16)):
         return reference.ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, lr=lr,
                                   update_every=update_every, state_dtype=torch.float32,
-                                  return_last_dw_norm=return_last_dw_norm, matmul=_cuda().matmul)
+                                  return_last_dw_norm=return_last_dw_norm, matmul=_cuda().matmul, cp=cp)
     return reference.ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, lr=lr,
                               update_every=update_every, state_dtype=state_dtype,
                               normalize_student=normalize_student, norm_proj_diff=norm_proj_diff,
-                              post_proj=post_proj, return_last_dw_norm=return_last_dw_norm)
+                              post_proj=post_proj, return_last_dw_norm=return_last_dw_norm, cp=cp)
 
 
 # -- losses ------------------------------------------------------------------------------------

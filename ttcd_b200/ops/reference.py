@@ -239,7 +239,7 @@ def dwconv_sequence(x, weight, bias=None, activation: str | None = None, residua
 def ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, *, lr: float, update_every: int,
              state_dtype: torch.dtype | None = None, normalize_student: bool = False,
              norm_proj_diff: bool = False, post_proj: torch.Tensor | None = None,
-             return_last_dw_norm: bool = False, matmul=torch.matmul):
+             return_last_dw_norm: bool = False, matmul=torch.matmul, cp=None):
     """Grouped fast-weight scan.
 
     ``matmul`` is the batched-matmul primitive (torch.matmul, or the tensor-core
@@ -254,6 +254,10 @@ def ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, *, lr: float, update
         dW_j = P_j^T @ z_hat_j                      (j = 0..T-2)
         W_i  = w_down + lr * sum_{j<i} dW_j          (prefix kept in state_dtype, grouped)
         Y_i  = z_out_i @ W_i^T
+
+    ``cp`` (context-parallel state with ``rank``/``size``): the T chunks are this rank's slice of a
+    longer sequence; the scan then starts from ``w_down + lr * sum`` of every earlier rank's updates
+    (exclusive prefix over ranks) and this rank's last chunk also produces an update for its successors.
     """
     b, T, C, d_i = z_out.shape
     compute_dtype = z_out.dtype
@@ -261,6 +265,32 @@ def ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, *, lr: float, update
     w_cur = w_down.to(state_dtype).unsqueeze(0).expand(b, -1, -1)
     lr_t = w_cur.new_tensor(lr)
     group = max(1, min(T, update_every))
+
+    def delta_w(lo: int, hi: int):
+        diff = z_tgt[:, lo:hi] - z_hat[:, lo:hi]
+        proj = matmul(diff, w_update_t.to(compute_dtype))
+        if norm_proj_diff:
+            proj = F.normalize(proj, p=2, dim=-1, eps=1e-6)
+        zh = z_hat[:, lo:hi]
+        if normalize_student:
+            zh = F.normalize(zh, p=2, dim=-1, eps=1e-6)
+        if beta is not None:
+            proj = proj * beta[:, lo:hi]
+        if post_proj is not None:
+            proj = matmul(proj, post_proj.to(compute_dtype))
+        return matmul(proj.transpose(-1, -2), zh)
+
+    d_w_all = None
+    if cp is not None and cp.size > 1:
+        from ..parallel import context as _context
+        n_upd = T if cp.rank < cp.size - 1 else T - 1     # globally, only the very last chunk never updates
+        if n_upd > 0:
+            d_w_all = delta_w(0, n_upd)
+            local_sum = lr_t * d_w_all.to(state_dtype).sum(dim=1)
+        else:
+            local_sum = torch.zeros(b, w_down.shape[0], w_down.shape[1], dtype=state_dtype, device=z_out.device)
+        w_cur = w_cur + _context.rank_prefix(local_sum)
+
     outs = []
     last_norm = None
     for gs in range(0, T, group):
@@ -269,18 +299,7 @@ def ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, *, lr: float, update
         k_upd = upd_end - gs
         cs = None
         if k_upd > 0:
-            diff = z_tgt[:, gs:upd_end] - z_hat[:, gs:upd_end]
-            proj = matmul(diff, w_update_t.to(compute_dtype))
-            if norm_proj_diff:
-                proj = F.normalize(proj, p=2, dim=-1, eps=1e-6)
-            zh = z_hat[:, gs:upd_end]
-            if normalize_student:
-                zh = F.normalize(zh, p=2, dim=-1, eps=1e-6)
-            if beta is not None:
-                proj = proj * beta[:, gs:upd_end]
-            if post_proj is not None:
-                proj = matmul(proj, post_proj.to(compute_dtype))
-            d_w = matmul(proj.transpose(-1, -2), zh)
+            d_w = d_w_all[:, gs:upd_end] if d_w_all is not None else delta_w(gs, upd_end)
             if return_last_dw_norm:
                 last_norm = d_w[:, -1].detach().float().norm()
             cs = lr_t * torch.cumsum(d_w.to(state_dtype), dim=1)

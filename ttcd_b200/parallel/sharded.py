@@ -183,6 +183,15 @@ class ShardedDataParallel:
         peer mode: flag barrier (every rank's gradients of this group are complete), then ONE kernel pulls
         this rank's shard from every peer over NVLink and fuses the bf16->fp32 cast, the 1/world scale and
         the squared-norm partial.  nccl mode: cast/scale kernel + ``reduce_scatter_tensor``."""
+        if self.comm_stream is None:
+            # host tensors (gloo): all-reduce in fp32 and keep this rank's slice
+            shard = g.numel // self.world
+            g.grad_full32.copy_(g.flat_grad)
+            g.grad_full32.mul_(1.0 / self.world)
+            dist.all_reduce(g.grad_full32, group=self.pg)
+            g.grad_shard.copy_(g.grad_full32[self.rank * shard:(self.rank + 1) * shard])
+            g.reduce_event = True
+            return
         cur = torch.cuda.current_stream()
         self.comm_stream.wait_stream(cur)
         with torch.cuda.stream(self.comm_stream):
@@ -230,7 +239,8 @@ class ShardedDataParallel:
             for g in self.groups:
                 if g.reduce_event is None:
                     self._reduce_group(g)
-            cur.wait_stream(self.comm_stream)
+            if self.comm_stream is not None:
+                cur.wait_stream(self.comm_stream)
         # ---- global grad norm (device side); in peer mode the reduce kernels already accumulated it
         if self.peer:
             pass
@@ -279,7 +289,9 @@ class ShardedDataParallel:
                 ref_ops.adamw_step(g.master, grad, g.exp_avg, g.exp_avg_sq, lr=lr, beta1=b1, beta2=b2, eps=self.eps,
                                    weight_decay=self.weight_decay, step=self.step_count)
                 out_slice.copy_(g.master)
-            if self.world > 1:
+            if self.world > 1 and self.comm_stream is None:
+                dist.all_gather_into_tensor(g.flat_param, out_slice.clone(), group=self.pg)
+            elif self.world > 1:
                 # publish: every rank contributes its updated slice; overlaps the next group's AdamW
                 self.comm_stream.wait_stream(cur)
                 with torch.cuda.stream(self.comm_stream):
@@ -287,7 +299,7 @@ class ShardedDataParallel:
         if self.peer:
             # every rank's pushes have landed everywhere (and nobody still reads this rank's gradients)
             self.barrier.sync(slot=1)
-        elif self.world > 1:
+        elif self.world > 1 and self.comm_stream is not None:
             cur.wait_stream(self.comm_stream)
         return norm
 

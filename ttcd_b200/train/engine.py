@@ -109,11 +109,36 @@ class TrainEngine:
                          **model_kwargs) -> torch.Tensor:
         ids = self._to_device(input_ids)
         lab = ids if labels is None else self._to_device(labels)
+        cp = getattr(self, "cp", None)
+        if cp is not None:
+            return self._forward_backward_cp(ids, lab, scale, cp, **model_kwargs)
         out = self.model(input_ids=ids, labels=lab, **model_kwargs)
         loss = out.loss
         (loss * scale if scale != 1.0 else loss).backward()
         self.tokens_seen += ids.numel()
         return loss.detach()
+
+    def _forward_backward_cp(self, ids, lab, scale, cp, **model_kwargs):
+        """Context-parallel step: every rank of the group receives the same full sequences, shifts the
+        labels globally, keeps its contiguous shard and weights its mean loss by its share of the valid
+        tokens, so that averaging gradients over all ranks yields the gradient of the global mean loss."""
+        B, S = ids.shape
+        if S % cp.size:
+            raise ValueError(f"sequence length {S} is not divisible by the context-parallel degree {cp.size}")
+        s_l = S // cp.size
+        shifted = torch.cat((lab[:, 1:], torch.full_like(lab[:, :1], -100)), dim=1)
+        lo = cp.rank * s_l
+        ids_l, lab_l = ids[:, lo:lo + s_l].contiguous(), shifted[:, lo:lo + s_l].contiguous()
+        out = self.model(input_ids=ids_l, labels=lab_l, shift_labels=False, **model_kwargs)
+        n_local = lab_l.ne(-100).sum().float()
+        n_total = n_local.clone()
+        dist.all_reduce(n_total, group=cp.group)
+        weight = n_local * cp.size / n_total.clamp_min(1.0)
+        (out.loss * (weight * scale)).backward()
+        global_loss = (out.loss.detach() * n_local)
+        dist.all_reduce(global_loss, group=cp.group)
+        self.tokens_seen += ids.numel() // cp.size
+        return global_loss / n_total.clamp_min(1.0)
 
     def train_step(self, input_ids: torch.Tensor, labels: torch.Tensor | None = None, lr: float | None = None,
                    return_loss_on_host: bool = True, **model_kwargs):
