@@ -50,8 +50,10 @@ class RotaryEmbedding(nn.Module):
         self.base = float(base)
         self.yarn = None
         self.attn_scale = 1.0
+        kind = None if rope_scaling is None else (rope_scaling.get("type") or rope_scaling.get("rope_type"))
+        if kind in (None, "default"):      # transformers >= 5 writes {"rope_type": "default"} for plain RoPE
+            rope_scaling = None
         if rope_scaling is not None:
-            kind = rope_scaling.get("type") or rope_scaling.get("rope_type")
             if kind != "yarn":
                 raise NotImplementedError(f"rope_scaling type {kind!r} is not supported (only 'yarn')")
             factor = float(rope_scaling.get("factor", 1.0))
