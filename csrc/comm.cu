@@ -145,6 +145,22 @@ __global__ void __launch_bounds__(256) adamw_push_kernel(float* __restrict__ p, 
   }
 }
 
+// params.p[r][offset + i] = bf16(src[i]) for every rank r: publishes an owner-computed fp32 tensor
+__global__ void __launch_bounds__(256) push_cast_kernel(const float* __restrict__ src, PeerPtrs params, int world,
+                                                        int64_t offset, int64_t n) {
+  const int64_t nvec = n / 8;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const float4 a = *reinterpret_cast<const float4*>(src + i * 8);
+    const float4 b = *reinterpret_cast<const float4*>(src + i * 8 + 4);
+    uint4 pk;
+    pk.x = pack_bf16(a.x, a.y); pk.y = pack_bf16(a.z, a.w);
+    pk.z = pack_bf16(b.x, b.y); pk.w = pack_bf16(b.z, b.w);
+    for (int r = 0; r < world; ++r)
+      *reinterpret_cast<uint4*>(static_cast<bf16*>(params.p[r]) + offset + i * 8) = pk;
+  }
+}
+
 // dst[i] (+)= src[i] over 16-byte vectors of bf16 (src is usually a peer pointer)
 __global__ void __launch_bounds__(256) peer_add_kernel(bf16* __restrict__ dst, const bf16* __restrict__ src, int64_t n,
                                                        int accumulate) {
@@ -242,6 +258,15 @@ TTCD_EXPORT int ttcd_adamw_push(float* p, const float* g, float* m, float* v, co
   if (n == 0) return TTCD_OK;
   adamw_push_kernel<<<grid_for(n / 8), 256, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
       p, g, m, v, make_ptrs(param_ptrs, world), world, offset, n, lr, beta1, beta2, eps, wd, bc1, bc2_sqrt, coef, skip);
+  return static_cast<int>(cudaGetLastError());
+}
+
+TTCD_EXPORT int ttcd_push_cast(const float* src, const long long* param_ptrs, int world, long long offset, long long n,
+                               void* stream_ptr) {
+  if (world < 1 || world > MAX_RANKS || n % 8 != 0 || offset % 8 != 0) return TTCD_ERR_ARG;
+  if (n == 0) return TTCD_OK;
+  push_cast_kernel<<<grid_for(n / 8), 256, 0, static_cast<cudaStream_t>(stream_ptr)>>>(src, make_ptrs(param_ptrs, world),
+                                                                                     world, offset, n);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -30,8 +30,9 @@ def check_symmetric():
     buf.close()
 
 
-def check_sharded_modes():
-    """Two optimizer steps with the fused peer-memory path and with the NCCL baseline must agree."""
+def check_sharded_modes(muon: bool = False):
+    """Optimizer steps with the fused peer-memory path and with the NCCL baseline must agree (AdamW, or
+    Muon with the owner pulling whole-parameter gradients and pushing the new weights to every rank)."""
     from ttcd_b200.models import IPTTCDv9Config
     from ttcd_b200.train.engine import EngineConfig, TrainEngine
     rank = dist.get_rank()
@@ -42,11 +43,11 @@ def check_sharded_modes():
     results = {}
     for mode in ("peer", "nccl"):
         os.environ["TTCD_COMM"] = mode
-        engine = TrainEngine(cfg, EngineConfig(lr=1e-3, seed=7), device=f"cuda:{torch.cuda.current_device()}")
+        engine = TrainEngine(cfg, EngineConfig(lr=1e-3, seed=7, enable_muon=muon), device=f"cuda:{torch.cuda.current_device()}")
         assert engine.sdp.peer == (mode == "peer")
         g = torch.Generator().manual_seed(100 + rank)
         losses = []
-        for _ in range(3):
+        for _ in range(1 if muon else 3):      # Newton-Schulz amplifies rounding noise: compare one step
             ids = torch.randint(0, cfg.vocab_size, (1, 512), generator=g).cuda()
             losses.append(engine.train_step(ids))
         flat = torch.cat([grp.flat_param.float() for grp in engine.sdp.groups])
@@ -75,6 +76,8 @@ def main():
         check_symmetric()
     if what in ("all", "sharded"):
         check_sharded_modes()
+    if what in ("all", "muon"):
+        check_sharded_modes(muon=True)
     if what in ("all", "cp"):
         from tests.multi_gpu_cp import check_context_parallel
         check_context_parallel()

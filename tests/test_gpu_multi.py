@@ -47,5 +47,10 @@ def test_fused_sharded_step_matches_nccl_baseline():
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
+def test_muon_owner_pull_push_matches_nccl_baseline():
+    _launch("muon", 2)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
 def test_context_parallel_halo_attention_matches_single_gpu():
     _launch("cp", 2)

@@ -71,17 +71,22 @@ class DecoderPreTrainedModel(PreTrainedModel):
     def _init_weights(self, module: nn.Module, rescale_prenorm_residual: bool = False,
                       num_residuals_per_layer: int = 2):
         std = self.config.initializer_range
+
+        def fresh(t) -> bool:
+            """True for tensors that still need initialising (HF marks checkpoint-loaded tensors)."""
+            return t is not None and t.device.type != "meta" and not getattr(t, "_is_hf_initialized", False)
+
         with torch.no_grad():
             if isinstance(module, (nn.Linear, nn.Conv1d)):
-                if module.weight.device.type != "meta":
+                if fresh(module.weight):
                     module.weight.normal_(mean=0.0, std=std)
-                    if module.bias is not None:
-                        module.bias.zero_()
+                if fresh(module.bias):
+                    module.bias.zero_()
             elif isinstance(module, nn.Embedding):
-                if module.weight.device.type != "meta":
+                if fresh(module.weight):
                     module.weight.normal_(mean=0.0, std=std)
             elif isinstance(module, RMSNorm):
-                if module.weight is not None and module.weight.device.type != "meta":
+                if fresh(module.weight):
                     module.weight.fill_(1.0)
             if rescale_prenorm_residual:
                 for name in ("o_proj", "down_proj"):

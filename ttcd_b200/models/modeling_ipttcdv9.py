@@ -273,7 +273,7 @@ class _IPTTCDInit:
         std = cfg.initializer_range
         if isinstance(module, nn.Linear) and getattr(module, "_is_ttt_proj", False):
             w = module.weight
-            if w.device.type == "meta":
+            if w.device.type == "meta" or getattr(w, "_is_hf_initialized", False):
                 return
             kind = getattr(cfg, "ttt_proj_init", "diagonal")
             n = min(w.shape)
@@ -288,7 +288,7 @@ class _IPTTCDInit:
                 w.zero_()
         if isinstance(module, nn.Conv1d) and getattr(module, "_is_ttt_conv", False):
             w = module.weight
-            if w.device.type == "meta":
+            if w.device.type == "meta" or getattr(w, "_is_hf_initialized", False):
                 return
             role = getattr(module, "_ttt_conv_role", "ttt")
             kind = getattr(cfg, f"ttt_{role}_conv_init", getattr(cfg, "ttt_conv_init", "zero"))
@@ -301,7 +301,7 @@ class _IPTTCDInit:
             elif kind != "random":
                 raise ValueError(f"Unsupported TTT conv init {kind!r} for role {role!r}")
         if isinstance(module, IPTTCDMLP) and module.is_ttt_layer and module.dynamic_lr:
-            if module.b_proj.device.type != "meta":
+            if module.b_proj.device.type != "meta" and not getattr(module.b_proj, "_is_hf_initialized", False):
                 module.b_proj.normal_(mean=0.0, std=std)
 
 

@@ -123,7 +123,7 @@ class _IPTTTInit:
     def _init_extra(self, module: nn.Module) -> None:
         cfg = self.config
         if isinstance(module, nn.Linear) and getattr(module, "_is_ttt_proj", False):
-            if module.weight.device.type == "meta":
+            if module.weight.device.type == "meta" or getattr(module.weight, "_is_hf_initialized", False):
                 return
             if cfg.ttt_proj_init in {"diagonal", "diagonal_gaussian"}:
                 n = min(module.weight.shape)
@@ -134,7 +134,7 @@ class _IPTTTInit:
             elif cfg.ttt_proj_init == "zero":
                 module.weight.zero_()
         if isinstance(module, nn.Conv1d) and getattr(module, "_is_ttt_conv", False):
-            if module.weight.device.type != "meta":
+            if module.weight.device.type != "meta" and not getattr(module.weight, "_is_hf_initialized", False):
                 module.weight.zero_()
 
 

@@ -45,6 +45,8 @@ class ParamGroup:
     offsets: list[int] = field(default_factory=list)
     numel: int = 0             # padded to a multiple of 8 * world
     base: int = 0              # element offset of this group inside the symmetric buffers
+    total: int = 0             # numel (AdamW region) + the Muon-owned parameters laid out after it
+    muon: list = field(default_factory=list)   # MuonParam entries of this group
     flat_param: torch.Tensor | None = None   # bf16 [numel]
     flat_grad: torch.Tensor | None = None    # bf16 [numel]
     master: torch.Tensor | None = None       # fp32 [numel / world]
@@ -62,7 +64,8 @@ class ShardedDataParallel:
     def __init__(self, model: nn.Module, blocks: list[nn.Module] | None = None,
                  process_group: dist.ProcessGroup | None = None, *, lr: float = 1e-4, betas=(0.9, 0.95),
                  eps: float = 1e-8, weight_decay: float = 0.1, max_norm: float | None = 1.0,
-                 param_dtype: torch.dtype = torch.bfloat16, overlap: bool = True, comm: str | None = None):
+                 param_dtype: torch.dtype = torch.bfloat16, overlap: bool = True, comm: str | None = None,
+                 muon: bool = False, muon_momentum: float = 0.95, muon_filter=None):
         """``comm``: 'peer' = fused peer-memory kernels over NVLink (default on CUDA with the native
         library), 'nccl' = the NCCL reduce-scatter / all-gather baseline (also TTCD_COMM=nccl)."""
         import os
@@ -81,6 +84,8 @@ class ShardedDataParallel:
         if self.device.type == "cuda" and param_dtype == torch.bfloat16 and not self.use_native:
             _native.load(required=not _native.torch_fallback_allowed())
         self.peer = self.world > 1 and self.use_native and self.comm == "peer"
+        self.muon_enabled, self.muon_momentum, self.muon_filter = muon, muon_momentum, muon_filter
+        self.muon_params: list = []
         self.sym_params = self.sym_grads = self.barrier = None
         self.groups: list[ParamGroup] = []
         self._build_groups(blocks)
@@ -111,13 +116,32 @@ class ShardedDataParallel:
                 seen.add(id(p)); ps.append(p); ns.append(n)
         if ps:
             groups.append(ParamGroup("root", ps, ns))
-        for g in groups:
+        global_names = {id(p): n for n, p in self.model.named_parameters()}
+        from ..train.muon import MuonParam, assign_owners, default_is_muon
+        is_muon = self.muon_filter or default_is_muon
+        for gi, g in enumerate(groups):
+            pairs = list(zip(g.params, g.names))
+            chosen = [(p, n) for p, n in pairs if self.muon_enabled and p.requires_grad and is_muon(global_names[id(p)], p)
+                      and p.numel() % 8 == 0]      # 16-byte granules for the vectorised pull/push kernels
+            chosen_ids = {id(p) for p, _ in chosen}
+            adam = [(p, n) for p, n in pairs if id(p) not in chosen_ids]
             off = 0
-            for p in g.params:
+            for p, _ in adam:
                 g.offsets.append(off)
                 off += _align(p.numel(), 8)          # 16-byte aligned starts (TMA / vector loads)
-            g.numel = _align(off, 8 * self.world)
-        total = sum(g.numel for g in groups)
+            g.numel = _align(off, 8 * self.world)    # AdamW region: sharded 1/world by flat position
+            off = g.numel
+            for p, n in chosen:                      # Muon region: whole parameters, owned by one rank each
+                g.offsets.append(off)
+                mp = MuonParam(global_names[id(p)], p, gi, off)
+                g.muon.append(mp)
+                self.muon_params.append(mp)
+                off += _align(p.numel(), 8)
+            g.total = _align(off, 8)
+            g.params = [p for p, _ in adam] + [p for p, _ in chosen]
+            g.names = [n for _, n in adam] + [n for _, n in chosen]
+        assign_owners(self.muon_params, self.world)
+        total = sum(g.total for g in groups)
         if self.peer:
             # flat parameters and gradients live in peer-addressable memory: the fused kernels read every
             # rank's gradients and write every rank's parameters directly over NVLink
@@ -130,12 +154,12 @@ class ShardedDataParallel:
         for g in groups:
             g.base = base
             if self.peer:
-                g.flat_param = self.sym_params.view(self.param_dtype, g.numel, base * esize)
-                g.flat_grad = self.sym_grads.view(self.param_dtype, g.numel, base * esize)
+                g.flat_param = self.sym_params.view(self.param_dtype, g.total, base * esize)
+                g.flat_grad = self.sym_grads.view(self.param_dtype, g.total, base * esize)
             else:
-                g.flat_param = torch.zeros(g.numel, dtype=self.param_dtype, device=self.device)
-                g.flat_grad = torch.zeros(g.numel, dtype=self.param_dtype, device=self.device)
-            base += g.numel
+                g.flat_param = torch.zeros(g.total, dtype=self.param_dtype, device=self.device)
+                g.flat_grad = torch.zeros(g.total, dtype=self.param_dtype, device=self.device)
+            base += g.total
             for p, o in zip(g.params, g.offsets):
                 view = g.flat_param[o:o + p.numel()].view(p.shape)
                 view.copy_(p.data)
@@ -150,6 +174,12 @@ class ShardedDataParallel:
                 g.grad_shard = torch.zeros(shard, dtype=torch.float32, device=self.device)
                 if not self.peer:
                     g.grad_full32 = torch.empty(g.numel, dtype=torch.float32, device=self.device)
+            for mp in g.muon:
+                if mp.owner == self.rank:
+                    n = mp.param.numel()
+                    mp.master = g.flat_param[mp.offset:mp.offset + n].float()
+                    mp.momentum = torch.zeros(n, dtype=torch.float32, device=self.device)
+                    mp.grad32 = torch.zeros(_align(n, 8), dtype=torch.float32, device=self.device)
         self.groups = groups
 
     def resync_master(self) -> None:
@@ -157,6 +187,9 @@ class ShardedDataParallel:
         for g in self.groups:
             shard = g.numel // self.world
             g.master.copy_(g.flat_param[self.rank * shard:(self.rank + 1) * shard].float())
+            for mp in g.muon:
+                if mp.master is not None:
+                    mp.master.copy_(g.flat_param[mp.offset:mp.offset + mp.param.numel()].float())
 
     # ---------------------------------------------------------------------------------- reduce-scatter
     def _install_hooks(self):
@@ -186,10 +219,11 @@ class ShardedDataParallel:
         if self.comm_stream is None:
             # host tensors (gloo): all-reduce in fp32 and keep this rank's slice
             shard = g.numel // self.world
-            g.grad_full32.copy_(g.flat_grad)
+            g.grad_full32.copy_(g.flat_grad[:g.numel])
             g.grad_full32.mul_(1.0 / self.world)
             dist.all_reduce(g.grad_full32, group=self.pg)
             g.grad_shard.copy_(g.grad_full32[self.rank * shard:(self.rank + 1) * shard])
+            self._reduce_muon_baseline(g)
             g.reduce_event = True
             return
         cur = torch.cuda.current_stream()
@@ -202,16 +236,33 @@ class ShardedDataParallel:
                 _native.call("ttcd_rs_cast_scale_norm", self.sym_grads.ptr_array(), _native.i32(self.world),
                              _native.i64(g.base + self.rank * shard), _native.i64(shard), _native.f32(1.0 / self.world),
                              _native.ptr(g.grad_shard), _native.ptr(self._norm_sq), _native.stream_ptr())
+                for mp in g.muon:
+                    # Muon: the owner pulls the WHOLE parameter's gradient from every peer while reducing
+                    if mp.owner == self.rank:
+                        _native.call("ttcd_rs_cast_scale_norm", self.sym_grads.ptr_array(), _native.i32(self.world),
+                                     _native.i64(g.base + mp.offset), _native.i64(mp.grad32.numel()),
+                                     _native.f32(1.0 / self.world), _native.ptr(mp.grad32), _native.ptr(self._norm_sq),
+                                     _native.stream_ptr())
             else:
                 if self.use_native:
                     from ..ops import cuda
-                    cuda.cast_scale(g.flat_grad, g.grad_full32, 1.0 / self.world)
+                    cuda.cast_scale(g.flat_grad[:g.numel], g.grad_full32, 1.0 / self.world)
                 else:
-                    g.grad_full32.copy_(g.flat_grad)
+                    g.grad_full32.copy_(g.flat_grad[:g.numel])
                     g.grad_full32.mul_(1.0 / self.world)
                 dist.reduce_scatter_tensor(g.grad_shard, g.grad_full32, group=self.pg)
+                self._reduce_muon_baseline(g)
             g.reduce_event = torch.cuda.Event()
             g.reduce_event.record(self.comm_stream)
+
+    def _reduce_muon_baseline(self, g: ParamGroup):
+        """NCCL / gloo statement of the owner reduction: ``dist.reduce`` of each Muon parameter's gradient."""
+        for mp in g.muon:
+            n = mp.param.numel()
+            buf = g.flat_grad[mp.offset:mp.offset + n].float().mul_(1.0 / self.world)
+            dist.reduce(buf, dst=dist.get_global_rank(self.pg, mp.owner) if self.pg is not None else mp.owner, group=self.pg)
+            if mp.owner == self.rank:
+                mp.grad32[:n].copy_(buf)
 
     # ---------------------------------------------------------------------------------- step
     def zero_grad(self):
@@ -226,7 +277,7 @@ class ShardedDataParallel:
                     p.grad = g.flat_grad[o:o + p.numel()].view(p.shape)
 
     def _local_grad(self, g: ParamGroup) -> torch.Tensor:
-        return g.grad_shard if self.world > 1 else g.flat_grad
+        return g.grad_shard if self.world > 1 else g.flat_grad[:g.numel]
 
     @torch.no_grad()
     def step(self, lr: float | None = None) -> torch.Tensor:
@@ -241,7 +292,12 @@ class ShardedDataParallel:
                     self._reduce_group(g)
             if self.comm_stream is not None:
                 cur.wait_stream(self.comm_stream)
+        if self.world == 1:
+            for mp in self.muon_params:
+                n = mp.param.numel()
+                mp.grad32[:n].copy_(self.groups[mp.group_index].flat_grad[mp.offset:mp.offset + n])
         # ---- global grad norm (device side); in peer mode the reduce kernels already accumulated it
+        owned = [mp for mp in self.muon_params if mp.owner == self.rank]
         if self.peer:
             pass
         elif self.use_native:
@@ -249,10 +305,14 @@ class ShardedDataParallel:
             from ..ops import cuda
             for g in self.groups:
                 cuda.sumsq(self._local_grad(g), self._norm_sq)
+            for mp in owned:
+                cuda.sumsq(mp.grad32, self._norm_sq)
         else:
             self._norm_sq.zero_()
             for g in self.groups:
                 self._norm_sq += self._local_grad(g).float().pow(2).sum()
+            for mp in owned:
+                self._norm_sq += mp.grad32.pow(2).sum()
         if self.world > 1:
             dist.all_reduce(self._norm_sq, group=self.pg)
         norm = self._norm_sq.sqrt()
@@ -290,18 +350,45 @@ class ShardedDataParallel:
                                    weight_decay=self.weight_decay, step=self.step_count)
                 out_slice.copy_(g.master)
             if self.world > 1 and self.comm_stream is None:
-                dist.all_gather_into_tensor(g.flat_param, out_slice.clone(), group=self.pg)
+                dist.all_gather_into_tensor(g.flat_param[:g.numel], out_slice.clone(), group=self.pg)
             elif self.world > 1:
                 # publish: every rank contributes its updated slice; overlaps the next group's AdamW
                 self.comm_stream.wait_stream(cur)
                 with torch.cuda.stream(self.comm_stream):
-                    dist.all_gather_into_tensor(g.flat_param, out_slice, group=self.pg)
+                    dist.all_gather_into_tensor(g.flat_param[:g.numel], out_slice, group=self.pg)
+        if self.muon_params:
+            self._step_muon(lr, cur)
         if self.peer:
             # every rank's pushes have landed everywhere (and nobody still reads this rank's gradients)
             self.barrier.sync(slot=1)
         elif self.world > 1 and self.comm_stream is not None:
             cur.wait_stream(self.comm_stream)
         return norm
+
+    def _step_muon(self, lr: float, cur) -> None:
+        """Owner-side Muon updates, then publication of the new bf16 weights to every rank."""
+        from ..train.muon import muon_update
+        coef = self._coef if self.max_norm is not None else None
+        for mp in self.muon_params:
+            g = self.groups[mp.group_index]
+            n = mp.param.numel()
+            dst = g.flat_param[mp.offset:mp.offset + n]
+            if mp.owner == self.rank:
+                saved = mp.grad32
+                mp.grad32 = saved[:n]
+                muon_update(mp, lr, self.weight_decay, self.muon_momentum, coef)
+                mp.grad32 = saved
+                if self.peer:
+                    n8 = n // 8 * 8
+                    _native.call("ttcd_push_cast", _native.ptr(mp.master), self.sym_params.ptr_array(), _native.i32(self.world),
+                                 _native.i64(g.base + mp.offset), _native.i64(n8), _native.stream_ptr())
+                    if n8 != n:
+                        dst[n8:].copy_(mp.master[n8:])
+                else:
+                    dst.copy_(mp.master)
+            if self.world > 1 and not self.peer:
+                src = dist.get_global_rank(self.pg, mp.owner) if self.pg is not None else mp.owner
+                dist.broadcast(dst, src=src, group=self.pg)
 
     # ---------------------------------------------------------------------------------- state
     def optimizer_state_dict(self) -> dict:
@@ -341,8 +428,12 @@ class ShardedDataParallel:
         out = {}
         for g in self.groups:
             flat = self._gather_flat(g, which)
+            muon_ids = {id(mp.param) for mp in g.muon}
             for p, o in zip(g.params, g.offsets):
-                out[p.data_ptr()] = flat[o:o + p.numel()].view(p.shape)
+                if id(p) in muon_ids:      # Muon-owned: the bf16 weights every rank holds
+                    out[p.data_ptr()] = p.detach().float()
+                else:
+                    out[p.data_ptr()] = flat[o:o + p.numel()].view(p.shape)
         return out
 
     def full_optimizer_state(self, template: bool = False) -> dict[str, torch.Tensor]:
@@ -353,7 +444,19 @@ class ShardedDataParallel:
             flats = {}
             for which in ("exp_avg", "exp_avg_sq"):
                 flats[which] = None if template else self._gather_flat(g, which)
+            muon_ids = {id(mp.param) for mp in g.muon}
+            for mp in g.muon:
+                key = f"{mp.name}.momentum_buffer"
+                buf = torch.zeros(mp.param.shape, dtype=torch.float32, device="cpu" if template else self.device)
+                if not template:
+                    if mp.owner == self.rank:
+                        buf.copy_(mp.momentum.view(mp.param.shape))
+                    if self.world > 1:
+                        dist.all_reduce(buf, group=self.pg)
+                sd[key] = buf
             for p, o in zip(g.params, g.offsets):
+                if id(p) in muon_ids:
+                    continue
                 for which in ("exp_avg", "exp_avg_sq"):
                     key = f"{names[id(p)]}.{which}"
                     if template:
@@ -368,9 +471,15 @@ class ShardedDataParallel:
         for g in self.groups:
             shard = g.numel // self.world
             lo, hi = self.rank * shard, (self.rank + 1) * shard
+            muon_ids = {id(mp.param) for mp in g.muon}
+            for mp in g.muon:
+                if mp.owner == self.rank and f"{mp.name}.momentum_buffer" in sd:
+                    mp.momentum.copy_(sd[f"{mp.name}.momentum_buffer"].reshape(-1))
             for which in ("exp_avg", "exp_avg_sq"):
                 dst = getattr(g, which)
                 for p, o in zip(g.params, g.offsets):
+                    if id(p) in muon_ids:
+                        continue
                     src = sd[f"{names[id(p)]}.{which}"].reshape(-1)
                     a, b = max(o, lo), min(o + p.numel(), hi)
                     if a < b:

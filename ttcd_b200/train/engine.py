@@ -83,7 +83,8 @@ class TrainEngine:
         self.sdp = ShardedDataParallel(
             self.model, blocks=list(self.model.model.layers), process_group=process_group if multi else False,
             lr=self.cfg.lr, betas=self.cfg.betas, eps=self.cfg.eps, weight_decay=self.cfg.weight_decay,
-            max_norm=self.cfg.max_norm, param_dtype=self.cfg.dtype)
+            max_norm=self.cfg.max_norm, param_dtype=self.cfg.dtype, muon=self.cfg.enable_muon,
+            muon_momentum=self.cfg.muon_momentum)
         self.sdp.skip_nan_inf = self.cfg.skip_nan_inf
         self.world = self.sdp.world
         self._dev_ids = None

@@ -1,0 +1,81 @@
+"""Muon for the flat-buffer sharded runtime: owner-compute Newton–Schulz with the gradient gather fused
+into the reduction.
+
+Behaviour follows the reference optimizer (custom_components/muon_v2.py:587-1310): Muon is applied to
+parameters with ``ndim >= 2`` that are not embeddings, the LM head or the final norm (513-515), with
+Nesterov momentum ``buf = g + mu*buf; g = g + mu*buf`` (904-912), five fixed-coefficient Newton–Schulz
+iterations in bf16 (30-65), the update ``p *= 1 - lr*wd; p -= lr*0.2*sqrt(max(rows, cols)) * u`` (707-716,
+914-919); everything else uses AdamW.  Ownership: parameters are sorted by Newton–Schulz cost and dealt
+round-robin over the ranks (739-796).
+
+Where the reference moves gradient shards to the owner with two ``all_to_all_single`` calls per chunk of
+parameters and scatters the update back the same way, here the owner's reduction kernel *pulls* the
+parameter's gradient from every peer's flat gradient buffer over NVLink while summing, casting and
+scaling (one kernel, no staging), runs the orthogonalisation on the tcgen05 GEMM (A = XX^T, B = bA + cA^2,
+X = aX + BX with alpha/beta epilogues), and stores the new bf16 weights straight into every peer's flat
+parameter buffer.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from .. import _native, ops
+
+MUON_EXCLUDE = ("embeddings", "lm_head", "model.norm")
+
+
+def default_is_muon(name: str, param: torch.Tensor) -> bool:
+    return param.ndim >= 2 and not any(key in name for key in MUON_EXCLUDE)
+
+
+def ns_cost(shape) -> int:
+    rows, cols = int(shape[-2]), int(shape[-1])
+    small, large = min(rows, cols), max(rows, cols)
+    return int(math.prod(shape[:-2])) * small * small * large
+
+
+@dataclass
+class MuonParam:
+    name: str
+    param: torch.nn.Parameter
+    group_index: int
+    offset: int                 # element offset inside the group's flat buffers
+    owner: int = 0
+    master: torch.Tensor | None = None      # fp32, owner only
+    momentum: torch.Tensor | None = None    # fp32, owner only
+    grad32: torch.Tensor | None = None      # fp32 reduced gradient, owner only
+
+
+def assign_owners(params: list[MuonParam], world: int) -> None:
+    order = sorted(range(len(params)), key=lambda i: -ns_cost(params[i].param.shape))
+    for k, i in enumerate(order):
+        params[i].owner = k % world
+
+
+def orthogonalize(g: torch.Tensor) -> torch.Tensor:
+    """Newton–Schulz on a 2-D gradient (3-D parameters are treated as a batch over the first dim)."""
+    if g.dim() == 2:
+        return ops.newton_schulz(g)
+    g3 = g.reshape(-1, g.shape[-2], g.shape[-1])     # independent matrices over the leading dims (312-309, 820-826)
+    if min(g3.shape[-2:]) < 64:
+        # depthwise-conv taps and the like: a few scalars per matrix, not tensor-core work
+        from ..ops import reference as ref_ops
+        return ref_ops.newton_schulz(g3).reshape(g.shape)
+    return ops.newton_schulz(g3).reshape(g.shape)
+
+
+def muon_update(mp: MuonParam, lr: float, weight_decay: float, momentum: float, coef: torch.Tensor | None,
+                nesterov: bool = True) -> torch.Tensor:
+    """Owner-side update of one parameter; returns the new fp32 master (in place)."""
+    g = mp.grad32 if coef is None else mp.grad32 * coef
+    mp.momentum.mul_(momentum).add_(g)
+    g = g.add(mp.momentum, alpha=momentum) if nesterov else mp.momentum
+    u = orthogonalize(g.view(mp.param.shape)).float().reshape(-1)
+    rows, cols = mp.param.shape[-2], mp.param.shape[-1]      # last two dims also for >2-D parameters (707-716)
+    adj_lr = lr * 0.2 * math.sqrt(max(rows, cols))
+    mp.master.mul_(1.0 - lr * weight_decay).add_(u, alpha=-adj_lr)
+    return mp.master
