@@ -450,3 +450,84 @@ TTCD_EXPORT int ttcd_qk_norm_rope_bwd(const void* dq, long long lddq, const void
   else qk_norm_rope_bwd_kernel<4><<<nblocks, 256, 0, st>>>(p);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ------------------------------------------------------------------------------------------------
+// RMSNorm backward that allocates nothing: the per-block weight-gradient partial sums go to an array
+// in the library image instead of a caller-provided buffer, and a second small kernel folds them into
+// dw[D].  Contract and limits: ttcd_no_alloc.h.
+// ------------------------------------------------------------------------------------------------
+#include "ttcd_no_alloc.h"
+
+namespace ttcd {
+
+static __device__ __align__(256) float g_rmsnorm_dw_scratch[TTCD_NO_ALLOC_MAX_BLOCKS * TTCD_NO_ALLOC_MAX_D];
+
+__global__ void __launch_bounds__(256) rmsnorm_dw_fold_kernel(const float* __restrict__ partial, int nblocks, int D,
+                                                              float* __restrict__ dw) {
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= D) return;
+  float acc = 0.f;
+  for (int b = 0; b < nblocks; ++b) acc += partial[static_cast<int64_t>(b) * D + col];   // fixed order: deterministic
+  dw[col] = acc;
+}
+
+constexpr int kNoAllocMaxDevices = 64;
+static float* g_scratch_addr[kNoAllocMaxDevices] = {};
+
+// Device address of this device's copy of the array; looked up once per device.
+static int no_alloc_scratch(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) return TTCD_NO_ALLOC_ERR_DEVICE;
+  if (g_scratch_addr[dev] == nullptr) {
+    float* addr = nullptr;
+    const cudaError_t rc = cudaGetSymbolAddress(reinterpret_cast<void**>(&addr), g_rmsnorm_dw_scratch);
+    if (rc != cudaSuccess || addr == nullptr) {
+      (void)cudaGetLastError();
+      return TTCD_NO_ALLOC_ERR_DEVICE;
+    }
+    if (cudaFuncSetAttribute(rmsnorm_bwd_kernel<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(rmsnorm_bwd_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return TTCD_NO_ALLOC_ERR_DEVICE;
+    }
+    g_scratch_addr[dev] = addr;
+  }
+  *out = g_scratch_addr[dev];
+  return TTCD_NO_ALLOC_OK;
+}
+
+}  // namespace ttcd
+
+TTCD_EXPORT int ttcd_rmsnorm_bwd_no_alloc(const void* dy, const void* s, const void* w, const float* rstd,
+                                          const void* dres, void* dx, float* dw, long long rows, int D,
+                                          void* stream_ptr) {
+  if (dy == nullptr || s == nullptr || rstd == nullptr || dx == nullptr || rows <= 0 || D <= 0 || D % 8 != 0 ||
+      (w != nullptr && dw == nullptr))
+    return TTCD_NO_ALLOC_ERR_SHAPE;
+  if (D > TTCD_NO_ALLOC_MAX_D) return TTCD_NO_ALLOC_ERR_TOO_LARGE;
+  float* scratch = nullptr;
+  const int rc = no_alloc_scratch(&scratch);
+  if (rc != TTCD_NO_ALLOC_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream_ptr);
+  const int warps = 8;
+  const long long want = (rows + warps - 1) / warps;
+  const int nblocks = static_cast<int>(want < TTCD_NO_ALLOC_MAX_BLOCKS ? want : TTCD_NO_ALLOC_MAX_BLOCKS);
+  const size_t smem = static_cast<size_t>(warps) * D * sizeof(float);
+  float* partial = w != nullptr ? scratch : nullptr;
+  const int chunks = (D + 255) / 256;
+#define LAUNCH(C)                                                                                           \
+  rmsnorm_bwd_kernel<C><<<nblocks, warps * 32, smem, st>>>(                                                 \
+      static_cast<const bf16*>(dy), static_cast<const bf16*>(s), static_cast<const bf16*>(w), rstd,          \
+      static_cast<const bf16*>(dres), static_cast<bf16*>(dx), partial, rows, D)
+  switch (chunks) {
+    case 1: LAUNCH(1); break;
+    case 2: LAUNCH(2); break;
+    case 3: LAUNCH(3); break;
+    case 4: LAUNCH(4); break;
+    case 5: case 6: LAUNCH(6); break;
+    default: LAUNCH(8); break;
+  }
+#undef LAUNCH
+  if (partial != nullptr) rmsnorm_dw_fold_kernel<<<(D + 255) / 256, 256, 0, st>>>(partial, nblocks, D, dw);
+  return static_cast<int>(cudaGetLastError());
+}
