@@ -236,7 +236,7 @@ def build_dataset(dataset: str, tokenizer, seq_len: int, rank: int, world_size: 
         return SyntheticTokenDataset(v, seq_len, rank, world_size, seed)
     if dataset.startswith("mds:"):
         from .data_mds import build_mds_dataset
-        return build_mds_dataset(dataset, rank=rank, world_size=world_size, seed=seed, default_seq_len=65536,
+        return build_mds_dataset(dataset, seq_len=seq_len, rank=rank, world_size=world_size, seed=seed,
                                  shuffle=shuffle_buffer_size > 0)
     from datasets import interleave_datasets, load_dataset
 
