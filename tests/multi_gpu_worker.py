@@ -78,6 +78,9 @@ def main():
         check_sharded_modes()
     if what in ("all", "muon"):
         check_sharded_modes(muon=True)
+    if what in ("all", "tp"):
+        from tests.multi_gpu_tp import check_tensor_parallel
+        check_tensor_parallel()
     if what in ("all", "cp"):
         from tests.multi_gpu_cp import check_context_parallel
         check_context_parallel()

@@ -52,5 +52,10 @@ def test_muon_owner_pull_push_matches_nccl_baseline():
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
+def test_fused_allgather_gemm_and_gemm_reducescatter():
+    _launch("tp", 2)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
 def test_context_parallel_halo_attention_matches_single_gpu():
     _launch("cp", 2)

@@ -130,7 +130,7 @@ def device_status(reset: bool = True) -> int:
     if lib is None:
         return 0
     status = 0
-    for unit in ("gemm", "attn", "comm"):
+    for unit in ("gemm", "attn", "comm", "gemm_comm"):
         fn = getattr(lib, f"ttcd_read_status_{unit}", None)
         if fn is None:
             continue

@@ -1,0 +1,198 @@
+"""Tensor + sequence parallelism on fused GEMM/collective kernels.
+
+Layout (the reference's plan, flame/models/parallelize_fla.py:118-208): between blocks the residual stream
+is sharded over tokens (``SequenceParallel`` norms); q/k/v and gate/up are column parallel (all-gather of the
+token shards feeding the GEMM), o_proj and down_proj are row parallel (GEMM feeding a reduce-scatter back
+to token shards).  Where the reference composes DTensor redistributes with cuBLAS (or torch's async-TP
+micro-pipelining, 283-287), each of the two patterns is ONE kernel here (``csrc/gemm_comm.cu``):
+
+* ``ag_linear``  : all-gather -> GEMM.  Peers' row blocks are pulled into a local gathered buffer by bulk
+  async copies inside the GEMM kernel; tiles start on the rank's own rows and follow the flags.
+* ``rs_linear``  : GEMM -> reduce-scatter.  Other ranks' row blocks are computed first and flagged; reducer
+  warps sum the peers' partial tiles over NVLink while the tensor cores finish the rank's own rows, whose
+  epilogue adds the sum.
+
+Backward uses the same two kernels with the weight read MN-major (dX of a column-parallel layer is a
+GEMM -> reduce-scatter, dX of a row-parallel layer an all-gather -> GEMM) and the plain GEMM for dW on the
+gathered operand the forward kernel left behind.  CPU / gloo: the same functions run as
+``all_gather`` / ``reduce_scatter`` + matmul so the layer logic is testable without GPUs.
+
+Buffers are double buffered and every fused call is preceded by one flag barrier: a buffer is rewritten two
+calls after peers read it, and every peer has passed the barrier in between.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from .. import _native as nv
+
+_CTX: "TensorParallel | None" = None
+
+
+def current() -> "TensorParallel | None":
+    return _CTX
+
+
+class TensorParallel:
+    """Per-process state of one tensor-parallel group: symmetric staging buffers, flags, barrier."""
+
+    BM, BN = 128, 256
+
+    def __init__(self, group=None, device=None, max_rows_per_rank: int = 8192, max_features: int = 6144,
+                 wait_ns: int = 0, fused: bool | None = None):
+        global _CTX
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.device = torch.device(device if device is not None else "cpu")
+        self.fused = (self.device.type == "cuda" and nv.available()) if fused is None else fused
+        self.wait_ns = wait_ns
+        self.epoch = 0
+        self.calls = 0
+        if self.fused:
+            from ..comm.symmetric import PeerBarrier, SymmetricBuffer
+            rows, feat, w = max_rows_per_rank, max_features, self.world
+            self.max_rows, self.max_feat = rows, feat
+            self.x_sym = [SymmetricBuffer(rows * feat * 2, group, self.device) for _ in range(2)]
+            self.part_sym = [SymmetricBuffer(rows * w * feat * 2, group, self.device) for _ in range(2)]
+            nflags = (rows // self.BM) * w * (feat // self.BN)
+            self.flag_sym = [SymmetricBuffer(nflags * 4, group, self.device) for _ in range(2)]
+            self.gathered = torch.empty(rows * w * feat, dtype=torch.bfloat16, device=self.device)
+            self.peer_sum = torch.empty(rows * feat, dtype=torch.float32, device=self.device)
+            self.ready = torch.zeros((rows // self.BM) * w, dtype=torch.int32, device=self.device)
+            self.sum_flags = torch.zeros((rows // self.BM) * (feat // self.BN), dtype=torch.int32, device=self.device)
+            self.barrier = PeerBarrier(group, slots=2, wait_ns=wait_ns)
+        _CTX = self
+
+    def close(self):
+        global _CTX
+        if self.fused:
+            torch.cuda.synchronize()
+            for b in self.x_sym + self.part_sym + self.flag_sym + [self.barrier.buf]:
+                b.close()
+        if _CTX is self:
+            _CTX = None
+
+    # ------------------------------------------------------------------------------- raw collectives+GEMM
+    def _fits(self, m_shard: int, n: int, k: int) -> bool:
+        return (self.fused and m_shard % self.BM == 0 and n % self.BN == 0 and k % 64 == 0 and m_shard <= self.max_rows
+                and max(n, k) <= self.max_feat and (self.BM * k * 2) % 16384 == 0)
+
+    def ag_gemm(self, x_shard: torch.Tensor, w: torch.Tensor, w_is_kn: bool = False):
+        """``(all_gather_rows(x_shard) @ W^T, gathered)``.  ``w``: [N, K], or [K, N] when ``w_is_kn``."""
+        m, k = x_shard.shape
+        n = w.shape[1] if w_is_kn else w.shape[0]
+        if not self._fits(m, n, k):
+            return self._ag_gemm_baseline(x_shard, w, w_is_kn)
+        self.calls += 1
+        self.epoch += 1
+        b = self.calls & 1
+        xs = self.x_sym[b]
+        xs.view(torch.bfloat16, m * k).view(m, k).copy_(x_shard)
+        self.barrier.sync(slot=0)
+        out = torch.empty(m * self.world, n, dtype=torch.bfloat16, device=self.device)
+        w = w if w.stride(-1) == 1 else w.contiguous()
+        nv.call("ttcd_ag_gemm", xs.ptr_array(), nv.ptr(w), nv.ptr(out), nv.ptr(self.gathered), nv.ptr(self.ready),
+                nv.i32(self.rank), nv.i32(self.world), nv.i64(m), nv.i64(n), nv.i64(k), nv.i64(w.stride(0)), nv.i64(n),
+                nv.i32(1 if w_is_kn else 0), nv.i32(self.epoch), nv.i64(self.wait_ns), nv.stream_ptr())
+        full = self.gathered[:m * self.world * k].view(m * self.world, k)
+        full[self.rank * m:(self.rank + 1) * m].copy_(x_shard)       # the kernel read the own rows in place
+        return out, full
+
+    def gemm_rs(self, x: torch.Tensor, w: torch.Tensor, w_is_kn: bool = False) -> torch.Tensor:
+        """Rows of this rank of ``sum_ranks(x_r @ W_r^T)``.  ``x``: [world*m_shard, K_local]."""
+        mt, k = x.shape
+        m = mt // self.world
+        n = w.shape[1] if w_is_kn else w.shape[0]
+        if mt % self.world or not self._fits(m, n, k):
+            return self._gemm_rs_baseline(x, w, w_is_kn)
+        self.calls += 1
+        self.epoch += 1
+        b = self.calls & 1
+        self.barrier.sync(slot=0)
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=self.device)
+        x = x if x.stride(-1) == 1 else x.contiguous()
+        w = w if w.stride(-1) == 1 else w.contiguous()
+        nv.call("ttcd_gemm_rs", nv.ptr(x), nv.ptr(w), nv.ptr(out), self.part_sym[b].ptr_array(), self.flag_sym[b].ptr_array(),
+                nv.ptr(self.peer_sum), nv.ptr(self.sum_flags), nv.i32(self.rank), nv.i32(self.world), nv.i64(m), nv.i64(n),
+                nv.i64(k), nv.i64(x.stride(0)), nv.i64(w.stride(0)), nv.i64(n), nv.i32(1 if w_is_kn else 0),
+                nv.i32(self.epoch), nv.i64(self.wait_ns), nv.stream_ptr())
+        return out
+
+    # NCCL / gloo statement of the same two operations (baseline and CPU path)
+    def _ag_gemm_baseline(self, x_shard, w, w_is_kn):
+        full = torch.empty(x_shard.shape[0] * self.world, x_shard.shape[1], dtype=x_shard.dtype, device=x_shard.device)
+        dist.all_gather_into_tensor(full, x_shard.contiguous(), group=self.group)
+        from .. import ops
+        return (ops.matmul(full, w) if w_is_kn else ops.linear(full, w)), full
+
+    def _gemm_rs_baseline(self, x, w, w_is_kn):
+        from .. import ops
+        y = ops.matmul(x, w) if w_is_kn else ops.linear(x, w)
+        out = torch.empty(y.shape[0] // self.world, y.shape[1], dtype=y.dtype, device=y.device)
+        if y.device.type == "cpu":          # gloo has no reduce_scatter
+            dist.all_reduce(y, group=self.group)
+            out.copy_(y[self.rank * out.shape[0]:(self.rank + 1) * out.shape[0]])
+        else:
+            dist.reduce_scatter_tensor(out, y.contiguous(), group=self.group)
+        return out
+
+    def check(self) -> None:
+        """Raise if any bounded wait of a fused kernel expired."""
+        if self.fused:
+            torch.cuda.synchronize()
+            code = nv.device_status()
+            if code:
+                raise RuntimeError(f"tensor-parallel kernel wait expired (status {code})")
+
+
+# ----------------------------------------------------------------------------------------- autograd
+class _ColumnParallel(torch.autograd.Function):
+    """y[all tokens, N_local] = all_gather(x_shard) @ W_local^T."""
+
+    @staticmethod
+    def forward(ctx, x_shard, weight, tp: TensorParallel):
+        y, full = tp.ag_gemm(x_shard, weight)
+        ctx.save_for_backward(full.clone() if tp.fused else full, weight)
+        ctx.tp = tp
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from .. import ops
+        full, weight = ctx.saved_tensors
+        tp = ctx.tp
+        dy = dy.contiguous()
+        dx_shard = tp.gemm_rs(dy, weight, w_is_kn=True)            # dX = dY @ W, reduce-scattered over tokens
+        dw = ops.matmul(dy.t(), full).to(weight.dtype)               # [N_local, K]
+        return dx_shard, dw, None
+
+
+class _RowParallel(torch.autograd.Function):
+    """y_shard[my tokens, N] = reduce_scatter(x[all tokens, K_local] @ W_local^T)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, tp: TensorParallel):
+        ctx.save_for_backward(x, weight)
+        ctx.tp = tp
+        return tp.gemm_rs(x, weight)
+
+    @staticmethod
+    def backward(ctx, dy_shard):
+        from .. import ops
+        x, weight = ctx.saved_tensors
+        tp = ctx.tp
+        dx, dy_full = tp.ag_gemm(dy_shard.contiguous(), weight, w_is_kn=True)   # dX = all_gather(dY) @ W
+        dw = ops.matmul(dy_full.t(), x).to(weight.dtype)                          # [N, K_local]
+        return dx, dw, None
+
+
+def column_parallel_linear(x_shard: torch.Tensor, weight: torch.Tensor, tp: TensorParallel | None = None) -> torch.Tensor:
+    return _ColumnParallel.apply(x_shard, weight, tp or _CTX)
+
+
+def row_parallel_linear(x: torch.Tensor, weight: torch.Tensor, tp: TensorParallel | None = None) -> torch.Tensor:
+    return _RowParallel.apply(x, weight, tp or _CTX)
