@@ -30,6 +30,11 @@ def register_all() -> None:
 
 register_all()
 
+# This package's own classes by ``model_type``: the engine resolves through this table, so another package
+# registering the same ``model_type`` strings with the HF Auto classes later cannot redirect it.
+MODEL_CLASSES = {cfg.model_type: (cfg, causal) for cfg, causal in (
+    (TransformerConfig, TransformerForCausalLM), (IPTTTConfig, IPTTTForCausalLM), (IPTTCDv9Config, IPTTCDForCausalLM))}
+
 __all__ = [
     "TransformerConfig", "IPTTTConfig", "IPTTCDConfig", "IPTTCDv8Config", "IPTTCDv9Config", "IPTTCDv9LowCopyConfig",
     "TransformerModel", "TransformerForCausalLM", "TransformerBlock",

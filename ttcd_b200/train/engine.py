@@ -43,6 +43,9 @@ def load_model_config(path_or_cfg, **overrides):
         if "num_hidden_layers" in overrides and "ttt_layers" in data:
             data["ttt_layers"] = [i for i in data["ttt_layers"] if i < overrides["num_hidden_layers"]]
         model_type = data.pop("model_type")
+        from ..models import MODEL_CLASSES
+        if model_type in MODEL_CLASSES:
+            return MODEL_CLASSES[model_type][0](**data)
         return AutoConfig.for_model(model_type, **data)
     for k, v in overrides.items():
         setattr(path_or_cfg, k, v)
@@ -56,8 +59,13 @@ def build_model(config, device, dtype, seed: int = 42):
     prev = torch.get_default_dtype()
     torch.set_default_dtype(dtype)
     try:
+        from ..models import MODEL_CLASSES
+        own = MODEL_CLASSES.get(getattr(config, "model_type", None))
         with torch.device(device):
-            model = AutoModelForCausalLM.from_config(config)
+            if own is not None and isinstance(config, own[0]):
+                model = own[1](config)
+            else:
+                model = AutoModelForCausalLM.from_config(config)
     finally:
         torch.set_default_dtype(prev)
     model.to(device=device, dtype=dtype)
