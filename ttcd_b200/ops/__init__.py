@@ -120,8 +120,23 @@ def attention(q, k, v, window=None, scale=None, cu_seqlens=None, return_lse: boo
     return reference.attention(q, k, v, window, scale, cu_seqlens, return_lse)
 
 
+_DUAL_IMPL = "fused"
+
+
+def set_dual_attention_impl(impl: str) -> str:
+    """``fused`` (default: one pass over K/V) or ``two_pass`` (two single-window calls, the reference's
+    unpatched behaviour) — an A/B switch for benchmarks.  Returns the previous setting."""
+    global _DUAL_IMPL
+    if impl not in ("fused", "two_pass"):
+        raise ValueError(f"unknown dual attention implementation {impl!r}")
+    prev, _DUAL_IMPL = _DUAL_IMPL, impl
+    return prev
+
+
 def dual_window_attention(q, k, v, window_teacher, window_student, scale=None, cu_seqlens=None):
     """Teacher and student sliding-window outputs in one pass over K/V."""
+    if _DUAL_IMPL == "two_pass":
+        return (attention(q, k, v, window_teacher, scale, cu_seqlens), attention(q, k, v, window_student, scale, cu_seqlens))
     if _native.use_native(q):
         return _cuda().dual_window_attention(q, k, v, window_teacher, window_student, scale, cu_seqlens)
     return reference.dual_window_attention(q, k, v, window_teacher, window_student, scale, cu_seqlens)
