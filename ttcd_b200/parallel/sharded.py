@@ -344,6 +344,8 @@ class ShardedDataParallel:
                                 g.exp_avg, g.exp_avg_sq, out_slice, lr=lr, beta1=b1, beta2=b2, eps=self.eps,
                                 weight_decay=self.weight_decay, step=self.step_count, coef=self._coef,
                                 skip=self._skip if self.skip_nan_inf else None)
+            elif self.skip_nan_inf and bool(self._skip):
+                pass          # PyTorch statement of the step (CPU): the host may look at the flag
             else:
                 grad = (self._local_grad(g) if self.world > 1 else g.flat_grad[lo:lo + shard]).float() * self._coef
                 ref_ops.adamw_step(g.master, grad, g.exp_avg, g.exp_avg_sq, lr=lr, beta1=b1, beta2=b2, eps=self.eps,
@@ -376,7 +378,8 @@ class ShardedDataParallel:
             if mp.owner == self.rank:
                 saved = mp.grad32
                 mp.grad32 = saved[:n]
-                muon_update(mp, lr, self.weight_decay, self.muon_momentum, coef)
+                muon_update(mp, lr, self.weight_decay, self.muon_momentum, coef,
+                            skip=self._skip if self.skip_nan_inf else None)
                 mp.grad32 = saved
                 if self.peer:
                     n8 = n // 8 * 8

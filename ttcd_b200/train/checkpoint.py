@@ -236,11 +236,16 @@ class CheckpointManager:
         else:
             return False
         t0 = time.perf_counter()
-        load_model_weights(self.engine.model, path, self.exclude)
-        self.engine.sdp.resync_master()
-        keys = checkpoint_keys(path)
-        if not weights_only and any(k.startswith("optimizer.") for k in keys):
-            self._load_training_state(path, keys)
+        try:
+            load_model_weights(self.engine.model, path, self.exclude)
+            self.engine.sdp.resync_master()
+            keys = checkpoint_keys(path)
+            if not weights_only and any(k.startswith("optimizer.") for k in keys):
+                self._load_training_state(path, keys)
+        except dcp.api.CheckpointException as exc:      # derives from BaseException: turn it into a normal error
+            older = [s for s in steps if s < step] if steps else []
+            hint = f"; resume from an older one with --checkpoint.load_step {older[-1]}" if older else ""
+            raise RuntimeError(f"checkpoint {path} is unreadable (truncated or corrupted shard){hint}") from exc
         self._log(f"loaded checkpoint {path} in {time.perf_counter() - t0:.1f}s")
         return True
 

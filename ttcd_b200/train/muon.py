@@ -69,13 +69,20 @@ def orthogonalize(g: torch.Tensor) -> torch.Tensor:
 
 
 def muon_update(mp: MuonParam, lr: float, weight_decay: float, momentum: float, coef: torch.Tensor | None,
-                nesterov: bool = True) -> torch.Tensor:
-    """Owner-side update of one parameter; returns the new fp32 master (in place)."""
+                nesterov: bool = True, skip: torch.Tensor | None = None) -> torch.Tensor:
+    """Owner-side update of one parameter; returns the new fp32 master (in place).  ``skip``: device int
+    scalar, non-zero when the step must leave momentum and weights untouched (non-finite gradient norm)."""
     g = mp.grad32 if coef is None else mp.grad32 * coef
-    mp.momentum.mul_(momentum).add_(g)
-    g = g.add(mp.momentum, alpha=momentum) if nesterov else mp.momentum
+    new_mom = mp.momentum * momentum + g
+    g = g.add(new_mom, alpha=momentum) if nesterov else new_mom
     u = orthogonalize(g.view(mp.param.shape)).float().reshape(-1)
     rows, cols = mp.param.shape[-2], mp.param.shape[-1]      # last two dims also for >2-D parameters (707-716)
     adj_lr = lr * 0.2 * math.sqrt(max(rows, cols))
-    mp.master.mul_(1.0 - lr * weight_decay).add_(u, alpha=-adj_lr)
+    new_master = (mp.master * (1.0 - lr * weight_decay)).add_(u, alpha=-adj_lr)
+    if skip is not None:
+        keep = skip == 0
+        new_mom = torch.where(keep, new_mom, mp.momentum)
+        new_master = torch.where(keep, new_master, mp.master)
+    mp.momentum.copy_(new_mom)
+    mp.master.copy_(new_master)
     return mp.master
