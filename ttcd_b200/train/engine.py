@@ -25,6 +25,7 @@ class EngineConfig:
     eps: float = 1e-15
     weight_decay: float = 0.1
     max_norm: float | None = 1.0
+    activation_offload: bool = False          # saved activations -> pinned host memory on a side stream
     activation_checkpoint: str = "full"       # full | none | everyN (checkpoint every Nth block) | ttt (TTT blocks only)
     dtype: torch.dtype = torch.bfloat16
     skip_nan_inf: bool = False
@@ -121,8 +122,10 @@ class TrainEngine:
         cp = getattr(self, "cp", None)
         if cp is not None:
             return self._forward_backward_cp(ids, lab, scale, cp, **model_kwargs)
-        out = self.model(input_ids=ids, labels=lab, **model_kwargs)
-        loss = out.loss
+        from .activation_offload import get_act_offloading_ctx_manager
+        with get_act_offloading_ctx_manager(self.cfg.activation_offload and self.device.type == "cuda"):
+            out = self.model(input_ids=ids, labels=lab, **model_kwargs)
+            loss = out.loss
         (loss * scale if scale != 1.0 else loss).backward()
         self.tokens_seen += ids.numel()
         return loss.detach()
