@@ -176,3 +176,33 @@ def test_trainer_runs_checkpoints_and_resumes(tmp_path):
     dcp.load(a, checkpoint_id=str(run / "checkpoint" / "step-4"), no_dist=True)
     dcp.load(b, checkpoint_id=str(other / "run" / "checkpoint" / "step-4"), no_dist=True)
     torch.testing.assert_close(a[name], b[name], rtol=1e-5, atol=1e-6)
+
+
+# ------------------------------------------------------------------------------------------- IP-TTT inference
+def test_ipttt_fast_weights_persist_across_incremental_calls():
+    """Feeding a prompt in pieces (and token by token) through the fast-weight cache gives the logits of one
+    full forward: the adapted down_proj weight and the unfinished chunk survive between calls
+    (custom_models/ipttt/inference.py:505-538)."""
+    from ttcd_b200.models import IPTTTConfig, IPTTTForCausalLM
+    from ttcd_b200.models.modeling_ipttt import FastWeightCache
+    torch.manual_seed(0)
+    cfg = IPTTTConfig(hidden_size=32, num_hidden_layers=2, num_heads=4, num_kv_heads=2, intermediate_size=64, vocab_size=64,
+                      window_size=64, ttt_mode=True, ttt_chunk=8, ttt_layers=[0, 1], ttt_lr=0.5, ttt_proj=True, ttt_conv=True,
+                      fuse_cross_entropy=False, max_position_embeddings=128, tie_word_embeddings=False)
+    model = IPTTTForCausalLM(cfg).eval()
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if "ttt_conv" in n or "ttt_proj" in n:
+                p.normal_(0, 0.3)
+    ids = torch.randint(0, 64, (1, 29))
+    with torch.no_grad():
+        full = model(input_ids=ids, use_cache=True).logits
+        cache = FastWeightCache()
+        pieces = [model(input_ids=ids[:, a:b], past_key_values=cache, use_cache=True).logits
+                  for a, b in ((0, 11), (11, 12), (12, 13), (13, 24), (24, 29))]
+    assert cache.ttt_get(0)[2] is not None and cache.ttt_get(0)[0].shape[1] == 29 % 8
+    torch.testing.assert_close(torch.cat(pieces, dim=1), full, rtol=1e-4, atol=1e-4)
+    # the fast weight did move away from the slow weight
+    assert (cache.ttt_get(0)[2][0] - model.model.layers[0].mlp.down_proj.weight).abs().max() > 1e-4
+    out = model.generate(ids, max_new_tokens=4)
+    assert out.shape == (1, 33)

@@ -6,9 +6,10 @@ Importing this package registers ``transformer``, ``ipttt`` and ``ipttcdv9`` wit
 """
 from transformers import AutoConfig, AutoModel, AutoModelForCausalLM
 
-from .configuration import (IPTTCDConfig, IPTTCDv8Config, IPTTCDv9Config, IPTTCDv9LowCopyConfig, IPTTTConfig,
+from .configuration import (DeltaNetBaselineConfig, IPTTCDConfig, IPTTCDv8Config, IPTTCDv9Config, IPTTCDv9LowCopyConfig, IPTTTConfig,
                             TransformerConfig)
 from .layers import Attention, GatedMLP, RMSNorm, RotaryEmbedding, WindowKVCache
+from .modeling_deltanet_baseline import DeltaNetBaselineBlock, DeltaNetBaselineForCausalLM, DeltaNetBaselineModel
 from .modeling_ipttcdv9 import IPTTCDBlock, IPTTCDForCausalLM, IPTTCDMLP, IPTTCDModel
 from .modeling_ipttt import IPTTTBlock, IPTTTForCausalLM, IPTTTMLP, IPTTTModel
 from .modeling_transformer import TransformerBlock, TransformerForCausalLM, TransformerModel
@@ -22,6 +23,7 @@ def register_all() -> None:
         (TransformerConfig, TransformerModel, TransformerForCausalLM),
         (IPTTTConfig, IPTTTModel, IPTTTForCausalLM),
         (IPTTCDv9Config, IPTTCDModel, IPTTCDForCausalLM),
+        (DeltaNetBaselineConfig, DeltaNetBaselineModel, DeltaNetBaselineForCausalLM),
     ):
         AutoConfig.register(cfg.model_type, cfg, exist_ok=True)
         AutoModel.register(cfg, model, exist_ok=True)
@@ -33,9 +35,11 @@ register_all()
 # This package's own classes by ``model_type``: the engine resolves through this table, so another package
 # registering the same ``model_type`` strings with the HF Auto classes later cannot redirect it.
 MODEL_CLASSES = {cfg.model_type: (cfg, causal) for cfg, causal in (
-    (TransformerConfig, TransformerForCausalLM), (IPTTTConfig, IPTTTForCausalLM), (IPTTCDv9Config, IPTTCDForCausalLM))}
+    (TransformerConfig, TransformerForCausalLM), (IPTTTConfig, IPTTTForCausalLM), (IPTTCDv9Config, IPTTCDForCausalLM),
+    (DeltaNetBaselineConfig, DeltaNetBaselineForCausalLM))}
 
 __all__ = [
+    "DeltaNetBaselineConfig", "DeltaNetBaselineModel", "DeltaNetBaselineForCausalLM", "DeltaNetBaselineBlock",
     "TransformerConfig", "IPTTTConfig", "IPTTCDConfig", "IPTTCDv8Config", "IPTTCDv9Config", "IPTTCDv9LowCopyConfig",
     "TransformerModel", "TransformerForCausalLM", "TransformerBlock",
     "IPTTTModel", "IPTTTForCausalLM", "IPTTTBlock", "IPTTTMLP",

@@ -155,7 +155,7 @@ class DecoderModel(DecoderPreTrainedModel):
         if (input_ids is None) == (inputs_embeds is None):
             raise ValueError("Specify exactly one of input_ids / inputs_embeds")
         if use_cache and not isinstance(past_key_values, WindowKVCache):
-            past_key_values = WindowKVCache()
+            past_key_values = getattr(self, "cache_class", WindowKVCache)()
         if not use_cache:
             past_key_values = past_key_values if isinstance(past_key_values, WindowKVCache) else None
         if inputs_embeds is None:
@@ -276,7 +276,7 @@ class DecoderForCausalLM(DecoderPreTrainedModel):
         """
         eos = set(eos_token_id if isinstance(eos_token_id, (list, tuple)) else
                   ([eos_token_id] if eos_token_id is not None else []))
-        cache = WindowKVCache()
+        cache = getattr(self.model, "cache_class", WindowKVCache)()
         out = self(input_ids=input_ids, attention_mask=attention_mask, past_key_values=cache,
                    use_cache=True, logits_to_keep=1)
         tokens = input_ids

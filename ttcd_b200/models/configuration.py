@@ -325,7 +325,17 @@ class IPTTCDv9LowCopyConfig(IPTTCDv9Config):
         super().__init__(**kwargs)
 
 
+class DeltaNetBaselineConfig(IPTTCDConfig):
+    """SWA transformer + training-only DeltaNet sub-layer on ``ttt_layers`` (same fields as ``ipttcd``)."""
+
+    model_type = "deltanet_baseline"
+
+    def __init__(self, **kwargs):  # explicit: keeps HF from generating a dataclass __init__
+        super().__init__(**kwargs)
+
+
 __all__ = [
+    "DeltaNetBaselineConfig",
     "TransformerConfig",
     "IPTTTConfig",
     "IPTTCDConfig",

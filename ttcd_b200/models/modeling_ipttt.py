@@ -20,7 +20,7 @@ import torch.nn.functional as F
 from .. import ops
 from .base import DecoderForCausalLM, DecoderModel
 from .configuration import IPTTTConfig
-from .layers import GatedMLP, RMSNorm
+from .layers import WindowKVCache, GatedMLP, RMSNorm
 from .modeling_transformer import build_attention
 
 
@@ -83,6 +83,52 @@ class IPTTTMLP(GatedMLP):
         v = getattr(self, "_last_delta_w_norm_t", None)
         return None if v is None else float(v)
 
+    def forward_online(self, x, t, past_w=None):
+        """Incremental inference (custom_models/ipttt/inference.py:248-310): chunk by chunk, output with the
+        current fast weight, then update it from every COMPLETE chunk.  Returns ``(y, present_w)`` with
+        ``present_w`` [b, d_h, d_i] to carry into the next call."""
+        b, seq_len, _ = x.shape
+        h = self.features(x)
+        w = self.down_proj.weight.to(h.dtype).expand(b, -1, -1) if past_w is None else past_w
+        if t is None or not self.is_ttt_layer or seq_len < self.ttt_chunk:
+            return torch.matmul(h, w.transpose(-1, -2)), w
+        hp, tgt = pad_to_chunks(h, self.ttt_chunk), pad_to_chunks(t, self.ttt_chunk)
+        if self.ttt_conv is not None:
+            tgt = ops.dwconv_chunked(tgt, self.ttt_conv.weight, self.ttt_conv_causal)
+        if self.ttt_activation_conv is not None:
+            hp = ops.dwconv_chunked(hp, self.ttt_activation_conv.weight, self.ttt_conv_causal)
+        p = tgt if self.ttt_proj is None else torch.matmul(tgt, self.ttt_proj.weight.to(tgt.dtype))
+        n_chunks = hp.shape[1]
+        complete = seq_len // self.ttt_chunk
+        ys = []
+        for i in range(n_chunks):
+            ys.append(torch.matmul(hp[:, i], w.transpose(-1, -2)))
+            if i < complete:
+                w = w + self.ttt_lr * torch.matmul(p[:, i].transpose(-1, -2), hp[:, i])
+        return torch.cat(ys, dim=1)[:, :seq_len], w
+
+
+class FastWeightCache(WindowKVCache):
+    """KV cache that also carries, per TTT layer, the adapted ``down_proj`` weight and the MLP inputs /
+    targets of the last incomplete chunk (custom_models/ipttt/inference.py:64-79, 505-538), so fast weights
+    persist across incremental ``forward`` calls and decode steps."""
+
+    def __init__(self):
+        super().__init__()
+        self.ttt_states: dict[int, tuple] = {}
+
+    def ttt_get(self, layer_idx: int):
+        return self.ttt_states.get(layer_idx, (None, None, None))
+
+    def ttt_update(self, state: tuple, layer_idx: int) -> None:
+        self.ttt_states[layer_idx] = state
+
+    def reorder(self, beam_idx: torch.Tensor):
+        super().reorder(beam_idx)
+        for i, (h, t, w) in self.ttt_states.items():
+            sel = lambda v: None if v is None else v.index_select(0, beam_idx)  # noqa: E731
+            self.ttt_states[i] = (sel(h), sel(t), sel(w))
+
 
 def _ipttt_scan(p, h, w_down, lr):
     """Scan with externally supplied update vectors: dW_j = p_j^T h_j."""
@@ -115,8 +161,23 @@ class IPTTTBlock(nn.Module):
         target = None
         if self.is_ttt_layer:
             target = ttt_target_states if self.config.ttt_target == "embedding" else hidden_states
+        if self.is_ttt_layer and isinstance(past_key_values, FastWeightCache) and not self.training:
+            return residual + self._online_mlp(hidden_states, target, past_key_values)
         hidden_states = self.mlp(hidden_states, t=target)
         return residual + hidden_states
+
+    def _online_mlp(self, hidden_states, target, cache: "FastWeightCache"):
+        """MLP with fast weights carried across calls: prepend the unfinished chunk kept in the cache, run the
+        online scan from the cached weight, return the outputs of the new positions, keep the new remainder."""
+        n_new = hidden_states.shape[1]
+        past_h, past_t, past_w = cache.ttt_get(self.layer_idx)
+        h_all = hidden_states if past_h is None else torch.cat([past_h, hidden_states], dim=1)
+        t_all = target if past_t is None else torch.cat([past_t, target], dim=1)
+        y, w = self.mlp.forward_online(h_all, t_all, past_w)
+        rem = h_all.shape[1] % self.mlp.ttt_chunk
+        tail_h, tail_t = (h_all[:, -rem:], t_all[:, -rem:]) if rem else (None, None)
+        cache.ttt_update((tail_h, tail_t, w), self.layer_idx)
+        return y[:, -n_new:]
 
 
 class _IPTTTInit:
@@ -139,6 +200,7 @@ class _IPTTTInit:
 
 
 class IPTTTModel(_IPTTTInit, DecoderModel):
+    cache_class = FastWeightCache       # inference carries fast weights across calls
     config_class = IPTTTConfig
     block_class = IPTTTBlock
     _no_split_modules = ["IPTTTBlock"]

@@ -390,3 +390,63 @@ def adamw_step(param, grad, exp_avg, exp_avg_sq, *, lr, beta1, beta2, eps, weigh
     denom = (exp_avg_sq.sqrt() / math.sqrt(bc2)).add_(eps)
     param.addcdiv_(exp_avg, denom, value=-lr / bc1)
     return param
+
+
+# ---------------------------------------------------------------------------------------------
+# delta rule (DeltaNet baseline)
+# ---------------------------------------------------------------------------------------------
+def delta_rule_recurrent(q, k, v, beta, scale=None, l2norm: bool = True):
+    """Token-by-token statement: S_t = S_{t-1} + k_t (beta_t (v_t - S_{t-1}^T k_t))^T, o_t = S_t^T (scale q_t).
+    q, k, v: [B, T, H, D]; beta: [B, T, H].  The oracle for ``delta_rule_chunked``."""
+    qf, kf, vf, bf = q.float(), k.float(), v.float(), beta.float()
+    if l2norm:
+        qf, kf = F.normalize(qf, dim=-1, eps=1e-6), F.normalize(kf, dim=-1, eps=1e-6)
+    scale = q.shape[-1] ** -0.5 if scale is None else scale
+    B, T, H, D = qf.shape
+    S = qf.new_zeros(B, H, D, vf.shape[-1])
+    out = []
+    for t in range(T):
+        kt, vt, bt = kf[:, t], vf[:, t], bf[:, t].unsqueeze(-1)
+        pred = torch.einsum("bhkv,bhk->bhv", S, kt)
+        S = S + torch.einsum("bhk,bhv->bhkv", kt, bt * (vt - pred))
+        out.append(torch.einsum("bhkv,bhk->bhv", S, qf[:, t] * scale))
+    return torch.stack(out, dim=1).to(q.dtype)
+
+
+def delta_rule_chunked(q, k, v, beta, scale=None, l2norm: bool = True, chunk: int = 64, cu_seqlens=None):
+    """Chunk-parallel delta rule (WY representation): inside a chunk the updates are solved with one
+    unit-lower-triangular system, the state is carried chunk to chunk (the computation of
+    fla/ops/delta_rule/chunk.py with ``use_qk_l2norm_in_kernel``).  Differentiable through autograd."""
+    if cu_seqlens is not None:
+        bounds = cu_seqlens.tolist()
+        return torch.cat([delta_rule_chunked(q[:, a:b], k[:, a:b], v[:, a:b], beta[:, a:b], scale, l2norm, chunk)
+                          for a, b in zip(bounds[:-1], bounds[1:])], dim=1)
+    dtype = q.dtype
+    qf, kf, vf, bf = q.float(), k.float(), v.float(), beta.float()
+    if l2norm:
+        qf, kf = F.normalize(qf, dim=-1, eps=1e-6), F.normalize(kf, dim=-1, eps=1e-6)
+    scale = q.shape[-1] ** -0.5 if scale is None else scale
+    B, T, H, D = qf.shape
+    pad = (-T) % chunk
+    if pad:
+        qf, kf, vf = (F.pad(x, (0, 0, 0, 0, 0, pad)) for x in (qf, kf, vf))
+        bf = F.pad(bf, (0, 0, 0, pad))
+    n = (T + pad) // chunk
+    # [B, H, n, C, D]
+    qc, kc, vc = (x.view(B, n, chunk, H, -1).permute(0, 3, 1, 2, 4) for x in (qf * scale, kf, vf))
+    bc = bf.view(B, n, chunk, H).permute(0, 3, 1, 2).unsqueeze(-1)
+    kb, vb = kc * bc, vc * bc
+    eye = torch.eye(chunk, device=q.device)
+    lower = torch.tril(kb @ kc.transpose(-1, -2), -1)
+    t_inv = torch.linalg.solve_triangular(eye + lower, eye.expand_as(lower), upper=False)
+    w, u = t_inv @ kb, t_inv @ vb
+    qk = torch.tril(qc @ kc.transpose(-1, -2))
+    S = qf.new_zeros(B, H, D, vf.shape[-1])
+    outs = []
+    for i in range(n):
+        u_i = u[:, :, i] - w[:, :, i] @ S
+        outs.append(qc[:, :, i] @ S + qk[:, :, i] @ u_i)
+        S = S + kc[:, :, i].transpose(-1, -2) @ u_i
+    o = torch.stack(outs, dim=2)                           # [B, H, n, C, Dv]
+    o = o.permute(0, 2, 3, 1, 4).reshape(B, n * chunk, H, -1)[:, :T]
+    return o.to(dtype)
