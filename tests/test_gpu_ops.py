@@ -328,3 +328,33 @@ def test_activation_offload_roundtrip_matches_resident():
         torch.testing.assert_close(a, b)
     got2 = run(off)          # second pass reuses the pooled host buffers
     torch.testing.assert_close(ref[0], got2[0])
+
+
+@pytest.mark.parametrize("b,T,with_beta", [(1, 4, True), (2, 3, True), (1, 5, False), (1, 1, True)])
+def test_fused_ttt_scan_matches_reference(b, T, with_beta):
+    """Batched-GEMM scan with prefix/suffix kernels vs the fp32 statement of the same math: outputs and all
+    six gradients."""
+    from ttcd_b200.ops import cuda
+    from ttcd_b200.ops import reference as ref
+    torch.manual_seed(3)
+    C, d_i, d_h, lr = 128, 256, 128, 0.3
+    mk = lambda *s, scale=1.0: (torch.randn(*s, device="cuda") * scale).bfloat16().requires_grad_()  # noqa: E731
+    z_out, z_tgt, z_hat = mk(b, T, C, d_i, scale=0.5), mk(b, T, C, d_i, scale=0.5), mk(b, T, C, d_i, scale=0.5)
+    beta = torch.sigmoid(torch.randn(b, T, C, 1, device="cuda")).bfloat16().requires_grad_() if with_beta else None
+    w_down, w_upd = mk(d_h, d_i, scale=0.05), mk(d_i, d_h, scale=0.05)
+    dy = (torch.randn(b, T, C, d_h, device="cuda") * 0.1).bfloat16()
+    inputs = [t for t in (z_out, z_tgt, z_hat, beta, w_down, w_upd) if t is not None]
+    y, last = cuda.ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_upd, lr)
+    got = torch.autograd.grad(y, inputs, dy)
+    f = lambda t: None if t is None else t.detach().float().requires_grad_()  # noqa: E731
+    fin = [f(t) for t in (z_out, z_tgt, z_hat, beta, w_down, w_upd)]
+    y_ref, last_ref = ref.ttt_scan(*fin, lr=lr, update_every=2, state_dtype=torch.float32, return_last_dw_norm=True)
+    want = torch.autograd.grad(y_ref, [t for t in fin if t is not None], dy.float())
+    torch.testing.assert_close(y.float(), y_ref, rtol=3e-2, atol=3e-2)
+    if T > 1:
+        torch.testing.assert_close(last.float(), last_ref.float(), rtol=3e-2, atol=1e-2)
+    names = [n for n, t in zip(("z_out", "z_tgt", "z_hat", "beta", "w_down", "w_upd"), (z_out, z_tgt, z_hat, beta, w_down, w_upd)) if t is not None]
+    for n, a, w in zip(names, got, want):
+        err = (a.float() - w).abs().max().item()
+        ref_mag = w.abs().max().item() + 1e-6
+        assert err / ref_mag < 6e-2, (n, err, ref_mag)

@@ -759,3 +759,100 @@ def cast_scale(x: torch.Tensor, y: torch.Tensor, scale: float = 1.0, accumulate:
     kinds = {(_BF16, torch.float32): 0, (torch.float32, _BF16): 1, (torch.float32, torch.float32): 2, (_BF16, _BF16): 3}
     nv.call("ttcd_cast_scale", nv.ptr(x), nv.ptr(y), nv.i64(x.numel()), nv.f32(scale), nv.i32(kinds[(x.dtype, y.dtype)]),
             nv.i32(1 if accumulate else 0), nv.stream_ptr())
+
+
+# ---------------------------------------------------------------------------------------------
+# fast-weight chunk scan
+# ---------------------------------------------------------------------------------------------
+class _TTTScan(torch.autograd.Function):
+    """Grouped fast-weight scan of the TTT layers as batched tensor-core GEMMs with fused epilogues:
+
+        P   = beta * ((z_tgt - z_hat) @ Wu)            one GEMM, beta in the epilogue (row scale)
+        dW  = P^T @ z_hat                              one batched GEMM (fp32 out), chunks 0..T-2
+        W_i = W_down + lr * sum_{j<i} dW_j             one streaming kernel (prefix + add + cast)
+        Y_i = z_out_i @ W_i^T                          one batched GEMM
+
+    with a hand-written backward (five batched GEMMs + the reverse-prefix kernel).  Same math as
+    ``reference.ttt_scan`` for the plain configuration (no feature normalisation, fp32 state).
+    """
+
+    @staticmethod
+    def forward(ctx, z_out, z_tgt, z_hat, beta, w_down, w_update_t, lr):
+        b, T, C, d_i = z_out.shape
+        d_h = w_down.shape[0]
+        z_out, z_tgt, z_hat = z_out.contiguous(), z_tgt.contiguous(), z_hat.contiguous()
+        w_down_c = w_down.to(_BF16).contiguous()
+        wu = w_update_t.to(_BF16)
+        wu = wu if wu.stride(-1) == 1 or wu.stride(-2) == 1 else wu.contiguous()
+        nu = T - 1
+        R = d_h * d_i
+        states = torch.empty(b, T, d_h, d_i, dtype=_BF16, device=z_out.device)
+        P = None
+        last_norm = torch.zeros((), dtype=torch.float32, device=z_out.device)
+        if nu > 0:
+            diff = z_tgt[:, :nu] - z_hat[:, :nu]
+            scale = None if beta is None else beta[:, :nu].reshape(-1).to(_BF16).contiguous()
+            P = gemm(diff.reshape(b * nu * C, d_i), wu, row_scale=scale).view(b * nu, C, d_h)
+            del diff
+            zh_u = z_hat[:, :nu].reshape(b * nu, C, d_i)
+            d_w = gemm(P.transpose(-1, -2), zh_u, out_dtype=torch.float32)            # [b*nu, d_h, d_i]
+            last_norm = d_w.view(b, nu, -1)[:, -1].norm()
+        else:
+            d_w = torch.empty(0, dtype=torch.float32, device=z_out.device)
+        nv.call("ttcd_ttt_prefix_weights", nv.ptr(d_w if nu > 0 else None), nv.ptr(w_down_c), nv.ptr(None), nv.ptr(states),
+                nv.f32(float(lr)), nv.i32(b), nv.i32(T), nv.i64(R), nv.stream_ptr())
+        del d_w
+        y = gemm(z_out.view(b * T, C, d_i), states.view(b * T, d_h, d_i).transpose(-1, -2)).view(b, T, C, d_h)
+        ctx.save_for_backward(z_out, z_tgt, z_hat, beta, wu, states, P)
+        ctx.lr, ctx.w_dtype, ctx.wu_dtype = float(lr), w_down.dtype, w_update_t.dtype
+        ctx.mark_non_differentiable(last_norm)
+        return y, last_norm
+
+    @staticmethod
+    def backward(ctx, dy, _dnorm):
+        z_out, z_tgt, z_hat, beta, wu, states, P = ctx.saved_tensors
+        b, T, C, d_i = z_out.shape
+        d_h = states.shape[2]
+        nu, R, lr = T - 1, d_h * d_i, ctx.lr
+        dy3 = dy.to(_BF16).contiguous().view(b * T, C, d_h)
+        dz_out = gemm(dy3, states.view(b * T, d_h, d_i)).view(b, T, C, d_i)
+        d_states = gemm(dy3.transpose(-1, -2), z_out.view(b * T, C, d_i), out_dtype=torch.float32)       # [b*T, d_h, d_i]
+        g = torch.empty(b, max(nu, 1), d_h, d_i, dtype=_BF16, device=dy.device)
+        d_w_down = torch.empty(d_h, d_i, dtype=torch.float32, device=dy.device)
+        nv.call("ttcd_ttt_suffix_grads", nv.ptr(d_states), nv.ptr(g), nv.ptr(d_w_down), nv.f32(lr), nv.i32(b), nv.i32(T),
+                nv.i64(R), nv.stream_ptr())
+        del d_states
+        dz_tgt = torch.zeros_like(z_tgt) if b > 1 or nu == 0 else torch.empty_like(z_tgt)
+        dz_hat = torch.zeros_like(z_hat) if b > 1 or nu == 0 else torch.empty_like(z_hat)
+        d_beta = d_wu = None
+        if nu > 0:
+            g3 = g.view(b * nu, d_h, d_i)
+            zh_u = z_hat[:, :nu].reshape(b * nu, C, d_i)
+            dP = gemm(zh_u, g3.transpose(-1, -2))                                         # [b*nu, C, d_h]
+            if beta is not None:
+                bu = beta[:, :nu].reshape(b * nu, C, 1)
+                d_beta_u = ((dP.float() * P.float()).sum(-1, keepdim=True) / bu.float().clamp_min(1e-20)).to(beta.dtype)
+                d_beta = torch.cat([d_beta_u.view(b, nu, C, 1), torch.zeros_like(beta[:, :1])], dim=1)
+                dP = dP * bu.to(_BF16)
+            diff = (z_tgt[:, :nu] - z_hat[:, :nu]).reshape(b * nu * C, d_i)
+            d_wu = gemm(diff.transpose(-1, -2), dP.view(b * nu * C, d_h)).view(d_i, d_h).to(ctx.wu_dtype)
+            del diff
+            if b == 1:
+                dd = dz_tgt[0, :nu].view(nu, C, d_i)
+                gemm(dP.view(nu * C, d_h), wu.transpose(-1, -2), out=dd.view(1, nu * C, d_i))
+                gemm(P, g3, alpha=1.0, beta=-1.0, c_in=dd, out=dz_hat[0, :nu].view(nu, C, d_i))
+                dz_tgt[0, nu:].zero_()
+                dz_hat[0, nu:].zero_()
+            else:
+                dd = gemm(dP.view(b * nu * C, d_h), wu.transpose(-1, -2)).view(b * nu, C, d_i)
+                dzh = gemm(P, g3, alpha=1.0, beta=-1.0, c_in=dd)
+                dz_tgt[:, :nu] = dd.view(b, nu, C, d_i)
+                dz_hat[:, :nu] = dzh.view(b, nu, C, d_i)
+        return dz_out, dz_tgt, dz_hat, d_beta, d_w_down.to(ctx.w_dtype), d_wu, None
+
+
+def ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, lr: float):
+    """Returns ``(y [b,T,C,d_h], norm of the last chunk update)``; see ``_TTTScan``."""
+    for name, t in (("z_out", z_out), ("z_tgt", z_tgt), ("z_hat", z_hat)):
+        _check(t, name)
+    return _TTTScan.apply(z_out, z_tgt, z_hat, beta, w_down, w_update_t, float(lr))
