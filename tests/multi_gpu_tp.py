@@ -44,3 +44,37 @@ def check_tensor_parallel():
     torch.testing.assert_close(w2.grad.float(), dyf.t() @ x2.detach().float(), rtol=3e-2, atol=6e-2)
     tp.check()
     tp.close()
+
+
+def check_tp_model():
+    """IP-TTCD under tensor+sequence parallelism (fused kernels where the shapes allow) vs the same model on
+    one GPU: loss, gradient norm and weights after one optimizer step."""
+    from ttcd_b200.models import IPTTCDv9Config
+    from ttcd_b200.parallel import tensor as tpmod
+    from ttcd_b200.train.engine import EngineConfig, TrainEngine
+    rank, world = dist.get_rank(), dist.get_world_size()
+    dev = f"cuda:{torch.cuda.current_device()}"
+    cfg = IPTTCDv9Config(hidden_size=256, num_hidden_layers=2, num_heads=4, num_kv_heads=2, head_dim=64, intermediate_size=1024,
+                         vocab_size=4096, window_size=256, max_position_embeddings=2048, ttt_mode=True, ttt_chunk=128,
+                         ttt_layers=[1], ttt_update_every=4, qk_norm=True, tie_word_embeddings=False, fuse_cross_entropy=False,
+                         fuse_linear_cross_entropy=True, ttt_teacher_conv_init="identity", ttt_normalize_student_features=False)
+    ids = torch.randint(0, cfg.vocab_size, (1, 1024), generator=torch.Generator().manual_seed(5)).cuda()
+    ref = TrainEngine(cfg, EngineConfig(lr=1e-3, seed=7, activation_checkpoint="none"), device=dev, process_group=False)
+    ref.sdp.zero_grad()
+    ref_loss = float(ref.forward_backward(ids))
+    ref_norm = float(ref.sdp.step(1e-3))
+    ref_after = {n: p.detach().float().clone() for n, p in ref.model.named_parameters()}
+    del ref
+    eng = TrainEngine(cfg, EngineConfig(lr=1e-3, seed=7, activation_checkpoint="none", tensor_parallel=world), device=dev)
+    assert eng.tp is not None and eng.tp.fused
+    eng.sdp.zero_grad()
+    loss = float(eng.forward_backward(ids))
+    norm = float(eng.sdp.step(1e-3))
+    assert eng.tp.calls > 0, "no fused tensor-parallel kernel ran"
+    assert abs(loss - ref_loss) < 2e-2, (loss, ref_loss)
+    assert abs(norm - ref_norm) < 5e-2 * max(1.0, ref_norm), (norm, ref_norm)
+    full = tpmod.gather_full_state_dict(eng.model, eng.tp)
+    worst = max(((full[n].float() - ref_after[n]).abs().max().item(), n) for n in ref_after)
+    assert worst[0] < 2e-2, worst
+    eng.tp.check()
+    eng.tp.close()

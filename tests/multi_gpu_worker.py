@@ -79,8 +79,9 @@ def main():
     if what in ("all", "muon"):
         check_sharded_modes(muon=True)
     if what in ("all", "tp"):
-        from tests.multi_gpu_tp import check_tensor_parallel
+        from tests.multi_gpu_tp import check_tensor_parallel, check_tp_model
         check_tensor_parallel()
+        check_tp_model()
     if what in ("all", "cp"):
         from tests.multi_gpu_cp import check_context_parallel
         check_context_parallel()

@@ -1,0 +1,97 @@
+"""Tensor + sequence parallel wiring on CPU (gloo, 2 ranks): head / row / column sharding, token-sharded
+residual stream, the TP-legal fast-weight scan (all-reduced projection, reduce-scattered output), globally
+shifted labels and replicated-gradient sums must reproduce the single-process loss and gradients."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from ttcd_b200.models import IPTTCDv9Config
+
+KW = dict(hidden_size=64, num_hidden_layers=2, num_heads=4, num_kv_heads=2, head_dim=16, intermediate_size=128,
+          vocab_size=256, window_size=48, ttt_mode=True, ttt_chunk=16, ttt_visible_chunks=1, ttt_layers=[1], ttt_lr=0.05,
+          ttt_update_every=2, fuse_cross_entropy=False, ttt_teacher_conv_init="identity", qk_norm=True,
+          ttt_normalize_student_features=False, max_position_embeddings=256, tie_word_embeddings=False)
+
+
+def _prepare(eng):
+    with torch.no_grad():
+        for n, p in eng.model.named_parameters():
+            if "conv" in n:
+                p.normal_(0, 0.3, generator=torch.Generator().manual_seed(11))
+    eng.sdp.resync_master()
+
+
+def _worker(rank, world, port, ids, ref_loss, ref_grads, ref_after, q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        from ttcd_b200.train.engine import EngineConfig, TrainEngine
+        # the full model is built first (same seed everywhere), conv weights set, then sharded by the engine
+        import ttcd_b200.parallel.tensor as tpmod
+        orig = tpmod.shard_model
+
+        def shard_after_prepare(model, tp):
+            with torch.no_grad():
+                for n, p in model.named_parameters():
+                    if "conv" in n:
+                        p.normal_(0, 0.3, generator=torch.Generator().manual_seed(11))
+            orig(model, tp)
+
+        tpmod.shard_model = shard_after_prepare
+        eng = TrainEngine(IPTTCDv9Config(**KW), EngineConfig(dtype=torch.float32, lr=1e-2, seed=3, activation_checkpoint="none",
+                                                             tensor_parallel=world, max_norm=1.0), device="cpu")
+        eng.sdp.zero_grad()
+        loss = eng.forward_backward(ids)
+        worst = (0.0, "")
+        for n, p in eng.model.named_parameters():
+            want = ref_grads[n]
+            shard = getattr(p, "_tp_shard", None)
+            if shard is not None:
+                per = want.shape[shard[0]] // world
+                want = want.narrow(shard[0], rank * per, per)
+            err = (p.grad - want).abs().max().item() / (want.abs().max().item() + 1e-6)
+            worst = max(worst, (err, n))
+        norm = float(eng.sdp.step(1e-2))
+        full = tpmod.gather_full_state_dict(eng.model, eng.tp)
+        after = max(((full[n] - ref_after[n]).abs().max().item(), n) for n in ref_after)
+        q.put((rank, abs(float(loss) - ref_loss), worst, norm, after))
+        dist.destroy_process_group()
+    except Exception:  # pragma: no cover
+        import traceback
+        q.put((rank, "error", traceback.format_exc(), 0, 0))
+
+
+@pytest.mark.timeout(300)
+def test_tensor_parallel_matches_single_process():
+    torch.manual_seed(0)
+    ids = torch.randint(0, 256, (1, 128))
+    from ttcd_b200.train.engine import EngineConfig, TrainEngine
+    eng = TrainEngine(IPTTCDv9Config(**KW), EngineConfig(dtype=torch.float32, lr=1e-2, seed=3, activation_checkpoint="none",
+                                                         max_norm=1.0), device="cpu")
+    _prepare(eng)
+    eng.sdp.zero_grad()
+    loss = float(eng.forward_backward(ids))
+    grads = {n: p.grad.clone() for n, p in eng.model.named_parameters()}
+    ref_norm = float(eng.sdp.step(1e-2))
+    after = {n: p.detach().clone() for n, p in eng.model.named_parameters()}
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, ids, loss, grads, after, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(30)
+    for rank, err, worst, norm, aft in results:
+        assert err != "error", worst
+        assert err < 1e-4, (rank, err)
+        assert worst[0] < 2e-3, (rank, worst)
+        assert abs(norm - ref_norm) < 1e-3 * max(1.0, ref_norm), (norm, ref_norm)
+        assert aft[0] < 1e-4, aft

@@ -161,8 +161,9 @@ class Attention(nn.Module):
     # -- pieces shared with the TTT block ------------------------------------------------
     def project_qkv(self, hidden_states, seqlen_offset=0, max_seqlen=None, positions=None):
         """q/k/v projections, per-head norm and rotary.  Returns q[B,T,H,D], k, v[B,T,HK,D]."""
-        B, T, _ = hidden_states.shape
+        B = hidden_states.shape[0]
         q, k, v = _fused_qkv(self, hidden_states)
+        T = q.shape[1]                      # all tokens: under tensor parallelism the input is a token shard
         q = q.view(B, T, self.num_heads, self.head_dim)
         k = k.view(B, T, self.num_kv_heads, self.head_dim)
         v = v.view(B, T, self.num_kv_heads, self.head_dim)
@@ -191,6 +192,10 @@ class Attention(nn.Module):
             o = self.g_norm(o).reshape(B, T, -1) * self.gate_fn(g)
         else:
             o = o.reshape(B, T, -1)
+        tp = _tp_state()
+        if tp is not None:
+            from ..parallel.tensor import row_parallel_linear
+            return row_parallel_linear(o.reshape(B * T, -1), self.o_proj.weight, tp).view(B, T // tp.world, -1)
         return ops.linear(o, self.o_proj.weight)
 
     # -- standard forward ---------------------------------------------------------------------
@@ -229,6 +234,13 @@ def _cp_state():
     import sys
     mod = sys.modules.get("ttcd_b200.parallel.context")
     return mod.active() if mod is not None else None
+
+
+def _tp_state():
+    """The active tensor-parallel state, if any (token-sharded residual stream, head/row-sharded weights)."""
+    import sys
+    mod = sys.modules.get("ttcd_b200.parallel.tensor")
+    return mod.current() if mod is not None else None
 
 
 def positions_from_cu_seqlens(cu_seqlens: torch.Tensor, total: int, device) -> torch.Tensor:
@@ -281,6 +293,12 @@ def _slab_view(params: list[torch.Tensor]) -> torch.Tensor | None:
 def _fused_qkv(attn: Attention, x):
     """One GEMM for q, k and v when their weights are laid out contiguously, else three."""
     ws = [attn.q_proj.weight, attn.k_proj.weight, attn.v_proj.weight]
+    tp = _tp_state()
+    if tp is not None:
+        from ..parallel.tensor import column_parallel_multi
+        if x.shape[0] != 1:
+            raise NotImplementedError("tensor parallelism shards the tokens of ONE sequence per step (batch 1)")
+        return tuple(y.unsqueeze(0) for y in column_parallel_multi(x[0], ws, _slab_view(ws), tp))
     if attn.q_proj.bias is None and x.is_cuda:
         out = ops_fused_linear(x, ws)
         if out is not None:
@@ -312,10 +330,23 @@ class GatedMLP(nn.Module):
 
     def features(self, x):
         """swiglu(gate(x), up(x)) with the two projections fused into one GEMM when possible."""
+        tp = _tp_state()
+        if tp is not None:
+            from ..parallel.tensor import column_parallel_multi
+            ws = [self.gate_proj.weight, self.up_proj.weight]
+            flat = x.reshape(-1, x.shape[-1])
+            g, u = column_parallel_multi(flat, ws, _slab_view(ws), tp)
+            return ops.swiglu(g, u).view(*x.shape[:-2], x.shape[-2] * tp.world, -1)
         out = ops_fused_linear(x, [self.gate_proj.weight, self.up_proj.weight]) if x.is_cuda else None
         if out is not None:
             return ops.swiglu(out[0], out[1])
         return ops.swiglu(ops.linear(x, self.gate_proj.weight), ops.linear(x, self.up_proj.weight))
 
     def forward(self, x, **_):
+        tp = _tp_state()
+        if tp is not None:
+            from ..parallel.tensor import row_parallel_linear
+            feats = self.features(x)
+            y = row_parallel_linear(feats.reshape(-1, feats.shape[-1]), self.down_proj.weight, tp)
+            return y.view(*x.shape[:-1], -1)
         return ops.linear(self.features(x), self.down_proj.weight)

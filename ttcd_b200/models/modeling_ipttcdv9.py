@@ -30,7 +30,7 @@ from torch.profiler import record_function
 from .. import ops
 from .base import DecoderForCausalLM, DecoderModel
 from .configuration import IPTTCDv9Config
-from .layers import GatedMLP, RMSNorm, WindowKVCache, _cp_state
+from .layers import GatedMLP, RMSNorm, WindowKVCache, _cp_state, _tp_state
 from .modeling_ipttt import make_depthwise_conv, pad_to_chunks
 from .modeling_transformer import build_attention
 
@@ -94,11 +94,21 @@ class IPTTCDMLP(GatedMLP):
         if t is None or not self.is_ttt_layer:
             return super().forward(x)
         tag = f"ipttcdv9_scanfuse.mlp.{{}}.layer{self.layer_idx}"
+        tp = _tp_state()
         b, seq_len, _ = x.shape
-        with record_function(tag.format("teacher_gateup")):
-            # teacher and student rows share the gate/up weights: one GEMM over 2x rows
-            feats = self.features(torch.cat([x, t], dim=0))
-        z, z_hat = feats[:b], feats[b:]
+        if tp is not None:
+            # token-sharded inputs: each stream is all-gathered inside its own gate/up GEMM
+            if self.ttt_normalize_student_features or self.ttt_norm_proj_diff or self.ttt_weight_renorm or self.use_muon:
+                raise NotImplementedError("tensor parallelism: feature normalisation / renorm over the sharded d_i")
+            z, z_hat = self.features(x), self.features(t)
+            seq_len = z.shape[1]
+            if seq_len % self.ttt_chunk:
+                raise ValueError("tensor parallelism needs the sequence length to be a multiple of ttt_chunk")
+        else:
+            with record_function(tag.format("teacher_gateup")):
+                # teacher and student rows share the gate/up weights: one GEMM over 2x rows
+                feats = self.features(torch.cat([x, t], dim=0))
+            z, z_hat = feats[:b], feats[b:]
         with record_function(tag.format("teacher_ttt_prepare")):
             z_p = pad_to_chunks(z, self.ttt_chunk)
             z_tgt = self._conv(z_p, self.ttt_teacher_conv)
@@ -110,7 +120,12 @@ class IPTTCDMLP(GatedMLP):
         beta = None
         if self.dynamic_lr:
             with record_function(tag.format("student_beta")):
-                beta = torch.sigmoid(pad_to_chunks(t, self.ttt_chunk) @ self.b_proj.to(t.dtype)).unsqueeze(-1)
+                if tp is not None:
+                    from ..parallel.tensor import gather_rows
+                    gate = gather_rows(torch.sigmoid(t[0] @ self.b_proj.to(t.dtype)), tp)        # [S]
+                    beta = gate.view(1, T, C, 1)
+                else:
+                    beta = torch.sigmoid(pad_to_chunks(t, self.ttt_chunk) @ self.b_proj.to(t.dtype)).unsqueeze(-1)
 
         compute_dtype = z_p.dtype
         w_down = self.down_proj.weight
@@ -128,10 +143,15 @@ class IPTTCDMLP(GatedMLP):
                     z_out, z_tgt, z_hat_p, beta, w_down, w_update_t, lr=self.ttt_lr,
                     update_every=min(T, self.ttt_update_every), state_dtype=self._state_dtype(compute_dtype),
                     normalize_student=self.ttt_normalize_student_features, norm_proj_diff=self.ttt_norm_proj_diff,
-                    post_proj=post, return_last_dw_norm=True, cp=_cp_state() if self.training else None)
+                    post_proj=post, return_last_dw_norm=True, cp=_cp_state() if self.training else None,
+                    proj_reduce=None if tp is None else (lambda v: _tp_sum(v, tp)))
             if self.training and last is not None:
                 self._last_delta_w_norm_t = last  # device scalar; read lazily, no host sync here
-        return y.reshape(b, T * C, -1)[:, :seq_len]
+        y = y.reshape(b, T * C, -1)[:, :seq_len]
+        if tp is not None:
+            from ..parallel.tensor import scatter_rows_sum
+            return scatter_rows_sum(y[0], tp).unsqueeze(0)       # partial sums over d_i shards -> token shard
+        return y
 
     @property
     def _last_delta_w_norm(self):
@@ -189,6 +209,11 @@ class IPTTCDMLP(GatedMLP):
         return torch.cat(outs, dim=1)
 
 
+def _tp_sum(v, tp):
+    from ..parallel.tensor import sum_over_group
+    return sum_over_group(v, tp)
+
+
 def _fast_prefill_ok(block, hidden_states, attention_mask, kwargs) -> bool:
     if os.environ.get("IPTTCD_DISABLE_FAST_PREFILL") == "1":
         return False
@@ -238,6 +263,8 @@ class IPTTCDBlock(nn.Module):
             o_t, o_s = _context.dual_window_attention(q, k, v, attn.window_size, self.student_window, None, attn.layer_idx)
         else:
             o_t, o_s = ops.dual_window_attention(q, k, v, attn.window_size, self.student_window, cu_seqlens=cu)
+        if _tp_state() is not None:     # row-parallel o_proj reduce-scatters over tokens: one stream per call
+            return attn.finish(o_t, hidden_states), attn.finish(o_s, hidden_states)
         b = hidden_states.shape[0]
         both = attn.finish(torch.cat([o_t, o_s], dim=0), torch.cat([hidden_states, hidden_states], dim=0)
                            if attn.use_output_gate else hidden_states)

@@ -151,11 +151,12 @@ def lse_merge(o_a, lse_a, o_b, lse_b):
 # -- fast-weight scan ----------------------------------------------------------------------
 
 def ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, *, lr, update_every, state_dtype=None,
-             normalize_student=False, norm_proj_diff=False, post_proj=None, return_last_dw_norm=False, cp=None):
+             normalize_student=False, norm_proj_diff=False, post_proj=None, return_last_dw_norm=False, cp=None,
+             proj_reduce=None):
     plain = not normalize_student and not norm_proj_diff and post_proj is None
     if _native.use_native(z_out) and plain and (state_dtype in (None, torch.bfloat16, torch.float32)):
         T, C = z_out.shape[1], z_out.shape[2]
-        fused_ok = ((cp is None or cp.size == 1) and C >= 128 and z_out.shape[3] >= 128
+        fused_ok = ((cp is None or cp.size == 1) and proj_reduce is None and C >= 128 and z_out.shape[3] >= 128
                     and w_down.shape[0] >= 128 and z_out.shape[3] % 8 == 0 and w_down.shape[0] % 8 == 0)
         if fused_ok:
             # grouping by update_every only bounds the reference's memory; the prefix over chunks is the same sum:
@@ -164,11 +165,11 @@ def ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, *, lr, update_every,
             return (y, last) if return_last_dw_norm else y
         return reference.ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, lr=lr,
                                   update_every=update_every, state_dtype=torch.float32,
-                                  return_last_dw_norm=return_last_dw_norm, matmul=_cuda().matmul, cp=cp)
+                                  return_last_dw_norm=return_last_dw_norm, matmul=_cuda().matmul, cp=cp, proj_reduce=proj_reduce)
     return reference.ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, lr=lr,
                               update_every=update_every, state_dtype=state_dtype,
                               normalize_student=normalize_student, norm_proj_diff=norm_proj_diff,
-                              post_proj=post_proj, return_last_dw_norm=return_last_dw_norm, cp=cp)
+                              post_proj=post_proj, return_last_dw_norm=return_last_dw_norm, cp=cp, proj_reduce=proj_reduce)
 
 
 # -- losses ------------------------------------------------------------------------------------

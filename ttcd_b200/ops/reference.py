@@ -239,7 +239,7 @@ def dwconv_sequence(x, weight, bias=None, activation: str | None = None, residua
 def ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, *, lr: float, update_every: int,
              state_dtype: torch.dtype | None = None, normalize_student: bool = False,
              norm_proj_diff: bool = False, post_proj: torch.Tensor | None = None,
-             return_last_dw_norm: bool = False, matmul=torch.matmul, cp=None):
+             return_last_dw_norm: bool = False, matmul=torch.matmul, cp=None, proj_reduce=None):
     """Grouped fast-weight scan.
 
     ``matmul`` is the batched-matmul primitive (torch.matmul, or the tensor-core
@@ -255,6 +255,9 @@ def ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, *, lr: float, update
         W_i  = w_down + lr * sum_{j<i} dW_j          (prefix kept in state_dtype, grouped)
         Y_i  = z_out_i @ W_i^T
 
+    ``proj_reduce``: applied to the projected difference before beta (tensor parallelism shards d_i, so each
+    rank holds a partial sum there; the caller passes an all-reduce that also all-reduces in backward).
+
     ``cp`` (context-parallel state with ``rank``/``size``): the T chunks are this rank's slice of a
     longer sequence; the scan then starts from ``w_down + lr * sum`` of every earlier rank's updates
     (exclusive prefix over ranks) and this rank's last chunk also produces an update for its successors.
@@ -269,6 +272,8 @@ def ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, *, lr: float, update
     def delta_w(lo: int, hi: int):
         diff = z_tgt[:, lo:hi] - z_hat[:, lo:hi]
         proj = matmul(diff, w_update_t.to(compute_dtype))
+        if proj_reduce is not None:       # tensor parallel: d_i is sharded, the projection is a partial sum
+            proj = proj_reduce(proj)
         if norm_proj_diff:
             proj = F.normalize(proj, p=2, dim=-1, eps=1e-6)
         zh = z_hat[:, lo:hi]

@@ -85,6 +85,7 @@ class ShardedDataParallel:
             _native.load(required=not _native.torch_fallback_allowed())
         self.peer = self.world > 1 and self.use_native and self.comm == "peer"
         self.muon_enabled, self.muon_momentum, self.muon_filter = muon, muon_momentum, muon_filter
+        self.norm_sq_hook = None
         self.muon_params: list = []
         self.sym_params = self.sym_grads = self.barrier = None
         self.groups: list[ParamGroup] = []
@@ -315,6 +316,8 @@ class ShardedDataParallel:
                 self._norm_sq += mp.grad32.pow(2).sum()
         if self.world > 1:
             dist.all_reduce(self._norm_sq, group=self.pg)
+        if self.norm_sq_hook is not None:      # e.g. tensor parallelism: add the other ranks' weight shards
+            self.norm_sq_hook(self._norm_sq)
         norm = self._norm_sq.sqrt()
         self.last_grad_norm = norm
         if self.max_norm is not None:

@@ -196,3 +196,214 @@ def column_parallel_linear(x_shard: torch.Tensor, weight: torch.Tensor, tp: Tens
 
 def row_parallel_linear(x: torch.Tensor, weight: torch.Tensor, tp: TensorParallel | None = None) -> torch.Tensor:
     return _RowParallel.apply(x, weight, tp or _CTX)
+
+
+# ----------------------------------------------------------------------------------------- model wiring
+class _ColumnParallelSlab(torch.autograd.Function):
+    """Several column-parallel projections of the same token-sharded input through ONE all-gather -> GEMM:
+    the weights are adjacent rows of one slab (the flat parameter buffer lays q/k/v and gate/up back to
+    back); outputs are column slices of the product."""
+
+    @staticmethod
+    def forward(ctx, x_shard, tp, slab, *weights):
+        w_all = slab if slab is not None else torch.cat([w.detach() for w in weights], dim=0)
+        y, full = tp.ag_gemm(x_shard, w_all)
+        ctx.save_for_backward(full.clone() if tp.fused else full, w_all)
+        ctx.tp, ctx.sizes = tp, [w.shape[0] for w in weights]
+        return tuple(y.split(ctx.sizes, dim=1))
+
+    @staticmethod
+    def backward(ctx, *dys):
+        from .. import ops
+        full, w_all = ctx.saved_tensors
+        dy = torch.cat([d.to(w_all.dtype) for d in dys], dim=1)
+        dx_shard = ctx.tp.gemm_rs(dy, w_all, w_is_kn=True)
+        dw = ops.matmul(dy.t(), full)
+        return (dx_shard, None, None) + tuple(dw.split(ctx.sizes, dim=0))
+
+
+class _SumOverGroup(torch.autograd.Function):
+    """Sum of per-rank partial results whose consumers are again rank-local shards: all-reduce in forward
+    (leaving one parallel region) and in backward (entering the next)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        y = x.contiguous().clone()
+        dist.all_reduce(y, group=group)
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous().clone()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
+class _GatherRows(torch.autograd.Function):
+    """all_gather along dim 0 (backward: reduce-scatter)."""
+
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        out = torch.empty(x.shape[0] * tp.world, *x.shape[1:], dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, x.contiguous(), group=tp.group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        tp = ctx.tp
+        g = g.contiguous()
+        n = g.shape[0] // tp.world
+        if g.device.type == "cpu":
+            g = g.clone()
+            dist.all_reduce(g, group=tp.group)
+            return g[tp.rank * n:(tp.rank + 1) * n], None
+        out = torch.empty(n, *g.shape[1:], dtype=g.dtype, device=g.device)
+        dist.reduce_scatter_tensor(out, g, group=tp.group)
+        return out, None
+
+
+class _ScatterRowsSum(torch.autograd.Function):
+    """reduce-scatter along dim 0 of per-rank partial sums (backward: all-gather)."""
+
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        n = x.shape[0] // tp.world
+        if x.device.type == "cpu":
+            y = x.contiguous().clone()
+            dist.all_reduce(y, group=tp.group)
+            return y[tp.rank * n:(tp.rank + 1) * n].clone()
+        out = torch.empty(n, *x.shape[1:], dtype=x.dtype, device=x.device)
+        dist.reduce_scatter_tensor(out, x.contiguous(), group=tp.group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        tp = ctx.tp
+        out = torch.empty(g.shape[0] * tp.world, *g.shape[1:], dtype=g.dtype, device=g.device)
+        dist.all_gather_into_tensor(out, g.contiguous(), group=tp.group)
+        return out, None
+
+
+def column_parallel_multi(x_shard, weights, slab=None, tp: TensorParallel | None = None):
+    return _ColumnParallelSlab.apply(x_shard, tp or _CTX, slab, *weights)
+
+
+def sum_over_group(x, tp: TensorParallel | None = None):
+    tp = tp or _CTX
+    return _SumOverGroup.apply(x, tp.group)
+
+
+def gather_rows(x, tp: TensorParallel | None = None):
+    return _GatherRows.apply(x, tp or _CTX)
+
+
+def scatter_rows_sum(x, tp: TensorParallel | None = None):
+    return _ScatterRowsSum.apply(x, tp or _CTX)
+
+
+def _slice_param(module, name: str, dim: int, rank: int, world: int, block: int = 1) -> None:
+    """Replace ``module.<name>`` by this rank's 1/world slice along ``dim`` (in units of ``block``)."""
+    p = getattr(module, name)
+    units = p.shape[dim] // block
+    if units % world:
+        raise ValueError(f"{name}: {units} units of {block} along dim {dim} do not divide by tp={world}")
+    per = units // world * block
+    new = torch.nn.Parameter(p.detach().narrow(dim, rank * per, per).clone(), requires_grad=p.requires_grad)
+    new._tp_shard = (dim, world)
+    setattr(module, name, new)
+
+
+def shard_model(model, tp: TensorParallel) -> None:
+    """Megatron-style sharding of every block in place: q/k/v by heads and gate/up by rows (column
+    parallel), o_proj/down_proj by columns (row parallel), depthwise conv channels with the intermediate
+    dimension.  Norm weights, ``ttt_proj``, ``b_proj``, embeddings and the LM head stay replicated."""
+    r, w = tp.rank, tp.world
+    for layer in model.model.layers:
+        attn = layer.attn
+        if attn.num_heads % w or attn.num_kv_heads % w:
+            raise ValueError(f"heads ({attn.num_heads}, kv {attn.num_kv_heads}) do not divide by tp={w}")
+        if attn.use_output_gate or attn.q_proj.bias is not None:
+            raise NotImplementedError("tensor parallelism: output gate / qkv bias are not supported")
+        D = attn.head_dim
+        _slice_param(attn.q_proj, "weight", 0, r, w, D)
+        _slice_param(attn.k_proj, "weight", 0, r, w, D)
+        _slice_param(attn.v_proj, "weight", 0, r, w, D)
+        _slice_param(attn.o_proj, "weight", 1, r, w, D)
+        attn.num_heads //= w
+        attn.num_kv_heads //= w
+        attn.q_dim, attn.kv_dim = attn.num_heads * D, attn.num_kv_heads * D
+        mlp = layer.mlp
+        _slice_param(mlp.gate_proj, "weight", 0, r, w)
+        _slice_param(mlp.up_proj, "weight", 0, r, w)
+        _slice_param(mlp.down_proj, "weight", 1, r, w)
+        mlp.intermediate_size //= w
+        for name in ("ttt_teacher_conv", "ttt_student_conv", "ttt_activation_conv"):
+            conv = getattr(mlp, name, None)
+            if conv is not None:
+                _slice_param(conv, "weight", 0, r, w)
+    model._tp = tp
+
+
+def replicated_parameters(model):
+    return [p for p in model.parameters() if not hasattr(p, "_tp_shard")]
+
+
+def all_reduce_replicated_grads(model, tp: TensorParallel) -> None:
+    """Replicated parameters see only this rank's token shard (or heads): sum their gradients over the group."""
+    for p in replicated_parameters(model):
+        if p.grad is not None:
+            dist.all_reduce(p.grad, group=tp.group)
+
+
+def gather_full_state_dict(model, tp: TensorParallel) -> dict:
+    """State dict with every sharded tensor all-gathered back to its full shape (for checkpoints)."""
+    out = {}
+    for name, p in model.state_dict().items():
+        src = dict(model.named_parameters()).get(name)
+        shard = getattr(src, "_tp_shard", None) if src is not None else None
+        if shard is None:
+            out[name] = p.detach()
+            continue
+        dim = shard[0]
+        parts = [torch.empty_like(p) for _ in range(tp.world)]
+        dist.all_gather(parts, p.detach().contiguous(), group=tp.group)
+        out[name] = torch.cat(parts, dim=dim)
+    return out
+
+
+def load_full_state_dict(model, full: dict, tp: TensorParallel) -> None:
+    """Inverse of ``gather_full_state_dict``: every rank keeps its slice of the sharded tensors."""
+    params = dict(model.named_parameters())
+    with torch.no_grad():
+        for name, value in full.items():
+            p = params.get(name)
+            if p is None:
+                continue
+            shard = getattr(p, "_tp_shard", None)
+            if shard is not None:
+                per = value.shape[shard[0]] // tp.world
+                value = value.narrow(shard[0], tp.rank * per, per)
+            p.copy_(value.to(p.dtype))
+
+
+def configure(engine, degree: int) -> None:
+    """Called by the engine: build the tensor-parallel group of ``degree`` consecutive ranks, shard the
+    model and switch its layers to the parallel paths."""
+    world, rank = dist.get_world_size(), dist.get_rank()
+    if world % degree:
+        raise ValueError("world size must be a multiple of the tensor-parallel degree")
+    group = None
+    for start in range(0, world, degree):
+        ranks = list(range(start, start + degree))
+        g = dist.new_group(ranks)
+        if rank in ranks:
+            group = g
+    cfg = engine.model_config
+    feat = max(getattr(cfg, "resolved_intermediate_size", cfg.hidden_size), cfg.hidden_size)
+    rows = max(128, int(getattr(engine.cfg, "tp_max_tokens", 65536)) // degree)
+    tp = TensorParallel(group, engine.device, max_rows_per_rank=rows, max_features=max(feat, 1024))
+    shard_model(engine.model, tp)
+    engine.tp = tp

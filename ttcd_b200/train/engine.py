@@ -88,13 +88,22 @@ class TrainEngine:
         if self.cfg.tensor_parallel > 1 or self.cfg.context_parallel > 1:
             from ..parallel import context as _ctx
             _ctx.configure(self, tensor_parallel=self.cfg.tensor_parallel, context_parallel=self.cfg.context_parallel)
-        multi = dist.is_initialized() and dist.get_world_size(process_group) > 1
+        self.tp = getattr(self, "tp", None)
+        if self.tp is not None:
+            if self.tp.world != dist.get_world_size():
+                raise NotImplementedError("tensor parallelism combined with data parallelism is not supported yet")
+            if self.cfg.enable_muon:
+                raise NotImplementedError("Muon needs whole matrices; it is not available with tensor parallelism")
+            process_group = False           # every rank optimises its own weight shards
+        multi = process_group is not False and dist.is_initialized() and dist.get_world_size(process_group) > 1
         self.sdp = ShardedDataParallel(
             self.model, blocks=list(self.model.model.layers), process_group=process_group if multi else False,
             lr=self.cfg.lr, betas=self.cfg.betas, eps=self.cfg.eps, weight_decay=self.cfg.weight_decay,
             max_norm=self.cfg.max_norm, param_dtype=self.cfg.dtype, muon=self.cfg.enable_muon,
             muon_momentum=self.cfg.muon_momentum)
         self.sdp.skip_nan_inf = self.cfg.skip_nan_inf
+        if self.tp is not None:
+            self.sdp.norm_sq_hook = self._tp_norm_sq
         self.world = self.sdp.world
         self._dev_ids = None
         self.last_loss: torch.Tensor | None = None
@@ -122,6 +131,8 @@ class TrainEngine:
         cp = getattr(self, "cp", None)
         if cp is not None:
             return self._forward_backward_cp(ids, lab, scale, cp, **model_kwargs)
+        if self.tp is not None:
+            return self._forward_backward_tp(ids, lab, scale, **model_kwargs)
         from .activation_offload import get_act_offloading_ctx_manager
         with get_act_offloading_ctx_manager(self.cfg.activation_offload and self.device.type == "cuda"):
             out = self.model(input_ids=ids, labels=lab, **model_kwargs)
@@ -151,6 +162,44 @@ class TrainEngine:
         dist.all_reduce(global_loss, group=cp.group)
         self.tokens_seen += ids.numel() // cp.size
         return global_loss / n_total.clamp_min(1.0)
+
+    def _forward_backward_tp(self, ids, lab, scale, **model_kwargs):
+        """Tensor + sequence parallel step: every rank receives the same sequence, embeds and scores its own
+        token shard (labels shifted globally first); the blocks gather / scatter tokens inside their fused
+        GEMM+collective kernels.  Each rank back-propagates its share ``n_local / n_total`` of the mean loss;
+        gradients of replicated parameters are then summed over the group."""
+        from ..parallel.tensor import all_reduce_replicated_grads
+        tp = self.tp
+        B, S = ids.shape
+        if B != 1 or S % tp.world:
+            raise ValueError("tensor parallelism takes one sequence per step, length divisible by the degree")
+        s_l = S // tp.world
+        shifted = torch.cat((lab[:, 1:], torch.full_like(lab[:, :1], -100)), dim=1)
+        lo = tp.rank * s_l
+        ids_l, lab_l = ids[:, lo:lo + s_l].contiguous(), shifted[:, lo:lo + s_l].contiguous()
+        out = self.model(input_ids=ids_l, labels=lab_l, shift_labels=False, **model_kwargs)
+        n_local = lab_l.ne(-100).sum().float()
+        n_total = n_local.clone()
+        dist.all_reduce(n_total, group=tp.group)
+        share = n_local / n_total.clamp_min(1.0)
+        (out.loss * (share * scale)).backward()
+        all_reduce_replicated_grads(self.model, tp)
+        global_loss = out.loss.detach() * share
+        dist.all_reduce(global_loss, group=tp.group)
+        self.tokens_seen += ids.numel()
+        return global_loss
+
+    def _tp_norm_sq(self, norm_sq: torch.Tensor) -> None:
+        """Global gradient norm under tensor parallelism: sharded weights contribute from every rank,
+        replicated ones (identical after their all-reduce) once."""
+        from ..parallel.tensor import replicated_parameters
+        rep = torch.zeros_like(norm_sq)
+        for p in replicated_parameters(self.model):
+            if p.grad is not None:
+                rep += p.grad.float().pow(2).sum()
+        sharded = norm_sq - rep
+        dist.all_reduce(sharded, group=self.tp.group)
+        norm_sq.copy_(sharded + rep)
 
     def train_step(self, input_ids: torch.Tensor, labels: torch.Tensor | None = None, lr: float | None = None,
                    return_loss_on_host: bool = True, **model_kwargs):
