@@ -389,6 +389,50 @@ def load_full_state_dict(model, full: dict, tp: TensorParallel) -> None:
             p.copy_(value.to(p.dtype))
 
 
+def _shard_spec(model, key: str):
+    """``(dim, world)`` of the sharded parameter a state key belongs to (``name`` or ``name.<state>``)."""
+    params = dict(model.named_parameters())
+    p = params.get(key)
+    if p is None and "." in key:
+        p = params.get(key.rsplit(".", 1)[0])
+    return getattr(p, "_tp_shard", None) if p is not None else None
+
+
+def gather_named(model, tp: TensorParallel, tensors: dict) -> dict:
+    """All-gather every entry that belongs to a sharded parameter (weights or per-parameter optimizer state)."""
+    out = {}
+    for key, t in tensors.items():
+        spec = _shard_spec(model, key) if isinstance(t, torch.Tensor) and t.dim() > 0 else None
+        if spec is None:
+            out[key] = t
+            continue
+        parts = [torch.empty_like(t) for _ in range(tp.world)]
+        dist.all_gather(parts, t.contiguous(), group=tp.group)
+        out[key] = torch.cat(parts, dim=spec[0])
+    return out
+
+
+def slice_named(model, tp: TensorParallel, tensors: dict) -> dict:
+    """Inverse of ``gather_named``: keep this rank's slice of every entry of a sharded parameter."""
+    out = {}
+    for key, t in tensors.items():
+        spec = _shard_spec(model, key) if isinstance(t, torch.Tensor) and t.dim() > 0 else None
+        if spec is None:
+            out[key] = t
+        else:
+            per = t.shape[spec[0]] // tp.world
+            out[key] = t.narrow(spec[0], tp.rank * per, per).contiguous()
+    return out
+
+
+def full_shape(p: torch.Tensor) -> tuple:
+    spec = getattr(p, "_tp_shard", None)
+    shape = list(p.shape)
+    if spec is not None:
+        shape[spec[0]] *= spec[1]
+    return tuple(shape)
+
+
 def configure(engine, degree: int) -> None:
     """Called by the engine: build the tensor-parallel group of ``degree`` consecutive ranks, shard the
     model and switch its layers to the parallel paths."""

@@ -87,10 +87,16 @@ def load_model_weights(model: torch.nn.Module, path: str, exclude: list[str] | N
     exclude = exclude or []
     wanted, missing = {}, []
     seen_ptr: dict[int, str] = {}
+    tp = getattr(model, "_tp", None)          # tensor parallel: checkpoints hold full tensors, ranks keep slices
+    params = dict(model.named_parameters()) if tp is not None else {}
     for name, tensor in own.items():
         if any(name.startswith(e) for e in exclude):
             continue
         if prefix + name in keys:
+            if tp is not None and name in params:
+                from ..parallel.tensor import full_shape
+                wanted[prefix + name] = torch.empty(full_shape(params[name]), dtype=tensor.dtype, device="cpu")
+                continue
             wanted[prefix + name] = torch.empty_like(tensor, device="cpu")
         else:
             missing.append(name)
@@ -102,6 +108,9 @@ def load_model_weights(model: torch.nn.Module, path: str, exclude: list[str] | N
             if ptr in seen_ptr:          # tied tensors: the first name wins
                 continue
             seen_ptr[ptr] = name
+            if tp is not None:
+                from ..parallel.tensor import slice_named
+                value = slice_named(model, tp, {name: value})[name]
             own[name].copy_(value.to(own[name].dtype))
     tied_ok = {"lm_head.weight", "model.embeddings.weight"}
     hard_missing = [m for m in missing if m not in tied_ok and "rotary" not in m]
@@ -158,6 +167,10 @@ class CheckpointManager:
             src = full.get(p.data_ptr())
             t = src if src is not None else p.detach().float()
             out[name] = t.to(dtype) if dtype is not None else t
+        tp = getattr(self.engine, "tp", None)
+        if tp is not None:
+            from ..parallel.tensor import gather_named
+            out = gather_named(self.engine.model, tp, out)
         return out
 
     def _states(self, model_only: bool, dtype=None) -> dict[str, Any]:
@@ -165,6 +178,9 @@ class CheckpointManager:
             return self._model_state(dtype)          # raw keys: loadable as a seed / by converters
         sd: dict[str, Any] = {"model": self._model_state(None)}
         sd["optimizer"] = self.engine.sdp.full_optimizer_state()
+        if getattr(self.engine, "tp", None) is not None:
+            from ..parallel.tensor import gather_named
+            sd["optimizer"] = gather_named(self.engine.model, self.engine.tp, sd["optimizer"])
         sd["train_state"] = self.train_state.state_dict()
         if self.lr_state is not None:
             sd["lr_scheduler"] = {"last_step": torch.tensor(int(self.lr_state()), dtype=torch.int64)}
@@ -252,7 +268,18 @@ class CheckpointManager:
     def _load_training_state(self, path: str, keys: set[str]):
         no_dist = self.world == 1
         opt_template = {"optimizer": self.engine.sdp.full_optimizer_state(template=True)}
+        tp = getattr(self.engine, "tp", None)
+        if tp is not None:      # saved states of sharded weights have the full shape
+            from ..parallel.tensor import _shard_spec, slice_named
+            for key, t in list(opt_template["optimizer"].items()):
+                spec = _shard_spec(self.engine.model, key) if isinstance(t, torch.Tensor) and t.dim() > 0 else None
+                if spec is not None:
+                    shape = list(t.shape)
+                    shape[spec[0]] *= spec[1]
+                    opt_template["optimizer"][key] = torch.empty(shape, dtype=t.dtype, device=t.device)
         dcp.load(opt_template, checkpoint_id=path, no_dist=no_dist)
+        if tp is not None:
+            opt_template["optimizer"] = slice_named(self.engine.model, tp, opt_template["optimizer"])
         self.engine.sdp.load_full_optimizer_state(opt_template["optimizer"])
         ts = {"train_state": self.train_state.state_dict()}
         dcp.load(ts, checkpoint_id=path, no_dist=no_dist)
