@@ -42,6 +42,12 @@ struct GcPeers {
   void* p[GC_MAX_RANKS];
 };
 
+// Tensor maps over the peers' partial buffers, entry d-1 for the peer (rank + d) % world.
+struct alignas(64) GcPeerMaps {
+  CUtensorMap m[GC_MAX_RANKS - 1];
+};
+constexpr int GC_RS_STAGING = 2 * 64 * GC_BN * 2;   // two 64-row half tiles of bf16
+
 struct GcParams {
   int rank, world, epoch;
   int mbps;            // 128-row blocks per rank shard
@@ -360,9 +366,10 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tma_own, const __grid_constan
 template <bool B_MN>
 __global__ void __launch_bounds__(GC_THREADS, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-               const GcPeers peer_partial, const GcPeers peer_flags, bf16* __restrict__ out, const GcParams p) {
+               const __grid_constant__ GcPeerMaps peer_maps, const GcPeers peer_flags, bf16* __restrict__ out,
+               const GcParams p) {
   extern __shared__ uint8_t smem_raw[];
-  const GcSmem s = gc_setup<0>(smem_raw);
+  const GcSmem s = gc_setup<GC_RS_STAGING>(smem_raw);
   const uint32_t tmem_base = *s.tmem_slot;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t total_tiles = static_cast<int64_t>(p.world) * p.mbps * p.tiles_n;
@@ -446,62 +453,86 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     }
   } else if (p.world > 1) {
     // ------------------------------------------------------------------ reducers (warps 6..9, 128 threads)
+    // Peers' partial tiles are staged in shared memory by plain (never multicast) TMA loads from the peer's
+    // symmetric buffer, two 64-row half tiles (32 KB each) in flight per CTA, then summed into the local fp32
+    // buffer.  Work items: (tile of this rank's rows) x (peer) x (half).  All 128 threads run the same number
+    // of iterations and barriers; after an expired wait they only skip the work.
     const int rt = threadIdx.x - 6 * 32;
+    const uint32_t stage_base = s.base_u32 + GC_RING_BYTES;
+    const uint8_t* stage_ptr = s.base + GC_RING_BYTES;
+    constexpr uint32_t HALF_BYTES = 64 * GC_BN * 2;          // 32 KB: four 64x64 swizzled boxes
     const int64_t units = static_cast<int64_t>(p.mbps) * p.tiles_n;
-    for (int64_t u = blockIdx.x; u < units; u += gridDim.x) {
+    const int my_units = static_cast<int>(units > blockIdx.x ? (units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0);
+    const int ipu = 2 * (p.world - 1);
+    const int total = my_units * ipu;
+    bool dead = false;
+    auto issue = [&](int i) {     // thread rt == 0 only
+      const int64_t u = blockIdx.x + static_cast<int64_t>(i / ipu) * gridDim.x;
       const int mb = static_cast<int>(u / p.tiles_n), nt = static_cast<int>(u % p.tiles_n);
-      if (rt == 0) {
+      const int d = 1 + (i % ipu) / 2, h = i & 1;
+      const int peer = (p.rank + d) % p.world;
+      if (h == 0) {
         const int fidx = (p.rank * p.mbps + mb) * p.tiles_n + nt;
-        for (int d = 1; d < p.world; ++d) {
-          const int peer = (p.rank + d) % p.world;
-          if (!gc_wait_flag<true>(static_cast<const int*>(peer_flags.p[peer]) + fidx, p.epoch, p.wait_ns, s.abort_flag,
-                                  640 + peer))
-            break;
-        }
+        if (!gc_wait_flag<true>(static_cast<const int*>(peer_flags.p[peer]) + fidx, p.epoch, p.wait_ns, s.abort_flag,
+                                640 + peer))
+          return false;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (*s.abort_flag) break;
-      const int64_t grow0 = static_cast<int64_t>(p.rank) * p.m_shard + static_cast<int64_t>(mb) * GC_BM;
-      const int64_t col0 = static_cast<int64_t>(nt) * GC_BN;
-      // 128 rows x 32 vectors of 8 bf16; four vectors per thread in flight per peer
-#pragma unroll 1
-      for (int i = 0; i < 32; i += 4) {
-        float acc[4][8];
+      const uint32_t slot = i & 1;
+      const uint32_t dst = stage_base + slot * HALF_BYTES;
+      const int row = static_cast<int>(static_cast<int64_t>(p.rank) * p.m_shard + static_cast<int64_t>(mb) * GC_BM + 64 * h);
+      mbar_expect_tx(s.copy(slot), HALF_BYTES);
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
-#pragma unroll
-          for (int e = 0; e < 8; ++e) acc[q][e] = 0.f;
-        for (int d = 1; d < p.world; ++d) {
-          const int peer = (p.rank + d) % p.world;
-          const bf16* base = static_cast<const bf16*>(peer_partial.p[peer]);
-          uint4 raw[4];
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int v = rt + 128 * (i + q);
-            raw[q] = *reinterpret_cast<const uint4*>(base + (grow0 + (v >> 5)) * p.N + col0 + (v & 31) * 8);
-          }
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const uint32_t w[4] = {raw[q].x, raw[q].y, raw[q].z, raw[q].w};
+      for (int j = 0; j < GC_BN / 64; ++j)
+        tma_load_3d(dst + j * 8192, &peer_maps.m[d - 1], s.copy(slot), nt * GC_BN + 64 * j, row, 0);
+      return true;
+    };
+    int issued = 0;
+    if (rt == 0 && total > 0) { if (issue(0)) issued = 1; }
+    for (int i = 0; i < total; ++i) {
+      asm volatile("bar.sync 1, 128;" ::: "memory");      // everyone is done with the slot item i+1 will use
+      if (*s.abort_flag) dead = true;
+      if (rt == 0 && !dead && i + 1 < total) { if (issue(i + 1)) issued = i + 2; }
+      const int64_t u = blockIdx.x + static_cast<int64_t>(i / ipu) * gridDim.x;
+      const int mb = static_cast<int>(u / p.tiles_n), nt = static_cast<int>(u % p.tiles_n);
+      const int d = 1 + (i % ipu) / 2, h = i & 1;
+      if (!dead && !*s.abort_flag) {
+        if (mbar_wait(s.copy(i & 1), (i >> 1) & 1u, s.abort_flag, 642)) {
+          const uint8_t* src = stage_ptr + (i & 1) * HALF_BYTES;
+          float* out_base = p.peer_sum + (static_cast<int64_t>(mb) * GC_BM + 64 * h) * p.N + static_cast<int64_t>(nt) * GC_BN;
+#pragma unroll 4
+          for (int k = 0; k < 16; ++k) {
+            const int v = rt + 128 * k;
+            const int row = v >> 5, c8 = v & 31;
+            const uint4 raw = *reinterpret_cast<const uint4*>(src + (c8 >> 3) * 8192 + sw128_offset(row, c8 & 7));
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+            float f[8];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const float2 t = unpack_bf16(w[e]);
-              acc[q][2 * e] += t.x;
-              acc[q][2 * e + 1] += t.y;
+              f[2 * e] = t.x;
+              f[2 * e + 1] = t.y;
             }
+            float* dst = out_base + static_cast<int64_t>(row) * p.N + c8 * 8;
+            if (d > 1) {       // further peers accumulate onto the first one's values
+              const float4 a0 = *reinterpret_cast<const float4*>(dst);
+              const float4 a1 = *reinterpret_cast<const float4*>(dst + 4);
+              f[0] += a0.x; f[1] += a0.y; f[2] += a0.z; f[3] += a0.w;
+              f[4] += a1.x; f[5] += a1.y; f[6] += a1.z; f[7] += a1.w;
+            }
+            *reinterpret_cast<float4*>(dst) = make_float4(f[0], f[1], f[2], f[3]);
+            *reinterpret_cast<float4*>(dst + 4) = make_float4(f[4], f[5], f[6], f[7]);
           }
         }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int v = rt + 128 * (i + q);
-          float* dst = p.peer_sum + (static_cast<int64_t>(mb) * GC_BM + (v >> 5)) * p.N + col0 + (v & 31) * 8;
-          *reinterpret_cast<float4*>(dst) = make_float4(acc[q][0], acc[q][1], acc[q][2], acc[q][3]);
-          *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[q][4], acc[q][5], acc[q][6], acc[q][7]);
-        }
       }
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (rt == 0) gc_st_release_gpu(p.sum_flags + mb * p.tiles_n + nt, p.epoch);
+      if ((i % ipu) == ipu - 1) {                           // tile complete: publish it to the epilogue warps
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (rt == 0 && !dead && !*s.abort_flag) gc_st_release_gpu(p.sum_flags + mb * p.tiles_n + nt, p.epoch);
+      }
+    }
+    if (rt == 0 && *s.abort_flag && issued > 0) {           // loads nobody waited for: let them land
+      mbar_drain(s.copy(0), 0); mbar_drain(s.copy(0), 1);
+      mbar_drain(s.copy(1), 0); mbar_drain(s.copy(1), 1);
     }
   }
 
@@ -599,18 +630,24 @@ TTCD_EXPORT int ttcd_gemm_rs(const void* x, const void* w, void* out, const long
   p.partial = reinterpret_cast<bf16*>(partial_ptrs[rank]);
   p.part_flags = reinterpret_cast<int*>(flag_ptrs[rank]);
   p.peer_sum = peer_sum; p.sum_flags = sum_flags;
-  constexpr int smem_bytes = GC_RING_BYTES + GC_NBARS * 8 + 16 + 1024;
+  GcPeerMaps maps;
+  for (int d = 1; d < GC_MAX_RANKS; ++d) {
+    const int peer = (rank + (d < world ? d : 0)) % world;     // unused entries alias a valid buffer
+    rc = make_tmap_bf16_3d(&maps.m[d - 1], reinterpret_cast<const void*>(partial_ptrs[peer]), N, m_shard * world, 1, N, 0, 64, 64);
+    if (rc != TTCD_OK) return rc;
+  }
+  constexpr int smem_bytes = GC_RING_BYTES + GC_RS_STAGING + GC_NBARS * 8 + 16 + 1024;
   const long long total = static_cast<long long>(world) * p.mbps * p.tiles_n;
   const int grid = static_cast<int>(std::min<long long>(total, sm_count()));
   cudaStream_t st = static_cast<cudaStream_t>(stream_ptr);
   if (b_mn) {
     TTCD_CUDA_CHECK(static_cast<cudaError_t>(gc_configure(gemm_rs_kernel<true>, smem_bytes)));
-    gemm_rs_kernel<true><<<grid, GC_THREADS, smem_bytes, st>>>(t_a, t_b, gc_peers(partial_ptrs, world),
-                                                               gc_peers(flag_ptrs, world), static_cast<bf16*>(out), p);
+    gemm_rs_kernel<true><<<grid, GC_THREADS, smem_bytes, st>>>(t_a, t_b, maps, gc_peers(flag_ptrs, world),
+                                                               static_cast<bf16*>(out), p);
   } else {
     TTCD_CUDA_CHECK(static_cast<cudaError_t>(gc_configure(gemm_rs_kernel<false>, smem_bytes)));
-    gemm_rs_kernel<false><<<grid, GC_THREADS, smem_bytes, st>>>(t_a, t_b, gc_peers(partial_ptrs, world),
-                                                                gc_peers(flag_ptrs, world), static_cast<bf16*>(out), p);
+    gemm_rs_kernel<false><<<grid, GC_THREADS, smem_bytes, st>>>(t_a, t_b, maps, gc_peers(flag_ptrs, world),
+                                                                static_cast<bf16*>(out), p);
   }
   return static_cast<int>(cudaGetLastError());
 }

@@ -345,16 +345,19 @@ def test_fused_ttt_scan_matches_reference(b, T, with_beta):
     dy = (torch.randn(b, T, C, d_h, device="cuda") * 0.1).bfloat16()
     inputs = [t for t in (z_out, z_tgt, z_hat, beta, w_down, w_upd) if t is not None]
     y, last = cuda.ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_upd, lr)
-    got = torch.autograd.grad(y, inputs, dy)
+    got = torch.autograd.grad(y, inputs, dy, allow_unused=True)
     f = lambda t: None if t is None else t.detach().float().requires_grad_()  # noqa: E731
     fin = [f(t) for t in (z_out, z_tgt, z_hat, beta, w_down, w_upd)]
     y_ref, last_ref = ref.ttt_scan(*fin, lr=lr, update_every=2, state_dtype=torch.float32, return_last_dw_norm=True)
-    want = torch.autograd.grad(y_ref, [t for t in fin if t is not None], dy.float())
-    torch.testing.assert_close(y.float(), y_ref, rtol=3e-2, atol=3e-2)
+    want = torch.autograd.grad(y_ref, [t for t in fin if t is not None], dy.float(), allow_unused=True)
+    assert (y.float() - y_ref).abs().max().item() < 3e-2 * (y_ref.abs().max().item() + 1e-6)     # bf16 operands
     if T > 1:
         torch.testing.assert_close(last.float(), last_ref.float(), rtol=3e-2, atol=1e-2)
     names = [n for n, t in zip(("z_out", "z_tgt", "z_hat", "beta", "w_down", "w_upd"), (z_out, z_tgt, z_hat, beta, w_down, w_upd)) if t is not None]
     for n, a, w in zip(names, got, want):
+        if w is None:                      # T == 1: nothing updates, those inputs do not reach the output
+            assert a is None or float(a.float().abs().max()) == 0.0, n
+            continue
         err = (a.float() - w).abs().max().item()
         ref_mag = w.abs().max().item() + 1e-6
         assert err / ref_mag < 6e-2, (n, err, ref_mag)
