@@ -1,0 +1,114 @@
+"""The fused compute+collective kernels on ONE GPU with the peers emulated by local buffers, so that a
+profiler can look at them (a multi-rank command is never run under a profiler).  "Peer" pointers address other
+buffers of the same GPU; flags that a peer's kernel would raise are set beforehand; the kernels, their tile
+schedules, copies, flag protocol and reductions are exactly those of the multi-GPU runs, only the bytes do not
+cross NVLink.  Outputs are checked against a plain matmul.
+
+    python benchmarks/bench_fused_emulated.py --what ag_gemm|gemm_rs|rs_norm [--world 2] [--tokens 16384]
+"""
+import argparse
+import ctypes
+import json
+import statistics
+import sys
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+sys.path.insert(0, str(ROOT))
+
+from ttcd_b200 import _native as nv  # noqa: E402
+
+
+def ptrs(tensors):
+    return (ctypes.c_longlong * len(tensors))(*[t.data_ptr() for t in tensors])
+
+
+def timeit(fn, iters=10, warmup=3):
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    ts = []
+    for _ in range(iters):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    return statistics.median(ts)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--what", default="ag_gemm")
+    ap.add_argument("--world", type=int, default=2)
+    ap.add_argument("--tokens", type=int, default=16384)
+    ap.add_argument("--k", type=int, default=1024)
+    ap.add_argument("--n", type=int, default=2048)
+    args = ap.parse_args()
+    nv.load(required=True)
+    w_, m, k, n = args.world, args.tokens // args.world, args.k, args.n
+    torch.manual_seed(0)
+    epoch = [0]
+    if args.what == "ag_gemm":
+        xs = [(torch.randn(m, k, device="cuda") * 0.5).bfloat16() for _ in range(w_)]
+        wt = (torch.randn(n, k, device="cuda") * 0.05).bfloat16()
+        out = torch.empty(m * w_, n, device="cuda", dtype=torch.bfloat16)
+        gathered = torch.zeros(m * w_, k, device="cuda", dtype=torch.bfloat16)
+        ready = torch.zeros(w_ * (m // 128), device="cuda", dtype=torch.int32)
+
+        def run():
+            epoch[0] += 1
+            nv.call("ttcd_ag_gemm", ptrs(xs), nv.ptr(wt), nv.ptr(out), nv.ptr(gathered), nv.ptr(ready), nv.i32(0), nv.i32(w_),
+                    nv.i64(m), nv.i64(n), nv.i64(k), nv.i64(k), nv.i64(n), nv.i32(0), nv.i32(epoch[0]), nv.i64(2_000_000_000),
+                    nv.stream_ptr())
+        ms = timeit(run)
+        want = torch.cat(xs).float() @ wt.float().t()
+        err = (out.float() - want).abs().max().item() / want.abs().max().item()
+        flops = 2.0 * m * w_ * k * n
+    elif args.what == "gemm_rs":
+        x = (torch.randn(m * w_, k, device="cuda") * 0.5).bfloat16()
+        wt = (torch.randn(n, k, device="cuda") * 0.05).bfloat16()
+        out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+        parts = [(torch.randn(m * w_, n, device="cuda") * 0.1).bfloat16() for _ in range(w_)]   # peers' partials: given data
+        nflags = w_ * (m // 128) * (n // 256)
+        flags = [torch.full((nflags,), 1 << 30, device="cuda", dtype=torch.int32) for _ in range(w_)]   # peers: already raised
+        flags[0].zero_()
+        peer_sum = torch.empty(m, n, device="cuda")
+        sum_flags = torch.zeros((m // 128) * (n // 256), device="cuda", dtype=torch.int32)
+
+        def run():
+            epoch[0] += 1
+            nv.call("ttcd_gemm_rs", nv.ptr(x), nv.ptr(wt), nv.ptr(out), ptrs(parts), ptrs(flags), nv.ptr(peer_sum), nv.ptr(sum_flags),
+                    nv.i32(0), nv.i32(w_), nv.i64(m), nv.i64(n), nv.i64(k), nv.i64(k), nv.i64(k), nv.i64(n), nv.i32(0),
+                    nv.i32(epoch[0]), nv.i64(2_000_000_000), nv.stream_ptr())
+        ms = timeit(run)
+        want = x[:m].float() @ wt.float().t() + sum(p[:m].float() for p in parts[1:])
+        err = (out.float() - want).abs().max().item() / want.abs().max().item()
+        flops = 2.0 * m * w_ * k * n
+    elif args.what == "rs_norm":
+        numel = m * k
+        grads = [(torch.randn(numel * w_, device="cuda") * 0.1).bfloat16() for _ in range(w_)]
+        out = torch.empty(numel, device="cuda")
+        norm = torch.zeros(1, device="cuda")
+
+        def run():
+            nv.call("ttcd_rs_cast_scale_norm", ptrs(grads), nv.i32(w_), nv.i64(0), nv.i64(numel), nv.f32(1.0 / w_), nv.ptr(out),
+                    nv.ptr(norm), nv.stream_ptr())
+        ms = timeit(run)
+        want = sum(g[:numel].float() for g in grads) / w_
+        err = (out - want).abs().max().item()
+        flops = 0.0
+    else:
+        raise SystemExit(f"unknown --what {args.what}")
+    torch.cuda.synchronize()
+    print(json.dumps({"bench": "fused_emulated", "what": args.what, "world": w_, "m_shard": m, "n": n, "k": k, "ms": round(ms, 4),
+                      "tflops": round(flops / ms / 1e9, 1), "max_rel_err": round(err, 5), "device_status": nv.device_status()}))
+
+
+if __name__ == "__main__":
+    main()

@@ -112,9 +112,11 @@ def bench_attn(seqs, batches, wt=8192, ws=4096, bwd=False):
                     ms_dual = timeit(lambda: cuda.attn_forward(q, k, v, wt, ws, sc, True))
                     ms_t = timeit(lambda: cuda.attn_forward(q, k, v, wt, wt, sc, False))
                     ms_s = timeit(lambda: cuda.attn_forward(q, k, v, ws, ws, sc, False))
+                    from ttcd_b200 import ops
+                    ms_lse = timeit(lambda: ops.lse_dual_window_attention(q, k, v, wt, ws, sc))
                 fl = attn_flops(B, T, H, D, wt)
                 row.update(fused_dual_ms=round(ms_dual, 3), teacher_only_ms=round(ms_t, 3),
-                           two_calls_ms=round(ms_t + ms_s, 3), fused_tflops=round(fl / ms_dual / 1e9, 1),
+                           two_calls_ms=round(ms_t + ms_s, 3), lse_variant_ms=round(ms_lse, 3), fused_tflops=round(fl / ms_dual / 1e9, 1),
                            frac_of_peak=round(fl / ms_dual / 1e9 / tf_peak, 3))
                 if fa is not None:
                     with torch.no_grad():

@@ -19,6 +19,8 @@
 // (custom_models/ipttcd/modeling_ipttcdv9.py:686-690; profiling/FUSED_ATTENTION_DESIGN.md:68-69).
 #include "common.cuh"
 
+#include <cstdlib>
+
 #include <algorithm>
 
 namespace ttcd {
@@ -44,6 +46,8 @@ struct AttnBwdParams {
   float scale, scale_log2;
   // context parallel: keys [0, halo_len) live in the previous rank's K/V buffers (rows halo_row0..)
   int halo_len, halo_row0;
+  // single-window dQ kernel: keep Q and dO (loop-invariant A operands) in tensor memory
+  int a_in_tmem;
 };
 
 // 32 accumulator columns of one TMEM lane -> 32 bf16 (one 64-byte half row) of a K-major SW128 tile
@@ -200,6 +204,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   auto sdp_full = [&](int s) { return bars + 8u * (1 + C::NSLOTS + s); };
   const uint32_t ew_done = bars + 8u * (1 + C::NSLOTS + C::NSETS);
   const uint32_t acc_done = ew_done + 8u;
+  const uint32_t a_ready = acc_done + 8u;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::BAR_OFF + C::NBARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* vecs = reinterpret_cast<float*>(smem + C::VEC_OFF);
@@ -478,8 +483,11 @@ struct DqCfg {
   static constexpr int RING_OFF = DOS_OFF + (DUAL ? DB * Q_REGION : 0);   // NSLOTS x (K, V)
   static constexpr int DS_OFF = RING_OFF + NSLOTS * 2 * KV_BYTES;         // [128 x 64] bf16
   static constexpr int BAR_OFF = DS_OFF + Q_REGION;
-  // q_full, kv_full[NSLOTS], sdp_full[2], ew_done, acc_done
-  static constexpr int NBARS = 1 + NSLOTS + 2 + 2;
+  // q_full, kv_full[NSLOTS], sdp_full[2], ew_done, acc_done, a_ready
+  static constexpr int NBARS = 1 + NSLOTS + 2 + 2 + 1;
+  // single window: 128 (dQ) + 2 x 128 (S | dP sets) leaves 128 columns: Q and dO as bf16 A operands
+  static constexpr int A_COLS = D / 2;
+  static constexpr bool CAN_TS = !DUAL;
   static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16;
 };
 
@@ -498,6 +506,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   auto sdp_full = [&](int s) { return bars + 8u * (1 + C::NSLOTS + s); };
   const uint32_t ew_done = bars + 8u * (3 + C::NSLOTS);
   const uint32_t acc_done = ew_done + 8u;
+  const uint32_t a_ready = acc_done + 8u;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::BAR_OFF + C::NBARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -525,6 +534,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     mbar_init(sdp_full(1), 1);
     mbar_init(ew_done, 8);
     mbar_init(acc_done, 1);
+    mbar_init(a_ready, 8);
     mbar_fence_init();
   }
   if (warp == 8) {
@@ -536,6 +546,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t t_dq = tmem_base;
+  const bool use_ts = C::CAN_TS && p.a_in_tmem != 0;
+  const uint32_t t_qa = tmem_base + 128 + 2 * C::SET_COLS;      // [384, 384 + D/2): Q, then dO
+  const uint32_t t_doa = t_qa + C::A_COLS;
   auto t_set = [&](int it) { return tmem_base + 128 + (it & 1) * C::SET_COLS; };  // S | dP_T | dP_S
   const bool healthy = (*abort_flag == 0);
 
@@ -559,19 +572,32 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         const bool st = iter_student(it);
         const uint32_t sk = slot_base(it), sv = sk + C::KV_BYTES;
         const uint32_t ts = t_set(it);
+        if (use_ts) {
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t qo = (k / 4) * C::Q_REGION + (k % 4) * 32;
-          const uint32_t ko = (k / 4) * C::KV_REGION + (k % 4) * 32;
-          umma_ss(ts, umma_desc_sw128(sbase + C::Q_OFF + qo, 16, 1024), umma_desc_sw128(sk + ko, 16, 1024), idesc_s,
-                  k != 0);
-        }
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t ko = (k / 4) * C::KV_REGION + (k % 4) * 32;
+            umma_ts(ts, t_qa + k * 8, umma_desc_sw128(sk + ko, 16, 1024), idesc_s, k != 0);
+          }
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t qo = (k / 4) * C::Q_REGION + (k % 4) * 32;
-          const uint32_t ko = (k / 4) * C::KV_REGION + (k % 4) * 32;
-          umma_ss(ts + 64, umma_desc_sw128(sbase + C::DOT_OFF + qo, 16, 1024), umma_desc_sw128(sv + ko, 16, 1024),
-                  idesc_s, k != 0);
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t ko = (k / 4) * C::KV_REGION + (k % 4) * 32;
+            umma_ts(ts + 64, t_doa + k * 8, umma_desc_sw128(sv + ko, 16, 1024), idesc_s, k != 0);
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t qo = (k / 4) * C::Q_REGION + (k % 4) * 32;
+            const uint32_t ko = (k / 4) * C::KV_REGION + (k % 4) * 32;
+            umma_ss(ts, umma_desc_sw128(sbase + C::Q_OFF + qo, 16, 1024), umma_desc_sw128(sk + ko, 16, 1024), idesc_s,
+                    k != 0);
+          }
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t qo = (k / 4) * C::Q_REGION + (k % 4) * 32;
+            const uint32_t ko = (k / 4) * C::KV_REGION + (k % 4) * 32;
+            umma_ss(ts + 64, umma_desc_sw128(sbase + C::DOT_OFF + qo, 16, 1024), umma_desc_sw128(sv + ko, 16, 1024),
+                    idesc_s, k != 0);
+          }
         }
         if (DUAL && st) {
 #pragma unroll
@@ -594,6 +620,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       }
       for (int it = 0; it < C::NSLOTS - 1 && it < n_iters; ++it) load_kv(it);
       ok = mbar_wait(q_full, 0, abort_flag, 321) && mbar_wait(kv_full(0), 0, abort_flag, 322);
+      if (ok && use_ts) ok = mbar_wait(a_ready, 0, abort_flag, 326);      // Q and dO copied into tensor memory
       if (ok) { tc_fence_after_sync(); issue_sdp(0); }
       for (int it = 0; it < n_iters && ok; ++it) {
         if (it + 1 < n_iters) {
@@ -640,6 +667,28 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       const bool r = mbar_wait(bar, parity, abort_flag, code);
       return __all_sync(0xffffffffu, r) != 0;
     };
+    if (use_ts) {
+      // Q and dO rows: shared memory (128-byte swizzled, 64 columns per region) -> packed bf16 pairs in TMEM
+      ok = wait_all(q_full, 0, 334);
+      if (ok) {
+        for (int reg = half; reg < C::DB; reg += 2) {
+          uint32_t qa[32], da[32];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const uint4 a = *reinterpret_cast<const uint4*>(smem + C::Q_OFF + reg * C::Q_REGION + sw128_offset(qrow, c));
+            const uint4 g = *reinterpret_cast<const uint4*>(smem + C::DOT_OFF + reg * C::Q_REGION + sw128_offset(qrow, c));
+            qa[4 * c] = a.x; qa[4 * c + 1] = a.y; qa[4 * c + 2] = a.z; qa[4 * c + 3] = a.w;
+            da[4 * c] = g.x; da[4 * c + 1] = g.y; da[4 * c + 2] = g.z; da[4 * c + 3] = g.w;
+          }
+          tmem_st32(t_qa + lane_addr + reg * 32, qa);
+          tmem_st32(t_doa + lane_addr + reg * 32, da);
+        }
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(a_ready);
+      }
+    }
     for (int it = 0; it < n_iters && ok; ++it) {
       const bool st = iter_student(it);
       const int key0 = iter_key0(it) + half * 32;
@@ -800,6 +849,11 @@ TTCD_EXPORT int ttcd_attn_bwd_cp(const void* q, const void* k, const void* v, co
   if (!dual) p.w_s = p.w_t;
   p.scale = scale; p.scale_log2 = scale * LOG2E;
   p.halo_len = halo_len; p.halo_row0 = halo_rows - halo_len;
+  static const int a_in_tmem = [] {
+    const char* e = getenv("TTCD_ATTN_BWD_TS");
+    return (e != nullptr && e[0] == '0') ? 0 : 1;
+  }();
+  p.a_in_tmem = a_in_tmem;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   if (D == 128) return dual ? launch_bwd<128, true>(m, p, B, stream) : launch_bwd<128, false>(m, p, B, stream);
   return dual ? launch_bwd<64, true>(m, p, B, stream) : launch_bwd<64, false>(m, p, B, stream);

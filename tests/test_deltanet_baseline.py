@@ -50,3 +50,16 @@ def test_model_trains_sublayer_only_in_training_mode():
     model.eval()
     b = model(input_ids=ids, labels=ids).loss
     assert abs(float(a) - float(b)) > 1e-6                    # training-only path
+
+
+def test_lse_combination_equals_dual_window_attention():
+    """The LSE-merge formulation (student pass + shifted far-band pass) gives the fused op's outputs."""
+    from ttcd_b200 import ops
+    torch.manual_seed(0)
+    B, T, H, HK, D = 2, 96, 4, 2, 16
+    q, k, v = torch.randn(B, T, H, D), torch.randn(B, T, HK, D), torch.randn(B, T, HK, D)
+    for wt, ws in ((48, 16), (64, 32), (200, 24)):
+        t_ref, s_ref = ref.dual_window_attention(q, k, v, wt, ws)
+        t, s = ops.lse_dual_window_attention(q, k, v, wt, ws)
+        torch.testing.assert_close(s, s_ref, rtol=1e-5, atol=1e-5)
+        torch.testing.assert_close(t, t_ref, rtol=1e-4, atol=1e-5)

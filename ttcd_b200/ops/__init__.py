@@ -142,6 +142,21 @@ def dual_window_attention(q, k, v, window_teacher, window_student, scale=None, c
     return reference.dual_window_attention(q, k, v, window_teacher, window_student, scale, cu_seqlens)
 
 
+def lse_dual_window_attention(q, k, v, window_teacher, window_student, scale=None):
+    """Teacher and student outputs by LSE combination (the reference's ``lse_dual_window_attn``,
+    profiling/lse_dual_attn.py:16-39): student = attention(w_S); the keys only the teacher sees,
+    [i - w_T + 1, i - w_S], are attended by shifting the arrays by w_S (window w_T - w_S); the teacher is
+    the LSE-weighted merge of the two.  A benchmark variant: the fused kernel does the same in one pass."""
+    T = q.shape[1]
+    o_s, lse_s = attention(q, k, v, window_student, scale, return_lse=True)
+    if T <= window_student or window_teacher <= window_student:
+        return o_s, o_s
+    o_far, lse_far = attention(q[:, window_student:], k[:, :T - window_student], v[:, :T - window_student],
+                               window_teacher - window_student, scale, return_lse=True)
+    tail = lse_merge(o_s[:, window_student:], lse_s[..., window_student:], o_far, lse_far)
+    return torch.cat([o_s[:, :window_student], tail], dim=1), o_s
+
+
 def lse_merge(o_a, lse_a, o_b, lse_b):
     if _native.use_native(o_a):
         return _cuda().lse_merge(o_a, lse_a, o_b, lse_b)
