@@ -34,7 +34,10 @@ struct GemmSmem {
   static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
   static constexpr int B_BYTES = BN * GEMM_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  // epilogue staging for TMA stores: 4 warps x 2 buffers x (32 rows x 128 bytes), 128-byte swizzled
+  static constexpr int EPI_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int EPI_BYTES = 4 * 2 * 4096;
+  static constexpr int BAR_OFFSET = EPI_OFFSET + EPI_BYTES;
   // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem base word, abort flag
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16;
 };
@@ -42,7 +45,8 @@ struct GemmSmem {
 template <int BN, int STAGES, bool A_MN, bool B_MN, typename OutT, bool HAS_CIN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-            OutT* __restrict__ C, const OutT* __restrict__ Cin, const GemmParams p) {
+            const __grid_constant__ CUtensorMap tma_c, OutT* __restrict__ C, const OutT* __restrict__ Cin,
+            const GemmParams p) {
   using S = GemmSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: required by the 128-byte swizzle pattern shared by TMA and UMMA.
@@ -183,45 +187,62 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       OutT* crow = C + b * p.stride_c + row * p.ldc;
       const OutT* cin_row = HAS_CIN ? (Cin + b * p.stride_c + row * p.ldc) : nullptr;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      if constexpr (sizeof(OutT) == 2) {
+        // bf16 output: TMEM -> registers -> swizzled shared memory -> TMA store of a 32-row x 64-column box
+        // (full 128-byte lines, clipped at the matrix edges by the tensor map); two staging buffers per warp.
+        uint8_t* stage = smem + S::EPI_OFFSET + quarter * 8192;
+        int chunk = 0;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t v[32];
-        tmem_ld32(t_row + c, v);
-        tmem_ld_wait();
-        const int64_t col = n0 + c;
-        if (row_ok && col < p.N) {
-          if constexpr (sizeof(OutT) == 2) {
+        for (int c = 0; c < BN; c += 64, ++chunk) {
+          uint32_t v0[32], v1[32];
+          tmem_ld32(t_row + c, v0);
+          tmem_ld32(t_row + c + 32, v1);
+          if (lane == 0) tma_store_wait_read1();      // the store issued two chunks ago has released this buffer
+          __syncwarp();
+          tmem_ld_wait();
+          uint8_t* buf = stage + (chunk & 1) * 4096;
+          const int64_t col = n0 + c;
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (col + j + 8 <= p.N) {
-                float f[8];
+          for (int j = 0; j < 64; j += 8) {
+            float f[8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[j + e]) * rs;
-                if constexpr (HAS_CIN) {
-                  const uint4 cv = *reinterpret_cast<const uint4*>(cin_row + col + j);
-                  const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
+            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(j < 32 ? v0[(j & 31) + e] : v1[(j & 31) + e]) * rs;
+            if constexpr (HAS_CIN) {
+              if (row_ok && col + j + 8 <= p.N) {
+                const uint4 cv = *reinterpret_cast<const uint4*>(cin_row + col + j);
+                const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
 #pragma unroll
-                  for (int e = 0; e < 4; ++e) {
-                    const float2 t = unpack_bf16(cw[e]);
-                    f[2 * e] += p.beta * t.x;
-                    f[2 * e + 1] += p.beta * t.y;
-                  }
+                for (int e = 0; e < 4; ++e) {
+                  const float2 t = unpack_bf16(cw[e]);
+                  f[2 * e] += p.beta * t.x;
+                  f[2 * e + 1] += p.beta * t.y;
                 }
-                uint4 o;
-                o.x = pack_bf16(f[0], f[1]);
-                o.y = pack_bf16(f[2], f[3]);
-                o.z = pack_bf16(f[4], f[5]);
-                o.w = pack_bf16(f[6], f[7]);
-                *reinterpret_cast<uint4*>(crow + col + j) = o;
-              } else {
-                for (int e = 0; e < 8 && col + j + e < p.N; ++e) {
-                  float f = __uint_as_float(v[j + e]) * rs;
-                  if constexpr (HAS_CIN) f += p.beta * __bfloat162float(cin_row[col + j + e]);
-                  crow[col + j + e] = __float2bfloat16(f);
-                }
+              } else if (row_ok) {
+                for (int e = 0; e < 8 && col + j + e < p.N; ++e) f[e] += p.beta * __bfloat162float(cin_row[col + j + e]);
               }
             }
-          } else {
+            uint4 o;
+            o.x = pack_bf16(f[0], f[1]);
+            o.y = pack_bf16(f[2], f[3]);
+            o.z = pack_bf16(f[4], f[5]);
+            o.w = pack_bf16(f[6], f[7]);
+            *reinterpret_cast<uint4*>(buf + sw128_offset(lane, j >> 3)) = o;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && col < p.N) {
+            tma_store_3d(&tma_c, smem_u32(buf), static_cast<int>(col), static_cast<int>(m0 + quarter * 32), b);
+            tma_store_commit();
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(t_row + c, v);
+          tmem_ld_wait();
+          const int64_t col = n0 + c;
+          if (row_ok && col < p.N) {
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
               if (col + j + 4 <= p.N) {
@@ -252,6 +273,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       acc_phase[acc] ^= 1u;
       acc ^= 1;
     }
+    if (sizeof(OutT) == 2 && lane == 0) tma_store_wait0();   // staging buffers stay valid until the stores ran
   }
 
   tc_fence_before_sync();
@@ -263,8 +285,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
 }
 
 template <int BN, int STAGES, bool A_MN, bool B_MN, typename OutT, bool HAS_CIN>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, void* c, const void* cin, const GemmParams& p,
-                       cudaStream_t stream) {
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, void* c, const void* cin,
+                       const GemmParams& p, cudaStream_t stream) {
   using S = GemmSmem<BN, STAGES>;
   auto kern = gemm_kernel<BN, STAGES, A_MN, B_MN, OutT, HAS_CIN>;
   constexpr int smem_bytes = S::TOTAL + 1024;
@@ -275,29 +297,29 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, void* c, co
   }
   const int64_t total = p.tiles_m * p.tiles_n * p.batch;
   const int grid = static_cast<int>(total < sm_count() ? total : sm_count());
-  kern<<<grid, GEMM_THREADS, smem_bytes, stream>>>(ta, tb, static_cast<OutT*>(c), static_cast<const OutT*>(cin), p);
+  kern<<<grid, GEMM_THREADS, smem_bytes, stream>>>(ta, tb, tc, static_cast<OutT*>(c), static_cast<const OutT*>(cin), p);
   return static_cast<int>(cudaGetLastError());
 }
 
 template <int BN, int STAGES, bool A_MN, bool B_MN>
-static int dispatch_out(const CUtensorMap& ta, const CUtensorMap& tb, void* c, const void* cin, const GemmParams& p,
-                        int out_fp32, cudaStream_t stream) {
+static int dispatch_out(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, void* c, const void* cin,
+                        const GemmParams& p, int out_fp32, cudaStream_t stream) {
   const bool has_cin = cin != nullptr && p.beta != 0.f;
   if (out_fp32) {
-    return has_cin ? launch_gemm<BN, STAGES, A_MN, B_MN, float, true>(ta, tb, c, cin, p, stream)
-                   : launch_gemm<BN, STAGES, A_MN, B_MN, float, false>(ta, tb, c, cin, p, stream);
+    return has_cin ? launch_gemm<BN, STAGES, A_MN, B_MN, float, true>(ta, tb, tc, c, cin, p, stream)
+                   : launch_gemm<BN, STAGES, A_MN, B_MN, float, false>(ta, tb, tc, c, cin, p, stream);
   }
-  return has_cin ? launch_gemm<BN, STAGES, A_MN, B_MN, bf16, true>(ta, tb, c, cin, p, stream)
-                 : launch_gemm<BN, STAGES, A_MN, B_MN, bf16, false>(ta, tb, c, cin, p, stream);
+  return has_cin ? launch_gemm<BN, STAGES, A_MN, B_MN, bf16, true>(ta, tb, tc, c, cin, p, stream)
+                 : launch_gemm<BN, STAGES, A_MN, B_MN, bf16, false>(ta, tb, tc, c, cin, p, stream);
 }
 
 template <int BN, int STAGES>
-static int dispatch_major(const CUtensorMap& ta, const CUtensorMap& tb, void* c, const void* cin,
+static int dispatch_major(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, void* c, const void* cin,
                           const GemmParams& p, int a_mn, int b_mn, int out_fp32, cudaStream_t stream) {
-  if (!a_mn && !b_mn) return dispatch_out<BN, STAGES, false, false>(ta, tb, c, cin, p, out_fp32, stream);
-  if (!a_mn && b_mn) return dispatch_out<BN, STAGES, false, true>(ta, tb, c, cin, p, out_fp32, stream);
-  if (a_mn && !b_mn) return dispatch_out<BN, STAGES, true, false>(ta, tb, c, cin, p, out_fp32, stream);
-  return dispatch_out<BN, STAGES, true, true>(ta, tb, c, cin, p, out_fp32, stream);
+  if (!a_mn && !b_mn) return dispatch_out<BN, STAGES, false, false>(ta, tb, tc, c, cin, p, out_fp32, stream);
+  if (!a_mn && b_mn) return dispatch_out<BN, STAGES, false, true>(ta, tb, tc, c, cin, p, out_fp32, stream);
+  if (a_mn && !b_mn) return dispatch_out<BN, STAGES, true, false>(ta, tb, tc, c, cin, p, out_fp32, stream);
+  return dispatch_out<BN, STAGES, true, true>(ta, tb, tc, c, cin, p, out_fp32, stream);
 }
 
 }  // namespace ttcd
@@ -341,6 +363,11 @@ TTCD_EXPORT int ttcd_gemm_bf16(const void* a, const void* b, void* c, const void
   p.alpha = alpha; p.beta = beta;
   p.row_scale = static_cast<const bf16*>(row_scale);
   p.a_bcast = a_bcast; p.b_bcast = b_bcast;
-  if (BN == 256) return dispatch_major<256, 4>(ta, tb, c, c_in, p, a_mn, b_mn, out_fp32, stream);
-  return dispatch_major<128, 6>(ta, tb, c, c_in, p, a_mn, b_mn, out_fp32, stream);
+  CUtensorMap tc = ta;      // fp32 outputs are written with plain stores and never touch this map
+  if (!out_fp32) {
+    rc = make_tmap_bf16_3d(&tc, c, N, M, batch, ldc, stride_c, 64, 32);
+    if (rc != TTCD_OK) return rc;
+  }
+  if (BN == 256) return dispatch_major<256, 4>(ta, tb, tc, c, c_in, p, a_mn, b_mn, out_fp32, stream);
+  return dispatch_major<128, 6>(ta, tb, tc, c, c_in, p, a_mn, b_mn, out_fp32, stream);
 }

@@ -166,8 +166,7 @@ __device__ __forceinline__ GcSmem gc_setup(uint8_t* raw) {
     }
     for (int i = 0; i < GC_COPY_SLOTS; ++i) mbar_init(s.copy(i), 1);
     *s.abort_flag = 0;
-    s.epi_count[0] = 0;
-    s.epi_count[1] = 0;
+    for (int i = 0; i < 4; ++i) s.epi_count[i] = 0;
     mbar_fence_init();
   }
   if ((threadIdx.x >> 5) == 1) {
@@ -400,7 +399,9 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     const int quarter = warp & 3;
     uint32_t acc_phase[2] = {0, 0};
     int acc = 0;
+    int tile_seq = -1;
     for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      ++tile_seq;
       const GcTile c = gc_tile(tile, p, false);
       const bool own = c.owner == p.rank;
       if (!mbar_wait(s.tfull(acc), acc_phase[acc], s.abort_flag, 634)) break;
@@ -417,13 +418,21 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           tmem_ld_wait();
           gc_store_row32(v, prow + col, nullptr);
         }
+        // the accumulator is in registers / on its way to memory: hand the TMEM buffer back to the MMA warp
+        // before paying for the system-scope fence of the flag
+        tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {
+          mbar_arrive(s.tempty(acc));
           __threadfence_system();
-          // one counter per accumulator buffer: a warp cannot run two tiles ahead on the same buffer
-          if ((atomicAdd(s.epi_count + acc, 1) & 3) == 3)
+          // counters rotate over four slots: a warp is never more than two tiles ahead of another one's
+          // pending increment (the TMEM hand-over of tile i+2 needs every warp's arrival for tile i)
+          if ((atomicAdd(s.epi_count + (tile_seq & 3), 1) & 3) == 3)
             gc_st_release_sys(p.part_flags + (c.owner * p.mbps + c.mb) * p.tiles_n + c.nt, p.epoch);
         }
+        acc_phase[acc] ^= 1u;
+        acc ^= 1;
+        continue;
       } else {
         // this rank's rows: add the peers' sum left by the reducer warps, write the final output
         if (p.world > 1) {
@@ -591,7 +600,7 @@ TTCD_EXPORT int ttcd_ag_gemm(const long long* x_ptrs, const void* w, void* c, vo
   p.m_shard = m_shard; p.N = N; p.K = K; p.ldc = ldc;
   p.wait_ns = wait_ns > 0 ? static_cast<uint64_t>(wait_ns) : 10000000000ull;
   p.gathered = static_cast<bf16*>(gathered); p.ready = ready;
-  constexpr int smem_bytes = GC_RING_BYTES + GC_COPY_SLOTS * GC_COPY_BYTES + GC_NBARS * 8 + 16 + 1024;
+  constexpr int smem_bytes = GC_RING_BYTES + GC_COPY_SLOTS * GC_COPY_BYTES + GC_NBARS * 8 + 32 + 1024;
   const long long total = static_cast<long long>(world) * p.mbps * p.tiles_n;
   const int grid = static_cast<int>(std::min<long long>(total, sm_count()));
   cudaStream_t st = static_cast<cudaStream_t>(stream_ptr);
@@ -636,7 +645,7 @@ TTCD_EXPORT int ttcd_gemm_rs(const void* x, const void* w, void* out, const long
     rc = make_tmap_bf16_3d(&maps.m[d - 1], reinterpret_cast<const void*>(partial_ptrs[peer]), N, m_shard * world, 1, N, 0, 64, 64);
     if (rc != TTCD_OK) return rc;
   }
-  constexpr int smem_bytes = GC_RING_BYTES + GC_RS_STAGING + GC_NBARS * 8 + 16 + 1024;
+  constexpr int smem_bytes = GC_RING_BYTES + GC_RS_STAGING + GC_NBARS * 8 + 32 + 1024;
   const long long total = static_cast<long long>(world) * p.mbps * p.tiles_n;
   const int grid = static_cast<int>(std::min<long long>(total, sm_count()));
   cudaStream_t st = static_cast<cudaStream_t>(stream_ptr);
