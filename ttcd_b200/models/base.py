@@ -8,6 +8,8 @@ no logits tensor is produced, and tied embeddings share one parameter.
 """
 from __future__ import annotations
 
+import os
+
 import math
 from typing import Any
 
@@ -21,6 +23,9 @@ from .layers import RMSNorm, WindowKVCache
 
 IGNORE_INDEX = -100
 
+
+# TTCD_NVTX=1: one NVTX range per block (forward) for timeline tools; off by default (a push/pop per layer).
+_NVTX = os.environ.get("TTCD_NVTX", "0") == "1"
 
 class FusedLinearCrossEntropyLoss(nn.Module):
     """criterion(hidden, labels, weight, bias): CE without materialising [tokens, vocab] logits."""
@@ -164,14 +169,19 @@ class DecoderModel(DecoderPreTrainedModel):
 
         hidden_states = inputs_embeds
         all_hidden = () if output_hidden_states else None
-        for layer in self.layers:
+        nvtx = _NVTX and hidden_states.is_cuda
+        for i, layer in enumerate(self.layers):
             if output_hidden_states:
                 all_hidden += (hidden_states,)
+            if nvtx:
+                torch.cuda.nvtx.range_push(f"layer{i}")
             if self.gradient_checkpointing and self.training and self._checkpoint_layer(layer):
                 hidden_states = torch.utils.checkpoint.checkpoint(
                     layer, hidden_states, attention_mask, None, False, use_reentrant=False, **kwargs)
             else:
                 hidden_states = layer(hidden_states, attention_mask, past_key_values, use_cache, **kwargs)
+            if nvtx:
+                torch.cuda.nvtx.range_pop()
         hidden_states = self.norm(hidden_states)
         if output_hidden_states:
             all_hidden += (hidden_states,)

@@ -221,6 +221,7 @@ def main(job_config: JobConfig) -> None:
             metrics.sink.log({"loss_metrics/global_avg_loss": a, "loss_metrics/global_max_loss": m}, s)
 
     profiler = _maybe_profiler(job_config, rank)
+    snapshotter = MemorySnapshotter(job_config, rank)
     data_iter = iter(dataloader)
     accum = tr.gradient_accumulation_steps
     t_start = time.perf_counter()
@@ -266,6 +267,7 @@ def main(job_config: JobConfig) -> None:
         ckpt.save(step, last=step == tr.steps, force=external_save_requested(rank))
         if profiler is not None:
             profiler.step()
+        snapshotter.step(step)
         if step == 1:
             set_pg_timeouts(job_config.comm.train_timeout_seconds)
     if profiler is not None:
@@ -293,6 +295,28 @@ def _maybe_profiler(job_config, rank):
         schedule=torch.profiler.schedule(wait=freq - 4, warmup=3, active=1), on_trace_ready=handler)
     prof.__enter__()
     return prof
+
+
+class MemorySnapshotter:
+    """CUDA allocator history, dumped as a pickle per rank every ``profile_freq`` steps and on an out-of-memory
+    error (``--profiling.enable_memory_snapshot``; the files open in pytorch.org/memory_viz)."""
+
+    def __init__(self, job_config, rank: int):
+        p = job_config.profiling
+        self.enabled = bool(p.enable_memory_snapshot) and torch.cuda.is_available()
+        self.folder = os.path.join(job_config.job.dump_folder, p.save_memory_snapshot_folder)
+        self.freq, self.rank = max(1, p.profile_freq), rank
+        if self.enabled:
+            torch.cuda.memory._record_memory_history(max_entries=100000)
+
+    def dump(self, name: str) -> None:
+        d = os.path.join(self.folder, name)
+        os.makedirs(d, exist_ok=True)
+        torch.cuda.memory._dump_snapshot(os.path.join(d, f"rank{self.rank}_memory_snapshot.pickle"))
+
+    def step(self, step: int, oom: bool = False) -> None:
+        if self.enabled and (oom or step % self.freq == 0):
+            self.dump(f"iteration_{step}" + ("_exit" if oom else ""))
 
 
 def cli(argv=None):
