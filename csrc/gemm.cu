@@ -27,6 +27,7 @@ struct GemmParams {
   float alpha, beta;
   const bf16* row_scale;     // optional [batch*M]
   int a_bcast, b_bcast;      // operand shared by every batch entry (its tensor map has batch 1)
+  int m_fastest;             // raster order inside a batch entry: consecutive tiles walk M (the B panel is the big one)
 };
 
 template <int BN, int STAGES>
@@ -100,8 +101,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const int b = static_cast<int>(tile / tiles_per_batch);
         const int64_t r = tile % tiles_per_batch;
-        const int m0 = static_cast<int>(r / p.tiles_n) * GEMM_BM;
-        const int n0 = static_cast<int>(r % p.tiles_n) * BN;
+        const int m0 = static_cast<int>(p.m_fastest ? r % p.tiles_m : r / p.tiles_n) * GEMM_BM;
+        const int n0 = static_cast<int>(p.m_fastest ? r / p.tiles_m : r % p.tiles_n) * BN;
         const int za = p.a_bcast ? 0 : b, zb = p.b_bcast ? 0 : b;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 101)) { ok = false; break; }
@@ -176,8 +177,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
     for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       const int b = static_cast<int>(tile / tiles_per_batch);
       const int64_t r = tile % tiles_per_batch;
-      const int64_t m0 = (r / p.tiles_n) * GEMM_BM;
-      const int64_t n0 = (r % p.tiles_n) * BN;
+      const int64_t m0 = (p.m_fastest ? r % p.tiles_m : r / p.tiles_n) * GEMM_BM;
+      const int64_t n0 = (p.m_fastest ? r / p.tiles_m : r % p.tiles_n) * BN;
       if (!mbar_wait(tfull_bar(acc), acc_phase[acc], abort_flag, 104)) { ok = false; break; }
       tc_fence_after_sync();
       const int64_t row = m0 + quarter * 32 + lane;
@@ -363,6 +364,9 @@ TTCD_EXPORT int ttcd_gemm_bf16(const void* a, const void* b, void* c, const void
   p.alpha = alpha; p.beta = beta;
   p.row_scale = static_cast<const bf16*>(row_scale);
   p.a_bcast = a_bcast; p.b_bcast = b_bcast;
+  // the operand panel that is re-streamed once per step of the outer tile loop should be the smaller one (it then
+  // lives in the 126 MB L2): walk M fastest when the B panel (N x K) is the larger
+  p.m_fastest = N > M ? 1 : 0;
   CUtensorMap tc = ta;      // fp32 outputs are written with plain stores and never touch this map
   if (!out_fp32) {
     rc = make_tmap_bf16_3d(&tc, c, N, M, batch, ldc, stride_c, 64, 32);

@@ -446,12 +446,37 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         const int64_t lrow = static_cast<int64_t>(c.mb) * GC_BM + quarter * 32 + lane;
         bf16* orow = out + lrow * p.ldc + col0;
         const float* srow = p.world > 1 ? p.peer_sum + lrow * p.N + col0 : nullptr;
+        // the peers' sum comes from memory: its loads for the next 32 columns are in flight while the current
+        // 32 are read from TMEM, converted and stored
+        float4 nxt[8];
+        if (srow != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) nxt[j] = *reinterpret_cast<const float4*>(srow + 4 * j);
+        }
 #pragma unroll 1
         for (int col = 0; col < GC_BN; col += 32) {
           uint32_t v[32];
           tmem_ld32(t_row + col, v);
+          float4 cur[8];
+          if (srow != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) cur[j] = nxt[j];
+            if (col + 32 < GC_BN) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) nxt[j] = *reinterpret_cast<const float4*>(srow + col + 32 + 4 * j);
+            }
+          }
           tmem_ld_wait();
-          gc_store_row32(v, orow + col, srow != nullptr ? srow + col : nullptr);
+          if (srow != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) + cur[j].x);
+              v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + cur[j].y);
+              v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + cur[j].z);
+              v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + cur[j].w);
+            }
+          }
+          gc_store_row32(v, orow + col, nullptr);
         }
       }
       tc_fence_before_sync();

@@ -349,6 +349,171 @@ __global__ void __launch_bounds__(256) qk_norm_rope_bwd_kernel(const QKRopeParam
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Vectorised variants for the common layout (rotary over the whole head: 2 * half == D, half % 8 == 0):
+// LPH lanes share one (token, head); lane l owns elements [8l, 8l+8) of each half, so every access is a
+// 16-byte vector and a warp works on 32 / LPH heads at once.  Same math as the scalar kernels above.
+// ------------------------------------------------------------------------------------------------
+template <int LPH>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int o = LPH / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ void ld8(const bf16* p, float (&f)[8]) {
+  Vec8 v;
+  v.load(p);
+  v.to_float(f);
+}
+__device__ __forceinline__ void st8(bf16* p, const float (&f)[8]) {
+  Vec8 v;
+  v.from_float(f);
+  v.store(p);
+}
+
+template <int LPH>
+__global__ void __launch_bounds__(256) qk_norm_rope_fwd_vec_kernel(const QKRopeParams p) {
+  constexpr int GPW = 32 / LPH;                         // (token, head) items per warp
+  const int lane = threadIdx.x & 31, sub = lane % LPH, grp = lane / LPH;
+  const int warps = blockDim.x >> 5;
+  const int heads = p.H + p.HK;
+  const int64_t total = p.rows * heads;
+  const int64_t step = static_cast<int64_t>(gridDim.x) * warps * GPW;
+  for (int64_t base = (static_cast<int64_t>(blockIdx.x) * warps + (threadIdx.x >> 5)) * GPW; base < total; base += step) {
+    const int64_t item = base + grp;
+    const bool live = item < total;
+    const int64_t row = live ? item / heads : 0;
+    const int h = live ? static_cast<int>(item % heads) : 0;
+    const bool is_q = h < p.H;
+    const int hh = is_q ? h : h - p.H;
+    const bf16* in = (is_q ? p.q_in + row * p.ldq : p.k_in + row * p.ldk) + hh * p.D + sub * 8;
+    bf16* out = (is_q ? p.q_out + row * p.ldqo : p.k_out + row * p.ldko) + hh * p.D + sub * 8;
+    const bf16* w = is_q ? p.qw : p.kw;
+    const int pos = p.positions != nullptr ? p.positions[row] : static_cast<int>(row % p.T) + p.pos_offset;
+    float x1[8], x2[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x1[i] = x2[i] = 0.f;
+    if (live) { ld8(in, x1); ld8(in + p.half, x2); }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += x1[i] * x1[i] + x2[i] * x2[i];
+    float rstd = 1.f;
+    if (w != nullptr) rstd = rsqrtf(group_sum<LPH>(ss) / p.D + p.eps);
+    if (!live) continue;
+    float w1[8], w2[8], c[8], sn[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { w1[i] = w2[i] = c[i] = 1.f; sn[i] = 0.f; }
+    if (w != nullptr) { ld8(w + sub * 8, w1); ld8(w + p.half + sub * 8, w2); }
+    if (p.cos != nullptr) {
+      ld8(p.cos + static_cast<int64_t>(pos) * p.half + sub * 8, c);
+      ld8(p.sin + static_cast<int64_t>(pos) * p.half + sub * 8, sn);
+    }
+    float o1[8], o2[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float y1 = x1[i] * rstd * w1[i], y2 = x2[i] * rstd * w2[i];
+      o1[i] = y1 * c[i] - y2 * sn[i];
+      o2[i] = y1 * sn[i] + y2 * c[i];
+    }
+    st8(out, o1);
+    st8(out + p.half, o2);
+  }
+}
+
+template <int LPH>
+__global__ void __launch_bounds__(256) qk_norm_rope_bwd_vec_kernel(const QKRopeParams p) {
+  __shared__ float red[2][256];                           // [q|k][D <= 256], shared atomics at the end
+  constexpr int GPW = 32 / LPH;
+  const int lane = threadIdx.x & 31, sub = lane % LPH, grp = lane / LPH;
+  const int warps = blockDim.x >> 5;
+  const int heads = p.H + p.HK;
+  const int64_t total = p.rows * heads;
+  const int64_t step = static_cast<int64_t>(gridDim.x) * warps * GPW;
+  float dwq1[8], dwq2[8], dwk1[8], dwk2[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) dwq1[i] = dwq2[i] = dwk1[i] = dwk2[i] = 0.f;
+  for (int i = threadIdx.x; i < 512; i += blockDim.x) (&red[0][0])[i] = 0.f;
+  __syncthreads();
+
+  for (int64_t base = (static_cast<int64_t>(blockIdx.x) * warps + (threadIdx.x >> 5)) * GPW; base < total; base += step) {
+    const int64_t item = base + grp;
+    const bool live = item < total;
+    const int64_t row = live ? item / heads : 0;
+    const int h = live ? static_cast<int>(item % heads) : 0;
+    const bool is_q = h < p.H;
+    const int hh = is_q ? h : h - p.H;
+    const bf16* in = (is_q ? p.q_in + row * p.ldq : p.k_in + row * p.ldk) + hh * p.D + sub * 8;
+    const bf16* gin = (is_q ? p.dq + row * p.lddq : p.dk + row * p.lddk) + hh * p.D + sub * 8;
+    bf16* out = (is_q ? p.q_out + row * p.ldqo : p.k_out + row * p.ldko) + hh * p.D + sub * 8;
+    const bf16* w = is_q ? p.qw : p.kw;
+    const int pos = p.positions != nullptr ? p.positions[row] : static_cast<int>(row % p.T) + p.pos_offset;
+    float x1[8], x2[8], d1[8], d2[8], c[8], sn[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { x1[i] = x2[i] = d1[i] = d2[i] = 0.f; c[i] = 1.f; sn[i] = 0.f; }
+    if (live) {
+      ld8(gin, d1); ld8(gin + p.half, d2);
+      if (w != nullptr) { ld8(in, x1); ld8(in + p.half, x2); }
+      if (p.cos != nullptr) {
+        ld8(p.cos + static_cast<int64_t>(pos) * p.half + sub * 8, c);
+        ld8(p.sin + static_cast<int64_t>(pos) * p.half + sub * 8, sn);
+      }
+    }
+    float g1[8], g2[8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      g1[i] = d1[i] * c[i] + d2[i] * sn[i];               // transpose of the rotation
+      g2[i] = -d1[i] * sn[i] + d2[i] * c[i];
+      ss += x1[i] * x1[i] + x2[i] * x2[i];
+    }
+    if (w == nullptr) {
+      if (live) { st8(out, g1); st8(out + p.half, g2); }
+      continue;
+    }
+    const float rstd = rsqrtf(group_sum<LPH>(ss) / p.D + p.eps);
+    float w1[8], w2[8];
+    ld8(w + sub * 8, w1);
+    ld8(w + p.half + sub * 8, w2);
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      x1[i] *= rstd;
+      x2[i] *= rstd;
+      if (live) {
+        if (is_q) { dwq1[i] += g1[i] * x1[i]; dwq2[i] += g2[i] * x2[i]; }
+        else      { dwk1[i] += g1[i] * x1[i]; dwk2[i] += g2[i] * x2[i]; }
+      }
+      g1[i] *= w1[i];
+      g2[i] *= w2[i];
+      dot += g1[i] * x1[i] + g2[i] * x2[i];
+    }
+    dot = group_sum<LPH>(dot) / p.D;
+    if (!live) continue;
+    float o1[8], o2[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      o1[i] = rstd * (g1[i] - x1[i] * dot);
+      o2[i] = rstd * (g2[i] - x2[i] * dot);
+    }
+    st8(out, o1);
+    st8(out + p.half, o2);
+  }
+  if (p.dqw_partial == nullptr) return;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    atomicAdd(&red[0][sub * 8 + i], dwq1[i]);
+    atomicAdd(&red[0][p.half + sub * 8 + i], dwq2[i]);
+    atomicAdd(&red[1][sub * 8 + i], dwk1[i]);
+    atomicAdd(&red[1][p.half + sub * 8 + i], dwk2[i]);
+  }
+  __syncthreads();
+  for (int col = threadIdx.x; col < p.D; col += blockDim.x) {
+    p.dqw_partial[static_cast<int64_t>(blockIdx.x) * p.D + col] = red[0][col];
+    p.dkw_partial[static_cast<int64_t>(blockIdx.x) * p.D + col] = red[1][col];
+  }
+}
+
 }  // namespace ttcd
 
 using namespace ttcd;
@@ -405,6 +570,18 @@ TTCD_EXPORT int ttcd_rmsnorm_bwd(const void* dy, const void* s, const void* w, c
   return static_cast<int>(cudaGetLastError());
 }
 
+// The vectorised kernels need rotary over the whole head and 16-byte aligned rows / heads.
+static bool qk_vec_ok(const QKRopeParams& p) {
+  auto al = [](const void* q) { return q == nullptr || (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+  const int lph = p.half / 8;
+  if (2 * p.half != p.D || p.half % 8 != 0 || (lph != 4 && lph != 8 && lph != 16)) return false;
+  if ((p.qw == nullptr) != (p.kw == nullptr)) return false;      // group reductions must stay warp-uniform
+  if ((p.ldq | p.ldk | p.ldqo | p.ldko) % 8 != 0) return false;
+  if (p.dq != nullptr && (p.lddq | p.lddk) % 8 != 0) return false;
+  return al(p.q_in) && al(p.k_in) && al(p.q_out) && al(p.k_out) && al(p.dq) && al(p.dk) && al(p.qw) && al(p.kw) &&
+         al(p.cos) && al(p.sin);
+}
+
 static int qk_check(int D, int half) { return (D > 256 || half * 2 > D || half <= 0) ? TTCD_ERR_ARG : TTCD_OK; }
 
 // Forward: q_out/k_out = rope(headnorm(q_in/k_in)).  Row strides in elements.
@@ -422,6 +599,14 @@ TTCD_EXPORT int ttcd_qk_norm_rope_fwd(const void* q_in, long long ldq, const voi
   cudaStream_t st = static_cast<cudaStream_t>(stream_ptr);
   const long long items = rows * (H + HK);
   const unsigned grid = static_cast<unsigned>(std::min<long long>((items + 7) / 8, 148LL * 16));
+  if (qk_vec_ok(p)) {
+    const int lph = half / 8;
+    const unsigned vgrid = static_cast<unsigned>(std::min<long long>((items * lph / 32 + 7) / 8 + 1, 148LL * 16));
+    if (lph == 4) qk_norm_rope_fwd_vec_kernel<4><<<vgrid, 256, 0, st>>>(p);
+    else if (lph == 8) qk_norm_rope_fwd_vec_kernel<8><<<vgrid, 256, 0, st>>>(p);
+    else qk_norm_rope_fwd_vec_kernel<16><<<vgrid, 256, 0, st>>>(p);
+    return static_cast<int>(cudaGetLastError());
+  }
   if (half <= 32) qk_norm_rope_fwd_kernel<1><<<grid, 256, 0, st>>>(p);
   else if (half <= 64) qk_norm_rope_fwd_kernel<2><<<grid, 256, 0, st>>>(p);
   else qk_norm_rope_fwd_kernel<4><<<grid, 256, 0, st>>>(p);
@@ -445,6 +630,13 @@ TTCD_EXPORT int ttcd_qk_norm_rope_bwd(const void* dq, long long lddq, const void
   p.rows = rows; p.T = T; p.pos_offset = pos_offset; p.H = H; p.HK = HK; p.D = D; p.half = half; p.eps = eps;
   p.dqw_partial = dqw_partial; p.dkw_partial = dkw_partial;
   cudaStream_t st = static_cast<cudaStream_t>(stream_ptr);
+  if (qk_vec_ok(p)) {
+    const int lph = half / 8;
+    if (lph == 4) qk_norm_rope_bwd_vec_kernel<4><<<nblocks, 256, 0, st>>>(p);
+    else if (lph == 8) qk_norm_rope_bwd_vec_kernel<8><<<nblocks, 256, 0, st>>>(p);
+    else qk_norm_rope_bwd_vec_kernel<16><<<nblocks, 256, 0, st>>>(p);
+    return static_cast<int>(cudaGetLastError());
+  }
   if (half <= 32) qk_norm_rope_bwd_kernel<1><<<nblocks, 256, 0, st>>>(p);
   else if (half <= 64) qk_norm_rope_bwd_kernel<2><<<nblocks, 256, 0, st>>>(p);
   else qk_norm_rope_bwd_kernel<4><<<nblocks, 256, 0, st>>>(p);
