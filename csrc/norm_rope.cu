@@ -99,7 +99,7 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const bf16* __restrict
 // RMSNorm backward.  s: the (summed) pre-norm input saved by the forward.  dx = dnorm(dy) (+ dres).
 // dw partial sums are written per block to dw_partial[gridDim.x][D].
 template <int CHUNKS>
-__global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ s,
+__global__ void __launch_bounds__(256, (CHUNKS <= 4 ? 2 : 1)) rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ s,
                                                           const bf16* __restrict__ w, const float* __restrict__ rstd_in,
                                                           const bf16* __restrict__ dres, bf16* __restrict__ dx,
                                                           float* __restrict__ dw_partial, int64_t rows, int D) {
