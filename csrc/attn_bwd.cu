@@ -244,6 +244,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   const uint32_t t_dk = tmem_base, t_dv = tmem_base + 128;
   auto t_set = [&](int it) { return tmem_base + 256 + (it % C::NSETS) * C::SET_COLS; };  // S | dP_T | dP_S
   const bool healthy = (*abort_flag == 0);
+  // single window: P^T and dS^T go back into tensor memory over the S^T / dP^T columns they were computed from
+  // (bf16 pairs; the half of a warp pair keeps to its own 32 columns) and feed the dV / dK MMAs as TMEM A operands
+  const bool use_ts = !DUAL && p.a_in_tmem != 0;
 
   auto iter_head = [&](int it) { return kvh * G + it / nqb; };
   auto iter_row0 = [&](int it) { return (jb_lo + it % nqb) * 64; };
@@ -300,6 +303,21 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       auto issue_acc = [&](int it) {
         const bool st = iter_student(it);
         const uint32_t sq = slot_base(it), sdot = sq + C::TILE_BYTES, sdos = sq + 2 * C::TILE_BYTES;
+        if (use_ts) {
+          const uint32_t ts = t_set(it);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t a_off = 32 * (k / 2) + 8 * (k % 2);
+            umma_ts(t_dv, ts + a_off, umma_desc_sw128(sdot + k * 2048, C::ROW_REGION, 1024), idesc_acc, (it | k) != 0);
+          }
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t a_off = 64 + 32 * (k / 2) + 8 * (k % 2);
+            umma_ts(t_dk, ts + a_off, umma_desc_sw128(sq + k * 2048, C::ROW_REGION, 1024), idesc_acc, (it | k) != 0);
+          }
+          umma_commit(acc_done);
+          return;
+        }
 #pragma unroll
         for (int k = 0; k < 4; ++k)  // contraction over the 64 query rows
           umma_ss(t_dv, umma_desc_sw128(sbase + C::PT_OFF + k * 32, 16, 1024),
@@ -418,13 +436,20 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
             dkdv_elementwise<true, false>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, p.w_t, p.w_s, key_ok, ptp, psp, dsp);
         }
       }
+      if (use_ts) {
+        tmem_st16(ts, ptp);            // over this thread's own 32 S^T columns (already read)
+        tmem_st16(ts + 64, dsp);       // over its dP^T columns
+        tmem_st_wait();
+      }
       if (it >= 1) {
-        ok = wait_all(acc_done, (it - 1) & 1, 312);  // P / dS tiles are free again
+        ok = wait_all(acc_done, (it - 1) & 1, 312);  // P / dS tiles are free again (keeps the phase count in step)
         if (!ok) break;
       }
-      store_half_row_packed(smem + C::PT_OFF, krow, half, ptp);
-      if (DUAL && st) store_half_row_packed(smem + C::PS_OFF, krow, half, psp);
-      store_half_row_packed(smem + C::DS_OFF, krow, half, dsp);
+      if (!use_ts) {
+        store_half_row_packed(smem + C::PT_OFF, krow, half, ptp);
+        if (DUAL && st) store_half_row_packed(smem + C::PS_OFF, krow, half, psp);
+        store_half_row_packed(smem + C::DS_OFF, krow, half, dsp);
+      }
       vecs[((it + 1) & 1) * 256 + ctid] = next_stat;
       fence_proxy_async_smem();
       tc_fence_before_sync();

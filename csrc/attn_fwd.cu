@@ -17,6 +17,8 @@
 // (profiling/fused_dual_attn.py:34-241).
 #include "common.cuh"
 
+#include <cstdlib>
+
 namespace ttcd {
 
 constexpr int ATT_BM = 128;
@@ -33,6 +35,9 @@ struct AttnFwdParams {
   // context parallel: keys [0, halo_len) are the tail of the PREVIOUS rank's sequence shard and are read
   // straight from that rank's memory (rows halo_row0.. of its K/V buffers); keys >= halo_len are local
   int halo_len, halo_row0;
+  // P (bf16) is written back over the S columns it was computed from and read by the P.V MMA as a tensor-memory
+  // A operand instead of going through shared memory
+  int p_in_tmem;
 };
 
 template <int D>
@@ -173,11 +178,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       };
       auto issue_pv = [&](int i) {
         const uint32_t vslot = sbase + S::V_OFF + (i & 1) * S::KV_BYTES;
+        if (p.p_in_tmem) {
 #pragma unroll
-        for (int k = 0; k < ATT_BN / 16; ++k) {
-          const uint64_t ad = umma_desc_sw128(sbase + S::P_OFF + k * 32, 16, 1024);
-          const uint64_t bd = umma_desc_sw128(vslot + k * 2048, S::KV_REGION, 1024);
-          umma_ss(tmem_o, ad, bd, idesc_o, (i | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < ATT_BN / 16; ++k) {
+            const uint64_t bd = umma_desc_sw128(vslot + k * 2048, S::KV_REGION, 1024);
+            umma_ts(tmem_o, tmem_base + (i & 1) * ATT_BN + k * 8, bd, idesc_o, (i | k) != 0 ? 1u : 0u);
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < ATT_BN / 16; ++k) {
+            const uint64_t ad = umma_desc_sw128(sbase + S::P_OFF + k * 32, 16, 1024);
+            const uint64_t bd = umma_desc_sw128(vslot + k * 2048, S::KV_REGION, 1024);
+            umma_ss(tmem_o, ad, bd, idesc_o, (i | k) != 0 ? 1u : 0u);
+          }
         }
         umma_commit(pv_done);
       };
@@ -345,6 +358,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
       float psum = 0.f;
       uint8_t* prow = smem + S::P_OFF;
+      uint32_t ppk[ATT_BN / 2];
 #pragma unroll
       for (int c = 0; c < ATT_BN / 8; ++c) {
         float e[8];
@@ -353,15 +367,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
           e[j] = fast_exp2(__uint_as_float(sv[c * 8 + j]) - m_use);
           psum += e[j];
         }
-        uint4 pk;
-        pk.x = pack_bf16(e[0], e[1]);
-        pk.y = pack_bf16(e[2], e[3]);
-        pk.z = pack_bf16(e[4], e[5]);
-        pk.w = pack_bf16(e[6], e[7]);
-        *reinterpret_cast<uint4*>(prow + sw128_offset(row, c)) = pk;
+        ppk[4 * c] = pack_bf16(e[0], e[1]);
+        ppk[4 * c + 1] = pack_bf16(e[2], e[3]);
+        ppk[4 * c + 2] = pack_bf16(e[4], e[5]);
+        ppk[4 * c + 3] = pack_bf16(e[6], e[7]);
       }
       l_sum += psum;
-      fence_proxy_async_smem();   // generic-proxy smem writes -> visible to the MMA (async proxy)
+      if (p.p_in_tmem) {
+        tmem_st32(tmem_base + lane_addr + (i & 1) * ATT_BN, ppk);   // this lane's own S columns, already in registers
+        tmem_st_wait();
+      } else {
+#pragma unroll
+        for (int c = 0; c < ATT_BN / 8; ++c)
+          *reinterpret_cast<uint4*>(prow + sw128_offset(row, c)) =
+              make_uint4(ppk[4 * c], ppk[4 * c + 1], ppk[4 * c + 2], ppk[4 * c + 3]);
+        fence_proxy_async_smem();   // generic-proxy smem writes -> visible to the MMA (async proxy)
+      }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
@@ -446,6 +467,11 @@ TTCD_EXPORT int ttcd_attn_fwd_cp(const void* q, const void* k, const void* v, co
   p.w_s = window_s > 0 ? window_s : big;
   if (!dual) p.w_s = p.w_t;  // single-window mode runs phase A only, with the one window
   p.scale_log2 = scale * 1.4426950408889634f;
+  static const int p_in_tmem = [] {
+    const char* e = getenv("TTCD_ATTN_FWD_TS");
+    return (e != nullptr && e[0] == '0') ? 0 : 1;
+  }();
+  p.p_in_tmem = p_in_tmem;
   p.halo_len = halo_len;
   p.halo_row0 = halo_rows - halo_len;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
