@@ -2,9 +2,11 @@
 
 Rank r of a context-parallel group holds tokens [r*S_l, (r+1)*S_l).  Because every layer is windowed,
 the only remote data attention needs is the tail of the PREVIOUS rank's K/V (the last ``w_T - 1`` keys,
-rounded up to 128): the attention kernels read those key blocks straight from the previous rank's
-memory with plain TMA loads while they compute (no staging copy, no ring), and in backward the halo part
-of dK/dV is handed back to its owner through peer memory.  RoPE uses position offset r*S_l.  The
+rounded up to 128): those rows are pulled once per layer over NVLink into local memory by a plain-load
+kernel right before the attention kernel, whose TMA loads then treat them as key blocks in front of the shard
+(``TTCD_CP_HALO=direct`` lets the kernels' TMA loads address the previous rank's buffer themselves: no copy, but
+each query tile near the boundary then fetches its halo blocks across the link again, 2 GB instead of 33 MB per
+layer at 64K / 2 ranks); in backward the halo part of dK/dV is handed back to its owner through peer memory.  RoPE uses position offset r*S_l.  The
 fast-weight scan needs the exclusive prefix over ranks of each rank's summed update; labels are shifted
 before sharding so the shard boundary is handled by the data layout.
 
@@ -32,6 +34,8 @@ class _LayerBuffers:
     kv: object            # SymmetricBuffer: K then V, each [B, S_l, HK, D] bf16
     dkv: object           # SymmetricBuffer: halo dK then dV, each [B, halo, HK, D] bf16
     shape: tuple
+    halo_local: object = None   # [2, B, S, HK, D] bf16: local copy of the previous rank's K/V tail (tail rows only)
+    halo_ptrs: tuple = (0, 0)   # where the kernels find the halo keys / values (local copy, or the peer's buffer)
 
 
 class ContextParallel:
@@ -74,6 +78,38 @@ class ContextParallel:
         return self.rank * s_local
 
 
+import os as _os
+
+_HALO_MODE = _os.environ.get("TTCD_CP_HALO", "pull")      # pull (default) | direct
+
+
+def _pull_halo(lb: _LayerBuffers, cp: "ContextParallel", halo: int, B: int, S: int, HK: int, D: int, device):
+    """Copy the last ``halo`` keys/values of the previous rank's shard into local memory (one pass over NVLink,
+    plain peer loads) and return the local pointers.  Every query tile whose window reaches back over the
+    shard boundary reads them many times over; from local memory (and L2) instead of across the link."""
+    if not halo:
+        return 0, 0
+    if _HALO_MODE == "direct":
+        # the attention kernels' TMA loads address the previous rank's buffer themselves: no copy, but every
+        # query tile near the shard boundary fetches its halo blocks over the link again
+        n = B * S * HK * D
+        prev = cp.rank - 1
+        lb.halo_ptrs = (lb.kv.peer_ptrs[prev], lb.kv.peer_ptrs[prev] + n * 2)
+        return lb.halo_ptrs
+    if lb.halo_local is None:
+        lb.halo_local = torch.empty(2, B, S, HK, D, dtype=torch.bfloat16, device=device)
+    n = B * S * HK * D
+    prev = cp.rank - 1
+    cnt = halo * HK * D
+    for which in range(2):
+        for b in range(B):
+            off = (b * S + (S - halo)) * HK * D
+            nv.call("ttcd_peer_add", nv.i64(lb.halo_local[which].data_ptr() + off * 2),
+                    nv.i64(lb.kv.peer_ptrs[prev] + which * n * 2 + off * 2), nv.i64(cnt), nv.i32(0), nv.stream_ptr())
+    lb.halo_ptrs = (lb.halo_local[0].data_ptr(), lb.halo_local[1].data_ptr())
+    return lb.halo_ptrs
+
+
 class _CPAttention(torch.autograd.Function):
     """Sliding-window (dual) attention over a sequence shard with the halo read from the previous rank."""
 
@@ -89,9 +125,7 @@ class _CPAttention(torch.autograd.Function):
         v_sym.copy_(v)
         cp.barrier.sync(slot=0)                      # every rank's K/V of this layer is in place
         halo = cp.halo_len(S)
-        prev = cp.rank - 1
-        kh = lb.kv.peer_ptrs[prev] if halo else 0
-        vh = lb.kv.peer_ptrs[prev] + n * 2 if halo else 0
+        kh, vh = _pull_halo(lb, cp, halo, B, S, HK, D, q.device)
         qc = q.contiguous()
         o_t = torch.empty(B, S, H, D, dtype=torch.bfloat16, device=q.device)
         lse_t = torch.empty(B, H, S, dtype=torch.float32, device=q.device)
@@ -133,9 +167,8 @@ class _CPAttention(torch.autograd.Function):
 
         delta_t = delta(o_t, do_t)
         delta_s = delta(o_s, do_s) if dual else None
-        prev = cp.rank - 1
-        kh = lb.kv.peer_ptrs[prev] if halo else 0
-        vh = lb.kv.peer_ptrs[prev] + n * 2 if halo else 0
+        # the halo keys/values were copied into local memory by the forward pass
+        kh, vh = lb.halo_ptrs if halo else (0, 0)
         dq = torch.empty_like(qc)
         dk_ext = torch.empty(B, halo + S, HK, D, dtype=torch.bfloat16, device=qc.device)
         dv_ext = torch.empty_like(dk_ext)
