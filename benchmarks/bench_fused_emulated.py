@@ -103,6 +103,27 @@ def main():
         want = sum(g[:numel].float() for g in grads) / w_
         err = (out - want).abs().max().item()
         flops = 0.0
+    elif args.what == "adamw_push":
+        numel = m * k
+        master = torch.randn(numel, device="cuda")
+        grad = torch.randn(numel, device="cuda") * 0.01
+        m1, m2 = torch.zeros(numel, device="cuda"), torch.zeros(numel, device="cuda")
+        params = [torch.zeros(numel * w_, device="cuda", dtype=torch.bfloat16) for _ in range(w_)]    # every rank's flat buffer
+        coef = torch.ones(1, device="cuda")
+        want = master.clone()
+        g32 = grad.clone()
+
+        def run():
+            nv.call("ttcd_adamw_push", nv.ptr(master), nv.ptr(grad), nv.ptr(m1), nv.ptr(m2), ptrs(params), nv.i32(w_), nv.i64(0),
+                    nv.i64(numel), nv.f32(1e-3), nv.f32(0.9), nv.f32(0.95), nv.f32(1e-8), nv.f32(0.0), nv.f32(0.1),
+                    nv.f32(0.05 ** 0.5), nv.ptr(coef), nv.ptr(None), nv.stream_ptr())
+        run()
+        torch.cuda.synchronize()
+        # first step with these bias corrections: update = lr * (0.1 g / 0.1) / (sqrt(0.05 g^2 / 0.05) + eps) = lr * sign(g)
+        want = want - 1e-3 * g32 / (g32.abs() + 1e-8)
+        err = max((p_[:numel].float() - want).abs().max().item() for p_ in params)
+        ms = timeit(run)
+        flops = 0.0
     else:
         raise SystemExit(f"unknown --what {args.what}")
     torch.cuda.synchronize()

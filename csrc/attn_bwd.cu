@@ -48,6 +48,9 @@ struct AttnBwdParams {
   int halo_len, halo_row0;
   // single-window dQ kernel: keep Q and dO (loop-invariant A operands) in tensor memory
   int a_in_tmem;
+  // dV may be written into a wider row (the packed q|k|v gradient of a fused projection): row and batch strides
+  // in elements; 0 = contiguous [B, Tk, HK, D]
+  int64_t ld_dv, sb_dv;
 };
 
 // 32 accumulator columns of one TMEM lane -> 32 bf16 (one 64-byte half row) of a K-major SW128 tile
@@ -477,7 +480,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
           }
           if (store) {
             store_out32(p.dk + rowoff + half * COLS + c, a, p.scale);  // dS was kept unscaled
-            store_out32(p.dv + rowoff + half * COLS + c, v);
+            const int64_t voff = p.ld_dv != 0 ? static_cast<int64_t>(b) * p.sb_dv + static_cast<int64_t>(key) * p.ld_dv +
+                                                    static_cast<int64_t>(kvh) * D
+                                              : rowoff;
+            store_out32(p.dv + voff + half * COLS + c, v);
           }
         }
       }
@@ -835,6 +841,16 @@ TTCD_EXPORT int ttcd_attn_delta(const void* o, const void* d_o, float* delta, lo
 // Gradients of (dual-window) attention.  q/k/v strided as in ttcd_attn_fwd_cp; do_t/do_s contiguous
 // [B, Tq, H, D] (do_s null => single window); dq [B,Tq,H,D], dk/dv [B, halo_len + Tk_local, HK, D] bf16
 // contiguous: their first halo_len rows are the gradients of the previous rank's keys.
+// Row / batch strides (elements) of the dV output of the NEXT ttcd_attn_bwd / ttcd_attn_bwd_cp call of this thread;
+// consumed (reset to contiguous) by that call.
+static thread_local long long g_next_ld_dv = 0, g_next_sb_dv = 0;
+TTCD_EXPORT int ttcd_attn_bwd_set_dv_layout(long long ld_dv, long long sb_dv) {
+  if (ld_dv < 0 || sb_dv < 0 || ld_dv % 8 != 0 || sb_dv % 8 != 0) return TTCD_ERR_ARG;
+  g_next_ld_dv = ld_dv;
+  g_next_sb_dv = sb_dv;
+  return TTCD_OK;
+}
+
 TTCD_EXPORT int ttcd_attn_bwd_cp(const void* q, const void* k, const void* v, const void* k_halo, const void* v_halo,
                                  const void* do_t, const void* do_s, const float* lse_t, const float* lse_s,
                                  const float* delta_t, const float* delta_s, void* dq, void* dk, void* dv, int B, int Tq,
@@ -879,6 +895,9 @@ TTCD_EXPORT int ttcd_attn_bwd_cp(const void* q, const void* k, const void* v, co
     return (e != nullptr && e[0] == '0') ? 0 : 1;
   }();
   p.a_in_tmem = a_in_tmem;
+  p.ld_dv = g_next_ld_dv; p.sb_dv = g_next_sb_dv;
+  g_next_ld_dv = g_next_sb_dv = 0;
+  if (p.ld_dv != 0 && (reinterpret_cast<uintptr_t>(dv) & 15u)) return TTCD_ERR_ARG;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   if (D == 128) return dual ? launch_bwd<128, true>(m, p, B, stream) : launch_bwd<128, false>(m, p, B, stream);
   return dual ? launch_bwd<64, true>(m, p, B, stream) : launch_bwd<64, false>(m, p, B, stream);

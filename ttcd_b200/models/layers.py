@@ -164,9 +164,13 @@ class Attention(nn.Module):
         B = hidden_states.shape[0]
         q, k, v = _fused_qkv(self, hidden_states)
         T = q.shape[1]                      # all tokens: under tensor parallelism the input is a token shard
+        tags = [getattr(t, "_ttcd_grad_slab", None) for t in (q, k, v)]
         q = q.view(B, T, self.num_heads, self.head_dim)
         k = k.view(B, T, self.num_kv_heads, self.head_dim)
         v = v.view(B, T, self.num_kv_heads, self.head_dim)
+        for t, tag in zip((q, k, v), tags):
+            if tag is not None:
+                t._ttcd_grad_slab = tag     # the views keep pointing at the shared gradient buffer
         cos = sin = None
         if not self.use_nope:
             if max_seqlen is None:
@@ -302,6 +306,9 @@ def _fused_qkv(attn: Attention, x):
     if attn.q_proj.bias is None and x.is_cuda:
         out = ops_fused_linear(x, ws)
         if out is not None:
+            if torch.is_grad_enabled() and out[0].requires_grad:
+                from ..ops import cuda
+                cuda.GradSlab.tag(out, [w.shape[0] for w in ws])      # their gradients will meet in one buffer
             return out
     return (ops.linear(x, attn.q_proj.weight, attn.q_proj.bias),
             ops.linear(x, attn.k_proj.weight, attn.k_proj.bias),

@@ -109,6 +109,34 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, out_dtype=_BF16, alpha: float = 1.
     return out
 
 
+class GradSlab:
+    """Meeting point for the gradients of the column slices of one fused projection (q|k|v): the backward
+    kernels of the consumers write straight into one [rows, n_total] buffer, so the projection's backward
+    finds its packed gradient in place instead of assembling it with copies.  The forward tags the slices
+    (``tag``); whichever backward runs first allocates the buffer."""
+
+    def __init__(self, n_total: int):
+        self.n_total = n_total
+        self.buf = None
+
+    def get(self, rows: int, device) -> torch.Tensor:
+        if self.buf is None or self.buf.shape[0] != rows:
+            self.buf = torch.empty(rows, self.n_total, dtype=_BF16, device=device)
+        return self.buf
+
+    @staticmethod
+    def tag(tensors, widths):
+        slab, col = GradSlab(sum(widths)), 0
+        for t, w in zip(tensors, widths):
+            t._ttcd_grad_slab = (slab, col)
+            col += w
+        return slab
+
+
+def _slab_of(t):
+    return getattr(t, "_ttcd_grad_slab", None)
+
+
 class _MatMul(torch.autograd.Function):
     """Batched a @ b with native forward and backward."""
 
@@ -343,6 +371,8 @@ class _QKNormRope(torch.autograd.Function):
         B, T, H, D = q.shape
         HK = k.shape[2]
         rows = B * T
+        tq, tk = _slab_of(q), _slab_of(k)
+        ctx.slab = (tq[0], tq[1], tk[1]) if (tq is not None and tk is not None and tq[0] is tk[0] and HK > 0) else None
         if q.stride(-1) != 1 or q.stride(2) != D or k.stride(-1) != 1 or k.stride(2) != D:
             q, k = q.contiguous(), k.contiguous()
         ldq, ldk = q.stride(1), k.stride(1)
@@ -378,14 +408,23 @@ class _QKNormRope(torch.autograd.Function):
         B, T, H, HK, D, half, off, eps, ldq, ldk, qdt, kdt = ctx.meta
         rows = B * T
         dq, dk = dq.contiguous(), dk.contiguous()
-        dq_in = torch.empty(B, T, H, D, dtype=_BF16, device=q.device)
-        dk_in = torch.empty(B, T, HK, D, dtype=_BF16, device=q.device)
+        ldqo, ldko = H * D, HK * D
+        if ctx.slab is not None:
+            slab, cq, ck = ctx.slab
+            buf = slab.get(rows, q.device)
+            n_total = slab.n_total
+            dq_in = torch.as_strided(buf, (B, T, H, D), (T * n_total, n_total, D, 1), cq)
+            dk_in = torch.as_strided(buf, (B, T, HK, D), (T * n_total, n_total, D, 1), ck)
+            ldqo = ldko = n_total
+        else:
+            dq_in = torch.empty(B, T, H, D, dtype=_BF16, device=q.device)
+            dk_in = torch.empty(B, T, HK, D, dtype=_BF16, device=q.device)
         nblk = min(_SM_BLOCKS, (rows * (H + HK) + 7) // 8)
         has_w = qwb is not None
         dqw = torch.empty(nblk, D, dtype=torch.float32, device=q.device) if has_w else None
         dkw = torch.empty(nblk, D, dtype=torch.float32, device=q.device) if has_w else None
         nv.call("ttcd_qk_norm_rope_bwd", nv.ptr(dq), nv.i64(H * D), nv.ptr(dk), nv.i64(HK * D), nv.ptr(q), nv.i64(ldq),
-                nv.ptr(k), nv.i64(ldk), nv.ptr(dq_in), nv.i64(H * D), nv.ptr(dk_in), nv.i64(HK * D), nv.ptr(qwb),
+                nv.ptr(k), nv.i64(ldk), nv.ptr(dq_in), nv.i64(ldqo), nv.ptr(dk_in), nv.i64(ldko), nv.ptr(qwb),
                 nv.ptr(kwb), nv.ptr(cos), nv.ptr(sin), nv.ptr(pos), nv.ptr(dqw), nv.ptr(dkw), nv.i32(nblk),
                 nv.i64(rows), nv.i32(T), nv.i32(off), nv.i32(H), nv.i32(HK), nv.i32(D), nv.i32(half), nv.f32(eps),
                 nv.stream_ptr())
@@ -526,7 +565,7 @@ def attn_forward(q, k, v, window_t, window_s, scale, dual):
     return (q, k, v), o_t, o_s, lse_t, lse_s
 
 
-def attn_backward(q, k, v, o_t, o_s, lse_t, lse_s, do_t, do_s, window_t, window_s, scale):
+def attn_backward(q, k, v, o_t, o_s, lse_t, lse_s, do_t, do_s, window_t, window_s, scale, dv_slab=None):
     """dq, dk, dv of the (dual-window) attention; both outputs' gradients are summed in-kernel."""
     B, Tq, H, D = q.shape
     Tk, HK = k.shape[1], k.shape[2]
@@ -548,7 +587,14 @@ def attn_backward(q, k, v, o_t, o_s, lse_t, lse_s, do_t, do_s, window_t, window_
     delta_s = _delta(o_s, do_s) if dual else None
     dq = torch.empty(B, Tq, H, D, dtype=_BF16, device=q.device)
     dk = torch.empty(B, Tk, HK, D, dtype=_BF16, device=q.device)
-    dv = torch.empty(B, Tk, HK, D, dtype=_BF16, device=q.device)
+    if dv_slab is not None and nv.has("ttcd_attn_bwd_set_dv_layout") and (dv_slab[1] * 2) % 16 == 0:
+        slab, col = dv_slab
+        n_total = slab.n_total
+        buf = slab.get(B * Tk, q.device)
+        dv = torch.as_strided(buf, (B, Tk, HK, D), (Tk * n_total, n_total, D, 1), col)
+        nv.call("ttcd_attn_bwd_set_dv_layout", nv.i64(n_total), nv.i64(Tk * n_total))
+    else:
+        dv = torch.empty(B, Tk, HK, D, dtype=_BF16, device=q.device)
     nv.call("ttcd_attn_bwd", nv.ptr(q), nv.ptr(k), nv.ptr(v), nv.ptr(do_t), nv.ptr(do_s), nv.ptr(lse_t), nv.ptr(lse_s),
             nv.ptr(delta_t), nv.ptr(delta_s), nv.ptr(dq), nv.ptr(dk), nv.ptr(dv), nv.i32(B), nv.i32(Tq), nv.i32(Tk),
             nv.i32(H), nv.i32(HK), nv.i32(D), nv.i64(ldq), nv.i64(ldk), nv.i64(ldv), nv.i64(sq), nv.i64(sk), nv.i64(sv),
@@ -559,6 +605,7 @@ def attn_backward(q, k, v, o_t, o_s, lse_t, lse_s, do_t, do_s, window_t, window_
 class _Attention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, window_t, window_s, scale, dual):
+        ctx.v_slab = _slab_of(v)
         (qc, kc, vc), o_t, o_s, lse_t, lse_s = attn_forward(q, k, v, window_t, window_s, scale, dual)
         ctx.save_for_backward(qc, kc, vc, o_t, o_s, lse_t, lse_s)
         ctx.cfg = (window_t, window_s, scale, dual)
@@ -578,7 +625,8 @@ class _Attention(torch.autograd.Function):
             do_t = torch.zeros_like(o_t)
         if dual and do_s is None:
             do_s = torch.zeros_like(o_s)
-        dq, dk, dv = attn_backward(qc, kc, vc, o_t, o_s, lse_t, lse_s, do_t, do_s, window_t, window_s, scale)
+        dq, dk, dv = attn_backward(qc, kc, vc, o_t, o_s, lse_t, lse_s, do_t, do_s, window_t, window_s, scale,
+                                   dv_slab=ctx.v_slab)
         return dq, dk, dv, None, None, None, None
 
 
