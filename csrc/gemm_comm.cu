@@ -500,10 +500,13 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     const int ipu = 2 * (p.world - 1);
     const int total = my_units * ipu;
     bool dead = false;
+    // item i of this CTA: tile = i / ipu, then half-tile h (64 rows), then peer d: all peers of one half are summed
+    // in registers before the half is written, so the fp32 buffer is written once and never read back here
+    const int npeers = p.world - 1;
     auto issue = [&](int i) {     // thread rt == 0 only
       const int64_t u = blockIdx.x + static_cast<int64_t>(i / ipu) * gridDim.x;
       const int mb = static_cast<int>(u / p.tiles_n), nt = static_cast<int>(u % p.tiles_n);
-      const int d = 1 + (i % ipu) / 2, h = i & 1;
+      const int h = (i % ipu) / npeers, d = 1 + (i % ipu) % npeers;
       const int peer = (p.rank + d) % p.world;
       if (h == 0) {
         const int fidx = (p.rank * p.mbps + mb) * p.tiles_n + nt;
@@ -521,6 +524,11 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       return true;
     };
     int issued = 0;
+    float acc[16][8];
+#pragma unroll
+    for (int k = 0; k < 16; ++k)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[k][e] = 0.f;
     if (rt == 0 && total > 0) { if (issue(0)) issued = 1; }
     for (int i = 0; i < total; ++i) {
       asm volatile("bar.sync 1, 128;" ::: "memory");      // everyone is done with the slot item i+1 will use
@@ -528,33 +536,31 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       if (rt == 0 && !dead && i + 1 < total) { if (issue(i + 1)) issued = i + 2; }
       const int64_t u = blockIdx.x + static_cast<int64_t>(i / ipu) * gridDim.x;
       const int mb = static_cast<int>(u / p.tiles_n), nt = static_cast<int>(u % p.tiles_n);
-      const int d = 1 + (i % ipu) / 2, h = i & 1;
+      const int h = (i % ipu) / npeers, d = 1 + (i % ipu) % npeers;
+      const bool last_peer = d == npeers;
       if (!dead && !*s.abort_flag) {
         if (mbar_wait(s.copy(i & 1), (i >> 1) & 1u, s.abort_flag, 642)) {
           const uint8_t* src = stage_ptr + (i & 1) * HALF_BYTES;
           float* out_base = p.peer_sum + (static_cast<int64_t>(mb) * GC_BM + 64 * h) * p.N + static_cast<int64_t>(nt) * GC_BN;
-#pragma unroll 4
+#pragma unroll
           for (int k = 0; k < 16; ++k) {
             const int v = rt + 128 * k;
             const int row = v >> 5, c8 = v & 31;
             const uint4 raw = *reinterpret_cast<const uint4*>(src + (c8 >> 3) * 8192 + sw128_offset(row, c8 & 7));
             const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-            float f[8];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const float2 t = unpack_bf16(w[e]);
-              f[2 * e] = t.x;
-              f[2 * e + 1] = t.y;
+              acc[k][2 * e] += t.x;
+              acc[k][2 * e + 1] += t.y;
             }
-            float* dst = out_base + static_cast<int64_t>(row) * p.N + c8 * 8;
-            if (d > 1) {       // further peers accumulate onto the first one's values
-              const float4 a0 = *reinterpret_cast<const float4*>(dst);
-              const float4 a1 = *reinterpret_cast<const float4*>(dst + 4);
-              f[0] += a0.x; f[1] += a0.y; f[2] += a0.z; f[3] += a0.w;
-              f[4] += a1.x; f[5] += a1.y; f[6] += a1.z; f[7] += a1.w;
+            if (last_peer) {
+              float* dst = out_base + static_cast<int64_t>(row) * p.N + c8 * 8;
+              *reinterpret_cast<float4*>(dst) = make_float4(acc[k][0], acc[k][1], acc[k][2], acc[k][3]);
+              *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[k][4], acc[k][5], acc[k][6], acc[k][7]);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) acc[k][e] = 0.f;
             }
-            *reinterpret_cast<float4*>(dst) = make_float4(f[0], f[1], f[2], f[3]);
-            *reinterpret_cast<float4*>(dst + 4) = make_float4(f[4], f[5], f[6], f[7]);
           }
         }
       }
