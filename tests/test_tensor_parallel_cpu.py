@@ -140,3 +140,45 @@ def test_trainer_with_tensor_parallel_saves_full_tensors_and_resumes(tmp_path):
     full = {name: torch.empty(128, 64)}       # the checkpoint holds the un-sharded [intermediate, hidden] matrix
     dcp.load(full, checkpoint_id=str(tmp_path / "run" / "checkpoint" / "step-3"), no_dist=True)
     assert torch.isfinite(full[name]).all() and full[name].abs().sum() > 0
+
+
+def _vp_worker(rank, world, port, logits, labels, want_loss, want_grad, q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        from ttcd_b200.parallel.tensor import TensorParallel, vocab_parallel_cross_entropy
+        tp = TensorParallel(None, "cpu")
+        vl = logits.shape[1] // world
+        shard = logits[:, rank * vl:(rank + 1) * vl].clone().requires_grad_()
+        loss = vocab_parallel_cross_entropy(shard, labels, tp)
+        loss.backward()
+        q.put((rank, abs(float(loss) - want_loss), float((shard.grad - want_grad[:, rank * vl:(rank + 1) * vl]).abs().max())))
+        dist.destroy_process_group()
+    except Exception:  # pragma: no cover
+        import traceback
+        q.put((rank, "error", traceback.format_exc()))
+
+
+@pytest.mark.timeout(300)
+def test_vocab_parallel_cross_entropy_matches_dense():
+    torch.manual_seed(0)
+    logits = (torch.randn(24, 64) * 3).requires_grad_()
+    labels = torch.randint(0, 64, (24,))
+    labels[::5] = -100
+    loss = torch.nn.functional.cross_entropy(logits, labels, ignore_index=-100)
+    loss.backward()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    procs = [ctx.Process(target=_vp_worker, args=(r, 2, port, logits.detach(), labels, float(loss), logits.grad.clone(), q))
+             for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=200) for _ in procs]
+    for p in procs:
+        p.join(30)
+    for rank, e_loss, e_grad in results:
+        assert e_loss != "error", e_grad
+        assert e_loss < 1e-5 and e_grad < 1e-6

@@ -451,3 +451,48 @@ def configure(engine, degree: int) -> None:
     tp = TensorParallel(group, engine.device, max_rows_per_rank=rows, max_features=max(feat, 1024))
     shard_model(engine.model, tp)
     engine.tp = tp
+
+
+# ----------------------------------------------------------------------------------------- loss parallel
+class _VocabParallelCE(torch.autograd.Function):
+    """Cross entropy over logits whose vocabulary dimension is sharded across the group (the reference's
+    vocab-parallel path, fla/modules/fused_cross_entropy.py:205-212): every rank reduces its shard to a row
+    maximum / sum-exp and its share of the target logit; two small all-reduces combine them.  The default
+    tensor-parallel layout here keeps the LM head replicated and shards the tokens instead, so this is only
+    needed for column-parallel heads."""
+
+    @staticmethod
+    def forward(ctx, logits, labels, group, vocab_start, ignore_index):
+        lf = logits.float()
+        local_max = lf.max(dim=-1).values
+        gmax = local_max.clone()
+        dist.all_reduce(gmax, op=dist.ReduceOp.MAX, group=group)
+        ex = torch.exp(lf - gmax[:, None])
+        sumexp = ex.sum(-1)
+        dist.all_reduce(sumexp, group=group)
+        local = labels - vocab_start
+        mine = (local >= 0) & (local < logits.shape[-1]) & labels.ne(ignore_index)
+        tgt = torch.where(mine, lf.gather(-1, local.clamp(0, logits.shape[-1] - 1)[:, None]).squeeze(-1), torch.zeros_like(gmax))
+        dist.all_reduce(tgt, group=group)
+        valid = labels.ne(ignore_index)
+        n = valid.sum().clamp_min(1)
+        loss = ((torch.log(sumexp) + gmax - tgt) * valid).sum() / n
+        ctx.save_for_backward(ex / sumexp[:, None], local, mine, valid, n)
+        ctx.dtype = logits.dtype
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        probs, local, mine, valid, n = ctx.saved_tensors
+        grad = probs.clone()
+        rows = torch.nonzero(mine).squeeze(-1)
+        grad[rows, local[rows]] -= 1.0
+        grad = grad * (valid[:, None] * (g / n))
+        return grad.to(ctx.dtype), None, None, None, None
+
+
+def vocab_parallel_cross_entropy(logits_shard: torch.Tensor, labels: torch.Tensor, tp: TensorParallel | None = None,
+                                 ignore_index: int = -100) -> torch.Tensor:
+    """Mean CE of ``[rows, vocab / world]`` logit shards (rank r holds columns [r*V_l, (r+1)*V_l))."""
+    tp = tp or _CTX
+    return _VocabParallelCE.apply(logits_shard, labels, tp.group, tp.rank * logits_shard.shape[-1], ignore_index)
