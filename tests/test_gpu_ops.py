@@ -361,3 +361,24 @@ def test_fused_ttt_scan_matches_reference(b, T, with_beta):
         err = (a.float() - w).abs().max().item()
         ref_mag = w.abs().max().item() + 1e-6
         assert err / ref_mag < 6e-2, (n, err, ref_mag)
+
+
+def test_split_k_weight_gradient_gemm():
+    """Token dimension split into batched slices with fp32 partials == one long-K GEMM."""
+    from ttcd_b200.ops import cuda
+    torch.manual_seed(5)
+    T, n_out, k_in = 8192, 1024, 2048
+    assert cuda._split_k_factor(n_out, k_in, T) > 1
+    wide = (torch.randn(T, n_out + 512, device="cuda") * 0.1).bfloat16()
+    g = wide[:, :n_out]                                   # a column slice of a wider gradient buffer (row stride > width)
+    x = (torch.randn(T, k_in, device="cuda") * 0.1).bfloat16()
+    got = cuda.gemm_wgrad(g, x)
+    want = g.float().t() @ x.float()
+    assert got.shape == (n_out, k_in)
+    assert (got.float() - want).abs().max().item() < 2e-2 * want.abs().max().item()
+    lin = torch.nn.Linear(k_in, n_out, bias=False, device="cuda", dtype=torch.bfloat16)
+    xx = x.clone().requires_grad_()
+    y = cuda.linear(xx, lin.weight)
+    y.backward(wide[:, :n_out].contiguous())
+    ref = wide[:, :n_out].float().t() @ x.float()
+    assert (lin.weight.grad.float() - ref).abs().max().item() < 2e-2 * ref.abs().max().item()

@@ -180,6 +180,39 @@ def matmul(a, b):
     return _MatMul.apply(a, b)
 
 
+def _split_k_factor(M: int, N: int, K: int, sms: int = 148) -> int:
+    """Number of K slices for a weight-gradient GEMM (M, N = weight dims, K = tokens): the output has few tiles
+    (64-192 for this model) and would leave a third of the 148 SMs idle or run a mostly empty second wave."""
+    tiles = -(-M // 128) * -(-N // (256 if N >= 256 else 128))
+    if tiles >= 4 * sms:
+        return 1
+    best, best_eff = 1, tiles / (-(-tiles // sms) * sms)
+    for s_ in range(2, 17):
+        if K % (s_ * 64) or K // s_ < 2048:
+            continue
+        eff = tiles * s_ / (-(-tiles * s_ // sms) * sms)
+        if eff > best_eff + 0.02:
+            best, best_eff = s_, eff
+        if best_eff >= 0.95:
+            break
+    return best
+
+
+def gemm_wgrad(g: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """dW[N_out, K_in] = g[T, N_out]^T @ x[T, K_in] with the token dimension split into slices that run as a
+    batched GEMM (fp32 partials, summed once): fills the machine when the weight has few output tiles."""
+    T, n_out = g.shape
+    k_in = x.shape[1]
+    s_ = _split_k_factor(n_out, k_in, T)
+    if s_ == 1 or g.stride(1) != 1 or x.stride(1) != 1:
+        return gemm(g.transpose(0, 1), x).view(n_out, k_in)
+    ts = T // s_
+    ga = torch.as_strided(g, (s_, n_out, ts), (ts * g.stride(0), 1, g.stride(0)), g.storage_offset())      # [S, N_out, Ts] view of g^T
+    xa = torch.as_strided(x, (s_, ts, k_in), (ts * x.stride(0), x.stride(0), 1), x.storage_offset())
+    part = gemm(ga, xa, out_dtype=torch.float32)                                                             # [S, N_out, K_in]
+    return part.sum(0).to(_BF16)
+
+
 class _Linear(torch.autograd.Function):
     """y = x @ W^T for one or several weights that share x (one GEMM when they form a slab)."""
 
@@ -220,7 +253,7 @@ class _Linear(torch.autograd.Function):
         gx = None
         if ctx.needs_input_grad[0]:
             gx = gemm(g, w).view(ctx.x_shape)
-        gw_all = gemm(g.transpose(0, 1), x2).view(n_total, x2.shape[1])
+        gw_all = gemm_wgrad(g, x2)
         gws, row = [], 0
         for n in ctx.splits:
             gws.append(gw_all[row:row + n])
