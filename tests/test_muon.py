@@ -103,3 +103,51 @@ def test_two_ranks_match_one():
         assert worst != "error", keys
         assert worst[0] < 2e-3, worst
         assert keys, "Muon momentum missing from the optimizer state"
+
+
+def _ddp_worker(rank, world, port, ids, want, q):
+    import os
+    import torch.distributed as dist
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        eng = TrainEngine(IPTTCDv9Config(**KW), EngineConfig(dtype=torch.float32, lr=0.02, weight_decay=0.1, max_norm=1.0, seed=5,
+                                                             activation_checkpoint="none", replicate=True), device="cpu")
+        from ttcd_b200.parallel.replicated import ReplicatedDataParallel
+        assert isinstance(eng.sdp, ReplicatedDataParallel)
+        for _ in range(2):
+            eng.sdp.zero_grad()
+            eng.forward_backward(ids[rank:rank + 1])
+            eng.sdp.step(0.02)
+        got = {n: p.detach() for n, p in eng.model.named_parameters()}
+        q.put((rank, max(((got[n] - want[n]).abs().max().item(), n) for n in got), []))
+        dist.destroy_process_group()
+    except Exception:  # pragma: no cover
+        import traceback
+        q.put((rank, "error", traceback.format_exc()))
+
+
+def test_replicated_data_parallel_matches_single_process():
+    """DDP fallback: all-reduced flat gradient buckets + full optimizer on every rank == one process on the whole batch."""
+    import torch.multiprocessing as mp
+    torch.manual_seed(2)
+    ids = torch.randint(0, 128, (2, 64))
+    eng = TrainEngine(IPTTCDv9Config(**KW), EngineConfig(dtype=torch.float32, lr=0.02, weight_decay=0.1, max_norm=1.0, seed=5,
+                                                         activation_checkpoint="none"), device="cpu")
+    for _ in range(2):
+        eng.sdp.zero_grad()
+        eng.forward_backward(ids)
+        eng.sdp.step(0.02)
+    want = {n: p.detach().clone() for n, p in eng.model.named_parameters()}
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_ddp_worker, args=(r, 2, port, ids, want, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(30)
+    for rank, worst, extra in results:
+        assert worst != "error", extra
+        assert worst[0] < 1e-4, worst

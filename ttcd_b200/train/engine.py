@@ -25,6 +25,7 @@ class EngineConfig:
     eps: float = 1e-15
     weight_decay: float = 0.1
     max_norm: float | None = 1.0
+    replicate: bool = False                   # DDP-style replicated optimizer state + gradient all-reduce (fallback path)
     activation_offload: bool = False          # saved activations -> pinned host memory on a side stream
     activation_checkpoint: str = "full"       # full | none | everyN (checkpoint every Nth block) | ttt (TTT blocks only)
     dtype: torch.dtype = torch.bfloat16
@@ -96,7 +97,10 @@ class TrainEngine:
                 raise NotImplementedError("Muon needs whole matrices; it is not available with tensor parallelism")
             process_group = False           # every rank optimises its own weight shards
         multi = process_group is not False and dist.is_initialized() and dist.get_world_size(process_group) > 1
-        self.sdp = ShardedDataParallel(
+        runtime = ShardedDataParallel
+        if self.cfg.replicate and multi:
+            from ..parallel.replicated import ReplicatedDataParallel as runtime
+        self.sdp = runtime(
             self.model, blocks=list(self.model.model.layers), process_group=process_group if multi else False,
             lr=self.cfg.lr, betas=self.cfg.betas, eps=self.cfg.eps, weight_decay=self.cfg.weight_decay,
             max_norm=self.cfg.max_norm, param_dtype=self.cfg.dtype, muon=self.cfg.enable_muon,

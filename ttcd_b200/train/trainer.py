@@ -198,7 +198,8 @@ def main(job_config: JobConfig) -> None:
                         max_norm=tr.max_norm, activation_checkpoint=_ac_mode(job_config), dtype=dtype,
                         skip_nan_inf=tr.skip_nan_inf, seed=tr.seed, enable_muon=opt.enable_muon,
                         muon_momentum=opt.muon_momentum, tensor_parallel=tp, context_parallel=cp,
-                        activation_offload=job_config.activation_offload.mode not in ("none", "", None))
+                        activation_offload=job_config.activation_offload.mode not in ("none", "", None),
+                        replicate=(tr.data_parallel_shard_degree == 1 and tr.data_parallel_replicate_degree not in (0, 1)))
     engine = TrainEngine(model_config, ecfg, device=device)
     model = engine.model
     n_params = count_params(model, exclude_embedding=True)
