@@ -783,22 +783,32 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   }
 }
 
-// delta[b,h,t] = sum_d dO[b,t,h,d] * O[b,t,h,d]; one warp per (b,t,h)
+// delta[b,h,t] = sum_d dO[b,t,h,d] * O[b,t,h,d]; D / 8 lanes per (b,t,h) row, 16-byte loads
 __global__ void __launch_bounds__(256) attn_delta_kernel(const bf16* __restrict__ o, const bf16* __restrict__ d_o,
                                                          float* __restrict__ delta, int64_t B, int T, int H, int D) {
-  const int lane = threadIdx.x & 31;
-  const int64_t item = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (item >= B * T * H) return;
-  const int h = static_cast<int>(item % H);
-  const int64_t bt = item / H;
+  const int lpr = D / 8;                                   // lanes per row: 16 (D = 128) or 8 (D = 64)
+  const int rpw = 32 / lpr;                                // rows per warp
+  const int lane = threadIdx.x & 31, sub = lane % lpr, grp = lane / lpr;
+  const int64_t warp_id = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t item = warp_id * rpw + grp;
+  const bool live = item < B * T * H;
   float acc = 0.f;
-  for (int d = lane * 2; d < D; d += 64) {
-    const float2 a = unpack_bf16(*reinterpret_cast<const uint32_t*>(o + item * D + d));
-    const float2 g = unpack_bf16(*reinterpret_cast<const uint32_t*>(d_o + item * D + d));
-    acc += a.x * g.x + a.y * g.y;
+  if (live) {
+    const uint4 a = *reinterpret_cast<const uint4*>(o + item * D + sub * 8);
+    const uint4 g = *reinterpret_cast<const uint4*>(d_o + item * D + sub * 8);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = unpack_bf16(aw[i]), y = unpack_bf16(gw[i]);
+      acc += x.x * y.x + x.y * y.y;
+    }
   }
-  acc = warp_sum(acc);
-  if (lane == 0) delta[((bt / T) * H + h) * T + (bt % T)] = acc;
+  for (int off = lpr / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (live && sub == 0) {
+    const int h = static_cast<int>(item % H);
+    const int64_t bt = item / H;
+    delta[((bt / T) * H + h) * T + (bt % T)] = acc;
+  }
 }
 
 struct BwdMaps {
@@ -831,9 +841,11 @@ static int launch_bwd(const BwdMaps& m, const AttnBwdParams& p, int B, cudaStrea
 TTCD_EXPORT int ttcd_attn_delta(const void* o, const void* d_o, float* delta, long long B, int T, int H, int D,
                                 void* stream_ptr) {
   using namespace ttcd;
-  if (D % 2 != 0 || B <= 0) return TTCD_ERR_ARG;
+  if ((D != 64 && D != 128) || B <= 0) return TTCD_ERR_ARG;
   const long long items = B * T * H;
-  attn_delta_kernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
+  const long long rows_per_block = 8 * (32 / (D / 8));
+  attn_delta_kernel<<<static_cast<unsigned>((items + rows_per_block - 1) / rows_per_block), 256, 0,
+                      static_cast<cudaStream_t>(stream_ptr)>>>(
       static_cast<const bf16*>(o), static_cast<const bf16*>(d_o), delta, B, T, H, D);
   return static_cast<int>(cudaGetLastError());
 }
