@@ -208,7 +208,7 @@ def run_ours(args):
 def run_reference(args):
     ref_root = ROOT / "baseline" / "_ref"
     if not (ref_root / "custom_models").is_dir():
-        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed (pip install --target baseline/_ref /root/reference)"}))
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed (pip install --no-deps --target baseline/_ref <reference checkout>)"}))
         return
     sys.path.insert(0, str(ref_root))
     for k in [k for k in sys.modules if k.split(".")[0] in ("custom_models", "flame", "fla")]:

@@ -1,6 +1,6 @@
 """Turn an ``.ncu-rep`` file into the short text table kept under ``profiles/``.
 
-    python benchmarks/ncu_summary.py gpurun_out/prof.ncu-rep [--all-stalls]
+    python benchmarks/ncu_summary.py prof.ncu-rep [--all-stalls]
 
 Runs ``ncu -i <file> --page raw --csv`` (works without a GPU) and prints, per captured launch: duration, DRAM
 bytes and throughput, tensor-pipe and SM throughput, registers / block / grid / shared memory, and the warp

@@ -207,7 +207,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   auto sdp_full = [&](int s) { return bars + 8u * (1 + C::NSLOTS + s); };
   const uint32_t ew_done = bars + 8u * (1 + C::NSLOTS + C::NSETS);
   const uint32_t acc_done = ew_done + 8u;
-  const uint32_t a_ready = acc_done + 8u;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::BAR_OFF + C::NBARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* vecs = reinterpret_cast<float*>(smem + C::VEC_OFF);
