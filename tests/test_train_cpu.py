@@ -206,3 +206,61 @@ def test_ipttt_fast_weights_persist_across_incremental_calls():
     assert (cache.ttt_get(0)[2][0] - model.model.layers[0].mlp.down_proj.weight).abs().max() > 1e-4
     out = model.generate(ids, max_new_tokens=4)
     assert out.shape == (1, 33)
+
+
+# ------------------------------------------------------------------------------------------- checkpoint policy / metrics
+def test_checkpoint_policies_keep_k_weights_only_export_and_trigger(tmp_path):
+    import time as _time
+    import torch.distributed.checkpoint as dcp
+    from ttcd_b200.train import trainer
+    from ttcd_b200.train.checkpoint import checkpoint_keys
+    # keep_latest_k purges older steps; the last save is weights-only in the export dtype with raw keys
+    _train(tmp_path, 4, ["--checkpoint.interval", "1", "--checkpoint.keep_latest_k", "2", "--checkpoint.last_save_model_weights_only",
+                         "--checkpoint.export_dtype", "bfloat16"])
+    folder = tmp_path / "run" / "checkpoint"
+    for _ in range(50):                       # the purge runs on a background thread
+        if sorted(p.name for p in folder.iterdir()) == ["step-3", "step-4"]:
+            break
+        _time.sleep(0.1)
+    assert sorted(p.name for p in folder.iterdir()) == ["step-3", "step-4"]
+    last = checkpoint_keys(str(folder / "step-4"))
+    assert "model.layers.0.mlp.gate_proj.weight" in last and not any(k.startswith("optimizer") for k in last)
+    t = {"model.layers.0.mlp.gate_proj.weight": torch.empty(128, 64, dtype=torch.bfloat16)}
+    dcp.load(t, checkpoint_id=str(folder / "step-4"), no_dist=True)
+    full = checkpoint_keys(str(folder / "step-3"))
+    assert any(k.startswith("optimizer.") for k in full) and any(k.startswith("model.model.") for k in full)
+    # external trigger: SIGUSR1 (or the trigger file) asks for one save at the next step boundary
+    trainer._on_sigusr1(None, None)
+    assert trainer.external_save_requested(0) is True
+    assert trainer.external_save_requested(0) is False
+    open(trainer.SAVE_TRIGGER_FILE, "w").close()
+    assert trainer.external_save_requested(0) is True and not os.path.exists(trainer.SAVE_TRIGGER_FILE)
+
+
+def test_seed_checkpoint_and_initial_load(tmp_path):
+    from ttcd_b200.train.checkpoint import checkpoint_keys
+    seed_dir = tmp_path / "seed"
+    seed_dir.mkdir()
+    _train(seed_dir, 1, ["--checkpoint.create_seed_checkpoint"])
+    step0 = seed_dir / "run" / "checkpoint" / "step-0"
+    keys = checkpoint_keys(str(step0))
+    assert "model.embeddings.weight" in keys and not any(k.startswith("optimizer") for k in keys)     # raw keys, weights only
+    # a fresh run that starts from it trains normally
+    run2 = tmp_path / "ft"
+    run2.mkdir()
+    _train(run2, 2, ["--checkpoint.initial_load_path", str(step0)])
+    assert (run2 / "run" / "checkpoint" / "step-2" / ".metadata").is_file()
+
+
+def test_flop_and_param_counts():
+    from ttcd_b200.models import TransformerConfig, TransformerForCausalLM
+    from ttcd_b200.train.metrics import count_params, get_num_flop_per_token, get_peak_flops
+    cfg = TransformerConfig(hidden_size=32, num_hidden_layers=2, num_heads=4, num_kv_heads=2, intermediate_size=64, vocab_size=64,
+                            tie_word_embeddings=False, fuse_cross_entropy=False)
+    model = TransformerForCausalLM(cfg)
+    total = sum(p.numel() for p in model.parameters())
+    assert count_params(model, exclude_embedding=False) == total
+    assert count_params(model, exclude_embedding=True) == total - 64 * 32
+    n = count_params(model)
+    assert get_num_flop_per_token(n, cfg, 128) == 6 * n + 12 * 2 * 4 * 8 * 128
+    assert get_peak_flops("NVIDIA B200") == 2.25e15
