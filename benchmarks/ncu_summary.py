@@ -53,4 +53,7 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except BrokenPipeError:      # output piped into head
+        pass
