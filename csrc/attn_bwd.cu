@@ -51,6 +51,12 @@ struct AttnBwdParams {
   // dV may be written into a wider row (the packed q|k|v gradient of a fused projection): row and batch strides
   // in elements; 0 = contiguous [B, Tk, HK, D]
   int64_t ld_dv, sb_dv;
+  // dK/dV kernel, dual window through ONE softmax: inside the student window P_S = r * P_T with the per-row ratio
+  // r = exp(lse_T - lse_S), so the two gradient streams collapse into dO' = dO_T + r dO_S and delta' = delta_T +
+  // r delta_S there, and outside it only the teacher stream exists.  combine != 0: `delta_s` holds delta', the
+  // second dO tensor map addresses dO', and every block step uses either (dO', delta', keys inside the student
+  // window) or (dO_T, delta_T, keys outside it); blocks that straddle the window edge take both steps.
+  int combine;
 };
 
 // 32 accumulator columns of one TMEM lane -> 32 bf16 (one 64-byte half row) of a K-major SW128 tile
@@ -96,7 +102,8 @@ template <bool MASKED, bool STUDENT>
 __device__ __forceinline__ void dkdv_elementwise(const uint32_t (&sv)[32], const uint32_t (&dpt)[32],
                                                  const uint32_t (&dps)[32], const float* stats, float scale_log2,
                                                  int key, int qpos0, int w_t, int w_s, bool key_ok,
-                                                 uint32_t (&ptp)[16], uint32_t (&psp)[16], uint32_t (&dsp)[16]) {
+                                                 uint32_t (&ptp)[16], uint32_t (&psp)[16], uint32_t (&dsp)[16],
+                                                 int lo_t = 0) {
 #pragma unroll
   for (int c = 0; c < 32; c += 4) {
     const float4 nl = *reinterpret_cast<const float4*>(stats + c);
@@ -117,7 +124,7 @@ __device__ __forceinline__ void dkdv_elementwise(const uint32_t (&sv)[32], const
       pt[j] = ex2(fmaf(s, scale_log2, nls[j]));
       if (MASKED) {
         const int qpos = qpos0 + c + j;
-        if (!(key_ok && key <= qpos && key > qpos - w_t)) pt[j] = 0.f;
+        if (!(key_ok && key <= qpos - lo_t && key > qpos - w_t)) pt[j] = 0.f;
       }
       d[j] = pt[j] * (__uint_as_float(dpt[c + j]) - dls[j]);
       if (STUDENT) {
@@ -223,7 +230,21 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   const int row_hi = min(p.Tq - 1, n0 + 127 + p.w_t - 1 - off);
   const int jb_lo = row_lo / 64;
   const int nqb = row_hi >= row_lo ? (row_hi / 64 - jb_lo + 1) : 0;
-  const int n_iters = nqb * G;
+  // combined dual mode: query blocks [jb_lo, jb1) only hold pairs inside the student window, (jb2, ..] only pairs
+  // outside it, [jb1, jb2] straddle its edge and take two steps (student part, then teacher-only part)
+  const bool combine = !DUAL && p.combine != 0;
+  int pre = nqb, nb = 0, jb1 = 0;
+  if (combine && nqb > 0) {
+    auto fdiv = [](int a, int d) { return a >= 0 ? a / d : -((-a + d - 1) / d); };
+    const int first_t = fdiv(n0 + p.w_s - off - 63 + 63, 64);        // ceil((n0 + w_s - off - 63) / 64)
+    const int last_s = fdiv(n0 + 126 + p.w_s - off, 64);
+    jb1 = min(max(first_t, jb_lo), jb_lo + nqb);
+    const int jb2 = min(last_s, jb_lo + nqb - 1);
+    pre = jb1 - jb_lo;
+    nb = max(0, jb2 - jb1 + 1);
+  }
+  const int steps = nqb + nb;
+  const int n_iters = steps * G;
 
   if (threadIdx.x == 0) {
     *abort_flag = ((sbase & 1023u) != 0) ? 1 : 0;
@@ -250,8 +271,21 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   // (bf16 pairs; the half of a warp pair keeps to its own 32 columns) and feed the dV / dK MMAs as TMEM A operands
   const bool use_ts = !DUAL && p.a_in_tmem != 0;
 
-  auto iter_head = [&](int it) { return kvh * G + it / nqb; };
-  auto iter_row0 = [&](int it) { return (jb_lo + it % nqb) * 64; };
+  auto iter_head = [&](int it) { return kvh * G + it / steps; };
+  auto iter_block = [&](int it) {          // query block of step `it`
+    const int s = it % steps;
+    if (s < pre) return jb_lo + s;
+    if (s < pre + 2 * nb) return jb1 + (s - pre) / 2;
+    return jb_lo + s - nb;
+  };
+  auto iter_inner = [&](int it) {          // combined mode: 1 = student part (dO', delta'), 0 = teacher-only part
+    if (!combine) return 0;
+    const int s = it % steps;
+    if (s < pre) return 1;
+    if (s < pre + 2 * nb) return ((s - pre) & 1) ? 0 : 1;
+    return 0;
+  };
+  auto iter_row0 = [&](int it) { return iter_block(it) * 64; };
   auto iter_student = [&](int it) { return DUAL && (iter_row0(it) + off < n0 + 127 + p.w_s); };
   auto slot_base = [&](int it) { return sbase + C::RING_OFF + (it % C::NSLOTS) * C::NTILES * C::TILE_BYTES; };
 
@@ -268,7 +302,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
 #pragma unroll
         for (int d = 0; d < C::DB; ++d) {
           tma_load_3d(base + d * C::ROW_REGION, &tma_q, tiles_full(slot), h * D + d * 64, r0, b);
-          tma_load_3d(base + C::TILE_BYTES + d * C::ROW_REGION, &tma_dot, tiles_full(slot), h * D + d * 64, r0, b);
+          tma_load_3d(base + C::TILE_BYTES + d * C::ROW_REGION, iter_inner(it) ? &tma_dos : &tma_dot, tiles_full(slot),
+                      h * D + d * 64, r0, b);
           if (DUAL && st)
             tma_load_3d(base + 2 * C::TILE_BYTES + d * C::ROW_REGION, &tma_dos, tiles_full(slot), h * D + d * 64, r0, b);
         }
@@ -397,7 +432,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       const int64_t idx = (static_cast<int64_t>(b) * p.H + iter_head(it)) * p.Tq + row;
       if (row >= p.Tq) return (which == 0 || which == 2) ? -INFINITY : 0.f;  // p = 0 past the end
       if (which == 0) return -p.lse_t[idx] * LOG2E;
-      if (which == 1) return p.delta_t[idx];
+      if (which == 1) return iter_inner(it) ? p.delta_s[idx] : p.delta_t[idx];
       if (!DUAL || !iter_student(it)) return 0.f;
       return which == 2 ? -p.lse_s[idx] * LOG2E : p.delta_s[idx];
     };
@@ -431,6 +466,16 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
             dkdv_elementwise<false, true>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, p.w_t, p.w_s, key_ok, ptp, psp, dsp);
           else
             dkdv_elementwise<true, true>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, p.w_t, p.w_s, key_ok, ptp, psp, dsp);
+        } else if (combine) {
+          // one softmax (the teacher's): keys inside the student window with (dO', delta'), keys outside it with
+          // (dO_T, delta_T); visible pairs are  qpos - hi < key <= qpos - lo
+          const int inner = iter_inner(it);
+          const int lo = inner ? 0 : p.w_s, hi = inner ? p.w_s : p.w_t;
+          const bool full = (n0 + 127 <= qlo_b - lo) && (n0 > qhi_b - hi) && (n0 + 127 < p.Tk);
+          if (full)
+            dkdv_elementwise<false, false>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, hi, hi, key_ok, ptp, psp, dsp, lo);
+          else
+            dkdv_elementwise<true, false>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, hi, hi, key_ok, ptp, psp, dsp, lo);
         } else {
           if (full_t)
             dkdv_elementwise<false, false>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, p.w_t, p.w_s, key_ok, ptp, psp, dsp);
@@ -834,6 +879,30 @@ static int launch_bwd(const BwdMaps& m, const AttnBwdParams& p, int B, cudaStrea
   return static_cast<int>(cudaGetLastError());
 }
 
+// Dual window with the dK/dV kernel in combined mode (single-window pipeline, one softmax) and the dual dQ kernel.
+template <int D>
+static int launch_bwd_combined(const BwdMaps& m, const CUtensorMap& dop64, const AttnBwdParams& p, const float* delta_p,
+                               int B, cudaStream_t stream) {
+  auto k1 = attn_bwd_dkdv_kernel<D, false>;
+  auto k2 = attn_bwd_dq_kernel<D, true>;
+  constexpr int smem1 = DkdvCfg<D, false>::TOTAL, smem2 = DqCfg<D, true>::TOTAL;
+  static bool configured = false;
+  if (!configured) {
+    TTCD_CUDA_CHECK(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1));
+    TTCD_CUDA_CHECK(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2));
+    configured = true;
+  }
+  AttnBwdParams p1 = p;
+  p1.combine = 1;
+  p1.delta_s = delta_p;
+  dim3 g1((p.Tk + 127) / 128, p.HK, B);
+  k1<<<g1, BWD_THREADS, smem1, stream>>>(m.q64, m.k128, m.v128, m.dot64, dop64, m.kh128, m.vh128, p1);
+  TTCD_CUDA_CHECK(cudaGetLastError());
+  dim3 g2(p.H, (p.Tq + 127) / 128, B);
+  k2<<<g2, BWD_THREADS, smem2, stream>>>(m.q128, m.k64, m.v64, m.dot128, m.dos128, m.kh64, m.vh64, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
 }  // namespace ttcd
 
 // delta = rowsum(dO * O): o, d_o contiguous [B, T, H, D]; delta [B, H, T] fp32.
@@ -855,6 +924,15 @@ TTCD_EXPORT int ttcd_attn_delta(const void* o, const void* d_o, float* delta, lo
 // Row / batch strides (elements) of the dV output of the NEXT ttcd_attn_bwd / ttcd_attn_bwd_cp call of this thread;
 // consumed (reset to contiguous) by that call.
 static thread_local long long g_next_ld_dv = 0, g_next_sb_dv = 0;
+// Combined gradient stream of the NEXT dual-window call of this thread: dO' = dO_T + r dO_S ([B, Tq, H, D] bf16) and
+// delta' = delta_T + r delta_S ([B, H, Tq] fp32) with r = exp(lse_T - lse_S); consumed by that call.
+static thread_local const void* g_next_dop = nullptr;
+static thread_local const float* g_next_delta_p = nullptr;
+TTCD_EXPORT int ttcd_attn_bwd_set_combined(const void* do_combined, const float* delta_combined) {
+  g_next_dop = do_combined;
+  g_next_delta_p = delta_combined;
+  return TTCD_OK;
+}
 TTCD_EXPORT int ttcd_attn_bwd_set_dv_layout(long long ld_dv, long long sb_dv) {
   if (ld_dv < 0 || sb_dv < 0 || ld_dv % 8 != 0 || sb_dv % 8 != 0) return TTCD_ERR_ARG;
   g_next_ld_dv = ld_dv;
@@ -908,8 +986,20 @@ TTCD_EXPORT int ttcd_attn_bwd_cp(const void* q, const void* k, const void* v, co
   p.a_in_tmem = a_in_tmem;
   p.ld_dv = g_next_ld_dv; p.sb_dv = g_next_sb_dv;
   g_next_ld_dv = g_next_sb_dv = 0;
+  p.combine = 0;
+  const void* dop = g_next_dop;
+  const float* delta_p = g_next_delta_p;
+  g_next_dop = nullptr;
+  g_next_delta_p = nullptr;
   if (p.ld_dv != 0 && (reinterpret_cast<uintptr_t>(dv) & 15u)) return TTCD_ERR_ARG;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  if (dual && dop != nullptr && delta_p != nullptr) {
+    CUtensorMap dop64;
+    rc = make_tmap_bf16_3d(&dop64, dop, qi, Tq, B, qi, qi * Tq, 64, 64);
+    if (rc != TTCD_OK) return rc;
+    return D == 128 ? launch_bwd_combined<128>(m, dop64, p, delta_p, B, stream)
+                    : launch_bwd_combined<64>(m, dop64, p, delta_p, B, stream);
+  }
   if (D == 128) return dual ? launch_bwd<128, true>(m, p, B, stream) : launch_bwd<128, false>(m, p, B, stream);
   return dual ? launch_bwd<64, true>(m, p, B, stream) : launch_bwd<64, false>(m, p, B, stream);
 }

@@ -6,6 +6,8 @@ validated on the host before a launch (the kernels do no bounds recovery).
 """
 from __future__ import annotations
 
+import os
+
 import math
 
 import torch
@@ -598,6 +600,9 @@ def attn_forward(q, k, v, window_t, window_s, scale, dual):
     return (q, k, v), o_t, o_s, lse_t, lse_s
 
 
+_BWD_COMBINE = os.environ.get("TTCD_ATTN_BWD_COMBINE", "1") != "0"
+
+
 def attn_backward(q, k, v, o_t, o_s, lse_t, lse_s, do_t, do_s, window_t, window_s, scale, dv_slab=None):
     """dq, dk, dv of the (dual-window) attention; both outputs' gradients are summed in-kernel."""
     B, Tq, H, D = q.shape
@@ -620,6 +625,13 @@ def attn_backward(q, k, v, o_t, o_s, lse_t, lse_s, do_t, do_s, window_t, window_
     delta_s = _delta(o_s, do_s) if dual else None
     dq = torch.empty(B, Tq, H, D, dtype=_BF16, device=q.device)
     dk = torch.empty(B, Tk, HK, D, dtype=_BF16, device=q.device)
+    if dual and _BWD_COMBINE and nv.has("ttcd_attn_bwd_set_combined"):
+        # inside the student window P_S = r P_T (r = exp(lse_T - lse_S), per row): fold the student gradient stream
+        # into the teacher's so that the dK/dV kernel runs its single-window pipeline
+        r = torch.exp(lse_t - lse_s)                                            # [B, H, Tq] fp32
+        do_comb = torch.addcmul(do_t.float(), do_s.float(), r.transpose(1, 2).unsqueeze(-1)).to(_BF16)
+        delta_comb = torch.addcmul(delta_t, delta_s, r)
+        nv.call("ttcd_attn_bwd_set_combined", nv.ptr(do_comb), nv.ptr(delta_comb))
     if dv_slab is not None and nv.has("ttcd_attn_bwd_set_dv_layout") and (dv_slab[1] * 2) % 16 == 0:
         slab, col = dv_slab
         n_total = slab.n_total
