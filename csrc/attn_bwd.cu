@@ -152,7 +152,7 @@ template <bool MASKED, bool STUDENT>
 __device__ __forceinline__ void dq_elementwise(const uint32_t (&sv)[32], const uint32_t (&dpt)[32],
                                                const uint32_t (&dps)[32], float scale_log2, float nlse_t, float del_t,
                                                float nlse_s, float del_s, int qpos, int key0, int w_t, int w_s,
-                                               uint32_t (&dsp)[16]) {
+                                               uint32_t (&dsp)[16], int lo_t = 0) {
 #pragma unroll
   for (int c = 0; c < 32; c += 2) {
     float d[2];
@@ -161,7 +161,7 @@ __device__ __forceinline__ void dq_elementwise(const uint32_t (&sv)[32], const u
       const float s = __uint_as_float(sv[c + j]);
       const int key = key0 + c + j;
       float pt = ex2(fmaf(s, scale_log2, nlse_t));
-      if (MASKED && !(key <= qpos && key > qpos - w_t)) pt = 0.f;
+      if (MASKED && !(key <= qpos - lo_t && key > qpos - w_t)) pt = 0.f;
       d[j] = pt * (__uint_as_float(dpt[c + j]) - del_t);
       if (STUDENT) {
         float ps = ex2(fmaf(s, scale_log2, nlse_s));
@@ -595,9 +595,32 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   const int key_hi = min(qhi, p.Tk - 1);
   const int key_lo = max(0, qlo - p.w_t + 1);
   const int blk_lo = key_lo / 64;
-  const int n_iters = key_hi / 64 - blk_lo + 1;
-  auto iter_key0 = [&](int it) { return (blk_lo + it) * 64; };
-  auto iter_student = [&](int it) { return DUAL && (iter_key0(it) + 63 > qlo - p.w_s); };
+  const int nblk = key_hi / 64 - blk_lo + 1;
+  // combined dual mode (see AttnBwdParams::combine): key blocks [blk_lo, kb1) hold only teacher-only pairs,
+  // (kb2, ..] only pairs inside the student window, [kb1, kb2] straddle its edge and take two steps
+  const bool combine = DUAL && p.combine != 0;
+  int pre = nblk, nb = 0, kb1 = 0;
+  if (combine) {
+    auto fdiv = [](int a, int d) { return a >= 0 ? a / d : -((-a + d - 1) / d); };
+    kb1 = min(max(fdiv(qlo - p.w_s + 1, 64), blk_lo), blk_lo + nblk);
+    const int kb2 = min(fdiv(qhi - p.w_s, 64), blk_lo + nblk - 1);
+    pre = kb1 - blk_lo;
+    nb = max(0, kb2 - kb1 + 1);
+  }
+  const int n_iters = nblk + nb;
+  auto iter_block = [&](int it) {
+    if (it < pre) return blk_lo + it;
+    if (it < pre + 2 * nb) return kb1 + (it - pre) / 2;
+    return blk_lo + it - nb;
+  };
+  auto iter_inner = [&](int it) {          // 1 = pairs inside the student window (dO', delta'), 0 = teacher-only pairs
+    if (!combine) return 0;
+    if (it < pre) return 0;
+    if (it < pre + 2 * nb) return (it - pre) & 1;
+    return 1;
+  };
+  auto iter_key0 = [&](int it) { return iter_block(it) * 64; };
+  auto iter_student = [&](int it) { return DUAL && !combine && (iter_key0(it) + 63 > qlo - p.w_s); };
   auto slot_base = [&](int it) { return sbase + C::RING_OFF + (it % C::NSLOTS) * 2 * C::KV_BYTES; };
 
   if (threadIdx.x == 0) {
@@ -670,8 +693,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
           for (int k = 0; k < D / 16; ++k) {
             const uint32_t qo = (k / 4) * C::Q_REGION + (k % 4) * 32;
             const uint32_t ko = (k / 4) * C::KV_REGION + (k % 4) * 32;
-            umma_ss(ts + 64, umma_desc_sw128(sbase + C::DOT_OFF + qo, 16, 1024), umma_desc_sw128(sv + ko, 16, 1024),
-                    idesc_s, k != 0);
+            umma_ss(ts + 64, umma_desc_sw128(sbase + (iter_inner(it) ? C::DOS_OFF : C::DOT_OFF) + qo, 16, 1024),
+                    umma_desc_sw128(sv + ko, 16, 1024), idesc_s, k != 0);
           }
         }
         if (DUAL && st) {
@@ -786,6 +809,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
             dq_elementwise<false, true>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, key0, p.w_t, p.w_s, dsp);
           else
             dq_elementwise<true, true>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, key0, p.w_t, p.w_s, dsp);
+        } else if (combine) {
+          const int inner = iter_inner(it);
+          const int lo = inner ? 0 : p.w_s, hi = inner ? p.w_s : p.w_t;
+          const float del = inner ? del_s : del_t;            // delta' was passed in place of delta_S
+          const bool full = (kb0 + 63 <= qlo - lo) && (kb0 > qhi - hi);
+          if (full)
+            dq_elementwise<false, false>(sv, dpt, dps, p.scale_log2, nlse_t, del, nlse_s, del_s, qpos, key0, hi, hi, dsp, lo);
+          else
+            dq_elementwise<true, false>(sv, dpt, dps, p.scale_log2, nlse_t, del, nlse_s, del_s, qpos, key0, hi, hi, dsp, lo);
         } else {
           if (full_t)
             dq_elementwise<false, false>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, key0, p.w_t, p.w_s, dsp);
@@ -881,8 +913,8 @@ static int launch_bwd(const BwdMaps& m, const AttnBwdParams& p, int B, cudaStrea
 
 // Dual window with the dK/dV kernel in combined mode (single-window pipeline, one softmax) and the dual dQ kernel.
 template <int D>
-static int launch_bwd_combined(const BwdMaps& m, const CUtensorMap& dop64, const AttnBwdParams& p, const float* delta_p,
-                               int B, cudaStream_t stream) {
+static int launch_bwd_combined(const BwdMaps& m, const CUtensorMap& dop64, const CUtensorMap& dop128, const AttnBwdParams& p,
+                               const float* delta_p, int B, cudaStream_t stream) {
   auto k1 = attn_bwd_dkdv_kernel<D, false>;
   auto k2 = attn_bwd_dq_kernel<D, true>;
   constexpr int smem1 = DkdvCfg<D, false>::TOTAL, smem2 = DqCfg<D, true>::TOTAL;
@@ -899,7 +931,7 @@ static int launch_bwd_combined(const BwdMaps& m, const CUtensorMap& dop64, const
   k1<<<g1, BWD_THREADS, smem1, stream>>>(m.q64, m.k128, m.v128, m.dot64, dop64, m.kh128, m.vh128, p1);
   TTCD_CUDA_CHECK(cudaGetLastError());
   dim3 g2(p.H, (p.Tq + 127) / 128, B);
-  k2<<<g2, BWD_THREADS, smem2, stream>>>(m.q128, m.k64, m.v64, m.dot128, m.dos128, m.kh64, m.vh64, p);
+  k2<<<g2, BWD_THREADS, smem2, stream>>>(m.q128, m.k64, m.v64, m.dot128, dop128, m.kh64, m.vh64, p1);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -994,11 +1026,12 @@ TTCD_EXPORT int ttcd_attn_bwd_cp(const void* q, const void* k, const void* v, co
   if (p.ld_dv != 0 && (reinterpret_cast<uintptr_t>(dv) & 15u)) return TTCD_ERR_ARG;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   if (dual && dop != nullptr && delta_p != nullptr) {
-    CUtensorMap dop64;
+    CUtensorMap dop64, dop128;
     rc = make_tmap_bf16_3d(&dop64, dop, qi, Tq, B, qi, qi * Tq, 64, 64);
+    if (rc == TTCD_OK) rc = make_tmap_bf16_3d(&dop128, dop, qi, Tq, B, qi, qi * Tq, 64, 128);
     if (rc != TTCD_OK) return rc;
-    return D == 128 ? launch_bwd_combined<128>(m, dop64, p, delta_p, B, stream)
-                    : launch_bwd_combined<64>(m, dop64, p, delta_p, B, stream);
+    return D == 128 ? launch_bwd_combined<128>(m, dop64, dop128, p, delta_p, B, stream)
+                    : launch_bwd_combined<64>(m, dop64, dop128, p, delta_p, B, stream);
   }
   if (D == 128) return dual ? launch_bwd<128, true>(m, p, B, stream) : launch_bwd<128, false>(m, p, B, stream);
   return dual ? launch_bwd<64, true>(m, p, B, stream) : launch_bwd<64, false>(m, p, B, stream);
