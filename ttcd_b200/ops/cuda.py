@@ -600,7 +600,7 @@ def attn_forward(q, k, v, window_t, window_s, scale, dual):
     return (q, k, v), o_t, o_s, lse_t, lse_s
 
 
-_BWD_COMBINE = os.environ.get("TTCD_ATTN_BWD_COMBINE", "1") != "0"
+_BWD_COMBINE = os.environ.get("TTCD_ATTN_BWD_COMBINE", "0") == "1"      # opt-in until validated on every shape
 
 
 def attn_backward(q, k, v, o_t, o_s, lse_t, lse_s, do_t, do_s, window_t, window_s, scale, dv_slab=None):
