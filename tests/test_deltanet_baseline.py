@@ -63,3 +63,19 @@ def test_lse_combination_equals_dual_window_attention():
         t, s = ops.lse_dual_window_attention(q, k, v, wt, ws)
         torch.testing.assert_close(s, s_ref, rtol=1e-5, atol=1e-5)
         torch.testing.assert_close(t, t_ref, rtol=1e-4, atol=1e-5)
+
+
+def test_dual_window_backward_through_one_softmax():
+    """The per-row ratio identity behind the combined backward kernels equals autograd of the two-softmax op."""
+    torch.manual_seed(1)
+    B, T, H, HK, D = 2, 80, 4, 2, 8
+    q = torch.randn(B, T, H, D, dtype=torch.float64, requires_grad=True)
+    k = torch.randn(B, T, HK, D, dtype=torch.float64, requires_grad=True)
+    v = torch.randn(B, T, HK, D, dtype=torch.float64, requires_grad=True)
+    for wt, ws in ((48, 16), (64, 24)):
+        o_t, o_s = ref.dual_window_attention(q, k, v, wt, ws)
+        g_t, g_s = torch.randn_like(o_t), torch.randn_like(o_s)
+        want = torch.autograd.grad([o_t, o_s], [q, k, v], [g_t, g_s])
+        got = ref.dual_window_attention_backward_combined(q.detach(), k.detach(), v.detach(), g_t, g_s, wt, ws)
+        for a, b in zip(got, want):
+            torch.testing.assert_close(a, b.float(), rtol=1e-4, atol=1e-4)

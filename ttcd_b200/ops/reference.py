@@ -455,3 +455,39 @@ def delta_rule_chunked(q, k, v, beta, scale=None, l2norm: bool = True, chunk: in
     o = torch.stack(outs, dim=2)                           # [B, H, n, C, Dv]
     o = o.permute(0, 2, 3, 1, 4).reshape(B, n * chunk, H, -1)[:, :T]
     return o.to(dtype)
+
+
+def dual_window_attention_backward_combined(q, k, v, d_o_t, d_o_s, window_teacher, window_student, scale=None):
+    """Gradients of ``dual_window_attention`` through ONE softmax (the statement the combined backward kernels
+    implement).  Inside the student window P_S = r * P_T with the per-row ratio r = exp(lse_T - lse_S), so the two
+    incoming gradient streams collapse into dO' = dO_T + r dO_S and delta' = delta_T + r delta_S there; outside it
+    only the teacher stream exists.  q [B,T,H,D], k/v [B,T,HK,D]; returns (dq, dk, dv) in fp32."""
+    B, T, H, D = q.shape
+    HK = k.shape[2]
+    g = H // HK
+    scale = D ** -0.5 if scale is None else scale
+    qf, kf, vf = q.float(), k.float().repeat_interleave(g, dim=2), v.float().repeat_interleave(g, dim=2)
+    s = torch.einsum("bqhd,bkhd->bhqk", qf, kf) * scale
+    i = torch.arange(T, device=q.device)[:, None]
+    j = torch.arange(T, device=q.device)[None, :]
+    in_t = (j <= i) & (j > i - window_teacher)
+    in_s = (j <= i) & (j > i - window_student)
+    lse_t = torch.logsumexp(s.masked_fill(~in_t, float("-inf")), -1)
+    lse_s = torch.logsumexp(s.masked_fill(~in_s, float("-inf")), -1)
+    p_t = torch.exp(s - lse_t[..., None]).masked_fill(~in_t, 0.0)
+    o_t = torch.einsum("bhqk,bkhd->bqhd", p_t, vf)
+    o_s = torch.einsum("bhqk,bkhd->bqhd", torch.exp(s - lse_s[..., None]).masked_fill(~in_s, 0.0), vf)
+    r = torch.exp(lse_t - lse_s)                                            # [B, H, T]
+    do_t, do_s = d_o_t.float(), d_o_s.float()
+    do_c = do_t + r.transpose(1, 2).unsqueeze(-1) * do_s
+    delta_t = (do_t * o_t).sum(-1).transpose(1, 2)
+    delta_c = delta_t + r * (do_s * o_s).sum(-1).transpose(1, 2)
+    dp_t = torch.einsum("bqhd,bkhd->bhqk", do_t, vf)
+    dp_c = torch.einsum("bqhd,bkhd->bhqk", do_c, vf)
+    only_t = in_t & ~in_s
+    ds = p_t * (torch.where(in_s, dp_c - delta_c[..., None], torch.zeros_like(dp_c))
+                + torch.where(only_t, dp_t - delta_t[..., None], torch.zeros_like(dp_t))) * scale
+    dq = torch.einsum("bhqk,bkhd->bqhd", ds, kf)
+    dk = torch.einsum("bhqk,bqhd->bkhd", ds, qf).view(B, T, HK, g, D).sum(3)
+    dv = (torch.einsum("bhqk,bqhd->bkhd", p_t * in_s, do_c) + torch.einsum("bhqk,bqhd->bkhd", p_t * only_t, do_t))
+    return dq, dk, dv.view(B, T, HK, g, D).sum(3)
