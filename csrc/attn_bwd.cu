@@ -887,6 +887,60 @@ __global__ void __launch_bounds__(256) attn_delta_kernel(const bf16* __restrict_
   }
 }
 
+// One pass over both outputs and their gradients for the combined dual backward: delta_t = rowsum(dO_T * O_T),
+// r = exp(lse_T - lse_S), delta' = delta_t + r * rowsum(dO_S * O_S), dO' = dO_T + r * dO_S (bf16).
+__global__ void __launch_bounds__(256) attn_combine_kernel(const bf16* __restrict__ o_t, const bf16* __restrict__ do_t,
+                                                           const bf16* __restrict__ o_s, const bf16* __restrict__ do_s,
+                                                           const float* __restrict__ lse_t, const float* __restrict__ lse_s,
+                                                           float* __restrict__ delta_t, float* __restrict__ delta_p,
+                                                           bf16* __restrict__ do_p, int64_t B, int T, int H, int D) {
+  const int lpr = D / 8;
+  const int rpw = 32 / lpr;
+  const int lane = threadIdx.x & 31, sub = lane % lpr, grp = lane / lpr;
+  const int64_t warp_id = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t item = warp_id * rpw + grp;
+  const bool live = item < B * T * H;
+  float acc_t = 0.f, acc_s = 0.f, r = 0.f;
+  int64_t stat = 0;
+  float gt[8], gs[8];
+  if (live) {
+    const int h = static_cast<int>(item % H);
+    const int64_t bt = item / H;
+    stat = ((bt / T) * H + h) * T + (bt % T);
+    r = __expf(lse_t[stat] - lse_s[stat]);
+    const int64_t off = item * D + sub * 8;
+    const uint4 a = *reinterpret_cast<const uint4*>(o_t + off);
+    const uint4 g = *reinterpret_cast<const uint4*>(do_t + off);
+    const uint4 c = *reinterpret_cast<const uint4*>(o_s + off);
+    const uint4 e = *reinterpret_cast<const uint4*>(do_s + off);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
+    const uint32_t cw[4] = {c.x, c.y, c.z, c.w}, ew[4] = {e.x, e.y, e.z, e.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = unpack_bf16(aw[i]), y = unpack_bf16(gw[i]);
+      const float2 u = unpack_bf16(cw[i]), w = unpack_bf16(ew[i]);
+      acc_t += x.x * y.x + x.y * y.y;
+      acc_s += u.x * w.x + u.y * w.y;
+      gt[2 * i] = y.x; gt[2 * i + 1] = y.y;
+      gs[2 * i] = w.x; gs[2 * i + 1] = w.y;
+    }
+    uint4 outv;
+    outv.x = pack_bf16(fmaf(r, gs[0], gt[0]), fmaf(r, gs[1], gt[1]));
+    outv.y = pack_bf16(fmaf(r, gs[2], gt[2]), fmaf(r, gs[3], gt[3]));
+    outv.z = pack_bf16(fmaf(r, gs[4], gt[4]), fmaf(r, gs[5], gt[5]));
+    outv.w = pack_bf16(fmaf(r, gs[6], gt[6]), fmaf(r, gs[7], gt[7]));
+    *reinterpret_cast<uint4*>(do_p + off) = outv;
+  }
+  for (int off = lpr / 2; off > 0; off >>= 1) {
+    acc_t += __shfl_xor_sync(0xffffffffu, acc_t, off);
+    acc_s += __shfl_xor_sync(0xffffffffu, acc_s, off);
+  }
+  if (live && sub == 0) {
+    delta_t[stat] = acc_t;
+    delta_p[stat] = fmaf(r, acc_s, acc_t);
+  }
+}
+
 struct BwdMaps {
   CUtensorMap q64, q128, k64, k128, v64, v128, dot64, dot128, dos64, dos128, kh64, kh128, vh64, vh128;
 };
@@ -947,6 +1001,22 @@ TTCD_EXPORT int ttcd_attn_delta(const void* o, const void* d_o, float* delta, lo
   attn_delta_kernel<<<static_cast<unsigned>((items + rows_per_block - 1) / rows_per_block), 256, 0,
                       static_cast<cudaStream_t>(stream_ptr)>>>(
       static_cast<const bf16*>(o), static_cast<const bf16*>(d_o), delta, B, T, H, D);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Inputs of the combined dual backward in one pass: o_*, do_* contiguous [B, T, H, D] bf16, lse_* [B, H, T] fp32;
+// writes delta_t, delta_p ([B, H, T] fp32) and do_p ([B, T, H, D] bf16).
+TTCD_EXPORT int ttcd_attn_bwd_combine(const void* o_t, const void* do_t, const void* o_s, const void* do_s,
+                                      const float* lse_t, const float* lse_s, float* delta_t, float* delta_p, void* do_p,
+                                      long long B, int T, int H, int D, void* stream_ptr) {
+  using namespace ttcd;
+  if ((D != 64 && D != 128) || B <= 0) return TTCD_ERR_ARG;
+  const long long items = B * T * H;
+  const long long rows_per_block = 8 * (32 / (D / 8));
+  attn_combine_kernel<<<static_cast<unsigned>((items + rows_per_block - 1) / rows_per_block), 256, 0,
+                        static_cast<cudaStream_t>(stream_ptr)>>>(
+      static_cast<const bf16*>(o_t), static_cast<const bf16*>(do_t), static_cast<const bf16*>(o_s),
+      static_cast<const bf16*>(do_s), lse_t, lse_s, delta_t, delta_p, static_cast<bf16*>(do_p), B, T, H, D);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -92,3 +92,43 @@ def test_strided_qkv_views_and_packed_sequences():
     o_r.backward(g.float())
     _check(o, o_r, "o", atol=8e-3, rtol=1e-2)
     _check(qkv.grad, f.grad, "dqkv")
+
+
+@pytest.mark.parametrize("combine", [True, False])
+@pytest.mark.parametrize("B,T,H,HK,D,WT,WS", [(2, 900, 4, 2, 128, 384, 128), (1, 1300, 2, 1, 64, 512, 192)])
+def test_dual_backward_both_formulations(monkeypatch, combine, B, T, H, HK, D, WT, WS):
+    """The one-softmax (combined gradient stream) and the two-softmax dual backward against the same oracle."""
+    from ttcd_b200.ops import cuda
+    monkeypatch.setattr(cuda, "_BWD_COMBINE", combine)
+    q, k, v = _inputs(B, T, H, HK, D)
+    o_t, o_s = ops.dual_window_attention(q, k, v, WT, WS)
+    g_t, g_s = torch.randn_like(o_t), torch.randn_like(o_s)
+    torch.autograd.backward([o_t, o_s], [g_t, g_s])
+    qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+    r_t, r_s = ref.dual_window_attention(qf, kf, vf, WT, WS)
+    torch.autograd.backward([r_t, r_s], [g_t.float(), g_s.float()])
+    _check(q.grad, qf.grad, "dq")
+    _check(k.grad, kf.grad, "dk")
+    _check(v.grad, vf.grad, "dv")
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_combine_kernel_matches_torch(D):
+    """delta_T, delta' = delta_T + r delta_S and dO' = dO_T + r dO_S (r = exp(lse_T - lse_S)) from one kernel."""
+    from ttcd_b200._native import call, i32, i64, ptr, stream_ptr
+    B, T, H = 2, 333, 3
+    mk = lambda: torch.randn(B, T, H, D, device=DEV).to(BF)  # noqa: E731
+    o_t, do_t, o_s, do_s = mk(), mk(), mk(), mk()
+    lse_s = torch.randn(B, H, T, device=DEV)
+    lse_t = lse_s + torch.rand(B, H, T, device=DEV) * 2
+    delta_t, delta_p = torch.empty(B, H, T, device=DEV), torch.empty(B, H, T, device=DEV)
+    do_p = torch.empty_like(do_t)
+    call("ttcd_attn_bwd_combine", ptr(o_t), ptr(do_t), ptr(o_s), ptr(do_s), ptr(lse_t), ptr(lse_s), ptr(delta_t), ptr(delta_p),
+         ptr(do_p), i64(B), i32(T), i32(H), i32(D), stream_ptr())
+    r = torch.exp(lse_t - lse_s)
+    want_t = (o_t.float() * do_t.float()).sum(-1).transpose(1, 2)
+    want_s = (o_s.float() * do_s.float()).sum(-1).transpose(1, 2)
+    torch.testing.assert_close(delta_t, want_t, rtol=1e-4, atol=1e-3)
+    torch.testing.assert_close(delta_p, want_t + r * want_s, rtol=1e-4, atol=2e-3)
+    want_do = do_t.float() + r.transpose(1, 2).unsqueeze(-1) * do_s.float()
+    torch.testing.assert_close(do_p.float(), want_do, rtol=1e-2, atol=1e-2)

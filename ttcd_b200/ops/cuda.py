@@ -600,7 +600,7 @@ def attn_forward(q, k, v, window_t, window_s, scale, dual):
     return (q, k, v), o_t, o_s, lse_t, lse_s
 
 
-_BWD_COMBINE = os.environ.get("TTCD_ATTN_BWD_COMBINE", "0") == "1"      # opt-in until validated on every shape
+_BWD_COMBINE = os.environ.get("TTCD_ATTN_BWD_COMBINE", "1") != "0"      # one-softmax dual backward (0: two softmaxes)
 
 
 def attn_backward(q, k, v, o_t, o_s, lse_t, lse_s, do_t, do_s, window_t, window_s, scale, dv_slab=None):
@@ -621,17 +621,23 @@ def attn_backward(q, k, v, o_t, o_s, lse_t, lse_s, do_t, do_s, window_t, window_
                 nv.stream_ptr())
         return out
 
-    delta_t = _delta(o_t, do_t)
-    delta_s = _delta(o_s, do_s) if dual else None
     dq = torch.empty(B, Tq, H, D, dtype=_BF16, device=q.device)
     dk = torch.empty(B, Tk, HK, D, dtype=_BF16, device=q.device)
-    if dual and _BWD_COMBINE and nv.has("ttcd_attn_bwd_set_combined"):
+    if dual and _BWD_COMBINE and nv.has("ttcd_attn_bwd_combine"):
         # inside the student window P_S = r P_T (r = exp(lse_T - lse_S), per row): fold the student gradient stream
-        # into the teacher's so that the dK/dV kernel runs its single-window pipeline
-        r = torch.exp(lse_t - lse_s)                                            # [B, H, Tq] fp32
-        do_comb = torch.addcmul(do_t.float(), do_s.float(), r.transpose(1, 2).unsqueeze(-1)).to(_BF16)
-        delta_comb = torch.addcmul(delta_t, delta_s, r)
+        # into the teacher's (dO' = dO_T + r dO_S, delta' = delta_T + r delta_S) so that the dK/dV kernel runs its
+        # single-window pipeline; one kernel makes delta_T, delta' and dO'
+        delta_t = torch.empty(B, H, Tq, dtype=torch.float32, device=q.device)
+        delta_s = None
+        delta_comb = torch.empty_like(delta_t)
+        do_comb = torch.empty(B, Tq, H, D, dtype=_BF16, device=q.device)
+        nv.call("ttcd_attn_bwd_combine", nv.ptr(o_t), nv.ptr(do_t), nv.ptr(o_s), nv.ptr(do_s), nv.ptr(lse_t),
+                nv.ptr(lse_s), nv.ptr(delta_t), nv.ptr(delta_comb), nv.ptr(do_comb), nv.i64(B), nv.i32(Tq), nv.i32(H),
+                nv.i32(D), nv.stream_ptr())
         nv.call("ttcd_attn_bwd_set_combined", nv.ptr(do_comb), nv.ptr(delta_comb))
+    else:
+        delta_t = _delta(o_t, do_t)
+        delta_s = _delta(o_s, do_s) if dual else None
     if dv_slab is not None and nv.has("ttcd_attn_bwd_set_dv_layout") and (dv_slab[1] * 2) % 16 == 0:
         slab, col = dv_slab
         n_total = slab.n_total

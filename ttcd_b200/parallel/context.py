@@ -165,8 +165,20 @@ class _CPAttention(torch.autograd.Function):
                     nv.stream_ptr())
             return out
 
-        delta_t = delta(o_t, do_t)
-        delta_s = delta(o_s, do_s) if dual else None
+        from ..ops import cuda as _cuda
+        if dual and _cuda._BWD_COMBINE and nv.has("ttcd_attn_bwd_combine"):
+            # one-softmax dual backward (see ops.cuda.attn_backward): delta_T, delta' and dO' from one kernel
+            delta_t = torch.empty(B, H, S, dtype=torch.float32, device=qc.device)
+            delta_s = None
+            delta_comb = torch.empty_like(delta_t)
+            do_comb = torch.empty_like(do_t)
+            nv.call("ttcd_attn_bwd_combine", nv.ptr(o_t), nv.ptr(do_t), nv.ptr(o_s), nv.ptr(do_s), nv.ptr(lse_t),
+                    nv.ptr(lse_s), nv.ptr(delta_t), nv.ptr(delta_comb), nv.ptr(do_comb), nv.i64(B), nv.i32(S), nv.i32(H),
+                    nv.i32(D), nv.stream_ptr())
+            nv.call("ttcd_attn_bwd_set_combined", nv.ptr(do_comb), nv.ptr(delta_comb))
+        else:
+            delta_t = delta(o_t, do_t)
+            delta_s = delta(o_s, do_s) if dual else None
         # the halo keys/values were copied into local memory by the forward pass
         kh, vh = lb.halo_ptrs if halo else (0, 0)
         dq = torch.empty_like(qc)
