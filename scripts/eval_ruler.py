@@ -1,7 +1,8 @@
 """RULER-style long-context generation tasks (needle-in-a-haystack and friends): reference
 scripts/eval_niah.py and scripts/eval_ruler.py.
 
-Data layout: ``<data_dir>/<ctx_len>/<task>/validation.jsonl`` (also accepted: ``<data_dir>/<task>_<ctx_len>.jsonl``),
+Data layout: ``<data_dir>/<ctx_len>/<task>/validation.jsonl`` (also accepted: ``<data_dir>/ctx<ctx_len>/<task>/...`` as written
+by ``gen_ruler_data.py``, and ``<data_dir>/<task>_<ctx_len>.jsonl``),
 one JSON object per line with ``input``, ``outputs`` (list of reference strings), optional ``answer_prefix`` and
 ``index``.  The prompt is ``input`` (+ ``answer_prefix`` unless ``--no_answer_prefix``); decoding is greedy
 through the model's own prefill + windowed cache; the score is RULER's ``string_match_all``: the mean over
@@ -34,7 +35,8 @@ def string_match_all(preds: list[str], refs: list[list[str]]) -> float:
 
 
 def find_file(data_dir: Path, task: str, ctx: int) -> Path | None:
-    for cand in (data_dir / str(ctx) / task / "validation.jsonl", data_dir / task / str(ctx) / "validation.jsonl",
+    for cand in (data_dir / str(ctx) / task / "validation.jsonl", data_dir / f"ctx{ctx}" / task / "validation.jsonl",
+                 data_dir / task / str(ctx) / "validation.jsonl",
                  data_dir / f"{task}_{ctx}.jsonl"):
         if cand.is_file():
             return cand

@@ -65,3 +65,94 @@ def test_prepare_books_and_summarize_logs(tmp_path):
                          capture_output=True, text=True, check=True)
     row = json.loads(res.stdout.strip())
     assert row["steps"] == 5 and row["tps_mean"] == 1005.0 and row["mfu_mean"] == 40.0
+
+
+class _WordTokenizer:
+    """Whitespace tokenizer with the call shape the scripts use."""
+    truncation_side = "right"
+
+    def __call__(self, text, add_special_tokens=False, return_attention_mask=False, truncation=False, max_length=None,
+                 return_tensors=None):
+        from types import SimpleNamespace
+
+        def enc(t):
+            ids = [hash(w) % 251 for w in t.split()]
+            if truncation and max_length is not None and len(ids) > max_length:
+                ids = ids[-max_length:] if self.truncation_side == "left" else ids[:max_length]
+            return ids
+        if isinstance(text, list):
+            return {"input_ids": [enc(t) for t in text]}
+        return SimpleNamespace(input_ids=enc(text))
+
+
+def test_ruler_data_generator_fits_the_context_and_hides_the_answers():
+    import random
+
+    import gen_ruler_data as g
+    tok = _WordTokenizer()
+    for task in g.ALL_TASKS:
+        family = "niah" if task in g.NIAH_TASKS else task
+        d = g.make_sample(task, tok, 1024, random.Random(task))
+        assert d["length"] <= 1024 - g.TOKENS_TO_GENERATE[family] + len(d["answer_prefix"].split()), task
+        assert d["length"] > 600, (task, d["length"])                 # the prompt is grown to (nearly) fill the context
+        assert d["outputs"] and all(o in d["input"] for o in d["outputs"]), task
+    multi = g.make_sample("niah_multivalue", tok, 512, random.Random(1))
+    assert len(multi["outputs"]) == 4
+    vt = g.make_sample("vt", tok, 512, random.Random(2))
+    assert len(vt["outputs"]) == 5
+    order = [vt["input"].index(f"VAR {v} =") for v in vt["outputs"]]
+    assert order == sorted(order)                                      # the chain appears in assignment order
+
+
+def test_final_block_eval_manifest_and_merges(tmp_path):
+    import numpy as np
+
+    import eval_final_block_doc_ppl as ffb
+    import merge_eval_results as mg
+    from ttcd_b200.models import TransformerConfig, TransformerForCausalLM
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+    texts = [" ".join(f"w{(i * 7 + j) % 97}" for j in range(n)) for i, n in enumerate([40, 120, 300, 90, 260])]
+    pq.write_table(pa.table({"text": texts}), tmp_path / "a.parquet")
+    docs, stats = ffb.select_documents(_WordTokenizer(), [str(tmp_path / "a.parquet")], seq_len=200, token_budget=10 ** 6,
+                                       min_doc_tokens=100)
+    assert [len(d) for d in docs] == [120, 200, 200] and stats["eligible_docs"] == 3 and stats["sampled_docs"] == 5
+    ffb.save_manifest(str(tmp_path / "m.npz"), docs, stats)
+    docs2, stats2 = ffb.load_manifest(str(tmp_path / "m.npz"))
+    assert stats2 == stats and all(np.array_equal(a, b) for a, b in zip(docs, docs2))
+
+    torch.manual_seed(0)
+    model = TransformerForCausalLM(TransformerConfig(hidden_size=32, num_hidden_layers=1, num_heads=4, num_kv_heads=2,
+                                                     intermediate_size=64, vocab_size=256, window_size=64, fuse_cross_entropy=False,
+                                                     fuse_linear_cross_entropy=False, max_position_embeddings=256)).eval()
+    rows = ffb.final_block_curve(model, docs, [16, 100, 150], block=32, batch_size=2, device="cpu")
+    assert [r["num_sequences"] for r in rows] == [3, 2, 2] and rows[0]["total_pred_tokens"] == 96
+    ids = torch.from_numpy(docs[0][-48:].astype("int64"))[None]
+    want = torch.nn.functional.cross_entropy(model(input_ids=ids).logits[0, 15:-1].float(), ids[0, 16:], reduction="sum")
+    one = ffb.final_block_curve(model, docs[:1], [16], block=32, batch_size=1, device="cpu")[0]
+    assert abs(one["avg_nll"] * 32 - float(want)) < 1e-3
+
+    meta = {"seq_len": 200, "final_block_size": 32, "context_lens": [16, 100, 150], "selected_total_tokens": 520,
+            "min_doc_tokens": 100, "num_documents": 3}
+    for name in ("a", "b"):
+        (tmp_path / name).mkdir()
+        ffb.write_outputs(tmp_path / name, meta, stats, {name: rows})
+    merged = mg.merge_final_block([str(tmp_path / "a"), str(tmp_path / "b" / "fixed_final_block_doc_ppl.json")], str(tmp_path / "ab"))
+    assert list(merged["results"]) == ["a", "b"]
+    assert (tmp_path / "ab" / "fixed_final_block_doc_ppl.csv").read_text().splitlines()[0] == "context_len,a,b"
+
+    for seed, n, v in ((1, 2, 1.0), (2, 6, 2.0)):
+        (tmp_path / f"s{seed}.json").write_text(json.dumps({"seq_len": 5, "num_samples": n, "nll_per_position": [v] * 4}))
+    out = mg.merge_offset_shards([str(tmp_path / "s1.json"), str(tmp_path / "s2.json")], str(tmp_path / "s.json"))
+    assert out["num_samples"] == 8 and abs(out["nll"] - 1.75) < 1e-12
+
+    import report_results as rr
+    text, by_task = rr.niah_tables({"m": {"4096": {"niah_single_1": {"accuracy": 80.0}, "average": 80.0}}})
+    assert "niah_single_1" in text and by_task["average"]["m"][4096] == 80.0
+    rr.main(["final-block", "--input", str(tmp_path / "ab" / "fixed_final_block_doc_ppl.json")])
+    rr.main(["token-ppl", "--inputs", f"x={tmp_path / 's.json'}"])
+
+
+def test_verify_configs_reports_every_config():
+    import verify_configs
+    assert verify_configs.main(["--build"]) == 0
