@@ -25,7 +25,9 @@
 
 namespace ttcd {
 
-constexpr int BWD_THREADS = 288;  // 8 compute warps + 1 control warp
+// NEW element-wise warps (8 or 16) + 1 control warp.  A warp may only touch the TMEM lanes of its quarter
+// (warp % 4), so the NEW / 4 warps of a quarter split the 64 S columns of a step between them.
+constexpr int bwd_threads(int n_ew) { return (n_ew + 1) * 32; }
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ float ex2(float x) {
@@ -35,6 +37,14 @@ __device__ __forceinline__ float ex2(float x) {
 }
 __device__ __forceinline__ void named_barrier_sync(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+// TMEM column offset (inside an S / dP column group of 64) of the 8 packed bf16 columns that hold k-step `k` (16
+// rows of the contraction) when each of NEW / 4 warps per quarter packs its 64 / (NEW / 4) columns in place
+template <int NEW>
+__device__ __forceinline__ constexpr uint32_t ts_packed_off(int k) {
+  constexpr int NC = 64 / (NEW / 4);
+  return static_cast<uint32_t>(((16 * k) / NC) * NC + ((16 * k) % NC) / 2);
 }
 
 struct AttnBwdParams {
@@ -59,24 +69,12 @@ struct AttnBwdParams {
   int combine;
 };
 
-// 32 accumulator columns of one TMEM lane -> 32 bf16 (one 64-byte half row) of a K-major SW128 tile
-__device__ __forceinline__ void store_half_row(uint8_t* tile, int row, int half, const float (&v)[32]) {
+// NP packed bf16 pairs (2 NP values) -> part `part` (of 32 / NP) of one 128-byte row of a K-major SW128 tile
+template <int NP>
+__device__ __forceinline__ void store_row_part_packed(uint8_t* tile, int row, int part, const uint32_t (&v)[NP]) {
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    uint4 pk;
-    pk.x = pack_bf16(v[c * 8 + 0], v[c * 8 + 1]);
-    pk.y = pack_bf16(v[c * 8 + 2], v[c * 8 + 3]);
-    pk.z = pack_bf16(v[c * 8 + 4], v[c * 8 + 5]);
-    pk.w = pack_bf16(v[c * 8 + 6], v[c * 8 + 7]);
-    *reinterpret_cast<uint4*>(tile + sw128_offset(row, half * 4 + c)) = pk;
-  }
-}
-
-// 16 packed bf16 pairs (32 values) -> one 64-byte half row of a K-major SW128 tile
-__device__ __forceinline__ void store_half_row_packed(uint8_t* tile, int row, int half, const uint32_t (&v)[16]) {
-#pragma unroll
-  for (int c = 0; c < 4; ++c)
-    *reinterpret_cast<uint4*>(tile + sw128_offset(row, half * 4 + c)) =
+  for (int c = 0; c < NP / 4; ++c)
+    *reinterpret_cast<uint4*>(tile + sw128_offset(row, part * (NP / 4) + c)) =
         make_uint4(v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
 }
 
@@ -93,19 +91,19 @@ __device__ __forceinline__ void store_out32(bf16* dst, const uint32_t (&a)[32], 
   }
 }
 
-// Element-wise core of the dK/dV step for one thread: 32 query columns of one key row.
+// Element-wise core of the dK/dV step for one thread: NC query columns of one key row.
 //   stats: shared-memory block [-lse_t*log2e | delta_t | -lse_s*log2e | delta_s] (64 floats each),
 //          already offset to this thread's first column.
 //   p_t = 2^(s*c - lse_t),  dS (unscaled) = p_t (dP_t - delta_t) [+ p_s (dP_s - delta_s)]
 // MASKED = false is the common case of a block that is fully inside every window.
-template <bool MASKED, bool STUDENT>
-__device__ __forceinline__ void dkdv_elementwise(const uint32_t (&sv)[32], const uint32_t (&dpt)[32],
-                                                 const uint32_t (&dps)[32], const float* stats, float scale_log2,
+template <bool MASKED, bool STUDENT, int NC>
+__device__ __forceinline__ void dkdv_elementwise(const uint32_t (&sv)[NC], const uint32_t (&dpt)[NC],
+                                                 const uint32_t (&dps)[NC], const float* stats, float scale_log2,
                                                  int key, int qpos0, int w_t, int w_s, bool key_ok,
-                                                 uint32_t (&ptp)[16], uint32_t (&psp)[16], uint32_t (&dsp)[16],
-                                                 int lo_t = 0) {
+                                                 uint32_t (&ptp)[NC / 2], uint32_t (&psp)[NC / 2],
+                                                 uint32_t (&dsp)[NC / 2], int lo_t = 0) {
 #pragma unroll
-  for (int c = 0; c < 32; c += 4) {
+  for (int c = 0; c < NC; c += 4) {
     const float4 nl = *reinterpret_cast<const float4*>(stats + c);
     const float4 dl = *reinterpret_cast<const float4*>(stats + 64 + c);
     const float nls[4] = {nl.x, nl.y, nl.z, nl.w};
@@ -147,14 +145,14 @@ __device__ __forceinline__ void dkdv_elementwise(const uint32_t (&sv)[32], const
   }
 }
 
-// Element-wise core of the dQ step: 32 key columns of one query row (statistics live in registers).
-template <bool MASKED, bool STUDENT>
-__device__ __forceinline__ void dq_elementwise(const uint32_t (&sv)[32], const uint32_t (&dpt)[32],
-                                               const uint32_t (&dps)[32], float scale_log2, float nlse_t, float del_t,
+// Element-wise core of the dQ step: NC key columns of one query row (statistics live in registers).
+template <bool MASKED, bool STUDENT, int NC>
+__device__ __forceinline__ void dq_elementwise(const uint32_t (&sv)[NC], const uint32_t (&dpt)[NC],
+                                               const uint32_t (&dps)[NC], float scale_log2, float nlse_t, float del_t,
                                                float nlse_s, float del_s, int qpos, int key0, int w_t, int w_s,
-                                               uint32_t (&dsp)[16], int lo_t = 0) {
+                                               uint32_t (&dsp)[NC / 2], int lo_t = 0) {
 #pragma unroll
-  for (int c = 0; c < 32; c += 2) {
+  for (int c = 0; c < NC; c += 2) {
     float d[2];
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
@@ -199,8 +197,8 @@ struct DkdvCfg {
   static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16;
 };
 
-template <int D, bool DUAL>
-__global__ void __launch_bounds__(BWD_THREADS, 1)
+template <int D, bool DUAL, int NEW>
+__global__ void __launch_bounds__(bwd_threads(NEW), 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                      const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ CUtensorMap tma_dot,
                      const __grid_constant__ CUtensorMap tma_dos, const __grid_constant__ CUtensorMap tma_kh,
@@ -252,11 +250,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
     mbar_init(kv_full, 1);
     for (int s = 0; s < C::NSLOTS; ++s) mbar_init(tiles_full(s), 1);
     for (int s = 0; s < C::NSETS; ++s) mbar_init(sdp_full(s), 1);
-    mbar_init(ew_done, 8);
+    mbar_init(ew_done, NEW);
     mbar_init(acc_done, 1);
     mbar_fence_init();
   }
-  if (warp == 8) {
+  if (warp == NEW) {
     tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
   }
@@ -289,7 +287,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   auto iter_student = [&](int it) { return DUAL && (iter_row0(it) + off < n0 + 127 + p.w_s); };
   auto slot_base = [&](int it) { return sbase + C::RING_OFF + (it % C::NSLOTS) * C::NTILES * C::TILE_BYTES; };
 
-  if (warp == 8 && healthy && n_iters > 0) {
+  if (warp == NEW && healthy && n_iters > 0) {
     if (elect_one()) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, false, false);  // [keys x q] = A(K-major) B(K-major)
       constexpr uint32_t idesc_acc = umma_idesc_bf16(128, D, false, true);   // [keys x D] = A(K-major) B(MN-major)
@@ -343,13 +341,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
         if (use_ts) {
           const uint32_t ts = t_set(it);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint32_t a_off = 32 * (k / 2) + 8 * (k % 2);
+          for (int k = 0; k < 4; ++k) {     // 16 queries = 8 packed columns at the start of their warp's column group
+            const uint32_t a_off = ts_packed_off<NEW>(k);
             umma_ts(t_dv, ts + a_off, umma_desc_sw128(sdot + k * 2048, C::ROW_REGION, 1024), idesc_acc, (it | k) != 0);
           }
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const uint32_t a_off = 64 + 32 * (k / 2) + 8 * (k % 2);
+            const uint32_t a_off = 64 + ts_packed_off<NEW>(k);
             umma_ts(t_dk, ts + a_off, umma_desc_sw128(sq + k * 2048, C::ROW_REGION, 1024), idesc_acc, (it | k) != 0);
           }
           umma_commit(acc_done);
@@ -413,12 +411,14 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
         for (int s = 0; s < C::NSLOTS; ++s) { mbar_drain(tiles_full(s), 0); mbar_drain(tiles_full(s), 1); }
       }
     }
-  } else if (warp < 8 && healthy) {
-    const int quarter = warp & 3, half = warp >> 2;
+  } else if (warp < NEW && healthy) {
+    constexpr int PARTS = NEW / 4;              // warps per TMEM lane quarter
+    constexpr int NC = 64 / PARTS;              // S^T columns (queries) of a step per thread
+    const int quarter = warp & 3, part = warp >> 2;
     const int krow = quarter * 32 + lane;       // key row inside the block == TMEM lane
     const int key = n0 + krow;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    const int ctid = threadIdx.x;               // 0..255
+    const int ctid = threadIdx.x;               // 0 .. 32 NEW - 1; the first 256 fetch the row statistics
     bool ok = true;
     auto wait_all = [&](uint32_t bar, uint32_t parity, int code) {
       const bool r = mbar_wait(bar, parity, abort_flag, code);
@@ -436,36 +436,36 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       if (!DUAL || !iter_student(it)) return 0.f;
       return which == 2 ? -p.lse_s[idx] * LOG2E : p.delta_s[idx];
     };
-    if (n_iters > 0) vecs[ctid] = fetch_stat(0);
+    if (n_iters > 0 && ctid < 256) vecs[ctid] = fetch_stat(0);
     for (int it = 0; it < n_iters && ok; ++it) {
       const int r0 = iter_row0(it);
       const bool st = iter_student(it);
       const float* vslot = vecs + (it & 1) * 256;
-      const float next_stat = (it + 1 < n_iters) ? fetch_stat(it + 1) : 0.f;  // in flight during this step
-      named_barrier_sync(1, 256);
+      const float next_stat = (it + 1 < n_iters && ctid < 256) ? fetch_stat(it + 1) : 0.f;  // in flight during this step
+      named_barrier_sync(1, NEW * 32);
       ok = wait_all(sdp_full(it % C::NSETS), (it / C::NSETS) & 1, 311);
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t ts = t_set(it) + lane_addr + half * 32;
-      uint32_t sv[32], dpt[32], dps[32];
-      tmem_ld32(ts, sv);
-      tmem_ld32(ts + 64, dpt);
-      if (DUAL && st) tmem_ld32(ts + 128, dps);
+      const uint32_t ts = t_set(it) + lane_addr + part * NC;
+      uint32_t sv[NC], dpt[NC], dps[NC];
+      tmem_ld_n<NC>(ts, sv);
+      tmem_ld_n<NC>(ts + 64, dpt);
+      if (DUAL && st) tmem_ld_n<NC>(ts + 128, dps);
       tmem_ld_wait();
-      uint32_t ptp[16], psp[16], dsp[16];
+      uint32_t ptp[NC / 2], psp[NC / 2], dsp[NC / 2];
       {
         const int qlo_b = r0 + off, qhi_b = r0 + 63 + off;
         // fully visible block: every (key, query) pair is inside the teacher (and student) window
         const bool full_t = (n0 + 127 <= qlo_b) && (n0 > qhi_b - p.w_t) && (n0 + 127 < p.Tk);
         const bool full_s = (n0 > qhi_b - p.w_s);
-        const float* stats = vslot + half * 32;
-        const int qpos0 = r0 + half * 32 + off;
+        const float* stats = vslot + part * NC;
+        const int qpos0 = r0 + part * NC + off;
         const bool key_ok = key < p.Tk;
         if (DUAL && st) {
           if (full_t && full_s)
-            dkdv_elementwise<false, true>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, p.w_t, p.w_s, key_ok, ptp, psp, dsp);
+            dkdv_elementwise<false, true, NC>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, p.w_t, p.w_s, key_ok, ptp, psp, dsp);
           else
-            dkdv_elementwise<true, true>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, p.w_t, p.w_s, key_ok, ptp, psp, dsp);
+            dkdv_elementwise<true, true, NC>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, p.w_t, p.w_s, key_ok, ptp, psp, dsp);
         } else if (combine) {
           // one softmax (the teacher's): keys inside the student window with (dO', delta'), keys outside it with
           // (dO_T, delta_T); visible pairs are  qpos - hi < key <= qpos - lo
@@ -473,19 +473,19 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
           const int lo = inner ? 0 : p.w_s, hi = inner ? p.w_s : p.w_t;
           const bool full = (n0 + 127 <= qlo_b - lo) && (n0 > qhi_b - hi) && (n0 + 127 < p.Tk);
           if (full)
-            dkdv_elementwise<false, false>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, hi, hi, key_ok, ptp, psp, dsp, lo);
+            dkdv_elementwise<false, false, NC>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, hi, hi, key_ok, ptp, psp, dsp, lo);
           else
-            dkdv_elementwise<true, false>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, hi, hi, key_ok, ptp, psp, dsp, lo);
+            dkdv_elementwise<true, false, NC>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, hi, hi, key_ok, ptp, psp, dsp, lo);
         } else {
           if (full_t)
-            dkdv_elementwise<false, false>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, p.w_t, p.w_s, key_ok, ptp, psp, dsp);
+            dkdv_elementwise<false, false, NC>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, p.w_t, p.w_s, key_ok, ptp, psp, dsp);
           else
-            dkdv_elementwise<true, false>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, p.w_t, p.w_s, key_ok, ptp, psp, dsp);
+            dkdv_elementwise<true, false, NC>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, p.w_t, p.w_s, key_ok, ptp, psp, dsp);
         }
       }
       if (use_ts) {
-        tmem_st16(ts, ptp);            // over this thread's own 32 S^T columns (already read)
-        tmem_st16(ts + 64, dsp);       // over its dP^T columns
+        tmem_st_n<NC / 2>(ts, ptp);        // over this thread's own S^T columns (already read)
+        tmem_st_n<NC / 2>(ts + 64, dsp);   // over its dP^T columns
         tmem_st_wait();
       }
       if (it >= 1) {
@@ -493,11 +493,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
         if (!ok) break;
       }
       if (!use_ts) {
-        store_half_row_packed(smem + C::PT_OFF, krow, half, ptp);
-        if (DUAL && st) store_half_row_packed(smem + C::PS_OFF, krow, half, psp);
-        store_half_row_packed(smem + C::DS_OFF, krow, half, dsp);
+        store_row_part_packed<NC / 2>(smem + C::PT_OFF, krow, part, ptp);
+        if (DUAL && st) store_row_part_packed<NC / 2>(smem + C::PS_OFF, krow, part, psp);
+        store_row_part_packed<NC / 2>(smem + C::DS_OFF, krow, part, dsp);
       }
-      vecs[((it + 1) & 1) * 256 + ctid] = next_stat;
+      if (ctid < 256) vecs[((it + 1) & 1) * 256 + ctid] = next_stat;
       fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncwarp();
@@ -506,7 +506,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
     // epilogue: dK, dV -> global (this thread: key row `krow`, one half of the D columns)
     if (ok) {
       if (n_iters > 0) ok = wait_all(acc_done, (n_iters - 1) & 1, 313);
-      if (ok) {
+      if (ok && part < 2) {               // two warps per quarter write the accumulators out, half the columns each
+        const int half = part;
         tc_fence_after_sync();
         const bool store = key < p.Tk;
         const int64_t rowoff = ((static_cast<int64_t>(b) * p.Tk + key) * p.HK + kvh) * D;
@@ -535,7 +536,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == NEW) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
@@ -566,8 +567,8 @@ struct DqCfg {
   static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16;
 };
 
-template <int D, bool DUAL>
-__global__ void __launch_bounds__(BWD_THREADS, 1)
+template <int D, bool DUAL, int NEW>
+__global__ void __launch_bounds__(bwd_threads(NEW), 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                    const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ CUtensorMap tma_dot,
                    const __grid_constant__ CUtensorMap tma_dos, const __grid_constant__ CUtensorMap tma_kh,
@@ -630,12 +631,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     for (int s = 0; s < C::NSLOTS; ++s) mbar_init(kv_full(s), 1);
     mbar_init(sdp_full(0), 1);
     mbar_init(sdp_full(1), 1);
-    mbar_init(ew_done, 8);
+    mbar_init(ew_done, NEW);
     mbar_init(acc_done, 1);
-    mbar_init(a_ready, 8);
+    mbar_init(a_ready, NEW);
     mbar_fence_init();
   }
-  if (warp == 8) {
+  if (warp == NEW) {
     tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
   }
@@ -645,12 +646,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t t_dq = tmem_base;
   const bool use_ts = C::CAN_TS && p.a_in_tmem != 0;
+  // every mode: dS goes back into tensor memory over the S columns it was computed from (bf16 pairs) and feeds the
+  // dQ MMA as its TMEM A operand; the S MMA that next writes those columns is issued after that dQ MMA
+  const bool ds_ts = p.a_in_tmem != 0;
   const uint32_t t_qa = tmem_base + 128 + 2 * C::SET_COLS;      // [384, 384 + D/2): Q, then dO
   const uint32_t t_doa = t_qa + C::A_COLS;
   auto t_set = [&](int it) { return tmem_base + 128 + (it & 1) * C::SET_COLS; };  // S | dP_T | dP_S
   const bool healthy = (*abort_flag == 0);
 
-  if (warp == 8 && healthy) {
+  if (warp == NEW && healthy) {
     if (elect_one()) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, false, false);
       constexpr uint32_t idesc_acc = umma_idesc_bf16(128, D, false, true);
@@ -737,10 +741,17 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t sk = slot_base(it);
+        if (ds_ts) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k)  // contraction over the 64 keys of the block
-          umma_ss(t_dq, umma_desc_sw128(sbase + C::DS_OFF + k * 32, 16, 1024),
-                  umma_desc_sw128(sk + k * 2048, C::KV_REGION, 1024), idesc_acc, (it | k) != 0);
+          for (int k = 0; k < 4; ++k)  // dS as the TMEM A operand: 16 keys = 8 packed columns
+            umma_ts(t_dq, t_set(it) + ts_packed_off<NEW>(k), umma_desc_sw128(sk + k * 2048, C::KV_REGION, 1024),
+                    idesc_acc, (it | k) != 0);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; ++k)  // contraction over the 64 keys of the block
+            umma_ss(t_dq, umma_desc_sw128(sbase + C::DS_OFF + k * 32, 16, 1024),
+                    umma_desc_sw128(sk + k * 2048, C::KV_REGION, 1024), idesc_acc, (it | k) != 0);
+        }
         umma_commit(acc_done);
       }
       if (!ok) {
@@ -748,8 +759,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         for (int s = 0; s < C::NSLOTS; ++s) { mbar_drain(kv_full(s), 0); mbar_drain(kv_full(s), 1); }
       }
     }
-  } else if (warp < 8 && healthy) {
-    const int quarter = warp & 3, half = warp >> 2;
+  } else if (warp < NEW && healthy) {
+    constexpr int PARTS = NEW / 4;              // warps per TMEM lane quarter
+    constexpr int NC = 64 / PARTS;              // S columns (keys) of a step per thread
+    const int quarter = warp & 3, part = warp >> 2;
     const int qrow = quarter * 32 + lane;
     const int row = m0 + qrow;
     const int qpos = row + off;
@@ -769,17 +782,18 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       // Q and dO rows: shared memory (128-byte swizzled, 64 columns per region) -> packed bf16 pairs in TMEM
       ok = wait_all(q_full, 0, 334);
       if (ok) {
-        for (int reg = half; reg < C::DB; reg += 2) {
-          uint32_t qa[32], da[32];
+        for (int u = part; u < C::DB * 2; u += PARTS) {      // units of 32 columns (16 packed) of a row
+          const int reg = u >> 1, hc = u & 1;
+          uint32_t qa[16], da[16];
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            const uint4 a = *reinterpret_cast<const uint4*>(smem + C::Q_OFF + reg * C::Q_REGION + sw128_offset(qrow, c));
-            const uint4 g = *reinterpret_cast<const uint4*>(smem + C::DOT_OFF + reg * C::Q_REGION + sw128_offset(qrow, c));
+          for (int c = 0; c < 4; ++c) {
+            const uint4 a = *reinterpret_cast<const uint4*>(smem + C::Q_OFF + reg * C::Q_REGION + sw128_offset(qrow, hc * 4 + c));
+            const uint4 g = *reinterpret_cast<const uint4*>(smem + C::DOT_OFF + reg * C::Q_REGION + sw128_offset(qrow, hc * 4 + c));
             qa[4 * c] = a.x; qa[4 * c + 1] = a.y; qa[4 * c + 2] = a.z; qa[4 * c + 3] = a.w;
             da[4 * c] = g.x; da[4 * c + 1] = g.y; da[4 * c + 2] = g.z; da[4 * c + 3] = g.w;
           }
-          tmem_st32(t_qa + lane_addr + reg * 32, qa);
-          tmem_st32(t_doa + lane_addr + reg * 32, da);
+          tmem_st16(t_qa + lane_addr + reg * 32 + hc * 16, qa);
+          tmem_st16(t_doa + lane_addr + reg * 32 + hc * 16, da);
         }
         tmem_st_wait();
         tc_fence_before_sync();
@@ -789,55 +803,61 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     }
     for (int it = 0; it < n_iters && ok; ++it) {
       const bool st = iter_student(it);
-      const int key0 = iter_key0(it) + half * 32;
+      const int key0 = iter_key0(it) + part * NC;
       ok = wait_all(sdp_full(it & 1), (it >> 1) & 1, 331);
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t ts = t_set(it) + lane_addr + half * 32;
-      uint32_t sv[32], dpt[32], dps[32];
-      tmem_ld32(ts, sv);
-      tmem_ld32(ts + 64, dpt);
-      if (DUAL && st) tmem_ld32(ts + 128, dps);
+      const uint32_t ts = t_set(it) + lane_addr + part * NC;
+      uint32_t sv[NC], dpt[NC], dps[NC];
+      tmem_ld_n<NC>(ts, sv);
+      tmem_ld_n<NC>(ts + 64, dpt);
+      if (DUAL && st) tmem_ld_n<NC>(ts + 128, dps);
       tmem_ld_wait();
-      uint32_t dsp[16];
+      uint32_t dsp[NC / 2];
       {
         const int kb0 = iter_key0(it);
         const bool full_t = (kb0 + 63 <= qlo) && (kb0 > qhi - p.w_t);
         const bool full_s = (kb0 > qhi - p.w_s);
         if (DUAL && st) {
           if (full_t && full_s)
-            dq_elementwise<false, true>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, key0, p.w_t, p.w_s, dsp);
+            dq_elementwise<false, true, NC>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, key0, p.w_t, p.w_s, dsp);
           else
-            dq_elementwise<true, true>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, key0, p.w_t, p.w_s, dsp);
+            dq_elementwise<true, true, NC>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, key0, p.w_t, p.w_s, dsp);
         } else if (combine) {
           const int inner = iter_inner(it);
           const int lo = inner ? 0 : p.w_s, hi = inner ? p.w_s : p.w_t;
           const float del = inner ? del_s : del_t;            // delta' was passed in place of delta_S
           const bool full = (kb0 + 63 <= qlo - lo) && (kb0 > qhi - hi);
           if (full)
-            dq_elementwise<false, false>(sv, dpt, dps, p.scale_log2, nlse_t, del, nlse_s, del_s, qpos, key0, hi, hi, dsp, lo);
+            dq_elementwise<false, false, NC>(sv, dpt, dps, p.scale_log2, nlse_t, del, nlse_s, del_s, qpos, key0, hi, hi, dsp, lo);
           else
-            dq_elementwise<true, false>(sv, dpt, dps, p.scale_log2, nlse_t, del, nlse_s, del_s, qpos, key0, hi, hi, dsp, lo);
+            dq_elementwise<true, false, NC>(sv, dpt, dps, p.scale_log2, nlse_t, del, nlse_s, del_s, qpos, key0, hi, hi, dsp, lo);
         } else {
           if (full_t)
-            dq_elementwise<false, false>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, key0, p.w_t, p.w_s, dsp);
+            dq_elementwise<false, false, NC>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, key0, p.w_t, p.w_s, dsp);
           else
-            dq_elementwise<true, false>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, key0, p.w_t, p.w_s, dsp);
+            dq_elementwise<true, false, NC>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, key0, p.w_t, p.w_s, dsp);
         }
       }
       if (it >= 1) {
         ok = wait_all(acc_done, (it - 1) & 1, 332);  // dS tile is free again
         if (!ok) break;
       }
-      store_half_row_packed(smem + C::DS_OFF, qrow, half, dsp);
-      fence_proxy_async_smem();
+      if (ds_ts) {
+        tmem_st_n<NC / 2>(ts, dsp);    // over this thread's own S columns (already read)
+        tmem_st_wait();
+      } else {
+        store_row_part_packed<NC / 2>(smem + C::DS_OFF, qrow, part, dsp);
+        fence_proxy_async_smem();
+      }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(ew_done);
     }
     if (ok) {
       ok = wait_all(acc_done, (n_iters - 1) & 1, 333);
-      if (ok) {
+      if (ok && part < 2) {               // two warps per quarter write dQ out, half the columns each
+        const int half = part;
         tc_fence_after_sync();
         constexpr int COLS = D / 2;
         const int64_t rowoff = ((static_cast<int64_t>(b) * p.Tq + row) * p.H + h) * D;
@@ -853,7 +873,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == NEW) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
@@ -945,10 +965,10 @@ struct BwdMaps {
   CUtensorMap q64, q128, k64, k128, v64, v128, dot64, dot128, dos64, dos128, kh64, kh128, vh64, vh128;
 };
 
-template <int D, bool DUAL>
+template <int D, bool DUAL, int NEW>
 static int launch_bwd(const BwdMaps& m, const AttnBwdParams& p, int B, cudaStream_t stream) {
-  auto k1 = attn_bwd_dkdv_kernel<D, DUAL>;
-  auto k2 = attn_bwd_dq_kernel<D, DUAL>;
+  auto k1 = attn_bwd_dkdv_kernel<D, DUAL, NEW>;
+  auto k2 = attn_bwd_dq_kernel<D, DUAL, NEW>;
   constexpr int smem1 = DkdvCfg<D, DUAL>::TOTAL, smem2 = DqCfg<D, DUAL>::TOTAL;
   static_assert(smem1 <= 232448 && smem2 <= 232448, "shared memory budget exceeded");
   static bool configured = false;
@@ -958,19 +978,19 @@ static int launch_bwd(const BwdMaps& m, const AttnBwdParams& p, int B, cudaStrea
     configured = true;
   }
   dim3 g1((p.Tk + 127) / 128, p.HK, B);
-  k1<<<g1, BWD_THREADS, smem1, stream>>>(m.q64, m.k128, m.v128, m.dot64, m.dos64, m.kh128, m.vh128, p);
+  k1<<<g1, bwd_threads(NEW), smem1, stream>>>(m.q64, m.k128, m.v128, m.dot64, m.dos64, m.kh128, m.vh128, p);
   TTCD_CUDA_CHECK(cudaGetLastError());
   dim3 g2(p.H, (p.Tq + 127) / 128, B);
-  k2<<<g2, BWD_THREADS, smem2, stream>>>(m.q128, m.k64, m.v64, m.dot128, m.dos128, m.kh64, m.vh64, p);
+  k2<<<g2, bwd_threads(NEW), smem2, stream>>>(m.q128, m.k64, m.v64, m.dot128, m.dos128, m.kh64, m.vh64, p);
   return static_cast<int>(cudaGetLastError());
 }
 
 // Dual window with the dK/dV kernel in combined mode (single-window pipeline, one softmax) and the dual dQ kernel.
-template <int D>
+template <int D, int NEW>
 static int launch_bwd_combined(const BwdMaps& m, const CUtensorMap& dop64, const CUtensorMap& dop128, const AttnBwdParams& p,
                                const float* delta_p, int B, cudaStream_t stream) {
-  auto k1 = attn_bwd_dkdv_kernel<D, false>;
-  auto k2 = attn_bwd_dq_kernel<D, true>;
+  auto k1 = attn_bwd_dkdv_kernel<D, false, NEW>;
+  auto k2 = attn_bwd_dq_kernel<D, true, NEW>;
   constexpr int smem1 = DkdvCfg<D, false>::TOTAL, smem2 = DqCfg<D, true>::TOTAL;
   static bool configured = false;
   if (!configured) {
@@ -982,11 +1002,17 @@ static int launch_bwd_combined(const BwdMaps& m, const CUtensorMap& dop64, const
   p1.combine = 1;
   p1.delta_s = delta_p;
   dim3 g1((p.Tk + 127) / 128, p.HK, B);
-  k1<<<g1, BWD_THREADS, smem1, stream>>>(m.q64, m.k128, m.v128, m.dot64, dop64, m.kh128, m.vh128, p1);
+  k1<<<g1, bwd_threads(NEW), smem1, stream>>>(m.q64, m.k128, m.v128, m.dot64, dop64, m.kh128, m.vh128, p1);
   TTCD_CUDA_CHECK(cudaGetLastError());
   dim3 g2(p.H, (p.Tq + 127) / 128, B);
-  k2<<<g2, BWD_THREADS, smem2, stream>>>(m.q128, m.k64, m.v64, m.dot128, dop128, m.kh64, m.vh64, p1);
+  k2<<<g2, bwd_threads(NEW), smem2, stream>>>(m.q128, m.k64, m.v64, m.dot128, dop128, m.kh64, m.vh64, p1);
   return static_cast<int>(cudaGetLastError());
+}
+
+template <int NEW>
+static int dispatch_bwd(const BwdMaps& m, const AttnBwdParams& p, int B, int D, bool dual, cudaStream_t stream) {
+  if (D == 128) return dual ? launch_bwd<128, true, NEW>(m, p, B, stream) : launch_bwd<128, false, NEW>(m, p, B, stream);
+  return dual ? launch_bwd<64, true, NEW>(m, p, B, stream) : launch_bwd<64, false, NEW>(m, p, B, stream);
 }
 
 }  // namespace ttcd
@@ -1086,6 +1112,11 @@ TTCD_EXPORT int ttcd_attn_bwd_cp(const void* q, const void* k, const void* v, co
     return (e != nullptr && e[0] == '0') ? 0 : 1;
   }();
   p.a_in_tmem = a_in_tmem;
+  // element-wise warps per CTA: 16 (four per scheduler, hides the TMEM-load and MUFU latencies) or 8
+  static const int ew_warps = [] {
+    const char* e = getenv("TTCD_ATTN_BWD_WARPS");
+    return (e != nullptr && atoi(e) == 8) ? 8 : 16;
+  }();
   p.ld_dv = g_next_ld_dv; p.sb_dv = g_next_sb_dv;
   g_next_ld_dv = g_next_sb_dv = 0;
   p.combine = 0;
@@ -1100,11 +1131,13 @@ TTCD_EXPORT int ttcd_attn_bwd_cp(const void* q, const void* k, const void* v, co
     rc = make_tmap_bf16_3d(&dop64, dop, qi, Tq, B, qi, qi * Tq, 64, 64);
     if (rc == TTCD_OK) rc = make_tmap_bf16_3d(&dop128, dop, qi, Tq, B, qi, qi * Tq, 64, 128);
     if (rc != TTCD_OK) return rc;
-    return D == 128 ? launch_bwd_combined<128>(m, dop64, dop128, p, delta_p, B, stream)
-                    : launch_bwd_combined<64>(m, dop64, dop128, p, delta_p, B, stream);
+    if (ew_warps == 16)
+      return D == 128 ? launch_bwd_combined<128, 16>(m, dop64, dop128, p, delta_p, B, stream)
+                      : launch_bwd_combined<64, 16>(m, dop64, dop128, p, delta_p, B, stream);
+    return D == 128 ? launch_bwd_combined<128, 8>(m, dop64, dop128, p, delta_p, B, stream)
+                    : launch_bwd_combined<64, 8>(m, dop64, dop128, p, delta_p, B, stream);
   }
-  if (D == 128) return dual ? launch_bwd<128, true>(m, p, B, stream) : launch_bwd<128, false>(m, p, B, stream);
-  return dual ? launch_bwd<64, true>(m, p, B, stream) : launch_bwd<64, false>(m, p, B, stream);
+  return ew_warps == 16 ? dispatch_bwd<16>(m, p, B, D, dual, stream) : dispatch_bwd<8>(m, p, B, D, dual, stream);
 }
 
 TTCD_EXPORT int ttcd_attn_bwd(const void* q, const void* k, const void* v, const void* do_t, const void* do_s,
