@@ -58,6 +58,8 @@ struct AttnBwdParams {
   int halo_len, halo_row0;
   // single-window dQ kernel: keep Q and dO (loop-invariant A operands) in tensor memory
   int a_in_tmem;
+  // with operands in tensor memory the freed staging tiles become extra TMA ring slots (0: keep the 3-slot ring)
+  int deep_ring;
   // dV may be written into a wider row (the packed q|k|v gradient of a fused projection): row and batch strides
   // in elements; 0 = contiguous [B, Tk, HK, D]
   int64_t ld_dv, sb_dv;
@@ -178,7 +180,10 @@ template <int D, bool DUAL>
 struct DkdvCfg {
   static constexpr int DB = D / 64;
   static constexpr int NSETS = DUAL ? 1 : 2;    // S/dP accumulator sets in TMEM
-  static constexpr int NSLOTS = DUAL ? 2 : 3;   // Q/dO tile ring
+  static constexpr int NSLOTS = DUAL ? 2 : 3;   // Q/dO tile ring when P^T / dS^T are staged in shared memory
+  // single window with P^T / dS^T in tensor memory: their staging tiles (32 KB, right behind the ring) are a fourth
+  // ring slot, so that a tile load has two steps to arrive instead of one
+  static constexpr int MAXSLOTS = DUAL ? 2 : 4;
   static constexpr int SET_COLS = DUAL ? 192 : 128;
   static constexpr int KEY_REGION = 128 * 128;  // [128 keys x 64 d] swizzled
   static constexpr int ROW_REGION = 64 * 128;   // [64 rows x 64 d] swizzled
@@ -192,8 +197,9 @@ struct DkdvCfg {
   static constexpr int DS_OFF = PS_OFF + (DUAL ? KEY_REGION : 0);
   static constexpr int VEC_OFF = DS_OFF + KEY_REGION;                 // 2 slots x 4 vectors x 64 floats
   static constexpr int BAR_OFF = VEC_OFF + 2 * 4 * 64 * 4;
-  // kv_full, tiles_full[NSLOTS], sdp_full[NSETS], ew_done, acc_done
-  static constexpr int NBARS = 1 + NSLOTS + NSETS + 2;
+  // kv_full, tiles_full[MAXSLOTS], sdp_full[NSETS], ew_done, acc_done
+  static constexpr int NBARS = 1 + MAXSLOTS + NSETS + 2;
+  static_assert(DUAL || 2 * KEY_REGION >= NTILES * TILE_BYTES, "the staging tiles must hold one more ring slot");
   static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16;
 };
 
@@ -209,8 +215,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   const uint32_t bars = sbase + C::BAR_OFF;
   const uint32_t kv_full = bars;
   auto tiles_full = [&](int s) { return bars + 8u * (1 + s); };
-  auto sdp_full = [&](int s) { return bars + 8u * (1 + C::NSLOTS + s); };
-  const uint32_t ew_done = bars + 8u * (1 + C::NSLOTS + C::NSETS);
+  auto sdp_full = [&](int s) { return bars + 8u * (1 + C::MAXSLOTS + s); };
+  const uint32_t ew_done = bars + 8u * (1 + C::MAXSLOTS + C::NSETS);
   const uint32_t acc_done = ew_done + 8u;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::BAR_OFF + C::NBARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -248,7 +254,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
     *abort_flag = ((sbase & 1023u) != 0) ? 1 : 0;
     if (*abort_flag) atomicCAS(&g_status, 0, 399);
     mbar_init(kv_full, 1);
-    for (int s = 0; s < C::NSLOTS; ++s) mbar_init(tiles_full(s), 1);
+    for (int s = 0; s < C::MAXSLOTS; ++s) mbar_init(tiles_full(s), 1);
     for (int s = 0; s < C::NSETS; ++s) mbar_init(sdp_full(s), 1);
     mbar_init(ew_done, NEW);
     mbar_init(acc_done, 1);
@@ -268,6 +274,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   // single window: P^T and dS^T go back into tensor memory over the S^T / dP^T columns they were computed from
   // (bf16 pairs; the half of a warp pair keeps to its own 32 columns) and feed the dV / dK MMAs as TMEM A operands
   const bool use_ts = !DUAL && p.a_in_tmem != 0;
+  const int nslots = (use_ts && p.deep_ring != 0) ? C::MAXSLOTS : C::NSLOTS;
 
   auto iter_head = [&](int it) { return kvh * G + it / steps; };
   auto iter_block = [&](int it) {          // query block of step `it`
@@ -285,14 +292,14 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   };
   auto iter_row0 = [&](int it) { return iter_block(it) * 64; };
   auto iter_student = [&](int it) { return DUAL && (iter_row0(it) + off < n0 + 127 + p.w_s); };
-  auto slot_base = [&](int it) { return sbase + C::RING_OFF + (it % C::NSLOTS) * C::NTILES * C::TILE_BYTES; };
+  auto slot_base = [&](int it) { return sbase + C::RING_OFF + (it % nslots) * C::NTILES * C::TILE_BYTES; };
 
   if (warp == NEW && healthy && n_iters > 0) {
     if (elect_one()) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, false, false);  // [keys x q] = A(K-major) B(K-major)
       constexpr uint32_t idesc_acc = umma_idesc_bf16(128, D, false, true);   // [keys x D] = A(K-major) B(MN-major)
       auto load_tiles = [&](int it) {
-        const int slot = it % C::NSLOTS;
+        const int slot = it % nslots;
         const int h = iter_head(it), r0 = iter_row0(it);
         const bool st = iter_student(it);
         const uint32_t base = slot_base(it);
@@ -379,7 +386,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
         tma_load_3d(sbase + C::K_OFF + d * C::KEY_REGION, halo ? &tma_kh : &tma_k, kv_full, kvh * D + d * 64, krow, b);
         tma_load_3d(sbase + C::V_OFF + d * C::KEY_REGION, halo ? &tma_vh : &tma_v, kv_full, kvh * D + d * 64, krow, b);
       }
-      for (int it = 0; it < C::NSLOTS - 1 && it < n_iters; ++it) load_tiles(it);
+      for (int it = 0; it < nslots - 1 && it < n_iters; ++it) load_tiles(it);
       ok = mbar_wait(kv_full, 0, abort_flag, 301);
       if (ok && C::NSETS == 2) {
         ok = mbar_wait(tiles_full(0), 0, abort_flag, 302);
@@ -389,13 +396,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
         // S/dP for the step the compute warps will need next
         const int nxt = C::NSETS == 2 ? it + 1 : it;
         if (nxt < n_iters) {
-          ok = mbar_wait(tiles_full(nxt % C::NSLOTS), (nxt / C::NSLOTS) & 1, abort_flag, 303);
+          ok = mbar_wait(tiles_full(nxt % nslots), (nxt / nslots) & 1, abort_flag, 303);
           if (!ok) break;
           tc_fence_after_sync();
           issue_sdp(nxt);  // its TMEM set was last read before ew_done(nxt - NSETS), already observed
         }
         // refill the ring: the slot of step it-1 is free once its accumulate MMAs have completed
-        const int pre = it + C::NSLOTS - 1;
+        const int pre = it + nslots - 1;
         if (pre < n_iters) {
           if (it >= 1) ok = mbar_wait(acc_done, (it - 1) & 1, abort_flag, 304);
           if (!ok) break;
@@ -408,7 +415,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       }
       if (!ok) {
         mbar_drain(kv_full, 0);
-        for (int s = 0; s < C::NSLOTS; ++s) { mbar_drain(tiles_full(s), 0); mbar_drain(tiles_full(s), 1); }
+        for (int s = 0; s < nslots; ++s) { mbar_drain(tiles_full(s), 0); mbar_drain(tiles_full(s), 1); }
       }
     }
   } else if (warp < NEW && healthy) {
@@ -548,7 +555,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
 template <int D, bool DUAL>
 struct DqCfg {
   static constexpr int DB = D / 64;
-  static constexpr int NSLOTS = 3;
+  static constexpr int NSLOTS = 3;                 // K/V ring when dS is staged in shared memory
+  // with dS in tensor memory its staging tile and the rest of the 227 KB hold more ring slots: a K/V tile load then
+  // has MAXSLOTS - 2 steps to arrive instead of one
+  static constexpr int MAXSLOTS = DUAL ? 4 : 5;
   static constexpr int SET_COLS = DUAL ? 192 : 128;
   static constexpr int Q_REGION = 128 * 128;
   static constexpr int KV_REGION = 64 * 128;
@@ -558,9 +568,10 @@ struct DqCfg {
   static constexpr int DOS_OFF = DOT_OFF + DB * Q_REGION;                 // only used when DUAL
   static constexpr int RING_OFF = DOS_OFF + (DUAL ? DB * Q_REGION : 0);   // NSLOTS x (K, V)
   static constexpr int DS_OFF = RING_OFF + NSLOTS * 2 * KV_BYTES;         // [128 x 64] bf16
-  static constexpr int BAR_OFF = DS_OFF + Q_REGION;
-  // q_full, kv_full[NSLOTS], sdp_full[2], ew_done, acc_done, a_ready
-  static constexpr int NBARS = 1 + NSLOTS + 2 + 2 + 1;
+  static constexpr int RING_END = RING_OFF + MAXSLOTS * 2 * KV_BYTES;
+  static constexpr int BAR_OFF = RING_END > DS_OFF + Q_REGION ? RING_END : DS_OFF + Q_REGION;
+  // q_full, kv_full[MAXSLOTS], sdp_full[2], ew_done, acc_done, a_ready
+  static constexpr int NBARS = 1 + MAXSLOTS + 2 + 2 + 1;
   // single window: 128 (dQ) + 2 x 128 (S | dP sets) leaves 128 columns: Q and dO as bf16 A operands
   static constexpr int A_COLS = D / 2;
   static constexpr bool CAN_TS = !DUAL;
@@ -579,8 +590,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   const uint32_t bars = sbase + C::BAR_OFF;
   const uint32_t q_full = bars;
   auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
-  auto sdp_full = [&](int s) { return bars + 8u * (1 + C::NSLOTS + s); };
-  const uint32_t ew_done = bars + 8u * (3 + C::NSLOTS);
+  auto sdp_full = [&](int s) { return bars + 8u * (1 + C::MAXSLOTS + s); };
+  const uint32_t ew_done = bars + 8u * (3 + C::MAXSLOTS);
   const uint32_t acc_done = ew_done + 8u;
   const uint32_t a_ready = acc_done + 8u;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::BAR_OFF + C::NBARS * 8);
@@ -622,13 +633,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   };
   auto iter_key0 = [&](int it) { return iter_block(it) * 64; };
   auto iter_student = [&](int it) { return DUAL && !combine && (iter_key0(it) + 63 > qlo - p.w_s); };
-  auto slot_base = [&](int it) { return sbase + C::RING_OFF + (it % C::NSLOTS) * 2 * C::KV_BYTES; };
+  const int nslots = (p.a_in_tmem != 0 && p.deep_ring != 0) ? C::MAXSLOTS : C::NSLOTS;
+  auto slot_base = [&](int it) { return sbase + C::RING_OFF + (it % nslots) * 2 * C::KV_BYTES; };
 
   if (threadIdx.x == 0) {
     *abort_flag = ((sbase & 1023u) != 0) ? 1 : 0;
     if (*abort_flag) atomicCAS(&g_status, 0, 398);
     mbar_init(q_full, 1);
-    for (int s = 0; s < C::NSLOTS; ++s) mbar_init(kv_full(s), 1);
+    for (int s = 0; s < C::MAXSLOTS; ++s) mbar_init(kv_full(s), 1);
     mbar_init(sdp_full(0), 1);
     mbar_init(sdp_full(1), 1);
     mbar_init(ew_done, NEW);
@@ -659,7 +671,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, false, false);
       constexpr uint32_t idesc_acc = umma_idesc_bf16(128, D, false, true);
       auto load_kv = [&](int it) {
-        const int slot = it % C::NSLOTS;
+        const int slot = it % nslots;
         const uint32_t base = slot_base(it);
         mbar_expect_tx(kv_full(slot), 2 * C::KV_BYTES);
         const int key0 = iter_key0(it);
@@ -720,18 +732,18 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         tma_load_3d(sbase + C::DOT_OFF + d * C::Q_REGION, &tma_dot, q_full, h * D + d * 64, m0, b);
         if (DUAL) tma_load_3d(sbase + C::DOS_OFF + d * C::Q_REGION, &tma_dos, q_full, h * D + d * 64, m0, b);
       }
-      for (int it = 0; it < C::NSLOTS - 1 && it < n_iters; ++it) load_kv(it);
+      for (int it = 0; it < nslots - 1 && it < n_iters; ++it) load_kv(it);
       ok = mbar_wait(q_full, 0, abort_flag, 321) && mbar_wait(kv_full(0), 0, abort_flag, 322);
       if (ok && use_ts) ok = mbar_wait(a_ready, 0, abort_flag, 326);      // Q and dO copied into tensor memory
       if (ok) { tc_fence_after_sync(); issue_sdp(0); }
       for (int it = 0; it < n_iters && ok; ++it) {
         if (it + 1 < n_iters) {
-          ok = mbar_wait(kv_full((it + 1) % C::NSLOTS), ((it + 1) / C::NSLOTS) & 1, abort_flag, 323);
+          ok = mbar_wait(kv_full((it + 1) % nslots), ((it + 1) / nslots) & 1, abort_flag, 323);
           if (!ok) break;
           tc_fence_after_sync();
           issue_sdp(it + 1);  // its TMEM set was last read before ew_done(it-1), already observed
         }
-        const int pre = it + C::NSLOTS - 1;
+        const int pre = it + nslots - 1;
         if (pre < n_iters) {
           if (it >= 1) ok = mbar_wait(acc_done, (it - 1) & 1, abort_flag, 324);  // slot of step it-1 is free
           if (!ok) break;
@@ -756,7 +768,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       }
       if (!ok) {
         mbar_drain(q_full, 0);
-        for (int s = 0; s < C::NSLOTS; ++s) { mbar_drain(kv_full(s), 0); mbar_drain(kv_full(s), 1); }
+        for (int s = 0; s < nslots; ++s) { mbar_drain(kv_full(s), 0); mbar_drain(kv_full(s), 1); }
       }
     }
   } else if (warp < NEW && healthy) {
@@ -1112,6 +1124,11 @@ TTCD_EXPORT int ttcd_attn_bwd_cp(const void* q, const void* k, const void* v, co
     return (e != nullptr && e[0] == '0') ? 0 : 1;
   }();
   p.a_in_tmem = a_in_tmem;
+  static const int deep_ring = [] {
+    const char* e = getenv("TTCD_ATTN_BWD_RING");
+    return (e != nullptr && e[0] == '3') ? 0 : 1;
+  }();
+  p.deep_ring = deep_ring;
   // element-wise warps per CTA: 16 (four per scheduler, hides the TMEM-load and MUFU latencies) or 8
   static const int ew_warps = [] {
     const char* e = getenv("TTCD_ATTN_BWD_WARPS");

@@ -97,6 +97,71 @@ def test_tensor_parallel_matches_single_process():
         assert aft[0] < 1e-4, aft
 
 
+def _dp_tp_worker(rank, world, tp_degree, port, ids, ref_loss, ref_norm, ref_after, q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        from ttcd_b200.train.engine import EngineConfig, TrainEngine
+        import ttcd_b200.parallel.tensor as tpmod
+        orig = tpmod.shard_model
+
+        def shard_after_prepare(model, tp):
+            with torch.no_grad():
+                for n, p in model.named_parameters():
+                    if "conv" in n:
+                        p.normal_(0, 0.3, generator=torch.Generator().manual_seed(11))
+            orig(model, tp)
+
+        tpmod.shard_model = shard_after_prepare
+        eng = TrainEngine(IPTTCDv9Config(**KW), EngineConfig(dtype=torch.float32, lr=1e-2, seed=3, activation_checkpoint="none",
+                                                             tensor_parallel=tp_degree, max_norm=1.0), device="cpu")
+        assert eng.sdp.world == world // tp_degree and eng.tp.world == tp_degree
+        dp_rank = rank // tp_degree
+        eng.sdp.zero_grad()
+        loss = eng.forward_backward(ids[dp_rank:dp_rank + 1]).clone()
+        dist.all_reduce(loss)                                   # every replica's loss, tp_degree times each
+        norm = float(eng.sdp.step(1e-2))
+        full = tpmod.gather_full_state_dict(eng.model, eng.tp)
+        after = max(((full[n] - ref_after[n]).abs().max().item(), n) for n in ref_after)
+        q.put((rank, abs(float(loss) / world - ref_loss), abs(norm - ref_norm), after))
+        dist.destroy_process_group()
+    except Exception:  # pragma: no cover
+        import traceback
+        q.put((rank, "error", traceback.format_exc(), 0))
+
+
+@pytest.mark.timeout(400)
+def test_data_parallel_times_tensor_parallel_matches_single_process():
+    """2 data-parallel replicas x 2 tensor-parallel ranks (4 gloo processes), one sequence per replica: loss,
+    clipped gradient norm and the weights after one AdamW step equal the single-process batch of two."""
+    torch.manual_seed(1)
+    ids = torch.randint(0, 256, (2, 128))
+    from ttcd_b200.train.engine import EngineConfig, TrainEngine
+    eng = TrainEngine(IPTTCDv9Config(**KW), EngineConfig(dtype=torch.float32, lr=1e-2, seed=3, activation_checkpoint="none",
+                                                         max_norm=1.0), device="cpu")
+    _prepare(eng)
+    eng.sdp.zero_grad()
+    loss = float(eng.forward_backward(ids))
+    ref_norm = float(eng.sdp.step(1e-2))
+    after = {n: p.detach().clone() for n, p in eng.model.named_parameters()}
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    procs = [ctx.Process(target=_dp_tp_worker, args=(r, 4, 2, port, ids, loss, ref_norm, after, q)) for r in range(4)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(30)
+    for rank, dloss, dnorm, aft in results:
+        assert dloss != "error", dnorm
+        assert dloss < 1e-4, (rank, dloss)
+        assert dnorm < 1e-3 * max(1.0, ref_norm), (rank, dnorm, ref_norm)
+        assert aft[0] < 1e-4, (rank, aft)
+
+
 def _trainer_rank(rank, world, port, folder, steps, q):
     try:
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),

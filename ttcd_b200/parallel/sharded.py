@@ -280,6 +280,24 @@ class ShardedDataParallel:
     def _local_grad(self, g: ParamGroup) -> torch.Tensor:
         return g.grad_shard if self.world > 1 else g.flat_grad[:g.numel]
 
+    def local_grad_slices(self, params) -> list[torch.Tensor]:
+        """Views of this rank's (reduced) gradient shard that belong to ``params``, in group order.  Ranks with the
+        same position in different data-parallel groups get slices of the same elements."""
+        wanted = {id(p) for p in params}
+        out = []
+        for g in self.groups:
+            shard = g.numel // self.world
+            lo = self.rank * shard if self.world > 1 else 0
+            hi = lo + shard
+            grad = self._local_grad(g)
+            for p, off in zip(g.params, g.offsets):
+                if id(p) not in wanted:
+                    continue
+                a, b = max(off, lo), min(off + p.numel(), hi)
+                if a < b:
+                    out.append(grad[a - lo:b - lo])
+        return out
+
     @torch.no_grad()
     def step(self, lr: float | None = None) -> torch.Tensor:
         """Clip (global norm), AdamW on the local shards, publish bf16 params.  Returns the grad norm

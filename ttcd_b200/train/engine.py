@@ -90,12 +90,20 @@ class TrainEngine:
             from ..parallel import context as _ctx
             _ctx.configure(self, tensor_parallel=self.cfg.tensor_parallel, context_parallel=self.cfg.context_parallel)
         self.tp = getattr(self, "tp", None)
+        self._tp_dp = False
         if self.tp is not None:
-            if self.tp.world != dist.get_world_size():
-                raise NotImplementedError("tensor parallelism combined with data parallelism is not supported yet")
             if self.cfg.enable_muon:
                 raise NotImplementedError("Muon needs whole matrices; it is not available with tensor parallelism")
+            world, rank = dist.get_world_size(), dist.get_rank()
             process_group = False           # every rank optimises its own weight shards
+            if self.tp.world != world:
+                # data parallel x tensor parallel: consecutive ranks form a tensor-parallel group, ranks with the
+                # same position in their group hold the same weight shards and form a sharded data-parallel group
+                for t in range(self.tp.world):
+                    g = dist.new_group(list(range(t, world, self.tp.world)))
+                    if rank % self.tp.world == t:
+                        process_group = g
+                self._tp_dp = True
         multi = process_group is not False and dist.is_initialized() and dist.get_world_size(process_group) > 1
         runtime = ShardedDataParallel
         if self.cfg.replicate and multi:
@@ -187,7 +195,8 @@ class TrainEngine:
         dist.all_reduce(n_total, group=tp.group)
         share = n_local / n_total.clamp_min(1.0)
         (out.loss * (share * scale)).backward()
-        all_reduce_replicated_grads(self.model, tp)
+        if not self._tp_dp:                 # with data parallelism the reduced shards are summed instead (_tp_norm_sq)
+            all_reduce_replicated_grads(self.model, tp)
         global_loss = out.loss.detach() * share
         dist.all_reduce(global_loss, group=tp.group)
         self.tokens_seen += ids.numel()
@@ -195,15 +204,37 @@ class TrainEngine:
 
     def _tp_norm_sq(self, norm_sq: torch.Tensor) -> None:
         """Global gradient norm under tensor parallelism: sharded weights contribute from every rank,
-        replicated ones (identical after their all-reduce) once."""
+        replicated ones (identical after their all-reduce) once.
+
+        Combined with data parallelism the gradients have already been reduce-scattered over the data-parallel
+        group when this runs, so the sum of the replicated parameters' gradients over the tensor-parallel group is
+        taken here, on this rank's slice of the reduced gradient (1/dp of the bytes), before the optimizer reads it."""
         from ..parallel.tensor import replicated_parameters
-        rep = torch.zeros_like(norm_sq)
-        for p in replicated_parameters(self.model):
-            if p.grad is not None:
-                rep += p.grad.float().pow(2).sum()
-        sharded = norm_sq - rep
+        rep_params = replicated_parameters(self.model)
+        if not self._tp_dp:
+            rep = torch.zeros_like(norm_sq)
+            for p in rep_params:
+                if p.grad is not None:
+                    rep += p.grad.float().pow(2).sum()
+            sharded = norm_sq - rep
+            dist.all_reduce(sharded, group=self.tp.group)
+            norm_sq.copy_(sharded + rep)
+            return
+        pieces = self.sdp.local_grad_slices(rep_params)
+        flat = torch.cat([x.reshape(-1) for x in pieces]) if pieces else norm_sq.new_zeros(0)
+        stats = torch.zeros(2, dtype=torch.float32, device=norm_sq.device)
+        stats[0] = flat.float().pow(2).sum()
+        dist.all_reduce(flat, group=self.tp.group)
+        stats[1] = flat.float().pow(2).sum()
+        off = 0
+        for x in pieces:
+            x.copy_(flat[off:off + x.numel()].view_as(x))
+            off += x.numel()
+        if self.sdp.world > 1:
+            dist.all_reduce(stats, group=self.sdp.pg)
+        sharded = norm_sq - stats[0]
         dist.all_reduce(sharded, group=self.tp.group)
-        norm_sq.copy_(sharded + rep)
+        norm_sq.copy_(sharded + stats[1])
 
     def train_step(self, input_ids: torch.Tensor, labels: torch.Tensor | None = None, lr: float | None = None,
                    return_loss_on_host: bool = True, **model_kwargs):
