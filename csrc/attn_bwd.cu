@@ -25,9 +25,11 @@
 
 namespace ttcd {
 
-// NEW element-wise warps (8 or 16) + 1 control warp.  A warp may only touch the TMEM lanes of its quarter
-// (warp % 4), so the NEW / 4 warps of a quarter split the 64 S columns of a step between them.
-constexpr int bwd_threads(int n_ew) { return (n_ew + 1) * 32; }
+// NEW element-wise warps + 1 tensor-core issue warp + 1 TMA producer warp (one elected thread each: a thread that
+// issued the copies as well spent more clocks per step on them than the tensor core needs for the step).  A warp may only touch the TMEM lanes of its quarter (warp % 4); two
+// warps per quarter split the 64 S columns of a step.  NEW == 8: one group does every step.  NEW == 16: two such
+// groups take alternate steps (needs two S / dP sets and P / dS kept in tensor memory).
+constexpr int bwd_threads(int n_ew) { return (n_ew + 2) * 32; }
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ float ex2(float x) {
@@ -40,12 +42,23 @@ __device__ __forceinline__ void named_barrier_sync(int id, int count) {
 }
 
 // TMEM column offset (inside an S / dP column group of 64) of the 8 packed bf16 columns that hold k-step `k` (16
-// rows of the contraction) when each of NEW / 4 warps per quarter packs its 64 / (NEW / 4) columns in place
-template <int NEW>
+// rows of the contraction): each of the two warps of a lane quarter packs its 32 columns in place into 16
 __device__ __forceinline__ constexpr uint32_t ts_packed_off(int k) {
-  constexpr int NC = 64 / (NEW / 4);
-  return static_cast<uint32_t>(((16 * k) / NC) * NC + ((16 * k) % NC) / 2);
+  return static_cast<uint32_t>(32 * (k / 2) + 8 * (k % 2));
 }
+
+// Division of a step index by a per-CTA constant (steps per head, ring slots) without the integer-division
+// sequence: exact for n, d < 65536 with magic = 2^32 / d + 1.  The control thread runs this several times between
+// two tensor-core issues, where every instruction of latency is idle tensor time.
+struct FastDiv {
+  uint32_t d, magic;
+  __device__ __forceinline__ explicit FastDiv(int div) : d(static_cast<uint32_t>(div < 1 ? 1 : div)), magic(0xffffffffu / d + 1u) {}
+  __device__ __forceinline__ int div(int n) const {
+    return (n < 65536 && d < 65536u && d > 1u) ? static_cast<int>(__umulhi(static_cast<uint32_t>(n), magic))
+                                     : static_cast<int>(static_cast<uint32_t>(n) / d);
+  }
+  __device__ __forceinline__ int mod(int n) const { return n - div(n) * static_cast<int>(d); }
+};
 
 struct AttnBwdParams {
   const float* lse_t; const float* lse_s;      // [B, H, Tq] natural log
@@ -60,6 +73,10 @@ struct AttnBwdParams {
   int a_in_tmem;
   // with operands in tensor memory the freed staging tiles become extra TMA ring slots (0: keep the 3-slot ring)
   int deep_ring;
+  // optional timeline probe: when non-null, one CTA in the middle of the grid writes clock64() stamps of steps
+  // [8, 24) here, 16 slots per step (0-4 control thread, 5-8 first element-wise warp of the step's group)
+  long long* probe;
+  int probe_mask;      // bit e set: event e is stamped (every stamp costs the stamping thread ~100 clocks)
   // dV may be written into a wider row (the packed q|k|v gradient of a fused projection): row and batch strides
   // in elements; 0 = contiguous [B, Tk, HK, D]
   int64_t ld_dv, sb_dv;
@@ -195,10 +212,10 @@ struct DkdvCfg {
   static constexpr int PT_OFF = RING_OFF + NSLOTS * NTILES * TILE_BYTES;
   static constexpr int PS_OFF = PT_OFF + KEY_REGION;                  // only used when DUAL
   static constexpr int DS_OFF = PS_OFF + (DUAL ? KEY_REGION : 0);
-  static constexpr int VEC_OFF = DS_OFF + KEY_REGION;                 // 2 slots x 4 vectors x 64 floats
-  static constexpr int BAR_OFF = VEC_OFF + 2 * 4 * 64 * 4;
-  // kv_full, tiles_full[MAXSLOTS], sdp_full[NSETS], ew_done, acc_done
-  static constexpr int NBARS = 1 + MAXSLOTS + NSETS + 2;
+  static constexpr int VEC_OFF = DS_OFF + KEY_REGION;                 // 4 slots x 4 vectors x 64 floats
+  static constexpr int BAR_OFF = VEC_OFF + 4 * 4 * 64 * 4;
+  // kv_full, tiles_full[MAXSLOTS], sdp_full[NSETS], ew_done[2], acc_done, all_done, slot_free[MAXSLOTS]
+  static constexpr int NBARS = 1 + MAXSLOTS + NSETS + 4 + MAXSLOTS;
   static_assert(DUAL || 2 * KEY_REGION >= NTILES * TILE_BYTES, "the staging tiles must hold one more ring slot");
   static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16;
 };
@@ -216,8 +233,14 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   const uint32_t kv_full = bars;
   auto tiles_full = [&](int s) { return bars + 8u * (1 + s); };
   auto sdp_full = [&](int s) { return bars + 8u * (1 + C::MAXSLOTS + s); };
-  const uint32_t ew_done = bars + 8u * (1 + C::MAXSLOTS + C::NSETS);
-  const uint32_t acc_done = ew_done + 8u;
+  // NEW == 16: two groups of eight element-wise warps take alternate steps (group g the steps of TMEM set g), so
+  // the element-wise work of step i+1 starts as soon as its S / dP are there instead of after step i's
+  constexpr bool PP = NEW == 16;
+  static_assert(!PP || C::NSETS == 2, "alternating groups need two S / dP sets");
+  auto ew_done = [&](int g) { return bars + 8u * (1 + C::MAXSLOTS + C::NSETS + g); };
+  const uint32_t acc_done = ew_done(2);
+  const uint32_t all_done = acc_done + 8u;
+  auto slot_free = [&](int s) { return all_done + 8u * (1 + s); };   // the MMAs that read ring slot s have completed
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::BAR_OFF + C::NBARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* vecs = reinterpret_cast<float*>(smem + C::VEC_OFF);
@@ -256,8 +279,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
     mbar_init(kv_full, 1);
     for (int s = 0; s < C::MAXSLOTS; ++s) mbar_init(tiles_full(s), 1);
     for (int s = 0; s < C::NSETS; ++s) mbar_init(sdp_full(s), 1);
-    mbar_init(ew_done, NEW);
+    mbar_init(ew_done(0), 8);
+    mbar_init(ew_done(1), 8);
     mbar_init(acc_done, 1);
+    mbar_init(all_done, 1);
+    for (int s = 0; s < C::MAXSLOTS; ++s) mbar_init(slot_free(s), 1);
     mbar_fence_init();
   }
   if (warp == NEW) {
@@ -275,36 +301,40 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   // (bf16 pairs; the half of a warp pair keeps to its own 32 columns) and feed the dV / dK MMAs as TMEM A operands
   const bool use_ts = !DUAL && p.a_in_tmem != 0;
   const int nslots = (use_ts && p.deep_ring != 0) ? C::MAXSLOTS : C::NSLOTS;
+  const bool probing = p.probe != nullptr && blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && blockIdx.z == 0;
+  auto stamp = [&](int it, int ev) {
+    if (probing && it >= 8 && it < 24 && ((p.probe_mask >> ev) & 1)) p.probe[(it - 8) * 16 + ev] = clock64();
+  };
 
-  auto iter_head = [&](int it) { return kvh * G + it / steps; };
+  const FastDiv by_steps(steps), by_slots(nslots);
+  auto iter_head = [&](int it) { return kvh * G + by_steps.div(it); };
   auto iter_block = [&](int it) {          // query block of step `it`
-    const int s = it % steps;
+    const int s = by_steps.mod(it);
     if (s < pre) return jb_lo + s;
     if (s < pre + 2 * nb) return jb1 + (s - pre) / 2;
     return jb_lo + s - nb;
   };
   auto iter_inner = [&](int it) {          // combined mode: 1 = student part (dO', delta'), 0 = teacher-only part
     if (!combine) return 0;
-    const int s = it % steps;
+    const int s = by_steps.mod(it);
     if (s < pre) return 1;
     if (s < pre + 2 * nb) return ((s - pre) & 1) ? 0 : 1;
     return 0;
   };
   auto iter_row0 = [&](int it) { return iter_block(it) * 64; };
   auto iter_student = [&](int it) { return DUAL && (iter_row0(it) + off < n0 + 127 + p.w_s); };
-  auto slot_base = [&](int it) { return sbase + C::RING_OFF + (it % nslots) * C::NTILES * C::TILE_BYTES; };
+  auto slot_base = [&](int it) { return sbase + C::RING_OFF + by_slots.mod(it) * C::NTILES * C::TILE_BYTES; };
 
-  if (warp == NEW && healthy && n_iters > 0) {
+  if (warp == NEW + 1 && healthy && n_iters > 0) {
+    // ---- TMA producer: K/V of this key block once, then the Q / dO tiles of every step through the ring
     if (elect_one()) {
-      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, false, false);  // [keys x q] = A(K-major) B(K-major)
-      constexpr uint32_t idesc_acc = umma_idesc_bf16(128, D, false, true);   // [keys x D] = A(K-major) B(MN-major)
       auto load_tiles = [&](int it) {
-        const int slot = it % nslots;
+        const int slot = by_slots.mod(it);
         const int h = iter_head(it), r0 = iter_row0(it);
         const bool st = iter_student(it);
         const uint32_t base = slot_base(it);
         mbar_expect_tx(tiles_full(slot), C::TILE_BYTES * (st ? 3 : 2));
-#pragma unroll
+    #pragma unroll
         for (int d = 0; d < C::DB; ++d) {
           tma_load_3d(base + d * C::ROW_REGION, &tma_q, tiles_full(slot), h * D + d * 64, r0, b);
           tma_load_3d(base + C::TILE_BYTES + d * C::ROW_REGION, iter_inner(it) ? &tma_dos : &tma_dot, tiles_full(slot),
@@ -313,70 +343,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
             tma_load_3d(base + 2 * C::TILE_BYTES + d * C::ROW_REGION, &tma_dos, tiles_full(slot), h * D + d * 64, r0, b);
         }
       };
-      auto issue_sdp = [&](int it) {
-        const bool st = iter_student(it);
-        const uint32_t sq = slot_base(it), sdot = sq + C::TILE_BYTES, sdos = sq + 2 * C::TILE_BYTES;
-        const uint32_t ts = t_set(it);
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t ko = (k / 4) * C::KEY_REGION + (k % 4) * 32;
-          const uint32_t ro = (k / 4) * C::ROW_REGION + (k % 4) * 32;
-          umma_ss(ts, umma_desc_sw128(sbase + C::K_OFF + ko, 16, 1024), umma_desc_sw128(sq + ro, 16, 1024), idesc_s,
-                  k != 0);
-        }
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t ko = (k / 4) * C::KEY_REGION + (k % 4) * 32;
-          const uint32_t ro = (k / 4) * C::ROW_REGION + (k % 4) * 32;
-          umma_ss(ts + 64, umma_desc_sw128(sbase + C::V_OFF + ko, 16, 1024), umma_desc_sw128(sdot + ro, 16, 1024),
-                  idesc_s, k != 0);
-        }
-        if (DUAL && st) {
-#pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint32_t ko = (k / 4) * C::KEY_REGION + (k % 4) * 32;
-            const uint32_t ro = (k / 4) * C::ROW_REGION + (k % 4) * 32;
-            umma_ss(ts + 128, umma_desc_sw128(sbase + C::V_OFF + ko, 16, 1024), umma_desc_sw128(sdos + ro, 16, 1024),
-                    idesc_s, k != 0);
-          }
-        }
-        umma_commit(sdp_full(it % C::NSETS));
-      };
-      auto issue_acc = [&](int it) {
-        const bool st = iter_student(it);
-        const uint32_t sq = slot_base(it), sdot = sq + C::TILE_BYTES, sdos = sq + 2 * C::TILE_BYTES;
-        if (use_ts) {
-          const uint32_t ts = t_set(it);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {     // 16 queries = 8 packed columns at the start of their warp's column group
-            const uint32_t a_off = ts_packed_off<NEW>(k);
-            umma_ts(t_dv, ts + a_off, umma_desc_sw128(sdot + k * 2048, C::ROW_REGION, 1024), idesc_acc, (it | k) != 0);
-          }
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint32_t a_off = 64 + ts_packed_off<NEW>(k);
-            umma_ts(t_dk, ts + a_off, umma_desc_sw128(sq + k * 2048, C::ROW_REGION, 1024), idesc_acc, (it | k) != 0);
-          }
-          umma_commit(acc_done);
-          return;
-        }
-#pragma unroll
-        for (int k = 0; k < 4; ++k)  // contraction over the 64 query rows
-          umma_ss(t_dv, umma_desc_sw128(sbase + C::PT_OFF + k * 32, 16, 1024),
-                  umma_desc_sw128(sdot + k * 2048, C::ROW_REGION, 1024), idesc_acc, (it | k) != 0);
-        if (DUAL && st) {
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_ss(t_dv, umma_desc_sw128(sbase + C::PS_OFF + k * 32, 16, 1024),
-                    umma_desc_sw128(sdos + k * 2048, C::ROW_REGION, 1024), idesc_acc, 1u);
-        }
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          umma_ss(t_dk, umma_desc_sw128(sbase + C::DS_OFF + k * 32, 16, 1024),
-                  umma_desc_sw128(sq + k * 2048, C::ROW_REGION, 1024), idesc_acc, (it | k) != 0);
-        umma_commit(acc_done);
-      };
-
       bool ok = true;
       mbar_expect_tx(kv_full, 2 * C::DB * C::KEY_REGION);
 #pragma unroll
@@ -386,7 +352,90 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
         tma_load_3d(sbase + C::K_OFF + d * C::KEY_REGION, halo ? &tma_kh : &tma_k, kv_full, kvh * D + d * 64, krow, b);
         tma_load_3d(sbase + C::V_OFF + d * C::KEY_REGION, halo ? &tma_vh : &tma_v, kv_full, kvh * D + d * 64, krow, b);
       }
-      for (int it = 0; it < nslots - 1 && it < n_iters; ++it) load_tiles(it);
+      for (int it = 0; it < n_iters && ok; ++it) {
+        if (it >= nslots) {                 // the slot's previous tiles (step it - nslots) have been consumed
+          ok = mbar_wait(slot_free(by_slots.mod(it)), (by_slots.div(it) - 1) & 1, abort_flag, 304);
+          if (!ok) break;
+        }
+        load_tiles(it);
+      }
+      // stay until every copy has been consumed (or the CTA gave up): no copy may be in flight at exit
+      if (ok) ok = mbar_wait(all_done, 0, abort_flag, 306);
+      if (!ok) {
+        mbar_drain(kv_full, 0);
+        for (int s = 0; s < nslots; ++s) { mbar_drain(tiles_full(s), 0); mbar_drain(tiles_full(s), 1); }
+      }
+    }
+  } else if (warp == NEW && healthy && n_iters > 0) {
+    // ---- tensor-core issue
+    if (elect_one()) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, false, false);  // [keys x q] = A(K-major) B(K-major)
+      constexpr uint32_t idesc_acc = umma_idesc_bf16(128, D, false, true);   // [keys x D] = A(K-major) B(MN-major)
+      // descriptors as (low word + constant step, constant high word): one add per k-step on this thread
+      constexpr uint32_t HI = umma_desc_hi_sw128(1024);
+      const uint32_t k_lo = umma_desc_lo(sbase + C::K_OFF, 16), v_lo = umma_desc_lo(sbase + C::V_OFF, 16);
+      const uint32_t pt_lo = umma_desc_lo(sbase + C::PT_OFF, 16), ps_lo = umma_desc_lo(sbase + C::PS_OFF, 16);
+      const uint32_t ds_lo = umma_desc_lo(sbase + C::DS_OFF, 16);
+      auto issue_sdp = [&](int it) {
+        const bool st = iter_student(it);
+        const uint32_t sq = slot_base(it);
+        const uint32_t q_lo = umma_desc_lo(sq, 16), dot_lo = q_lo + (C::TILE_BYTES >> 4), dos_lo = q_lo + (2 * C::TILE_BYTES >> 4);
+        const uint32_t ts = t_set(it);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t ko = ((k / 4) * C::KEY_REGION + (k % 4) * 32) >> 4;
+          const uint32_t ro = ((k / 4) * C::ROW_REGION + (k % 4) * 32) >> 4;
+          umma_ss(ts, umma_desc_join(k_lo + ko, HI), umma_desc_join(q_lo + ro, HI), idesc_s, k != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t ko = ((k / 4) * C::KEY_REGION + (k % 4) * 32) >> 4;
+          const uint32_t ro = ((k / 4) * C::ROW_REGION + (k % 4) * 32) >> 4;
+          umma_ss(ts + 64, umma_desc_join(v_lo + ko, HI), umma_desc_join(dot_lo + ro, HI), idesc_s, k != 0);
+        }
+        if (DUAL && st) {
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t ko = ((k / 4) * C::KEY_REGION + (k % 4) * 32) >> 4;
+            const uint32_t ro = ((k / 4) * C::ROW_REGION + (k % 4) * 32) >> 4;
+            umma_ss(ts + 128, umma_desc_join(v_lo + ko, HI), umma_desc_join(dos_lo + ro, HI), idesc_s, k != 0);
+          }
+        }
+        umma_commit(sdp_full(it % C::NSETS));
+      };
+      auto issue_acc = [&](int it) {
+        const bool st = iter_student(it);
+        const uint32_t sq = slot_base(it);
+        // Q / dO tiles as MN-major B operands: 64 rows of the contraction, the next 64 columns ROW_REGION bytes on
+        const uint32_t qm_lo = umma_desc_lo(sq, C::ROW_REGION), dotm_lo = qm_lo + (C::TILE_BYTES >> 4);
+        const uint32_t dosm_lo = qm_lo + (2 * C::TILE_BYTES >> 4);
+        const uint32_t acc = it != 0;
+        if (use_ts) {
+          const uint32_t ts = t_set(it);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)       // 16 queries = 8 packed columns at the start of their warp's column group
+            umma_ts(t_dv, ts + ts_packed_off(k), umma_desc_join(dotm_lo + k * (2048 >> 4), HI), idesc_acc, acc | (k != 0));
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_ts(t_dk, ts + 64 + ts_packed_off(k), umma_desc_join(qm_lo + k * (2048 >> 4), HI), idesc_acc, acc | (k != 0));
+          if (!PP) umma_commit(acc_done);   // only the single-group element-wise warps wait on it
+          return;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k)  // contraction over the 64 query rows
+          umma_ss(t_dv, umma_desc_join(pt_lo + k * 2, HI), umma_desc_join(dotm_lo + k * (2048 >> 4), HI), idesc_acc, acc | (k != 0));
+        if (DUAL && st) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_ss(t_dv, umma_desc_join(ps_lo + k * 2, HI), umma_desc_join(dosm_lo + k * (2048 >> 4), HI), idesc_acc, 1u);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_ss(t_dk, umma_desc_join(ds_lo + k * 2, HI), umma_desc_join(qm_lo + k * (2048 >> 4), HI), idesc_acc, acc | (k != 0));
+        umma_commit(acc_done);
+      };
+
+      bool ok = true;
       ok = mbar_wait(kv_full, 0, abort_flag, 301);
       if (ok && C::NSETS == 2) {
         ok = mbar_wait(tiles_full(0), 0, abort_flag, 302);
@@ -396,78 +445,90 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
         // S/dP for the step the compute warps will need next
         const int nxt = C::NSETS == 2 ? it + 1 : it;
         if (nxt < n_iters) {
-          ok = mbar_wait(tiles_full(nxt % nslots), (nxt / nslots) & 1, abort_flag, 303);
+          ok = mbar_wait(tiles_full(by_slots.mod(nxt)), by_slots.div(nxt) & 1, abort_flag, 303);
           if (!ok) break;
+          stamp(it, 0);
           tc_fence_after_sync();
           issue_sdp(nxt);  // its TMEM set was last read before ew_done(nxt - NSETS), already observed
+          stamp(it, 1);
         }
-        // refill the ring: the slot of step it-1 is free once its accumulate MMAs have completed
-        const int pre = it + nslots - 1;
-        if (pre < n_iters) {
-          if (it >= 1) ok = mbar_wait(acc_done, (it - 1) & 1, abort_flag, 304);
-          if (!ok) break;
-          load_tiles(pre);
-        }
-        ok = mbar_wait(ew_done, it & 1, abort_flag, 305);
+        stamp(it, 2);
+        ok = PP ? mbar_wait(ew_done(it & 1), (it >> 1) & 1, abort_flag, 305) : mbar_wait(ew_done(0), it & 1, abort_flag, 305);
         if (!ok) break;
+        stamp(it, 3);
         tc_fence_after_sync();
         issue_acc(it);
+        umma_commit(slot_free(by_slots.mod(it)));   // the producer may refill this step's ring slot
+        stamp(it, 4);
       }
-      if (!ok) {
-        mbar_drain(kv_full, 0);
-        for (int s = 0; s < nslots; ++s) { mbar_drain(tiles_full(s), 0); mbar_drain(tiles_full(s), 1); }
-      }
+      if (ok) umma_commit(all_done);      // every accumulate MMA has completed when this arrives
     }
   } else if (warp < NEW && healthy) {
-    constexpr int PARTS = NEW / 4;              // warps per TMEM lane quarter
-    constexpr int NC = 64 / PARTS;              // S^T columns (queries) of a step per thread
-    const int quarter = warp & 3, part = warp >> 2;
+    constexpr int NPASS = PP ? 2 : 1;
+    constexpr int NC = 32 / NPASS;              // S^T columns (queries) per pass; a thread owns 32 of a step
+    constexpr int STEP = PP ? 2 : 1;
+    const int grp = PP ? (warp >> 3) : 0;       // this warp's group takes steps grp, grp + STEP, ...
+    const int quarter = warp & 3, part = (warp >> 2) & 1;
     const int krow = quarter * 32 + lane;       // key row inside the block == TMEM lane
     const int key = n0 + krow;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    const int ctid = threadIdx.x;               // 0 .. 32 NEW - 1; the first 256 fetch the row statistics
+    const int ctid = threadIdx.x & 255;         // thread of the group: fetches one row statistic per step
+    // statistics slot of a step: the two groups own two slots each
+    auto vslot_of = [&](int it) { return vecs + (PP ? ((it & 1) * 2 + ((it >> 1) & 1)) : (it & 1)) * 256; };
     bool ok = true;
     auto wait_all = [&](uint32_t bar, uint32_t parity, int code) {
       const bool r = mbar_wait(bar, parity, abort_flag, code);
       return __all_sync(0xffffffffu, r) != 0;
     };
     // per-row statistics of a query block: [-lse_t*log2e | delta_t | -lse_s*log2e | delta_s], 64 each;
-    // this thread fetches element (which, r) of the block used by step `it`
+    // this thread fetches element (which, r) of the block used by step `it`.  The load is issued here and its
+    // value is first touched by finish_stat at the end of the step, so that its latency is not waited out here.
+    const int which = ctid >> 6;
+    const bool stat_is_lse = which == 0 || which == 2;
     auto fetch_stat = [&](int it) -> float {
-      const int which = ctid >> 6, r = ctid & 63;
-      const int row = iter_row0(it) + r;
+      const int row = iter_row0(it) + (ctid & 63);
       const int64_t idx = (static_cast<int64_t>(b) * p.H + iter_head(it)) * p.Tq + row;
-      if (row >= p.Tq) return (which == 0 || which == 2) ? -INFINITY : 0.f;  // p = 0 past the end
-      if (which == 0) return -p.lse_t[idx] * LOG2E;
-      if (which == 1) return iter_inner(it) ? p.delta_s[idx] : p.delta_t[idx];
-      if (!DUAL || !iter_student(it)) return 0.f;
-      return which == 2 ? -p.lse_s[idx] * LOG2E : p.delta_s[idx];
+      const float* src = which == 0 ? p.lse_t : which == 1 ? (iter_inner(it) ? p.delta_s : p.delta_t)
+                                                : which == 2 ? p.lse_s : p.delta_s;
+      const bool live = row < p.Tq && (which < 2 || (DUAL && iter_student(it)));
+      float raw = (stat_is_lse && row >= p.Tq) ? INFINITY : 0.f;      // p = 0 past the end (after the negation below)
+      if (live) raw = src[idx];
+      return raw;
     };
-    if (n_iters > 0 && ctid < 256) vecs[ctid] = fetch_stat(0);
-    for (int it = 0; it < n_iters && ok; ++it) {
+    auto finish_stat = [&](float raw) { return stat_is_lse ? -raw * LOG2E : raw; };
+    if (grp < n_iters) vslot_of(grp)[ctid] = finish_stat(fetch_stat(grp));
+    for (int it = grp; it < n_iters && ok; it += STEP) {
       const int r0 = iter_row0(it);
       const bool st = iter_student(it);
-      const float* vslot = vecs + (it & 1) * 256;
-      const float next_stat = (it + 1 < n_iters && ctid < 256) ? fetch_stat(it + 1) : 0.f;  // in flight during this step
-      named_barrier_sync(1, NEW * 32);
+      const float* vslot = vslot_of(it);
+      const float next_stat = (it + STEP < n_iters) ? fetch_stat(it + STEP) : 0.f;  // in flight during this step
+      const bool stamper = (warp & 7) == 0 && lane == 0;
+      if (stamper) stamp(it, 5);
+      named_barrier_sync(1 + grp, 256);
       ok = wait_all(sdp_full(it % C::NSETS), (it / C::NSETS) & 1, 311);
       if (!ok) break;
+      if (stamper) stamp(it, 6);
       tc_fence_after_sync();
-      const uint32_t ts = t_set(it) + lane_addr + part * NC;
-      uint32_t sv[NC], dpt[NC], dps[NC];
-      tmem_ld_n<NC>(ts, sv);
-      tmem_ld_n<NC>(ts + 64, dpt);
-      if (DUAL && st) tmem_ld_n<NC>(ts + 128, dps);
-      tmem_ld_wait();
-      uint32_t ptp[NC / 2], psp[NC / 2], dsp[NC / 2];
-      {
-        const int qlo_b = r0 + off, qhi_b = r0 + 63 + off;
-        // fully visible block: every (key, query) pair is inside the teacher (and student) window
-        const bool full_t = (n0 + 127 <= qlo_b) && (n0 > qhi_b - p.w_t) && (n0 + 127 < p.Tk);
-        const bool full_s = (n0 > qhi_b - p.w_s);
-        const float* stats = vslot + part * NC;
-        const int qpos0 = r0 + part * NC + off;
-        const bool key_ok = key < p.Tk;
+      const uint32_t ts = t_set(it) + lane_addr + part * 32;      // (alternating groups: set == grp)
+      const int qlo_b = r0 + off, qhi_b = r0 + 63 + off;
+      // fully visible block: every (key, query) pair is inside the teacher (and student) window
+      const bool full_t = (n0 + 127 <= qlo_b) && (n0 > qhi_b - p.w_t) && (n0 + 127 < p.Tk);
+      const bool full_s = (n0 > qhi_b - p.w_s);
+      const bool key_ok = key < p.Tk;
+      if (!PP && !use_ts && it >= 1) {
+        ok = wait_all(acc_done, (it - 1) & 1, 312);  // the P / dS staging tiles are free again
+        if (!ok) break;
+      }
+#pragma unroll
+      for (int h = 0; h < NPASS; ++h) {       // alternating groups: two passes of 16 columns keep the registers low
+        uint32_t sv[NC], dpt[NC], dps[NC];
+        tmem_ld_n<NC>(ts + h * NC, sv);
+        tmem_ld_n<NC>(ts + 64 + h * NC, dpt);
+        if (DUAL && st) tmem_ld_n<NC>(ts + 128 + h * NC, dps);
+        tmem_ld_wait();
+        uint32_t ptp[NC / 2], psp[NC / 2], dsp[NC / 2];
+        const float* stats = vslot + part * 32 + h * NC;
+        const int qpos0 = r0 + part * 32 + h * NC + off;
         if (DUAL && st) {
           if (full_t && full_s)
             dkdv_elementwise<false, true, NC>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, p.w_t, p.w_s, key_ok, ptp, psp, dsp);
@@ -489,53 +550,67 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
           else
             dkdv_elementwise<true, false, NC>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, p.w_t, p.w_s, key_ok, ptp, psp, dsp);
         }
+        if (use_ts) {
+          // packed over the first half of this thread's own S^T / dP^T columns, all of which (up to this pass) are read
+          tmem_st_n<NC / 2>(ts + h * (NC / 2), ptp);
+          tmem_st_n<NC / 2>(ts + 64 + h * (NC / 2), dsp);
+        } else {
+          store_row_part_packed<NC / 2>(smem + C::PT_OFF, krow, part * NPASS + h, ptp);
+          if (DUAL && st) store_row_part_packed<NC / 2>(smem + C::PS_OFF, krow, part * NPASS + h, psp);
+          store_row_part_packed<NC / 2>(smem + C::DS_OFF, krow, part * NPASS + h, dsp);
+        }
       }
       if (use_ts) {
-        tmem_st_n<NC / 2>(ts, ptp);        // over this thread's own S^T columns (already read)
-        tmem_st_n<NC / 2>(ts + 64, dsp);   // over its dP^T columns
         tmem_st_wait();
+        if (!PP && it >= 1) {
+          ok = wait_all(acc_done, (it - 1) & 1, 312);  // keeps this warp's phase count of the barrier in step
+          if (!ok) break;
+        }
       }
-      if (it >= 1) {
-        ok = wait_all(acc_done, (it - 1) & 1, 312);  // P / dS tiles are free again (keeps the phase count in step)
-        if (!ok) break;
-      }
-      if (!use_ts) {
-        store_row_part_packed<NC / 2>(smem + C::PT_OFF, krow, part, ptp);
-        if (DUAL && st) store_row_part_packed<NC / 2>(smem + C::PS_OFF, krow, part, psp);
-        store_row_part_packed<NC / 2>(smem + C::DS_OFF, krow, part, dsp);
-      }
-      if (ctid < 256) vecs[((it + 1) & 1) * 256 + ctid] = next_stat;
+      if (stamper) stamp(it, 7);
+      vslot_of(it + STEP)[ctid] = finish_stat(next_stat);
       fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(ew_done);
+      if (lane == 0) mbar_arrive(ew_done(PP ? (it & 1) : 0));
+      if (stamper) stamp(it, 8);
     }
-    // epilogue: dK, dV -> global (this thread: key row `krow`, one half of the D columns)
+    // epilogue: dK, dV -> global (this thread: key row `krow`, one half of the D columns; with alternating groups
+    // group 0 writes dK and group 1 dV)
     if (ok) {
-      if (n_iters > 0) ok = wait_all(acc_done, (n_iters - 1) & 1, 313);
-      if (ok && part < 2) {               // two warps per quarter write the accumulators out, half the columns each
+      if (n_iters > 0) ok = wait_all(all_done, 0, 313);
+      if (ok) {
         const int half = part;
+        const bool do_k = !PP || grp == 0, do_v = !PP || grp == 1;
         tc_fence_after_sync();
         const bool store = key < p.Tk;
         const int64_t rowoff = ((static_cast<int64_t>(b) * p.Tk + key) * p.HK + kvh) * D;
+        const int64_t voff = p.ld_dv != 0 ? static_cast<int64_t>(b) * p.sb_dv + static_cast<int64_t>(key) * p.ld_dv +
+                                                static_cast<int64_t>(kvh) * D
+                                          : rowoff;
         constexpr int COLS = D / 2;
 #pragma unroll
         for (int c = 0; c < COLS; c += 32) {
-          uint32_t a[32], v[32];
-          if (n_iters > 0) {
-            tmem_ld32(t_dk + lane_addr + half * COLS + c, a);
-            tmem_ld32(t_dv + lane_addr + half * COLS + c, v);
-            tmem_ld_wait();
-          } else {
+          uint32_t a[32];
+          if (do_k) {
+            if (n_iters > 0) {
+              tmem_ld32(t_dk + lane_addr + half * COLS + c, a);
+              tmem_ld_wait();
+            } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) a[j] = v[j] = 0u;
+              for (int j = 0; j < 32; ++j) a[j] = 0u;
+            }
+            if (store) store_out32(p.dk + rowoff + half * COLS + c, a, p.scale);  // dS was kept unscaled
           }
-          if (store) {
-            store_out32(p.dk + rowoff + half * COLS + c, a, p.scale);  // dS was kept unscaled
-            const int64_t voff = p.ld_dv != 0 ? static_cast<int64_t>(b) * p.sb_dv + static_cast<int64_t>(key) * p.ld_dv +
-                                                    static_cast<int64_t>(kvh) * D
-                                              : rowoff;
-            store_out32(p.dv + voff + half * COLS + c, v);
+          if (do_v) {
+            if (n_iters > 0) {
+              tmem_ld32(t_dv + lane_addr + half * COLS + c, a);
+              tmem_ld_wait();
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) a[j] = 0u;
+            }
+            if (store) store_out32(p.dv + voff + half * COLS + c, a);
           }
         }
       }
@@ -570,8 +645,8 @@ struct DqCfg {
   static constexpr int DS_OFF = RING_OFF + NSLOTS * 2 * KV_BYTES;         // [128 x 64] bf16
   static constexpr int RING_END = RING_OFF + MAXSLOTS * 2 * KV_BYTES;
   static constexpr int BAR_OFF = RING_END > DS_OFF + Q_REGION ? RING_END : DS_OFF + Q_REGION;
-  // q_full, kv_full[MAXSLOTS], sdp_full[2], ew_done, acc_done, a_ready
-  static constexpr int NBARS = 1 + MAXSLOTS + 2 + 2 + 1;
+  // q_full, kv_full[MAXSLOTS], sdp_full[2], ew_done[2], acc_done, a_ready, all_done, slot_free[MAXSLOTS]
+  static constexpr int NBARS = 1 + MAXSLOTS + 2 + 2 + 3 + MAXSLOTS;
   // single window: 128 (dQ) + 2 x 128 (S | dP sets) leaves 128 columns: Q and dO as bf16 A operands
   static constexpr int A_COLS = D / 2;
   static constexpr bool CAN_TS = !DUAL;
@@ -591,9 +666,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   const uint32_t q_full = bars;
   auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
   auto sdp_full = [&](int s) { return bars + 8u * (1 + C::MAXSLOTS + s); };
-  const uint32_t ew_done = bars + 8u * (3 + C::MAXSLOTS);
-  const uint32_t acc_done = ew_done + 8u;
+  // NEW == 16: two groups of eight element-wise warps take alternate steps (group g the steps of TMEM set g)
+  constexpr bool PP = NEW == 16;
+  auto ew_done = [&](int g) { return bars + 8u * (3 + C::MAXSLOTS + g); };
+  const uint32_t acc_done = ew_done(2);
   const uint32_t a_ready = acc_done + 8u;
+  const uint32_t all_done = a_ready + 8u;
+  auto slot_free = [&](int s) { return all_done + 8u * (1 + s); };   // the MMAs that read ring slot s have completed
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::BAR_OFF + C::NBARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -634,7 +713,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   auto iter_key0 = [&](int it) { return iter_block(it) * 64; };
   auto iter_student = [&](int it) { return DUAL && !combine && (iter_key0(it) + 63 > qlo - p.w_s); };
   const int nslots = (p.a_in_tmem != 0 && p.deep_ring != 0) ? C::MAXSLOTS : C::NSLOTS;
-  auto slot_base = [&](int it) { return sbase + C::RING_OFF + (it % nslots) * 2 * C::KV_BYTES; };
+  const FastDiv by_slots(nslots);
+  auto slot_base = [&](int it) { return sbase + C::RING_OFF + by_slots.mod(it) * 2 * C::KV_BYTES; };
 
   if (threadIdx.x == 0) {
     *abort_flag = ((sbase & 1023u) != 0) ? 1 : 0;
@@ -643,9 +723,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     for (int s = 0; s < C::MAXSLOTS; ++s) mbar_init(kv_full(s), 1);
     mbar_init(sdp_full(0), 1);
     mbar_init(sdp_full(1), 1);
-    mbar_init(ew_done, NEW);
+    mbar_init(ew_done(0), 8);
+    mbar_init(ew_done(1), 8);
     mbar_init(acc_done, 1);
     mbar_init(a_ready, NEW);
+    mbar_init(all_done, 1);
+    for (int s = 0; s < C::MAXSLOTS; ++s) mbar_init(slot_free(s), 1);
     mbar_fence_init();
   }
   if (warp == NEW) {
@@ -666,12 +749,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   auto t_set = [&](int it) { return tmem_base + 128 + (it & 1) * C::SET_COLS; };  // S | dP_T | dP_S
   const bool healthy = (*abort_flag == 0);
 
-  if (warp == NEW && healthy) {
+  if (warp == NEW + 1 && healthy) {
+    // ---- TMA producer: this query block's Q / dO once, then the K / V tiles of every step through the ring
     if (elect_one()) {
-      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, false, false);
-      constexpr uint32_t idesc_acc = umma_idesc_bf16(128, D, false, true);
       auto load_kv = [&](int it) {
-        const int slot = it % nslots;
+        const int slot = by_slots.mod(it);
         const uint32_t base = slot_base(it);
         mbar_expect_tx(kv_full(slot), 2 * C::KV_BYTES);
         const int key0 = iter_key0(it);
@@ -682,48 +764,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
           tma_load_3d(base + C::KV_BYTES + d * C::KV_REGION, halo ? &tma_vh : &tma_v, kv_full(slot), kvh * D + d * 64, krow, b);
         }
       };
-      auto issue_sdp = [&](int it) {
-        const bool st = iter_student(it);
-        const uint32_t sk = slot_base(it), sv = sk + C::KV_BYTES;
-        const uint32_t ts = t_set(it);
-        if (use_ts) {
-#pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint32_t ko = (k / 4) * C::KV_REGION + (k % 4) * 32;
-            umma_ts(ts, t_qa + k * 8, umma_desc_sw128(sk + ko, 16, 1024), idesc_s, k != 0);
-          }
-#pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint32_t ko = (k / 4) * C::KV_REGION + (k % 4) * 32;
-            umma_ts(ts + 64, t_doa + k * 8, umma_desc_sw128(sv + ko, 16, 1024), idesc_s, k != 0);
-          }
-        } else {
-#pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint32_t qo = (k / 4) * C::Q_REGION + (k % 4) * 32;
-            const uint32_t ko = (k / 4) * C::KV_REGION + (k % 4) * 32;
-            umma_ss(ts, umma_desc_sw128(sbase + C::Q_OFF + qo, 16, 1024), umma_desc_sw128(sk + ko, 16, 1024), idesc_s,
-                    k != 0);
-          }
-#pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint32_t qo = (k / 4) * C::Q_REGION + (k % 4) * 32;
-            const uint32_t ko = (k / 4) * C::KV_REGION + (k % 4) * 32;
-            umma_ss(ts + 64, umma_desc_sw128(sbase + (iter_inner(it) ? C::DOS_OFF : C::DOT_OFF) + qo, 16, 1024),
-                    umma_desc_sw128(sv + ko, 16, 1024), idesc_s, k != 0);
-          }
-        }
-        if (DUAL && st) {
-#pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint32_t qo = (k / 4) * C::Q_REGION + (k % 4) * 32;
-            const uint32_t ko = (k / 4) * C::KV_REGION + (k % 4) * 32;
-            umma_ss(ts + 128, umma_desc_sw128(sbase + C::DOS_OFF + qo, 16, 1024), umma_desc_sw128(sv + ko, 16, 1024),
-                    idesc_s, k != 0);
-          }
-        }
-        umma_commit(sdp_full(it & 1));
-      };
       bool ok = true;
       mbar_expect_tx(q_full, C::DB * C::Q_REGION * (DUAL ? 3 : 2));
 #pragma unroll
@@ -732,49 +772,107 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         tma_load_3d(sbase + C::DOT_OFF + d * C::Q_REGION, &tma_dot, q_full, h * D + d * 64, m0, b);
         if (DUAL) tma_load_3d(sbase + C::DOS_OFF + d * C::Q_REGION, &tma_dos, q_full, h * D + d * 64, m0, b);
       }
-      for (int it = 0; it < nslots - 1 && it < n_iters; ++it) load_kv(it);
-      ok = mbar_wait(q_full, 0, abort_flag, 321) && mbar_wait(kv_full(0), 0, abort_flag, 322);
-      if (ok && use_ts) ok = mbar_wait(a_ready, 0, abort_flag, 326);      // Q and dO copied into tensor memory
-      if (ok) { tc_fence_after_sync(); issue_sdp(0); }
       for (int it = 0; it < n_iters && ok; ++it) {
-        if (it + 1 < n_iters) {
-          ok = mbar_wait(kv_full((it + 1) % nslots), ((it + 1) / nslots) & 1, abort_flag, 323);
+        if (it >= nslots) {                 // the slot's previous tiles (step it - nslots) have been consumed
+          ok = mbar_wait(slot_free(by_slots.mod(it)), (by_slots.div(it) - 1) & 1, abort_flag, 324);
           if (!ok) break;
-          tc_fence_after_sync();
-          issue_sdp(it + 1);  // its TMEM set was last read before ew_done(it-1), already observed
         }
-        const int pre = it + nslots - 1;
-        if (pre < n_iters) {
-          if (it >= 1) ok = mbar_wait(acc_done, (it - 1) & 1, abort_flag, 324);  // slot of step it-1 is free
-          if (!ok) break;
-          load_kv(pre);
-        }
-        ok = mbar_wait(ew_done, it & 1, abort_flag, 325);
-        if (!ok) break;
-        tc_fence_after_sync();
-        const uint32_t sk = slot_base(it);
-        if (ds_ts) {
-#pragma unroll
-          for (int k = 0; k < 4; ++k)  // dS as the TMEM A operand: 16 keys = 8 packed columns
-            umma_ts(t_dq, t_set(it) + ts_packed_off<NEW>(k), umma_desc_sw128(sk + k * 2048, C::KV_REGION, 1024),
-                    idesc_acc, (it | k) != 0);
-        } else {
-#pragma unroll
-          for (int k = 0; k < 4; ++k)  // contraction over the 64 keys of the block
-            umma_ss(t_dq, umma_desc_sw128(sbase + C::DS_OFF + k * 32, 16, 1024),
-                    umma_desc_sw128(sk + k * 2048, C::KV_REGION, 1024), idesc_acc, (it | k) != 0);
-        }
-        umma_commit(acc_done);
+        load_kv(it);
       }
+      // stay until every copy has been consumed (or the CTA gave up): no copy may be in flight at exit
+      if (ok) ok = mbar_wait(all_done, 0, abort_flag, 327);
       if (!ok) {
         mbar_drain(q_full, 0);
         for (int s = 0; s < nslots; ++s) { mbar_drain(kv_full(s), 0); mbar_drain(kv_full(s), 1); }
       }
     }
+  } else if (warp == NEW && healthy) {
+    // ---- tensor-core issue
+    if (elect_one()) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, false, false);
+      constexpr uint32_t idesc_acc = umma_idesc_bf16(128, D, false, true);
+      // descriptors as (low word + constant step, constant high word): one add per k-step on this thread
+      constexpr uint32_t HI = umma_desc_hi_sw128(1024);
+      const uint32_t q_lo = umma_desc_lo(sbase + C::Q_OFF, 16), dot_lo = umma_desc_lo(sbase + C::DOT_OFF, 16);
+      const uint32_t dos_lo = umma_desc_lo(sbase + C::DOS_OFF, 16), ds_lo = umma_desc_lo(sbase + C::DS_OFF, 16);
+      auto issue_sdp = [&](int it) {
+        const bool st = iter_student(it);
+        const uint32_t sk = slot_base(it);
+        const uint32_t k_lo = umma_desc_lo(sk, 16), v_lo = k_lo + (C::KV_BYTES >> 4);
+        const uint32_t ts = t_set(it);
+        if (use_ts) {
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t ko = ((k / 4) * C::KV_REGION + (k % 4) * 32) >> 4;
+            umma_ts(ts, t_qa + k * 8, umma_desc_join(k_lo + ko, HI), idesc_s, k != 0);
+          }
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t ko = ((k / 4) * C::KV_REGION + (k % 4) * 32) >> 4;
+            umma_ts(ts + 64, t_doa + k * 8, umma_desc_join(v_lo + ko, HI), idesc_s, k != 0);
+          }
+        } else {
+          const uint32_t do_lo = iter_inner(it) ? dos_lo : dot_lo;
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t qo = ((k / 4) * C::Q_REGION + (k % 4) * 32) >> 4;
+            const uint32_t ko = ((k / 4) * C::KV_REGION + (k % 4) * 32) >> 4;
+            umma_ss(ts, umma_desc_join(q_lo + qo, HI), umma_desc_join(k_lo + ko, HI), idesc_s, k != 0);
+          }
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t qo = ((k / 4) * C::Q_REGION + (k % 4) * 32) >> 4;
+            const uint32_t ko = ((k / 4) * C::KV_REGION + (k % 4) * 32) >> 4;
+            umma_ss(ts + 64, umma_desc_join(do_lo + qo, HI), umma_desc_join(v_lo + ko, HI), idesc_s, k != 0);
+          }
+        }
+        if (DUAL && st) {
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t qo = ((k / 4) * C::Q_REGION + (k % 4) * 32) >> 4;
+            const uint32_t ko = ((k / 4) * C::KV_REGION + (k % 4) * 32) >> 4;
+            umma_ss(ts + 128, umma_desc_join(dos_lo + qo, HI), umma_desc_join(v_lo + ko, HI), idesc_s, k != 0);
+          }
+        }
+        umma_commit(sdp_full(it & 1));
+      };
+      bool ok = true;
+      ok = mbar_wait(q_full, 0, abort_flag, 321) && mbar_wait(kv_full(0), 0, abort_flag, 322);
+      if (ok && use_ts) ok = mbar_wait(a_ready, 0, abort_flag, 326);      // Q and dO copied into tensor memory
+      if (ok) { tc_fence_after_sync(); issue_sdp(0); }
+      for (int it = 0; it < n_iters && ok; ++it) {
+        if (it + 1 < n_iters) {
+          ok = mbar_wait(kv_full(by_slots.mod(it + 1)), by_slots.div(it + 1) & 1, abort_flag, 323);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_sdp(it + 1);  // its TMEM set was last read before ew_done(it-1), already observed
+        }
+        ok = PP ? mbar_wait(ew_done(it & 1), (it >> 1) & 1, abort_flag, 325) : mbar_wait(ew_done(0), it & 1, abort_flag, 325);
+        if (!ok) break;
+        tc_fence_after_sync();
+        // the K tile as the MN-major B operand: 64 keys of the contraction, the next 64 columns KV_REGION bytes on
+        const uint32_t km_lo = umma_desc_lo(slot_base(it), C::KV_REGION);
+        const uint32_t acc = it != 0;
+        if (ds_ts) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k)  // dS as the TMEM A operand: 16 keys = 8 packed columns
+            umma_ts(t_dq, t_set(it) + ts_packed_off(k), umma_desc_join(km_lo + k * (2048 >> 4), HI), idesc_acc, acc | (k != 0));
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; ++k)  // contraction over the 64 keys of the block
+            umma_ss(t_dq, umma_desc_join(ds_lo + k * 2, HI), umma_desc_join(km_lo + k * (2048 >> 4), HI), idesc_acc, acc | (k != 0));
+        }
+        if (!PP) umma_commit(acc_done);     // only the single-group element-wise warps wait on it
+        umma_commit(slot_free(by_slots.mod(it)));   // the producer may refill this step's ring slot
+      }
+      if (ok) umma_commit(all_done);      // every dQ MMA has completed when this arrives
+    }
   } else if (warp < NEW && healthy) {
-    constexpr int PARTS = NEW / 4;              // warps per TMEM lane quarter
-    constexpr int NC = 64 / PARTS;              // S columns (keys) of a step per thread
-    const int quarter = warp & 3, part = warp >> 2;
+    constexpr int NPASS = PP ? 2 : 1;
+    constexpr int NC = 32 / NPASS;              // S columns (keys) per pass; a thread owns 32 of a step
+    constexpr int STEP = PP ? 2 : 1;
+    const int grp = PP ? (warp >> 3) : 0;       // this warp's group takes steps grp, grp + STEP, ...
+    const int quarter = warp & 3, part = (warp >> 2) & 1;
     const int qrow = quarter * 32 + lane;
     const int row = m0 + qrow;
     const int qpos = row + off;
@@ -794,7 +892,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       // Q and dO rows: shared memory (128-byte swizzled, 64 columns per region) -> packed bf16 pairs in TMEM
       ok = wait_all(q_full, 0, 334);
       if (ok) {
-        for (int u = part; u < C::DB * 2; u += PARTS) {      // units of 32 columns (16 packed) of a row
+        for (int u = part + 2 * grp; u < C::DB * 2; u += 2 * STEP) {      // units of 32 columns (16 packed) of a row
           const int reg = u >> 1, hc = u & 1;
           uint32_t qa[16], da[16];
 #pragma unroll
@@ -813,62 +911,70 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         if (lane == 0) mbar_arrive(a_ready);
       }
     }
-    for (int it = 0; it < n_iters && ok; ++it) {
+    for (int it = grp; it < n_iters && ok; it += STEP) {
       const bool st = iter_student(it);
-      const int key0 = iter_key0(it) + part * NC;
+      const int key0 = iter_key0(it) + part * 32;
       ok = wait_all(sdp_full(it & 1), (it >> 1) & 1, 331);
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t ts = t_set(it) + lane_addr + part * NC;
-      uint32_t sv[NC], dpt[NC], dps[NC];
-      tmem_ld_n<NC>(ts, sv);
-      tmem_ld_n<NC>(ts + 64, dpt);
-      if (DUAL && st) tmem_ld_n<NC>(ts + 128, dps);
-      tmem_ld_wait();
-      uint32_t dsp[NC / 2];
-      {
-        const int kb0 = iter_key0(it);
-        const bool full_t = (kb0 + 63 <= qlo) && (kb0 > qhi - p.w_t);
-        const bool full_s = (kb0 > qhi - p.w_s);
+      const uint32_t ts = t_set(it) + lane_addr + part * 32;
+      const int kb0 = iter_key0(it);
+      const bool full_t = (kb0 + 63 <= qlo) && (kb0 > qhi - p.w_t);
+      const bool full_s = (kb0 > qhi - p.w_s);
+      if (!PP && !ds_ts && it >= 1) {
+        ok = wait_all(acc_done, (it - 1) & 1, 332);  // the dS staging tile is free again
+        if (!ok) break;
+      }
+#pragma unroll
+      for (int h = 0; h < NPASS; ++h) {       // alternating groups: two passes of 16 columns keep the registers low
+        uint32_t sv[NC], dpt[NC], dps[NC];
+        tmem_ld_n<NC>(ts + h * NC, sv);
+        tmem_ld_n<NC>(ts + 64 + h * NC, dpt);
+        if (DUAL && st) tmem_ld_n<NC>(ts + 128 + h * NC, dps);
+        tmem_ld_wait();
+        uint32_t dsp[NC / 2];
+        const int kpos0 = key0 + h * NC;
         if (DUAL && st) {
           if (full_t && full_s)
-            dq_elementwise<false, true, NC>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, key0, p.w_t, p.w_s, dsp);
+            dq_elementwise<false, true, NC>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, kpos0, p.w_t, p.w_s, dsp);
           else
-            dq_elementwise<true, true, NC>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, key0, p.w_t, p.w_s, dsp);
+            dq_elementwise<true, true, NC>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, kpos0, p.w_t, p.w_s, dsp);
         } else if (combine) {
           const int inner = iter_inner(it);
           const int lo = inner ? 0 : p.w_s, hi = inner ? p.w_s : p.w_t;
           const float del = inner ? del_s : del_t;            // delta' was passed in place of delta_S
           const bool full = (kb0 + 63 <= qlo - lo) && (kb0 > qhi - hi);
           if (full)
-            dq_elementwise<false, false, NC>(sv, dpt, dps, p.scale_log2, nlse_t, del, nlse_s, del_s, qpos, key0, hi, hi, dsp, lo);
+            dq_elementwise<false, false, NC>(sv, dpt, dps, p.scale_log2, nlse_t, del, nlse_s, del_s, qpos, kpos0, hi, hi, dsp, lo);
           else
-            dq_elementwise<true, false, NC>(sv, dpt, dps, p.scale_log2, nlse_t, del, nlse_s, del_s, qpos, key0, hi, hi, dsp, lo);
+            dq_elementwise<true, false, NC>(sv, dpt, dps, p.scale_log2, nlse_t, del, nlse_s, del_s, qpos, kpos0, hi, hi, dsp, lo);
         } else {
           if (full_t)
-            dq_elementwise<false, false, NC>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, key0, p.w_t, p.w_s, dsp);
+            dq_elementwise<false, false, NC>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, kpos0, p.w_t, p.w_s, dsp);
           else
-            dq_elementwise<true, false, NC>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, key0, p.w_t, p.w_s, dsp);
+            dq_elementwise<true, false, NC>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, kpos0, p.w_t, p.w_s, dsp);
         }
-      }
-      if (it >= 1) {
-        ok = wait_all(acc_done, (it - 1) & 1, 332);  // dS tile is free again
-        if (!ok) break;
+        if (ds_ts)
+          tmem_st_n<NC / 2>(ts + h * (NC / 2), dsp);    // over this thread's own S columns (already read)
+        else
+          store_row_part_packed<NC / 2>(smem + C::DS_OFF, qrow, part * NPASS + h, dsp);
       }
       if (ds_ts) {
-        tmem_st_n<NC / 2>(ts, dsp);    // over this thread's own S columns (already read)
         tmem_st_wait();
+        if (!PP && it >= 1) {
+          ok = wait_all(acc_done, (it - 1) & 1, 332);  // keeps this warp's phase count of the barrier in step
+          if (!ok) break;
+        }
       } else {
-        store_row_part_packed<NC / 2>(smem + C::DS_OFF, qrow, part, dsp);
         fence_proxy_async_smem();
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(ew_done);
+      if (lane == 0) mbar_arrive(ew_done(PP ? (it & 1) : 0));
     }
     if (ok) {
-      ok = wait_all(acc_done, (n_iters - 1) & 1, 333);
-      if (ok && part < 2) {               // two warps per quarter write dQ out, half the columns each
+      ok = wait_all(all_done, 0, 333);
+      if (ok && grp == 0) {               // two warps per quarter write dQ out, half the columns each
         const int half = part;
         tc_fence_after_sync();
         constexpr int COLS = D / 2;
@@ -1023,8 +1129,9 @@ static int launch_bwd_combined(const BwdMaps& m, const CUtensorMap& dop64, const
 
 template <int NEW>
 static int dispatch_bwd(const BwdMaps& m, const AttnBwdParams& p, int B, int D, bool dual, cudaStream_t stream) {
-  if (D == 128) return dual ? launch_bwd<128, true, NEW>(m, p, B, stream) : launch_bwd<128, false, NEW>(m, p, B, stream);
-  return dual ? launch_bwd<64, true, NEW>(m, p, B, stream) : launch_bwd<64, false, NEW>(m, p, B, stream);
+  // the two-softmax dual kernels have one S / dP set in dK/dV: always the single group of eight warps
+  if (D == 128) return dual ? launch_bwd<128, true, 8>(m, p, B, stream) : launch_bwd<128, false, NEW>(m, p, B, stream);
+  return dual ? launch_bwd<64, true, 8>(m, p, B, stream) : launch_bwd<64, false, NEW>(m, p, B, stream);
 }
 
 }  // namespace ttcd
@@ -1066,11 +1173,20 @@ TTCD_EXPORT int ttcd_attn_bwd_combine(const void* o_t, const void* do_t, const v
 static thread_local long long g_next_ld_dv = 0, g_next_sb_dv = 0;
 // Combined gradient stream of the NEXT dual-window call of this thread: dO' = dO_T + r dO_S ([B, Tq, H, D] bf16) and
 // delta' = delta_T + r delta_S ([B, H, Tq] fp32) with r = exp(lse_T - lse_S); consumed by that call.
+static thread_local long long* g_next_probe = nullptr;
+static thread_local int g_next_probe_mask = 0;
 static thread_local const void* g_next_dop = nullptr;
 static thread_local const float* g_next_delta_p = nullptr;
 TTCD_EXPORT int ttcd_attn_bwd_set_combined(const void* do_combined, const float* delta_combined) {
   g_next_dop = do_combined;
   g_next_delta_p = delta_combined;
+  return TTCD_OK;
+}
+// Timeline probe of the NEXT backward call of this thread: `buf` (device, 256 x int64, zeroed by the caller) receives
+// clock64() stamps from one dK/dV CTA (see AttnBwdParams::probe); consumed by that call.
+TTCD_EXPORT int ttcd_attn_bwd_set_probe(long long* buf, int event_mask) {
+  g_next_probe = buf;
+  g_next_probe_mask = event_mask;
   return TTCD_OK;
 }
 TTCD_EXPORT int ttcd_attn_bwd_set_dv_layout(long long ld_dv, long long sb_dv) {
@@ -1129,11 +1245,15 @@ TTCD_EXPORT int ttcd_attn_bwd_cp(const void* q, const void* k, const void* v, co
     return (e != nullptr && e[0] == '3') ? 0 : 1;
   }();
   p.deep_ring = deep_ring;
-  // element-wise warps per CTA: 16 (four per scheduler, hides the TMEM-load and MUFU latencies) or 8
-  static const int ew_warps = [] {
+  p.probe = g_next_probe;
+  p.probe_mask = g_next_probe_mask;
+  g_next_probe = nullptr;
+  // element-wise warps per CTA: 16 = two groups on alternate steps (needs the operands in tensor memory), or 8
+  static const int ew_warps_env = [] {
     const char* e = getenv("TTCD_ATTN_BWD_WARPS");
     return (e != nullptr && atoi(e) == 8) ? 8 : 16;
   }();
+  const int ew_warps = a_in_tmem ? ew_warps_env : 8;
   p.ld_dv = g_next_ld_dv; p.sb_dv = g_next_sb_dv;
   g_next_ld_dv = g_next_sb_dv = 0;
   p.combine = 0;

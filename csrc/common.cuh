@@ -184,6 +184,19 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t
   d |= 2ull << 61;  // SWIZZLE_128B
   return d;
 }
+// The same descriptor in two 32-bit words, for code that issues many MMAs from one thread: the high word is a
+// constant of the layout, the low word advances with the operand address (+ bytes / 16; no carry leaves the 14-bit
+// address field while the address stays below 256 KB), so that a k-step costs one integer add instead of the
+// and / shift / or sequence.
+__device__ __forceinline__ constexpr uint32_t umma_desc_hi_sw128(uint32_t sbo_bytes) {
+  return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+}
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return ((smem_addr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ uint64_t umma_desc_join(uint32_t lo, uint32_t hi) {
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
 // kind::f16 instruction descriptor: bf16 x bf16 -> fp32, M x N tile, operand majors.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n, bool a_mn_major, bool b_mn_major) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |

@@ -96,7 +96,7 @@ _ERRORS = {
 launch_count = 0  # kernels launched through this binding (entry points that launch two count twice)
 _MULTI_KERNEL = {"ttcd_attn_bwd": 2, "ttcd_attn_bwd_cp": 2, "ttcd_rmsnorm_bwd_no_alloc": 2,
                  # host-only entry points launch nothing
-                 "ttcd_attn_bwd_set_dv_layout": 0, "ttcd_attn_bwd_set_combined": 0, "ttcd_symm_alloc": 0, "ttcd_symm_free": 0, "ttcd_ipc_get_handle": 0,
+                 "ttcd_attn_bwd_set_dv_layout": 0, "ttcd_attn_bwd_set_combined": 0, "ttcd_attn_bwd_set_probe": 0, "ttcd_symm_alloc": 0, "ttcd_symm_free": 0, "ttcd_ipc_get_handle": 0,
                  "ttcd_ipc_open_handle": 0, "ttcd_ipc_close": 0}
 
 
