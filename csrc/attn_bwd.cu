@@ -17,6 +17,8 @@
 // K in dq), so nothing is transposed in memory.  The reference has no fused dual-window backward:
 // training there runs two flash-attn backward passes whose dq/dk/dv are summed by autograd
 // (custom_models/ipttcd/modeling_ipttcdv9.py:686-690; profiling/FUSED_ATTENTION_DESIGN.md:68-69).
+// every role of these kernels waits long enough per step for parked waits to pay (measured: 13.8 vs 14.3 ms)
+#define TTCD_PARK_ALL_WAITS 1
 #include "common.cuh"
 
 #include <cstdlib>
@@ -220,7 +222,7 @@ struct DkdvCfg {
   static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16;
 };
 
-template <int D, bool DUAL, int NEW>
+template <int D, bool DUAL, int NEW, bool SPLIT>
 __global__ void __launch_bounds__(bwd_threads(NEW), 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                      const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ CUtensorMap tma_dot,
@@ -235,7 +237,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   auto sdp_full = [&](int s) { return bars + 8u * (1 + C::MAXSLOTS + s); };
   // NEW == 16: two groups of eight element-wise warps take alternate steps (group g the steps of TMEM set g), so
   // the element-wise work of step i+1 starts as soon as its S / dP are there instead of after step i's
-  constexpr bool PP = NEW == 16;
+  // SPLIT (with NEW == 16): both groups work on the same step, group g on the g-th 16 columns of every warp's 32
+  constexpr bool PP = NEW == 16 && !SPLIT;
+  static_assert(!SPLIT || NEW == 16, "column split needs two groups");
   static_assert(!PP || C::NSETS == 2, "alternating groups need two S / dP sets");
   auto ew_done = [&](int g) { return bars + 8u * (1 + C::MAXSLOTS + C::NSETS + g); };
   const uint32_t acc_done = ew_done(2);
@@ -279,7 +283,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
     mbar_init(kv_full, 1);
     for (int s = 0; s < C::MAXSLOTS; ++s) mbar_init(tiles_full(s), 1);
     for (int s = 0; s < C::NSETS; ++s) mbar_init(sdp_full(s), 1);
-    mbar_init(ew_done(0), 8);
+    mbar_init(ew_done(0), SPLIT ? 16 : 8);
     mbar_init(ew_done(1), 8);
     mbar_init(acc_done, 1);
     mbar_init(all_done, 1);
@@ -354,13 +358,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       }
       for (int it = 0; it < n_iters && ok; ++it) {
         if (it >= nslots) {                 // the slot's previous tiles (step it - nslots) have been consumed
-          ok = mbar_wait(slot_free(by_slots.mod(it)), (by_slots.div(it) - 1) & 1, abort_flag, 304);
+          ok = mbar_wait_parked(slot_free(by_slots.mod(it)), (by_slots.div(it) - 1) & 1, abort_flag, 304);
           if (!ok) break;
         }
         load_tiles(it);
       }
       // stay until every copy has been consumed (or the CTA gave up): no copy may be in flight at exit
-      if (ok) ok = mbar_wait(all_done, 0, abort_flag, 306);
+      if (ok) ok = mbar_wait_parked(all_done, 0, abort_flag, 306);
       if (!ok) {
         mbar_drain(kv_full, 0);
         for (int s = 0; s < nslots; ++s) { mbar_drain(tiles_full(s), 0); mbar_drain(tiles_full(s), 1); }
@@ -464,10 +468,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       if (ok) umma_commit(all_done);      // every accumulate MMA has completed when this arrives
     }
   } else if (warp < NEW && healthy) {
-    constexpr int NPASS = PP ? 2 : 1;
+    constexpr int NPASS = NEW == 16 ? 2 : 1;
     constexpr int NC = 32 / NPASS;              // S^T columns (queries) per pass; a thread owns 32 of a step
     constexpr int STEP = PP ? 2 : 1;
-    const int grp = PP ? (warp >> 3) : 0;       // this warp's group takes steps grp, grp + STEP, ...
+    const int grp = NEW == 16 ? (warp >> 3) : 0;   // alternating: takes steps grp, grp + 2, ...; split: pass grp of every step
     const int quarter = warp & 3, part = (warp >> 2) & 1;
     const int krow = quarter * 32 + lane;       // key row inside the block == TMEM lane
     const int key = n0 + krow;
@@ -477,7 +481,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
     auto vslot_of = [&](int it) { return vecs + (PP ? ((it & 1) * 2 + ((it >> 1) & 1)) : (it & 1)) * 256; };
     bool ok = true;
     auto wait_all = [&](uint32_t bar, uint32_t parity, int code) {
-      const bool r = mbar_wait(bar, parity, abort_flag, code);
+      const bool r = mbar_wait_parked(bar, parity, abort_flag, code);
       return __all_sync(0xffffffffu, r) != 0;
     };
     // per-row statistics of a query block: [-lse_t*log2e | delta_t | -lse_s*log2e | delta_s], 64 each;
@@ -496,15 +500,17 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       return raw;
     };
     auto finish_stat = [&](float raw) { return stat_is_lse ? -raw * LOG2E : raw; };
-    if (grp < n_iters) vslot_of(grp)[ctid] = finish_stat(fetch_stat(grp));
-    for (int it = grp; it < n_iters && ok; it += STEP) {
+    const int it0 = PP ? grp : 0;
+    const bool fetcher = !SPLIT || grp == 0;    // split: the first group's 256 threads fetch the statistics
+    if (it0 < n_iters && fetcher) vslot_of(it0)[ctid] = finish_stat(fetch_stat(it0));
+    for (int it = it0; it < n_iters && ok; it += STEP) {
       const int r0 = iter_row0(it);
       const bool st = iter_student(it);
       const float* vslot = vslot_of(it);
-      const float next_stat = (it + STEP < n_iters) ? fetch_stat(it + STEP) : 0.f;  // in flight during this step
+      const float next_stat = (it + STEP < n_iters && fetcher) ? fetch_stat(it + STEP) : 0.f;  // in flight during this step
       const bool stamper = (warp & 7) == 0 && lane == 0;
       if (stamper) stamp(it, 5);
-      named_barrier_sync(1 + grp, 256);
+      if (SPLIT) named_barrier_sync(1, 512); else named_barrier_sync(1 + grp, 256);
       ok = wait_all(sdp_full(it % C::NSETS), (it / C::NSETS) & 1, 311);
       if (!ok) break;
       if (stamper) stamp(it, 6);
@@ -521,6 +527,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       }
 #pragma unroll
       for (int h = 0; h < NPASS; ++h) {       // alternating groups: two passes of 16 columns keep the registers low
+        if (SPLIT && h != grp) continue;      // column split: this group's pass only
         uint32_t sv[NC], dpt[NC], dps[NC];
         tmem_ld_n<NC>(ts + h * NC, sv);
         tmem_ld_n<NC>(ts + 64 + h * NC, dpt);
@@ -568,7 +575,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
         }
       }
       if (stamper) stamp(it, 7);
-      vslot_of(it + STEP)[ctid] = finish_stat(next_stat);
+      if (fetcher) vslot_of(it + STEP)[ctid] = finish_stat(next_stat);
       fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncwarp();
@@ -581,7 +588,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       if (n_iters > 0) ok = wait_all(all_done, 0, 313);
       if (ok) {
         const int half = part;
-        const bool do_k = !PP || grp == 0, do_v = !PP || grp == 1;
+        const bool do_k = NEW != 16 || grp == 0, do_v = NEW != 16 || grp == 1;
         tc_fence_after_sync();
         const bool store = key < p.Tk;
         const int64_t rowoff = ((static_cast<int64_t>(b) * p.Tk + key) * p.HK + kvh) * D;
@@ -653,7 +660,7 @@ struct DqCfg {
   static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16;
 };
 
-template <int D, bool DUAL, int NEW>
+template <int D, bool DUAL, int NEW, bool SPLIT>
 __global__ void __launch_bounds__(bwd_threads(NEW), 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                    const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ CUtensorMap tma_dot,
@@ -667,7 +674,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
   auto sdp_full = [&](int s) { return bars + 8u * (1 + C::MAXSLOTS + s); };
   // NEW == 16: two groups of eight element-wise warps take alternate steps (group g the steps of TMEM set g)
-  constexpr bool PP = NEW == 16;
+  constexpr bool PP = NEW == 16 && !SPLIT;      // SPLIT: both groups on the same step, 16 columns per warp each
+  static_assert(!SPLIT || NEW == 16, "column split needs two groups");
   auto ew_done = [&](int g) { return bars + 8u * (3 + C::MAXSLOTS + g); };
   const uint32_t acc_done = ew_done(2);
   const uint32_t a_ready = acc_done + 8u;
@@ -723,7 +731,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     for (int s = 0; s < C::MAXSLOTS; ++s) mbar_init(kv_full(s), 1);
     mbar_init(sdp_full(0), 1);
     mbar_init(sdp_full(1), 1);
-    mbar_init(ew_done(0), 8);
+    mbar_init(ew_done(0), SPLIT ? 16 : 8);
     mbar_init(ew_done(1), 8);
     mbar_init(acc_done, 1);
     mbar_init(a_ready, NEW);
@@ -774,13 +782,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       }
       for (int it = 0; it < n_iters && ok; ++it) {
         if (it >= nslots) {                 // the slot's previous tiles (step it - nslots) have been consumed
-          ok = mbar_wait(slot_free(by_slots.mod(it)), (by_slots.div(it) - 1) & 1, abort_flag, 324);
+          ok = mbar_wait_parked(slot_free(by_slots.mod(it)), (by_slots.div(it) - 1) & 1, abort_flag, 324);
           if (!ok) break;
         }
         load_kv(it);
       }
       // stay until every copy has been consumed (or the CTA gave up): no copy may be in flight at exit
-      if (ok) ok = mbar_wait(all_done, 0, abort_flag, 327);
+      if (ok) ok = mbar_wait_parked(all_done, 0, abort_flag, 327);
       if (!ok) {
         mbar_drain(q_full, 0);
         for (int s = 0; s < nslots; ++s) { mbar_drain(kv_full(s), 0); mbar_drain(kv_full(s), 1); }
@@ -868,10 +876,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       if (ok) umma_commit(all_done);      // every dQ MMA has completed when this arrives
     }
   } else if (warp < NEW && healthy) {
-    constexpr int NPASS = PP ? 2 : 1;
+    constexpr int NPASS = NEW == 16 ? 2 : 1;
     constexpr int NC = 32 / NPASS;              // S columns (keys) per pass; a thread owns 32 of a step
     constexpr int STEP = PP ? 2 : 1;
-    const int grp = PP ? (warp >> 3) : 0;       // this warp's group takes steps grp, grp + STEP, ...
+    const int grp = NEW == 16 ? (warp >> 3) : 0;   // alternating: takes steps grp, grp + 2, ...; split: pass grp of every step
     const int quarter = warp & 3, part = (warp >> 2) & 1;
     const int qrow = quarter * 32 + lane;
     const int row = m0 + qrow;
@@ -885,14 +893,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     const float del_s = (DUAL && row_ok) ? p.delta_s[sidx] : 0.f;
     bool ok = true;
     auto wait_all = [&](uint32_t bar, uint32_t parity, int code) {
-      const bool r = mbar_wait(bar, parity, abort_flag, code);
+      const bool r = mbar_wait_parked(bar, parity, abort_flag, code);
       return __all_sync(0xffffffffu, r) != 0;
     };
     if (use_ts) {
       // Q and dO rows: shared memory (128-byte swizzled, 64 columns per region) -> packed bf16 pairs in TMEM
       ok = wait_all(q_full, 0, 334);
       if (ok) {
-        for (int u = part + 2 * grp; u < C::DB * 2; u += 2 * STEP) {      // units of 32 columns (16 packed) of a row
+        for (int u = part + 2 * grp; u < C::DB * 2; u += NEW / 4) {      // units of 32 columns (16 packed) of a row
           const int reg = u >> 1, hc = u & 1;
           uint32_t qa[16], da[16];
 #pragma unroll
@@ -911,7 +919,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         if (lane == 0) mbar_arrive(a_ready);
       }
     }
-    for (int it = grp; it < n_iters && ok; it += STEP) {
+    for (int it = (PP ? grp : 0); it < n_iters && ok; it += STEP) {
       const bool st = iter_student(it);
       const int key0 = iter_key0(it) + part * 32;
       ok = wait_all(sdp_full(it & 1), (it >> 1) & 1, 331);
@@ -927,6 +935,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       }
 #pragma unroll
       for (int h = 0; h < NPASS; ++h) {       // alternating groups: two passes of 16 columns keep the registers low
+        if (SPLIT && h != grp) continue;      // column split: this group's pass only
         uint32_t sv[NC], dpt[NC], dps[NC];
         tmem_ld_n<NC>(ts + h * NC, sv);
         tmem_ld_n<NC>(ts + 64 + h * NC, dpt);
@@ -1083,10 +1092,10 @@ struct BwdMaps {
   CUtensorMap q64, q128, k64, k128, v64, v128, dot64, dot128, dos64, dos128, kh64, kh128, vh64, vh128;
 };
 
-template <int D, bool DUAL, int NEW>
+template <int D, bool DUAL, int NEW, bool SPLIT>
 static int launch_bwd(const BwdMaps& m, const AttnBwdParams& p, int B, cudaStream_t stream) {
-  auto k1 = attn_bwd_dkdv_kernel<D, DUAL, NEW>;
-  auto k2 = attn_bwd_dq_kernel<D, DUAL, NEW>;
+  auto k1 = attn_bwd_dkdv_kernel<D, DUAL, NEW, SPLIT>;
+  auto k2 = attn_bwd_dq_kernel<D, DUAL, NEW, SPLIT>;
   constexpr int smem1 = DkdvCfg<D, DUAL>::TOTAL, smem2 = DqCfg<D, DUAL>::TOTAL;
   static_assert(smem1 <= 232448 && smem2 <= 232448, "shared memory budget exceeded");
   static bool configured = false;
@@ -1104,11 +1113,11 @@ static int launch_bwd(const BwdMaps& m, const AttnBwdParams& p, int B, cudaStrea
 }
 
 // Dual window with the dK/dV kernel in combined mode (single-window pipeline, one softmax) and the dual dQ kernel.
-template <int D, int NEW>
+template <int D, int NEW, bool SPLIT>
 static int launch_bwd_combined(const BwdMaps& m, const CUtensorMap& dop64, const CUtensorMap& dop128, const AttnBwdParams& p,
                                const float* delta_p, int B, cudaStream_t stream) {
-  auto k1 = attn_bwd_dkdv_kernel<D, false, NEW>;
-  auto k2 = attn_bwd_dq_kernel<D, true, NEW>;
+  auto k1 = attn_bwd_dkdv_kernel<D, false, NEW, SPLIT>;
+  auto k2 = attn_bwd_dq_kernel<D, true, NEW, SPLIT>;
   constexpr int smem1 = DkdvCfg<D, false>::TOTAL, smem2 = DqCfg<D, true>::TOTAL;
   static bool configured = false;
   if (!configured) {
@@ -1127,11 +1136,12 @@ static int launch_bwd_combined(const BwdMaps& m, const CUtensorMap& dop64, const
   return static_cast<int>(cudaGetLastError());
 }
 
-template <int NEW>
+template <int NEW, bool SPLIT>
 static int dispatch_bwd(const BwdMaps& m, const AttnBwdParams& p, int B, int D, bool dual, cudaStream_t stream) {
   // the two-softmax dual kernels have one S / dP set in dK/dV: always the single group of eight warps
-  if (D == 128) return dual ? launch_bwd<128, true, 8>(m, p, B, stream) : launch_bwd<128, false, NEW>(m, p, B, stream);
-  return dual ? launch_bwd<64, true, 8>(m, p, B, stream) : launch_bwd<64, false, NEW>(m, p, B, stream);
+  if (D == 128)
+    return dual ? launch_bwd<128, true, 8, false>(m, p, B, stream) : launch_bwd<128, false, NEW, SPLIT>(m, p, B, stream);
+  return dual ? launch_bwd<64, true, 8, false>(m, p, B, stream) : launch_bwd<64, false, NEW, SPLIT>(m, p, B, stream);
 }
 
 }  // namespace ttcd
@@ -1254,6 +1264,12 @@ TTCD_EXPORT int ttcd_attn_bwd_cp(const void* q, const void* k, const void* v, co
     return (e != nullptr && atoi(e) == 8) ? 8 : 16;
   }();
   const int ew_warps = a_in_tmem ? ew_warps_env : 8;
+  // 16 warps: TTCD_ATTN_BWD_GROUPS=split puts both groups on the same step (16 columns per warp each) instead of
+  // alternate steps
+  static const bool ew_split = [] {
+    const char* e = getenv("TTCD_ATTN_BWD_GROUPS");
+    return e != nullptr && e[0] == 's';
+  }();
   p.ld_dv = g_next_ld_dv; p.sb_dv = g_next_sb_dv;
   g_next_ld_dv = g_next_sb_dv = 0;
   p.combine = 0;
@@ -1268,13 +1284,17 @@ TTCD_EXPORT int ttcd_attn_bwd_cp(const void* q, const void* k, const void* v, co
     rc = make_tmap_bf16_3d(&dop64, dop, qi, Tq, B, qi, qi * Tq, 64, 64);
     if (rc == TTCD_OK) rc = make_tmap_bf16_3d(&dop128, dop, qi, Tq, B, qi, qi * Tq, 64, 128);
     if (rc != TTCD_OK) return rc;
+    if (ew_warps == 16 && ew_split)
+      return D == 128 ? launch_bwd_combined<128, 16, true>(m, dop64, dop128, p, delta_p, B, stream)
+                      : launch_bwd_combined<64, 16, true>(m, dop64, dop128, p, delta_p, B, stream);
     if (ew_warps == 16)
-      return D == 128 ? launch_bwd_combined<128, 16>(m, dop64, dop128, p, delta_p, B, stream)
-                      : launch_bwd_combined<64, 16>(m, dop64, dop128, p, delta_p, B, stream);
-    return D == 128 ? launch_bwd_combined<128, 8>(m, dop64, dop128, p, delta_p, B, stream)
-                    : launch_bwd_combined<64, 8>(m, dop64, dop128, p, delta_p, B, stream);
+      return D == 128 ? launch_bwd_combined<128, 16, false>(m, dop64, dop128, p, delta_p, B, stream)
+                      : launch_bwd_combined<64, 16, false>(m, dop64, dop128, p, delta_p, B, stream);
+    return D == 128 ? launch_bwd_combined<128, 8, false>(m, dop64, dop128, p, delta_p, B, stream)
+                    : launch_bwd_combined<64, 8, false>(m, dop64, dop128, p, delta_p, B, stream);
   }
-  return ew_warps == 16 ? dispatch_bwd<16>(m, p, B, D, dual, stream) : dispatch_bwd<8>(m, p, B, D, dual, stream);
+  if (ew_warps == 16 && ew_split) return dispatch_bwd<16, true>(m, p, B, D, dual, stream);
+  return ew_warps == 16 ? dispatch_bwd<16, false>(m, p, B, D, dual, stream) : dispatch_bwd<8, false>(m, p, B, D, dual, stream);
 }
 
 TTCD_EXPORT int ttcd_attn_bwd(const void* q, const void* k, const void* v, const void* do_t, const void* do_s,

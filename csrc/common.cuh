@@ -88,6 +88,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// One try with a suspend-time hint (nanoseconds): the thread is parked until the phase completes or the hint runs
+// out, so that a warp with a long wait ahead does not compete for issue slots with the warps doing the work it
+// waits for.  Waking up costs a little more than the tight poll above: use it where the wait is long.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(20000u)
+      : "memory");
+  return ok != 0;
+}
 
 // Wait budget for barriers that only depend on this CTA's own copies and MMAs.
 #ifndef TTCD_WAIT_NS
@@ -95,7 +109,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 #endif
 
 // Bounded wait.  Returns false when the budget ran out or another role of the CTA aborted.
+__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code);
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+#ifdef TTCD_PARK_ALL_WAITS      // a translation unit may park every wait (define before including this header)
+  return mbar_wait_parked(bar, parity, abort_flag, code);
+#endif
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   for (uint32_t it = 1;; ++it) {
@@ -107,6 +125,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         atomicCAS(&g_status, 0, code);
         return false;
       }
+    }
+  }
+}
+// The same bounded wait for warps that expect to wait long (see mbar_try_wait_parked).
+__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {                                  // each try may sleep up to the hint: check the exits every time
+    if (mbar_try_wait_parked(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (globaltimer_ns() - t0 > TTCD_WAIT_NS) {
+      *abort_flag = 1;
+      atomicCAS(&g_status, 0, code);
+      return false;
     }
   }
 }
