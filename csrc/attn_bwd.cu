@@ -123,6 +123,32 @@ __device__ __forceinline__ void dkdv_elementwise(const uint32_t (&sv)[NC], const
                                                  int key, int qpos0, int w_t, int w_s, bool key_ok,
                                                  uint32_t (&ptp)[NC / 2], uint32_t (&psp)[NC / 2],
                                                  uint32_t (&dsp)[NC / 2], int lo_t = 0) {
+  if constexpr (!STUDENT) {
+    // packed fp32 pairs (two lanes per FFMA / FMUL): the element-wise phase is bound by instruction issue
+    const float2 sc2 = make_float2(scale_log2, scale_log2), neg1 = make_float2(-1.f, -1.f);
+#pragma unroll
+    for (int c = 0; c < NC; c += 4) {
+      const float4 nl = *reinterpret_cast<const float4*>(stats + c);
+      const float4 dl = *reinterpret_cast<const float4*>(stats + 64 + c);
+#pragma unroll
+      for (int hp = 0; hp < 2; ++hp) {
+        const int j0 = c + 2 * hp;
+        const float2 n2 = hp ? make_float2(nl.z, nl.w) : make_float2(nl.x, nl.y);
+        const float2 l2 = hp ? make_float2(dl.z, dl.w) : make_float2(dl.x, dl.y);
+        const float2 x2 = __ffma2_rn(make_float2(__uint_as_float(sv[j0]), __uint_as_float(sv[j0 + 1])), sc2, n2);
+        float2 p2 = make_float2(ex2(x2.x), ex2(x2.y));
+        if (MASKED) {
+          const int qpos = qpos0 + j0;
+          if (!(key_ok && key <= qpos - lo_t && key > qpos - w_t)) p2.x = 0.f;
+          if (!(key_ok && key <= qpos + 1 - lo_t && key > qpos + 1 - w_t)) p2.y = 0.f;
+        }
+        const float2 dd = __ffma2_rn(l2, neg1, make_float2(__uint_as_float(dpt[j0]), __uint_as_float(dpt[j0 + 1])));
+        const float2 d2 = __fmul2_rn(p2, dd);
+        ptp[j0 / 2] = pack_bf16(p2.x, p2.y);
+        dsp[j0 / 2] = pack_bf16(d2.x, d2.y);
+      }
+    }
+  } else {
 #pragma unroll
   for (int c = 0; c < NC; c += 4) {
     const float4 nl = *reinterpret_cast<const float4*>(stats + c);
@@ -164,6 +190,7 @@ __device__ __forceinline__ void dkdv_elementwise(const uint32_t (&sv)[NC], const
       psp[c / 2 + 1] = pack_bf16(ps[2], ps[3]);
     }
   }
+  }
 }
 
 // Element-wise core of the dQ step: NC key columns of one query row (statistics live in registers).
@@ -172,6 +199,23 @@ __device__ __forceinline__ void dq_elementwise(const uint32_t (&sv)[NC], const u
                                                const uint32_t (&dps)[NC], float scale_log2, float nlse_t, float del_t,
                                                float nlse_s, float del_s, int qpos, int key0, int w_t, int w_s,
                                                uint32_t (&dsp)[NC / 2], int lo_t = 0) {
+  if constexpr (!STUDENT) {
+    const float2 sc2 = make_float2(scale_log2, scale_log2), n2 = make_float2(nlse_t, nlse_t);
+    const float2 nd2 = make_float2(-del_t, -del_t);
+#pragma unroll
+    for (int c = 0; c < NC; c += 2) {
+      const float2 x2 = __ffma2_rn(make_float2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), sc2, n2);
+      float2 p2 = make_float2(ex2(x2.x), ex2(x2.y));
+      if (MASKED) {
+        const int key = key0 + c;
+        if (!(key <= qpos - lo_t && key > qpos - w_t)) p2.x = 0.f;
+        if (!(key + 1 <= qpos - lo_t && key + 1 > qpos - w_t)) p2.y = 0.f;
+      }
+      const float2 dd = __fadd2_rn(make_float2(__uint_as_float(dpt[c]), __uint_as_float(dpt[c + 1])), nd2);
+      const float2 d2 = __fmul2_rn(p2, dd);
+      dsp[c / 2] = pack_bf16(d2.x, d2.y);
+    }
+  } else {
 #pragma unroll
   for (int c = 0; c < NC; c += 2) {
     float d[2];
@@ -189,6 +233,7 @@ __device__ __forceinline__ void dq_elementwise(const uint32_t (&sv)[NC], const u
       }
     }
     dsp[c / 2] = pack_bf16(d[0], d[1]);
+  }
   }
 }
 
