@@ -76,7 +76,8 @@ struct AttnBwdParams {
   // with operands in tensor memory the freed staging tiles become extra TMA ring slots (0: keep the 3-slot ring)
   int deep_ring;
   // optional timeline probe: when non-null, one CTA in the middle of the grid writes clock64() stamps of steps
-  // [8, 24) here, 16 slots per step (0-4 control thread, 5-8 first element-wise warp of the step's group)
+  // [8, 24) here, 16 slots per step (0-4 control thread; 5-8 first element-wise warp of the step's group, only when
+  // built with -DTTCD_ATTN_BWD_PROBE_EW)
   long long* probe;
   int probe_mask;      // bit e set: event e is stamped (every stamp costs the stamping thread ~100 clocks)
   // dV may be written into a wider row (the packed q|k|v gradient of a fused projection): row and batch strides
@@ -553,7 +554,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       const bool st = iter_student(it);
       const float* vslot = vslot_of(it);
       const float next_stat = (it + STEP < n_iters && fetcher) ? fetch_stat(it + STEP) : 0.f;  // in flight during this step
+#ifdef TTCD_ATTN_BWD_PROBE_EW      // element-wise stamps cost every warp a few instructions per step: compiled in on demand
       const bool stamper = (warp & 7) == 0 && lane == 0;
+#else
+      constexpr bool stamper = false;
+#endif
       if (stamper) stamp(it, 5);
       if (SPLIT) named_barrier_sync(1, 512); else named_barrier_sync(1 + grp, 256);
       ok = wait_all(sdp_full(it % C::NSETS), (it / C::NSETS) & 1, 311);
