@@ -156,3 +156,40 @@ def test_final_block_eval_manifest_and_merges(tmp_path):
 def test_verify_configs_reports_every_config():
     import verify_configs
     assert verify_configs.main(["--build"]) == 0
+
+
+def test_checkpoint_bench_runs_both_attention_implementations(tmp_path):
+    """benchmarks/bench_checkpoint.py: timing + predictions with the fused and the two-call dual attention agree."""
+    sys.path.insert(0, str(ROOT / "benchmarks"))
+    import bench_checkpoint as bc
+    from ttcd_b200 import ops
+    from ttcd_b200.models import IPTTCDv9Config, IPTTCDForCausalLM
+
+    class Tok:
+        eos_token_id = None
+
+        def __call__(self, text, return_tensors=None, add_special_tokens=False):
+            from types import SimpleNamespace
+            return SimpleNamespace(input_ids=torch.tensor([[(ord(c) * 7) % 61 for c in text]]))
+
+        def decode(self, ids, skip_special_tokens=True):
+            return " ".join(str(i) for i in ids)
+
+    data = tmp_path / "validation.jsonl"
+    data.write_text("\n".join(json.dumps({"input": "abcdefgh" * (4 + i), "answer_prefix": " ans", "outputs": ["1"]}) for i in range(3)))
+    torch.manual_seed(0)
+    model = IPTTCDForCausalLM(IPTTCDv9Config(hidden_size=32, num_hidden_layers=2, num_heads=4, num_kv_heads=2, head_dim=8,
+                                             intermediate_size=64, vocab_size=64, window_size=24, window_size_student=8,
+                                             ttt_mode=True, ttt_chunk=8, ttt_layers=[1], fuse_cross_entropy=False,
+                                             fuse_linear_cross_entropy=False, max_position_embeddings=256)).eval()
+    prompts, refs = bc.load_prompts(str(data), 2)
+    assert len(prompts) == 3 and prompts[0].endswith(" ans")
+    dev = torch.device("cpu")
+    a = bc.run(model, Tok(), prompts, refs, 4, dev, "fused")
+    ops.set_dual_attention_impl("two_pass")
+    try:
+        b = bc.run(model, Tok(), prompts, refs, 4, dev, "two_pass")
+    finally:
+        ops.set_dual_attention_impl("fused")
+    assert len(a["predictions"]) == 2 and a["predictions"] == b["predictions"]
+    assert a["median_prefill_ms"] > 0 and "decode_ms_per_token" in a
