@@ -75,6 +75,8 @@ struct AttnBwdParams {
   int a_in_tmem;
   // with operands in tensor memory the freed staging tiles become extra TMA ring slots (0: keep the 3-slot ring)
   int deep_ring;
+  // element-wise warps poll the S / dP barrier tightly instead of parking on it (experiment switch)
+  int spin_sdp;
   // optional timeline probe: when non-null, one CTA in the middle of the grid writes clock64() stamps of steps
   // [8, 24) here, 16 slots per step (0-4 control thread; 5-8 first element-wise warp of the step's group, only when
   // built with -DTTCD_ATTN_BWD_PROBE_EW)
@@ -561,7 +563,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
 #endif
       if (stamper) stamp(it, 5);
       if (SPLIT) named_barrier_sync(1, 512); else named_barrier_sync(1 + grp, 256);
-      ok = wait_all(sdp_full(it % C::NSETS), (it / C::NSETS) & 1, 311);
+      ok = p.spin_sdp ? (__all_sync(0xffffffffu, mbar_wait_spin(sdp_full(it % C::NSETS), (it / C::NSETS) & 1, abort_flag, 311)) != 0)
+                      : wait_all(sdp_full(it % C::NSETS), (it / C::NSETS) & 1, 311);
       if (!ok) break;
       if (stamper) stamp(it, 6);
       tc_fence_after_sync();
@@ -972,7 +975,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     for (int it = (PP ? grp : 0); it < n_iters && ok; it += STEP) {
       const bool st = iter_student(it);
       const int key0 = iter_key0(it) + part * 32;
-      ok = wait_all(sdp_full(it & 1), (it >> 1) & 1, 331);
+      ok = p.spin_sdp ? (__all_sync(0xffffffffu, mbar_wait_spin(sdp_full(it & 1), (it >> 1) & 1, abort_flag, 331)) != 0)
+                      : wait_all(sdp_full(it & 1), (it >> 1) & 1, 331);
       if (!ok) break;
       tc_fence_after_sync();
       const uint32_t ts = t_set(it) + lane_addr + part * 32;
@@ -1305,6 +1309,11 @@ TTCD_EXPORT int ttcd_attn_bwd_cp(const void* q, const void* k, const void* v, co
     return (e != nullptr && e[0] == '3') ? 0 : 1;
   }();
   p.deep_ring = deep_ring;
+  static const int spin_sdp = [] {
+    const char* e = getenv("TTCD_ATTN_BWD_SPIN");
+    return (e != nullptr && e[0] == '1') ? 1 : 0;
+  }();
+  p.spin_sdp = spin_sdp;
   p.probe = g_next_probe;
   p.probe_mask = g_next_probe_mask;
   g_next_probe = nullptr;

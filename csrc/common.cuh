@@ -110,10 +110,16 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t pari
 
 // Bounded wait.  Returns false when the budget ran out or another role of the CTA aborted.
 __device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code);
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code);
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
 #ifdef TTCD_PARK_ALL_WAITS      // a translation unit may park every wait (define before including this header)
   return mbar_wait_parked(bar, parity, abort_flag, code);
+#else
+  return mbar_wait_spin(bar, parity, abort_flag, code);
 #endif
+}
+// The tight poll: lowest wake-up latency, but the polling warp keeps issuing instructions.
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   for (uint32_t it = 1;; ++it) {
