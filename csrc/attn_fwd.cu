@@ -166,31 +166,34 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
           tma_load_3d(sbase + S::V_OFF + slot * S::KV_BYTES + d * S::KV_REGION, map, v_full(slot),
                       kvh * D + d * 64, row, b);
       };
+      // descriptors as (low word + constant step, constant high word): one add per k-step on this thread
+      constexpr uint32_t HI = umma_desc_hi_sw128(1024);
+      const uint32_t q_lo = umma_desc_lo(sbase + S::Q_OFF, 16), p_lo = umma_desc_lo(sbase + S::P_OFF, 16);
       auto issue_s = [&](int i) {
-        const uint32_t kslot = sbase + S::K_OFF + (i & 1) * S::KV_BYTES;
+        const uint32_t k_lo = umma_desc_lo(sbase + S::K_OFF + (i & 1) * S::KV_BYTES, 16);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint64_t ad = umma_desc_sw128(sbase + S::Q_OFF + (k / 4) * S::Q_REGION + (k % 4) * 32, 16, 1024);
-          const uint64_t bd = umma_desc_sw128(kslot + (k / 4) * S::KV_REGION + (k % 4) * 32, 16, 1024);
-          umma_ss(tmem_base + (i & 1) * ATT_BN, ad, bd, idesc_s, k != 0 ? 1u : 0u);
+          const uint32_t qo = ((k / 4) * S::Q_REGION + (k % 4) * 32) >> 4;
+          const uint32_t ko = ((k / 4) * S::KV_REGION + (k % 4) * 32) >> 4;
+          umma_ss(tmem_base + (i & 1) * ATT_BN, umma_desc_join(q_lo + qo, HI), umma_desc_join(k_lo + ko, HI), idesc_s,
+                  k != 0 ? 1u : 0u);
         }
         umma_commit(s_full(i & 1));
       };
       auto issue_pv = [&](int i) {
-        const uint32_t vslot = sbase + S::V_OFF + (i & 1) * S::KV_BYTES;
+        // V as the MN-major B operand: 64 keys of the contraction, the next 64 columns KV_REGION bytes on
+        const uint32_t v_lo = umma_desc_lo(sbase + S::V_OFF + (i & 1) * S::KV_BYTES, S::KV_REGION);
+        const uint32_t acc = i != 0;
         if (p.p_in_tmem) {
 #pragma unroll
-          for (int k = 0; k < ATT_BN / 16; ++k) {
-            const uint64_t bd = umma_desc_sw128(vslot + k * 2048, S::KV_REGION, 1024);
-            umma_ts(tmem_o, tmem_base + (i & 1) * ATT_BN + k * 8, bd, idesc_o, (i | k) != 0 ? 1u : 0u);
-          }
+          for (int k = 0; k < ATT_BN / 16; ++k)
+            umma_ts(tmem_o, tmem_base + (i & 1) * ATT_BN + k * 8, umma_desc_join(v_lo + k * (2048 >> 4), HI), idesc_o,
+                    acc | (k != 0));
         } else {
 #pragma unroll
-          for (int k = 0; k < ATT_BN / 16; ++k) {
-            const uint64_t ad = umma_desc_sw128(sbase + S::P_OFF + k * 32, 16, 1024);
-            const uint64_t bd = umma_desc_sw128(vslot + k * 2048, S::KV_REGION, 1024);
-            umma_ss(tmem_o, ad, bd, idesc_o, (i | k) != 0 ? 1u : 0u);
-          }
+          for (int k = 0; k < ATT_BN / 16; ++k)
+            umma_ss(tmem_o, umma_desc_join(p_lo + k * 2, HI), umma_desc_join(v_lo + k * (2048 >> 4), HI), idesc_o,
+                    acc | (k != 0));
         }
         umma_commit(pv_done);
       };
