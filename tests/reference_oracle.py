@@ -14,7 +14,8 @@ from pathlib import Path
 import torch
 import torch.nn.functional as F
 
-REFERENCE_ROOT = Path(os.environ.get("TTCD_REFERENCE_ROOT", "/root/reference"))
+# the upstream checkout: TTCD_REFERENCE_ROOT, else a `reference` directory beside this repository
+REFERENCE_ROOT = Path(os.environ.get("TTCD_REFERENCE_ROOT", str(Path(__file__).resolve().parents[2] / "reference")))
 
 
 def available() -> bool:
