@@ -2,17 +2,20 @@
 //
 //   attn_bwd_dkdv : one CTA per (128-key block, kv head, batch); loops over the query blocks (64 rows)
 //                   and the query heads of the GQA group that can see those keys.  Per step it forms
-//                   S^T = K Q^T and dP^T = V dO^T on tcgen05 (keys on the TMEM lanes), eight warps turn
-//                   them into P^T and dS^T in shared memory, and dV += P^T dO, dK += dS^T Q accumulate
+//                   S^T = K Q^T and dP^T = V dO^T on tcgen05 (keys on the TMEM lanes), the element-wise warps
+//                   turn them into P^T and dS^T, and dV += P^T dO, dK += dS^T Q accumulate
 //                   in TMEM.  In dual-window mode the student and teacher gradients are summed here:
 //                   dS = P_T (dP_T - delta_T) + P_S (dP_S - delta_S),  dV += P_T^T dO_T + P_S^T dO_S.
 //   attn_bwd_dq   : one CTA per (128-query block, head, batch); loops over the key blocks (64 keys) of
 //                   the teacher window, recomputes S / dP and accumulates dQ += dS K in TMEM.
 //
-// Software pipeline: the S / dP accumulators are double-buffered in TMEM wherever the 512 columns
-// allow it (always in dq; in dkdv for the single-window case), so the tensor core computes the
-// S / dP of step i+1 while the eight warps do the element-wise work of step i; operand tiles come
-// through a 3-slot (2-slot for dual dkdv) TMA ring (128-byte swizzle, no multicast).  One swizzled
+// Roles per CTA: 8 or 16 element-wise warps (16 = two groups that take alternate steps, group g on TMEM set g), one
+// warp whose elected thread issues every tcgen05.mma / tcgen05.commit, one warp whose elected thread issues every
+// TMA copy.  Software pipeline: the S / dP accumulators are double-buffered in TMEM wherever the 512 columns
+// allow it (always in dq; in dkdv for the single-window and the one-softmax dual case), so the tensor core
+// computes the S / dP of step i+1 while the element-wise warps work on step i; P^T / dS^T go back into tensor
+// memory over the columns they were computed from and feed the accumulate MMAs as TMEM A operands; operand tiles
+// come through a 4-5 slot TMA ring (128-byte swizzle, no multicast) with per-slot "free" barriers.  One swizzled
 // tile serves as a K-major operand of one MMA and an MN-major operand of another (Q and dO in dkdv,
 // K in dq), so nothing is transposed in memory.  The reference has no fused dual-window backward:
 // training there runs two flash-attn backward passes whose dq/dk/dv are summed by autograd
