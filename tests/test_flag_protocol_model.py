@@ -112,3 +112,15 @@ def test_absent_peer_becomes_a_status_not_a_hang():
     assert m.call(0, 0, _value, budget=0.3, use_barrier=False) is False      # rank 1 never runs
     assert time.time() - t0 < 5.0
     assert m.status[0] in (641, 635)
+
+
+def test_magic_number_division_is_exact_for_step_indices():
+    """csrc/attn_bwd.cu FastDiv: n / d == (n * (0xffffffff // d + 1)) >> 32 for 1 < d < 65536 and 0 <= n < 65536
+    (the kernel takes the plain division outside that range)."""
+    import random
+    rng = random.Random(0)
+    cases = [(n, d) for d in (2, 3, 5, 7, 63, 64, 65, 130, 131, 260, 1024, 4097, 65535) for n in (0, 1, d - 1, d, d + 1, 65535)]
+    cases += [(rng.randrange(65536), rng.randrange(2, 65536)) for _ in range(20000)]
+    for n, d in cases:
+        magic = (0xFFFFFFFF // d + 1) & 0xFFFFFFFF
+        assert (n * magic) >> 32 == n // d, (n, d)
