@@ -5,7 +5,7 @@ write) between timed iterations, and is reported with the achieved fraction of t
 in MEASURED_PEAKS.json (cuBLAS bf16 burst throughput and copy bandwidth).  Library baselines
 (cuBLAS via torch.matmul, flash-attn 2) are timed the same way when importable.
 
-    python benchmarks/bench_kernels.py [--what gemm,attn,conv,attn_bwd] [--seq 65536] [--batch 1]
+    python benchmarks/bench_kernels.py [--what gemm,attn,conv,attn_bwd,misc] [--seq 65536] [--batch 1]
 """
 from __future__ import annotations
 
@@ -172,6 +172,78 @@ def bench_conv():
         emit(**row)
 
 
+def bench_misc():
+    """Fast-weight scan, linear-cross-entropy, Newton-Schulz and add+RMSNorm at the flagship shapes against plain
+    PyTorch statements of the same ops (cuBLAS matmuls, materialised logits)."""
+    from ttcd_b200 import ops
+    from ttcd_b200.ops import reference as ref
+    torch.manual_seed(0)
+    # --- fast-weight chunk scan: 1 x 16 chunks x 4096 tokens, d_i 3072, d_h 1024 (one TTT layer at 64K)
+    b, T, C, d_i, d_h = 1, 16, 4096, 3072, 1024
+    mk = lambda *sh, sc=1.0: (torch.randn(*sh, device="cuda") * sc).to(BF).requires_grad_()  # noqa: E731
+    z_out, z_tgt, z_hat = mk(b, T, C, d_i, sc=0.3), mk(b, T, C, d_i, sc=0.3), mk(b, T, C, d_i, sc=0.3)
+    beta = torch.sigmoid(torch.randn(b, T, C, 1, device="cuda")).to(BF).requires_grad_()
+    w_down, w_upd = mk(d_h, d_i, sc=0.02), mk(d_i, d_h, sc=0.02)
+    ins = [z_out, z_tgt, z_hat, beta, w_down, w_upd]
+
+    def scan_fused():
+        y = ops.ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_upd, lr=0.3, update_every=2)
+        return torch.autograd.grad(y, ins, torch.ones_like(y))
+
+    def scan_torch():
+        y = ref.ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_upd, lr=0.3, update_every=2, state_dtype=torch.bfloat16)
+        return torch.autograd.grad(y, ins, torch.ones_like(y))
+
+    emit(bench="ttt_scan_fwd_bwd", shape=[b, T, C, d_i, d_h], fused_ms=round(timeit(scan_fused, iters=5), 3),
+         torch_cublas_ms=round(timeit(scan_torch, iters=5), 3))
+    del z_out, z_tgt, z_hat, beta, ins
+    # --- linear-cross-entropy: 65536 tokens x 1024 -> 151936 classes
+    n, hdim, vocab = 65536, 1024, 151936
+    hid = (torch.randn(n, hdim, device="cuda") * 0.5).to(BF).requires_grad_()
+    w = (torch.randn(vocab, hdim, device="cuda") * 0.02).to(BF).requires_grad_()
+    labels = torch.randint(0, vocab, (n,), device="cuda")
+
+    def lce():
+        return torch.autograd.grad(ops.linear_cross_entropy(hid, labels, w), [hid, w])
+
+    def lce_torch():                                  # chunked so that the fp32 logits fit: 8 x [8192, vocab]
+        tot = 0.0
+        gh = torch.zeros_like(hid)
+        gw = torch.zeros_like(w, dtype=torch.float32)
+        for c0 in range(0, n, 8192):
+            hc = hid[c0:c0 + 8192].detach().requires_grad_()
+            wc = w.detach().requires_grad_()
+            loss = torch.nn.functional.cross_entropy((hc @ wc.t()).float(), labels[c0:c0 + 8192], reduction="sum") / n
+            a, b_ = torch.autograd.grad(loss, [hc, wc])
+            gh[c0:c0 + 8192] = a
+            gw += b_
+            tot += float(loss.detach())
+        return tot
+
+    emit(bench="linear_cross_entropy_fwd_bwd", tokens=n, hidden=hdim, vocab=vocab, fused_ms=round(timeit(lce, iters=3), 3),
+         torch_cublas_ms=round(timeit(lce_torch, iters=3, warmup=1), 3), tflops=round(6 * n * hdim * vocab / 1e12, 1))
+    del hid, w
+    # --- Newton-Schulz (5 steps) on the model's matrices
+    for shape in ((3072, 1024), (2048, 1024), (1024, 1024)):
+        g = torch.randn(*shape, device="cuda").to(BF)
+        with torch.no_grad():
+            emit(bench="newton_schulz5", shape=list(shape), fused_ms=round(timeit(lambda: ops.newton_schulz(g)), 4),
+                 torch_cublas_ms=round(timeit(lambda: ref.newton_schulz(g)), 4))
+    # --- add + RMSNorm, 65536 x 1024
+    _, bw_peak, src = peaks()
+    x = torch.randn(65536, 1024, device="cuda").to(BF).requires_grad_()
+    res = torch.randn(65536, 1024, device="cuda").to(BF)
+    wn = torch.ones(1024, device="cuda", dtype=BF, requires_grad=True)
+    with torch.no_grad():
+        ms_f = timeit(lambda: ops.rmsnorm(x, wn, 1e-6, residual=res, prenorm=True))
+    y, _ = ops.rmsnorm(x, wn, 1e-6, residual=res, prenorm=True)
+    gy = torch.randn_like(y)
+    ms_b = timeit(lambda: torch.autograd.grad(y, [x, wn], gy, retain_graph=True))
+    gb_f = 4 * x.numel() * 2 / 1e9          # x, residual in; y, new residual out
+    emit(bench="add_rmsnorm", shape=[65536, 1024], fwd_ms=round(ms_f, 4), fwd_frac_of_copy_bw=round(gb_f / ms_f * 1e3 / bw_peak, 3),
+         bwd_ms=round(ms_b, 4), peak_source=src)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--what", default="gemm,attn,conv")
@@ -190,6 +262,8 @@ def main():
         bench_attn(seqs, batches, bwd=True)
     if "conv" in what:
         bench_conv()
+    if "misc" in what:
+        bench_misc()
     st = _native.device_status()
     if st:
         emit(error=f"device status {st}")
