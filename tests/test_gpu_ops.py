@@ -382,3 +382,22 @@ def test_split_k_weight_gradient_gemm():
     y.backward(wide[:, :n_out].contiguous())
     ref = wide[:, :n_out].float().t() @ x.float()
     assert (lin.weight.grad.float() - ref).abs().max().item() < 2e-2 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 1024), (3, 304, 1088), (16, 1024, 3072), (5, 151936, 1024)])
+def test_small_row_linear_uses_the_weight_streaming_kernel(M, N, K):
+    """A handful of rows times a [N, K] weight (the decode step) against fp32 PyTorch; the same call with 17 rows takes
+    the tensor-core path and must agree with it."""
+    from ttcd_b200 import _native
+    from ttcd_b200.ops import cuda
+    torch.manual_seed(M + N)
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+    before = _native.launch_count
+    y = cuda.gemm(x, w.t())
+    assert _native.launch_count == before + 1          # one kernel, no padding copies
+    want = x.float() @ w.float().t()
+    torch.testing.assert_close(y.float(), want, rtol=2e-2, atol=2e-2)
+    x17 = torch.cat([x, torch.randn(17 - M, K, device="cuda").bfloat16()])
+    y17 = cuda.gemm(x17, w.t())
+    torch.testing.assert_close(y17.reshape(17, N)[:M].float(), y.float(), rtol=2e-2, atol=2e-2)

@@ -69,6 +69,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, out_dtype=_BF16, alpha: float = 1.
     """
     _check(a, "a"), _check(b, "b")
     M0, K0, N0 = a.shape[-2], a.shape[-1], b.shape[-1]
+    if (M0 <= 16 and a.dim() == 2 and b.dim() == 2 and out_dtype == _BF16 and beta == 0.0 and c_in is None
+            and row_scale is None and out is None and K0 % 8 == 0 and b.stride(0) == 1 and b.stride(1) % 8 == 0
+            and a.stride(1) == 1 and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0
+            and nv.has("ttcd_gemv_small")):
+        # a few rows times a [N, K] weight (b is its transposed view): the decode step; one pass over the weight
+        y = torch.empty(M0, N0, dtype=_BF16, device=a.device)
+        nv.call("ttcd_gemv_small", nv.ptr(a), nv.ptr(b), nv.ptr(y), nv.i32(M0), nv.i32(N0), nv.i32(K0), nv.i64(a.stride(0)),
+                nv.i64(b.stride(1)), nv.i64(N0), nv.f32(alpha), nv.stream_ptr())
+        return y
     if M0 < 128 or N0 < 128 or K0 < 64:
         # tiny problem: zero-pad up to one tile (TMA boxes must fit inside their tensors)
         if out is not None or c_in is not None or row_scale is not None:
