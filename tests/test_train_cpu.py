@@ -56,6 +56,29 @@ def test_lr_min_absolute_and_anneal_rewrite():
                                   "--lr_scheduler.warmup_steps", "10"])
     s = build_lr_schedule(cfg)
     assert s.lr_min == pytest.approx(0.1)
+    # a floor at or above the peak rate means "no decay" (ratio clamped to 1), never a rising rate
+    cfg = JobConfig().parse_args(["--training.steps", "100", "--optimizer.lr", "1e-4", "--lr_scheduler.lr_min_absolute", "3e-4",
+                                  "--lr_scheduler.warmup_steps", "0"])
+    s = build_lr_schedule(cfg)
+    assert s.lr_min == 1.0 and s.lr(99) == pytest.approx(1e-4)
+
+
+def test_anneal_begin_step_rewrites_the_run_length():
+    """steps 10000, begin 4000, ratio 0.1: the run ends at 4400 and decays linearly over its last 400 steps
+    (values worked out by hand from the reference's rewrite, flame/train.py:430-452)."""
+    cfg = JobConfig().parse_args(["--training.steps", "10000", "--optimizer.lr", "1.0", "--lr_scheduler.warmup_steps", "200",
+                                  "--lr_scheduler.decay_ratio", "0.1", "--lr_scheduler.anneal_begin_step", "4000",
+                                  "--lr_scheduler.decay_type", "linear"])
+    s = build_lr_schedule(cfg)
+    assert cfg.training.steps == 4400 and s.training_steps == 4400
+    assert cfg.lr_scheduler.decay_ratio == pytest.approx(400 / 4400)
+    assert s.decay_steps == 400 and s.stable_steps == 3800
+    assert s.lr(3999) == 1.0                                   # last stable step
+    assert s.lr(4000) == pytest.approx(1.0 - 1 / 401)          # first decay step
+    assert s.lr(4199) == pytest.approx(1.0 - 200 / 401)        # half way
+    assert s.lr(4399) == pytest.approx(1.0 - 400 / 401)        # last step stays above the floor
+    with pytest.raises(ValueError):
+        build_lr_schedule(JobConfig().parse_args(["--training.steps", "100", "--lr_scheduler.anneal_begin_step", "40"]))
 
 
 # ------------------------------------------------------------------------------------------- data

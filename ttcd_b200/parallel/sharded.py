@@ -192,6 +192,28 @@ class ShardedDataParallel:
                 if mp.master is not None:
                     mp.master.copy_(g.flat_param[mp.offset:mp.offset + mp.param.numel()].float())
 
+    def load_full_master(self, full: dict[int, torch.Tensor]) -> None:
+        """Take full-precision parameter values (``{param.data_ptr(): fp32 tensor of the parameter's shape}``, e.g. as
+        read from a checkpoint) into this rank's fp32 master shards; entries that are missing or not fp32 keep the
+        value derived from the bf16 parameter."""
+        for g in self.groups:
+            shard = g.numel // self.world
+            lo, hi = self.rank * shard, (self.rank + 1) * shard
+            muon = {id(mp.param): mp for mp in g.muon}
+            for p, o in zip(g.params, g.offsets):
+                src = full.get(p.data_ptr())
+                if src is None or src.dtype != torch.float32 or src.numel() != p.numel():
+                    continue
+                src = src.reshape(-1)
+                mp = muon.get(id(p))
+                if mp is not None:
+                    if mp.master is not None:
+                        mp.master.copy_(src)
+                    continue
+                a, b = max(o, lo), min(o + p.numel(), hi)
+                if a < b:
+                    g.master[a - lo:b - lo].copy_(src[a - o:b - o])
+
     # ---------------------------------------------------------------------------------- reduce-scatter
     def _install_hooks(self):
         """Launch a group's gradient reduce-scatter as soon as its last parameter gradient is ready."""
@@ -454,8 +476,17 @@ class ShardedDataParallel:
             flat = self._gather_flat(g, which)
             muon_ids = {id(mp.param) for mp in g.muon}
             for p, o in zip(g.params, g.offsets):
-                if id(p) in muon_ids:      # Muon-owned: the bf16 weights every rank holds
-                    out[p.data_ptr()] = p.detach().float()
+                if id(p) in muon_ids:      # Muon-owned: the owner's fp32 master (the moments are not per element)
+                    mp = next(m for m in g.muon if m.param is p)
+                    if which != "master":
+                        out[p.data_ptr()] = p.detach().float()
+                        continue
+                    buf = torch.zeros(p.shape, dtype=torch.float32, device=self.device)
+                    if mp.owner == self.rank:
+                        buf.copy_(mp.master.view(p.shape))
+                    if self.world > 1:
+                        dist.all_reduce(buf, group=self.pg)
+                    out[p.data_ptr()] = buf
                 else:
                     out[p.data_ptr()] = flat[o:o + p.numel()].view(p.shape)
         return out

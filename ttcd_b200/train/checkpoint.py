@@ -79,9 +79,16 @@ def detect_model_prefix(keys: set[str]) -> str:
     return ""
 
 
-def load_model_weights(model: torch.nn.Module, path: str, exclude: list[str] | None = None, strict: bool = False) -> list[str]:
-    """Load model tensors from a DCP directory of either key convention.  Returns missing names."""
-    keys = checkpoint_keys(path)
+def load_model_weights(model: torch.nn.Module, path: str, exclude: list[str] | None = None, strict: bool = False,
+                       loaded: dict[int, torch.Tensor] | None = None) -> list[str]:
+    """Load model tensors from a DCP directory of either key convention.  Returns missing names.
+
+    Tensors are read in the dtype they were saved in and cast on the copy into the model; ``loaded`` (if given)
+    receives ``{parameter data_ptr: tensor as saved}`` so that a caller holding fp32 master weights can take the
+    full-precision values instead of the rounded ones."""
+    reader = dcp.FileSystemReader(path)
+    meta = reader.read_metadata().state_dict_metadata
+    keys = set(meta.keys())
     prefix = detect_model_prefix(keys)
     own = model.state_dict()
     exclude = exclude or []
@@ -93,11 +100,13 @@ def load_model_weights(model: torch.nn.Module, path: str, exclude: list[str] | N
         if any(name.startswith(e) for e in exclude):
             continue
         if prefix + name in keys:
+            props = getattr(meta[prefix + name], "properties", None)
+            saved_dtype = getattr(props, "dtype", None) or tensor.dtype
             if tp is not None and name in params:
                 from ..parallel.tensor import full_shape
-                wanted[prefix + name] = torch.empty(full_shape(params[name]), dtype=tensor.dtype, device="cpu")
+                wanted[prefix + name] = torch.empty(full_shape(params[name]), dtype=saved_dtype, device="cpu")
                 continue
-            wanted[prefix + name] = torch.empty_like(tensor, device="cpu")
+            wanted[prefix + name] = torch.empty(tensor.shape, dtype=saved_dtype, device="cpu")
         else:
             missing.append(name)
     dcp.load(wanted, checkpoint_id=path, no_dist=not (dist.is_available() and dist.is_initialized()))
@@ -112,6 +121,8 @@ def load_model_weights(model: torch.nn.Module, path: str, exclude: list[str] | N
                 from ..parallel.tensor import slice_named
                 value = slice_named(model, tp, {name: value})[name]
             own[name].copy_(value.to(own[name].dtype))
+            if loaded is not None:
+                loaded[ptr] = value
     tied_ok = {"lm_head.weight", "model.embeddings.weight"}
     hard_missing = [m for m in missing if m not in tied_ok and "rotary" not in m]
     if strict and hard_missing:
@@ -253,8 +264,12 @@ class CheckpointManager:
             return False
         t0 = time.perf_counter()
         try:
-            load_model_weights(self.engine.model, path, self.exclude)
+            as_saved: dict[int, torch.Tensor] = {}
+            load_model_weights(self.engine.model, path, self.exclude, loaded=as_saved)
             self.engine.sdp.resync_master()
+            # checkpoints written by this trainer hold the fp32 masters: take them as they are, so that a resumed
+            # run continues from exactly the weights the interrupted one had (not from their bf16 rounding)
+            self.engine.sdp.load_full_master(as_saved)
             keys = checkpoint_keys(path)
             if not weights_only and any(k.startswith("optimizer.") for k in keys):
                 self._load_training_state(path, keys)

@@ -54,22 +54,34 @@ class LRSchedule:
 
 
 def build_lr_schedule(job_config, logger=None) -> LRSchedule:
-    """Apply the lr_min_absolute and anneal_begin_step rewrites, then build the schedule."""
+    """Apply the lr_min_absolute and anneal_begin_step rewrites, then build the schedule.
+
+    Both rewrites change ``job_config`` in place, as flame/train.py:413-452 does, so that the train loop and the
+    metrics read the rewritten ``training.steps``: with ``anneal_begin_step = B`` and ``decay_ratio = r`` the run
+    ends after ``B + round(B r)`` steps and decays over exactly those last ``round(B r)`` steps.
+    """
     sched, opt, training = job_config.lr_scheduler, job_config.optimizer, job_config.training
-    lr_min = sched.lr_min
     if sched.lr_min_absolute is not None:
-        if opt.lr <= 0:
-            raise ValueError("optimizer.lr must be > 0 when lr_min_absolute is given")
-        lr_min = sched.lr_min_absolute / opt.lr
-        if logger:
-            logger.info(f"lr_min_absolute={sched.lr_min_absolute:g} -> lr_min ratio {lr_min:g}")
-    steps, decay_ratio, warmup = training.steps, sched.decay_ratio, sched.warmup_steps
+        if sched.lr_min_absolute >= opt.lr:
+            if logger:
+                logger.warning(f"lr_min_absolute ({sched.lr_min_absolute:g}) >= optimizer.lr ({opt.lr:g}): "
+                               "lr_min set to 1.0 (no decay)")
+            sched.lr_min = 1.0
+        else:
+            sched.lr_min = sched.lr_min_absolute / opt.lr
+            if logger:
+                logger.info(f"lr_min_absolute={sched.lr_min_absolute:g} -> lr_min ratio {sched.lr_min:g}")
     if sched.anneal_begin_step is not None:
-        begin = int(sched.anneal_begin_step)
-        if not 0 <= begin < steps:
-            raise ValueError("anneal_begin_step must lie inside the run")
-        decay_ratio = (steps - begin) / steps
-        warmup = min(warmup, begin)
+        begin, ratio = int(sched.anneal_begin_step), sched.decay_ratio
+        if ratio is None or ratio <= 0:
+            raise ValueError(f"anneal_begin_step={begin} requires a positive decay_ratio, got {ratio}")
+        anneal_steps = round(begin * ratio)
+        new_total = begin + anneal_steps
+        if new_total <= 0:
+            raise ValueError("anneal_begin_step must be positive")
         if logger:
-            logger.info(f"anneal from step {begin}: decay_ratio {decay_ratio:.4f}")
-    return LRSchedule(opt.lr, steps, warmup, decay_ratio, sched.decay_type, lr_min)
+            logger.info(f"anneal from step {begin}: {anneal_steps} decay steps, training.steps "
+                        f"{training.steps} -> {new_total}, decay_ratio {ratio} -> {anneal_steps / new_total:.6f}")
+        training.steps = new_total
+        sched.decay_ratio = anneal_steps / new_total
+    return LRSchedule(opt.lr, training.steps, sched.warmup_steps, sched.decay_ratio, sched.decay_type, sched.lr_min)
