@@ -9,6 +9,11 @@ ttcd_b200: HF ``AutoModelForCausalLM.from_config`` of the upstream-registered ``
 checkpointing per block, FSDP2 ``fully_shard`` per block + root with bf16 parameters and fp32 gradient
 reduction (flame/models/parallelize_fla.py:436-497), fused AdamW (eps 1e-15, betas 0.9/0.95, wd 0.1) and
 ``clip_grad_norm_(1.0)``.
+
+Activation checkpointing (``--ref-ac``): ``full`` wraps every block in ``checkpoint_wrapper`` as the recipe does;
+``none`` does not; ``auto`` (default) builds the model without checkpointing, runs one step, and rebuilds it with
+full checkpointing if that step runs out of memory on any rank (the ranks agree through an all-reduce).  The
+printed line names the setting that the timed steps ran with.
 """
 from __future__ import annotations
 
@@ -53,23 +58,29 @@ def run(args, metric, ClockSampler, timed_region, dist_env):
             if isinstance(klass.__dict__.get("_tied_weights_keys"), (list, tuple)):
                 klass._tied_weights_keys = {"lm_head.weight": "model.embeddings.weight"}
                 compat.append(f"{klass.__name__}._tied_weights_keys list->dict (transformers 5.x)")
-    torch.manual_seed(42)
-    with torch.device("cuda"):
-        model = AutoModelForCausalLM.from_config(cfg)
-    model.train()
-    if cfg.fuse_linear_cross_entropy:
-        model.criterion = FusedLinearCrossEntropyLoss(num_chunks=8)
-
-    layers = model.model.layers
-    if not args.no_ac:
-        for i in range(len(layers)):
-            layers[i] = checkpoint_wrapper(layers[i], preserve_rng_state=False)
     mesh = init_device_mesh("cuda", (world,))
     mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
-    for i, blk in enumerate(layers):
-        fully_shard(blk, mesh=mesh, mp_policy=mp, reshard_after_forward=i < len(layers) - 1)
-    fully_shard(model, mesh=mesh, mp_policy=mp)
-    opt = torch.optim.AdamW(model.parameters(), lr=1e-4, betas=(0.9, 0.95), eps=1e-15, weight_decay=0.1, fused=True)
+
+    def build(use_ac: bool):
+        torch.manual_seed(42)
+        with torch.device("cuda"):
+            model = AutoModelForCausalLM.from_config(cfg)
+        model.train()
+        if cfg.fuse_linear_cross_entropy:
+            model.criterion = FusedLinearCrossEntropyLoss(num_chunks=8)
+        layers = model.model.layers
+        if use_ac:
+            for i in range(len(layers)):
+                layers[i] = checkpoint_wrapper(layers[i], preserve_rng_state=False)
+        for i, blk in enumerate(layers):
+            fully_shard(blk, mesh=mesh, mp_policy=mp, reshard_after_forward=i < len(layers) - 1)
+        fully_shard(model, mesh=mesh, mp_policy=mp)
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-4, betas=(0.9, 0.95), eps=1e-15, weight_decay=0.1, fused=True)
+        return model, opt
+
+    ref_ac = "none" if args.no_ac else getattr(args, "ref_ac", "full")
+    use_ac = ref_ac == "full"
+    model, opt = build(use_ac)
 
     B, S, V = args.batch_per_gpu, args.seq_len, cfg.vocab_size
     n_total = args.warmup + 2 * args.steps
@@ -86,6 +97,23 @@ def run(args, metric, ClockSampler, timed_region, dist_env):
         opt.step()
         return float(out.loss.item()) if read_loss else None
 
+    if ref_ac == "auto":
+        # does one step fit without activation checkpointing?  every rank must come to the same answer
+        failed = torch.zeros(1, device="cuda")
+        try:
+            step(host[0], False)
+            torch.cuda.synchronize()
+        except torch.OutOfMemoryError:
+            failed.fill_(1.0)
+        if world > 1:
+            dist.all_reduce(failed, op=dist.ReduceOp.MAX)
+        if float(failed) > 0:
+            del model, opt
+            import gc
+            gc.collect()
+            torch.cuda.empty_cache()
+            use_ac = True
+            model, opt = build(True)
     for i in range(args.warmup):
         step(host[i], False)
     torch.cuda.synchronize()
@@ -105,7 +133,8 @@ def run(args, metric, ClockSampler, timed_region, dist_env):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic uniform-random tokens, random-init weights",
             "config": {"model": Path(args.config).stem, "global_batch": B * world, "seq_len": S,
-                       "parallelism": f"fsdp2-dp{world}", "activation_checkpointing": "none" if args.no_ac else "full",
+                       "parallelism": f"fsdp2-dp{world}", "activation_checkpointing": "full" if use_ac else "none",
+                       "activation_checkpointing_requested": ref_ac,
                        "optimizer": "AdamW(fused)", "layers": cfg.num_hidden_layers,
                        "stack": "upstream model classes + Triton/flash-attn 2/cuBLAS/cuDNN + FSDP2"},
             "clocks": clocks,

@@ -2,8 +2,16 @@
 
 Default config = the continued-training recipe on the Qwen3-0.6B shape: 28 layers, hidden 1024, 16 Q / 8 KV
 heads, head_dim 128, SwiGLU 3072, vocab 151936, tied embeddings, window 8192, student window 4096, TTT layers
-[0, 7, 14, 21]; bf16 compute, one 65536-token sequence per GPU, full activation checkpointing, AdamW
-(eps 1e-15, clip 1.0), synthetic uniform-random tokens, random-init weights.
+[0, 7, 14, 21]; bf16 compute, one 65536-token sequence per GPU, AdamW (eps 1e-15, clip 1.0), synthetic
+uniform-random tokens, random-init weights.  Activation checkpointing: the headline ``value`` keeps the
+activations of the step resident (``--ac none``: they fit in the 180 GB of a B200); the same line also carries
+``ac_full`` (every block recomputed in backward, the recipe's setting for 80 GB GPUs) from a second timed
+region.  The reference arm tries to run without checkpointing first and falls back to full checkpointing when
+that does not fit; both arms name the setting they ran in ``config.activation_checkpointing``.
+
+On more than one GPU the line also carries ``extra.cp``: the same model on ONE 65536-token sequence sharded over
+all N ranks (context parallelism, strong scaling), measured in child processes so that a failure there cannot
+take the headline with it.
 
     python bench.py --gpus 1 --steps 3 --warmup 3
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port P \
@@ -50,6 +58,10 @@ def parse_args():
                     help="activation checkpointing of this framework's arm; 'none' keeps the activations of one "
                          "64K-token step resident, which fits the 180 GB of a B200 (the reference recipe needs 'full')")
     ap.add_argument("--no-ac", action="store_true", help="same as --ac none (kept for older command lines)")
+    ap.add_argument("--ref-ac", default="auto", choices=["auto", "none", "full"],
+                    help="reference arm: 'auto' runs without activation checkpointing if that fits, else with full")
+    ap.add_argument("--no-extra", action="store_true", help="skip the ac_full and context-parallel extras")
+    ap.add_argument("--cp-worker", action="store_true", help=argparse.SUPPRESS)
     return ap.parse_args()
 
 
@@ -183,6 +195,26 @@ def run_ours(args):
     tokens = B * S * world * args.steps
     value = tokens / (ms_dev / 1e3)
     e2e = tokens / (ms_e2e / 1e3)
+    ac_mode = "none" if args.no_ac else args.ac
+    ac_full, extra = None, {}
+    if not args.no_extra:
+        if ac_mode != "full":
+            # the recipe's setting (every block recomputed in backward): same engine, same inputs, second timed region
+            try:
+                engine.set_activation_checkpointing("full")
+                engine.train_step(host[0], return_loss_on_host=False)
+                ms_full = timed_region(torch, dist, world, lambda i: engine.train_step(dev[i], return_loss_on_host=False),
+                                       args.steps)
+                ac_full = {"ms_per_step": round(ms_full / args.steps, 2), "value": round(tokens / (ms_full / 1e3), 1),
+                           "unit": "tokens/s"}
+            except Exception as exc:  # pragma: no cover
+                ac_full = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+            engine.set_activation_checkpointing(ac_mode)
+        if world > 1:
+            del dev, host, e2e_host
+            engine.sdp.zero_grad()
+            torch.cuda.empty_cache()
+            extra["cp"] = run_cp_children(args, rank, local, world)
     if rank == 0:
         print(json.dumps({
             "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
@@ -190,16 +222,86 @@ def run_ours(args):
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
             "impl": "ours",
             "config": {"model": Path(args.config).stem, "global_batch": B * world, "seq_len": S,
-                       "parallelism": f"sharded-dp{world}", "activation_checkpointing": "none" if args.no_ac else args.ac,
+                       "parallelism": f"sharded-dp{world}", "activation_checkpointing": ac_mode,
                        "optimizer": "AdamW", "l2": "per-step working set (several GB) exceeds the 126 MB L2",
                        "layers": cfg.num_hidden_layers},
             "clocks": clocks,
             "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e / args.steps, 2),
                     "h2d_bytes_per_step": B * S * 8, "d2h_bytes_per_step": 4},
             "gpu_launches": launches, "final_loss": losses[-1] if losses else None, "device_status": status,
+            "ac_full": ac_full, "extra": extra,
         }), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+# ----------------------------------------------------------------------------------------------------
+# context-parallel extra (N > 1): one 64K sequence sharded over all ranks, measured in child processes
+# ----------------------------------------------------------------------------------------------------
+CP_STEPS, CP_WARMUP, CP_TIMEOUT_S = 5, 3, 420
+
+
+def run_cp_children(args, rank, local, world) -> dict:
+    """Every rank starts one child (``bench.py --cp-worker``) with the same rank / world size and its own rendezvous
+    port; the children form their own process group, run the context-parallel measurement and rank 0's child
+    prints its JSON.  A child that fails or outlives its time limit is killed by PID and reported as an error."""
+    env = dict(os.environ)
+    env["MASTER_PORT"] = str(int(env.get("MASTER_PORT", "29500")) + 23)
+    env["TORCHELASTIC_USE_AGENT_STORE"] = "False"          # rank 0's child hosts the store of the children's group
+    for k in ("TORCHELASTIC_RUN_ID", "TORCHELASTIC_RESTART_COUNT", "TORCHELASTIC_MAX_RESTARTS"):
+        env.pop(k, None)
+    cmd = [sys.executable, str(Path(__file__).resolve()), "--cp-worker", "--gpus", str(world), "--config", args.config,
+           "--seq-len", str(args.seq_len)]
+    if args.layers is not None:
+        cmd += ["--layers", str(args.layers)]
+    try:
+        proc = subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+        try:
+            out, err = proc.communicate(timeout=CP_TIMEOUT_S)
+        except subprocess.TimeoutExpired:
+            proc.kill()
+            proc.communicate()
+            return {"degree": world, "error": f"no result within {CP_TIMEOUT_S} s"}
+        if rank != 0:
+            return {}
+        for line in reversed(out.strip().splitlines()):
+            if line.startswith("{"):
+                return json.loads(line)
+        return {"degree": world, "error": f"child exit {proc.returncode}: {err.strip()[-300:]}"}
+    except Exception as exc:  # pragma: no cover
+        return {"degree": world, "error": f"{type(exc).__name__}: {exc}"[:300]}
+
+
+def run_cp_worker(args):
+    import torch
+    import torch.distributed as dist
+    from datetime import timedelta
+
+    rank, local, world = dist_env()
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=timedelta(seconds=120))
+    from ttcd_b200 import _native
+    from ttcd_b200.train.engine import EngineConfig, TrainEngine, load_model_config
+
+    _native.load(required=True)
+    overrides = {} if args.layers is None else {"num_hidden_layers": args.layers}
+    cfg = load_model_config(args.config, **overrides)
+    engine = TrainEngine(cfg, EngineConfig(activation_checkpoint="none", context_parallel=world), device=f"cuda:{local}")
+    S, V = args.seq_len, cfg.vocab_size
+    gen = torch.Generator().manual_seed(99)                 # every rank of the group sees the same sequence
+    ids = [torch.randint(0, V, (1, S), generator=gen, dtype=torch.int64).cuda() for _ in range(CP_WARMUP + CP_STEPS)]
+    for i in range(CP_WARMUP):
+        engine.train_step(ids[i], return_loss_on_host=False)
+    ms = timed_region(torch, dist, world, lambda i: engine.train_step(ids[CP_WARMUP + i], return_loss_on_host=False), CP_STEPS)
+    loss = float(engine.last_loss)
+    status = _native.device_status()
+    peak = torch.cuda.max_memory_allocated() / 2 ** 30
+    if rank == 0:
+        print(json.dumps({"degree": world, "parallelism": f"context-parallel {world} (one {S}-token sequence over {world} GPUs)",
+                          "steps": CP_STEPS, "warmup": CP_WARMUP, "ms_per_step": round(ms / CP_STEPS, 2),
+                          "tokens_per_s": round(S * CP_STEPS / (ms / 1e3), 1), "scaling": "strong", "final_loss": loss,
+                          "device_status": status, "peak_mem_gib": round(peak, 1)}), flush=True)
+    dist.destroy_process_group()
 
 
 # ----------------------------------------------------------------------------------------------------
@@ -230,6 +332,9 @@ def main():
             rank = int(os.environ.get("RANK", "0"))
             if rank == 0:
                 print(json.dumps({"impl": "reference", "unavailable": f"{type(exc).__name__}: {exc}"[:400]}), flush=True)
+        return
+    if args.cp_worker:
+        run_cp_worker(args)
         return
     run_ours(args)
 

@@ -3,38 +3,45 @@
 //   attn_bwd_dkdv : one CTA per (128-key block, kv head, batch); loops over the query blocks (64 rows)
 //                   and the query heads of the GQA group that can see those keys.  Per step it forms
 //                   S^T = K Q^T and dP^T = V dO^T on tcgen05 (keys on the TMEM lanes), the element-wise warps
-//                   turn them into P^T and dS^T, and dV += P^T dO, dK += dS^T Q accumulate
-//                   in TMEM.  In dual-window mode the student and teacher gradients are summed here:
-//                   dS = P_T (dP_T - delta_T) + P_S (dP_S - delta_S),  dV += P_T^T dO_T + P_S^T dO_S.
+//                   turn them into P^T and dS^T, and dV += P^T dO, dK += dS^T Q accumulate in TMEM.
 //   attn_bwd_dq   : one CTA per (128-query block, head, batch); loops over the key blocks (64 keys) of
 //                   the teacher window, recomputes S / dP and accumulates dQ += dS K in TMEM.
 //
-// Roles per CTA: 8 or 16 element-wise warps (16 = two groups that take alternate steps, group g on TMEM set g), one
-// warp whose elected thread issues every tcgen05.mma / tcgen05.commit, one warp whose elected thread issues every
-// TMA copy.  Software pipeline: the S / dP accumulators are double-buffered in TMEM wherever the 512 columns
-// allow it (always in dq; in dkdv for the single-window and the one-softmax dual case), so the tensor core
-// computes the S / dP of step i+1 while the element-wise warps work on step i; P^T / dS^T go back into tensor
-// memory over the columns they were computed from and feed the accumulate MMAs as TMEM A operands; operand tiles
-// come through a 4-5 slot TMA ring (128-byte swizzle, no multicast) with per-slot "free" barriers.  One swizzled
-// tile serves as a K-major operand of one MMA and an MN-major operand of another (Q and dO in dkdv,
-// K in dq), so nothing is transposed in memory.  The reference has no fused dual-window backward:
-// training there runs two flash-attn backward passes whose dq/dk/dv are summed by autograd
-// (custom_models/ipttcd/modeling_ipttcdv9.py:686-690; profiling/FUSED_ATTENTION_DESIGN.md:68-69).
+// Dual window goes through ONE softmax: inside the student window P_S = r P_T with the per-row ratio
+// r = exp(lse_T - lse_S), so the student's gradient stream folds into the teacher's (dO' = dO_T + r dO_S,
+// delta' = delta_T + r delta_S, formed once per layer by attn_combine_kernel); every block step then uses either
+// (dO', delta', keys inside the student window) or (dO_T, delta_T, keys outside it), and the blocks that straddle
+// the window edge take one step of each.
+//
+// Roles per CTA: 16 element-wise warps in two groups that take alternate steps (group g works on TMEM set g, so the
+// element-wise work of step i+1 starts as soon as its S / dP are there), one warp whose elected thread issues every
+// tcgen05.mma / tcgen05.commit, one warp whose elected thread issues every TMA copy.  The S / dP accumulators are
+// double-buffered in TMEM; P^T / dS^T go back into tensor memory over the columns they were computed from and feed
+// the accumulate MMAs as TMEM A operands; operand tiles come through a 4-5 slot TMA ring (128-byte swizzle, no
+// multicast) with per-slot "free" barriers.  One swizzled tile serves as a K-major operand of one MMA and an
+// MN-major operand of another (Q and dO in dkdv, K in dq), so nothing is transposed in memory.
+//
+// Packed batches (several sequences in one row): per-token `seg_start` / `seg_end` arrays bound the visible keys of
+// a query to its own sequence inside the kernels (the role of flash_attn_varlen_func in fla/layers/attn.py:229-270),
+// and the block ranges are clipped to the sequences that a tile touches.
+//
+// The reference has no fused dual-window backward: training there runs two flash-attn backward passes whose
+// dq/dk/dv are summed by autograd (custom_models/ipttcd/modeling_ipttcdv9.py:686-690;
+// profiling/FUSED_ATTENTION_DESIGN.md:68-69).
 // every role of these kernels waits long enough per step for parked waits to pay (measured: 13.8 vs 14.3 ms)
 #define TTCD_PARK_ALL_WAITS 1
 #include "common.cuh"
-
-#include <cstdlib>
 
 #include <algorithm>
 
 namespace ttcd {
 
-// NEW element-wise warps + 1 tensor-core issue warp + 1 TMA producer warp (one elected thread each: a thread that
-// issued the copies as well spent more clocks per step on them than the tensor core needs for the step).  A warp may only touch the TMEM lanes of its quarter (warp % 4); two
-// warps per quarter split the 64 S columns of a step.  NEW == 8: one group does every step.  NEW == 16: two such
-// groups take alternate steps (needs two S / dP sets and P / dS kept in tensor memory).
-constexpr int bwd_threads(int n_ew) { return (n_ew + 2) * 32; }
+// 16 element-wise warps + 1 tensor-core issue warp + 1 TMA producer warp (one elected thread each: a thread that
+// issued the copies as well spent more clocks per step on them than the tensor core needs for the step).  A warp
+// may only touch the TMEM lanes of its quarter (warp % 4); two warps per quarter split the 64 S columns of a step,
+// and the two groups of eight warps take alternate steps.
+constexpr int BWD_EW_WARPS = 16;
+constexpr int BWD_THREADS = (BWD_EW_WARPS + 2) * 32;
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ float ex2(float x) {
@@ -66,44 +73,25 @@ struct FastDiv {
 };
 
 struct AttnBwdParams {
-  const float* lse_t; const float* lse_s;      // [B, H, Tq] natural log
-  const float* delta_t; const float* delta_s;  // [B, H, Tq] rowsum(dO * O)
+  const float* lse_t;                           // [B, H, Tq] natural log (teacher / only window)
+  const float* delta_t;                         // [B, H, Tq] rowsum(dO_T * O_T)
+  const float* delta_c;                         // dual: delta' = delta_T + r delta_S
   bf16* dq; bf16* dk; bf16* dv;                 // [B,Tq,H,D], [B,Tk,HK,D], [B,Tk,HK,D]
   int Tq, Tk, H, HK;
   int w_t, w_s;
   float scale, scale_log2;
   // context parallel: keys [0, halo_len) live in the previous rank's K/V buffers (rows halo_row0..)
   int halo_len, halo_row0;
-  // single-window dQ kernel: keep Q and dO (loop-invariant A operands) in tensor memory
-  int a_in_tmem;
-  // with operands in tensor memory the freed staging tiles become extra TMA ring slots (0: keep the 3-slot ring)
-  int deep_ring;
-  // element-wise warps poll the S / dP barrier tightly instead of parking on it (experiment switch)
-  int spin_sdp;
-  // optional timeline probe: when non-null, one CTA in the middle of the grid writes clock64() stamps of steps
-  // [8, 24) here, 16 slots per step (0-4 control thread; 5-8 first element-wise warp of the step's group, only when
-  // built with -DTTCD_ATTN_BWD_PROBE_EW)
-  long long* probe;
-  int probe_mask;      // bit e set: event e is stamped (every stamp costs the stamping thread ~100 clocks)
   // dV may be written into a wider row (the packed q|k|v gradient of a fused projection): row and batch strides
   // in elements; 0 = contiguous [B, Tk, HK, D]
   int64_t ld_dv, sb_dv;
-  // dK/dV kernel, dual window through ONE softmax: inside the student window P_S = r * P_T with the per-row ratio
-  // r = exp(lse_T - lse_S), so the two gradient streams collapse into dO' = dO_T + r dO_S and delta' = delta_T +
-  // r delta_S there, and outside it only the teacher stream exists.  combine != 0: `delta_s` holds delta', the
-  // second dO tensor map addresses dO', and every block step uses either (dO', delta', keys inside the student
-  // window) or (dO_T, delta_T, keys outside it); blocks that straddle the window edge take both steps.
+  // dual window: the second dO tensor map addresses dO', `delta_c` holds delta' (see the file header)
   int combine;
+  // packed sequences (null: none): per token, the first token of its sequence and one past its last
+  const int* seg_start; const int* seg_end;
+  // check of the bounded waits: the dK/dV producer leaves out the K/V copies, so that the wait for them runs out
+  int skip_kv_load;
 };
-
-// NP packed bf16 pairs (2 NP values) -> part `part` (of 32 / NP) of one 128-byte row of a K-major SW128 tile
-template <int NP>
-__device__ __forceinline__ void store_row_part_packed(uint8_t* tile, int row, int part, const uint32_t (&v)[NP]) {
-#pragma unroll
-  for (int c = 0; c < NP / 4; ++c)
-    *reinterpret_cast<uint4*>(tile + sw128_offset(row, part * (NP / 4) + c)) =
-        make_uint4(v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
-}
 
 // 32 fp32 accumulator columns (times `scale`) -> 32 bf16 written to global memory (64 contiguous bytes)
 __device__ __forceinline__ void store_out32(bf16* dst, const uint32_t (&a)[32], float scale = 1.f) {
@@ -119,182 +107,106 @@ __device__ __forceinline__ void store_out32(bf16* dst, const uint32_t (&a)[32], 
 }
 
 // Element-wise core of the dK/dV step for one thread: NC query columns of one key row.
-//   stats: shared-memory block [-lse_t*log2e | delta_t | -lse_s*log2e | delta_s] (64 floats each),
+//   stats: shared-memory block [-lse*log2e | delta | first token of the query's sequence (int bits)], 64 each,
 //          already offset to this thread's first column.
-//   p_t = 2^(s*c - lse_t),  dS (unscaled) = p_t (dP_t - delta_t) [+ p_s (dP_s - delta_s)]
-// MASKED = false is the common case of a block that is fully inside every window.
-template <bool MASKED, bool STUDENT, int NC>
-__device__ __forceinline__ void dkdv_elementwise(const uint32_t (&sv)[NC], const uint32_t (&dpt)[NC],
-                                                 const uint32_t (&dps)[NC], const float* stats, float scale_log2,
-                                                 int key, int qpos0, int w_t, int w_s, bool key_ok,
-                                                 uint32_t (&ptp)[NC / 2], uint32_t (&psp)[NC / 2],
-                                                 uint32_t (&dsp)[NC / 2], int lo_t = 0) {
-  if constexpr (!STUDENT) {
-    // packed fp32 pairs (two lanes per FFMA / FMUL): the element-wise phase is bound by instruction issue
-    const float2 sc2 = make_float2(scale_log2, scale_log2), neg1 = make_float2(-1.f, -1.f);
-#pragma unroll
-    for (int c = 0; c < NC; c += 4) {
-      const float4 nl = *reinterpret_cast<const float4*>(stats + c);
-      const float4 dl = *reinterpret_cast<const float4*>(stats + 64 + c);
-#pragma unroll
-      for (int hp = 0; hp < 2; ++hp) {
-        const int j0 = c + 2 * hp;
-        const float2 n2 = hp ? make_float2(nl.z, nl.w) : make_float2(nl.x, nl.y);
-        const float2 l2 = hp ? make_float2(dl.z, dl.w) : make_float2(dl.x, dl.y);
-        const float2 x2 = __ffma2_rn(make_float2(__uint_as_float(sv[j0]), __uint_as_float(sv[j0 + 1])), sc2, n2);
-        float2 p2 = make_float2(ex2(x2.x), ex2(x2.y));
-        if (MASKED) {
-          const int qpos = qpos0 + j0;
-          if (!(key_ok && key <= qpos - lo_t && key > qpos - w_t)) p2.x = 0.f;
-          if (!(key_ok && key <= qpos + 1 - lo_t && key > qpos + 1 - w_t)) p2.y = 0.f;
-        }
-        const float2 dd = __ffma2_rn(l2, neg1, make_float2(__uint_as_float(dpt[j0]), __uint_as_float(dpt[j0 + 1])));
-        const float2 d2 = __fmul2_rn(p2, dd);
-        ptp[j0 / 2] = pack_bf16(p2.x, p2.y);
-        dsp[j0 / 2] = pack_bf16(d2.x, d2.y);
-      }
-    }
-  } else {
+//   p = 2^(s*c - lse),  dS (unscaled) = p (dP - delta);  visible pairs:  qpos - hi < key <= qpos - lo
+//   (and key >= the query's sequence start when PACKED).
+// MASKED = false is the common case of a block that is fully visible.
+// Packed fp32 pairs (two lanes per FFMA / FMUL): the element-wise phase is bound by instruction issue.
+template <bool MASKED, bool PACKED, int NC>
+__device__ __forceinline__ void dkdv_elementwise(const uint32_t (&sv)[NC], const uint32_t (&dpt)[NC], const float* stats,
+                                                 float scale_log2, int key, int qpos0, int lo, int hi, bool key_ok,
+                                                 uint32_t (&ptp)[NC / 2], uint32_t (&dsp)[NC / 2]) {
+  const float2 sc2 = make_float2(scale_log2, scale_log2), neg1 = make_float2(-1.f, -1.f);
 #pragma unroll
   for (int c = 0; c < NC; c += 4) {
     const float4 nl = *reinterpret_cast<const float4*>(stats + c);
     const float4 dl = *reinterpret_cast<const float4*>(stats + 64 + c);
-    const float nls[4] = {nl.x, nl.y, nl.z, nl.w};
-    const float dls[4] = {dl.x, dl.y, dl.z, dl.w};
-    float nss[4] = {0.f, 0.f, 0.f, 0.f}, dss[4] = {0.f, 0.f, 0.f, 0.f};
-    if (STUDENT) {
-      const float4 ns = *reinterpret_cast<const float4*>(stats + 128 + c);
-      const float4 dsv = *reinterpret_cast<const float4*>(stats + 192 + c);
-      nss[0] = ns.x; nss[1] = ns.y; nss[2] = ns.z; nss[3] = ns.w;
-      dss[0] = dsv.x; dss[1] = dsv.y; dss[2] = dsv.z; dss[3] = dsv.w;
-    }
-    float pt[4], ps[4], d[4];
+    int4 sg = make_int4(0, 0, 0, 0);
+    if (MASKED && PACKED) sg = *reinterpret_cast<const int4*>(stats + 128 + c);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float s = __uint_as_float(sv[c + j]);
-      pt[j] = ex2(fmaf(s, scale_log2, nls[j]));
+    for (int hp = 0; hp < 2; ++hp) {
+      const int j0 = c + 2 * hp;
+      const float2 n2 = hp ? make_float2(nl.z, nl.w) : make_float2(nl.x, nl.y);
+      const float2 l2 = hp ? make_float2(dl.z, dl.w) : make_float2(dl.x, dl.y);
+      const float2 x2 = __ffma2_rn(make_float2(__uint_as_float(sv[j0]), __uint_as_float(sv[j0 + 1])), sc2, n2);
+      float2 p2 = make_float2(ex2(x2.x), ex2(x2.y));
       if (MASKED) {
-        const int qpos = qpos0 + c + j;
-        if (!(key_ok && key <= qpos - lo_t && key > qpos - w_t)) pt[j] = 0.f;
+        const int qpos = qpos0 + j0;
+        const int s0 = hp ? sg.z : sg.x, s1 = hp ? sg.w : sg.y;
+        if (!(key_ok && key <= qpos - lo && key > qpos - hi && key >= s0)) p2.x = 0.f;
+        if (!(key_ok && key <= qpos + 1 - lo && key > qpos + 1 - hi && key >= s1)) p2.y = 0.f;
       }
-      d[j] = pt[j] * (__uint_as_float(dpt[c + j]) - dls[j]);
-      if (STUDENT) {
-        ps[j] = ex2(fmaf(s, scale_log2, nss[j]));
-        if (MASKED) {
-          const int qpos = qpos0 + c + j;
-          if (!(key_ok && key <= qpos && key > qpos - w_s)) ps[j] = 0.f;
-        }
-        d[j] = fmaf(ps[j], __uint_as_float(dps[c + j]) - dss[j], d[j]);
-      }
+      const float2 dd = __ffma2_rn(l2, neg1, make_float2(__uint_as_float(dpt[j0]), __uint_as_float(dpt[j0 + 1])));
+      const float2 d2 = __fmul2_rn(p2, dd);
+      ptp[j0 / 2] = pack_bf16(p2.x, p2.y);
+      dsp[j0 / 2] = pack_bf16(d2.x, d2.y);
     }
-    ptp[c / 2] = pack_bf16(pt[0], pt[1]);
-    ptp[c / 2 + 1] = pack_bf16(pt[2], pt[3]);
-    dsp[c / 2] = pack_bf16(d[0], d[1]);
-    dsp[c / 2 + 1] = pack_bf16(d[2], d[3]);
-    if (STUDENT) {
-      psp[c / 2] = pack_bf16(ps[0], ps[1]);
-      psp[c / 2 + 1] = pack_bf16(ps[2], ps[3]);
-    }
-  }
   }
 }
 
-// Element-wise core of the dQ step: NC key columns of one query row (statistics live in registers).
-template <bool MASKED, bool STUDENT, int NC>
-__device__ __forceinline__ void dq_elementwise(const uint32_t (&sv)[NC], const uint32_t (&dpt)[NC],
-                                               const uint32_t (&dps)[NC], float scale_log2, float nlse_t, float del_t,
-                                               float nlse_s, float del_s, int qpos, int key0, int w_t, int w_s,
-                                               uint32_t (&dsp)[NC / 2], int lo_t = 0) {
-  if constexpr (!STUDENT) {
-    const float2 sc2 = make_float2(scale_log2, scale_log2), n2 = make_float2(nlse_t, nlse_t);
-    const float2 nd2 = make_float2(-del_t, -del_t);
-#pragma unroll
-    for (int c = 0; c < NC; c += 2) {
-      const float2 x2 = __ffma2_rn(make_float2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), sc2, n2);
-      float2 p2 = make_float2(ex2(x2.x), ex2(x2.y));
-      if (MASKED) {
-        const int key = key0 + c;
-        if (!(key <= qpos - lo_t && key > qpos - w_t)) p2.x = 0.f;
-        if (!(key + 1 <= qpos - lo_t && key + 1 > qpos - w_t)) p2.y = 0.f;
-      }
-      const float2 dd = __fadd2_rn(make_float2(__uint_as_float(dpt[c]), __uint_as_float(dpt[c + 1])), nd2);
-      const float2 d2 = __fmul2_rn(p2, dd);
-      dsp[c / 2] = pack_bf16(d2.x, d2.y);
-    }
-  } else {
+// Element-wise core of the dQ step: NC key columns of one query row (statistics live in registers); visible pairs
+// qpos - hi < key <= qpos - lo and key >= seg_lo (the first key of the query's sequence; 0 without packing).
+template <bool MASKED, int NC>
+__device__ __forceinline__ void dq_elementwise(const uint32_t (&sv)[NC], const uint32_t (&dpt)[NC], float scale_log2,
+                                               float nlse, float del, int qpos, int key0, int lo, int hi, int seg_lo,
+                                               uint32_t (&dsp)[NC / 2]) {
+  const float2 sc2 = make_float2(scale_log2, scale_log2), n2 = make_float2(nlse, nlse);
+  const float2 nd2 = make_float2(-del, -del);
 #pragma unroll
   for (int c = 0; c < NC; c += 2) {
-    float d[2];
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const float s = __uint_as_float(sv[c + j]);
-      const int key = key0 + c + j;
-      float pt = ex2(fmaf(s, scale_log2, nlse_t));
-      if (MASKED && !(key <= qpos - lo_t && key > qpos - w_t)) pt = 0.f;
-      d[j] = pt * (__uint_as_float(dpt[c + j]) - del_t);
-      if (STUDENT) {
-        float ps = ex2(fmaf(s, scale_log2, nlse_s));
-        if (MASKED && !(key <= qpos && key > qpos - w_s)) ps = 0.f;
-        d[j] = fmaf(ps, __uint_as_float(dps[c + j]) - del_s, d[j]);
-      }
+    const float2 x2 = __ffma2_rn(make_float2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), sc2, n2);
+    float2 p2 = make_float2(ex2(x2.x), ex2(x2.y));
+    if (MASKED) {
+      const int key = key0 + c;
+      if (!(key <= qpos - lo && key > qpos - hi && key >= seg_lo)) p2.x = 0.f;
+      if (!(key + 1 <= qpos - lo && key + 1 > qpos - hi && key + 1 >= seg_lo)) p2.y = 0.f;
     }
-    dsp[c / 2] = pack_bf16(d[0], d[1]);
-  }
+    const float2 dd = __fadd2_rn(make_float2(__uint_as_float(dpt[c]), __uint_as_float(dpt[c + 1])), nd2);
+    const float2 d2 = __fmul2_rn(p2, dd);
+    dsp[c / 2] = pack_bf16(d2.x, d2.y);
   }
 }
 
 // =================================================================================================
 // dK / dV
 // =================================================================================================
-template <int D, bool DUAL>
+template <int D>
 struct DkdvCfg {
   static constexpr int DB = D / 64;
-  static constexpr int NSETS = DUAL ? 1 : 2;    // S/dP accumulator sets in TMEM
-  static constexpr int NSLOTS = DUAL ? 2 : 3;   // Q/dO tile ring when P^T / dS^T are staged in shared memory
-  // single window with P^T / dS^T in tensor memory: their staging tiles (32 KB, right behind the ring) are a fourth
-  // ring slot, so that a tile load has two steps to arrive instead of one
-  static constexpr int MAXSLOTS = DUAL ? 2 : 4;
-  static constexpr int SET_COLS = DUAL ? 192 : 128;
+  static constexpr int NSETS = 2;               // S/dP accumulator sets in TMEM
+  static constexpr int NSLOTS = 4;              // Q/dO tile ring: a tile load has two steps to arrive
+  static constexpr int SET_COLS = 128;
   static constexpr int KEY_REGION = 128 * 128;  // [128 keys x 64 d] swizzled
   static constexpr int ROW_REGION = 64 * 128;   // [64 rows x 64 d] swizzled
   static constexpr int TILE_BYTES = DB * ROW_REGION;
-  static constexpr int NTILES = DUAL ? 3 : 2;   // Q, dO_T (, dO_S) per slot
+  static constexpr int NTILES = 2;              // Q, dO per slot
   static constexpr int K_OFF = 0;
   static constexpr int V_OFF = K_OFF + DB * KEY_REGION;
   static constexpr int RING_OFF = V_OFF + DB * KEY_REGION;            // NSLOTS x NTILES x TILE_BYTES
-  static constexpr int PT_OFF = RING_OFF + NSLOTS * NTILES * TILE_BYTES;
-  static constexpr int PS_OFF = PT_OFF + KEY_REGION;                  // only used when DUAL
-  static constexpr int DS_OFF = PS_OFF + (DUAL ? KEY_REGION : 0);
-  static constexpr int VEC_OFF = DS_OFF + KEY_REGION;                 // 4 slots x 4 vectors x 64 floats
+  static constexpr int VEC_OFF = RING_OFF + NSLOTS * NTILES * TILE_BYTES;   // 4 slots x 4 vectors x 64 words
   static constexpr int BAR_OFF = VEC_OFF + 4 * 4 * 64 * 4;
-  // kv_full, tiles_full[MAXSLOTS], sdp_full[NSETS], ew_done[2], acc_done, all_done, slot_free[MAXSLOTS]
-  static constexpr int NBARS = 1 + MAXSLOTS + NSETS + 4 + MAXSLOTS;
-  static_assert(DUAL || 2 * KEY_REGION >= NTILES * TILE_BYTES, "the staging tiles must hold one more ring slot");
+  // kv_full, tiles_full[NSLOTS], sdp_full[NSETS], ew_done[2], all_done, slot_free[NSLOTS]
+  static constexpr int NBARS = 1 + NSLOTS + NSETS + 2 + 1 + NSLOTS;
   static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16;
 };
 
-template <int D, bool DUAL, int NEW, bool SPLIT>
-__global__ void __launch_bounds__(bwd_threads(NEW), 1)
+template <int D>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                      const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ CUtensorMap tma_dot,
-                     const __grid_constant__ CUtensorMap tma_dos, const __grid_constant__ CUtensorMap tma_kh,
+                     const __grid_constant__ CUtensorMap tma_doc, const __grid_constant__ CUtensorMap tma_kh,
                      const __grid_constant__ CUtensorMap tma_vh, const AttnBwdParams p) {
-  using C = DkdvCfg<D, DUAL>;
+  using C = DkdvCfg<D>;
+  constexpr int NEW = BWD_EW_WARPS;
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sbase = smem_u32(smem);
   const uint32_t bars = sbase + C::BAR_OFF;
   const uint32_t kv_full = bars;
   auto tiles_full = [&](int s) { return bars + 8u * (1 + s); };
-  auto sdp_full = [&](int s) { return bars + 8u * (1 + C::MAXSLOTS + s); };
-  // NEW == 16: two groups of eight element-wise warps take alternate steps (group g the steps of TMEM set g), so
-  // the element-wise work of step i+1 starts as soon as its S / dP are there instead of after step i's
-  // SPLIT (with NEW == 16): both groups work on the same step, group g on the g-th 16 columns of every warp's 32
-  constexpr bool PP = NEW == 16 && !SPLIT;
-  static_assert(!SPLIT || NEW == 16, "column split needs two groups");
-  static_assert(!PP || C::NSETS == 2, "alternating groups need two S / dP sets");
-  auto ew_done = [&](int g) { return bars + 8u * (1 + C::MAXSLOTS + C::NSETS + g); };
-  const uint32_t acc_done = ew_done(2);
-  const uint32_t all_done = acc_done + 8u;
+  auto sdp_full = [&](int s) { return bars + 8u * (1 + C::NSLOTS + s); };
+  auto ew_done = [&](int g) { return bars + 8u * (1 + C::NSLOTS + C::NSETS + g); };
+  const uint32_t all_done = ew_done(2);
   auto slot_free = [&](int s) { return all_done + 8u * (1 + s); };   // the MMAs that read ring slot s have completed
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::BAR_OFF + C::NBARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -306,15 +218,17 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   const int b = blockIdx.z;
   const int G = p.H / p.HK;
   const int off = p.Tk - p.Tq;
+  const bool packed = p.seg_start != nullptr;
 
-  // query rows that can see keys [n0, n0+127] through the teacher window
+  // query rows that can see keys [n0, n0+127] through the teacher window (and, packed, inside their sequences)
   const int row_lo = max(0, n0 - off);
-  const int row_hi = min(p.Tq - 1, n0 + 127 + p.w_t - 1 - off);
+  int row_hi = min(p.Tq - 1, n0 + 127 + p.w_t - 1 - off);
+  if (packed) row_hi = min(row_hi, p.seg_end[min(n0 + 127, p.Tk - 1)] - 1 - off);
   const int jb_lo = row_lo / 64;
   const int nqb = row_hi >= row_lo ? (row_hi / 64 - jb_lo + 1) : 0;
-  // combined dual mode: query blocks [jb_lo, jb1) only hold pairs inside the student window, (jb2, ..] only pairs
+  // dual window: query blocks [jb_lo, jb1) only hold pairs inside the student window, (jb2, ..] only pairs
   // outside it, [jb1, jb2] straddle its edge and take two steps (student part, then teacher-only part)
-  const bool combine = !DUAL && p.combine != 0;
+  const bool combine = p.combine != 0;
   int pre = nqb, nb = 0, jb1 = 0;
   if (combine && nqb > 0) {
     auto fdiv = [](int a, int d) { return a >= 0 ? a / d : -((-a + d - 1) / d); };
@@ -332,13 +246,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
     *abort_flag = ((sbase & 1023u) != 0) ? 1 : 0;
     if (*abort_flag) atomicCAS(&g_status, 0, 399);
     mbar_init(kv_full, 1);
-    for (int s = 0; s < C::MAXSLOTS; ++s) mbar_init(tiles_full(s), 1);
+    for (int s = 0; s < C::NSLOTS; ++s) mbar_init(tiles_full(s), 1);
     for (int s = 0; s < C::NSETS; ++s) mbar_init(sdp_full(s), 1);
-    mbar_init(ew_done(0), SPLIT ? 16 : 8);
+    mbar_init(ew_done(0), 8);
     mbar_init(ew_done(1), 8);
-    mbar_init(acc_done, 1);
     mbar_init(all_done, 1);
-    for (int s = 0; s < C::MAXSLOTS; ++s) mbar_init(slot_free(s), 1);
+    for (int s = 0; s < C::NSLOTS; ++s) mbar_init(slot_free(s), 1);
     mbar_fence_init();
   }
   if (warp == NEW) {
@@ -350,18 +263,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t t_dk = tmem_base, t_dv = tmem_base + 128;
-  auto t_set = [&](int it) { return tmem_base + 256 + (it % C::NSETS) * C::SET_COLS; };  // S | dP_T | dP_S
+  auto t_set = [&](int it) { return tmem_base + 256 + (it & 1) * C::SET_COLS; };  // S^T | dP^T
   const bool healthy = (*abort_flag == 0);
-  // single window: P^T and dS^T go back into tensor memory over the S^T / dP^T columns they were computed from
-  // (bf16 pairs; the half of a warp pair keeps to its own 32 columns) and feed the dV / dK MMAs as TMEM A operands
-  const bool use_ts = !DUAL && p.a_in_tmem != 0;
-  const int nslots = (use_ts && p.deep_ring != 0) ? C::MAXSLOTS : C::NSLOTS;
-  const bool probing = p.probe != nullptr && blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && blockIdx.z == 0;
-  auto stamp = [&](int it, int ev) {
-    if (probing && it >= 8 && it < 24 && ((p.probe_mask >> ev) & 1)) p.probe[(it - 8) * 16 + ev] = clock64();
-  };
 
-  const FastDiv by_steps(steps), by_slots(nslots);
+  const FastDiv by_steps(steps);
   auto iter_head = [&](int it) { return kvh * G + by_steps.div(it); };
   auto iter_block = [&](int it) {          // query block of step `it`
     const int s = by_steps.mod(it);
@@ -369,7 +274,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
     if (s < pre + 2 * nb) return jb1 + (s - pre) / 2;
     return jb_lo + s - nb;
   };
-  auto iter_inner = [&](int it) {          // combined mode: 1 = student part (dO', delta'), 0 = teacher-only part
+  auto iter_inner = [&](int it) {          // dual: 1 = student part (dO', delta'), 0 = teacher-only part
     if (!combine) return 0;
     const int s = by_steps.mod(it);
     if (s < pre) return 1;
@@ -377,39 +282,38 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
     return 0;
   };
   auto iter_row0 = [&](int it) { return iter_block(it) * 64; };
-  auto iter_student = [&](int it) { return DUAL && (iter_row0(it) + off < n0 + 127 + p.w_s); };
-  auto slot_base = [&](int it) { return sbase + C::RING_OFF + by_slots.mod(it) * C::NTILES * C::TILE_BYTES; };
+  auto slot_base = [&](int it) { return sbase + C::RING_OFF + (it & (C::NSLOTS - 1)) * C::NTILES * C::TILE_BYTES; };
+  static_assert((C::NSLOTS & (C::NSLOTS - 1)) == 0, "ring slots: power of two");
 
   if (warp == NEW + 1 && healthy && n_iters > 0) {
     // ---- TMA producer: K/V of this key block once, then the Q / dO tiles of every step through the ring
     if (elect_one()) {
       auto load_tiles = [&](int it) {
-        const int slot = by_slots.mod(it);
+        const int slot = it & (C::NSLOTS - 1);
         const int h = iter_head(it), r0 = iter_row0(it);
-        const bool st = iter_student(it);
         const uint32_t base = slot_base(it);
-        mbar_expect_tx(tiles_full(slot), C::TILE_BYTES * (st ? 3 : 2));
+        mbar_expect_tx(tiles_full(slot), C::TILE_BYTES * 2);
     #pragma unroll
         for (int d = 0; d < C::DB; ++d) {
           tma_load_3d(base + d * C::ROW_REGION, &tma_q, tiles_full(slot), h * D + d * 64, r0, b);
-          tma_load_3d(base + C::TILE_BYTES + d * C::ROW_REGION, iter_inner(it) ? &tma_dos : &tma_dot, tiles_full(slot),
+          tma_load_3d(base + C::TILE_BYTES + d * C::ROW_REGION, iter_inner(it) ? &tma_doc : &tma_dot, tiles_full(slot),
                       h * D + d * 64, r0, b);
-          if (DUAL && st)
-            tma_load_3d(base + 2 * C::TILE_BYTES + d * C::ROW_REGION, &tma_dos, tiles_full(slot), h * D + d * 64, r0, b);
         }
       };
       bool ok = true;
-      mbar_expect_tx(kv_full, 2 * C::DB * C::KEY_REGION);
+      if (!p.skip_kv_load) {
+        mbar_expect_tx(kv_full, 2 * C::DB * C::KEY_REGION);
 #pragma unroll
-      for (int d = 0; d < C::DB; ++d) {
-        const bool halo = n0 < p.halo_len;  // plain TMA loads from the previous rank's memory
-        const int krow = halo ? p.halo_row0 + n0 : n0 - p.halo_len;
-        tma_load_3d(sbase + C::K_OFF + d * C::KEY_REGION, halo ? &tma_kh : &tma_k, kv_full, kvh * D + d * 64, krow, b);
-        tma_load_3d(sbase + C::V_OFF + d * C::KEY_REGION, halo ? &tma_vh : &tma_v, kv_full, kvh * D + d * 64, krow, b);
+        for (int d = 0; d < C::DB; ++d) {
+          const bool halo = n0 < p.halo_len;  // plain TMA loads from the previous rank's memory
+          const int krow = halo ? p.halo_row0 + n0 : n0 - p.halo_len;
+          tma_load_3d(sbase + C::K_OFF + d * C::KEY_REGION, halo ? &tma_kh : &tma_k, kv_full, kvh * D + d * 64, krow, b);
+          tma_load_3d(sbase + C::V_OFF + d * C::KEY_REGION, halo ? &tma_vh : &tma_v, kv_full, kvh * D + d * 64, krow, b);
+        }
       }
       for (int it = 0; it < n_iters && ok; ++it) {
-        if (it >= nslots) {                 // the slot's previous tiles (step it - nslots) have been consumed
-          ok = mbar_wait_parked(slot_free(by_slots.mod(it)), (by_slots.div(it) - 1) & 1, abort_flag, 304);
+        if (it >= C::NSLOTS) {              // the slot's previous tiles (step it - NSLOTS) have been consumed
+          ok = mbar_wait_parked(slot_free(it & (C::NSLOTS - 1)), ((it / C::NSLOTS) - 1) & 1, abort_flag, 304);
           if (!ok) break;
         }
         load_tiles(it);
@@ -417,24 +321,21 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       // stay until every copy has been consumed (or the CTA gave up): no copy may be in flight at exit
       if (ok) ok = mbar_wait_parked(all_done, 0, abort_flag, 306);
       if (!ok) {
-        mbar_drain(kv_full, 0);
-        for (int s = 0; s < nslots; ++s) { mbar_drain(tiles_full(s), 0); mbar_drain(tiles_full(s), 1); }
+        if (!p.skip_kv_load) mbar_drain(kv_full, 0);
+        for (int s = 0; s < C::NSLOTS; ++s) { mbar_drain(tiles_full(s), 0); mbar_drain(tiles_full(s), 1); }
       }
     }
   } else if (warp == NEW && healthy && n_iters > 0) {
     // ---- tensor-core issue
     if (elect_one()) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, false, false);  // [keys x q] = A(K-major) B(K-major)
-      constexpr uint32_t idesc_acc = umma_idesc_bf16(128, D, false, true);   // [keys x D] = A(K-major) B(MN-major)
+      constexpr uint32_t idesc_acc = umma_idesc_bf16(128, D, false, true);   // [keys x D] = A(TMEM) B(MN-major)
       // descriptors as (low word + constant step, constant high word): one add per k-step on this thread
       constexpr uint32_t HI = umma_desc_hi_sw128(1024);
       const uint32_t k_lo = umma_desc_lo(sbase + C::K_OFF, 16), v_lo = umma_desc_lo(sbase + C::V_OFF, 16);
-      const uint32_t pt_lo = umma_desc_lo(sbase + C::PT_OFF, 16), ps_lo = umma_desc_lo(sbase + C::PS_OFF, 16);
-      const uint32_t ds_lo = umma_desc_lo(sbase + C::DS_OFF, 16);
       auto issue_sdp = [&](int it) {
-        const bool st = iter_student(it);
         const uint32_t sq = slot_base(it);
-        const uint32_t q_lo = umma_desc_lo(sq, 16), dot_lo = q_lo + (C::TILE_BYTES >> 4), dos_lo = q_lo + (2 * C::TILE_BYTES >> 4);
+        const uint32_t q_lo = umma_desc_lo(sq, 16), do_lo = q_lo + (C::TILE_BYTES >> 4);
         const uint32_t ts = t_set(it);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
@@ -446,205 +347,123 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t ko = ((k / 4) * C::KEY_REGION + (k % 4) * 32) >> 4;
           const uint32_t ro = ((k / 4) * C::ROW_REGION + (k % 4) * 32) >> 4;
-          umma_ss(ts + 64, umma_desc_join(v_lo + ko, HI), umma_desc_join(dot_lo + ro, HI), idesc_s, k != 0);
+          umma_ss(ts + 64, umma_desc_join(v_lo + ko, HI), umma_desc_join(do_lo + ro, HI), idesc_s, k != 0);
         }
-        if (DUAL && st) {
-#pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint32_t ko = ((k / 4) * C::KEY_REGION + (k % 4) * 32) >> 4;
-            const uint32_t ro = ((k / 4) * C::ROW_REGION + (k % 4) * 32) >> 4;
-            umma_ss(ts + 128, umma_desc_join(v_lo + ko, HI), umma_desc_join(dos_lo + ro, HI), idesc_s, k != 0);
-          }
-        }
-        umma_commit(sdp_full(it % C::NSETS));
+        umma_commit(sdp_full(it & 1));
       };
       auto issue_acc = [&](int it) {
-        const bool st = iter_student(it);
         const uint32_t sq = slot_base(it);
         // Q / dO tiles as MN-major B operands: 64 rows of the contraction, the next 64 columns ROW_REGION bytes on
-        const uint32_t qm_lo = umma_desc_lo(sq, C::ROW_REGION), dotm_lo = qm_lo + (C::TILE_BYTES >> 4);
-        const uint32_t dosm_lo = qm_lo + (2 * C::TILE_BYTES >> 4);
+        const uint32_t qm_lo = umma_desc_lo(sq, C::ROW_REGION), dom_lo = qm_lo + (C::TILE_BYTES >> 4);
         const uint32_t acc = it != 0;
-        if (use_ts) {
-          const uint32_t ts = t_set(it);
+        const uint32_t ts = t_set(it);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)       // 16 queries = 8 packed columns at the start of their warp's column group
-            umma_ts(t_dv, ts + ts_packed_off(k), umma_desc_join(dotm_lo + k * (2048 >> 4), HI), idesc_acc, acc | (k != 0));
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_ts(t_dk, ts + 64 + ts_packed_off(k), umma_desc_join(qm_lo + k * (2048 >> 4), HI), idesc_acc, acc | (k != 0));
-          if (!PP) umma_commit(acc_done);   // only the single-group element-wise warps wait on it
-          return;
-        }
-#pragma unroll
-        for (int k = 0; k < 4; ++k)  // contraction over the 64 query rows
-          umma_ss(t_dv, umma_desc_join(pt_lo + k * 2, HI), umma_desc_join(dotm_lo + k * (2048 >> 4), HI), idesc_acc, acc | (k != 0));
-        if (DUAL && st) {
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_ss(t_dv, umma_desc_join(ps_lo + k * 2, HI), umma_desc_join(dosm_lo + k * (2048 >> 4), HI), idesc_acc, 1u);
-        }
+        for (int k = 0; k < 4; ++k)       // 16 queries = 8 packed columns at the start of their warp's column group
+          umma_ts(t_dv, ts + ts_packed_off(k), umma_desc_join(dom_lo + k * (2048 >> 4), HI), idesc_acc, acc | (k != 0));
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          umma_ss(t_dk, umma_desc_join(ds_lo + k * 2, HI), umma_desc_join(qm_lo + k * (2048 >> 4), HI), idesc_acc, acc | (k != 0));
-        umma_commit(acc_done);
+          umma_ts(t_dk, ts + 64 + ts_packed_off(k), umma_desc_join(qm_lo + k * (2048 >> 4), HI), idesc_acc, acc | (k != 0));
       };
 
-      bool ok = true;
-      ok = mbar_wait(kv_full, 0, abort_flag, 301);
-      if (ok && C::NSETS == 2) {
-        ok = mbar_wait(tiles_full(0), 0, abort_flag, 302);
-        if (ok) { tc_fence_after_sync(); issue_sdp(0); }
-      }
+      bool ok = mbar_wait(kv_full, 0, abort_flag, 301);
+      if (ok) ok = mbar_wait(tiles_full(0), 0, abort_flag, 302);
+      if (ok) { tc_fence_after_sync(); issue_sdp(0); }
       for (int it = 0; it < n_iters && ok; ++it) {
-        // S/dP for the step the compute warps will need next
-        const int nxt = C::NSETS == 2 ? it + 1 : it;
+        // S/dP for the step the element-wise warps will need next
+        const int nxt = it + 1;
         if (nxt < n_iters) {
-          ok = mbar_wait(tiles_full(by_slots.mod(nxt)), by_slots.div(nxt) & 1, abort_flag, 303);
+          ok = mbar_wait(tiles_full(nxt & (C::NSLOTS - 1)), (nxt / C::NSLOTS) & 1, abort_flag, 303);
           if (!ok) break;
-          stamp(it, 0);
           tc_fence_after_sync();
-          issue_sdp(nxt);  // its TMEM set was last read before ew_done(nxt - NSETS), already observed
-          stamp(it, 1);
+          issue_sdp(nxt);  // its TMEM set was last read by the accumulate MMAs of step nxt - 2, issued before
         }
-        stamp(it, 2);
-        ok = PP ? mbar_wait(ew_done(it & 1), (it >> 1) & 1, abort_flag, 305) : mbar_wait(ew_done(0), it & 1, abort_flag, 305);
+        ok = mbar_wait(ew_done(it & 1), (it >> 1) & 1, abort_flag, 305);
         if (!ok) break;
-        stamp(it, 3);
         tc_fence_after_sync();
         issue_acc(it);
-        umma_commit(slot_free(by_slots.mod(it)));   // the producer may refill this step's ring slot
-        stamp(it, 4);
+        umma_commit(slot_free(it & (C::NSLOTS - 1)));   // the producer may refill this step's ring slot
       }
       if (ok) umma_commit(all_done);      // every accumulate MMA has completed when this arrives
     }
   } else if (warp < NEW && healthy) {
-    constexpr int NPASS = NEW == 16 ? 2 : 1;
-    constexpr int NC = 32 / NPASS;              // S^T columns (queries) per pass; a thread owns 32 of a step
-    constexpr int STEP = PP ? 2 : 1;
-    const int grp = NEW == 16 ? (warp >> 3) : 0;   // alternating: takes steps grp, grp + 2, ...; split: pass grp of every step
+    constexpr int NC = 16;                      // S^T columns (queries) per pass; a thread owns 32 of a step
+    const int grp = warp >> 3;                  // takes steps grp, grp + 2, ...
     const int quarter = warp & 3, part = (warp >> 2) & 1;
     const int krow = quarter * 32 + lane;       // key row inside the block == TMEM lane
     const int key = n0 + krow;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const int ctid = threadIdx.x & 255;         // thread of the group: fetches one row statistic per step
     // statistics slot of a step: the two groups own two slots each
-    auto vslot_of = [&](int it) { return vecs + (PP ? ((it & 1) * 2 + ((it >> 1) & 1)) : (it & 1)) * 256; };
+    auto vslot_of = [&](int it) { return vecs + ((it & 1) * 2 + ((it >> 1) & 1)) * 256; };
     bool ok = true;
     auto wait_all = [&](uint32_t bar, uint32_t parity, int code) {
       const bool r = mbar_wait_parked(bar, parity, abort_flag, code);
       return __all_sync(0xffffffffu, r) != 0;
     };
-    // per-row statistics of a query block: [-lse_t*log2e | delta_t | -lse_s*log2e | delta_s], 64 each;
-    // this thread fetches element (which, r) of the block used by step `it`.  The load is issued here and its
-    // value is first touched by finish_stat at the end of the step, so that its latency is not waited out here.
+    // per-row statistics of a query block: [-lse*log2e | delta | sequence start], 64 each; this thread fetches
+    // element (which, r) of the block used by step `it`.  The load is issued here and its value is first touched
+    // by finish_stat at the end of the step, so that its latency is not waited out here.
     const int which = ctid >> 6;
-    const bool stat_is_lse = which == 0 || which == 2;
     auto fetch_stat = [&](int it) -> float {
       const int row = iter_row0(it) + (ctid & 63);
       const int64_t idx = (static_cast<int64_t>(b) * p.H + iter_head(it)) * p.Tq + row;
-      const float* src = which == 0 ? p.lse_t : which == 1 ? (iter_inner(it) ? p.delta_s : p.delta_t)
-                                                : which == 2 ? p.lse_s : p.delta_s;
-      const bool live = row < p.Tq && (which < 2 || (DUAL && iter_student(it)));
-      float raw = (stat_is_lse && row >= p.Tq) ? INFINITY : 0.f;      // p = 0 past the end (after the negation below)
-      if (live) raw = src[idx];
-      return raw;
+      if (which == 0) return row < p.Tq ? p.lse_t[idx] : INFINITY;          // p = 0 past the end (after the negation)
+      if (which == 1) return row < p.Tq ? (iter_inner(it) ? p.delta_c : p.delta_t)[idx] : 0.f;
+      if (which == 2 && packed) return __int_as_float(p.seg_start[min(row, p.Tq - 1)] + off);
+      return 0.f;
     };
-    auto finish_stat = [&](float raw) { return stat_is_lse ? -raw * LOG2E : raw; };
-    const int it0 = PP ? grp : 0;
-    const bool fetcher = !SPLIT || grp == 0;    // split: the first group's 256 threads fetch the statistics
-    if (it0 < n_iters && fetcher) vslot_of(it0)[ctid] = finish_stat(fetch_stat(it0));
-    for (int it = it0; it < n_iters && ok; it += STEP) {
+    auto finish_stat = [&](float raw) { return which == 0 ? -raw * LOG2E : raw; };
+    const int it0 = grp;
+    if (it0 < n_iters) vslot_of(it0)[ctid] = finish_stat(fetch_stat(it0));
+    for (int it = it0; it < n_iters && ok; it += 2) {
       const int r0 = iter_row0(it);
-      const bool st = iter_student(it);
       const float* vslot = vslot_of(it);
-      const float next_stat = (it + STEP < n_iters && fetcher) ? fetch_stat(it + STEP) : 0.f;  // in flight during this step
-#ifdef TTCD_ATTN_BWD_PROBE_EW      // element-wise stamps cost every warp a few instructions per step: compiled in on demand
-      const bool stamper = (warp & 7) == 0 && lane == 0;
-#else
-      constexpr bool stamper = false;
-#endif
-      if (stamper) stamp(it, 5);
-      if (SPLIT) named_barrier_sync(1, 512); else named_barrier_sync(1 + grp, 256);
-      ok = p.spin_sdp ? (__all_sync(0xffffffffu, mbar_wait_spin(sdp_full(it % C::NSETS), (it / C::NSETS) & 1, abort_flag, 311)) != 0)
-                      : wait_all(sdp_full(it % C::NSETS), (it / C::NSETS) & 1, 311);
+      const float next_stat = (it + 2 < n_iters) ? fetch_stat(it + 2) : 0.f;  // in flight during this step
+      named_barrier_sync(1 + grp, 256);
+      ok = wait_all(sdp_full(it & 1), (it >> 1) & 1, 311);
       if (!ok) break;
-      if (stamper) stamp(it, 6);
       tc_fence_after_sync();
-      const uint32_t ts = t_set(it) + lane_addr + part * 32;      // (alternating groups: set == grp)
+      const uint32_t ts = t_set(it) + lane_addr + part * 32;      // set == grp
       const int qlo_b = r0 + off, qhi_b = r0 + 63 + off;
-      // fully visible block: every (key, query) pair is inside the teacher (and student) window
-      const bool full_t = (n0 + 127 <= qlo_b) && (n0 > qhi_b - p.w_t) && (n0 + 127 < p.Tk);
-      const bool full_s = (n0 > qhi_b - p.w_s);
       const bool key_ok = key < p.Tk;
-      if (!PP && !use_ts && it >= 1) {
-        ok = wait_all(acc_done, (it - 1) & 1, 312);  // the P / dS staging tiles are free again
-        if (!ok) break;
-      }
+      // visible pairs of this step:  qpos - hi < key <= qpos - lo  (dual: student part, then teacher-only part)
+      const int inner = iter_inner(it);
+      const int lo = combine ? (inner ? 0 : p.w_s) : 0, hi = combine ? (inner ? p.w_s : p.w_t) : p.w_t;
+      // fully visible block: every (key, query) pair passes
+      bool full = (n0 + 127 <= qlo_b - lo) && (n0 > qhi_b - hi) && (n0 + 127 < p.Tk);
+      if (packed) full = full && (n0 >= __float_as_int(vslot[128 + 63]));     // sequence starts do not decrease
 #pragma unroll
-      for (int h = 0; h < NPASS; ++h) {       // alternating groups: two passes of 16 columns keep the registers low
-        if (SPLIT && h != grp) continue;      // column split: this group's pass only
-        uint32_t sv[NC], dpt[NC], dps[NC];
+      for (int h = 0; h < 2; ++h) {             // two passes of 16 columns keep the registers low
+        uint32_t sv[NC], dpt[NC];
         tmem_ld_n<NC>(ts + h * NC, sv);
         tmem_ld_n<NC>(ts + 64 + h * NC, dpt);
-        if (DUAL && st) tmem_ld_n<NC>(ts + 128 + h * NC, dps);
         tmem_ld_wait();
-        uint32_t ptp[NC / 2], psp[NC / 2], dsp[NC / 2];
+        uint32_t ptp[NC / 2], dsp[NC / 2];
         const float* stats = vslot + part * 32 + h * NC;
         const int qpos0 = r0 + part * 32 + h * NC + off;
-        if (DUAL && st) {
-          if (full_t && full_s)
-            dkdv_elementwise<false, true, NC>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, p.w_t, p.w_s, key_ok, ptp, psp, dsp);
-          else
-            dkdv_elementwise<true, true, NC>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, p.w_t, p.w_s, key_ok, ptp, psp, dsp);
-        } else if (combine) {
-          // one softmax (the teacher's): keys inside the student window with (dO', delta'), keys outside it with
-          // (dO_T, delta_T); visible pairs are  qpos - hi < key <= qpos - lo
-          const int inner = iter_inner(it);
-          const int lo = inner ? 0 : p.w_s, hi = inner ? p.w_s : p.w_t;
-          const bool full = (n0 + 127 <= qlo_b - lo) && (n0 > qhi_b - hi) && (n0 + 127 < p.Tk);
-          if (full)
-            dkdv_elementwise<false, false, NC>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, hi, hi, key_ok, ptp, psp, dsp, lo);
-          else
-            dkdv_elementwise<true, false, NC>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, hi, hi, key_ok, ptp, psp, dsp, lo);
-        } else {
-          if (full_t)
-            dkdv_elementwise<false, false, NC>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, p.w_t, p.w_s, key_ok, ptp, psp, dsp);
-          else
-            dkdv_elementwise<true, false, NC>(sv, dpt, dps, stats, p.scale_log2, key, qpos0, p.w_t, p.w_s, key_ok, ptp, psp, dsp);
-        }
-        if (use_ts) {
-          // packed over the first half of this thread's own S^T / dP^T columns, all of which (up to this pass) are read
-          tmem_st_n<NC / 2>(ts + h * (NC / 2), ptp);
-          tmem_st_n<NC / 2>(ts + 64 + h * (NC / 2), dsp);
-        } else {
-          store_row_part_packed<NC / 2>(smem + C::PT_OFF, krow, part * NPASS + h, ptp);
-          if (DUAL && st) store_row_part_packed<NC / 2>(smem + C::PS_OFF, krow, part * NPASS + h, psp);
-          store_row_part_packed<NC / 2>(smem + C::DS_OFF, krow, part * NPASS + h, dsp);
-        }
+        if (full)
+          dkdv_elementwise<false, false, NC>(sv, dpt, stats, p.scale_log2, key, qpos0, lo, hi, key_ok, ptp, dsp);
+        else if (packed)
+          dkdv_elementwise<true, true, NC>(sv, dpt, stats, p.scale_log2, key, qpos0, lo, hi, key_ok, ptp, dsp);
+        else
+          dkdv_elementwise<true, false, NC>(sv, dpt, stats, p.scale_log2, key, qpos0, lo, hi, key_ok, ptp, dsp);
+        // packed over the first half of this thread's own S^T / dP^T columns, all of which (up to this pass) are read
+        tmem_st_n<NC / 2>(ts + h * (NC / 2), ptp);
+        tmem_st_n<NC / 2>(ts + 64 + h * (NC / 2), dsp);
       }
-      if (use_ts) {
-        tmem_st_wait();
-        if (!PP && it >= 1) {
-          ok = wait_all(acc_done, (it - 1) & 1, 312);  // keeps this warp's phase count of the barrier in step
-          if (!ok) break;
-        }
-      }
-      if (stamper) stamp(it, 7);
-      if (fetcher) vslot_of(it + STEP)[ctid] = finish_stat(next_stat);
-      fence_proxy_async_smem();
+      tmem_st_wait();
+      if (it + 2 < n_iters) vslot_of(it + 2)[ctid] = finish_stat(next_stat);
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(ew_done(PP ? (it & 1) : 0));
-      if (stamper) stamp(it, 8);
+      if (lane == 0) mbar_arrive(ew_done(it & 1));
     }
-    // epilogue: dK, dV -> global (this thread: key row `krow`, one half of the D columns; with alternating groups
-    // group 0 writes dK and group 1 dV)
+    // epilogue: dK, dV -> global (this thread: key row `krow`, one half of the D columns; group 0 writes dK and
+    // group 1 dV)
     if (ok) {
       if (n_iters > 0) ok = wait_all(all_done, 0, 313);
       if (ok) {
         const int half = part;
-        const bool do_k = NEW != 16 || grp == 0, do_v = NEW != 16 || grp == 1;
+        const bool do_k = grp == 0, do_v = grp == 1;
         tc_fence_after_sync();
         const bool store = key < p.Tk;
         const int64_t rowoff = ((static_cast<int64_t>(b) * p.Tk + key) * p.HK + kvh) * D;
@@ -655,26 +474,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
 #pragma unroll
         for (int c = 0; c < COLS; c += 32) {
           uint32_t a[32];
-          if (do_k) {
-            if (n_iters > 0) {
-              tmem_ld32(t_dk + lane_addr + half * COLS + c, a);
-              tmem_ld_wait();
-            } else {
+          if (n_iters > 0) {
+            tmem_ld32((do_k ? t_dk : t_dv) + lane_addr + half * COLS + c, a);
+            tmem_ld_wait();
+          } else {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) a[j] = 0u;
-            }
-            if (store) store_out32(p.dk + rowoff + half * COLS + c, a, p.scale);  // dS was kept unscaled
+            for (int j = 0; j < 32; ++j) a[j] = 0u;
           }
-          if (do_v) {
-            if (n_iters > 0) {
-              tmem_ld32(t_dv + lane_addr + half * COLS + c, a);
-              tmem_ld_wait();
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) a[j] = 0u;
-            }
-            if (store) store_out32(p.dv + voff + half * COLS + c, a);
-          }
+          if (store && do_k) store_out32(p.dk + rowoff + half * COLS + c, a, p.scale);  // dS was kept unscaled
+          if (store && do_v) store_out32(p.dv + voff + half * COLS + c, a);
         }
       }
     }
@@ -693,48 +501,41 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
 template <int D, bool DUAL>
 struct DqCfg {
   static constexpr int DB = D / 64;
-  static constexpr int NSLOTS = 3;                 // K/V ring when dS is staged in shared memory
-  // with dS in tensor memory its staging tile and the rest of the 227 KB hold more ring slots: a K/V tile load then
-  // has MAXSLOTS - 2 steps to arrive instead of one
-  static constexpr int MAXSLOTS = DUAL ? 4 : 5;
-  static constexpr int SET_COLS = DUAL ? 192 : 128;
+  static constexpr int NSLOTS = DUAL ? 4 : 5;      // K/V ring: a tile load has NSLOTS - 2 steps to arrive
+  static constexpr int SET_COLS = 128;
   static constexpr int Q_REGION = 128 * 128;
   static constexpr int KV_REGION = 64 * 128;
   static constexpr int KV_BYTES = DB * KV_REGION;
   static constexpr int Q_OFF = 0;
   static constexpr int DOT_OFF = Q_OFF + DB * Q_REGION;
-  static constexpr int DOS_OFF = DOT_OFF + DB * Q_REGION;                 // only used when DUAL
-  static constexpr int RING_OFF = DOS_OFF + (DUAL ? DB * Q_REGION : 0);   // NSLOTS x (K, V)
-  static constexpr int DS_OFF = RING_OFF + NSLOTS * 2 * KV_BYTES;         // [128 x 64] bf16
-  static constexpr int RING_END = RING_OFF + MAXSLOTS * 2 * KV_BYTES;
-  static constexpr int BAR_OFF = RING_END > DS_OFF + Q_REGION ? RING_END : DS_OFF + Q_REGION;
-  // q_full, kv_full[MAXSLOTS], sdp_full[2], ew_done[2], acc_done, a_ready, all_done, slot_free[MAXSLOTS]
-  static constexpr int NBARS = 1 + MAXSLOTS + 2 + 2 + 3 + MAXSLOTS;
-  // single window: 128 (dQ) + 2 x 128 (S | dP sets) leaves 128 columns: Q and dO as bf16 A operands
+  static constexpr int DOC_OFF = DOT_OFF + DB * Q_REGION;                 // dO': only used when DUAL
+  static constexpr int RING_OFF = DOC_OFF + (DUAL ? DB * Q_REGION : 0);   // NSLOTS x (K, V)
+  static constexpr int BAR_OFF = RING_OFF + NSLOTS * 2 * KV_BYTES;
+  // q_full, kv_full[NSLOTS], sdp_full[2], ew_done[2], a_ready, all_done, slot_free[NSLOTS]
+  static constexpr int NBARS = 1 + NSLOTS + 2 + 2 + 2 + NSLOTS;
+  // 128 (dQ) + 2 x 128 (S | dP sets) leaves 128 columns: Q and one dO as bf16 A operands in tensor memory (single
+  // window: dO; dual window: dO', used by the steps inside the student window; the teacher-only steps read dO_T from
+  // shared memory)
   static constexpr int A_COLS = D / 2;
-  static constexpr bool CAN_TS = !DUAL;
   static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16;
 };
 
-template <int D, bool DUAL, int NEW, bool SPLIT>
-__global__ void __launch_bounds__(bwd_threads(NEW), 1)
+template <int D, bool DUAL>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                    const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ CUtensorMap tma_dot,
-                   const __grid_constant__ CUtensorMap tma_dos, const __grid_constant__ CUtensorMap tma_kh,
+                   const __grid_constant__ CUtensorMap tma_doc, const __grid_constant__ CUtensorMap tma_kh,
                    const __grid_constant__ CUtensorMap tma_vh, const AttnBwdParams p) {
   using C = DqCfg<D, DUAL>;
+  constexpr int NEW = BWD_EW_WARPS;
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sbase = smem_u32(smem);
   const uint32_t bars = sbase + C::BAR_OFF;
   const uint32_t q_full = bars;
   auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
-  auto sdp_full = [&](int s) { return bars + 8u * (1 + C::MAXSLOTS + s); };
-  // NEW == 16: two groups of eight element-wise warps take alternate steps (group g the steps of TMEM set g)
-  constexpr bool PP = NEW == 16 && !SPLIT;      // SPLIT: both groups on the same step, 16 columns per warp each
-  static_assert(!SPLIT || NEW == 16, "column split needs two groups");
-  auto ew_done = [&](int g) { return bars + 8u * (3 + C::MAXSLOTS + g); };
-  const uint32_t acc_done = ew_done(2);
-  const uint32_t a_ready = acc_done + 8u;
+  auto sdp_full = [&](int s) { return bars + 8u * (1 + C::NSLOTS + s); };
+  auto ew_done = [&](int g) { return bars + 8u * (3 + C::NSLOTS + g); };
+  const uint32_t a_ready = ew_done(2);
   const uint32_t all_done = a_ready + 8u;
   auto slot_free = [&](int s) { return all_done + 8u * (1 + s); };   // the MMAs that read ring slot s have completed
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::BAR_OFF + C::NBARS * 8);
@@ -747,12 +548,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   const int kvh = h / (p.H / p.HK);
   const int off = p.Tk - p.Tq;
   const int qlo = m0 + off, qhi = m0 + 127 + off;
+  const bool packed = p.seg_start != nullptr;
+  // packed sequences: first key of the sequence of the tile's first / last row (sequence starts do not decrease)
+  const int seg_first = packed ? p.seg_start[m0] + off : 0;
+  const int seg_last = packed ? p.seg_start[min(m0 + 127, p.Tq - 1)] + off : 0;
   const int key_hi = min(qhi, p.Tk - 1);
-  const int key_lo = max(0, qlo - p.w_t + 1);
+  const int key_lo = max(max(0, qlo - p.w_t + 1), seg_first);
   const int blk_lo = key_lo / 64;
   const int nblk = key_hi / 64 - blk_lo + 1;
-  // combined dual mode (see AttnBwdParams::combine): key blocks [blk_lo, kb1) hold only teacher-only pairs,
-  // (kb2, ..] only pairs inside the student window, [kb1, kb2] straddle its edge and take two steps
+  // dual window: key blocks [blk_lo, kb1) hold only teacher-only pairs, (kb2, ..] only pairs inside the student
+  // window, [kb1, kb2] straddle its edge and take two steps
   const bool combine = DUAL && p.combine != 0;
   int pre = nblk, nb = 0, kb1 = 0;
   if (combine) {
@@ -775,24 +580,21 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     return 1;
   };
   auto iter_key0 = [&](int it) { return iter_block(it) * 64; };
-  auto iter_student = [&](int it) { return DUAL && !combine && (iter_key0(it) + 63 > qlo - p.w_s); };
-  const int nslots = (p.a_in_tmem != 0 && p.deep_ring != 0) ? C::MAXSLOTS : C::NSLOTS;
-  const FastDiv by_slots(nslots);
+  const FastDiv by_slots(C::NSLOTS);
   auto slot_base = [&](int it) { return sbase + C::RING_OFF + by_slots.mod(it) * 2 * C::KV_BYTES; };
 
   if (threadIdx.x == 0) {
     *abort_flag = ((sbase & 1023u) != 0) ? 1 : 0;
     if (*abort_flag) atomicCAS(&g_status, 0, 398);
     mbar_init(q_full, 1);
-    for (int s = 0; s < C::MAXSLOTS; ++s) mbar_init(kv_full(s), 1);
+    for (int s = 0; s < C::NSLOTS; ++s) mbar_init(kv_full(s), 1);
     mbar_init(sdp_full(0), 1);
     mbar_init(sdp_full(1), 1);
-    mbar_init(ew_done(0), SPLIT ? 16 : 8);
+    mbar_init(ew_done(0), 8);
     mbar_init(ew_done(1), 8);
-    mbar_init(acc_done, 1);
     mbar_init(a_ready, NEW);
     mbar_init(all_done, 1);
-    for (int s = 0; s < C::MAXSLOTS; ++s) mbar_init(slot_free(s), 1);
+    for (int s = 0; s < C::NSLOTS; ++s) mbar_init(slot_free(s), 1);
     mbar_fence_init();
   }
   if (warp == NEW) {
@@ -804,13 +606,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t t_dq = tmem_base;
-  const bool use_ts = C::CAN_TS && p.a_in_tmem != 0;
   // every mode: dS goes back into tensor memory over the S columns it was computed from (bf16 pairs) and feeds the
   // dQ MMA as its TMEM A operand; the S MMA that next writes those columns is issued after that dQ MMA
-  const bool ds_ts = p.a_in_tmem != 0;
-  const uint32_t t_qa = tmem_base + 128 + 2 * C::SET_COLS;      // [384, 384 + D/2): Q, then dO
+  const uint32_t t_qa = tmem_base + 128 + 2 * C::SET_COLS;      // [384, 384 + D/2): Q, then dO (dual: dO')
   const uint32_t t_doa = t_qa + C::A_COLS;
-  auto t_set = [&](int it) { return tmem_base + 128 + (it & 1) * C::SET_COLS; };  // S | dP_T | dP_S
+  auto t_set = [&](int it) { return tmem_base + 128 + (it & 1) * C::SET_COLS; };  // S | dP
   const bool healthy = (*abort_flag == 0);
 
   if (warp == NEW + 1 && healthy) {
@@ -834,10 +634,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       for (int d = 0; d < C::DB; ++d) {
         tma_load_3d(sbase + C::Q_OFF + d * C::Q_REGION, &tma_q, q_full, h * D + d * 64, m0, b);
         tma_load_3d(sbase + C::DOT_OFF + d * C::Q_REGION, &tma_dot, q_full, h * D + d * 64, m0, b);
-        if (DUAL) tma_load_3d(sbase + C::DOS_OFF + d * C::Q_REGION, &tma_dos, q_full, h * D + d * 64, m0, b);
+        if (DUAL) tma_load_3d(sbase + C::DOC_OFF + d * C::Q_REGION, &tma_doc, q_full, h * D + d * 64, m0, b);
       }
       for (int it = 0; it < n_iters && ok; ++it) {
-        if (it >= nslots) {                 // the slot's previous tiles (step it - nslots) have been consumed
+        if (it >= C::NSLOTS) {              // the slot's previous tiles (step it - NSLOTS) have been consumed
           ok = mbar_wait_parked(slot_free(by_slots.mod(it)), (by_slots.div(it) - 1) & 1, abort_flag, 324);
           if (!ok) break;
         }
@@ -847,7 +647,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       if (ok) ok = mbar_wait_parked(all_done, 0, abort_flag, 327);
       if (!ok) {
         mbar_drain(q_full, 0);
-        for (int s = 0; s < nslots; ++s) { mbar_drain(kv_full(s), 0); mbar_drain(kv_full(s), 1); }
+        for (int s = 0; s < C::NSLOTS; ++s) { mbar_drain(kv_full(s), 0); mbar_drain(kv_full(s), 1); }
       }
     }
   } else if (warp == NEW && healthy) {
@@ -857,85 +657,59 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       constexpr uint32_t idesc_acc = umma_idesc_bf16(128, D, false, true);
       // descriptors as (low word + constant step, constant high word): one add per k-step on this thread
       constexpr uint32_t HI = umma_desc_hi_sw128(1024);
-      const uint32_t q_lo = umma_desc_lo(sbase + C::Q_OFF, 16), dot_lo = umma_desc_lo(sbase + C::DOT_OFF, 16);
-      const uint32_t dos_lo = umma_desc_lo(sbase + C::DOS_OFF, 16), ds_lo = umma_desc_lo(sbase + C::DS_OFF, 16);
+      const uint32_t dot_lo = umma_desc_lo(sbase + C::DOT_OFF, 16);
       auto issue_sdp = [&](int it) {
-        const bool st = iter_student(it);
         const uint32_t sk = slot_base(it);
         const uint32_t k_lo = umma_desc_lo(sk, 16), v_lo = k_lo + (C::KV_BYTES >> 4);
         const uint32_t ts = t_set(it);
-        if (use_ts) {
 #pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint32_t ko = ((k / 4) * C::KV_REGION + (k % 4) * 32) >> 4;
-            umma_ts(ts, t_qa + k * 8, umma_desc_join(k_lo + ko, HI), idesc_s, k != 0);
-          }
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t ko = ((k / 4) * C::KV_REGION + (k % 4) * 32) >> 4;
+          umma_ts(ts, t_qa + k * 8, umma_desc_join(k_lo + ko, HI), idesc_s, k != 0);
+        }
+        if (!DUAL || iter_inner(it)) {
 #pragma unroll
           for (int k = 0; k < D / 16; ++k) {
             const uint32_t ko = ((k / 4) * C::KV_REGION + (k % 4) * 32) >> 4;
             umma_ts(ts + 64, t_doa + k * 8, umma_desc_join(v_lo + ko, HI), idesc_s, k != 0);
           }
         } else {
-          const uint32_t do_lo = iter_inner(it) ? dos_lo : dot_lo;
 #pragma unroll
           for (int k = 0; k < D / 16; ++k) {
             const uint32_t qo = ((k / 4) * C::Q_REGION + (k % 4) * 32) >> 4;
             const uint32_t ko = ((k / 4) * C::KV_REGION + (k % 4) * 32) >> 4;
-            umma_ss(ts, umma_desc_join(q_lo + qo, HI), umma_desc_join(k_lo + ko, HI), idesc_s, k != 0);
-          }
-#pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint32_t qo = ((k / 4) * C::Q_REGION + (k % 4) * 32) >> 4;
-            const uint32_t ko = ((k / 4) * C::KV_REGION + (k % 4) * 32) >> 4;
-            umma_ss(ts + 64, umma_desc_join(do_lo + qo, HI), umma_desc_join(v_lo + ko, HI), idesc_s, k != 0);
-          }
-        }
-        if (DUAL && st) {
-#pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint32_t qo = ((k / 4) * C::Q_REGION + (k % 4) * 32) >> 4;
-            const uint32_t ko = ((k / 4) * C::KV_REGION + (k % 4) * 32) >> 4;
-            umma_ss(ts + 128, umma_desc_join(dos_lo + qo, HI), umma_desc_join(v_lo + ko, HI), idesc_s, k != 0);
+            umma_ss(ts + 64, umma_desc_join(dot_lo + qo, HI), umma_desc_join(v_lo + ko, HI), idesc_s, k != 0);
           }
         }
         umma_commit(sdp_full(it & 1));
       };
       bool ok = true;
       ok = mbar_wait(q_full, 0, abort_flag, 321) && mbar_wait(kv_full(0), 0, abort_flag, 322);
-      if (ok && use_ts) ok = mbar_wait(a_ready, 0, abort_flag, 326);      // Q and dO copied into tensor memory
+      if (ok) ok = mbar_wait(a_ready, 0, abort_flag, 326);      // Q and dO copied into tensor memory
       if (ok) { tc_fence_after_sync(); issue_sdp(0); }
       for (int it = 0; it < n_iters && ok; ++it) {
         if (it + 1 < n_iters) {
           ok = mbar_wait(kv_full(by_slots.mod(it + 1)), by_slots.div(it + 1) & 1, abort_flag, 323);
           if (!ok) break;
           tc_fence_after_sync();
-          issue_sdp(it + 1);  // its TMEM set was last read before ew_done(it-1), already observed
+          issue_sdp(it + 1);  // its TMEM set was last read by the dQ MMA of step it - 1, issued before
         }
-        ok = PP ? mbar_wait(ew_done(it & 1), (it >> 1) & 1, abort_flag, 325) : mbar_wait(ew_done(0), it & 1, abort_flag, 325);
+        ok = mbar_wait(ew_done(it & 1), (it >> 1) & 1, abort_flag, 325);
         if (!ok) break;
         tc_fence_after_sync();
         // the K tile as the MN-major B operand: 64 keys of the contraction, the next 64 columns KV_REGION bytes on
         const uint32_t km_lo = umma_desc_lo(slot_base(it), C::KV_REGION);
         const uint32_t acc = it != 0;
-        if (ds_ts) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k)  // dS as the TMEM A operand: 16 keys = 8 packed columns
-            umma_ts(t_dq, t_set(it) + ts_packed_off(k), umma_desc_join(km_lo + k * (2048 >> 4), HI), idesc_acc, acc | (k != 0));
-        } else {
-#pragma unroll
-          for (int k = 0; k < 4; ++k)  // contraction over the 64 keys of the block
-            umma_ss(t_dq, umma_desc_join(ds_lo + k * 2, HI), umma_desc_join(km_lo + k * (2048 >> 4), HI), idesc_acc, acc | (k != 0));
-        }
-        if (!PP) umma_commit(acc_done);     // only the single-group element-wise warps wait on it
+        for (int k = 0; k < 4; ++k)  // dS as the TMEM A operand: 16 keys = 8 packed columns
+          umma_ts(t_dq, t_set(it) + ts_packed_off(k), umma_desc_join(km_lo + k * (2048 >> 4), HI), idesc_acc, acc | (k != 0));
         umma_commit(slot_free(by_slots.mod(it)));   // the producer may refill this step's ring slot
       }
       if (ok) umma_commit(all_done);      // every dQ MMA has completed when this arrives
     }
   } else if (warp < NEW && healthy) {
-    constexpr int NPASS = NEW == 16 ? 2 : 1;
-    constexpr int NC = 32 / NPASS;              // S columns (keys) per pass; a thread owns 32 of a step
-    constexpr int STEP = PP ? 2 : 1;
-    const int grp = NEW == 16 ? (warp >> 3) : 0;   // alternating: takes steps grp, grp + 2, ...; split: pass grp of every step
+    constexpr int NC = 16;                      // S columns (keys) per pass; a thread owns 32 of a step
+    const int grp = warp >> 3;                  // takes steps grp, grp + 2, ...
     const int quarter = warp & 3, part = (warp >> 2) & 1;
     const int qrow = quarter * 32 + lane;
     const int row = m0 + qrow;
@@ -945,15 +719,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     const int64_t sidx = (static_cast<int64_t>(b) * p.H + h) * p.Tq + row;
     const float nlse_t = row_ok ? -p.lse_t[sidx] * LOG2E : -INFINITY;
     const float del_t = row_ok ? p.delta_t[sidx] : 0.f;
-    const float nlse_s = (DUAL && row_ok) ? -p.lse_s[sidx] * LOG2E : -INFINITY;
-    const float del_s = (DUAL && row_ok) ? p.delta_s[sidx] : 0.f;
+    const float del_c = (DUAL && row_ok) ? p.delta_c[sidx] : 0.f;
+    const int seg_lo = (packed && row_ok) ? p.seg_start[row] + off : 0;
     bool ok = true;
     auto wait_all = [&](uint32_t bar, uint32_t parity, int code) {
       const bool r = mbar_wait_parked(bar, parity, abort_flag, code);
       return __all_sync(0xffffffffu, r) != 0;
     };
-    if (use_ts) {
+    {
       // Q and dO rows: shared memory (128-byte swizzled, 64 columns per region) -> packed bf16 pairs in TMEM
+      constexpr int DO_SRC = DUAL ? C::DOC_OFF : C::DOT_OFF;
       ok = wait_all(q_full, 0, 334);
       if (ok) {
         for (int u = part + 2 * grp; u < C::DB * 2; u += NEW / 4) {      // units of 32 columns (16 packed) of a row
@@ -962,7 +737,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             const uint4 a = *reinterpret_cast<const uint4*>(smem + C::Q_OFF + reg * C::Q_REGION + sw128_offset(qrow, hc * 4 + c));
-            const uint4 g = *reinterpret_cast<const uint4*>(smem + C::DOT_OFF + reg * C::Q_REGION + sw128_offset(qrow, hc * 4 + c));
+            const uint4 g = *reinterpret_cast<const uint4*>(smem + DO_SRC + reg * C::Q_REGION + sw128_offset(qrow, hc * 4 + c));
             qa[4 * c] = a.x; qa[4 * c + 1] = a.y; qa[4 * c + 2] = a.z; qa[4 * c + 3] = a.w;
             da[4 * c] = g.x; da[4 * c + 1] = g.y; da[4 * c + 2] = g.z; da[4 * c + 3] = g.w;
           }
@@ -975,68 +750,36 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         if (lane == 0) mbar_arrive(a_ready);
       }
     }
-    for (int it = (PP ? grp : 0); it < n_iters && ok; it += STEP) {
-      const bool st = iter_student(it);
+    for (int it = grp; it < n_iters && ok; it += 2) {
       const int key0 = iter_key0(it) + part * 32;
-      ok = p.spin_sdp ? (__all_sync(0xffffffffu, mbar_wait_spin(sdp_full(it & 1), (it >> 1) & 1, abort_flag, 331)) != 0)
-                      : wait_all(sdp_full(it & 1), (it >> 1) & 1, 331);
+      ok = wait_all(sdp_full(it & 1), (it >> 1) & 1, 331);
       if (!ok) break;
       tc_fence_after_sync();
       const uint32_t ts = t_set(it) + lane_addr + part * 32;
       const int kb0 = iter_key0(it);
-      const bool full_t = (kb0 + 63 <= qlo) && (kb0 > qhi - p.w_t);
-      const bool full_s = (kb0 > qhi - p.w_s);
-      if (!PP && !ds_ts && it >= 1) {
-        ok = wait_all(acc_done, (it - 1) & 1, 332);  // the dS staging tile is free again
-        if (!ok) break;
-      }
+      // visible pairs of this step:  qpos - hi < key <= qpos - lo  (dual: teacher-only part or student part)
+      const int inner = iter_inner(it);
+      const int lo = combine ? (inner ? 0 : p.w_s) : 0, hi = combine ? (inner ? p.w_s : p.w_t) : p.w_t;
+      const float del = (combine && inner) ? del_c : del_t;
+      const bool full = (kb0 + 63 <= qlo - lo) && (kb0 > qhi - hi) && (kb0 >= seg_last);
 #pragma unroll
-      for (int h = 0; h < NPASS; ++h) {       // alternating groups: two passes of 16 columns keep the registers low
-        if (SPLIT && h != grp) continue;      // column split: this group's pass only
-        uint32_t sv[NC], dpt[NC], dps[NC];
-        tmem_ld_n<NC>(ts + h * NC, sv);
-        tmem_ld_n<NC>(ts + 64 + h * NC, dpt);
-        if (DUAL && st) tmem_ld_n<NC>(ts + 128 + h * NC, dps);
+      for (int hh = 0; hh < 2; ++hh) {          // two passes of 16 columns keep the registers low
+        uint32_t sv[NC], dpt[NC];
+        tmem_ld_n<NC>(ts + hh * NC, sv);
+        tmem_ld_n<NC>(ts + 64 + hh * NC, dpt);
         tmem_ld_wait();
         uint32_t dsp[NC / 2];
-        const int kpos0 = key0 + h * NC;
-        if (DUAL && st) {
-          if (full_t && full_s)
-            dq_elementwise<false, true, NC>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, kpos0, p.w_t, p.w_s, dsp);
-          else
-            dq_elementwise<true, true, NC>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, kpos0, p.w_t, p.w_s, dsp);
-        } else if (combine) {
-          const int inner = iter_inner(it);
-          const int lo = inner ? 0 : p.w_s, hi = inner ? p.w_s : p.w_t;
-          const float del = inner ? del_s : del_t;            // delta' was passed in place of delta_S
-          const bool full = (kb0 + 63 <= qlo - lo) && (kb0 > qhi - hi);
-          if (full)
-            dq_elementwise<false, false, NC>(sv, dpt, dps, p.scale_log2, nlse_t, del, nlse_s, del_s, qpos, kpos0, hi, hi, dsp, lo);
-          else
-            dq_elementwise<true, false, NC>(sv, dpt, dps, p.scale_log2, nlse_t, del, nlse_s, del_s, qpos, kpos0, hi, hi, dsp, lo);
-        } else {
-          if (full_t)
-            dq_elementwise<false, false, NC>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, kpos0, p.w_t, p.w_s, dsp);
-          else
-            dq_elementwise<true, false, NC>(sv, dpt, dps, p.scale_log2, nlse_t, del_t, nlse_s, del_s, qpos, kpos0, p.w_t, p.w_s, dsp);
-        }
-        if (ds_ts)
-          tmem_st_n<NC / 2>(ts + h * (NC / 2), dsp);    // over this thread's own S columns (already read)
+        const int kpos0 = key0 + hh * NC;
+        if (full)
+          dq_elementwise<false, NC>(sv, dpt, p.scale_log2, nlse_t, del, qpos, kpos0, lo, hi, seg_lo, dsp);
         else
-          store_row_part_packed<NC / 2>(smem + C::DS_OFF, qrow, part * NPASS + h, dsp);
+          dq_elementwise<true, NC>(sv, dpt, p.scale_log2, nlse_t, del, qpos, kpos0, lo, hi, seg_lo, dsp);
+        tmem_st_n<NC / 2>(ts + hh * (NC / 2), dsp);    // over this thread's own S columns (already read)
       }
-      if (ds_ts) {
-        tmem_st_wait();
-        if (!PP && it >= 1) {
-          ok = wait_all(acc_done, (it - 1) & 1, 332);  // keeps this warp's phase count of the barrier in step
-          if (!ok) break;
-        }
-      } else {
-        fence_proxy_async_smem();
-      }
+      tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(ew_done(PP ? (it & 1) : 0));
+      if (lane == 0) mbar_arrive(ew_done(it & 1));
     }
     if (ok) {
       ok = wait_all(all_done, 0, 333);
@@ -1146,14 +889,14 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const bf16* __restric
 }
 
 struct BwdMaps {
-  CUtensorMap q64, q128, k64, k128, v64, v128, dot64, dot128, dos64, dos128, kh64, kh128, vh64, vh128;
+  CUtensorMap q64, q128, k64, k128, v64, v128, dot64, dot128, doc64, doc128, kh64, kh128, vh64, vh128;
 };
 
-template <int D, bool DUAL, int NEW, bool SPLIT>
+template <int D, bool DUAL>
 static int launch_bwd(const BwdMaps& m, const AttnBwdParams& p, int B, cudaStream_t stream) {
-  auto k1 = attn_bwd_dkdv_kernel<D, DUAL, NEW, SPLIT>;
-  auto k2 = attn_bwd_dq_kernel<D, DUAL, NEW, SPLIT>;
-  constexpr int smem1 = DkdvCfg<D, DUAL>::TOTAL, smem2 = DqCfg<D, DUAL>::TOTAL;
+  auto k1 = attn_bwd_dkdv_kernel<D>;
+  auto k2 = attn_bwd_dq_kernel<D, DUAL>;
+  constexpr int smem1 = DkdvCfg<D>::TOTAL, smem2 = DqCfg<D, DUAL>::TOTAL;
   static_assert(smem1 <= 232448 && smem2 <= 232448, "shared memory budget exceeded");
   static bool configured = false;
   if (!configured) {
@@ -1162,46 +905,16 @@ static int launch_bwd(const BwdMaps& m, const AttnBwdParams& p, int B, cudaStrea
     configured = true;
   }
   dim3 g1((p.Tk + 127) / 128, p.HK, B);
-  k1<<<g1, bwd_threads(NEW), smem1, stream>>>(m.q64, m.k128, m.v128, m.dot64, m.dos64, m.kh128, m.vh128, p);
+  k1<<<g1, BWD_THREADS, smem1, stream>>>(m.q64, m.k128, m.v128, m.dot64, m.doc64, m.kh128, m.vh128, p);
   TTCD_CUDA_CHECK(cudaGetLastError());
   dim3 g2(p.H, (p.Tq + 127) / 128, B);
-  k2<<<g2, bwd_threads(NEW), smem2, stream>>>(m.q128, m.k64, m.v64, m.dot128, m.dos128, m.kh64, m.vh64, p);
+  k2<<<g2, BWD_THREADS, smem2, stream>>>(m.q128, m.k64, m.v64, m.dot128, m.doc128, m.kh64, m.vh64, p);
   return static_cast<int>(cudaGetLastError());
-}
-
-// Dual window with the dK/dV kernel in combined mode (single-window pipeline, one softmax) and the dual dQ kernel.
-template <int D, int NEW, bool SPLIT>
-static int launch_bwd_combined(const BwdMaps& m, const CUtensorMap& dop64, const CUtensorMap& dop128, const AttnBwdParams& p,
-                               const float* delta_p, int B, cudaStream_t stream) {
-  auto k1 = attn_bwd_dkdv_kernel<D, false, NEW, SPLIT>;
-  auto k2 = attn_bwd_dq_kernel<D, true, NEW, SPLIT>;
-  constexpr int smem1 = DkdvCfg<D, false>::TOTAL, smem2 = DqCfg<D, true>::TOTAL;
-  static bool configured = false;
-  if (!configured) {
-    TTCD_CUDA_CHECK(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1));
-    TTCD_CUDA_CHECK(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2));
-    configured = true;
-  }
-  AttnBwdParams p1 = p;
-  p1.combine = 1;
-  p1.delta_s = delta_p;
-  dim3 g1((p.Tk + 127) / 128, p.HK, B);
-  k1<<<g1, bwd_threads(NEW), smem1, stream>>>(m.q64, m.k128, m.v128, m.dot64, dop64, m.kh128, m.vh128, p1);
-  TTCD_CUDA_CHECK(cudaGetLastError());
-  dim3 g2(p.H, (p.Tq + 127) / 128, B);
-  k2<<<g2, bwd_threads(NEW), smem2, stream>>>(m.q128, m.k64, m.v64, m.dot128, dop128, m.kh64, m.vh64, p1);
-  return static_cast<int>(cudaGetLastError());
-}
-
-template <int NEW, bool SPLIT>
-static int dispatch_bwd(const BwdMaps& m, const AttnBwdParams& p, int B, int D, bool dual, cudaStream_t stream) {
-  // the two-softmax dual kernels have one S / dP set in dK/dV: always the single group of eight warps
-  if (D == 128)
-    return dual ? launch_bwd<128, true, 8, false>(m, p, B, stream) : launch_bwd<128, false, NEW, SPLIT>(m, p, B, stream);
-  return dual ? launch_bwd<64, true, 8, false>(m, p, B, stream) : launch_bwd<64, false, NEW, SPLIT>(m, p, B, stream);
 }
 
 }  // namespace ttcd
+
+TTCD_DEFINE_STATUS_READER(attn_bwd)
 
 // delta = rowsum(dO * O): o, d_o contiguous [B, T, H, D]; delta [B, H, T] fp32.
 TTCD_EXPORT int ttcd_attn_delta(const void* o, const void* d_o, float* delta, long long B, int T, int H, int D,
@@ -1216,10 +929,11 @@ TTCD_EXPORT int ttcd_attn_delta(const void* o, const void* d_o, float* delta, lo
   return static_cast<int>(cudaGetLastError());
 }
 
-// Inputs of the combined dual backward in one pass: o_*, do_* contiguous [B, T, H, D] bf16, lse_* [B, H, T] fp32;
-// writes delta_t, delta_p ([B, H, T] fp32) and do_p ([B, T, H, D] bf16).
+// Inputs of the dual-window backward in one pass: o_*, do_* contiguous [B, T, H, D] bf16, lse_* [B, H, T] fp32;
+// writes delta_t, delta_c ([B, H, T] fp32) and do_c ([B, T, H, D] bf16): dO' = dO_T + r dO_S,
+// delta' = delta_T + r delta_S with r = exp(lse_T - lse_S).
 TTCD_EXPORT int ttcd_attn_bwd_combine(const void* o_t, const void* do_t, const void* o_s, const void* do_s,
-                                      const float* lse_t, const float* lse_s, float* delta_t, float* delta_p, void* do_p,
+                                      const float* lse_t, const float* lse_s, float* delta_t, float* delta_c, void* do_c,
                                       long long B, int T, int H, int D, void* stream_ptr) {
   using namespace ttcd;
   if ((D != 64 && D != 128) || B <= 0) return TTCD_ERR_ARG;
@@ -1228,52 +942,37 @@ TTCD_EXPORT int ttcd_attn_bwd_combine(const void* o_t, const void* do_t, const v
   attn_combine_kernel<<<static_cast<unsigned>((items + rows_per_block - 1) / rows_per_block), 256, 0,
                         static_cast<cudaStream_t>(stream_ptr)>>>(
       static_cast<const bf16*>(o_t), static_cast<const bf16*>(do_t), static_cast<const bf16*>(o_s),
-      static_cast<const bf16*>(do_s), lse_t, lse_s, delta_t, delta_p, static_cast<bf16*>(do_p), B, T, H, D);
+      static_cast<const bf16*>(do_s), lse_t, lse_s, delta_t, delta_c, static_cast<bf16*>(do_c), B, T, H, D);
   return static_cast<int>(cudaGetLastError());
 }
 
-// Gradients of (dual-window) attention.  q/k/v strided as in ttcd_attn_fwd_cp; do_t/do_s contiguous
-// [B, Tq, H, D] (do_s null => single window); dq [B,Tq,H,D], dk/dv [B, halo_len + Tk_local, HK, D] bf16
-// contiguous: their first halo_len rows are the gradients of the previous rank's keys.
-// Row / batch strides (elements) of the dV output of the NEXT ttcd_attn_bwd / ttcd_attn_bwd_cp call of this thread;
-// consumed (reset to contiguous) by that call.
-static thread_local long long g_next_ld_dv = 0, g_next_sb_dv = 0;
-// Combined gradient stream of the NEXT dual-window call of this thread: dO' = dO_T + r dO_S ([B, Tq, H, D] bf16) and
-// delta' = delta_T + r delta_S ([B, H, Tq] fp32) with r = exp(lse_T - lse_S); consumed by that call.
-static thread_local long long* g_next_probe = nullptr;
-static thread_local int g_next_probe_mask = 0;
-static thread_local const void* g_next_dop = nullptr;
-static thread_local const float* g_next_delta_p = nullptr;
-TTCD_EXPORT int ttcd_attn_bwd_set_combined(const void* do_combined, const float* delta_combined) {
-  g_next_dop = do_combined;
-  g_next_delta_p = delta_combined;
-  return TTCD_OK;
-}
-// Timeline probe of the NEXT backward call of this thread: `buf` (device, 256 x int64, zeroed by the caller) receives
-// clock64() stamps from one dK/dV CTA (see AttnBwdParams::probe); consumed by that call.
-TTCD_EXPORT int ttcd_attn_bwd_set_probe(long long* buf, int event_mask) {
-  g_next_probe = buf;
-  g_next_probe_mask = event_mask;
-  return TTCD_OK;
-}
-TTCD_EXPORT int ttcd_attn_bwd_set_dv_layout(long long ld_dv, long long sb_dv) {
-  if (ld_dv < 0 || sb_dv < 0 || ld_dv % 8 != 0 || sb_dv % 8 != 0) return TTCD_ERR_ARG;
-  g_next_ld_dv = ld_dv;
-  g_next_sb_dv = sb_dv;
-  return TTCD_OK;
-}
-
+// Gradients of (dual-window) attention.
+//   q/k/v strided as in ttcd_attn_fwd_cp; do_t contiguous [B, Tq, H, D]; lse_t, delta_t [B, H, Tq] fp32.
+//   Dual window: do_c / delta_c are the combined stream made by ttcd_attn_bwd_combine (null => single window).
+//   dq [B,Tq,H,D], dk [B, halo_len + Tk_local, HK, D] bf16 contiguous: the first halo_len rows are the gradients
+//   of the previous rank's keys.  dv likewise, or, with ld_dv != 0, rows ld_dv elements apart and batches sb_dv
+//   apart (the packed q|k|v gradient of a fused projection); both multiples of 8, dv 16-byte aligned.
+//   seg_start / seg_end (int32 [Tq], or null): packed sequences in one row (needs B == 1, Tq == Tk, no halo);
+//   for every token the first token of its sequence and one past its last.
+//   flags: bit 0 = leave out the K/V copies of the dK/dV kernel (check of the bounded waits: the call returns with
+//   a status code after the wait budget and its outputs are undefined).
 TTCD_EXPORT int ttcd_attn_bwd_cp(const void* q, const void* k, const void* v, const void* k_halo, const void* v_halo,
-                                 const void* do_t, const void* do_s, const float* lse_t, const float* lse_s,
-                                 const float* delta_t, const float* delta_s, void* dq, void* dk, void* dv, int B, int Tq,
-                                 int Tk_local, int H, int HK, int D, long long ldq, long long ldk, long long ldv,
-                                 long long sq, long long sk, long long sv, int halo_len, int halo_rows, int window_t,
-                                 int window_s, float scale, void* stream_ptr) {
+                                 const void* do_t, const void* do_c, const float* lse_t, const float* delta_t,
+                                 const float* delta_c, void* dq, void* dk, void* dv, int B, int Tq, int Tk_local, int H,
+                                 int HK, int D, long long ldq, long long ldk, long long ldv, long long sq, long long sk,
+                                 long long sv, long long ld_dv, long long sb_dv, int halo_len, int halo_rows,
+                                 int window_t, int window_s, float scale, const int* seg_start, const int* seg_end,
+                                 int flags, void* stream_ptr) {
   using namespace ttcd;
   if (B <= 0 || Tq < 128 || Tk_local < Tq || H <= 0 || HK <= 0 || H % HK != 0 || (D != 64 && D != 128)) return TTCD_ERR_ARG;
   if (halo_len < 0 || halo_len % 128 != 0 || (halo_len > 0 && (k_halo == nullptr || v_halo == nullptr || halo_rows < halo_len)))
     return TTCD_ERR_ARG;
-  const bool dual = do_s != nullptr;
+  if (ld_dv < 0 || sb_dv < 0 || ld_dv % 8 != 0 || sb_dv % 8 != 0) return TTCD_ERR_ARG;
+  if (ld_dv != 0 && (reinterpret_cast<uintptr_t>(dv) & 15u)) return TTCD_ERR_ARG;
+  const bool dual = do_c != nullptr;
+  if (dual && delta_c == nullptr) return TTCD_ERR_ARG;
+  if ((seg_start == nullptr) != (seg_end == nullptr)) return TTCD_ERR_ARG;
+  if (seg_start != nullptr && (B != 1 || Tq != Tk_local || halo_len != 0)) return TTCD_ERR_ARG;
   BwdMaps m;
   const uint64_t qi = static_cast<uint64_t>(H) * D, ki = static_cast<uint64_t>(HK) * D;
   int rc = TTCD_OK;
@@ -1284,8 +983,8 @@ TTCD_EXPORT int ttcd_attn_bwd_cp(const void* q, const void* k, const void* v, co
   mk(&m.k64, k, ki, Tk_local, ldk, sk, 64);   mk(&m.k128, k, ki, Tk_local, ldk, sk, 128);
   mk(&m.v64, v, ki, Tk_local, ldv, sv, 64);   mk(&m.v128, v, ki, Tk_local, ldv, sv, 128);
   mk(&m.dot64, do_t, qi, Tq, qi, qi * Tq, 64);   mk(&m.dot128, do_t, qi, Tq, qi, qi * Tq, 128);
-  const void* dos = dual ? do_s : do_t;
-  mk(&m.dos64, dos, qi, Tq, qi, qi * Tq, 64);    mk(&m.dos128, dos, qi, Tq, qi, qi * Tq, 128);
+  const void* doc = dual ? do_c : do_t;
+  mk(&m.doc64, doc, qi, Tq, qi, qi * Tq, 64);    mk(&m.doc128, doc, qi, Tq, qi, qi * Tq, 128);
   m.kh64 = m.k64; m.kh128 = m.k128; m.vh64 = m.v64; m.vh128 = m.v128;
   if (halo_len > 0) {
     mk(&m.kh64, k_halo, ki, halo_rows, ldk, sk, 64);   mk(&m.kh128, k_halo, ki, halo_rows, ldk, sk, 128);
@@ -1294,76 +993,29 @@ TTCD_EXPORT int ttcd_attn_bwd_cp(const void* q, const void* k, const void* v, co
   if (rc != TTCD_OK) return rc;
   const int big = 1 << 30;
   AttnBwdParams p;
-  p.lse_t = lse_t; p.lse_s = lse_s; p.delta_t = delta_t; p.delta_s = delta_s;
+  p.lse_t = lse_t; p.delta_t = delta_t; p.delta_c = dual ? delta_c : delta_t;
   p.dq = static_cast<bf16*>(dq); p.dk = static_cast<bf16*>(dk); p.dv = static_cast<bf16*>(dv);
   p.Tq = Tq; p.Tk = Tk_local + halo_len; p.H = H; p.HK = HK;
   p.w_t = window_t > 0 ? window_t : big;
-  p.w_s = window_s > 0 ? window_s : big;
-  if (!dual) p.w_s = p.w_t;
+  p.w_s = (dual && window_s > 0) ? window_s : p.w_t;
   p.scale = scale; p.scale_log2 = scale * LOG2E;
   p.halo_len = halo_len; p.halo_row0 = halo_rows - halo_len;
-  static const int a_in_tmem = [] {
-    const char* e = getenv("TTCD_ATTN_BWD_TS");
-    return (e != nullptr && e[0] == '0') ? 0 : 1;
-  }();
-  p.a_in_tmem = a_in_tmem;
-  static const int deep_ring = [] {
-    const char* e = getenv("TTCD_ATTN_BWD_RING");
-    return (e != nullptr && e[0] == '3') ? 0 : 1;
-  }();
-  p.deep_ring = deep_ring;
-  static const int spin_sdp = [] {
-    const char* e = getenv("TTCD_ATTN_BWD_SPIN");
-    return (e != nullptr && e[0] == '1') ? 1 : 0;
-  }();
-  p.spin_sdp = spin_sdp;
-  p.probe = g_next_probe;
-  p.probe_mask = g_next_probe_mask;
-  g_next_probe = nullptr;
-  // element-wise warps per CTA: 16 = two groups on alternate steps (needs the operands in tensor memory), or 8
-  static const int ew_warps_env = [] {
-    const char* e = getenv("TTCD_ATTN_BWD_WARPS");
-    return (e != nullptr && atoi(e) == 8) ? 8 : 16;
-  }();
-  const int ew_warps = a_in_tmem ? ew_warps_env : 8;
-  // 16 warps: TTCD_ATTN_BWD_GROUPS=split puts both groups on the same step (16 columns per warp each) instead of
-  // alternate steps
-  static const bool ew_split = [] {
-    const char* e = getenv("TTCD_ATTN_BWD_GROUPS");
-    return e != nullptr && e[0] == 's';
-  }();
-  p.ld_dv = g_next_ld_dv; p.sb_dv = g_next_sb_dv;
-  g_next_ld_dv = g_next_sb_dv = 0;
-  p.combine = 0;
-  const void* dop = g_next_dop;
-  const float* delta_p = g_next_delta_p;
-  g_next_dop = nullptr;
-  g_next_delta_p = nullptr;
-  if (p.ld_dv != 0 && (reinterpret_cast<uintptr_t>(dv) & 15u)) return TTCD_ERR_ARG;
+  p.ld_dv = ld_dv; p.sb_dv = sb_dv;
+  p.combine = dual ? 1 : 0;
+  p.seg_start = seg_start; p.seg_end = seg_end;
+  p.skip_kv_load = flags & 1;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
-  if (dual && dop != nullptr && delta_p != nullptr) {
-    CUtensorMap dop64, dop128;
-    rc = make_tmap_bf16_3d(&dop64, dop, qi, Tq, B, qi, qi * Tq, 64, 64);
-    if (rc == TTCD_OK) rc = make_tmap_bf16_3d(&dop128, dop, qi, Tq, B, qi, qi * Tq, 64, 128);
-    if (rc != TTCD_OK) return rc;
-    if (ew_warps == 16 && ew_split)
-      return D == 128 ? launch_bwd_combined<128, 16, true>(m, dop64, dop128, p, delta_p, B, stream)
-                      : launch_bwd_combined<64, 16, true>(m, dop64, dop128, p, delta_p, B, stream);
-    if (ew_warps == 16)
-      return D == 128 ? launch_bwd_combined<128, 16, false>(m, dop64, dop128, p, delta_p, B, stream)
-                      : launch_bwd_combined<64, 16, false>(m, dop64, dop128, p, delta_p, B, stream);
-    return D == 128 ? launch_bwd_combined<128, 8, false>(m, dop64, dop128, p, delta_p, B, stream)
-                    : launch_bwd_combined<64, 8, false>(m, dop64, dop128, p, delta_p, B, stream);
-  }
-  if (ew_warps == 16 && ew_split) return dispatch_bwd<16, true>(m, p, B, D, dual, stream);
-  return ew_warps == 16 ? dispatch_bwd<16, false>(m, p, B, D, dual, stream) : dispatch_bwd<8, false>(m, p, B, D, dual, stream);
+  if (D == 128) return dual ? launch_bwd<128, true>(m, p, B, stream) : launch_bwd<128, false>(m, p, B, stream);
+  return dual ? launch_bwd<64, true>(m, p, B, stream) : launch_bwd<64, false>(m, p, B, stream);
 }
 
-TTCD_EXPORT int ttcd_attn_bwd(const void* q, const void* k, const void* v, const void* do_t, const void* do_s,
-                              const float* lse_t, const float* lse_s, const float* delta_t, const float* delta_s,
-                              void* dq, void* dk, void* dv, int B, int Tq, int Tk, int H, int HK, int D,
-                              long long ldq, long long ldk, long long ldv, long long sq, long long sk, long long sv,
-                              int window_t, int window_s, float scale, void* stream_ptr) {
-  return ttcd_attn_bwd_cp(q, k, v, nullptr, nullptr, do_t, do_s, lse_t, lse_s, delta_t, delta_s, dq, dk, dv, B, Tq, Tk, H,
-                          HK, D, ldq, ldk, ldv, sq, sk, sv, 0, 0, window_t, window_s, scale, stream_ptr);
+TTCD_EXPORT int ttcd_attn_bwd(const void* q, const void* k, const void* v, const void* do_t, const void* do_c,
+                              const float* lse_t, const float* delta_t, const float* delta_c, void* dq, void* dk,
+                              void* dv, int B, int Tq, int Tk, int H, int HK, int D, long long ldq, long long ldk,
+                              long long ldv, long long sq, long long sk, long long sv, long long ld_dv, long long sb_dv,
+                              int window_t, int window_s, float scale, const int* seg_start, const int* seg_end, int flags,
+                              void* stream_ptr) {
+  return ttcd_attn_bwd_cp(q, k, v, nullptr, nullptr, do_t, do_c, lse_t, delta_t, delta_c, dq, dk, dv, B, Tq, Tk, H, HK, D,
+                          ldq, ldk, ldv, sq, sk, sv, ld_dv, sb_dv, 0, 0, window_t, window_s, scale, seg_start, seg_end,
+                          flags, stream_ptr);
 }

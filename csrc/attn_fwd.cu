@@ -12,12 +12,13 @@
 // normalised accumulator is written out as the student result, and accumulation simply continues
 // over the teacher-only keys with the same running max / sum (online-softmax rescale identity).
 // Blocks that straddle the student boundary are visited once per phase with complementary masks.
+// Packed batches (several sequences in one row, the role of flash_attn_varlen_func in fla/layers/attn.py:229-270):
+// a per-token `seg_start` array bounds each query's keys to its own sequence, and the key-block range of a tile is
+// clipped to the sequences that the tile touches.
 // This replaces the two flash-attn calls of the reference's TTT layers
 // (custom_models/ipttcd/modeling_ipttcdv9.py:686-690) and its forward-only Triton kernel
 // (profiling/fused_dual_attn.py:34-241).
 #include "common.cuh"
-
-#include <cstdlib>
 
 namespace ttcd {
 
@@ -35,9 +36,8 @@ struct AttnFwdParams {
   // context parallel: keys [0, halo_len) are the tail of the PREVIOUS rank's sequence shard and are read
   // straight from that rank's memory (rows halo_row0.. of its K/V buffers); keys >= halo_len are local
   int halo_len, halo_row0;
-  // P (bf16) is written back over the S columns it was computed from and read by the P.V MMA as a tensor-memory
-  // A operand instead of going through shared memory
-  int p_in_tmem;
+  // packed sequences (null: none): per token, the first token of its sequence
+  const int* seg_start;
 };
 
 template <int D>
@@ -50,8 +50,7 @@ struct AttnSmem {
   static constexpr int Q_OFF = 0;
   static constexpr int K_OFF = Q_OFF + Q_BYTES;           // 2 slots
   static constexpr int V_OFF = K_OFF + 2 * KV_BYTES;      // 2 slots
-  static constexpr int P_OFF = V_OFF + 2 * KV_BYTES;      // [128 x 64] bf16
-  static constexpr int BAR_OFF = P_OFF + ATT_BM * 128;
+  static constexpr int BAR_OFF = V_OFF + 2 * KV_BYTES;
   // bar_q, k_full[2], v_full[2], s_full[2], s_free[2], p_full, pv_done  = 11 barriers
   static constexpr int NBARS = 11;
   static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16;
@@ -92,16 +91,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   const int qlo = m0 + off;
   const int qhi = m0 + ATT_BM - 1 + off;
 
+  // packed sequences: first key of the sequence of the tile's first / last row (sequence starts do not decrease)
+  const bool packed = p.seg_start != nullptr;
+  const int seg_first = packed ? p.seg_start[m0] + off : 0;
+  const int seg_last = packed ? p.seg_start[min(m0 + ATT_BM - 1, p.Tq - 1)] + off : 0;
   // key-block schedule: phase A = keys inside the student (or only) window, phase B = teacher-only keys
   const int a_hi = min(qhi, p.Tk - 1);
-  const int a_lo = max(0, qlo - p.w_s + 1);
+  const int a_lo = max(max(0, qlo - p.w_s + 1), seg_first);
   const int a_blk_hi = a_hi / ATT_BN;
   const int a_blk_lo = a_lo / ATT_BN;
   const int n_a = a_blk_hi - a_blk_lo + 1;
   int n_b = 0, b_blk_hi = 0;
   if (DUAL) {
     const int b_hi = min(qhi - p.w_s, p.Tk - 1);
-    const int b_lo = max(0, qlo - p.w_t + 1);
+    const int b_lo = max(max(0, qlo - p.w_t + 1), seg_first);
     if (p.w_t > p.w_s && b_hi >= b_lo) {
       b_blk_hi = b_hi / ATT_BN;
       n_b = b_blk_hi - b_lo / ATT_BN + 1;
@@ -168,7 +171,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       };
       // descriptors as (low word + constant step, constant high word): one add per k-step on this thread
       constexpr uint32_t HI = umma_desc_hi_sw128(1024);
-      const uint32_t q_lo = umma_desc_lo(sbase + S::Q_OFF, 16), p_lo = umma_desc_lo(sbase + S::P_OFF, 16);
+      const uint32_t q_lo = umma_desc_lo(sbase + S::Q_OFF, 16);
       auto issue_s = [&](int i) {
         const uint32_t k_lo = umma_desc_lo(sbase + S::K_OFF + (i & 1) * S::KV_BYTES, 16);
 #pragma unroll
@@ -184,17 +187,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         // V as the MN-major B operand: 64 keys of the contraction, the next 64 columns KV_REGION bytes on
         const uint32_t v_lo = umma_desc_lo(sbase + S::V_OFF + (i & 1) * S::KV_BYTES, S::KV_REGION);
         const uint32_t acc = i != 0;
-        if (p.p_in_tmem) {
+        // P (bf16) was written back over the S columns it was computed from: a tensor-memory A operand
 #pragma unroll
-          for (int k = 0; k < ATT_BN / 16; ++k)
-            umma_ts(tmem_o, tmem_base + (i & 1) * ATT_BN + k * 8, umma_desc_join(v_lo + k * (2048 >> 4), HI), idesc_o,
-                    acc | (k != 0));
-        } else {
-#pragma unroll
-          for (int k = 0; k < ATT_BN / 16; ++k)
-            umma_ss(tmem_o, umma_desc_join(p_lo + k * 2, HI), umma_desc_join(v_lo + k * (2048 >> 4), HI), idesc_o,
-                    acc | (k != 0));
-        }
+        for (int k = 0; k < ATT_BN / 16; ++k)
+          umma_ts(tmem_o, tmem_base + (i & 1) * ATT_BN + k * 8, umma_desc_join(v_lo + k * (2048 >> 4), HI), idesc_o,
+                  acc | (k != 0));
         umma_commit(pv_done);
       };
 
@@ -246,6 +243,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     // ---------------------------------------------------------------- softmax warps: thread == query row
     const int row = warp * 32 + lane;          // row inside the tile == TMEM lane
     const int qpos = qlo + row;
+    const int seg_lo = (packed && m0 + row < p.Tq) ? p.seg_start[m0 + row] + off : 0;   // first key of this row's sequence
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
     float m_ref = -INFINITY;   // running reference max (log2 domain), possibly stale by < threshold
     float l_sum = 0.f;
@@ -315,7 +313,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       if (!phase_b) { hi_incl = qpos; lo_excl = qpos - p.w_s; }
       else          { hi_incl = qpos - p.w_s; lo_excl = qpos - p.w_t; }
       const bool full = (key0 + ATT_BN - 1 <= (phase_b ? qlo - p.w_s : qlo)) &&
-                        (key0 > (phase_b ? qhi - p.w_t : qhi - p.w_s));
+                        (key0 > (phase_b ? qhi - p.w_t : qhi - p.w_s)) && (key0 >= seg_last);
       float mx = -INFINITY;
       if (full) {
 #pragma unroll
@@ -328,7 +326,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
 #pragma unroll
         for (int j = 0; j < ATT_BN; ++j) {
           const int key = key0 + j;
-          const bool vis = key <= hi_incl && key > lo_excl;
+          const bool vis = key <= hi_incl && key > lo_excl && key >= seg_lo;
           const float s = vis ? __uint_as_float(sv[j]) * p.scale_log2 : -INFINITY;
           sv[j] = __float_as_uint(s);
           mx = fmaxf(mx, s);
@@ -360,7 +358,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       if (need) m_ref = m_new;
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
       float psum = 0.f;
-      uint8_t* prow = smem + S::P_OFF;
       uint32_t ppk[ATT_BN / 2];
 #pragma unroll
       for (int c = 0; c < ATT_BN / 8; ++c) {
@@ -376,16 +373,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         ppk[4 * c + 3] = pack_bf16(e[6], e[7]);
       }
       l_sum += psum;
-      if (p.p_in_tmem) {
-        tmem_st32(tmem_base + lane_addr + (i & 1) * ATT_BN, ppk);   // this lane's own S columns, already in registers
-        tmem_st_wait();
-      } else {
-#pragma unroll
-        for (int c = 0; c < ATT_BN / 8; ++c)
-          *reinterpret_cast<uint4*>(prow + sw128_offset(row, c)) =
-              make_uint4(ppk[4 * c], ppk[4 * c + 1], ppk[4 * c + 2], ppk[4 * c + 3]);
-        fence_proxy_async_smem();   // generic-proxy smem writes -> visible to the MMA (async proxy)
-      }
+      tmem_st32(tmem_base + lane_addr + (i & 1) * ATT_BN, ppk);   // this lane's own S columns, already in registers
+      tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
@@ -434,13 +423,16 @@ TTCD_DEFINE_STATUS_READER(attn)
 // [B, Tq, H, D] / [B, H, Tq].  window <= 0 means unlimited (full causal).
 // Context parallel: k_halo / v_halo point at the previous rank's K / V buffers (same layout and strides,
 // halo_rows rows); its last halo_len rows are prepended to the local keys.  halo_len % 128 == 0.
+// seg_start (int32 [Tq], or null): packed sequences in one row (needs B == 1, Tq == Tk, no halo); for every token the
+// first token of its sequence.
 TTCD_EXPORT int ttcd_attn_fwd_cp(const void* q, const void* k, const void* v, const void* k_halo, const void* v_halo,
                                  void* o_t, void* o_s, float* lse_t, float* lse_s, int B, int Tq, int Tk_local, int H,
                                  int HK, int D, long long ldq, long long ldk, long long ldv, long long sq, long long sk,
                                  long long sv, int halo_len, int halo_rows, int window_t, int window_s, float scale,
-                                 void* stream_ptr) {
+                                 const int* seg_start, void* stream_ptr) {
   using namespace ttcd;
   const int Tk = Tk_local + halo_len;
+  if (seg_start != nullptr && (B != 1 || Tq != Tk_local || halo_len != 0)) return TTCD_ERR_ARG;
   if (B <= 0 || Tq < ATT_BM || Tk_local < Tq || H <= 0 || HK <= 0 || H % HK != 0 || (D != 64 && D != 128))
     return TTCD_ERR_ARG;
   if (halo_len < 0 || halo_len % 128 != 0 || (halo_len > 0 && (k_halo == nullptr || v_halo == nullptr || halo_rows < halo_len)))
@@ -470,11 +462,7 @@ TTCD_EXPORT int ttcd_attn_fwd_cp(const void* q, const void* k, const void* v, co
   p.w_s = window_s > 0 ? window_s : big;
   if (!dual) p.w_s = p.w_t;  // single-window mode runs phase A only, with the one window
   p.scale_log2 = scale * 1.4426950408889634f;
-  static const int p_in_tmem = [] {
-    const char* e = getenv("TTCD_ATTN_FWD_TS");
-    return (e != nullptr && e[0] == '0') ? 0 : 1;
-  }();
-  p.p_in_tmem = p_in_tmem;
+  p.seg_start = seg_start;
   p.halo_len = halo_len;
   p.halo_row0 = halo_rows - halo_len;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
@@ -487,7 +475,7 @@ TTCD_EXPORT int ttcd_attn_fwd_cp(const void* q, const void* k, const void* v, co
 TTCD_EXPORT int ttcd_attn_fwd(const void* q, const void* k, const void* v, void* o_t, void* o_s, float* lse_t,
                               float* lse_s, int B, int Tq, int Tk, int H, int HK, int D, long long ldq,
                               long long ldk, long long ldv, long long sq, long long sk, long long sv,
-                              int window_t, int window_s, float scale, void* stream_ptr) {
+                              int window_t, int window_s, float scale, const int* seg_start, void* stream_ptr) {
   return ttcd_attn_fwd_cp(q, k, v, nullptr, nullptr, o_t, o_s, lse_t, lse_s, B, Tq, Tk, H, HK, D, ldq, ldk, ldv, sq, sk,
-                          sv, 0, 0, window_t, window_s, scale, stream_ptr);
+                          sv, 0, 0, window_t, window_s, scale, seg_start, stream_ptr);
 }

@@ -44,7 +44,10 @@ __device__ __forceinline__ int ld_acquire_sys(const int* addr) {
 
 // flags.p[r] -> rank r's flag array int[world * slots]; slot `slot`, entry [slot * world + writer].
 // Rank `rank` publishes `epoch` to every peer and waits until every peer has published >= epoch to it.
-__global__ void comm_barrier_kernel(PeerPtrs flags, int rank, int world, int slot, int epoch, uint64_t wait_ns) {
+// A wait that runs out records 500 + the absent rank in the status word and, when `fail` is given, stores 1.0f
+// there: kernels later in the step read that word and leave their outputs untouched (see adamw_push).
+__global__ void comm_barrier_kernel(PeerPtrs flags, int rank, int world, int slot, int epoch, uint64_t wait_ns,
+                                    float* fail) {
   const int r = threadIdx.x;
   if (r >= world) return;
   __threadfence_system();  // make this GPU's earlier writes visible before the flag
@@ -56,6 +59,7 @@ __global__ void comm_barrier_kernel(PeerPtrs flags, int rank, int world, int slo
     if ((it & 0x3f) == 0x3f) {
       if (globaltimer_ns() - t0 > wait_ns) {
         atomicCAS(&g_status, 0, 500 + r);
+        if (fail != nullptr) *fail = 1.f;
         break;
       }
       __nanosleep(200);
@@ -234,11 +238,11 @@ TTCD_EXPORT int ttcd_ipc_close(long long ptr) {
 
 // ---- kernels ---------------------------------------------------------------------------------------
 TTCD_EXPORT int ttcd_comm_barrier(const long long* flag_ptrs, int rank, int world, int slot, int epoch,
-                                  long long wait_ns, void* stream_ptr) {
+                                  long long wait_ns, float* fail, void* stream_ptr) {
   if (world < 1 || world > MAX_RANKS) return TTCD_ERR_ARG;
   const uint64_t w = wait_ns > 0 ? static_cast<uint64_t>(wait_ns) : TTCD_PEER_WAIT_NS;
   comm_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_ptr)>>>(make_ptrs(flag_ptrs, world), rank, world,
-                                                                           slot, epoch, w);
+                                                                           slot, epoch, w, fail);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -31,6 +31,12 @@ namespace ttcd {
 // Status word written by kernels whose bounded wait expired (0 = healthy).  One copy per
 // translation unit (no relocatable device code); TTCD_DEFINE_STATUS_READER exports its reader.
 static __device__ int g_status = 0;
+// Budget of the bounded mbarrier waits of this translation unit, in nanoseconds (TTCD_DEFINE_STATUS_READER also
+// exports its setter: a test shortens it to see a wait run out within milliseconds).
+#ifndef TTCD_WAIT_NS
+#define TTCD_WAIT_NS 2000000000ull  // 2 s
+#endif
+static __device__ unsigned long long g_wait_ns = TTCD_WAIT_NS;
 
 // ---------------------------------------------------------------------------------------------
 // host: tensor maps
@@ -103,11 +109,6 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t pari
   return ok != 0;
 }
 
-// Wait budget for barriers that only depend on this CTA's own copies and MMAs.
-#ifndef TTCD_WAIT_NS
-#define TTCD_WAIT_NS 2000000000ull  // 2 s
-#endif
-
 // Bounded wait.  Returns false when the budget ran out or another role of the CTA aborted.
 __device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code);
 __device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code);
@@ -126,7 +127,7 @@ __device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, vo
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 0xff) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > TTCD_WAIT_NS) {
+      if (globaltimer_ns() - t0 > g_wait_ns) {
         *abort_flag = 1;
         atomicCAS(&g_status, 0, code);
         return false;
@@ -141,7 +142,7 @@ __device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, 
   for (;;) {                                  // each try may sleep up to the hint: check the exits every time
     if (mbar_try_wait_parked(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (globaltimer_ns() - t0 > TTCD_WAIT_NS) {
+    if (globaltimer_ns() - t0 > g_wait_ns) {
       *abort_flag = 1;
       atomicCAS(&g_status, 0, code);
       return false;
@@ -357,7 +358,9 @@ __device__ __forceinline__ uint32_t sw128_offset(uint32_t row, uint32_t chunk16)
 }  // namespace ttcd
 
 // Exports `int ttcd_read_status_<name>(int reset)`: the status word of this translation unit on
-// the current device (0 = healthy), optionally cleared after the read.
+// the current device (0 = healthy), optionally cleared after the read; and
+// `int ttcd_set_wait_ns_<name>(long long ns)`: the budget of this unit's bounded mbarrier waits on the
+// current device (ns <= 0 restores the default).
 #define TTCD_DEFINE_STATUS_READER(name)                                              \
   TTCD_EXPORT int ttcd_read_status_##name(int reset) {                               \
     int v = 0;                                                                       \
@@ -367,4 +370,8 @@ __device__ __forceinline__ uint32_t sw128_offset(uint32_t row, uint32_t chunk16)
       cudaMemcpyToSymbol(ttcd::g_status, &z, sizeof(int));                           \
     }                                                                                \
     return v;                                                                        \
+  }                                                                                  \
+  TTCD_EXPORT int ttcd_set_wait_ns_##name(long long ns) {                            \
+    unsigned long long v = ns > 0 ? static_cast<unsigned long long>(ns) : TTCD_WAIT_NS; \
+    return static_cast<int>(cudaMemcpyToSymbol(ttcd::g_wait_ns, &v, sizeof(v)));     \
   }

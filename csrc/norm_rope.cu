@@ -182,6 +182,311 @@ __global__ void __launch_bounds__(256, (CHUNKS <= 4 ? 2 : 1)) rmsnorm_bwd_kernel
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Wide rows (D > 2048): the row no longer fits in a warp's registers, so each pass streams it (the second
+// pass hits L1 / L2).  One warp per row, same math as the kernels above.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) rmsnorm_fwd_wide_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res,
+                                                               const bf16* __restrict__ w, bf16* __restrict__ y,
+                                                               bf16* __restrict__ sum_out, float* __restrict__ rstd_out,
+                                                               int64_t rows, int D, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  auto load_sum = [&](int col, float (&v)[8]) {
+    Vec8 a;
+    a.load(x + row * D + col);
+    a.to_float(v);
+    if (res != nullptr) {
+      Vec8 b;
+      float r[8];
+      b.load(res + row * D + col);
+      b.to_float(r);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] += r[i];
+    }
+    if (sum_out != nullptr) {      // statistics use the stored (rounded) residual, as the backward will
+      Vec8 o;
+      o.from_float(v);
+      o.to_float(v);
+    }
+  };
+  float ss = 0.f;
+  for (int col = lane * 8; col < D; col += 256) {
+    float v[8];
+    load_sum(col, v);
+    if (sum_out != nullptr) {
+      Vec8 o;
+      o.from_float(v);
+      o.store(sum_out + row * D + col);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+  }
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss / D + eps);
+  if (lane == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+  for (int col = lane * 8; col < D; col += 256) {
+    float v[8], wv[8];
+    load_sum(col, v);
+    if (w != nullptr) {
+      Vec8 ww;
+      ww.load(w + col);
+      ww.to_float(wv);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) wv[i] = 1.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = v[i] * rstd * wv[i];
+    Vec8 ov;
+    ov.from_float(v);
+    ov.store(y + row * D + col);
+  }
+}
+
+// dw partial sums accumulate in shared memory ([warps][D], each lane owns its columns) instead of registers.
+__global__ void __launch_bounds__(128) rmsnorm_bwd_wide_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ s,
+                                                               const bf16* __restrict__ w, const float* __restrict__ rstd_in,
+                                                               const bf16* __restrict__ dres, bf16* __restrict__ dx,
+                                                               float* __restrict__ dw_partial, int64_t rows, int D) {
+  extern __shared__ float red[];  // [warps][D]
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int warps = blockDim.x >> 5;
+  float* mine = red + static_cast<size_t>(warp) * D;
+  for (int col = lane; col < D; col += 32) mine[col] = 0.f;
+  __syncwarp();
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * warps + warp; row < rows;
+       row += static_cast<int64_t>(gridDim.x) * warps) {
+    const float rstd = rstd_in[row];
+    float dot = 0.f;
+    for (int col = lane * 8; col < D; col += 256) {
+      Vec8 a, b;
+      float g[8], xh[8], wv[8];
+      a.load(dy + row * D + col);
+      b.load(s + row * D + col);
+      a.to_float(g);
+      b.to_float(xh);
+      if (w != nullptr) {
+        Vec8 ww;
+        ww.load(w + col);
+        ww.to_float(wv);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        xh[i] *= rstd;
+        mine[col + i] += g[i] * xh[i];
+        dot += (w != nullptr ? g[i] * wv[i] : g[i]) * xh[i];
+      }
+    }
+    dot = warp_sum(dot) / D;
+    for (int col = lane * 8; col < D; col += 256) {
+      Vec8 a, b;
+      float g[8], xh[8], wv[8], o[8];
+      a.load(dy + row * D + col);
+      b.load(s + row * D + col);
+      a.to_float(g);
+      b.to_float(xh);
+      if (w != nullptr) {
+        Vec8 ww;
+        ww.load(w + col);
+        ww.to_float(wv);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = rstd * ((w != nullptr ? g[i] * wv[i] : g[i]) - xh[i] * rstd * dot);
+      if (dres != nullptr) {
+        Vec8 r;
+        float rf[8];
+        r.load(dres + row * D + col);
+        r.to_float(rf);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] += rf[i];
+      }
+      Vec8 ov;
+      ov.from_float(o);
+      ov.store(dx + row * D + col);
+    }
+  }
+  if (dw_partial == nullptr) return;
+  __syncthreads();
+  for (int col = threadIdx.x; col < D; col += blockDim.x) {
+    float acc = 0.f;
+    for (int wi = 0; wi < warps; ++wi) acc += red[static_cast<size_t>(wi) * D + col];
+    dw_partial[static_cast<int64_t>(blockIdx.x) * D + col] = acc;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Two-input RMSNorm of the fast-weight blocks: x = norm(r + a_T), t = norm(r + a_S) with one weight, and the
+// updated residual r + a_T.  The residual is read once; both sums are stored for the backward.
+// (The reference calls its norm twice with the same residual: custom_models/ipttcd/modeling_ipttcdv9.py:700-708.)
+// ------------------------------------------------------------------------------------------------
+template <int CHUNKS>
+__global__ void __launch_bounds__(256) rmsnorm_dual_fwd_kernel(const bf16* __restrict__ a_t, const bf16* __restrict__ a_s,
+                                                               const bf16* __restrict__ res, const bf16* __restrict__ w,
+                                                               bf16* __restrict__ y_t, bf16* __restrict__ y_s,
+                                                               bf16* __restrict__ sum_t, bf16* __restrict__ sum_s,
+                                                               float* __restrict__ rstd_t, float* __restrict__ rstd_s,
+                                                               int64_t rows, int D, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  float vt[CHUNKS][8], vs[CHUNKS][8];
+  float sst = 0.f, sss = 0.f;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int col = (c * 32 + lane) * 8;
+    if (col < D) {
+      Vec8 a, b, r;
+      float rf[8];
+      a.load(a_t + row * D + col);
+      b.load(a_s + row * D + col);
+      r.load(res + row * D + col);
+      a.to_float(vt[c]);
+      b.to_float(vs[c]);
+      r.to_float(rf);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { vt[c][i] += rf[i]; vs[c][i] += rf[i]; }
+      Vec8 ot, os;
+      ot.from_float(vt[c]);
+      os.from_float(vs[c]);
+      ot.store(sum_t + row * D + col);
+      os.store(sum_s + row * D + col);
+      ot.to_float(vt[c]);      // statistics use the stored (rounded) sums so forward and backward see the same input
+      os.to_float(vs[c]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { sst += vt[c][i] * vt[c][i]; sss += vs[c][i] * vs[c][i]; }
+    }
+  }
+  sst = warp_sum(sst);
+  sss = warp_sum(sss);
+  const float rt = rsqrtf(sst / D + eps), rs = rsqrtf(sss / D + eps);
+  if (lane == 0) { rstd_t[row] = rt; rstd_s[row] = rs; }
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int col = (c * 32 + lane) * 8;
+    if (col < D) {
+      float wv[8];
+      Vec8 ww;
+      ww.load(w + col);
+      ww.to_float(wv);
+      float ot[8], os[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { ot[i] = vt[c][i] * rt * wv[i]; os[i] = vs[c][i] * rs * wv[i]; }
+      Vec8 o1, o2;
+      o1.from_float(ot);
+      o2.from_float(os);
+      o1.store(y_t + row * D + col);
+      o2.store(y_s + row * D + col);
+    }
+  }
+}
+
+// Backward of the two-input norm: d_at = dnorm_T(dy_t) + dres, d_as = dnorm_S(dy_s), d_res = d_at + d_as, and one
+// set of dw partial sums for both streams.  The two streams go through the registers one after the other.
+template <int CHUNKS>
+__global__ void __launch_bounds__(256) rmsnorm_dual_bwd_kernel(const bf16* __restrict__ dy_t, const bf16* __restrict__ dy_s,
+                                                               const bf16* __restrict__ s_t, const bf16* __restrict__ s_s,
+                                                               const bf16* __restrict__ w, const float* __restrict__ rstd_t,
+                                                               const float* __restrict__ rstd_s, const bf16* __restrict__ dres,
+                                                               bf16* __restrict__ d_at, bf16* __restrict__ d_as,
+                                                               bf16* __restrict__ d_res, float* __restrict__ dw_partial,
+                                                               int64_t rows, int D) {
+  extern __shared__ float red[];  // [warps][D]
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int warps = blockDim.x >> 5;
+  float dwacc[CHUNKS][8];
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dwacc[c][i] = 0.f;
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * warps + warp; row < rows;
+       row += static_cast<int64_t>(gridDim.x) * warps) {
+    uint4 first[CHUNKS];          // d_at of this row, kept packed until d_res is formed
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+      const bf16* dy = pass == 0 ? dy_t : dy_s;
+      const bf16* s = pass == 0 ? s_t : s_s;
+      const float rstd = (pass == 0 ? rstd_t : rstd_s)[row];
+      float g[CHUNKS][8], xh[CHUNKS][8];
+      float dot = 0.f;
+#pragma unroll
+      for (int c = 0; c < CHUNKS; ++c) {
+        const int col = (c * 32 + lane) * 8;
+        if (col < D) {
+          Vec8 a, b, ww;
+          float wv[8];
+          a.load(dy + row * D + col);
+          b.load(s + row * D + col);
+          ww.load(w + col);
+          a.to_float(g[c]);
+          b.to_float(xh[c]);
+          ww.to_float(wv);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            xh[c][i] *= rstd;
+            dwacc[c][i] += g[c][i] * xh[c][i];
+            g[c][i] *= wv[i];
+            dot += g[c][i] * xh[c][i];
+          }
+        }
+      }
+      dot = warp_sum(dot) / D;
+#pragma unroll
+      for (int c = 0; c < CHUNKS; ++c) {
+        const int col = (c * 32 + lane) * 8;
+        if (col < D) {
+          float o[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = rstd * (g[c][i] - xh[c][i] * dot);
+          Vec8 ov;
+          if (pass == 0) {
+            if (dres != nullptr) {
+              Vec8 r;
+              float rf[8];
+              r.load(dres + row * D + col);
+              r.to_float(rf);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) o[i] += rf[i];
+            }
+            ov.from_float(o);
+            ov.store(d_at + row * D + col);
+            first[c] = ov.raw;
+          } else {
+            ov.from_float(o);
+            ov.store(d_as + row * D + col);
+            Vec8 f;
+            float ff[8];
+            f.raw = first[c];
+            f.to_float(ff);
+            ov.to_float(o);           // the sum of the two stored (rounded) gradients
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] += ff[i];
+            ov.from_float(o);
+            ov.store(d_res + row * D + col);
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int col = (c * 32 + lane) * 8;
+    if (col < D) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) red[warp * D + col + i] = dwacc[c][i];
+    }
+  }
+  __syncthreads();
+  for (int col = threadIdx.x; col < D; col += blockDim.x) {
+    float acc = 0.f;
+    for (int wi = 0; wi < warps; ++wi) acc += red[wi * D + col];
+    dw_partial[static_cast<int64_t>(blockIdx.x) * D + col] = acc;
+  }
+}
+
 
 // ------------------------------------------------------------------------------------------------
 // Per-head RMSNorm (optional) + NeoX rotary.  One warp per (token, head); q heads then k heads.
@@ -518,13 +823,22 @@ __global__ void __launch_bounds__(256) qk_norm_rope_bwd_vec_kernel(const QKRopeP
 
 using namespace ttcd;
 
-// y = rmsnorm(x + res) * w.  res, w, sum_out, rstd may be null.  D % 8 == 0, D <= 2048.
+constexpr int RMSNORM_MAX_D = 16384;    // wide-row kernels: 4 warps x D floats of shared memory in the backward
+
+// y = rmsnorm(x + res) * w.  res, w, sum_out, rstd may be null.  D % 8 == 0, D <= 16384 (rows wider than 2048 take
+// the streaming kernels).
 TTCD_EXPORT int ttcd_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* sum_out, float* rstd,
                                  long long rows, int D, float eps, void* stream_ptr) {
-  if (D % 8 != 0 || D > 2048 || rows <= 0) return TTCD_ERR_ARG;
+  if (D % 8 != 0 || D > RMSNORM_MAX_D || rows <= 0) return TTCD_ERR_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream_ptr);
   const int warps = 8;
   const unsigned grid = static_cast<unsigned>((rows + warps - 1) / warps);
+  if (D > 2048) {
+    rmsnorm_fwd_wide_kernel<<<grid, warps * 32, 0, st>>>(static_cast<const bf16*>(x), static_cast<const bf16*>(res),
+                                                         static_cast<const bf16*>(w), static_cast<bf16*>(y),
+                                                         static_cast<bf16*>(sum_out), rstd, rows, D, eps);
+    return static_cast<int>(cudaGetLastError());
+  }
   const int chunks = (D + 255) / 256;
 #define LAUNCH(C)                                                                                          \
   rmsnorm_fwd_kernel<C><<<grid, warps * 32, 0, st>>>(static_cast<const bf16*>(x), static_cast<const bf16*>(res), \
@@ -545,8 +859,23 @@ TTCD_EXPORT int ttcd_rmsnorm_fwd(const void* x, const void* res, const void* w, 
 // dx = rmsnorm_backward(dy; s, w, rstd) (+ dres).  dw_partial: [nblocks][D] fp32 or null.
 TTCD_EXPORT int ttcd_rmsnorm_bwd(const void* dy, const void* s, const void* w, const float* rstd, const void* dres,
                                  void* dx, float* dw_partial, long long rows, int D, int nblocks, void* stream_ptr) {
-  if (D % 8 != 0 || D > 2048 || rows <= 0 || nblocks <= 0) return TTCD_ERR_ARG;
+  if (D % 8 != 0 || D > RMSNORM_MAX_D || rows <= 0 || nblocks <= 0) return TTCD_ERR_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream_ptr);
+  if (D > 2048) {
+    const size_t wide_smem = static_cast<size_t>(4) * D * sizeof(float);
+    static bool configured = false;
+    if (!configured) {
+      TTCD_CUDA_CHECK(cudaFuncSetAttribute(rmsnorm_bwd_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           4 * RMSNORM_MAX_D * static_cast<int>(sizeof(float)) > 227 * 1024
+                                               ? 227 * 1024 : 4 * RMSNORM_MAX_D * static_cast<int>(sizeof(float))));
+      configured = true;
+    }
+    if (wide_smem > 227 * 1024) return TTCD_ERR_SIZE;
+    rmsnorm_bwd_wide_kernel<<<nblocks, 128, wide_smem, st>>>(
+        static_cast<const bf16*>(dy), static_cast<const bf16*>(s), static_cast<const bf16*>(w), rstd,
+        static_cast<const bf16*>(dres), static_cast<bf16*>(dx), dw_partial, rows, D);
+    return static_cast<int>(cudaGetLastError());
+  }
   const int warps = 8;
   const size_t smem = static_cast<size_t>(warps) * D * sizeof(float);
   const int chunks = (D + 255) / 256;
@@ -557,6 +886,64 @@ TTCD_EXPORT int ttcd_rmsnorm_bwd(const void* dy, const void* s, const void* w, c
   if (smem > 48 * 1024) {
     if (chunks <= 6) cudaFuncSetAttribute(rmsnorm_bwd_kernel<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
     else cudaFuncSetAttribute(rmsnorm_bwd_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+  }
+  switch (chunks) {
+    case 1: LAUNCH(1); break;
+    case 2: LAUNCH(2); break;
+    case 3: LAUNCH(3); break;
+    case 4: LAUNCH(4); break;
+    case 5: case 6: LAUNCH(6); break;
+    default: LAUNCH(8); break;
+  }
+#undef LAUNCH
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Two-input norm of the fast-weight blocks (see rmsnorm_dual_fwd_kernel).  All tensors bf16 [rows][D] contiguous;
+// rstd_* fp32 [rows].  D % 8 == 0, D <= 2048.
+TTCD_EXPORT int ttcd_rmsnorm_dual_fwd(const void* a_t, const void* a_s, const void* res, const void* w, void* y_t, void* y_s,
+                                      void* sum_t, void* sum_s, float* rstd_t, float* rstd_s, long long rows, int D,
+                                      float eps, void* stream_ptr) {
+  if (D % 8 != 0 || D > 2048 || rows <= 0 || w == nullptr) return TTCD_ERR_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream_ptr);
+  const int warps = 8;
+  const unsigned grid = static_cast<unsigned>((rows + warps - 1) / warps);
+  const int chunks = (D + 255) / 256;
+#define LAUNCH(C)                                                                                              \
+  rmsnorm_dual_fwd_kernel<C><<<grid, warps * 32, 0, st>>>(                                                     \
+      static_cast<const bf16*>(a_t), static_cast<const bf16*>(a_s), static_cast<const bf16*>(res),             \
+      static_cast<const bf16*>(w), static_cast<bf16*>(y_t), static_cast<bf16*>(y_s), static_cast<bf16*>(sum_t), \
+      static_cast<bf16*>(sum_s), rstd_t, rstd_s, rows, D, eps)
+  switch (chunks) {
+    case 1: LAUNCH(1); break;
+    case 2: LAUNCH(2); break;
+    case 3: LAUNCH(3); break;
+    case 4: LAUNCH(4); break;
+    case 5: case 6: LAUNCH(6); break;
+    default: LAUNCH(8); break;
+  }
+#undef LAUNCH
+  return static_cast<int>(cudaGetLastError());
+}
+
+// d_at, d_as, d_res of the two-input norm; dres (gradient of the updated residual) may be null.
+// dw_partial: [nblocks][D] fp32 (both streams summed).
+TTCD_EXPORT int ttcd_rmsnorm_dual_bwd(const void* dy_t, const void* dy_s, const void* s_t, const void* s_s, const void* w,
+                                      const float* rstd_t, const float* rstd_s, const void* dres, void* d_at, void* d_as,
+                                      void* d_res, float* dw_partial, long long rows, int D, int nblocks, void* stream_ptr) {
+  if (D % 8 != 0 || D > 2048 || rows <= 0 || nblocks <= 0 || w == nullptr || dw_partial == nullptr) return TTCD_ERR_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream_ptr);
+  const int warps = 8;
+  const size_t smem = static_cast<size_t>(warps) * D * sizeof(float);
+  const int chunks = (D + 255) / 256;
+#define LAUNCH(C)                                                                                              \
+  rmsnorm_dual_bwd_kernel<C><<<nblocks, warps * 32, smem, st>>>(                                               \
+      static_cast<const bf16*>(dy_t), static_cast<const bf16*>(dy_s), static_cast<const bf16*>(s_t),           \
+      static_cast<const bf16*>(s_s), static_cast<const bf16*>(w), rstd_t, rstd_s, static_cast<const bf16*>(dres), \
+      static_cast<bf16*>(d_at), static_cast<bf16*>(d_as), static_cast<bf16*>(d_res), dw_partial, rows, D)
+  if (smem > 48 * 1024) {
+    if (chunks <= 6) cudaFuncSetAttribute(rmsnorm_dual_bwd_kernel<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    else cudaFuncSetAttribute(rmsnorm_dual_bwd_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
   }
   switch (chunks) {
     case 1: LAUNCH(1); break;

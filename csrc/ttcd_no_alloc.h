@@ -13,12 +13,14 @@
 //    TTCD_NO_ALLOC_MAX_BLOCKS x TTCD_NO_ALLOC_MAX_D floats (1.16 MiB) per device.  Any number of rows.
 //  * First call.  The first call on each device looks up the array's device address once
 //    (cudaGetSymbolAddress) and raises the kernel's dynamic shared-memory limit.  Make that first call
-//    during start-up, outside stream capture; later calls only launch two kernels and can be captured.
+//    during start-up, before any stream capture begins; later calls only launch two kernels.
 //  * Contents.  The array keeps whatever the previous call left in it.  Nothing in it has to be zero:
 //    every call overwrites all the entries it later reads.
 //  * Concurrency.  There is one array per device.  Two calls that may overlap on the same device (two
 //    streams, two threads, two graphs replayed concurrently) race on it; order them on one stream or
-//    with events.  Calls on different devices are independent.
+//    with events.  Calls on different devices are independent.  The host-side table of looked-up addresses
+//    is filled without a lock: two host threads that make the very first call on one device at the same
+//    time both run the look-up and store the same value, which is harmless.
 #pragma once
 
 #ifdef __cplusplus

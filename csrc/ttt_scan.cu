@@ -32,10 +32,12 @@ __device__ __forceinline__ void store8_bf16(bf16* p, const float (&v)[8], float 
   *reinterpret_cast<uint4*>(p) = o;
 }
 
-// d_w: [B, T-1, R] fp32; w_down: [R] bf16; w_init: [B, R] fp32 or null; states: [B, T, R] bf16
+// d_w: [B, n_upd, R] fp32 (n_upd = T - 1, or T when a later sequence shard continues the scan; only the first T - 1
+// are used here); w_down: [R] bf16; w_init: [B, R] fp32 or null (start state from earlier shards, already scaled);
+// states: [B, T, R] bf16
 __global__ void __launch_bounds__(256) ttt_prefix_weights_kernel(const float* __restrict__ d_w, const bf16* __restrict__ w_down,
                                                                  const float* __restrict__ w_init, bf16* __restrict__ states,
-                                                                 float lr, int B, int T, int64_t R) {
+                                                                 float lr, int B, int T, int64_t R, int n_upd) {
   const int64_t nvec = R / 8;
   for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < nvec * B;
        idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -59,7 +61,7 @@ __global__ void __launch_bounds__(256) ttt_prefix_weights_kernel(const float* __
       for (int i = 0; i < 8; ++i) acc[i] += a[i];
     }
     bf16* out = states + static_cast<int64_t>(b) * T * R + e;
-    const float* in = d_w + static_cast<int64_t>(b) * (T - 1) * R + e;
+    const float* in = d_w + static_cast<int64_t>(b) * n_upd * R + e;
     store8_bf16(out, acc, 1.f);
     for (int j = 0; j + 1 < T; ++j) {
       float d[8];
@@ -71,9 +73,12 @@ __global__ void __launch_bounds__(256) ttt_prefix_weights_kernel(const float* __
   }
 }
 
-// d_states: [B, T, R] fp32; g: [B, T-1, R] bf16 (g_j = lr * sum_{i>j} d_states_i); d_w_down: [R] fp32 (sum over b, i)
+// d_states: [B, T, R] fp32; g: [B, n_upd, R] bf16 (g_j = lr * (g_init + sum_{i>j} d_states_i)); d_w_down: [R] fp32
+// (sum over b, i).  g_init: [B, R] fp32 or null: what later sequence shards hand back for this shard's summed update;
+// n_upd = T - 1, or T when this shard's last chunk also updates (then g_{T-1} = lr * g_init).
 __global__ void __launch_bounds__(256) ttt_suffix_grads_kernel(const float* __restrict__ d_states, bf16* __restrict__ g,
-                                                               float* __restrict__ d_w_down, float lr, int B, int T, int64_t R) {
+                                                               float* __restrict__ d_w_down, const float* __restrict__ g_init,
+                                                               float lr, int B, int T, int64_t R, int n_upd) {
   const int64_t nvec = R / 8;
   for (int64_t v = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < nvec;
        v += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -81,19 +86,22 @@ __global__ void __launch_bounds__(256) ttt_suffix_grads_kernel(const float* __re
     float total[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int b = 0; b < B; ++b) {
       const float* in = d_states + static_cast<int64_t>(b) * T * R + e;
-      bf16* out = g + static_cast<int64_t>(b) * (T - 1) * R + e;
+      bf16* out = g + static_cast<int64_t>(b) * n_upd * R + e;
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      float local[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (g_init != nullptr) load8(g_init + static_cast<int64_t>(b) * R + e, acc);
+      if (n_upd == T) store8_bf16(out + static_cast<int64_t>(T - 1) * R, acc, lr);
       for (int i = T - 1; i >= 1; --i) {
         float d[8];
         load8(in + static_cast<int64_t>(i) * R, d);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) acc[k] += d[k];
+        for (int k = 0; k < 8; ++k) { acc[k] += d[k]; local[k] += d[k]; }
         store8_bf16(out + static_cast<int64_t>(i - 1) * R, acc, lr);
       }
       float d0[8];
       load8(in, d0);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) total[k] += acc[k] + d0[k];
+      for (int k = 0; k < 8; ++k) total[k] += local[k] + d0[k];
     }
     *reinterpret_cast<float4*>(d_w_down + e) = make_float4(total[0], total[1], total[2], total[3]);
     *reinterpret_cast<float4*>(d_w_down + e + 4) = make_float4(total[4], total[5], total[6], total[7]);
@@ -110,17 +118,17 @@ static unsigned ttt_grid(long long nvec) {
 }
 
 TTCD_EXPORT int ttcd_ttt_prefix_weights(const float* d_w, const void* w_down, const float* w_init, void* states, float lr,
-                                        int B, int T, long long R, void* stream_ptr) {
-  if (B <= 0 || T <= 0 || R <= 0 || R % 8 != 0) return TTCD_ERR_ARG;
+                                        int B, int T, long long R, int n_upd, void* stream_ptr) {
+  if (B <= 0 || T <= 0 || R <= 0 || R % 8 != 0 || (n_upd != T - 1 && n_upd != T)) return TTCD_ERR_ARG;
   ttt_prefix_weights_kernel<<<ttt_grid(R / 8 * B), 256, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
-      d_w, static_cast<const bf16*>(w_down), w_init, static_cast<bf16*>(states), lr, B, T, R);
+      d_w, static_cast<const bf16*>(w_down), w_init, static_cast<bf16*>(states), lr, B, T, R, n_upd);
   return static_cast<int>(cudaGetLastError());
 }
 
-TTCD_EXPORT int ttcd_ttt_suffix_grads(const float* d_states, void* g, float* d_w_down, float lr, int B, int T, long long R,
-                                      void* stream_ptr) {
-  if (B <= 0 || T <= 0 || R <= 0 || R % 8 != 0) return TTCD_ERR_ARG;
+TTCD_EXPORT int ttcd_ttt_suffix_grads(const float* d_states, void* g, float* d_w_down, const float* g_init, float lr, int B,
+                                      int T, long long R, int n_upd, void* stream_ptr) {
+  if (B <= 0 || T <= 0 || R <= 0 || R % 8 != 0 || (n_upd != T - 1 && n_upd != T)) return TTCD_ERR_ARG;
   ttt_suffix_grads_kernel<<<ttt_grid(R / 8), 256, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
-      d_states, static_cast<bf16*>(g), d_w_down, lr, B, T, R);
+      d_states, static_cast<bf16*>(g), d_w_down, g_init, lr, B, T, R, n_upd);
   return static_cast<int>(cudaGetLastError());
 }

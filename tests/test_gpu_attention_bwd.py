@@ -94,12 +94,8 @@ def test_strided_qkv_views_and_packed_sequences():
     _check(qkv.grad, f.grad, "dqkv")
 
 
-@pytest.mark.parametrize("combine", [True, False])
 @pytest.mark.parametrize("B,T,H,HK,D,WT,WS", [(2, 900, 4, 2, 128, 384, 128), (1, 1300, 2, 1, 64, 512, 192)])
-def test_dual_backward_both_formulations(monkeypatch, combine, B, T, H, HK, D, WT, WS):
-    """The one-softmax (combined gradient stream) and the two-softmax dual backward against the same oracle."""
-    from ttcd_b200.ops import cuda
-    monkeypatch.setattr(cuda, "_BWD_COMBINE", combine)
+def test_dual_backward_batched_and_small_heads(B, T, H, HK, D, WT, WS):
     q, k, v = _inputs(B, T, H, HK, D)
     o_t, o_s = ops.dual_window_attention(q, k, v, WT, WS)
     g_t, g_s = torch.randn_like(o_t), torch.randn_like(o_s)
@@ -110,6 +106,73 @@ def test_dual_backward_both_formulations(monkeypatch, combine, B, T, H, HK, D, W
     _check(q.grad, qf.grad, "dq")
     _check(k.grad, kf.grad, "dk")
     _check(v.grad, vf.grad, "dv")
+
+
+@pytest.mark.parametrize("dual", [False, True])
+@pytest.mark.parametrize("D,H,HK", [(128, 4, 2), (64, 3, 1)])
+def test_packed_documents_one_launch_equals_per_document(dual, D, H, HK):
+    """Eight documents of uneven length packed into one 4K row: the in-kernel sequence bounds give what running every
+    document on its own gives (forward and backward), with windows shorter and longer than the documents."""
+    lens = [37, 700, 129, 1, 1500, 256, 900, 573]
+    T = sum(lens)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device=DEV, dtype=torch.int32)
+    WT, WS = 512, 192
+    q, k, v = _inputs(1, T, H, HK, D)
+
+    def run(qq, kk, vv, cu_seqlens):
+        if dual:
+            return ops.dual_window_attention(qq, kk, vv, WT, WS, cu_seqlens=cu_seqlens)
+        return (ops.attention(qq, kk, vv, window=WT, cu_seqlens=cu_seqlens),)
+
+    launches = _native.launch_count
+    outs = run(q, k, v, cu)
+    assert _native.launch_count - launches == 1, "a packed row is one forward launch"
+    gs = [torch.randn_like(o) for o in outs]
+    torch.autograd.backward(list(outs), gs)
+    qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+    bounds = cu.tolist()
+    want = [[] for _ in outs]
+    for a, b in zip(bounds[:-1], bounds[1:]):
+        if dual:
+            r = ref.dual_window_attention(qf[:, a:b], kf[:, a:b], vf[:, a:b], WT, WS)
+        else:
+            r = (ref.attention(qf[:, a:b], kf[:, a:b], vf[:, a:b], WT),)
+        for i, t in enumerate(r):
+            want[i].append(t)
+    want = [torch.cat(w, dim=1) for w in want]
+    torch.autograd.backward(want, [g.float() for g in gs])
+    for o, w in zip(outs, want):
+        _check(o, w, "o", atol=8e-3, rtol=1e-2)
+    _check(q.grad, qf.grad, "dq")
+    _check(k.grad, kf.grad, "dk")
+    _check(v.grad, vf.grad, "dv")
+
+
+def test_expired_wait_in_the_backward_is_reported():
+    """The dK/dV kernel's wait for key/value tiles that never arrive runs out within its (shortened) budget, the
+    kernel returns, the status word of the backward's translation unit says so, and the next call is healthy."""
+    import ctypes
+    from ttcd_b200.ops import cuda
+    lib = _native.load(required=True)
+    q, k, v = _inputs(1, 256, 2, 1, 128)
+    o, lse = ops.attention(q, k, v, window=128, return_lse=True)
+    g = torch.randn_like(o)
+    _native.device_status()
+    assert lib.ttcd_set_wait_ns_attn_bwd(ctypes.c_longlong(20_000_000)) == 0          # 20 ms
+    try:
+        cuda.attn_backward(q.detach(), k.detach(), v.detach(), o.detach(), None, lse, None, g, None, 128, 128, 128 ** -0.5,
+                           flags=1)
+        torch.cuda.synchronize()
+        assert _native.device_status() in (301, 304, 311), "the wait ran out but nothing recorded it"
+    finally:
+        assert lib.ttcd_set_wait_ns_attn_bwd(ctypes.c_longlong(0)) == 0
+    dq, dk, dv = cuda.attn_backward(q.detach(), k.detach(), v.detach(), o.detach(), None, lse, None, g, None, 128, 128,
+                                    128 ** -0.5)
+    qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref.attention(qf, kf, vf, 128).backward(g.float())
+    _check(dq, qf.grad, "dq")
+    _check(dk, kf.grad, "dk")
+    _check(dv, vf.grad, "dv")
 
 
 @pytest.mark.parametrize("D", [64, 128])

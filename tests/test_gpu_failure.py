@@ -22,7 +22,7 @@ def test_barrier_wait_expires_with_status_and_context_survives():
     ghost = torch.zeros(256, dtype=torch.int32, device="cuda")             # stands for a peer that never arrives
     t0 = time.time()
     nv.call("ttcd_comm_barrier", _i64s([mine.data_ptr(), ghost.data_ptr()]), nv.i32(0), nv.i32(2), nv.i32(0), nv.i32(1),
-            nv.i64(300_000_000), nv.stream_ptr())                          # 0.3 s budget
+            nv.i64(300_000_000), nv.ptr(None), nv.stream_ptr())            # 0.3 s budget
     torch.cuda.synchronize()
     assert time.time() - t0 < 5.0
     assert nv.device_status() == 501                                       # 500 + the rank that never arrived
@@ -59,3 +59,50 @@ def test_gemm_reduce_scatter_gives_up_on_an_absent_peer():
     from ttcd_b200.ops import cuda
     torch.testing.assert_close(cuda.gemm(y, y.t()).view(512, 512).float(), y.float() @ y.float().t(), rtol=2e-2, atol=3e-1)
     assert nv.device_status() == 0
+
+
+def test_every_unit_with_bounded_waits_exports_its_status_reader():
+    """A wait that runs out in any kernel must be visible to ``device_status``: every translation unit that is built
+    with bounded waits has a reader, and the list the binding polls names them all."""
+    import re
+    from pathlib import Path
+    from ttcd_b200 import _native as nv
+    lib = nv.load(required=True)
+    root = Path(__file__).resolve().parents[1] / "csrc"
+    with_waits = {re.search(r"TTCD_DEFINE_STATUS_READER\((\w+)\)", f.read_text()).group(1)
+                  for f in root.glob("*.cu") if "mbar_wait" in f.read_text() or "atomicCAS(&g_status" in f.read_text()}
+    assert with_waits == set(nv.STATUS_UNITS), (with_waits, nv.STATUS_UNITS)
+    for unit in nv.STATUS_UNITS:
+        assert hasattr(lib, f"ttcd_read_status_{unit}") and hasattr(lib, f"ttcd_set_wait_ns_{unit}")
+
+
+def test_expired_peer_wait_makes_the_optimizer_kernel_leave_the_weights_alone():
+    """What the sharded runtime builds its skip on: the barrier kernel of a rank whose peer never arrives sets the
+    fail word, and the fused AdamW + publish kernel that is handed a non-zero skip word changes nothing."""
+    from ttcd_b200 import _native as nv
+    nv.load(required=True)
+    nv.device_status()
+    mine = torch.zeros(256, dtype=torch.int32, device="cuda")
+    ghost = torch.zeros(256, dtype=torch.int32, device="cuda")
+    fail = torch.zeros(1, device="cuda")
+    nv.call("ttcd_comm_barrier", _i64s([mine.data_ptr(), ghost.data_ptr()]), nv.i32(0), nv.i32(2), nv.i32(0), nv.i32(1),
+            nv.i64(100_000_000), nv.ptr(fail), nv.stream_ptr())
+    torch.cuda.synchronize()
+    assert float(fail) == 1.0 and nv.device_status() == 501
+    n = 4096
+    p32 = torch.randn(n, device="cuda")
+    g, m, v = torch.randn(n, device="cuda"), torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    flat = [p32.to(torch.bfloat16).clone() for _ in range(2)]            # the two "ranks'" bf16 parameter buffers
+    before = [t.clone() for t in (p32, m, v, *flat)]
+    skip = (fail > 0).to(torch.int32)
+    coef = torch.ones(1, device="cuda")
+    args = lambda sk: (nv.ptr(p32), nv.ptr(g), nv.ptr(m), nv.ptr(v), _i64s([t.data_ptr() for t in flat]), nv.i32(2), nv.i64(0),  # noqa: E731
+                       nv.i64(n), nv.f32(1e-2), nv.f32(0.9), nv.f32(0.95), nv.f32(1e-8), nv.f32(0.1), nv.f32(0.1), nv.f32(0.2236),
+                       nv.ptr(coef), nv.ptr(sk), nv.stream_ptr())
+    nv.call("ttcd_adamw_push", *args(skip))
+    torch.cuda.synchronize()
+    for t, b in zip((p32, m, v, *flat), before):
+        assert torch.equal(t, b)
+    nv.call("ttcd_adamw_push", *args(torch.zeros(1, dtype=torch.int32, device="cuda")))
+    torch.cuda.synchronize()
+    assert not torch.equal(p32, before[0]) and torch.equal(flat[0], flat[1]) and not torch.equal(flat[0], before[3])

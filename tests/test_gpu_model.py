@@ -1,0 +1,135 @@
+"""Whole-model checks on the GPU: the bf16 model on the native kernels against the same weights in fp32 through the
+PyTorch statements of the ops (loss and gradients), the op-level recompute policy, and the cached decode path."""
+import pytest
+import torch
+
+from ttcd_b200 import _native
+from ttcd_b200.models import IPTTCDv9Config, IPTTCDv9ForCausalLM
+from ttcd_b200.train.engine import EngineConfig, TrainEngine
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(autouse=True)
+def _status():
+    _native.load(required=True)
+    yield
+    torch.cuda.synchronize()
+    assert _native.device_status() == 0, "a bounded device wait expired"
+
+
+def _config(**over):
+    kw = dict(hidden_size=512, num_hidden_layers=4, num_heads=4, num_kv_heads=2, head_dim=128, intermediate_size=1536,
+              vocab_size=4096, window_size=1024, max_position_embeddings=4096, ttt_mode=True, ttt_chunk=512,
+              ttt_visible_chunks=1, ttt_layers=[2], ttt_update_every=8, qk_norm=True, tie_word_embeddings=True,
+              fuse_cross_entropy=False, fuse_linear_cross_entropy=True, ttt_teacher_conv_init="identity",
+              ttt_proj_init="diagonal_gaussian", ttt_normalize_student_features=False, ttt_output_use_teacher_conv=False)
+    kw.update(over)
+    return IPTTCDv9Config(**kw)
+
+
+def _cos(a, b):
+    a, b = a.float().flatten(), b.float().flatten()
+    return float(torch.dot(a, b) / (a.norm() * b.norm()).clamp_min(1e-30))
+
+
+def test_bf16_native_model_matches_fp32_statement():
+    """4 layers (one fast-weight layer), 4096 tokens, hidden 512: loss within 2e-2 and gradient cosine >= 0.99 on every
+    kind of parameter."""
+    torch.manual_seed(0)
+    cfg = _config()
+    ref_model = IPTTCDv9ForCausalLM(cfg).to(DEV, torch.float32).train()
+    with torch.no_grad():                      # give the fast-weight path something to do
+        for n, p in ref_model.named_parameters():
+            if "ttt_student_conv" in n or "b_proj" in n:
+                p.normal_(0, 0.1)
+    model = IPTTCDv9ForCausalLM(cfg).to(DEV, torch.bfloat16).train()
+    model.load_state_dict(ref_model.state_dict())
+    ref_model.load_state_dict(model.state_dict())          # both see the bf16-rounded weights
+    ids = torch.randint(0, cfg.vocab_size, (1, 4096), device=DEV)
+    before = _native.launch_count
+    loss = model(input_ids=ids, labels=ids).loss
+    loss.backward()
+    assert _native.launch_count - before > 100, "the native kernels did not run"
+    ref_loss = ref_model(input_ids=ids, labels=ids).loss
+    ref_loss.backward()
+    assert abs(float(loss) - float(ref_loss)) < 2e-2, (float(loss), float(ref_loss))
+    want = dict(ref_model.named_parameters())
+    kinds = ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj", "ttt_proj", "ttt_student_conv",
+             "ttt_teacher_conv", "b_proj", "embeddings", "attn_norm", "mlp_norm", "q_norm", "k_norm")
+    seen = set()
+    for n, p in model.named_parameters():
+        kind = next((k for k in kinds if k in n), None)
+        if kind is None or p.grad is None:
+            continue
+        seen.add(kind)
+        c = _cos(p.grad, want[n].grad)
+        floor = 0.98 if kind in ("ttt_teacher_conv", "b_proj", "q_norm", "k_norm") else 0.99     # tiny tensors: noisier
+        assert c >= floor, f"{n}: gradient cosine {c:.4f}"
+    assert {"q_proj", "down_proj", "ttt_proj", "ttt_student_conv", "b_proj", "embeddings"} <= seen, seen
+
+
+def test_op_recompute_policy_matches_resident_activations_with_fewer_launches():
+    cfg = _config()
+    ids = torch.randint(0, cfg.vocab_size, (1, 2048), device=DEV)
+    grads, launches, peak = {}, {}, {}
+    for mode in ("none", "op", "full"):
+        eng = TrainEngine(cfg, EngineConfig(lr=1e-3, activation_checkpoint=mode, seed=3), device=DEV)
+        eng.sdp.zero_grad()
+        eng.forward_backward(ids)                # warm-up (lazy initialisation of the kernels)
+        eng.sdp.zero_grad()
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats()
+        base = torch.cuda.memory_allocated()
+        before = _native.launch_count
+        eng.forward_backward(ids)
+        torch.cuda.synchronize()
+        launches[mode] = _native.launch_count - before
+        peak[mode] = torch.cuda.max_memory_allocated() - base
+        grads[mode] = {n: p.grad.detach().float().clone() for n, p in eng.model.named_parameters()}
+        del eng
+    for n, g in grads["none"].items():
+        assert _cos(grads["op"][n], g) > 0.9999, n          # the same kernels on the same inputs
+        torch.testing.assert_close(grads["op"][n], g, rtol=2e-2, atol=2e-3, msg=n)
+    assert launches["none"] < launches["op"] < launches["full"], launches
+    assert peak["full"] < peak["op"] < peak["none"], peak
+
+
+def test_decode_steps_match_one_forward():
+    """Prefill then token-by-token steps through the window cache (the small-query attention kernel) give the logits
+    of one forward over the whole sequence."""
+    torch.manual_seed(1)
+    cfg = _config(ttt_layers=[], ttt_mode=False, num_hidden_layers=2, window_size=384)
+    model = IPTTCDv9ForCausalLM(cfg).to(DEV, torch.bfloat16).eval()
+    ids = torch.randint(0, cfg.vocab_size, (2, 700), device=DEV)
+    with torch.no_grad():
+        full = model(input_ids=ids).logits.float()
+        out = model(input_ids=ids[:, :640], use_cache=True)
+        cache, steps = out.past_key_values, [out.logits.float()]
+        before = _native.launch_count
+        for t in range(640, 700, 20):                     # 20-token continuations, then single tokens
+            out = model(input_ids=ids[:, t:t + 19], past_key_values=cache, use_cache=True)
+            steps.append(out.logits.float())
+            out = model(input_ids=ids[:, t + 19:t + 20], past_key_values=cache, use_cache=True)
+            steps.append(out.logits.float())
+        assert _native.launch_count > before
+    got = torch.cat(steps, dim=1)
+    err = (got - full).abs()
+    assert err.max() < 0.25 and err.mean() < 2e-2, (float(err.max()), float(err.mean()))
+    agree = (got.argmax(-1) == full.argmax(-1)).float().mean()
+    assert agree > 0.97, float(agree)
+
+
+@pytest.mark.parametrize("Tq,Tk,H,HK,D,W", [(1, 8192, 16, 8, 128, 8192), (1, 300, 4, 2, 64, None), (19, 1000, 4, 2, 128, 512),
+                                             (127, 127, 3, 1, 64, 50), (5, 70000, 2, 1, 128, None)])
+def test_small_query_attention_kernel(Tq, Tk, H, HK, D, W):
+    from ttcd_b200.ops import cuda, reference as ref
+    q = torch.randn(2, Tq, H, D, device=DEV).bfloat16()
+    k = torch.randn(2, Tk, HK, D, device=DEV).bfloat16()
+    v = torch.randn(2, Tk, HK, D, device=DEV).bfloat16()
+    assert cuda.attn_small_q_supported(q, k)
+    got = cuda.attn_small_q(q, k, v, W)
+    want = ref.attention(q.float(), k.float(), v.float(), W)
+    err = (got.float() - want).abs()
+    assert err.max() < 2e-2, float(err.max())

@@ -92,7 +92,7 @@ def test_linear_and_fused_linear_autograd():
 
 # ----------------------------------------------------------------------------------- elementwise
 
-@pytest.mark.parametrize("D", [128, 960, 1024, 2048])
+@pytest.mark.parametrize("D", [128, 960, 1024, 2048, 4096, 5120])     # > 2048: the streaming (wide-row) kernels
 def test_rmsnorm_fwd_bwd(D):
     x = torch.randn(3, 77, D, device=DEV, dtype=BF, requires_grad=True)
     r = torch.randn(3, 77, D, device=DEV, dtype=BF, requires_grad=True)
@@ -110,10 +110,10 @@ def test_rmsnorm_fwd_bwd(D):
     _close(w.grad, wf.grad, 0.3, 3e-2, "rmsnorm dw")
 
 
-def test_rmsnorm_dual():
-    D = 1024
+@pytest.mark.parametrize("D", [960, 1024, 2048, 4096])      # one two-input kernel each way; wide rows use the single kernel twice
+def test_rmsnorm_dual(D):
     a_t, a_s, r = (torch.randn(2, 50, D, device=DEV, dtype=BF, requires_grad=True) for _ in range(3))
-    w = torch.ones(D, device=DEV, dtype=BF, requires_grad=True)
+    w = (torch.randn(D, device=DEV) * 0.1 + 1).to(BF).requires_grad_()
     outs = ops.rmsnorm_dual(a_t, a_s, r, w, 1e-6)
     gs = [torch.randn_like(o) for o in outs]
     torch.autograd.backward(outs, gs)

@@ -94,10 +94,10 @@ _ERRORS = {
 
 
 launch_count = 0  # kernels launched through this binding (entry points that launch two count twice)
-_MULTI_KERNEL = {"ttcd_attn_bwd": 2, "ttcd_attn_bwd_cp": 2, "ttcd_rmsnorm_bwd_no_alloc": 2,
+_MULTI_KERNEL = {"ttcd_attn_bwd": 2, "ttcd_attn_bwd_cp": 2, "ttcd_rmsnorm_bwd_no_alloc": 2, "ttcd_attn_small_q": 2,
                  # host-only entry points launch nothing
-                 "ttcd_attn_bwd_set_dv_layout": 0, "ttcd_attn_bwd_set_combined": 0, "ttcd_attn_bwd_set_probe": 0, "ttcd_symm_alloc": 0, "ttcd_symm_free": 0, "ttcd_ipc_get_handle": 0,
-                 "ttcd_ipc_open_handle": 0, "ttcd_ipc_close": 0}
+                 "ttcd_symm_alloc": 0, "ttcd_symm_free": 0, "ttcd_ipc_get_handle": 0, "ttcd_ipc_open_handle": 0,
+                 "ttcd_ipc_close": 0}
 
 
 def call(symbol: str, *args) -> None:
@@ -127,13 +127,17 @@ def f32(v) -> ctypes.c_float:
     return ctypes.c_float(float(v))
 
 
+# translation units of the library that contain bounded waits; each exports ttcd_read_status_<unit>
+STATUS_UNITS = ("gemm", "attn", "attn_bwd", "comm", "gemm_comm")
+
+
 def device_status(reset: bool = True) -> int:
     """Read (and clear) the device-side error word written by bounded waits."""
     lib = load()
     if lib is None:
         return 0
     status = 0
-    for unit in ("gemm", "attn", "comm", "gemm_comm"):
+    for unit in STATUS_UNITS:
         fn = getattr(lib, f"ttcd_read_status_{unit}", None)
         if fn is None:
             continue

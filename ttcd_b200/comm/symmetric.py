@@ -96,11 +96,14 @@ class SymmetricBuffer:
 class PeerBarrier:
     """All-to-all flag barrier over a symmetric flag array (``slots`` independent barriers)."""
 
-    def __init__(self, group=None, slots: int = 8, wait_ns: int = 0):
+    def __init__(self, group=None, slots: int = 8, wait_ns: int = 0, fail: torch.Tensor | None = None):
+        """``wait_ns``: budget of one wait (0: the library default, 10 s).  ``fail``: optional 1-element fp32 CUDA
+        tensor that a wait which runs out sets to 1 (kernels later in the step take it as their skip flag)."""
         self.buf = SymmetricBuffer(slots * 64 * 4, group)
         self.rank, self.world, self.slots = self.buf.rank, self.buf.world, slots
         self.epochs = [0] * slots
         self.wait_ns = wait_ns
+        self.fail = fail
 
     def sync(self, slot: int = 0, stream: torch.cuda.Stream | None = None) -> None:
         """Enqueue the barrier on ``stream`` (default: current).  Work enqueued after it on that stream
@@ -108,7 +111,7 @@ class PeerBarrier:
         self.epochs[slot] += 1
         s = ctypes.c_void_p((stream or torch.cuda.current_stream()).cuda_stream)
         nv.call("ttcd_comm_barrier", self.buf.ptr_array(), nv.i32(self.rank), nv.i32(self.world), nv.i32(slot),
-                nv.i32(self.epochs[slot]), nv.i64(self.wait_ns), s)
+                nv.i32(self.epochs[slot]), nv.i64(self.wait_ns), nv.ptr(self.fail), s)
 
     def check(self) -> None:
         """Raise if a bounded wait expired (a peer never arrived).  Synchronises the device."""

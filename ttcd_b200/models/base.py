@@ -135,12 +135,13 @@ class DecoderModel(DecoderPreTrainedModel):
     def _block_kwargs(self, input_ids, inputs_embeds, kwargs) -> dict[str, Any]:
         return kwargs
 
-    # which blocks are recomputed in backward: "full" (all), "everyN", "ttt" (fast-weight blocks only)
+    # which blocks are recomputed in backward: "full" (all), "everyN", "ttt" (fast-weight blocks only), "op" (all
+    # blocks, but the GEMM / attention launches are not repeated: ops/selective.py)
     checkpoint_policy: str = "full"
 
     def _checkpoint_layer(self, layer) -> bool:
         policy = self.checkpoint_policy
-        if policy == "full":
+        if policy in ("full", "op"):
             return True
         if policy == "ttt":
             return bool(getattr(layer, "is_ttt_layer", False))
@@ -176,8 +177,15 @@ class DecoderModel(DecoderPreTrainedModel):
             if nvtx:
                 torch.cuda.nvtx.range_push(f"layer{i}")
             if self.gradient_checkpointing and self.training and self._checkpoint_layer(layer):
+                fn = layer
+                if self.checkpoint_policy == "op":
+                    from ..ops.selective import OpCache
+
+                    def fn(*a, _layer=layer, _cache=OpCache(), **kw):
+                        with _cache.scope():
+                            return _layer(*a, **kw)
                 hidden_states = torch.utils.checkpoint.checkpoint(
-                    layer, hidden_states, attention_mask, None, False, use_reentrant=False, **kwargs)
+                    fn, hidden_states, attention_mask, None, False, use_reentrant=False, **kwargs)
             else:
                 hidden_states = layer(hidden_states, attention_mask, past_key_values, use_cache, **kwargs)
             if nvtx:

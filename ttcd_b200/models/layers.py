@@ -256,10 +256,24 @@ def positions_from_cu_seqlens(cu_seqlens: torch.Tensor, total: int, device) -> t
 
 
 def _padded_attention(q, k, v, attention_mask, window):
-    """Left- or right-padded batches: attend per row over that row's valid tokens only."""
+    """Left- or right-padded batches: every row attends over its own valid tokens only.
+
+    Prefill (as many queries as keys): the valid tokens of all rows are packed into one row and run as ONE
+    attention launch with per-sequence bounds, then scattered back (the unpad -> varlen -> pad sequence of
+    fla/layers/attn.py:229-254).  Decode over a padded cache keeps one call per row."""
     B, Tq = q.shape[:2]
     Tk = k.shape[1]
     mask = attention_mask[:, -Tk:].bool()
+    if Tq == Tk:
+        flat = mask.reshape(-1)
+        idx = flat.nonzero(as_tuple=False).squeeze(1)            # sizes the packed row (the one host sync of unpadding)
+        lens = mask.sum(-1)
+        cu = F.pad(lens.cumsum(0), (1, 0)).to(torch.int32)
+        pick = lambda t: t.reshape(1, B * Tq, *t.shape[2:])[:, idx]      # noqa: E731
+        o = ops.attention(pick(q), pick(k), pick(v), window=window, cu_seqlens=cu)
+        out = q.new_zeros(B * Tq, *q.shape[2:])
+        out[idx] = o[0].to(out.dtype)
+        return out.view(B, Tq, *q.shape[2:])
     outs = []
     for b in range(B):
         kb = k[b:b + 1, mask[b]]

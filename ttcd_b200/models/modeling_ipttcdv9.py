@@ -144,7 +144,7 @@ class IPTTCDMLP(GatedMLP):
                     update_every=min(T, self.ttt_update_every), state_dtype=self._state_dtype(compute_dtype),
                     normalize_student=self.ttt_normalize_student_features, norm_proj_diff=self.ttt_norm_proj_diff,
                     post_proj=post, return_last_dw_norm=True, cp=_cp_state() if self.training else None,
-                    proj_reduce=None if tp is None else (lambda v: _tp_sum(v, tp)))
+                    proj_reduce=None if tp is None else (lambda v: _tp_sum(v, tp)), key=("ttt_scan", self.layer_idx))
             if self.training and last is not None:
                 self._last_delta_w_norm_t = last  # device scalar; read lazily, no host sync here
         y = y.reshape(b, T * C, -1)[:, :seq_len]

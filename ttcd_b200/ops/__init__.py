@@ -167,16 +167,20 @@ def lse_merge(o_a, lse_a, o_b, lse_b):
 
 def ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, *, lr, update_every, state_dtype=None,
              normalize_student=False, norm_proj_diff=False, post_proj=None, return_last_dw_norm=False, cp=None,
-             proj_reduce=None):
+             proj_reduce=None, key=None):
+    """``key``: identifies the calling layer (context parallel: names the peer buffers of its rank prefix)."""
     plain = not normalize_student and not norm_proj_diff and post_proj is None
     if _native.use_native(z_out) and plain and (state_dtype in (None, torch.bfloat16, torch.float32)):
         T, C = z_out.shape[1], z_out.shape[2]
-        fused_ok = ((cp is None or cp.size == 1) and proj_reduce is None and C >= 128 and z_out.shape[3] >= 128
-                    and w_down.shape[0] >= 128 and z_out.shape[3] % 8 == 0 and w_down.shape[0] % 8 == 0)
+        sharded = cp is not None and cp.size > 1
+        fused_ok = ((not sharded or getattr(cp, "barrier", None) is not None) and proj_reduce is None and C >= 128
+                    and z_out.shape[3] >= 128 and w_down.shape[0] >= 128 and z_out.shape[3] % 8 == 0
+                    and w_down.shape[0] % 8 == 0)
         if fused_ok:
             # grouping by update_every only bounds the reference's memory; the prefix over chunks is the same sum:
-            # batched GEMMs + one streaming prefix kernel (ops/cuda.py::_TTTScan)
-            y, last = _cuda().ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, lr)
+            # batched GEMMs + one streaming prefix kernel (ops/cuda.py::_TTTScan); under context parallelism the
+            # prefix over ranks runs over peer memory
+            y, last = _cuda().ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, lr, cp if sharded else None, key)
             return (y, last) if return_last_dw_norm else y
         return reference.ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, lr=lr,
                                   update_every=update_every, state_dtype=torch.float32,

@@ -6,14 +6,13 @@ validated on the host before a launch (the kernels do no bounds recovery).
 """
 from __future__ import annotations
 
-import os
-
 import math
 
 import torch
 
 from .. import _native as nv
 from . import reference
+from .selective import keep
 
 _BF16 = torch.bfloat16
 _SM_BLOCKS = 148 * 2
@@ -155,7 +154,7 @@ class _MatMul(torch.autograd.Function):
     def forward(ctx, a, b):
         ctx.save_for_backward(a, b)
         out_shape = torch.broadcast_shapes(a.shape[:-2], b.shape[:-2]) + (a.shape[-2], b.shape[-1])
-        return gemm(a, b).view(out_shape)
+        return keep(lambda: gemm(a, b)).view(out_shape)
 
     @staticmethod
     def backward(ctx, g):
@@ -234,7 +233,7 @@ class _Linear(torch.autograd.Function):
         ctx.save_for_backward(x2, w)
         ctx.x_shape = x.shape
         ctx.splits = [wi.shape[0] for wi in weights]
-        y = gemm(x2, w.transpose(0, 1)).view(x2.shape[0], w.shape[0])
+        y = keep(lambda: gemm(x2, w.transpose(0, 1))).view(x2.shape[0], w.shape[0])
         if len(weights) == 1:
             return y.view(*x.shape[:-1], w.shape[0])
         outs, col = [], 0
@@ -367,14 +366,25 @@ def rmsnorm(x, weight, eps, residual=None, prenorm=False):
 
 
 class _RMSNormDual(torch.autograd.Function):
-    """x = norm(r + a_T), t = norm(r + a_S), r_out = r + a_T with one shared weight."""
+    """x = norm(r + a_T), t = norm(r + a_S), r_out = r + a_T with one shared weight: one kernel forward (the residual
+    is read once), one kernel backward (d_a_T, d_a_S, d_r and the weight-gradient partial sums of both streams)."""
 
     @staticmethod
     def forward(ctx, a_t, a_s, residual, weight, eps):
         at2, as2, r2 = (_rows2d(v).contiguous() for v in (a_t, a_s, residual))
         w = weight.to(_BF16).contiguous()
-        x, s_t, rstd_t = _rmsnorm_fwd(at2, r2, w, eps, True)
-        t, s_s, rstd_s = _rmsnorm_fwd(as2, r2, w, eps, True)
+        rows, D = at2.shape
+        ctx.fused = D <= 2048
+        if ctx.fused:
+            x, t, s_t, s_s = (torch.empty_like(at2) for _ in range(4))
+            rstd_t = torch.empty(rows, dtype=torch.float32, device=at2.device)
+            rstd_s = torch.empty_like(rstd_t)
+            nv.call("ttcd_rmsnorm_dual_fwd", nv.ptr(at2), nv.ptr(as2), nv.ptr(r2), nv.ptr(w), nv.ptr(x), nv.ptr(t),
+                    nv.ptr(s_t), nv.ptr(s_s), nv.ptr(rstd_t), nv.ptr(rstd_s), nv.i64(rows), nv.i32(D), nv.f32(eps),
+                    nv.stream_ptr())
+        else:       # wide rows: the single-input streaming kernel, twice
+            x, s_t, rstd_t = _rmsnorm_fwd(at2, r2, w, eps, True)
+            t, s_s, rstd_s = _rmsnorm_fwd(as2, r2, w, eps, True)
         ctx.save_for_backward(s_t, s_s, w, rstd_t, rstd_s)
         ctx.wdtype = weight.dtype
         shp = a_t.shape
@@ -384,11 +394,20 @@ class _RMSNormDual(torch.autograd.Function):
     def backward(ctx, dx, dt, dres):
         s_t, s_s, w, rstd_t, rstd_s = ctx.saved_tensors
         shp = dx.shape
-        d_at, dw_t = _rmsnorm_bwd(_rows2d(dx).contiguous(), s_t, w, rstd_t,
-                                  None if dres is None else _rows2d(dres).contiguous())
-        d_as, dw_s = _rmsnorm_bwd(_rows2d(dt).contiguous(), s_s, w, rstd_s, None)
-        d_res = d_at + d_as
-        return d_at.view(shp), d_as.view(shp), d_res.view(shp), (dw_t + dw_s).to(ctx.wdtype), None
+        dx2, dt2 = _rows2d(dx).contiguous(), _rows2d(dt).contiguous()
+        dres2 = None if dres is None else _rows2d(dres).contiguous()
+        if not ctx.fused:
+            d_at, dw_t = _rmsnorm_bwd(dx2, s_t, w, rstd_t, dres2)
+            d_as, dw_s = _rmsnorm_bwd(dt2, s_s, w, rstd_s, None)
+            return d_at.view(shp), d_as.view(shp), (d_at + d_as).view(shp), (dw_t + dw_s).to(ctx.wdtype), None
+        rows, D = dx2.shape
+        d_at, d_as, d_res = (torch.empty_like(dx2) for _ in range(3))
+        nblk = min(148, (rows + 7) // 8)
+        dwp = torch.empty(nblk, D, dtype=torch.float32, device=dx2.device)
+        nv.call("ttcd_rmsnorm_dual_bwd", nv.ptr(dx2), nv.ptr(dt2), nv.ptr(s_t), nv.ptr(s_s), nv.ptr(w), nv.ptr(rstd_t),
+                nv.ptr(rstd_s), nv.ptr(dres2), nv.ptr(d_at), nv.ptr(d_as), nv.ptr(d_res), nv.ptr(dwp), nv.i64(rows),
+                nv.i32(D), nv.i32(nblk), nv.stream_ptr())
+        return d_at.view(shp), d_as.view(shp), d_res.view(shp), dwp.sum(0).to(ctx.wdtype), None
 
 
 def rmsnorm_dual(a_t, a_s, residual, weight, eps):
@@ -590,11 +609,23 @@ def _attn_layout(t: torch.Tensor):
     return t, t.stride(1), (t.stride(0) if B > 1 else T * t.stride(1))
 
 
-def attn_forward(q, k, v, window_t, window_s, scale, dual):
+def segment_bounds(cu_seqlens: torch.Tensor, total: int):
+    """Per-token (first token of its sequence, one past its last) as int32 tensors, from the boundaries of a packed
+    row; computed on the device, nothing synchronises with the host."""
+    cu = cu_seqlens.to(torch.int64).reshape(-1)
+    pos = torch.arange(total, device=cu.device)
+    seg = torch.searchsorted(cu, pos, right=True) - 1
+    seg = seg.clamp_(0, cu.numel() - 2)
+    return cu[seg].to(torch.int32).contiguous(), cu[seg + 1].clamp(max=total).to(torch.int32).contiguous()
+
+
+def attn_forward(q, k, v, window_t, window_s, scale, dual, seg=None):
     B, Tq, H, D = q.shape
     Tk, HK = k.shape[1], k.shape[2]
     if D not in (64, 128):
         raise ValueError(f"head_dim {D} not supported by the attention kernel (64 or 128)")
+    if seg is not None and (B != 1 or Tq != Tk):
+        raise ValueError("packed sequences need one row of queries and keys of equal length")
     q, ldq, sq = _attn_layout(q)
     k, ldk, sk = _attn_layout(k)
     v, ldv, sv = _attn_layout(v)
@@ -605,69 +636,69 @@ def attn_forward(q, k, v, window_t, window_s, scale, dual):
     nv.call("ttcd_attn_fwd", nv.ptr(q), nv.ptr(k), nv.ptr(v), nv.ptr(o_t), nv.ptr(o_s), nv.ptr(lse_t), nv.ptr(lse_s),
             nv.i32(B), nv.i32(Tq), nv.i32(Tk), nv.i32(H), nv.i32(HK), nv.i32(D), nv.i64(ldq), nv.i64(ldk), nv.i64(ldv),
             nv.i64(sq), nv.i64(sk), nv.i64(sv), nv.i32(window_t or 0), nv.i32(window_s or 0), nv.f32(scale),
-            nv.stream_ptr())
+            nv.ptr(None if seg is None else seg[0]), nv.stream_ptr())
     return (q, k, v), o_t, o_s, lse_t, lse_s
 
 
-_BWD_COMBINE = os.environ.get("TTCD_ATTN_BWD_COMBINE", "1") != "0"      # one-softmax dual backward (0: two softmaxes)
+def attn_backward_streams(o_t, o_s, lse_t, lse_s, do_t, do_s):
+    """Row statistics of the backward: ``(delta_t, do_c, delta_c)``.  Dual window goes through one softmax: inside the
+    student window P_S = r P_T (r = exp(lse_T - lse_S), per row), so the student gradient stream folds into the
+    teacher's, dO' = dO_T + r dO_S and delta' = delta_T + r delta_S; one kernel makes delta_T, delta' and dO'."""
+    B, Tq, H, D = o_t.shape
+    delta_t = torch.empty(B, H, Tq, dtype=torch.float32, device=o_t.device)
+    if o_s is None:
+        nv.call("ttcd_attn_delta", nv.ptr(o_t), nv.ptr(do_t), nv.ptr(delta_t), nv.i64(B), nv.i32(Tq), nv.i32(H), nv.i32(D),
+                nv.stream_ptr())
+        return delta_t, None, None
+    delta_c = torch.empty_like(delta_t)
+    do_c = torch.empty(B, Tq, H, D, dtype=_BF16, device=o_t.device)
+    nv.call("ttcd_attn_bwd_combine", nv.ptr(o_t), nv.ptr(do_t), nv.ptr(o_s), nv.ptr(do_s), nv.ptr(lse_t), nv.ptr(lse_s),
+            nv.ptr(delta_t), nv.ptr(delta_c), nv.ptr(do_c), nv.i64(B), nv.i32(Tq), nv.i32(H), nv.i32(D), nv.stream_ptr())
+    return delta_t, do_c, delta_c
 
 
-def attn_backward(q, k, v, o_t, o_s, lse_t, lse_s, do_t, do_s, window_t, window_s, scale, dv_slab=None):
+def attn_backward(q, k, v, o_t, o_s, lse_t, lse_s, do_t, do_s, window_t, window_s, scale, dv_slab=None, seg=None,
+                  flags: int = 0):
     """dq, dk, dv of the (dual-window) attention; both outputs' gradients are summed in-kernel."""
     B, Tq, H, D = q.shape
     Tk, HK = k.shape[1], k.shape[2]
-    if not nv.has("ttcd_attn_bwd"):
-        raise nv.NativeError("ttcd_attn_bwd missing from the native library")
     dual = o_s is not None
     q, ldq, sq = _attn_layout(q)
     k, ldk, sk = _attn_layout(k)
     v, ldv, sv = _attn_layout(v)
     do_t = do_t.contiguous()
     do_s = do_s.contiguous() if dual else None
-    def _delta(o, d_o):
-        out = torch.empty(B, H, Tq, dtype=torch.float32, device=q.device)
-        nv.call("ttcd_attn_delta", nv.ptr(o), nv.ptr(d_o), nv.ptr(out), nv.i64(B), nv.i32(Tq), nv.i32(H), nv.i32(D),
-                nv.stream_ptr())
-        return out
-
+    delta_t, do_c, delta_c = attn_backward_streams(o_t, o_s, lse_t, lse_s, do_t, do_s)
     dq = torch.empty(B, Tq, H, D, dtype=_BF16, device=q.device)
     dk = torch.empty(B, Tk, HK, D, dtype=_BF16, device=q.device)
-    if dual and _BWD_COMBINE and nv.has("ttcd_attn_bwd_combine"):
-        # inside the student window P_S = r P_T (r = exp(lse_T - lse_S), per row): fold the student gradient stream
-        # into the teacher's (dO' = dO_T + r dO_S, delta' = delta_T + r delta_S) so that the dK/dV kernel runs its
-        # single-window pipeline; one kernel makes delta_T, delta' and dO'
-        delta_t = torch.empty(B, H, Tq, dtype=torch.float32, device=q.device)
-        delta_s = None
-        delta_comb = torch.empty_like(delta_t)
-        do_comb = torch.empty(B, Tq, H, D, dtype=_BF16, device=q.device)
-        nv.call("ttcd_attn_bwd_combine", nv.ptr(o_t), nv.ptr(do_t), nv.ptr(o_s), nv.ptr(do_s), nv.ptr(lse_t),
-                nv.ptr(lse_s), nv.ptr(delta_t), nv.ptr(delta_comb), nv.ptr(do_comb), nv.i64(B), nv.i32(Tq), nv.i32(H),
-                nv.i32(D), nv.stream_ptr())
-        nv.call("ttcd_attn_bwd_set_combined", nv.ptr(do_comb), nv.ptr(delta_comb))
-    else:
-        delta_t = _delta(o_t, do_t)
-        delta_s = _delta(o_s, do_s) if dual else None
-    if dv_slab is not None and nv.has("ttcd_attn_bwd_set_dv_layout") and (dv_slab[1] * 2) % 16 == 0:
+    ld_dv = sb_dv = 0
+    if dv_slab is not None and (dv_slab[1] * 2) % 16 == 0:
+        # dV goes straight into the packed q|k|v gradient of the fused projection
         slab, col = dv_slab
         n_total = slab.n_total
         buf = slab.get(B * Tk, q.device)
         dv = torch.as_strided(buf, (B, Tk, HK, D), (Tk * n_total, n_total, D, 1), col)
-        nv.call("ttcd_attn_bwd_set_dv_layout", nv.i64(n_total), nv.i64(Tk * n_total))
+        ld_dv, sb_dv = n_total, Tk * n_total
     else:
         dv = torch.empty(B, Tk, HK, D, dtype=_BF16, device=q.device)
-    nv.call("ttcd_attn_bwd", nv.ptr(q), nv.ptr(k), nv.ptr(v), nv.ptr(do_t), nv.ptr(do_s), nv.ptr(lse_t), nv.ptr(lse_s),
-            nv.ptr(delta_t), nv.ptr(delta_s), nv.ptr(dq), nv.ptr(dk), nv.ptr(dv), nv.i32(B), nv.i32(Tq), nv.i32(Tk),
-            nv.i32(H), nv.i32(HK), nv.i32(D), nv.i64(ldq), nv.i64(ldk), nv.i64(ldv), nv.i64(sq), nv.i64(sk), nv.i64(sv),
-            nv.i32(window_t or 0), nv.i32(window_s or 0), nv.f32(scale), nv.stream_ptr())
+    nv.call("ttcd_attn_bwd", nv.ptr(q), nv.ptr(k), nv.ptr(v), nv.ptr(do_t), nv.ptr(do_c), nv.ptr(lse_t), nv.ptr(delta_t),
+            nv.ptr(delta_c), nv.ptr(dq), nv.ptr(dk), nv.ptr(dv), nv.i32(B), nv.i32(Tq), nv.i32(Tk), nv.i32(H), nv.i32(HK),
+            nv.i32(D), nv.i64(ldq), nv.i64(ldk), nv.i64(ldv), nv.i64(sq), nv.i64(sk), nv.i64(sv), nv.i64(ld_dv),
+            nv.i64(sb_dv), nv.i32(window_t or 0), nv.i32(window_s or 0), nv.f32(scale),
+            nv.ptr(None if seg is None else seg[0]), nv.ptr(None if seg is None else seg[1]), nv.i32(flags),
+            nv.stream_ptr())
     return dq, dk, dv
 
 
 class _Attention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, window_t, window_s, scale, dual):
+    def forward(ctx, q, k, v, window_t, window_s, scale, dual, seg_start, seg_end):
         ctx.v_slab = _slab_of(v)
-        (qc, kc, vc), o_t, o_s, lse_t, lse_s = attn_forward(q, k, v, window_t, window_s, scale, dual)
-        ctx.save_for_backward(qc, kc, vc, o_t, o_s, lse_t, lse_s)
+        seg = None if seg_start is None else (seg_start, seg_end)
+        qc, kc, vc = (_attn_layout(t)[0] for t in (q, k, v))
+        # the kept outputs are o / lse only: q, k, v are rebuilt by the recomputation
+        o_t, o_s, lse_t, lse_s = keep(lambda: attn_forward(qc, kc, vc, window_t, window_s, scale, dual, seg)[1:])
+        ctx.save_for_backward(qc, kc, vc, o_t, o_s, lse_t, lse_s, seg_start, seg_end)
         ctx.cfg = (window_t, window_s, scale, dual)
         ctx.mark_non_differentiable(lse_t)
         if dual:
@@ -677,7 +708,7 @@ class _Attention(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, *grads):
-        qc, kc, vc, o_t, o_s, lse_t, lse_s = ctx.saved_tensors
+        qc, kc, vc, o_t, o_s, lse_t, lse_s, seg_start, seg_end = ctx.saved_tensors
         window_t, window_s, scale, dual = ctx.cfg
         do_t = grads[0]
         do_s = grads[1] if dual else None
@@ -686,47 +717,68 @@ class _Attention(torch.autograd.Function):
         if dual and do_s is None:
             do_s = torch.zeros_like(o_s)
         dq, dk, dv = attn_backward(qc, kc, vc, o_t, o_s, lse_t, lse_s, do_t, do_s, window_t, window_s, scale,
-                                   dv_slab=ctx.v_slab)
-        return dq, dk, dv, None, None, None, None
-
-
-def _per_segment(fn, q, k, v, cu_seqlens):
-    """Packed (varlen) batches: run each sequence separately and concatenate."""
-    bounds = cu_seqlens.tolist()
-    outs = [fn(q[:, s:e], k[:, s:e], v[:, s:e]) for s, e in zip(bounds[:-1], bounds[1:])]
-    if isinstance(outs[0], tuple):
-        return tuple(torch.cat([o[i] for o in outs], dim=1 if outs[0][i].dim() == 4 else 2) for i in range(len(outs[0])))
-    return torch.cat(outs, dim=1)
+                                   dv_slab=ctx.v_slab, seg=None if seg_start is None else (seg_start, seg_end))
+        return dq, dk, dv, None, None, None, None, None, None
 
 
 def _too_short(q, k) -> bool:
-    """Single-token decode and other tiny problems (< one 128-row tile) use the PyTorch statement."""
+    """Fewer than one 128-row tile of queries or keys: the small-query kernel or the PyTorch statement."""
     return q.shape[1] < 128 or k.shape[1] < 128
+
+
+def _packed_args(q, k, cu_seqlens):
+    """Packed (varlen) rows are handled inside the kernels: one launch, per-token sequence bounds."""
+    if cu_seqlens is None:
+        return None, None
+    if q.shape[0] != 1 or q.shape[1] != k.shape[1]:
+        raise ValueError("cu_seqlens needs a single packed row with as many keys as queries")
+    return segment_bounds(cu_seqlens.to(q.device), q.shape[1])
 
 
 def attention(q, k, v, window=None, scale=None, cu_seqlens=None, return_lse=False):
     _check(q, "q")
-    if _too_short(q, k) and cu_seqlens is None:
-        return reference.attention(q, k, v, window, scale, None, return_lse)
+    if _too_short(q, k):
+        if cu_seqlens is None and not return_lse and not torch.is_grad_enabled() and attn_small_q_supported(q, k):
+            return attn_small_q(q, k, v, window, scale)
+        return reference.attention(q, k, v, window, scale, cu_seqlens, return_lse)
     scale = q.shape[-1] ** -0.5 if scale is None else scale
-    if cu_seqlens is not None:
-        out = _per_segment(lambda a, b, c: attention(a, b, c, window, scale, None, True), q, k, v, cu_seqlens)
-        return out if return_lse else out[0]
-    o, lse = _Attention.apply(q, k, v, window, window, scale, False)
+    seg_start, seg_end = _packed_args(q, k, cu_seqlens)
+    o, lse = _Attention.apply(q, k, v, window, window, scale, False, seg_start, seg_end)
     return (o, lse) if return_lse else o
 
 
 def dual_window_attention(q, k, v, window_teacher, window_student, scale=None, cu_seqlens=None):
     _check(q, "q")
-    if _too_short(q, k) and cu_seqlens is None:
-        return reference.dual_window_attention(q, k, v, window_teacher, window_student, scale)
+    if _too_short(q, k):
+        return reference.dual_window_attention(q, k, v, window_teacher, window_student, scale, cu_seqlens)
     scale = q.shape[-1] ** -0.5 if scale is None else scale
-    if cu_seqlens is not None:
-        out = _per_segment(lambda a, b, c: dual_window_attention(a, b, c, window_teacher, window_student, scale),
-                           q, k, v, cu_seqlens)
-        return out[0], out[1]
-    o_t, o_s, _, _ = _Attention.apply(q, k, v, window_teacher, window_student, scale, True)
+    seg_start, seg_end = _packed_args(q, k, cu_seqlens)
+    o_t, o_s, _, _ = _Attention.apply(q, k, v, window_teacher, window_student, scale, True, seg_start, seg_end)
     return o_t, o_s
+
+
+def attn_small_q_supported(q, k) -> bool:
+    return (nv.has("ttcd_attn_small_q") and q.shape[-1] in (64, 128) and 1 <= q.shape[1] < 128
+            and k.shape[1] >= q.shape[1] and q.shape[2] % k.shape[2] == 0)
+
+
+def attn_small_q(q, k, v, window=None, scale=None):
+    """Attention of a few query rows (a decode step or a short continuation) over a key/value cache: bottom-right
+    aligned causal mask, optional window; forward only (split over the keys, merged by a second pass)."""
+    B, Tq, H, D = q.shape
+    Tk, HK = k.shape[1], k.shape[2]
+    scale = D ** -0.5 if scale is None else scale
+    q, ldq, sq = _attn_layout(q)
+    k, ldk, sk = _attn_layout(k)
+    v, ldv, sv = _attn_layout(v)
+    splits = -(-Tk // 256)                  # 256 keys per CTA; the partial results are merged by a second pass
+    out = torch.empty(B, Tq, H, D, dtype=_BF16, device=q.device)
+    part_o = torch.empty(B, H, Tq, splits, D, dtype=torch.float32, device=q.device)
+    part_ml = torch.empty(B, H, Tq, splits, 2, dtype=torch.float32, device=q.device)
+    nv.call("ttcd_attn_small_q", nv.ptr(q), nv.ptr(k), nv.ptr(v), nv.ptr(out), nv.ptr(part_o), nv.ptr(part_ml), nv.i32(B),
+            nv.i32(Tq), nv.i32(Tk), nv.i32(H), nv.i32(HK), nv.i32(D), nv.i64(ldq), nv.i64(ldk), nv.i64(ldv), nv.i64(sq),
+            nv.i64(sk), nv.i64(sv), nv.i32(window or 0), nv.f32(scale), nv.i32(splits), nv.stream_ptr())
+    return out
 
 
 def lse_merge(o_a, lse_a, o_b, lse_b):
@@ -882,37 +934,53 @@ class _TTTScan(torch.autograd.Function):
 
     with a hand-written backward (five batched GEMMs + the reverse-prefix kernel).  Same math as
     ``reference.ttt_scan`` for the plain configuration (no feature normalisation, fp32 state).
+
+    Context parallel (``cp``: the T chunks are this rank's slice of a longer sequence): every chunk but the
+    globally last one updates, the scan starts from ``W_down + sum over earlier ranks of their lr * sum_j dW_j``
+    and hands the gradient of that start state back to the earlier ranks.  The two exclusive sums over ranks
+    run over peer memory (``cp.exclusive_sum``); everything else is the same kernels.
     """
 
     @staticmethod
-    def forward(ctx, z_out, z_tgt, z_hat, beta, w_down, w_update_t, lr):
+    def forward(ctx, z_out, z_tgt, z_hat, beta, w_down, w_update_t, lr, cp, key):
         b, T, C, d_i = z_out.shape
         d_h = w_down.shape[0]
         z_out, z_tgt, z_hat = z_out.contiguous(), z_tgt.contiguous(), z_hat.contiguous()
         w_down_c = w_down.to(_BF16).contiguous()
         wu = w_update_t.to(_BF16)
         wu = wu if wu.stride(-1) == 1 or wu.stride(-2) == 1 else wu.contiguous()
-        nu = T - 1
+        sharded = cp is not None and cp.size > 1
+        nu = T if (sharded and cp.rank < cp.size - 1) else T - 1       # globally, only the very last chunk never updates
         R = d_h * d_i
-        states = torch.empty(b, T, d_h, d_i, dtype=_BF16, device=z_out.device)
-        P = None
-        last_norm = torch.zeros((), dtype=torch.float32, device=z_out.device)
-        if nu > 0:
-            diff = z_tgt[:, :nu] - z_hat[:, :nu]
-            scale = None if beta is None else beta[:, :nu].reshape(-1).to(_BF16).contiguous()
-            P = gemm(diff.reshape(b * nu * C, d_i), wu, row_scale=scale).view(b * nu, C, d_h)
-            del diff
-            zh_u = z_hat[:, :nu].reshape(b * nu, C, d_i)
-            d_w = gemm(P.transpose(-1, -2), zh_u, out_dtype=torch.float32)            # [b*nu, d_h, d_i]
-            last_norm = d_w.view(b, nu, -1)[:, -1].norm()
-        else:
-            d_w = torch.empty(0, dtype=torch.float32, device=z_out.device)
-        nv.call("ttcd_ttt_prefix_weights", nv.ptr(d_w if nu > 0 else None), nv.ptr(w_down_c), nv.ptr(None), nv.ptr(states),
-                nv.f32(float(lr)), nv.i32(b), nv.i32(T), nv.i64(R), nv.stream_ptr())
-        del d_w
-        y = gemm(z_out.view(b * T, C, d_i), states.view(b * T, d_h, d_i).transpose(-1, -2)).view(b, T, C, d_h)
+
+        def compute():
+            states = torch.empty(b, T, d_h, d_i, dtype=_BF16, device=z_out.device)
+            P = None
+            last_norm = torch.zeros((), dtype=torch.float32, device=z_out.device)
+            if nu > 0:
+                diff = z_tgt[:, :nu] - z_hat[:, :nu]
+                scale = None if beta is None else beta[:, :nu].reshape(-1).to(_BF16).contiguous()
+                P = gemm(diff.reshape(b * nu * C, d_i), wu, row_scale=scale).view(b * nu, C, d_h)
+                del diff
+                zh_u = z_hat[:, :nu].reshape(b * nu, C, d_i)
+                d_w = gemm(P.transpose(-1, -2), zh_u, out_dtype=torch.float32)            # [b*nu, d_h, d_i]
+                last_norm = d_w.view(b, nu, -1)[:, -1].norm()
+            else:
+                d_w = torch.empty(0, dtype=torch.float32, device=z_out.device)
+            w_init = None
+            if sharded:
+                local = (d_w.view(b, nu, R).sum(1) * float(lr)) if nu > 0 else torch.zeros(b, R, device=z_out.device)
+                w_init = cp.exclusive_sum(local, key, before=True)       # sum over the ranks before this one
+            nv.call("ttcd_ttt_prefix_weights", nv.ptr(d_w if nu > 0 else None), nv.ptr(w_down_c), nv.ptr(w_init),
+                    nv.ptr(states), nv.f32(float(lr)), nv.i32(b), nv.i32(T), nv.i64(R), nv.i32(nu), nv.stream_ptr())
+            del d_w
+            y = gemm(z_out.view(b * T, C, d_i), states.view(b * T, d_h, d_i).transpose(-1, -2)).view(b, T, C, d_h)
+            return y, states, P, last_norm
+
+        y, states, P, last_norm = keep(compute)
         ctx.save_for_backward(z_out, z_tgt, z_hat, beta, wu, states, P)
         ctx.lr, ctx.w_dtype, ctx.wu_dtype = float(lr), w_down.dtype, w_update_t.dtype
+        ctx.cp, ctx.key, ctx.nu = (cp if sharded else None), key, nu
         ctx.mark_non_differentiable(last_norm)
         return y, last_norm
 
@@ -921,17 +989,23 @@ class _TTTScan(torch.autograd.Function):
         z_out, z_tgt, z_hat, beta, wu, states, P = ctx.saved_tensors
         b, T, C, d_i = z_out.shape
         d_h = states.shape[2]
-        nu, R, lr = T - 1, d_h * d_i, ctx.lr
+        nu, R, lr, cp = ctx.nu, d_h * d_i, ctx.lr, ctx.cp
         dy3 = dy.to(_BF16).contiguous().view(b * T, C, d_h)
         dz_out = gemm(dy3, states.view(b * T, d_h, d_i)).view(b, T, C, d_i)
         d_states = gemm(dy3.transpose(-1, -2), z_out.view(b * T, C, d_i), out_dtype=torch.float32)       # [b*T, d_h, d_i]
+        g_init = None
+        if cp is not None:
+            # gradient of this rank's start state = sum_i d_states_i; every earlier rank's summed update fed it
+            d_start = d_states.view(b, T, R).sum(1)
+            g_init = cp.exclusive_sum(d_start, ctx.key, before=False)     # sum over the ranks after this one
         g = torch.empty(b, max(nu, 1), d_h, d_i, dtype=_BF16, device=dy.device)
         d_w_down = torch.empty(d_h, d_i, dtype=torch.float32, device=dy.device)
-        nv.call("ttcd_ttt_suffix_grads", nv.ptr(d_states), nv.ptr(g), nv.ptr(d_w_down), nv.f32(lr), nv.i32(b), nv.i32(T),
-                nv.i64(R), nv.stream_ptr())
+        nv.call("ttcd_ttt_suffix_grads", nv.ptr(d_states), nv.ptr(g), nv.ptr(d_w_down), nv.ptr(g_init), nv.f32(lr),
+                nv.i32(b), nv.i32(T), nv.i64(R), nv.i32(nu), nv.stream_ptr())
         del d_states
-        dz_tgt = torch.zeros_like(z_tgt) if b > 1 or nu == 0 else torch.empty_like(z_tgt)
-        dz_hat = torch.zeros_like(z_hat) if b > 1 or nu == 0 else torch.empty_like(z_hat)
+        fresh = b == 1 and nu > 0              # every row but the never-updating tail is written below
+        dz_tgt = torch.empty_like(z_tgt) if fresh else torch.zeros_like(z_tgt)
+        dz_hat = torch.empty_like(z_hat) if fresh else torch.zeros_like(z_hat)
         d_beta = d_wu = None
         if nu > 0:
             g3 = g.view(b * nu, d_h, d_i)
@@ -940,7 +1014,7 @@ class _TTTScan(torch.autograd.Function):
             if beta is not None:
                 bu = beta[:, :nu].reshape(b * nu, C, 1)
                 d_beta_u = ((dP.float() * P.float()).sum(-1, keepdim=True) / bu.float().clamp_min(1e-20)).to(beta.dtype)
-                d_beta = torch.cat([d_beta_u.view(b, nu, C, 1), torch.zeros_like(beta[:, :1])], dim=1)
+                d_beta = torch.cat([d_beta_u.view(b, nu, C, 1), torch.zeros_like(beta[:, :T - nu])], dim=1)
                 dP = dP * bu.to(_BF16)
             diff = (z_tgt[:, :nu] - z_hat[:, :nu]).reshape(b * nu * C, d_i)
             d_wu = gemm(diff.transpose(-1, -2), dP.view(b * nu * C, d_h)).view(d_i, d_h).to(ctx.wu_dtype)
@@ -949,18 +1023,19 @@ class _TTTScan(torch.autograd.Function):
                 dd = dz_tgt[0, :nu].view(nu, C, d_i)
                 gemm(dP.view(nu * C, d_h), wu.transpose(-1, -2), out=dd.view(1, nu * C, d_i))
                 gemm(P, g3, alpha=1.0, beta=-1.0, c_in=dd, out=dz_hat[0, :nu].view(nu, C, d_i))
-                dz_tgt[0, nu:].zero_()
-                dz_hat[0, nu:].zero_()
+                if nu < T:
+                    dz_tgt[0, nu:].zero_()
+                    dz_hat[0, nu:].zero_()
             else:
                 dd = gemm(dP.view(b * nu * C, d_h), wu.transpose(-1, -2)).view(b * nu, C, d_i)
                 dzh = gemm(P, g3, alpha=1.0, beta=-1.0, c_in=dd)
                 dz_tgt[:, :nu] = dd.view(b, nu, C, d_i)
                 dz_hat[:, :nu] = dzh.view(b, nu, C, d_i)
-        return dz_out, dz_tgt, dz_hat, d_beta, d_w_down.to(ctx.w_dtype), d_wu, None
+        return dz_out, dz_tgt, dz_hat, d_beta, d_w_down.to(ctx.w_dtype), d_wu, None, None, None
 
 
-def ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, lr: float):
+def ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, lr: float, cp=None, key=None):
     """Returns ``(y [b,T,C,d_h], norm of the last chunk update)``; see ``_TTTScan``."""
     for name, t in (("z_out", z_out), ("z_tgt", z_tgt), ("z_hat", z_hat)):
         _check(t, name)
-    return _TTTScan.apply(z_out, z_tgt, z_hat, beta, w_down, w_update_t, float(lr))
+    return _TTTScan.apply(z_out, z_tgt, z_hat, beta, w_down, w_update_t, float(lr), cp, key)

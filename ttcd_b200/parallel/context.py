@@ -49,6 +49,7 @@ class ContextParallel:
         self.window = window
         self.barrier = PeerBarrier(group, slots=4) if (torch.cuda.is_available() and nv.available()) else None
         self.layers: dict[int, _LayerBuffers] = {}
+        self._sum_bufs: dict = {}
         if window is None:
             raise NotImplementedError("context parallelism needs a sliding-window teacher (window_size set)")
 
@@ -76,6 +77,30 @@ class ContextParallel:
 
     def position_offset(self, s_local: int) -> int:
         return self.rank * s_local
+
+    def exclusive_sum(self, x: torch.Tensor, key, before: bool) -> torch.Tensor:
+        """Sum of ``x`` (fp32, same shape on every rank) over the ranks before (``before=True``) or after this one,
+        read straight from the peers' memory by one kernel (fixed order: deterministic); zeros where there is no
+        such rank.  ``key`` names the calling layer: each (key, direction) has its own peer buffer, and the flag
+        barriers around the read make it reusable every step."""
+        from ..comm.symmetric import SymmetricBuffer
+        n = x.numel()
+        slot_key = (key, before, n)
+        buf = self._sum_bufs.get(slot_key)
+        if buf is None:
+            buf = SymmetricBuffer(n * 4, self.group)
+            self._sum_bufs[slot_key] = buf
+        buf.view(torch.float32, n).copy_(x.reshape(-1))
+        self.barrier.sync(slot=3)                    # every rank's contribution is in place
+        out = torch.empty_like(x, dtype=torch.float32)
+        first, count = (0, self.rank) if before else (self.rank + 1, self.size - 1 - self.rank)
+        if count > 0:
+            nv.call("ttcd_peer_sum_f32", nv.ptr(out), buf.ptr_array(), nv.i32(self.size), nv.i64(n), nv.i32(first),
+                    nv.i32(count), nv.stream_ptr())
+        else:
+            out.zero_()
+        self.barrier.sync(slot=3)                    # peers are done reading before the buffer is written again
+        return out
 
 
 import os as _os
@@ -135,7 +160,7 @@ class _CPAttention(torch.autograd.Function):
         nv.call("ttcd_attn_fwd_cp", nv.ptr(qc), nv.ptr(k_sym), nv.ptr(v_sym), nv.i64(kh), nv.i64(vh), nv.ptr(o_t), nv.ptr(o_s),
                 nv.ptr(lse_t), nv.ptr(lse_s), nv.i32(B), nv.i32(S), nv.i32(S), nv.i32(H), nv.i32(HK), nv.i32(D),
                 nv.i64(H * D), nv.i64(ld), nv.i64(ld), nv.i64(S * H * D), nv.i64(sb), nv.i64(sb), nv.i32(halo), nv.i32(S),
-                nv.i32(window_t or 0), nv.i32(window_s or 0), nv.f32(scale), nv.stream_ptr())
+                nv.i32(window_t or 0), nv.i32(window_s or 0), nv.f32(scale), nv.ptr(None), nv.stream_ptr())
         ctx.save_for_backward(qc, o_t, o_s, lse_t, lse_s)
         ctx.cfg = (window_t, window_s, scale, dual, cp, layer_idx, halo)
         ctx.mark_non_differentiable(lse_t)
@@ -159,37 +184,21 @@ class _CPAttention(torch.autograd.Function):
         if dual:
             do_s = (grads[1] if grads[1] is not None else torch.zeros_like(o_s)).contiguous()
 
-        def delta(o, d_o):
-            out = torch.empty(B, H, S, dtype=torch.float32, device=qc.device)
-            nv.call("ttcd_attn_delta", nv.ptr(o), nv.ptr(d_o), nv.ptr(out), nv.i64(B), nv.i32(S), nv.i32(H), nv.i32(D),
-                    nv.stream_ptr())
-            return out
-
         from ..ops import cuda as _cuda
-        if dual and _cuda._BWD_COMBINE and nv.has("ttcd_attn_bwd_combine"):
-            # one-softmax dual backward (see ops.cuda.attn_backward): delta_T, delta' and dO' from one kernel
-            delta_t = torch.empty(B, H, S, dtype=torch.float32, device=qc.device)
-            delta_s = None
-            delta_comb = torch.empty_like(delta_t)
-            do_comb = torch.empty_like(do_t)
-            nv.call("ttcd_attn_bwd_combine", nv.ptr(o_t), nv.ptr(do_t), nv.ptr(o_s), nv.ptr(do_s), nv.ptr(lse_t),
-                    nv.ptr(lse_s), nv.ptr(delta_t), nv.ptr(delta_comb), nv.ptr(do_comb), nv.i64(B), nv.i32(S), nv.i32(H),
-                    nv.i32(D), nv.stream_ptr())
-            nv.call("ttcd_attn_bwd_set_combined", nv.ptr(do_comb), nv.ptr(delta_comb))
-        else:
-            delta_t = delta(o_t, do_t)
-            delta_s = delta(o_s, do_s) if dual else None
+        # row statistics; dual window: delta_T, delta' and dO' from one kernel (see ops.cuda.attn_backward_streams)
+        delta_t, do_c, delta_c = _cuda.attn_backward_streams(o_t, o_s, lse_t, lse_s, do_t, do_s)
         # the halo keys/values were copied into local memory by the forward pass
         kh, vh = lb.halo_ptrs if halo else (0, 0)
         dq = torch.empty_like(qc)
         dk_ext = torch.empty(B, halo + S, HK, D, dtype=torch.bfloat16, device=qc.device)
         dv_ext = torch.empty_like(dk_ext)
         ld, sb = HK * D, S * HK * D
-        nv.call("ttcd_attn_bwd_cp", nv.ptr(qc), nv.ptr(k_sym), nv.ptr(v_sym), nv.i64(kh), nv.i64(vh), nv.ptr(do_t), nv.ptr(do_s),
-                nv.ptr(lse_t), nv.ptr(lse_s), nv.ptr(delta_t), nv.ptr(delta_s), nv.ptr(dq), nv.ptr(dk_ext), nv.ptr(dv_ext),
+        nv.call("ttcd_attn_bwd_cp", nv.ptr(qc), nv.ptr(k_sym), nv.ptr(v_sym), nv.i64(kh), nv.i64(vh), nv.ptr(do_t), nv.ptr(do_c),
+                nv.ptr(lse_t), nv.ptr(delta_t), nv.ptr(delta_c), nv.ptr(dq), nv.ptr(dk_ext), nv.ptr(dv_ext),
                 nv.i32(B), nv.i32(S), nv.i32(S), nv.i32(H), nv.i32(HK), nv.i32(D), nv.i64(H * D), nv.i64(ld), nv.i64(ld),
-                nv.i64(S * H * D), nv.i64(sb), nv.i64(sb), nv.i32(halo), nv.i32(S), nv.i32(window_t or 0),
-                nv.i32(window_s or 0), nv.f32(scale), nv.stream_ptr())
+                nv.i64(S * H * D), nv.i64(sb), nv.i64(sb), nv.i64(0), nv.i64(0), nv.i32(halo), nv.i32(S),
+                nv.i32(window_t or 0), nv.i32(window_s or 0), nv.f32(scale), nv.ptr(None), nv.ptr(None), nv.i32(0),
+                nv.stream_ptr())
         dk = dk_ext[:, halo:].contiguous()
         dv = dv_ext[:, halo:].contiguous()
         # hand the halo part back to its owner: publish it, then every rank pulls from its successor

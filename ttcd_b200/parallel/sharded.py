@@ -9,12 +9,18 @@ to free its bf16 weights between uses, so this runtime is organised around that:
   module parameters are views into it, laid out in registration order so that q/k/v and gate/up
   weights are contiguous slabs (one GEMM each);
 * a **flat bf16 gradient buffer** per group receives autograd's accumulation in place;
-* each rank owns a contiguous 1/world **fp32 master shard** with its Adam moments; after backward the
-  group's gradient is cast/scaled to fp32 and reduce-scattered (overlapped with the remaining
-  backward on a side stream), the fused AdamW kernel updates the shard and writes the new bf16
-  values straight into the owner's slice of the flat parameter buffer, and an all-gather publishes
-  them (overlapped with the next group's update);
-* gradient clipping uses device-side squared norms and a device-side coefficient: no host sync.
+* each rank owns a contiguous 1/world **fp32 master shard** with its Adam moments.  Default transport
+  (``comm='peer'``): the flat buffers live in peer-addressable memory; after a group's backward a flag barrier
+  and ONE kernel pull this rank's shard of the gradients from every peer over NVLink, fused with the bf16->fp32
+  cast, the 1/world scale and the squared-norm partial (overlapped with the remaining backward on a side
+  stream); the fused AdamW kernel then stores the new bf16 values straight into every peer's flat parameter
+  buffer.  ``comm='nccl'`` is the baseline: cast/scale kernel + ``reduce_scatter_tensor``, AdamW, and
+  ``all_gather_into_tensor`` of the updated slices;
+* gradient clipping uses device-side squared norms and a device-side coefficient: no host sync;
+* a peer wait that runs out (a rank more than the wait budget late) sets a device-side word that every rank's
+  optimizer kernels of that step honour (the step is skipped everywhere, agreed through the gradient-norm
+  all-reduce), and ``check_health()`` turns it into an exception at the next point that already synchronises;
+* with gradient accumulation the reduction runs once, after the last micro-batch (``set_last_microbatch``).
 
 ``world_size == 1`` degenerates to flat buffers + fused AdamW with no communication.
 """
@@ -65,10 +71,18 @@ class ShardedDataParallel:
                  process_group: dist.ProcessGroup | None = None, *, lr: float = 1e-4, betas=(0.9, 0.95),
                  eps: float = 1e-8, weight_decay: float = 0.1, max_norm: float | None = 1.0,
                  param_dtype: torch.dtype = torch.bfloat16, overlap: bool = True, comm: str | None = None,
-                 muon: bool = False, muon_momentum: float = 0.95, muon_filter=None):
+                 muon: bool = False, muon_momentum: float = 0.95, muon_filter=None, peer_wait_ns: int = 0,
+                 replicate_group: dist.ProcessGroup | None = None):
         """``comm``: 'peer' = fused peer-memory kernels over NVLink (default on CUDA with the native
-        library), 'nccl' = the NCCL reduce-scatter / all-gather baseline (also TTCD_COMM=nccl)."""
+        library), 'nccl' = the NCCL reduce-scatter / all-gather baseline (also TTCD_COMM=nccl).
+        ``peer_wait_ns``: budget of one peer-flag wait (0: the library default of 10 s).
+        ``replicate_group``: hybrid sharding (the reference's HSDP mesh, flame/models/parallelize_fla.py:75-78):
+        ``process_group`` shards the optimizer state, and the ranks of ``replicate_group`` (one per shard group,
+        holding the same shard) average their reduced gradient shards with an all-reduce before the update."""
         import os
+        self.replicate_pg = replicate_group
+        self.replicate_world = dist.get_world_size(replicate_group) if replicate_group is not None else 1
+        self.peer_wait_ns = int(peer_wait_ns or os.environ.get("TTCD_PEER_WAIT_NS", "0"))
         self.model = model
         self.comm = comm or os.environ.get("TTCD_COMM", "peer")
         self.pg = process_group
@@ -88,10 +102,15 @@ class ShardedDataParallel:
         self.norm_sq_hook = None
         self.muon_params: list = []
         self.sym_params = self.sym_grads = self.barrier = None
+        # [sum of squared gradients, "a peer wait ran out" (set by the barrier kernel)]: all-reduced together
+        self._stats = torch.zeros(2, dtype=torch.float32, device=self.device)
         self.groups: list[ParamGroup] = []
         self._build_groups(blocks)
         self.comm_stream = torch.cuda.Stream() if (self.device.type == "cuda" and self.world > 1) else None
-        self._norm_sq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._norm_sq = self._stats[0:1]
+        self._fail = self._stats[1:2]
+        self._last_microbatch = True
+        self._failed_steps = torch.zeros(1, dtype=torch.float32, device=self.device)   # steps skipped after a wait ran out
         self._coef = torch.ones(1, dtype=torch.float32, device=self.device)
         self._skip = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.last_grad_norm: torch.Tensor | None = None
@@ -150,7 +169,7 @@ class ShardedDataParallel:
             esize = torch.empty((), dtype=self.param_dtype).element_size()
             self.sym_params = SymmetricBuffer(total * esize, self.pg, self.device)
             self.sym_grads = SymmetricBuffer(total * esize, self.pg, self.device)
-            self.barrier = PeerBarrier(self.pg, slots=4)
+            self.barrier = PeerBarrier(self.pg, slots=4, wait_ns=self.peer_wait_ns, fail=self._stats[1:2])
         base = 0
         for g in groups:
             g.base = base
@@ -229,9 +248,15 @@ class ShardedDataParallel:
             g.pending_hooks += 1
             if g.pending_hooks == n_params:
                 g.pending_hooks = 0
-                if self.overlap:
+                if self.overlap and self._last_microbatch:
                     self._reduce_group(g)
         return hook
+
+    def set_last_microbatch(self, last: bool) -> None:
+        """Gradient accumulation: call with False before every micro-batch but the last one.  The flat gradient
+        buffers accumulate locally and the reduction (which also takes the gradient norm) runs once, from the
+        hooks of the last micro-batch or from ``step``."""
+        self._last_microbatch = bool(last)
 
     def _reduce_group(self, g: ParamGroup):
         """Gradient reduce-scatter of one group into this rank's fp32 shard, on the side stream.
@@ -289,8 +314,9 @@ class ShardedDataParallel:
 
     # ---------------------------------------------------------------------------------- step
     def zero_grad(self):
+        self._last_microbatch = True
         if self.peer:
-            self._norm_sq.zero_()
+            self._norm_sq.zero_()       # the reduce kernels add into it; the fail word next to it is cleared in step()
         for g in self.groups:
             g.flat_grad.zero_()
             g.reduce_event = None
@@ -337,9 +363,19 @@ class ShardedDataParallel:
             for mp in self.muon_params:
                 n = mp.param.numel()
                 mp.grad32[:n].copy_(self.groups[mp.group_index].flat_grad[mp.offset:mp.offset + n])
-        # ---- global grad norm (device side); in peer mode the reduce kernels already accumulated it
         owned = [mp for mp in self.muon_params if mp.owner == self.rank]
-        if self.peer:
+        hybrid = self.replicate_world > 1
+        if hybrid:
+            # hybrid sharding: the ranks that hold the same shard in different shard groups average it
+            for g in self.groups:
+                grad = self._local_grad(g)
+                dist.all_reduce(grad, group=self.replicate_pg)
+                grad.mul_(1.0 / self.replicate_world)
+            for mp in owned:
+                dist.all_reduce(mp.grad32, group=self.replicate_pg)
+                mp.grad32.mul_(1.0 / self.replicate_world)
+        # ---- global grad norm (device side); in peer mode the reduce kernels already accumulated it
+        if self.peer and not hybrid:
             pass
         elif self.use_native:
             self._norm_sq.zero_()
@@ -355,7 +391,8 @@ class ShardedDataParallel:
             for mp in owned:
                 self._norm_sq += mp.grad32.pow(2).sum()
         if self.world > 1:
-            dist.all_reduce(self._norm_sq, group=self.pg)
+            # the "a wait ran out" word travels with the norm, so that every rank takes the same decision
+            dist.all_reduce(self._stats if self.peer else self._norm_sq, group=self.pg)
         if self.norm_sq_hook is not None:      # e.g. tensor parallelism: add the other ranks' weight shards
             self.norm_sq_hook(self._norm_sq)
         norm = self._norm_sq.sqrt()
@@ -364,7 +401,13 @@ class ShardedDataParallel:
             torch.clamp(self.max_norm / (norm + 1e-6), max=1.0, out=self._coef)
         else:
             self._coef.fill_(1.0)
-        if self.skip_nan_inf:
+        if self.peer:
+            failed = self._fail > 0
+            self._failed_steps += failed.to(torch.float32)
+            bad = failed | ~torch.isfinite(norm) if self.skip_nan_inf else failed
+            self._skip.copy_(bad.to(torch.int32))
+            self._fail.zero_()          # from here on the word collects the waits of the step's closing barrier
+        elif self.skip_nan_inf:
             self._skip.copy_((~torch.isfinite(norm)).to(torch.int32))
         b1, b2 = self.betas
         for g in self.groups:
@@ -378,8 +421,7 @@ class ShardedDataParallel:
                              _native.ptr(g.exp_avg_sq), self.sym_params.ptr_array(), _native.i32(self.world),
                              _native.i64(g.base + lo), _native.i64(shard), _native.f32(lr), _native.f32(b1), _native.f32(b2),
                              _native.f32(self.eps), _native.f32(self.weight_decay), _native.f32(bc1), _native.f32(bc2_sqrt),
-                             _native.ptr(self._coef), _native.ptr(self._skip if self.skip_nan_inf else None),
-                             _native.stream_ptr())
+                             _native.ptr(self._coef), _native.ptr(self._skip), _native.stream_ptr())
                 continue
             if self.use_native:
                 from ..ops import cuda
@@ -422,7 +464,7 @@ class ShardedDataParallel:
                 saved = mp.grad32
                 mp.grad32 = saved[:n]
                 muon_update(mp, lr, self.weight_decay, self.muon_momentum, coef,
-                            skip=self._skip if self.skip_nan_inf else None)
+                            skip=self._skip if (self.skip_nan_inf or self.peer) else None)
                 mp.grad32 = saved
                 if self.peer:
                     n8 = n // 8 * 8
@@ -435,6 +477,23 @@ class ShardedDataParallel:
             if self.world > 1 and not self.peer:
                 src = dist.get_global_rank(self.pg, mp.owner) if self.pg is not None else mp.owner
                 dist.broadcast(dst, src=src, group=self.pg)
+
+    def check_health(self) -> None:
+        """Raise if a bounded device-side wait ran out since the last check (a peer was later than the wait budget,
+        or a kernel's own pipeline stalled).  Synchronises the device: call it where the host already waits (a
+        logging step, before a checkpoint).  The steps in question were skipped on every rank, so the weights
+        are still consistent when this raises."""
+        if self.device.type != "cuda" or not self.use_native:
+            return
+        torch.cuda.synchronize(self.device)
+        code = _native.device_status()
+        skipped = int(self._failed_steps.item())
+        pending = float(self._fail.item()) > 0
+        if code or skipped or pending:
+            self._failed_steps.zero_()
+            who = f"peer rank {code - 500} never arrived" if 500 <= code < 500 + 64 else f"code {code}"
+            raise RuntimeError(f"rank {self.rank}: a bounded device wait ran out ({who}); {skipped} optimizer step(s) were "
+                               "skipped on every rank, the weights are unchanged by them")
 
     # ---------------------------------------------------------------------------------- state
     def optimizer_state_dict(self) -> dict:

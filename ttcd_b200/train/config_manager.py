@@ -221,3 +221,28 @@ class JobConfig:
         assert self.activation_checkpoint.mode in {"none", "selective", "full"}
         assert self.checkpoint.async_mode in {"disabled", "async", "async_with_pinned_mem"}
         assert self.lr_scheduler.decay_type in {"linear", "sqrt", "cosine"}
+        self._refuse_unsupported()
+
+    # Flags of the reference trainer that select machinery this framework does not have.  They parse (scripts that
+    # pass their defaults keep working) but a non-default value is an error rather than a silent no-op.
+    UNSUPPORTED = {
+        "optimizer.early_step_in_backward": "the optimizer step runs after backward, fused with the parameter publication",
+        "training.enable_cpu_offload": "optimizer state stays in device memory (180 GB per GPU)",
+        "training.enable_expert_parallel": "no mixture-of-experts model is built",
+        "training.compile": "there is no tracing compiler on the hot path; the fusions are hand-written kernels",
+        "experimental.enable_compiled_autograd": "there is no tracing compiler on the hot path",
+        "memory_estimation.enabled": "no fake-mode memory estimator is built",
+        "fault_tolerance.enable": "replica-group fault tolerance (torchft) is not built",
+        "float8.enable_fsdp_float8_all_gather": "float8 training is not built",
+        "float8.precompute_float8_dynamic_scale_for_fsdp": "float8 training is not built",
+        "float8.force_recompute_fp8_weight_in_bwd": "float8 training is not built",
+        "float8.recipe_name": "float8 training is not built",
+        "model.converters": "model converters (float8) are not built",
+    }
+
+    def _refuse_unsupported(self) -> None:
+        for key, why in self.UNSUPPORTED.items():
+            section, name = key.split(".", 1)
+            value = getattr(getattr(self, section), name)
+            if value not in (False, None, [], ""):
+                raise NotImplementedError(f"--{key} is not supported: {why}")

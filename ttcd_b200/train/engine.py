@@ -26,8 +26,9 @@ class EngineConfig:
     weight_decay: float = 0.1
     max_norm: float | None = 1.0
     replicate: bool = False                   # DDP-style replicated optimizer state + gradient all-reduce (fallback path)
+    replicate_degree: int = 1                 # hybrid sharding: this many shard groups, gradients averaged across them
     activation_offload: bool = False          # saved activations -> pinned host memory on a side stream
-    activation_checkpoint: str = "full"       # full | none | everyN (checkpoint every Nth block) | ttt (TTT blocks only)
+    activation_checkpoint: str = "full"       # full | none | everyN (every Nth block) | ttt (TTT blocks only) | op (cheap ops only)
     dtype: torch.dtype = torch.bfloat16
     skip_nan_inf: bool = False
     seed: int = 42
@@ -104,6 +105,25 @@ class TrainEngine:
                     if rank % self.tp.world == t:
                         process_group = g
                 self._tp_dp = True
+        extra = {}
+        if self.cfg.replicate_degree > 1 and not self.cfg.replicate:
+            # hybrid sharding (replicate x shard): rank = r * S + s; a shard group holds the ranks with the same r,
+            # a replicate group the ranks with the same s
+            if self.tp is not None or getattr(self, "cp", None) is not None:
+                raise NotImplementedError("hybrid sharding is not combined with tensor or context parallelism")
+            world, rank = dist.get_world_size(), dist.get_rank()
+            R = self.cfg.replicate_degree
+            if world % R:
+                raise ValueError(f"world size {world} is not divisible by the replicate degree {R}")
+            S = world // R
+            for r in range(R):
+                g = dist.new_group(list(range(r * S, (r + 1) * S)))
+                if rank // S == r:
+                    process_group = g
+            for s_ in range(S):
+                g = dist.new_group(list(range(s_, world, S)))
+                if rank % S == s_:
+                    extra["replicate_group"] = g
         multi = process_group is not False and dist.is_initialized() and dist.get_world_size(process_group) > 1
         runtime = ShardedDataParallel
         if self.cfg.replicate and multi:
@@ -112,19 +132,22 @@ class TrainEngine:
             self.model, blocks=list(self.model.model.layers), process_group=process_group if multi else False,
             lr=self.cfg.lr, betas=self.cfg.betas, eps=self.cfg.eps, weight_decay=self.cfg.weight_decay,
             max_norm=self.cfg.max_norm, param_dtype=self.cfg.dtype, muon=self.cfg.enable_muon,
-            muon_momentum=self.cfg.muon_momentum)
+            muon_momentum=self.cfg.muon_momentum, **extra)
         self.sdp.skip_nan_inf = self.cfg.skip_nan_inf
         if self.tp is not None:
             self.sdp.norm_sq_hook = self._tp_norm_sq
         self.world = self.sdp.world
         self._dev_ids = None
         self.last_loss: torch.Tensor | None = None
+        self.last_logits: torch.Tensor | None = None      # detached logits of the last micro-batch, when the model makes them
+        self.last_labels: torch.Tensor | None = None
         self.tokens_seen = 0
 
     # ------------------------------------------------------------------------------------------
     def set_activation_checkpointing(self, mode: str) -> None:
         """'full' recomputes every block in backward (the reference recipe, sized for 80 GB GPUs);
-        'ttt' recomputes only the fast-weight blocks; 'everyN' every Nth block; 'none' keeps all
+        'ttt' recomputes only the fast-weight blocks; 'everyN' every Nth block; 'op' recomputes the norm / rotary /
+        SwiGLU / conv work of every block but keeps its GEMM and attention outputs; 'none' keeps all
         activations resident (fits at 64K tokens on a 180 GB B200)."""
         inner = self.model.model
         inner.gradient_checkpointing = mode != "none"
@@ -149,6 +172,9 @@ class TrainEngine:
         with get_act_offloading_ctx_manager(self.cfg.activation_offload and self.device.type == "cuda"):
             out = self.model(input_ids=ids, labels=lab, **model_kwargs)
             loss = out.loss
+        logits = getattr(out, "logits", None)
+        self.last_logits = None if logits is None else logits.detach()
+        self.last_labels = lab if logits is not None else None
         (loss * scale if scale != 1.0 else loss).backward()
         self.tokens_seen += ids.numel()
         return loss.detach()

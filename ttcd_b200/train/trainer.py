@@ -142,7 +142,11 @@ def _ac_mode(job_config) -> str:
     if ac.mode == "full":
         return "full"
     opt = str(ac.selective_ac_option)
-    return f"every{int(opt)}" if opt.isdigit() else "full"
+    if opt.isdigit():
+        return f"every{int(opt)}"
+    if opt == "op":
+        return "op"          # recompute the cheap ops, keep the GEMM / attention outputs (ops/selective.py)
+    raise ValueError(f"--activation_checkpoint.selective_ac_option must be an integer or 'op', got {opt!r}")
 
 
 def main(job_config: JobConfig) -> None:
@@ -199,7 +203,9 @@ def main(job_config: JobConfig) -> None:
                         skip_nan_inf=tr.skip_nan_inf, seed=tr.seed, enable_muon=opt.enable_muon,
                         muon_momentum=opt.muon_momentum, tensor_parallel=tp, context_parallel=cp,
                         activation_offload=job_config.activation_offload.mode not in ("none", "", None),
-                        replicate=(tr.data_parallel_shard_degree == 1 and tr.data_parallel_replicate_degree not in (0, 1)))
+                        replicate=(tr.data_parallel_shard_degree == 1 and tr.data_parallel_replicate_degree not in (0, 1)),
+                        replicate_degree=(tr.data_parallel_replicate_degree
+                                          if tr.data_parallel_shard_degree != 1 and tr.data_parallel_replicate_degree > 1 else 1))
     engine = TrainEngine(model_config, ecfg, device=device)
     model = engine.model
     n_params = count_params(model, exclude_embedding=True)
@@ -235,7 +241,8 @@ def main(job_config: JobConfig) -> None:
             gc.collect(1)
         engine.sdp.zero_grad()
         losses = []
-        for _ in range(accum):
+        for micro in range(accum):
+            engine.sdp.set_last_microbatch(micro == accum - 1)
             t0 = time.perf_counter()
             batch = next(data_iter)
             metrics.data_loading_times.append(time.perf_counter() - t0)
@@ -255,17 +262,23 @@ def main(job_config: JobConfig) -> None:
             train_state.skipped_step += 1
             logger.warning(f"step {step}: non-finite gradient norm, optimizer step skipped")
         if metrics.should_log(step):
+            engine.sdp.check_health()          # a bounded device wait that ran out since the last log raises here
             avg, mx = dist_mean_max(loss)
             extra = {"optimizer/lr": schedule.lr(step - 1), "optimizer/grad_norm": float(grad_norm),
                      "optimizer/skipped_step": train_state.skipped_step}
             if hasattr(model, "get_ttt_norm_metrics"):
                 extra.update(model.get_ttt_norm_metrics())
+            if engine.last_logits is not None:     # only when the model materialises logits (no fused linear-CE)
+                extra.update(loss_by_position(engine.last_logits, engine.last_labels))
             train_state.log_steps.append(step)
             train_state.global_avg_losses.append(avg)
             train_state.global_max_losses.append(mx)
             train_state.elapsed = time.perf_counter() - t_start
             metrics.log(step, avg, mx, extra)
-        ckpt.save(step, last=step == tr.steps, force=external_save_requested(rank))
+        force_save = external_save_requested(rank)
+        if ckpt.should_save(step, last=step == tr.steps, force=force_save):
+            engine.sdp.check_health()          # never write weights of a run whose device-side waits ran out
+        ckpt.save(step, last=step == tr.steps, force=force_save)
         if profiler is not None:
             profiler.step()
         snapshotter.step(step)
