@@ -63,7 +63,7 @@ def main():
     q, k, v = mk(S, H), mk(S, HK), mk(S, HK)
     if args.bwd:
         def whole():
-            o_t, o_s, _, _ = cuda._Attention.apply(q, k, v, args.wt, args.ws, sc, True)
+            o_t, o_s, _, _ = cuda._Attention.apply(q, k, v, args.wt, args.ws, sc, True, None, None)
             torch.autograd.grad([o_t, o_s], [q, k, v], [o_t, o_s])
     else:
         def whole():

@@ -5,7 +5,13 @@ write) between timed iterations, and is reported with the achieved fraction of t
 in MEASURED_PEAKS.json (cuBLAS bf16 burst throughput and copy bandwidth).  Library baselines
 (cuBLAS via torch.matmul, flash-attn 2) are timed the same way when importable.
 
-    python benchmarks/bench_kernels.py [--what gemm,attn,conv,attn_bwd,misc] [--seq 65536] [--batch 1]
+    python benchmarks/bench_kernels.py [--what gemm,attn,conv,attn_bwd,misc,ref] [--seq 65536] [--batch 1]
+
+``--what ref`` times the reference project's own kernels on this GPU next to this library's: its fused dual-window
+Triton kernel (profiling/fused_dual_attn.py:244-272), its LSE-combination variant on flash-attn 2
+(profiling/lse_dual_attn.py:16-39), two flash-attn calls, and its Triton chunked depthwise conv
+(profiling/fused_conv.py:51-61) against the cuDNN path.  They are imported, unmodified, from the reference checkout
+(``TTCD_REFERENCE_ROOT``, a ``reference`` directory beside this repository, or ``baseline/_ref``).
 """
 from __future__ import annotations
 
@@ -125,12 +131,12 @@ def bench_attn(seqs, batches, wt=8192, ws=4096, bwd=False):
                     row.update(fa2_teacher_ms=round(ms_fa_t, 3), fa2_two_calls_ms=round(ms_fa_t + ms_fa_s, 3),
                                speedup_vs_fa2_two_calls=round((ms_fa_t + ms_fa_s) / ms_dual, 2))
             else:
-                o_t, o_s, _, _ = cuda._Attention.apply(q, k, v, wt, ws, sc, True)
+                o_t, o_s, _, _ = cuda._Attention.apply(q, k, v, wt, ws, sc, True, None, None)
                 g_t, g_s = torch.randn_like(o_t), torch.randn_like(o_s)
                 ms = timeit(lambda: torch.autograd.grad([o_t, o_s], [q, k, v], [g_t, g_s], retain_graph=True), iters=5)
                 fl = 2.5 * attn_flops(B, T, H, D, wt) + 2.5 * attn_flops(B, T, H, D, ws)  # two separate backward passes
                 row.update(fused_dual_bwd_ms=round(ms, 3), tflops=round(fl / ms / 1e9, 1))
-                o1, _ = cuda._Attention.apply(q, k, v, wt, wt, sc, False)
+                o1, _ = cuda._Attention.apply(q, k, v, wt, wt, sc, False, None, None)
                 ms1 = timeit(lambda: torch.autograd.grad([o1], [q, k, v], [g_t], retain_graph=True), iters=5)
                 fl1 = 2.5 * attn_flops(B, T, H, D, wt)  # algorithmic: 5 GEMMs
                 row.update(single_window_bwd_ms=round(ms1, 3), single_tflops=round(fl1 / ms1 / 1e9, 1),
@@ -244,6 +250,83 @@ def bench_misc():
          bwd_ms=round(ms_b, 4), peak_source=src)
 
 
+def _reference_profiling():
+    """The reference checkout's ``profiling`` directory on sys.path; returns it, or None when it is not there."""
+    import os
+    cands = [os.environ.get("TTCD_REFERENCE_ROOT"), str(ROOT.parent / "reference"), str(ROOT / "baseline" / "_ref")]
+    for c in cands:
+        if c and (Path(c) / "profiling" / "fused_dual_attn.py").is_file():
+            if c not in sys.path:
+                sys.path.insert(0, c)
+            return Path(c)
+    return None
+
+
+def bench_reference(seqs, batches, wt=8192, ws=4096):
+    """The reference's kernels, run on this GPU, beside this library's (same inputs, same timing)."""
+    root = _reference_profiling()
+    if root is None:
+        emit(bench="reference", error="reference checkout with profiling/ not found")
+        return
+    from profiling.fused_dual_attn import fused_dual_window_attn
+    from profiling.lse_dual_attn import lse_dual_window_attn
+    from profiling.fused_conv import causal_dwconv_chunked
+    fa = _flash()
+    H, HK, D = 16, 8, 128
+    sc = D ** -0.5
+    for B in batches:
+        for T in seqs:
+            q = torch.randn(B, T, H, D, device="cuda", dtype=BF)
+            k = torch.randn(B, T, HK, D, device="cuda", dtype=BF)
+            v = torch.randn(B, T, HK, D, device="cuda", dtype=BF)
+            row = dict(bench="reference_attn_fwd", B=B, T=T, w_t=wt, w_s=ws)
+            with torch.no_grad():
+                ours = timeit(lambda: cuda.attn_forward(q, k, v, wt, ws, sc, True))
+                row["ours_fused_ms"] = round(ours, 3)
+                try:
+                    o_ref = fused_dual_window_attn(q, k, v, wt, ws)
+                    row["ref_triton_fused_ms"] = round(timeit(lambda: fused_dual_window_attn(q, k, v, wt, ws)), 3)
+                    o_t = cuda.attn_forward(q, k, v, wt, ws, sc, True)[1]
+                    row["max_abs_diff_vs_ref_teacher"] = round(float((o_t.float() - o_ref[0].float()).abs().max()), 5)
+                except Exception as exc:
+                    row["ref_triton_fused_error"] = f"{type(exc).__name__}: {exc}"[:160]
+                try:
+                    row["ref_lse_fa2_ms"] = round(timeit(lambda: lse_dual_window_attn(q, k, v, wt, ws)), 3)
+                except Exception as exc:
+                    row["ref_lse_fa2_error"] = f"{type(exc).__name__}: {exc}"[:160]
+                if fa is not None:
+                    ms_t = timeit(lambda: fa(q, k, v, causal=True, window_size=(wt - 1, 0)))
+                    ms_s = timeit(lambda: fa(q, k, v, causal=True, window_size=(ws - 1, 0)))
+                    row["ref_two_fa2_calls_ms"] = round(ms_t + ms_s, 3)
+            best = min(v_ for k_, v_ in row.items() if k_.startswith("ref_") and k_.endswith("_ms"))
+            row["speedup_vs_best_reference"] = round(best / ours, 2)
+            emit(**row)
+            del q, k, v
+            torch.cuda.empty_cache()
+    for K in (5, 4):
+        for B in batches:
+            x = torch.randn(B, 16, 4096, 3072, device="cuda", dtype=BF)
+            conv = torch.nn.Conv1d(3072, 3072, K, groups=3072, bias=False, device="cuda", dtype=BF)
+            w = conv.weight.detach().view(3072, K).contiguous()
+            row = dict(bench="reference_dwconv_fwd", K=K, shape=list(x.shape))
+            with torch.no_grad():
+                row["ours_ms"] = round(timeit(lambda: cuda.dwconv_chunked(x, w, True)), 4)
+                try:
+                    y_ref = causal_dwconv_chunked(x, conv)
+                    row["ref_triton_ms"] = round(timeit(lambda: causal_dwconv_chunked(x, conv)), 4)
+                    row["max_abs_diff_vs_ref"] = round(float((cuda.dwconv_chunked(x, w, True).float() - y_ref.float()).abs().max()), 5)
+                except Exception as exc:
+                    row["ref_triton_error"] = f"{type(exc).__name__}: {exc}"[:160]
+
+                def cudnn_path():                    # the reference's training path (modeling_ipttcdv9.py:203-211)
+                    xf = x.view(B * 16, 4096, 3072).transpose(1, 2)
+                    return conv(torch.nn.functional.pad(xf, (K - 1, 0))).transpose(1, 2)
+                row["ref_cudnn_path_ms"] = round(timeit(cudnn_path), 4)
+            emit(**row)
+            del x
+            torch.cuda.empty_cache()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--what", default="gemm,attn,conv")
@@ -264,6 +347,8 @@ def main():
         bench_conv()
     if "misc" in what:
         bench_misc()
+    if "ref" in what:
+        bench_reference(seqs, batches)
     st = _native.device_status()
     if st:
         emit(error=f"device status {st}")

@@ -65,6 +65,88 @@ def check_sharded_modes(muon: bool = False):
     assert lp[-1] < lp[0] + 0.5, lp
 
 
+def _small_engine(**over):
+    from ttcd_b200.models import IPTTCDv9Config
+    from ttcd_b200.train.engine import EngineConfig, TrainEngine
+    cfg = IPTTCDv9Config(hidden_size=256, num_hidden_layers=2, num_heads=4, num_kv_heads=2, head_dim=64, intermediate_size=768,
+                         vocab_size=4096, window_size=256, max_position_embeddings=2048, ttt_mode=True, ttt_chunk=128,
+                         ttt_layers=[1], ttt_update_every=4, qk_norm=True, tie_word_embeddings=True, fuse_cross_entropy=False,
+                         fuse_linear_cross_entropy=True, ttt_teacher_conv_init="identity")
+    kw = dict(lr=1e-3, seed=7, activation_checkpoint="none")
+    kw.update(over)
+    return cfg, TrainEngine(cfg, EngineConfig(**kw), device=f"cuda:{torch.cuda.current_device()}")
+
+
+def check_late_rank_is_detected_and_the_step_skipped():
+    """A rank that is later than the peer-wait budget (a stalled data loader: it sleeps on the host between two
+    steps, with nothing of its own in flight): its peers' flag wait runs out, every rank skips that optimizer step
+    (agreed through the gradient-norm all-reduce), the weights stay identical, ``check_health`` raises on every
+    rank, and training continues afterwards."""
+    import time
+    rank = dist.get_rank()
+    os.environ["TTCD_COMM"] = "peer"
+    os.environ["TTCD_PEER_WAIT_NS"] = "300000000"          # 0.3 s
+    try:
+        cfg, eng = _small_engine()
+    finally:
+        del os.environ["TTCD_PEER_WAIT_NS"]
+    assert eng.sdp.peer and eng.sdp.peer_wait_ns == 300000000
+    g = torch.Generator().manual_seed(100 + rank)
+    batch = lambda: torch.randint(0, cfg.vocab_size, (1, 512), generator=g).cuda()      # noqa: E731
+    eng.train_step(batch())
+    eng.sdp.check_health()                                 # a healthy step raises nothing
+    before = torch.cat([grp.flat_param.float() for grp in eng.sdp.groups]).clone()
+    masters = [grp.master.clone() for grp in eng.sdp.groups]
+    torch.cuda.synchronize()
+    dist.barrier()
+    if rank == 1:
+        time.sleep(1.5)                                    # late by five wait budgets
+    eng.train_step(batch())
+    torch.cuda.synchronize()
+    after = torch.cat([grp.flat_param.float() for grp in eng.sdp.groups])
+    assert torch.equal(before, after), "the step after an expired wait must leave the weights alone"
+    for grp, m in zip(eng.sdp.groups, masters):
+        assert torch.equal(grp.master, m)
+    raised = False
+    try:
+        eng.sdp.check_health()
+    except RuntimeError as exc:
+        raised = True
+        assert "wait ran out" in str(exc), exc
+    assert raised, f"rank {rank}: the expired wait went unnoticed"
+    dist.barrier()
+    loss = eng.train_step(batch())                         # the run goes on
+    eng.sdp.check_health()
+    now = torch.cat([grp.flat_param.float() for grp in eng.sdp.groups])
+    assert not torch.equal(now, before) and loss == loss
+    other = now.clone()
+    dist.broadcast(other, src=0)
+    assert torch.equal(other, now), "parameters differ between ranks after the recovery step"
+
+
+def check_accumulation_on_gpus():
+    """Two micro-batches with the reduction after the last one == one batch of both sequences (norm and weights)."""
+    rank = dist.get_rank()
+    os.environ["TTCD_COMM"] = "peer"
+    g = torch.Generator().manual_seed(300 + rank)
+    cfg, whole = _small_engine(max_norm=0.05)
+    ids = torch.randint(0, cfg.vocab_size, (2, 512), generator=g).cuda()
+    whole.sdp.zero_grad()
+    whole.forward_backward(ids)
+    norm_a = float(whole.sdp.step(1e-3))
+    _, split = _small_engine(max_norm=0.05)
+    split.sdp.zero_grad()
+    for m in range(2):
+        split.sdp.set_last_microbatch(m == 1)
+        split.forward_backward(ids[m:m + 1], scale=0.5)
+    norm_b = float(split.sdp.step(1e-3))
+    assert norm_a > 0.05, norm_a                           # the clip is active, so a wrong norm would change the update
+    assert abs(norm_a - norm_b) < 3e-2 * norm_a, (norm_a, norm_b)
+    fa = torch.cat([grp.flat_param.float() for grp in whole.sdp.groups])
+    fb = torch.cat([grp.flat_param.float() for grp in split.sdp.groups])
+    assert (fa - fb).abs().max().item() < 1e-2, (fa - fb).abs().max().item()
+
+
 def main():
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -82,6 +164,10 @@ def main():
         from tests.multi_gpu_tp import check_tensor_parallel, check_tp_model
         check_tensor_parallel()
         check_tp_model()
+    if what in ("all", "late_rank"):
+        check_late_rank_is_detected_and_the_step_skipped()
+    if what in ("all", "accum"):
+        check_accumulation_on_gpus()
     if what in ("all", "cp"):
         from tests.multi_gpu_cp import check_context_parallel
         check_context_parallel()

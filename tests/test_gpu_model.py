@@ -31,6 +31,8 @@ def _config(**over):
 
 def _cos(a, b):
     a, b = a.float().flatten(), b.float().flatten()
+    if float(a.norm()) == 0.0 and float(b.norm()) == 0.0:
+        return 1.0                                   # e.g. a gate whose input features are zero at initialisation
     return float(torch.dot(a, b) / (a.norm() * b.norm()).clamp_min(1e-30))
 
 

@@ -1,7 +1,8 @@
 """Multi-GPU checks (symmetric memory, flag barrier, fused reduce-scatter / AdamW-push vs the NCCL baseline).
 
 Each test launches one process per GPU with torch.distributed.run and is skipped on machines with fewer
-than two GPUs.  Host-side protocol logic is covered on CPU in tests/test_comm_protocol.py.
+than two GPUs.  Host-side protocol logic is covered on CPU in tests/test_flag_protocol_model.py and
+tests/test_sharded_runtime_cpu.py.
 """
 import os
 import socket
@@ -22,10 +23,10 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _launch(what: str, nproc: int, timeout: int = 600) -> str:
+def _launch(what: str, nproc: int, timeout: int = 600, **extra_env) -> str:
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), str(ROOT / "tests" / "multi_gpu_worker.py"), what]
-    env = dict(os.environ, PYTHONPATH=str(ROOT))
+    env = dict(os.environ, PYTHONPATH=str(ROOT), **extra_env)
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=str(ROOT))
     out = res.stdout + res.stderr
     assert res.returncode == 0 and "MULTI_GPU_OK" in out, out[-4000:]
@@ -59,3 +60,14 @@ def test_fused_allgather_gemm_and_gemm_reducescatter():
 @pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
 def test_context_parallel_halo_attention_matches_single_gpu():
     _launch("cp", 2)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
+def test_late_rank_expires_the_peer_wait_and_every_rank_skips_the_step():
+    # failure-detection runs keep NVLS off: a rank in trouble must not sit on an NVLink multicast object
+    _launch("late_rank", 2, NCCL_NVLS_ENABLE="0")
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
+def test_gradient_accumulation_reduces_once_on_gpus():
+    _launch("accum", 2)
