@@ -49,6 +49,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=16384)
     ap.add_argument("--k", type=int, default=1024)
     ap.add_argument("--n", type=int, default=2048)
+    ap.add_argument("--lag", type=int, default=0, help="gemm_rs: rounds by which own row blocks trail the pushes (0: last)")
     args = ap.parse_args()
     nv.load(required=True)
     w_, m, k, n = args.world, args.tokens // args.world, args.k, args.n
@@ -74,21 +75,27 @@ def main():
         x = (torch.randn(m * w_, k, device="cuda") * 0.5).bfloat16()
         wt = (torch.randn(n, k, device="cuda") * 0.05).bfloat16()
         out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
-        parts = [(torch.randn(m * w_, n, device="cuda") * 0.1).bfloat16() for _ in range(w_)]   # peers' partials: given data
-        nflags = w_ * (m // 128) * (n // 256)
-        flags = [torch.full((nflags,), 1 << 30, device="cuda", dtype=torch.int32) for _ in range(w_)]   # peers: already raised
-        flags[0].zero_()
-        peer_sum = torch.empty(m, n, device="cuda")
-        sum_flags = torch.zeros((m // 128) * (n // 256), device="cuda", dtype=torch.int32)
+        # receive buffers: ours holds the tiles that the peers "pushed" (given data, flags already raised); the peers'
+        # buffers take what this rank pushes for their rows (local memory standing in for the other GPUs)
+        parts = [(torch.randn(m * max(w_ - 1, 1), n, device="cuda") * 0.1).bfloat16() for _ in range(w_)]
+        nflags = max(w_ - 1, 1) * (m // 128) * (n // 256)
+        flags = [torch.zeros(nflags, device="cuda", dtype=torch.int32) for _ in range(w_)]
+        flags[0].fill_(1 << 30)
+        mine = parts[0].clone()
 
         def run():
             epoch[0] += 1
-            nv.call("ttcd_gemm_rs", nv.ptr(x), nv.ptr(wt), nv.ptr(out), ptrs(parts), ptrs(flags), nv.ptr(peer_sum), nv.ptr(sum_flags),
-                    nv.i32(0), nv.i32(w_), nv.i64(m), nv.i64(n), nv.i64(k), nv.i64(k), nv.i64(k), nv.i64(n), nv.i32(0),
-                    nv.i32(epoch[0]), nv.i64(2_000_000_000), nv.stream_ptr())
+            nv.call("ttcd_gemm_rs", nv.ptr(x), nv.ptr(wt), nv.ptr(out), ptrs(parts), ptrs(flags), nv.i32(0), nv.i32(w_), nv.i64(m),
+                    nv.i64(n), nv.i64(k), nv.i64(k), nv.i64(k), nv.i64(n), nv.i32(0), nv.i32(epoch[0]), nv.i64(2_000_000_000),
+                    nv.i32(args.lag), nv.stream_ptr())
         ms = timeit(run)
-        want = x[:m].float() @ wt.float().t() + sum(p[:m].float() for p in parts[1:])
+        want = x[:m].float() @ wt.float().t() + sum(mine[d * m:(d + 1) * m].float() for d in range(w_ - 1))
         err = (out.float() - want).abs().max().item() / want.abs().max().item()
+        # what this rank pushed for the next rank's rows (slot world - 2 of that rank's buffer)
+        if w_ > 1:
+            pushed = parts[1][(w_ - 2) * m:(w_ - 1) * m].float()
+            want_p = x[m:2 * m].float() @ wt.float().t()
+            err = max(err, (pushed - want_p).abs().max().item() / want_p.abs().max().item())
         flops = 2.0 * m * w_ * k * n
     elif args.what == "rs_norm":
         numel = m * k

@@ -42,6 +42,7 @@ def timed(fn, iters=10, warmup=3):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=65536)
+    ap.add_argument("--lags", default="0", help="comma list of gemm_rs lags to time (rounds; 0 = own row blocks last)")
     args = ap.parse_args()
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
@@ -86,12 +87,16 @@ def main():
             dist.reduce_scatter_tensor(out, y)
             return out
 
-        t_f = timed(lambda: tp.gemm_rs(x, w))
+        by_lag = {lag: timed(lambda: tp.gemm_rs(x, w, lag=lag)) for lag in [int(v) for v in args.lags.split(",")]}
+        best_lag = min(by_lag, key=by_lag.get)
+        t_f = by_lag[best_lag]
         t_b = timed(base)
         flops = 2.0 * m * world * kl * n
         link = (world - 1) * m * n * 2 / 770e9 * 1e3
         roof = max(flops / (peak * 1e12) * 1e3, link)
-        rows.append({"op": f"gemm_rs {name}", "M": m * world, "N": n, "K": kl, "fused_ms": round(t_f, 4), "nccl_cublas_ms": round(t_b, 4),
+        rows.append({"op": f"gemm_rs {name}", "M": m * world, "N": n, "K": kl, "lag": best_lag,
+                     "ms_by_lag": {str(k_): round(v_, 4) for k_, v_ in by_lag.items()},
+                     "fused_ms": round(t_f, 4), "nccl_cublas_ms": round(t_b, 4),
                      "speedup": round(t_b / t_f, 3), "roofline_ms": round(roof, 4), "of_roofline": round(roof / t_f, 3)})
     tp.check()
     if rank == 0:

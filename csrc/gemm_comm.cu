@@ -10,12 +10,14 @@
 //              flag is up.  The gathered buffer is left behind for the weight-gradient GEMM.
 //
 //   gemm_rs :  Y_shard[M_shard, N] = reduce_scatter_rows( X[M_total, K_local] * W^T )
-//              Every rank computes the row blocks of the OTHER ranks first and stores them (bf16) in its
-//              symmetric partial buffer with a per-tile release flag; four reducer warps per CTA pull
-//              the peers' partial tiles of this rank's rows as their flags come up and leave the fp32
-//              sum in a local buffer; the rank's own row blocks are computed last and their epilogue
-//              adds that sum and writes the final bf16 output.  No separate reduction pass, no staging
-//              copy, and the NVLink traffic overlaps the tensor-core work of the remaining tiles.
+//              Every rank computes the row blocks of the OTHER ranks first and PUSHES each finished tile
+//              (bf16) straight into its owner's memory: the epilogue warps transpose the tile through
+//              shared memory so that every store instruction writes 512 contiguous bytes of one row over
+//              NVLink (posted writes: no round trip), then raise the tile's flag in the owner's flag array.
+//              The rank's own row blocks are computed last; their epilogue waits for the peers' flags
+//              (local memory), adds the peers' tiles in a fixed order (deterministic) and writes the final
+//              bf16 output.  No separate reduction pass, no pull across the link, and the NVLink traffic
+//              overlaps the tensor-core work of the remaining tiles.
 //
 // Both kernels: persistent, one CTA per SM, 128x256x64 tiles, 3-stage TMA ring (never multicast),
 // tcgen05.mma into a double-buffered TMEM accumulator.  Every wait (mbarrier or flag) is bounded; on
@@ -42,17 +44,15 @@ struct GcPeers {
   void* p[GC_MAX_RANKS];
 };
 
-// Tensor maps over the peers' partial buffers, entry d-1 for the peer (rank + d) % world.
-struct alignas(64) GcPeerMaps {
-  CUtensorMap m[GC_MAX_RANKS - 1];
-};
-constexpr int GC_RS_STAGING = 2 * 64 * GC_BN * 2;   // two 64-row half tiles of bf16
+constexpr int GC_RS_THREADS = 224;                  // producer, MMA issue, four epilogue warps, flag warp
+constexpr int GC_RS_STAGING = 4 * 32 * GC_BN * 2;   // per epilogue warp: 32 rows x 256 bf16 for the transpose
 
 struct GcParams {
   int rank, world, epoch;
   int mbps;            // 128-row blocks per rank shard
   int tiles_n;         // N / 256
   int num_kb;          // K / 64
+  int lag;             // gemm_rs: rounds by which this rank's own row blocks trail the pushes (1..mbps)
   int64_t m_shard, N, K;
   int64_t ldc;         // row stride of the output (elements)
   uint64_t wait_ns;    // budget of one flag wait
@@ -60,10 +60,9 @@ struct GcParams {
   bf16* gathered;      // [world*m_shard, K] local
   int* ready;          // [world*mbps] local flags
   // gemm_rs
-  bf16* partial;       // this rank's symmetric partial buffer [world*m_shard, N]
-  int* part_flags;     // this rank's symmetric flags [world*mbps*tiles_n]
-  float* peer_sum;     // [m_shard, N] local fp32
-  int* sum_flags;      // [mbps*tiles_n] local flags
+  bf16* partial;       // this rank's symmetric receive buffer [(world-1)*m_shard, N]: slot d-1 holds what rank
+                       // (rank + d) % world computed for this rank's rows
+  int* part_flags;     // this rank's symmetric flags [(world-1)*mbps*tiles_n], same slot order
 };
 
 __device__ __forceinline__ void gc_st_release_sys(int* addr, int v) {
@@ -120,13 +119,38 @@ struct GcTile {
   int owner, mb, nt;
   int64_t row0;   // first row in the [world*m_shard] index space
 };
-// Tile t of the persistent schedule.  own_first: the rank's own shard leads (ag_gemm), else trails (gemm_rs).
+// Tile t of the persistent schedule.
+//   own_first (ag_gemm): the rank's own shard leads, then the peers' shards one after the other (their rows arrive
+//   while the own rows are multiplied).
+//   else (gemm_rs): rounds.  Round r holds row block r of every OTHER rank (pushed to its owner) and row block r - lag
+//   of this rank (whose peers' tiles were pushed `lag` rounds earlier, so its epilogue does not wait for them); the
+//   first `lag` rounds only push, the last `lag` rounds only finish own blocks.  lag = mbps puts all own blocks last;
+//   a smaller lag keeps the link busy for more of the kernel.
 __device__ __forceinline__ GcTile gc_tile(int64_t t, const GcParams& p, bool own_first) {
   GcTile c;
   const int64_t mi = t / p.tiles_n;
   c.nt = static_cast<int>(t % p.tiles_n);
-  const int s = static_cast<int>(mi / p.mbps);
-  c.mb = static_cast<int>(mi % p.mbps);
+  int s;
+  if (own_first) {
+    s = static_cast<int>(mi / p.mbps);
+    c.mb = static_cast<int>(mi % p.mbps);
+  } else {
+    const int others = p.world - 1, lag = p.lag;
+    const int64_t head = static_cast<int64_t>(lag) * others;                       // rounds [0, lag): pushes only
+    const int64_t mid = static_cast<int64_t>(p.mbps - lag) * p.world;               // rounds [lag, mbps): pushes + own
+    if (mi < head) {
+      s = static_cast<int>(mi % others);
+      c.mb = static_cast<int>(mi / others);
+    } else if (mi < head + mid) {
+      const int64_t m2 = mi - head;
+      s = static_cast<int>(m2 % p.world);
+      const int round = lag + static_cast<int>(m2 / p.world);
+      c.mb = s < others ? round : round - lag;
+    } else {
+      s = others;
+      c.mb = p.mbps - lag + static_cast<int>(mi - head - mid);
+    }
+  }
   c.owner = (p.rank + s + (own_first ? 0 : 1)) % p.world;
   c.row0 = static_cast<int64_t>(c.owner) * p.m_shard + static_cast<int64_t>(c.mb) * GC_BM;
   return c;
@@ -363,10 +387,9 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tma_own, const __grid_constan
 // GEMM -> reduce-scatter
 // ================================================================================================
 template <bool B_MN>
-__global__ void __launch_bounds__(GC_THREADS, 1)
+__global__ void __launch_bounds__(GC_RS_THREADS, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-               const __grid_constant__ GcPeerMaps peer_maps, const GcPeers peer_flags, bf16* __restrict__ out,
-               const GcParams p) {
+               const GcPeers peer_part, const GcPeers peer_flags, bf16* __restrict__ out, const GcParams p) {
   extern __shared__ uint8_t smem_raw[];
   const GcSmem s = gc_setup<GC_RS_STAGING>(smem_raw);
   const uint32_t tmem_base = *s.tmem_slot;
@@ -399,9 +422,10 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     const int quarter = warp & 3;
     uint32_t acc_phase[2] = {0, 0};
     int acc = 0;
-    int tile_seq = -1;
+    uint8_t* stage = s.base + GC_RING_BYTES + quarter * (32 * GC_BN * 2);     // this warp's 32 x 512-byte rows
+    volatile int* pushed = s.epi_count;      // per epilogue warp: tiles of other ranks whose stores it has issued
+    int n_pushed = 0;
     for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-      ++tile_seq;
       const GcTile c = gc_tile(tile, p, false);
       const bool own = c.owner == p.rank;
       if (!mbar_wait(s.tfull(acc), acc_phase[acc], s.abort_flag, 634)) break;
@@ -409,75 +433,97 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * GC_BN;
       const int64_t col0 = static_cast<int64_t>(c.nt) * GC_BN;
       if (!own) {
-        // another rank's rows: bf16 partial into this rank's symmetric buffer, then the tile's flag
-        bf16* prow = p.partial + (c.row0 + quarter * 32 + lane) * p.N + col0;
+        // another rank's rows.  TMEM lane == row, so a thread holds one row; a store instruction of the warp should
+        // cover one row's 512 contiguous bytes instead (NVLink writes of whole lines): transpose through shared
+        // memory, 16-byte chunk c of row r at chunk position c ^ r (conflict-free both ways)
 #pragma unroll 1
         for (int col = 0; col < GC_BN; col += 32) {
           uint32_t v[32];
           tmem_ld32(t_row + col, v);
           tmem_ld_wait();
-          gc_store_row32(v, prow + col, nullptr);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 o;
+            o.x = pack_bf16(__uint_as_float(v[8 * j]), __uint_as_float(v[8 * j + 1]));
+            o.y = pack_bf16(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+            o.z = pack_bf16(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+            o.w = pack_bf16(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+            const int chunk = col / 8 + j;
+            *reinterpret_cast<uint4*>(stage + lane * 512 + ((chunk ^ lane) & 31) * 16) = o;
+          }
         }
-        // the accumulator is in registers / on its way to memory: hand the TMEM buffer back to the MMA warp
-        // before paying for the system-scope fence of the flag
+        // the accumulator has left TMEM: hand the buffer back to the MMA warp before the remote stores
         tc_fence_before_sync();
         __syncwarp();
+        if (lane == 0) mbar_arrive(s.tempty(acc));
+        const int slot = (p.rank - c.owner - 1 + p.world) % p.world;
+        bf16* dst = static_cast<bf16*>(peer_part.p[c.owner]) +
+                    (static_cast<int64_t>(slot) * p.m_shard + static_cast<int64_t>(c.mb) * GC_BM + quarter * 32) * p.N + col0 +
+                    lane * 8;
+#pragma unroll 4
+        for (int r = 0; r < 32; ++r) {
+          const uint4 val = *reinterpret_cast<const uint4*>(stage + r * 512 + ((lane ^ r) & 31) * 16);
+          *reinterpret_cast<uint4*>(dst + static_cast<int64_t>(r) * p.N) = val;
+        }
+        // The stores are posted; waiting here for their acknowledgement (a system-scope fence) would stall this warp
+        // for a link round trip per tile.  Instead the warp only publishes, at CTA scope, that its stores of this
+        // tile are issued; the flag warp fences at system scope and raises the tile's flag in the owner's memory
+        // (release semantics are cumulative over what it observed).
+        __syncwarp();                 // the staging rows are free for the next tile
         if (lane == 0) {
-          mbar_arrive(s.tempty(acc));
-          __threadfence_system();
-          // counters rotate over four slots: a warp is never more than two tiles ahead of another one's
-          // pending increment (the TMEM hand-over of tile i+2 needs every warp's arrival for tile i)
-          if ((atomicAdd(s.epi_count + (tile_seq & 3), 1) & 3) == 3)
-            gc_st_release_sys(p.part_flags + (c.owner * p.mbps + c.mb) * p.tiles_n + c.nt, p.epoch);
+          __threadfence_block();
+          pushed[quarter] = ++n_pushed;          // one counter per epilogue warp: the warps may be two tiles apart
         }
         acc_phase[acc] ^= 1u;
         acc ^= 1;
         continue;
-      } else {
-        // this rank's rows: add the peers' sum left by the reducer warps, write the final output
-        if (p.world > 1) {
-          const int* flag = p.sum_flags + c.mb * p.tiles_n + c.nt;
-          int ready = 1;
-          if (lane == 0) ready = gc_wait_flag<false>(flag, p.epoch, p.wait_ns, s.abort_flag, 635) ? 1 : 0;
-          ready = __shfl_sync(0xffffffffu, ready, 0);
-          if (!ready) break;
-          (void)gc_ld_acquire_gpu(flag);   // every lane orders its reads of the sum after the flag
-        }
-        const int64_t lrow = static_cast<int64_t>(c.mb) * GC_BM + quarter * 32 + lane;
-        bf16* orow = out + lrow * p.ldc + col0;
-        const float* srow = p.world > 1 ? p.peer_sum + lrow * p.N + col0 : nullptr;
-        // the peers' sum comes from memory: its loads for the next 32 columns are in flight while the current
-        // 32 are read from TMEM, converted and stored
-        float4 nxt[8];
-        if (srow != nullptr) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) nxt[j] = *reinterpret_cast<const float4*>(srow + 4 * j);
-        }
+      }
+      // this rank's rows: wait for the peers' tiles (pushed into local memory), add them in slot order, write the output
+      bool ready = true;
+      for (int d = 0; d + 1 < p.world && ready; ++d) {
+        const int* flag = p.part_flags + (d * p.mbps + c.mb) * p.tiles_n + c.nt;
+        int r = 1;
+        if (lane == 0) r = gc_wait_flag<true>(flag, p.epoch, p.wait_ns, s.abort_flag, 635) ? 1 : 0;   // written by a peer GPU
+        ready = __shfl_sync(0xffffffffu, r, 0) != 0;
+        if (ready) (void)gc_ld_acquire_sys(flag);   // every lane orders its reads of the tile after the flag
+      }
+      if (!ready) break;
+      const int64_t lrow = static_cast<int64_t>(c.mb) * GC_BM + quarter * 32 + lane;
+      bf16* orow = out + lrow * p.ldc + col0;
+      const bf16* prow = p.partial + lrow * p.N + col0;
+      const int64_t slot_stride = p.m_shard * p.N;
 #pragma unroll 1
-        for (int col = 0; col < GC_BN; col += 32) {
-          uint32_t v[32];
-          tmem_ld32(t_row + col, v);
-          float4 cur[8];
-          if (srow != nullptr) {
+      for (int col = 0; col < GC_BN; col += 32) {
+        uint32_t v[32];
+        tmem_ld32(t_row + col, v);
+        // peers' tiles: the loads of slot d + 1 are in flight while slot d is added (fixed order: deterministic)
+        uint4 cur[4], nxt[4];
+        auto load_slot = [&](uint4 (&dstv)[4], int d) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) cur[j] = nxt[j];
-            if (col + 32 < GC_BN) {
+          for (int j = 0; j < 4; ++j)
+            dstv[j] = *reinterpret_cast<const uint4*>(prow + static_cast<int64_t>(d) * slot_stride + col + 8 * j);
+        };
+        if (p.world > 1) load_slot(cur, 0);
+        tmem_ld_wait();
 #pragma unroll
-              for (int j = 0; j < 8; ++j) nxt[j] = *reinterpret_cast<const float4*>(srow + col + 32 + 4 * j);
+        for (int d = 0; d < GC_MAX_RANKS - 1; ++d) {
+          if (d + 1 < p.world) {
+            if (d + 2 < p.world) load_slot(nxt, d + 1);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t w[4] = {cur[j].x, cur[j].y, cur[j].z, cur[j].w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 t = unpack_bf16(w[e]);
+                v[8 * j + 2 * e] = __float_as_uint(__uint_as_float(v[8 * j + 2 * e]) + t.x);
+                v[8 * j + 2 * e + 1] = __float_as_uint(__uint_as_float(v[8 * j + 2 * e + 1]) + t.y);
+              }
             }
-          }
-          tmem_ld_wait();
-          if (srow != nullptr) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) + cur[j].x);
-              v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + cur[j].y);
-              v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + cur[j].z);
-              v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + cur[j].w);
-            }
+            for (int j = 0; j < 4; ++j) cur[j] = nxt[j];
           }
-          gc_store_row32(v, orow + col, nullptr);
         }
+        gc_store_row32(v, orow + col, nullptr);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -485,94 +531,34 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       acc_phase[acc] ^= 1u;
       acc ^= 1;
     }
-  } else if (p.world > 1) {
-    // ------------------------------------------------------------------ reducers (warps 6..9, 128 threads)
-    // Peers' partial tiles are staged in shared memory by plain (never multicast) TMA loads from the peer's
-    // symmetric buffer, two 64-row half tiles (32 KB each) in flight per CTA, then summed into the local fp32
-    // buffer.  Work items: (tile of this rank's rows) x (peer) x (half).  All 128 threads run the same number
-    // of iterations and barriers; after an expired wait they only skip the work.
-    const int rt = threadIdx.x - 6 * 32;
-    const uint32_t stage_base = s.base_u32 + GC_RING_BYTES;
-    const uint8_t* stage_ptr = s.base + GC_RING_BYTES;
-    constexpr uint32_t HALF_BYTES = 64 * GC_BN * 2;          // 32 KB: four 64x64 swizzled boxes
-    const int64_t units = static_cast<int64_t>(p.mbps) * p.tiles_n;
-    const int my_units = static_cast<int>(units > blockIdx.x ? (units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0);
-    const int ipu = 2 * (p.world - 1);
-    const int total = my_units * ipu;
-    bool dead = false;
-    // item i of this CTA: tile = i / ipu, then half-tile h (64 rows), then peer d: all peers of one half are summed
-    // in registers before the half is written, so the fp32 buffer is written once and never read back here
-    const int npeers = p.world - 1;
-    auto issue = [&](int i) {     // thread rt == 0 only
-      const int64_t u = blockIdx.x + static_cast<int64_t>(i / ipu) * gridDim.x;
-      const int mb = static_cast<int>(u / p.tiles_n), nt = static_cast<int>(u % p.tiles_n);
-      const int h = (i % ipu) / npeers, d = 1 + (i % ipu) % npeers;
-      const int peer = (p.rank + d) % p.world;
-      if (h == 0) {
-        const int fidx = (p.rank * p.mbps + mb) * p.tiles_n + nt;
-        if (!gc_wait_flag<true>(static_cast<const int*>(peer_flags.p[peer]) + fidx, p.epoch, p.wait_ns, s.abort_flag,
-                                640 + peer))
-          return false;
-      }
-      const uint32_t slot = i & 1;
-      const uint32_t dst = stage_base + slot * HALF_BYTES;
-      const int row = static_cast<int>(static_cast<int64_t>(p.rank) * p.m_shard + static_cast<int64_t>(mb) * GC_BM + 64 * h);
-      mbar_expect_tx(s.copy(slot), HALF_BYTES);
-#pragma unroll
-      for (int j = 0; j < GC_BN / 64; ++j)
-        tma_load_3d(dst + j * 8192, &peer_maps.m[d - 1], s.copy(slot), nt * GC_BN + 64 * j, row, 0);
-      return true;
-    };
-    int issued = 0;
-    float acc[16][8];
-#pragma unroll
-    for (int k = 0; k < 16; ++k)
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc[k][e] = 0.f;
-    if (rt == 0 && total > 0) { if (issue(0)) issued = 1; }
-    for (int i = 0; i < total; ++i) {
-      asm volatile("bar.sync 1, 128;" ::: "memory");      // everyone is done with the slot item i+1 will use
-      if (*s.abort_flag) dead = true;
-      if (rt == 0 && !dead && i + 1 < total) { if (issue(i + 1)) issued = i + 2; }
-      const int64_t u = blockIdx.x + static_cast<int64_t>(i / ipu) * gridDim.x;
-      const int mb = static_cast<int>(u / p.tiles_n), nt = static_cast<int>(u % p.tiles_n);
-      const int h = (i % ipu) / npeers, d = 1 + (i % ipu) % npeers;
-      const bool last_peer = d == npeers;
-      if (!dead && !*s.abort_flag) {
-        if (mbar_wait(s.copy(i & 1), (i >> 1) & 1u, s.abort_flag, 642)) {
-          const uint8_t* src = stage_ptr + (i & 1) * HALF_BYTES;
-          float* out_base = p.peer_sum + (static_cast<int64_t>(mb) * GC_BM + 64 * h) * p.N + static_cast<int64_t>(nt) * GC_BN;
-#pragma unroll
-          for (int k = 0; k < 16; ++k) {
-            const int v = rt + 128 * k;
-            const int row = v >> 5, c8 = v & 31;
-            const uint4 raw = *reinterpret_cast<const uint4*>(src + (c8 >> 3) * 8192 + sw128_offset(row, c8 & 7));
-            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 t = unpack_bf16(w[e]);
-              acc[k][2 * e] += t.x;
-              acc[k][2 * e + 1] += t.y;
-            }
-            if (last_peer) {
-              float* dst = out_base + static_cast<int64_t>(row) * p.N + c8 * 8;
-              *reinterpret_cast<float4*>(dst) = make_float4(acc[k][0], acc[k][1], acc[k][2], acc[k][3]);
-              *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[k][4], acc[k][5], acc[k][6], acc[k][7]);
-#pragma unroll
-              for (int e = 0; e < 8; ++e) acc[k][e] = 0.f;
-            }
+  } else if (warp == 6 && p.world > 1) {
+    // ------------------------------------------------------------------ flag warp
+    // Walks this CTA's tiles of other ranks in schedule order; when all four epilogue warps have issued the stores
+    // of a tile, makes them visible system-wide and raises the tile's flag at its owner.
+    if (lane == 0) {
+      volatile int* pushed = s.epi_count;
+      int done = 0;
+      for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        const GcTile c = gc_tile(tile, p, false);
+        if (c.owner == p.rank) continue;
+        ++done;
+        const uint64_t t0 = globaltimer_ns();
+        bool ok = true;
+        while (pushed[0] < done || pushed[1] < done || pushed[2] < done || pushed[3] < done) {
+          if (*s.abort_flag) { ok = false; break; }
+          if (globaltimer_ns() - t0 > p.wait_ns) {      // the epilogue warps never got there: give up like they did
+            *s.abort_flag = 1;
+            atomicCAS(&g_status, 0, 636);
+            ok = false;
+            break;
           }
+          __nanosleep(100);
         }
+        if (!ok) break;
+        __threadfence_system();
+        const int slot = (p.rank - c.owner - 1 + p.world) % p.world;
+        gc_st_release_sys(static_cast<int*>(peer_flags.p[c.owner]) + (slot * p.mbps + c.mb) * p.tiles_n + c.nt, p.epoch);
       }
-      if ((i % ipu) == ipu - 1) {                           // tile complete: publish it to the epilogue warps
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (rt == 0 && !dead && !*s.abort_flag) gc_st_release_gpu(p.sum_flags + mb * p.tiles_n + nt, p.epoch);
-      }
-    }
-    if (rt == 0 && *s.abort_flag && issued > 0) {           // loads nobody waited for: let them land
-      mbar_drain(s.copy(0), 0); mbar_drain(s.copy(0), 1);
-      mbar_drain(s.copy(1), 0); mbar_drain(s.copy(1), 1);
     }
   }
 
@@ -647,13 +633,14 @@ TTCD_EXPORT int ttcd_ag_gemm(const long long* x_ptrs, const void* w, void* c, vo
 
 // out[m_shard, N] (row stride ldc) = rows [rank*m_shard, (rank+1)*m_shard) of sum_r ( x_r[world*m_shard, K] * w_r^T ).
 // x: local bf16 [world*m_shard, K] (row stride ldx); w: [N, K] or [K, N] (b_mn).  partial_ptrs[r] / flag_ptrs[r]:
-// rank r's symmetric partial buffer (bf16 [world*m_shard, N]) and flags (int[world*mbps*tiles_n], values < epoch).
-// peer_sum: local fp32 [m_shard, N]; sum_flags: local int[mbps*tiles_n], values < epoch.  Every rank must have
-// finished reading the partial buffers of the previous call before this launch (barrier).
+// rank r's symmetric receive buffer (bf16 [(world-1)*m_shard, N]) and flags (int[(world-1)*mbps*tiles_n], values <
+// epoch): the peers' tiles of rank r's rows arrive there.  Every rank must have finished the previous call that used
+// these buffers before this launch (barrier): peers start writing into them at once.
+// lag_blocks: see gc_tile (<= 0: the rank's own row blocks come last).
 TTCD_EXPORT int ttcd_gemm_rs(const void* x, const void* w, void* out, const long long* partial_ptrs,
-                             const long long* flag_ptrs, float* peer_sum, int* sum_flags, int rank, int world,
-                             long long m_shard, long long N, long long K, long long ldx, long long ldw, long long ldc,
-                             int b_mn, int epoch, long long wait_ns, void* stream_ptr) {
+                             const long long* flag_ptrs, int rank, int world, long long m_shard, long long N, long long K,
+                             long long ldx, long long ldw, long long ldc, int b_mn, int epoch, long long wait_ns,
+                             int lag_blocks, void* stream_ptr) {
   int rc = gc_check(rank, world, m_shard, N, K);
   if (rc != TTCD_OK) return rc;
   if ((ldc * 2) % 16 != 0) return TTCD_ERR_ARG;
@@ -669,25 +656,20 @@ TTCD_EXPORT int ttcd_gemm_rs(const void* x, const void* w, void* out, const long
   p.wait_ns = wait_ns > 0 ? static_cast<uint64_t>(wait_ns) : 10000000000ull;
   p.partial = reinterpret_cast<bf16*>(partial_ptrs[rank]);
   p.part_flags = reinterpret_cast<int*>(flag_ptrs[rank]);
-  p.peer_sum = peer_sum; p.sum_flags = sum_flags;
-  GcPeerMaps maps;
-  for (int d = 1; d < GC_MAX_RANKS; ++d) {
-    const int peer = (rank + (d < world ? d : 0)) % world;     // unused entries alias a valid buffer
-    rc = make_tmap_bf16_3d(&maps.m[d - 1], reinterpret_cast<const void*>(partial_ptrs[peer]), N, m_shard * world, 1, N, 0, 64, 64);
-    if (rc != TTCD_OK) return rc;
-  }
+  // lag_blocks <= 0: all own row blocks last
+  p.lag = (lag_blocks <= 0 || lag_blocks > p.mbps || world == 1) ? p.mbps : lag_blocks;
   constexpr int smem_bytes = GC_RING_BYTES + GC_RS_STAGING + GC_NBARS * 8 + 32 + 1024;
   const long long total = static_cast<long long>(world) * p.mbps * p.tiles_n;
   const int grid = static_cast<int>(std::min<long long>(total, sm_count()));
   cudaStream_t st = static_cast<cudaStream_t>(stream_ptr);
   if (b_mn) {
     TTCD_CUDA_CHECK(static_cast<cudaError_t>(gc_configure(gemm_rs_kernel<true>, smem_bytes)));
-    gemm_rs_kernel<true><<<grid, GC_THREADS, smem_bytes, st>>>(t_a, t_b, maps, gc_peers(flag_ptrs, world),
-                                                               static_cast<bf16*>(out), p);
+    gemm_rs_kernel<true><<<grid, GC_RS_THREADS, smem_bytes, st>>>(t_a, t_b, gc_peers(partial_ptrs, world),
+                                                                  gc_peers(flag_ptrs, world), static_cast<bf16*>(out), p);
   } else {
     TTCD_CUDA_CHECK(static_cast<cudaError_t>(gc_configure(gemm_rs_kernel<false>, smem_bytes)));
-    gemm_rs_kernel<false><<<grid, GC_THREADS, smem_bytes, st>>>(t_a, t_b, maps, gc_peers(flag_ptrs, world),
-                                                                static_cast<bf16*>(out), p);
+    gemm_rs_kernel<false><<<grid, GC_RS_THREADS, smem_bytes, st>>>(t_a, t_b, gc_peers(partial_ptrs, world),
+                                                                   gc_peers(flag_ptrs, world), static_cast<bf16*>(out), p);
   }
   return static_cast<int>(cudaGetLastError());
 }

@@ -41,20 +41,19 @@ def test_gemm_reduce_scatter_gives_up_on_an_absent_peer():
     x = torch.randn(2 * m, k, device="cuda").bfloat16()
     w = torch.randn(n, k, device="cuda").bfloat16()
     out = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
-    part = [torch.zeros(2 * m, n, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
-    flags = [torch.zeros(64, device="cuda", dtype=torch.int32) for _ in range(2)]     # flags[1] is never written
-    peer_sum = torch.zeros(m, n, device="cuda")
-    sum_flags = torch.zeros(64, device="cuda", dtype=torch.int32)
+    # receive buffers and flags of "rank 0" (this call) and of a peer that never runs: nothing ever arrives in ours
+    part = [torch.zeros(m, n, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+    flags = [torch.zeros(64, device="cuda", dtype=torch.int32) for _ in range(2)]
     t0 = time.time()
     nv.call("ttcd_gemm_rs", nv.ptr(x), nv.ptr(w), nv.ptr(out), _i64s([t.data_ptr() for t in part]),
-            _i64s([t.data_ptr() for t in flags]), nv.ptr(peer_sum), nv.ptr(sum_flags), nv.i32(0), nv.i32(2), nv.i64(m), nv.i64(n),
-            nv.i64(k), nv.i64(k), nv.i64(k), nv.i64(n), nv.i32(0), nv.i32(1), nv.i64(200_000_000), nv.stream_ptr())
+            _i64s([t.data_ptr() for t in flags]), nv.i32(0), nv.i32(2), nv.i64(m), nv.i64(n), nv.i64(k), nv.i64(k), nv.i64(k),
+            nv.i64(n), nv.i32(0), nv.i32(1), nv.i64(200_000_000), nv.i32(0), nv.stream_ptr())
     torch.cuda.synchronize()
     assert time.time() - t0 < 10.0
-    assert nv.device_status() in (641, 635)            # the reducer gave up on peer 1 (or the epilogue on its sum)
-    # this rank's partial for the peer's rows was still produced and flagged
-    torch.testing.assert_close(part[0][m:].float(), x[m:].float() @ w.float().t(), rtol=2e-2, atol=2e-1)
-    assert int(flags[0][1 * 1 * 1]) == 1               # tile (owner 1, block 0, n-tile 0)
+    assert nv.device_status() == 635                   # the epilogue of this rank's own rows gave up on the peer's tile
+    # this rank's tile of the peer's rows was still pushed into the peer's receive buffer and flagged there
+    torch.testing.assert_close(part[1].float(), x[m:].float() @ w.float().t(), rtol=2e-2, atol=2e-1)
+    assert int(flags[1][0]) == 1                       # slot 0 (the only peer), block 0, n-tile 0
     y = torch.randn(512, 512, device="cuda").bfloat16()
     from ttcd_b200.ops import cuda
     torch.testing.assert_close(cuda.gemm(y, y.t()).view(512, 512).float(), y.float() @ y.float().t(), rtol=2e-2, atol=3e-1)

@@ -27,8 +27,12 @@ def _launch(what: str, nproc: int, timeout: int = 600, **extra_env) -> str:
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), str(ROOT / "tests" / "multi_gpu_worker.py"), what]
     env = dict(os.environ, PYTHONPATH=str(ROOT), **extra_env)
-    res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=str(ROOT))
-    out = res.stdout + res.stderr
+    for attempt in range(3):
+        res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=str(ROOT))
+        out = res.stdout + res.stderr
+        if "EADDRINUSE" not in out:
+            break
+        cmd[cmd.index("--master-port") + 1] = str(_free_port())      # somebody took the port between the probe and the bind
     assert res.returncode == 0 and "MULTI_GPU_OK" in out, out[-4000:]
     return out
 

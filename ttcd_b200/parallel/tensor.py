@@ -8,9 +8,9 @@ micro-pipelining, 283-287), each of the two patterns is ONE kernel here (``csrc/
 
 * ``ag_linear``  : all-gather -> GEMM.  Peers' row blocks are pulled into a local gathered buffer by bulk
   async copies inside the GEMM kernel; tiles start on the rank's own rows and follow the flags.
-* ``rs_linear``  : GEMM -> reduce-scatter.  Other ranks' row blocks are computed first and flagged; reducer
-  warps sum the peers' partial tiles over NVLink while the tensor cores finish the rank's own rows, whose
-  epilogue adds the sum.
+* ``rs_linear``  : GEMM -> reduce-scatter.  Other ranks' row blocks are computed first and each finished tile
+  is pushed (coalesced bf16 stores over NVLink) into its owner's receive buffer and flagged there; the rank's
+  own rows are computed last and their epilogue adds the tiles the peers pushed, in a fixed order.
 
 Backward uses the same two kernels with the weight read MN-major (dX of a column-parallel layer is a
 GEMM -> reduce-scatter, dX of a row-parallel layer an all-gather -> GEMM) and the plain GEMM for dW on the
@@ -50,6 +50,7 @@ class TensorParallel:
         self.device = torch.device(device if device is not None else "cpu")
         self.fused = (self.device.type == "cuda" and nv.available()) if fused is None else fused
         self.wait_ns = wait_ns
+        self.rs_lag = 32              # gemm_rs schedule: own row blocks trail the pushes by 32 rounds (csrc/gemm_comm.cu::gc_tile)
         self.epoch = 0
         self.calls = 0
         if self.fused:
@@ -61,9 +62,7 @@ class TensorParallel:
             nflags = (rows // self.BM) * w * (feat // self.BN)
             self.flag_sym = [SymmetricBuffer(nflags * 4, group, self.device) for _ in range(2)]
             self.gathered = torch.empty(rows * w * feat, dtype=torch.bfloat16, device=self.device)
-            self.peer_sum = torch.empty(rows * feat, dtype=torch.float32, device=self.device)
             self.ready = torch.zeros((rows // self.BM) * w, dtype=torch.int32, device=self.device)
-            self.sum_flags = torch.zeros((rows // self.BM) * (feat // self.BN), dtype=torch.int32, device=self.device)
             self.barrier = PeerBarrier(group, slots=2, wait_ns=wait_ns)
         _CTX = self
 
@@ -102,8 +101,9 @@ class TensorParallel:
         full[self.rank * m:(self.rank + 1) * m].copy_(x_shard)       # the kernel read the own rows in place
         return out, full
 
-    def gemm_rs(self, x: torch.Tensor, w: torch.Tensor, w_is_kn: bool = False) -> torch.Tensor:
-        """Rows of this rank of ``sum_ranks(x_r @ W_r^T)``.  ``x``: [world*m_shard, K_local]."""
+    def gemm_rs(self, x: torch.Tensor, w: torch.Tensor, w_is_kn: bool = False, lag: int | None = None) -> torch.Tensor:
+        """Rows of this rank of ``sum_ranks(x_r @ W_r^T)``.  ``x``: [world*m_shard, K_local].  ``lag``: rounds by which
+        the rank's own row blocks trail the pushes to the peers (default ``self.rs_lag``; 0 = all own blocks last)."""
         mt, k = x.shape
         m = mt // self.world
         n = w.shape[1] if w_is_kn else w.shape[0]
@@ -117,9 +117,9 @@ class TensorParallel:
         x = x if x.stride(-1) == 1 else x.contiguous()
         w = w if w.stride(-1) == 1 else w.contiguous()
         nv.call("ttcd_gemm_rs", nv.ptr(x), nv.ptr(w), nv.ptr(out), self.part_sym[b].ptr_array(), self.flag_sym[b].ptr_array(),
-                nv.ptr(self.peer_sum), nv.ptr(self.sum_flags), nv.i32(self.rank), nv.i32(self.world), nv.i64(m), nv.i64(n),
-                nv.i64(k), nv.i64(x.stride(0)), nv.i64(w.stride(0)), nv.i64(n), nv.i32(1 if w_is_kn else 0),
-                nv.i32(self.epoch), nv.i64(self.wait_ns), nv.stream_ptr())
+                nv.i32(self.rank), nv.i32(self.world), nv.i64(m), nv.i64(n), nv.i64(k), nv.i64(x.stride(0)),
+                nv.i64(w.stride(0)), nv.i64(n), nv.i32(1 if w_is_kn else 0), nv.i32(self.epoch), nv.i64(self.wait_ns),
+                nv.i32(self.rs_lag if lag is None else lag), nv.stream_ptr())
         return out
 
     # NCCL / gloo statement of the same two operations (baseline and CPU path)
