@@ -61,7 +61,7 @@ def parse_args():
     ap.add_argument("--ref-ac", default="auto", choices=["auto", "none", "full"],
                     help="reference arm: 'auto' runs without activation checkpointing if that fits, else with full")
     ap.add_argument("--no-extra", action="store_true", help="skip the ac_full and context-parallel extras")
-    ap.add_argument("--cp-worker", action="store_true", help=argparse.SUPPRESS)
+    ap.add_argument("--worker", default=None, choices=["cp", "zero3"], help=argparse.SUPPRESS)
     return ap.parse_args()
 
 
@@ -214,7 +214,8 @@ def run_ours(args):
             del dev, host, e2e_host
             engine.sdp.zero_grad()
             torch.cuda.empty_cache()
-            extra["cp"] = run_cp_children(args, rank, local, world)
+            extra["cp"] = run_children(args, rank, world, "cp", 23)
+            extra["zero3"] = run_children(args, rank, world, "zero3", 41)
     if rank == 0:
         print(json.dumps({
             "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
@@ -241,16 +242,16 @@ def run_ours(args):
 CP_STEPS, CP_WARMUP, CP_TIMEOUT_S = 5, 3, 420
 
 
-def run_cp_children(args, rank, local, world) -> dict:
-    """Every rank starts one child (``bench.py --cp-worker``) with the same rank / world size and its own rendezvous
-    port; the children form their own process group, run the context-parallel measurement and rank 0's child
-    prints its JSON.  A child that fails or outlives its time limit is killed by PID and reported as an error."""
+def run_children(args, rank, world, what: str, port_offset: int) -> dict:
+    """Every rank starts one child (``bench.py --worker <what>``) with the same rank / world size and its own
+    rendezvous port; the children form their own process group, run the measurement and rank 0's child prints its
+    JSON.  A child that fails or outlives its time limit is killed by PID and reported as an error."""
     env = dict(os.environ)
-    env["MASTER_PORT"] = str(int(env.get("MASTER_PORT", "29500")) + 23)
+    env["MASTER_PORT"] = str(int(env.get("MASTER_PORT", "29500")) + port_offset)
     env["TORCHELASTIC_USE_AGENT_STORE"] = "False"          # rank 0's child hosts the store of the children's group
     for k in ("TORCHELASTIC_RUN_ID", "TORCHELASTIC_RESTART_COUNT", "TORCHELASTIC_MAX_RESTARTS"):
         env.pop(k, None)
-    cmd = [sys.executable, str(Path(__file__).resolve()), "--cp-worker", "--gpus", str(world), "--config", args.config,
+    cmd = [sys.executable, str(Path(__file__).resolve()), "--worker", what, "--gpus", str(world), "--config", args.config,
            "--seq-len", str(args.seq_len)]
     if args.layers is not None:
         cmd += ["--layers", str(args.layers)]
@@ -270,6 +271,41 @@ def run_cp_children(args, rank, local, world) -> dict:
         return {"degree": world, "error": f"child exit {proc.returncode}: {err.strip()[-300:]}"}
     except Exception as exc:  # pragma: no cover
         return {"degree": world, "error": f"{type(exc).__name__}: {exc}"[:300]}
+
+
+def run_zero3_worker(args):
+    """The headline configuration (one sequence per GPU, sharded data parallel) with the blocks' weights stored 1/N per
+    rank and gathered inside each block's first GEMM (forward) / by the gather kernel (backward)."""
+    import torch
+    import torch.distributed as dist
+    from datetime import timedelta
+
+    rank, local, world = dist_env()
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=timedelta(seconds=120))
+    from ttcd_b200 import _native
+    from ttcd_b200.train.engine import EngineConfig, TrainEngine, load_model_config
+
+    _native.load(required=True)
+    overrides = {} if args.layers is None else {"num_hidden_layers": args.layers}
+    cfg = load_model_config(args.config, **overrides)
+    engine = TrainEngine(cfg, EngineConfig(activation_checkpoint="none", shard_weights=True), device=f"cuda:{local}")
+    S, V = args.seq_len, cfg.vocab_size
+    gen = torch.Generator().manual_seed(77 + rank)
+    ids = [torch.randint(0, V, (1, S), generator=gen, dtype=torch.int64).cuda() for _ in range(CP_WARMUP + CP_STEPS)]
+    for i in range(CP_WARMUP):
+        engine.train_step(ids[i], return_loss_on_host=False)
+    ms = timed_region(torch, dist, world, lambda i: engine.train_step(ids[CP_WARMUP + i], return_loss_on_host=False), CP_STEPS)
+    status = _native.device_status()
+    peak = torch.cuda.max_memory_allocated() / 2 ** 30
+    n_block = sum(g.numel for g in engine.sdp.groups if g.sharded)
+    if rank == 0:
+        print(json.dumps({"degree": world, "parallelism": f"sharded-dp{world}, block weights sharded 1/{world} (gather fused into the q|k|v GEMM)",
+                          "steps": CP_STEPS, "warmup": CP_WARMUP, "ms_per_step": round(ms / CP_STEPS, 2),
+                          "tokens_per_s": round(S * world * CP_STEPS / (ms / 1e3), 1), "scaling": "weak",
+                          "final_loss": float(engine.last_loss), "device_status": status, "peak_mem_gib": round(peak, 1),
+                          "block_params_per_rank_mib": round(n_block * 2 / world / 2 ** 20, 1)}), flush=True)
+    dist.destroy_process_group()
 
 
 def run_cp_worker(args):
@@ -333,8 +369,11 @@ def main():
             if rank == 0:
                 print(json.dumps({"impl": "reference", "unavailable": f"{type(exc).__name__}: {exc}"[:400]}), flush=True)
         return
-    if args.cp_worker:
+    if args.worker == "cp":
         run_cp_worker(args)
+        return
+    if args.worker == "zero3":
+        run_zero3_worker(args)
         return
     run_ours(args)
 

@@ -19,7 +19,15 @@
 //              bf16 output.  No separate reduction pass, no pull across the link, and the NVLink traffic
 //              overlaps the tensor-core work of the remaining tiles.
 //
-// Both kernels: persistent, one CTA per SM, 128x256x64 tiles, 3-stage TMA ring (never multicast),
+//   wgather_gemm :  C[M, N] = X[M, K] * W^T with W a slice of a sharded flat parameter buffer (ZeRO-3 / FSDP):
+//              every rank keeps 1/world of a block's parameters; the first GEMM that consumes them (the fused
+//              q|k|v projection) gathers the WHOLE block inside the kernel: one elected thread per CTA pulls 64 KB
+//              units of the peers' shards (and of the rank's own) into the local gathered buffer with bulk async
+//              copies, the units that hold W first, and raises a flag per unit; the TMA producer waits for the
+//              flags of the units under the W rows of its tile.  The rest of the block's parameters land while
+//              the tensor cores work and are there, by stream order, for the block's other kernels.
+//
+// All kernels: persistent, one CTA per SM, 128x256x64 tiles, 3-stage TMA ring (never multicast),
 // tcgen05.mma into a double-buffered TMEM accumulator.  Every wait (mbarrier or flag) is bounded; on
 // expiry the kernel records a code in the status word, drains its copies, frees TMEM and returns.
 // They replace NCCL all-gather / reduce-scatter + cuBLAS behind the reference's tensor-parallel plan
@@ -59,6 +67,11 @@ struct GcParams {
   // ag_gemm
   bf16* gathered;      // [world*m_shard, K] local
   int* ready;          // [world*mbps] local flags
+  // wgather_gemm
+  int64_t shard_bytes;   // bytes of one rank's shard of the flat buffer (multiple of the 64 KB unit)
+  int64_t w_byte_off;    // byte offset of W inside the flat buffer
+  int units;             // 64 KB units in the flat buffer (world * shard_bytes / 64 KB)
+  uint8_t* flat;         // local gathered flat buffer
   // gemm_rs
   bf16* partial;       // this rank's symmetric receive buffer [(world-1)*m_shard, N]: slot d-1 holds what rank
                        // (rank + d) % world computed for this rank's rows
@@ -384,6 +397,139 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tma_own, const __grid_constan
 }
 
 // ================================================================================================
+// sharded-parameter gather -> GEMM
+// ================================================================================================
+constexpr int GC_UNIT_BYTES = GC_COPY_SLOTS * GC_COPY_BYTES;     // 64 KB: flag granularity of the gathered buffer
+
+template <bool B_MN>
+__global__ void __launch_bounds__(GC_THREADS, 1)
+wgather_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                    const GcPeers shards, bf16* __restrict__ C, const GcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  constexpr int STAGING = GC_COPY_SLOTS * GC_COPY_BYTES;
+  const GcSmem s = gc_setup<STAGING>(smem_raw);
+  const uint32_t tmem_base = *s.tmem_slot;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t tiles_m = p.m_shard / GC_BM;
+  const int64_t total_tiles = tiles_m * p.tiles_n;
+  // bytes of W under one n-tile of the output: B_MN = false: W is [N, K], 256 rows; B_MN = true: W is [K, N] and an
+  // n-tile touches every row, so all of W must be there
+  const int64_t w_bytes = p.N * p.K * 2;
+  const int u_w0 = static_cast<int>(p.w_byte_off / GC_UNIT_BYTES);
+  const int u_w1 = static_cast<int>((p.w_byte_off + w_bytes - 1) / GC_UNIT_BYTES);      // inclusive
+
+  if (warp == 0) {
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int ready_hi = u_w0 - 1;        // units [u_w0, ready_hi] are known to be there
+      for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int mi = static_cast<int>(tile / p.tiles_n), nt = static_cast<int>(tile % p.tiles_n);
+        const int64_t hi_byte = B_MN ? p.w_byte_off + w_bytes - 1
+                                     : p.w_byte_off + (static_cast<int64_t>(nt + 1) * GC_BN) * p.K * 2 - 1;
+        const int need = static_cast<int>(hi_byte / GC_UNIT_BYTES);       // the units arrive in ascending order of W
+        while (ready_hi < need) {
+          if (!gc_wait_flag<false>(p.ready + ready_hi + 1, p.epoch, p.wait_ns, s.abort_flag, 650)) { ok = false; break; }
+          ++ready_hi;
+        }
+        if (!ok) break;
+        gc_fence_proxy_async();       // the rows were written through the async proxy of another CTA
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(s.empty(stage), phase ^ 1u, s.abort_flag, 651)) { ok = false; break; }
+          const uint32_t sa = s.base_u32 + stage * GC_STAGE_BYTES;
+          mbar_expect_tx(s.full(stage), GC_STAGE_BYTES);
+          tma_load_3d(sa, &tma_a, s.full(stage), kb * GC_BK, mi * GC_BM, 0);
+          gc_load_b(B_MN, sa + GC_A_BYTES, &tma_b, s.full(stage), kb * GC_BK, nt * GC_BN);
+          if (++stage == GC_STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (*s.abort_flag)
+        for (int i = 0; i < GC_STAGES; ++i) mbar_drain(s.full(i), 0), mbar_drain(s.full(i), 1);
+    }
+  } else if (warp == 1) {
+    if (elect_one()) gc_mma_role<B_MN>(s, tmem_base, total_tiles, p.num_kb);
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;
+    uint32_t acc_phase[2] = {0, 0};
+    int acc = 0;
+    for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      const int mi = static_cast<int>(tile / p.tiles_n), nt = static_cast<int>(tile % p.tiles_n);
+      if (!mbar_wait(s.tfull(acc), acc_phase[acc], s.abort_flag, 654)) break;
+      tc_fence_after_sync();
+      bf16* crow = C + (static_cast<int64_t>(mi) * GC_BM + quarter * 32 + lane) * p.ldc + static_cast<int64_t>(nt) * GC_BN;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * GC_BN;
+#pragma unroll 1
+      for (int col = 0; col < GC_BN; col += 32) {
+        uint32_t v[32];
+        tmem_ld32(t_row + col, v);
+        tmem_ld_wait();
+        gc_store_row32(v, crow + col, nullptr);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s.tempty(acc));
+      acc_phase[acc] ^= 1u;
+      acc ^= 1;
+    }
+  } else if (warp == 6) {
+    // ------------------------------------------------------------------ gather: every rank's shard -> local flat buffer
+    // Units are taken in the order [units of W, ascending] then [the other units of the block]; unit j of that
+    // order goes to CTA j % gridDim.x, so the W units are spread over the first CTAs and land first.
+    if (elect_one()) {
+      const uint32_t stage_base = s.base_u32 + GC_RING_BYTES;
+      const int n_w = u_w1 - u_w0 + 1;
+      uint32_t g = 0;   // running chunk counter: slot = g % SLOTS, parity = (g / SLOTS) & 1
+      bool ok = true;
+      for (int j = blockIdx.x; j < p.units && ok; j += gridDim.x) {
+        // order: W units first; then units [0, u_w0); then units (u_w1, units)
+        const int unit = j < n_w ? u_w0 + j : (j - n_w < u_w0 ? j - n_w : j);
+        const int64_t byte0 = static_cast<int64_t>(unit) * GC_UNIT_BYTES;
+        const int owner = static_cast<int>(byte0 / p.shard_bytes);
+        const uint8_t* src = static_cast<const uint8_t*>(shards.p[owner]) + (byte0 - static_cast<int64_t>(owner) * p.shard_bytes);
+        uint8_t* dst = p.flat + byte0;
+        constexpr int n_chunks = GC_COPY_SLOTS;
+        for (int i = 0; i < n_chunks + GC_COPY_LOOK; ++i) {
+          if (i < n_chunks) {
+            gc_bulk_wait_read1();   // the store that last used this slot has finished reading it
+            const uint32_t slot = (g + i) % GC_COPY_SLOTS;
+            mbar_expect_tx(s.copy(slot), GC_COPY_BYTES);
+            gc_bulk_g2s(stage_base + slot * GC_COPY_BYTES, src + static_cast<int64_t>(i) * GC_COPY_BYTES, GC_COPY_BYTES,
+                        s.copy(slot));
+          }
+          if (i >= GC_COPY_LOOK) {
+            const uint32_t jj = g + i - GC_COPY_LOOK;
+            const uint32_t slot = jj % GC_COPY_SLOTS;
+            if (!mbar_wait(s.copy(slot), (jj / GC_COPY_SLOTS) & 1u, s.abort_flag, 652)) { ok = false; break; }
+            gc_bulk_s2g(dst + static_cast<int64_t>(i - GC_COPY_LOOK) * GC_COPY_BYTES, stage_base + slot * GC_COPY_BYTES,
+                        GC_COPY_BYTES);
+            tma_store_commit();
+          }
+        }
+        if (!ok) break;
+        g += n_chunks;
+        tma_store_wait0();          // the unit is complete in local memory
+        gc_fence_proxy_async();
+        __threadfence();
+        gc_st_release_gpu(p.ready + unit, p.epoch);
+      }
+      if (!ok) {
+        for (int i = 0; i < GC_COPY_SLOTS; ++i) mbar_drain(s.copy(i), 0), mbar_drain(s.copy(i), 1);
+      }
+      tma_store_wait0();
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 2 * GC_BN);
+  }
+}
+
+// ================================================================================================
 // GEMM -> reduce-scatter
 // ================================================================================================
 template <bool B_MN>
@@ -670,6 +816,74 @@ TTCD_EXPORT int ttcd_gemm_rs(const void* x, const void* w, void* out, const long
     TTCD_CUDA_CHECK(static_cast<cudaError_t>(gc_configure(gemm_rs_kernel<false>, smem_bytes)));
     gemm_rs_kernel<false><<<grid, GC_RS_THREADS, smem_bytes, st>>>(t_a, t_b, gc_peers(partial_ptrs, world),
                                                                    gc_peers(flag_ptrs, world), static_cast<bf16*>(out), p);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+namespace ttcd {
+// flat[r * shard_elems + i] = shards.p[r][i]: the stand-alone statement of the parameter all-gather (plain peer loads),
+// used where no GEMM of a fitting shape consumes the block first (backward re-gather, odd widths).
+__global__ void __launch_bounds__(256) peer_gather_kernel(GcPeers shards, int world, int64_t shard_vecs, uint4* __restrict__ flat) {
+  const int64_t total = shard_vecs * world;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(i / shard_vecs);
+    flat[i] = static_cast<const uint4*>(shards.p[r])[i - static_cast<int64_t>(r) * shard_vecs];
+  }
+}
+}  // namespace ttcd
+
+// flat (local bf16 [world * shard_elems]) <- every rank's shard (shard_ptrs[r]: bf16 [shard_elems], peer-addressable).
+TTCD_EXPORT int ttcd_peer_gather(void* flat, const long long* shard_ptrs, int world, long long shard_elems, void* stream_ptr) {
+  if (world < 1 || world > GC_MAX_RANKS || shard_elems <= 0 || shard_elems % 8 != 0) return TTCD_ERR_ARG;
+  const long long vecs = shard_elems / 8;
+  const unsigned grid = static_cast<unsigned>(std::min<long long>((vecs * world + 255) / 256, 148LL * 8));
+  peer_gather_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream_ptr)>>>(gc_peers(shard_ptrs, world), world, vecs,
+                                                                              static_cast<uint4*>(flat));
+  return static_cast<int>(cudaGetLastError());
+}
+
+// C[M, N] (row stride ldc) = x[M, K] (row stride ldx) * W^T, W = flat + w_elem_off: [N, K] contiguous (b_mn = 0) or
+// [K, N] contiguous (b_mn = 1), where flat (local bf16 [world * shard_elems]) is filled INSIDE the kernel from every
+// rank's shard (shard_ptrs[r], peer-addressable; shard_ptrs[rank] is local).  ready: local int[world * shard_elems * 2 /
+// 65536], values < epoch; on return every unit's flag is at epoch and the whole flat buffer is gathered.
+// M % 128 == 0, N % 256 == 0, K % 64 == 0, shard_elems * 2 % 65536 == 0, w_elem_off % 8 == 0.
+// All peers must have finished writing their shards before the launch (barrier or stream order after the optimizer).
+TTCD_EXPORT int ttcd_wgather_gemm(const void* x, void* c, void* flat, const long long* shard_ptrs, int* ready, int rank,
+                                  int world, long long M, long long N, long long K, long long ldx, long long ldc,
+                                  long long w_elem_off, long long shard_elems, int b_mn, int epoch, long long wait_ns,
+                                  void* stream_ptr) {
+  int rc = gc_check(rank, world, M, N, K);
+  if (rc != TTCD_OK) return rc;
+  if ((ldc * 2) % 16 != 0 || (ldx * 2) % 16 != 0 || w_elem_off % 8 != 0 || w_elem_off < 0) return TTCD_ERR_ARG;
+  if (shard_elems <= 0 || (shard_elems * 2) % GC_UNIT_BYTES != 0) return TTCD_ERR_ARG;
+  if (w_elem_off + N * K > shard_elems * world) return TTCD_ERR_ARG;
+  const bf16* w = static_cast<const bf16*>(flat) + w_elem_off;
+  CUtensorMap t_a, t_b;
+  rc = make_tmap_bf16_3d(&t_a, x, K, M, 1, ldx, 0, 64, GC_BM);
+  if (rc != TTCD_OK) return rc;
+  rc = b_mn ? make_tmap_bf16_3d(&t_b, w, N, K, 1, N, 0, 64, GC_BK) : make_tmap_bf16_3d(&t_b, w, K, N, 1, K, 0, 64, GC_BN);
+  if (rc != TTCD_OK) return rc;
+  GcParams p{};
+  p.rank = rank; p.world = world; p.epoch = epoch;
+  p.tiles_n = static_cast<int>(N / GC_BN); p.num_kb = static_cast<int>(K / GC_BK);
+  p.m_shard = M; p.N = N; p.K = K; p.ldc = ldc;
+  p.wait_ns = wait_ns > 0 ? static_cast<uint64_t>(wait_ns) : 10000000000ull;
+  p.ready = ready;
+  p.shard_bytes = shard_elems * 2; p.w_byte_off = w_elem_off * 2;
+  p.units = static_cast<int>(shard_elems * 2 * world / GC_UNIT_BYTES);
+  p.flat = static_cast<uint8_t*>(flat);
+  constexpr int smem_bytes = GC_RING_BYTES + GC_COPY_SLOTS * GC_COPY_BYTES + GC_NBARS * 8 + 32 + 1024;
+  // every CTA must be resident at once (the producers wait for units that other CTAs gather): one CTA per SM at most
+  const long long total = (M / GC_BM) * p.tiles_n;
+  const int grid = static_cast<int>(std::min<long long>(std::max<long long>(total, 1), sm_count()));
+  cudaStream_t st = static_cast<cudaStream_t>(stream_ptr);
+  if (b_mn) {
+    TTCD_CUDA_CHECK(static_cast<cudaError_t>(gc_configure(wgather_gemm_kernel<true>, smem_bytes)));
+    wgather_gemm_kernel<true><<<grid, GC_THREADS, smem_bytes, st>>>(t_a, t_b, gc_peers(shard_ptrs, world), static_cast<bf16*>(c), p);
+  } else {
+    TTCD_CUDA_CHECK(static_cast<cudaError_t>(gc_configure(wgather_gemm_kernel<false>, smem_bytes)));
+    wgather_gemm_kernel<false><<<grid, GC_THREADS, smem_bytes, st>>>(t_a, t_b, gc_peers(shard_ptrs, world), static_cast<bf16*>(c), p);
   }
   return static_cast<int>(cudaGetLastError());
 }

@@ -147,6 +147,54 @@ def check_accumulation_on_gpus():
     assert (fa - fb).abs().max().item() < 1e-2, (fa - fb).abs().max().item()
 
 
+def check_sharded_weights():
+    """ZeRO-3 layout on GPUs: block parameters stored 1/world per rank, gathered INSIDE the fused q|k|v GEMM in the
+    forward (and in the recomputation), by the stand-alone kernel for a backward without recomputation; three steps
+    end where the resident layout ends."""
+    from ttcd_b200.parallel import sharded as sharded_mod
+    rank = dist.get_rank()
+    os.environ["TTCD_COMM"] = "peer"
+    results = {}
+    for name, kw in (("resident", {}), ("sharded", {"shard_weights": True}), ("sharded_ac", {"shard_weights": True,
+                                                                                            "activation_checkpoint": "full"})):
+        calls = []
+        orig = sharded_mod._native.call
+
+        def counting(sym, *a, _orig=orig, _calls=calls):
+            _calls.append(sym)
+            return _orig(sym, *a)
+        sharded_mod._native.call = counting
+        try:
+            cfg, eng = _small_engine(**kw)
+            g = torch.Generator().manual_seed(100 + rank)
+            losses = [eng.train_step(torch.randint(0, cfg.vocab_size, (1, 512), generator=g).cuda()) for _ in range(3)]
+            torch.cuda.synchronize()
+            eng.sdp.check_health()
+        finally:
+            sharded_mod._native.call = orig
+        with eng.sdp.full_parameters():
+            flat = torch.cat([p.detach().float().reshape(-1) for p in eng.model.parameters()]).clone()
+        results[name] = (losses, flat)
+        fused = calls.count("ttcd_wgather_gemm")
+        plain = calls.count("ttcd_peer_gather")
+        if name == "resident":
+            assert fused == 0 and plain == 0
+        elif name == "sharded":          # 2 blocks x 3 steps: fused in forward, stand-alone for backward (+ the final read)
+            assert fused == 6 and plain >= 6, (fused, plain)
+        else:                            # with recomputation the backward's gather is fused too
+            assert fused == 12, (fused, plain)
+        other = flat.clone()
+        dist.broadcast(other, src=0)
+        assert torch.equal(other, flat), f"{name}: parameters differ between ranks"
+        del eng
+        torch.cuda.synchronize()
+    base_l, base_f = results["resident"]
+    for name in ("sharded", "sharded_ac"):
+        l, f = results[name]
+        assert abs(l[0] - base_l[0]) < 1e-3 and abs(l[-1] - base_l[-1]) < 5e-2, (name, l, base_l)
+        assert (f - base_f).abs().max().item() < 2e-2, (name, (f - base_f).abs().max().item())
+
+
 def main():
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -164,6 +212,8 @@ def main():
         from tests.multi_gpu_tp import check_tensor_parallel, check_tp_model
         check_tensor_parallel()
         check_tp_model()
+    if what in ("all", "zero3"):
+        check_sharded_weights()
     if what in ("all", "late_rank"):
         check_late_rank_is_detected_and_the_step_skipped()
     if what in ("all", "accum"):

@@ -75,3 +75,8 @@ def test_late_rank_expires_the_peer_wait_and_every_rank_skips_the_step():
 @pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
 def test_gradient_accumulation_reduces_once_on_gpus():
     _launch("accum", 2)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
+def test_sharded_weights_gathered_inside_the_first_gemm():
+    _launch("zero3", 2)

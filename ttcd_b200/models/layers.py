@@ -324,6 +324,10 @@ def _fused_qkv(attn: Attention, x):
                 from ..ops import cuda
                 cuda.GradSlab.tag(out, [w.shape[0] for w in ws])      # their gradients will meet in one buffer
             return out
+    handle = getattr(attn.q_proj.weight, "_ttcd_gather", None)
+    if handle is not None:              # sharded weights: no fused projection will gather the block, do it now
+        attn.q_proj.weight._ttcd_gather = None
+        handle.ensure()
     return (ops.linear(x, attn.q_proj.weight, attn.q_proj.bias),
             ops.linear(x, attn.k_proj.weight, attn.k_proj.bias),
             ops.linear(x, attn.v_proj.weight, attn.v_proj.bias))

@@ -223,17 +223,31 @@ def gemm_wgrad(g: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
     return part.sum(0).to(_BF16)
 
 
+_gather_handle = None      # sharded-weights mode: the PendingGather of the projection being run (set by fused_linear)
+
+
 class _Linear(torch.autograd.Function):
     """y = x @ W^T for one or several weights that share x (one GEMM when they form a slab)."""
 
     @staticmethod
     def forward(ctx, x, slab, *weights):
+        global _gather_handle
+        handle, _gather_handle = _gather_handle, None
         x2 = _dense_rows(x)
+        if handle is not None and slab is None:
+            handle.ensure()            # no single slab to gather into a GEMM: gather first
         w = slab if slab is not None else (weights[0] if len(weights) == 1 else torch.cat(weights, dim=0))
         ctx.save_for_backward(x2, w)
         ctx.x_shape = x.shape
         ctx.splits = [wi.shape[0] for wi in weights]
-        y = keep(lambda: gemm(x2, w.transpose(0, 1))).view(x2.shape[0], w.shape[0])
+
+        def run():
+            # sharded weights: this GEMM is the block's first consumer and gathers the block while it multiplies
+            y_ = handle.linear(x2, w) if handle is not None else None
+            return y_ if y_ is not None else gemm(x2, w.transpose(0, 1))
+        y = keep(run).view(x2.shape[0], w.shape[0])
+        if handle is not None:
+            handle.ensure()            # a replayed (not re-launched) GEMM gathered nothing
         if len(weights) == 1:
             return y.view(*x.shape[:-1], w.shape[0])
         outs, col = [], 0
@@ -299,9 +313,14 @@ def linear(x, weight, bias=None):
 
 def fused_linear(x, weights, slab):
     """Several projections of the same input; returns a tuple of column views of one output."""
+    global _gather_handle
     ws = [w if w.dtype == _BF16 else w.to(_BF16) for w in weights]
     if any(w.dtype != weights[i].dtype for i, w in enumerate(ws)):
         slab = None
+    handle = getattr(weights[0], "_ttcd_gather", None)
+    if handle is not None:
+        weights[0]._ttcd_gather = None
+        _gather_handle = handle if handle.pending else None
     return _Linear.apply(x, slab, *ws)
 
 

@@ -20,7 +20,13 @@ to free its bf16 weights between uses, so this runtime is organised around that:
 * a peer wait that runs out (a rank more than the wait budget late) sets a device-side word that every rank's
   optimizer kernels of that step honour (the step is skipped everywhere, agreed through the gradient-norm
   all-reduce), and ``check_health()`` turns it into an exception at the next point that already synchronises;
-* with gradient accumulation the reduction runs once, after the last micro-batch (``set_last_microbatch``).
+* with gradient accumulation the reduction runs once, after the last micro-batch (``set_last_microbatch``);
+* ``shard_weights=True`` (the reference's ZeRO-3 / ``fully_shard`` layout, flame/models/parallelize_fla.py:436-497):
+  a block's bf16 parameters are stored 1/world per rank and exist in full only while the block runs.  The gather is
+  fused into the block's first GEMM (``csrc/gemm_comm.cu::wgather_gemm``: the fused q|k|v projection pulls every
+  rank's shard of the whole block into a pooled buffer while it multiplies, tile flags ordering the two); the buffer
+  is handed back after the block's forward and gathered again for its backward.  The root group (embeddings, final
+  norm, LM head) stays resident.
 
 ``world_size == 1`` degenerates to flat buffers + fused AdamW with no communication.
 """
@@ -50,7 +56,8 @@ class ParamGroup:
     names: list[str]
     offsets: list[int] = field(default_factory=list)
     numel: int = 0             # padded to a multiple of 8 * world
-    base: int = 0              # element offset of this group inside the symmetric buffers
+    base: int = 0              # element offset of this group inside the symmetric gradient buffer
+    pbase: int = 0             # element offset inside the symmetric (resident) parameter buffer
     total: int = 0             # numel (AdamW region) + the Muon-owned parameters laid out after it
     muon: list = field(default_factory=list)   # MuonParam entries of this group
     flat_param: torch.Tensor | None = None   # bf16 [numel]
@@ -62,6 +69,58 @@ class ParamGroup:
     grad_full32: torch.Tensor | None = None  # fp32 [numel] staging for the reduce-scatter (world > 1)
     reduce_event: torch.cuda.Event | None = None
     pending_hooks: int = 0
+    # sharded-weights mode (block groups only)
+    sharded: bool = False
+    shard_store: torch.Tensor | None = None  # bf16 [numel / world]: this rank's persistent shard of the parameters
+    shard_base: int = 0                      # element offset of the shard inside the symmetric shard buffer
+    head_elems: int = 0                      # leading elements that hold the < 2-D parameters (needed before the first GEMM)
+    ready: torch.Tensor | None = None        # int32 [units]: flags of the fused gather
+    epoch: int = 0
+    pool_slot: int = -1                      # pooled full buffer currently holding the gathered parameters (-1: none)
+    fixed_slot: int = 0                      # the pooled buffer this block always uses (block index % 2)
+    gather: object = None                    # PendingGather while the block waits for its first GEMM
+    in_backward: bool = False
+
+
+class PendingGather:
+    """A block whose sharded parameters are to be gathered by its first GEMM.
+
+    ``linear(x, w)`` is called by the fused q|k|v projection: when the shapes fit the fused kernel it runs
+    ``ttcd_wgather_gemm`` (the GEMM pulls every rank's shard of the whole block into the pooled buffer while it
+    multiplies); otherwise it gathers with the stand-alone kernel and returns None so that the caller runs its
+    ordinary GEMM.  Either way the block's parameters are complete, by stream order, for every later kernel."""
+
+    def __init__(self, sdp, group, flat, shard_ptrs, shard_elems):
+        self.sdp, self.group, self.flat, self.ptrs, self.shard = sdp, group, flat, shard_ptrs, shard_elems
+        self.pending = True
+
+    def ensure(self) -> None:
+        if self.pending:
+            self.pending = False
+            _native.call("ttcd_peer_gather", _native.ptr(self.flat), self.ptrs, _native.i32(self.sdp.world),
+                         _native.i64(self.shard), _native.stream_ptr())
+
+    def linear(self, x2: torch.Tensor, w: torch.Tensor):
+        """y = x2 @ w^T with ``w`` [N, K] a contiguous slice of the block's flat buffer; None if the shapes do not fit."""
+        if not self.pending:
+            return None
+        M, K = x2.shape
+        N = w.shape[0]
+        off = (w.data_ptr() - self.flat.data_ptr()) // 2
+        fits = (M % 128 == 0 and N % 256 == 0 and K % 64 == 0 and x2.stride(1) == 1 and x2.stride(0) % 8 == 0
+                and w.is_contiguous() and 0 <= off and off + N * K <= self.flat.numel() and off % 8 == 0
+                and x2.data_ptr() % 16 == 0)
+        if not fits:
+            self.ensure()
+            return None
+        self.pending = False
+        g = self.group
+        y = torch.empty(M, N, dtype=x2.dtype, device=x2.device)
+        _native.call("ttcd_wgather_gemm", _native.ptr(x2), _native.ptr(y), _native.ptr(self.flat), self.ptrs, _native.ptr(g.ready),
+                     _native.i32(self.sdp.rank), _native.i32(self.sdp.world), _native.i64(M), _native.i64(N), _native.i64(K),
+                     _native.i64(x2.stride(0)), _native.i64(N), _native.i64(off), _native.i64(self.shard), _native.i32(0),
+                     _native.i32(g.epoch), _native.i64(self.sdp.peer_wait_ns), _native.stream_ptr())
+        return y
 
 
 class ShardedDataParallel:
@@ -72,7 +131,7 @@ class ShardedDataParallel:
                  eps: float = 1e-8, weight_decay: float = 0.1, max_norm: float | None = 1.0,
                  param_dtype: torch.dtype = torch.bfloat16, overlap: bool = True, comm: str | None = None,
                  muon: bool = False, muon_momentum: float = 0.95, muon_filter=None, peer_wait_ns: int = 0,
-                 replicate_group: dist.ProcessGroup | None = None):
+                 replicate_group: dist.ProcessGroup | None = None, shard_weights: bool = False):
         """``comm``: 'peer' = fused peer-memory kernels over NVLink (default on CUDA with the native
         library), 'nccl' = the NCCL reduce-scatter / all-gather baseline (also TTCD_COMM=nccl).
         ``peer_wait_ns``: budget of one peer-flag wait (0: the library default of 10 s).
@@ -80,6 +139,7 @@ class ShardedDataParallel:
         ``process_group`` shards the optimizer state, and the ranks of ``replicate_group`` (one per shard group,
         holding the same shard) average their reduced gradient shards with an all-reduce before the update."""
         import os
+        self.shard_weights = bool(shard_weights)
         self.replicate_pg = replicate_group
         self.replicate_world = dist.get_world_size(replicate_group) if replicate_group is not None else 1
         self.peer_wait_ns = int(peer_wait_ns or os.environ.get("TTCD_PEER_WAIT_NS", "0"))
@@ -117,6 +177,8 @@ class ShardedDataParallel:
         self.skip_nan_inf = False
         if self.world > 1:
             self._install_hooks()
+        if self.shard_weights and self.world > 1:
+            self._install_shard_hooks(blocks)
 
     # ---------------------------------------------------------------------------------- layout
     def _build_groups(self, blocks):
@@ -145,11 +207,20 @@ class ShardedDataParallel:
                       and p.numel() % 8 == 0]      # 16-byte granules for the vectorised pull/push kernels
             chosen_ids = {id(p) for p, _ in chosen}
             adam = [(p, n) for p, n in pairs if id(p) not in chosen_ids]
+            g.sharded = self.shard_weights and self.world > 1 and g.name != "root"
+            if g.sharded:
+                if chosen:
+                    raise NotImplementedError("sharded weights are not combined with Muon (it needs whole matrices)")
+                adam.sort(key=lambda pn: 0 if pn[0].dim() < 2 else 1)     # norm weights etc. first: needed before the first GEMM
             off = 0
             for p, _ in adam:
                 g.offsets.append(off)
                 off += _align(p.numel(), 8)          # 16-byte aligned starts (TMA / vector loads)
-            g.numel = _align(off, 8 * self.world)    # AdamW region: sharded 1/world by flat position
+            if g.sharded:
+                g.head_elems = sum(_align(p.numel(), 8) for p, _ in adam if p.dim() < 2)
+                g.numel = _align(off, 32768 * self.world)      # 64 KB units per shard: flag granularity of the fused gather
+            else:
+                g.numel = _align(off, 8 * self.world)    # AdamW region: sharded 1/world by flat position
             off = g.numel
             for p, n in chosen:                      # Muon region: whole parameters, owned by one rank each
                 g.offsets.append(off)
@@ -162,24 +233,51 @@ class ShardedDataParallel:
             g.names = [n for _, n in adam] + [n for _, n in chosen]
         assign_owners(self.muon_params, self.world)
         total = sum(g.total for g in groups)
+        shard_total = sum(g.numel // self.world for g in groups if g.sharded)
+        self.sym_shards = None
+        if shard_total:
+            esz = torch.empty((), dtype=self.param_dtype).element_size()
+            if self.peer:
+                from ..comm.symmetric import SymmetricBuffer
+                self.sym_shards = SymmetricBuffer(shard_total * esz, self.pg, self.device)
+                shard_flat = self.sym_shards.view(self.param_dtype, shard_total, 0)
+            else:
+                shard_flat = torch.zeros(shard_total, dtype=self.param_dtype, device=self.device)
+            pool_numel = max(g.total for g in groups if g.sharded)
+            self._pool = [torch.empty(pool_numel, dtype=self.param_dtype, device=self.device) for _ in range(2)]
+            self._pool_owner: list = [None, None]
         if self.peer:
             # flat parameters and gradients live in peer-addressable memory: the fused kernels read every
             # rank's gradients and write every rank's parameters directly over NVLink
             from ..comm.symmetric import PeerBarrier, SymmetricBuffer
             esize = torch.empty((), dtype=self.param_dtype).element_size()
-            self.sym_params = SymmetricBuffer(total * esize, self.pg, self.device)
+            resident = sum(g.total for g in groups if not g.sharded)
+            self.sym_params = SymmetricBuffer(max(resident, 8) * esize, self.pg, self.device)
             self.sym_grads = SymmetricBuffer(total * esize, self.pg, self.device)
             self.barrier = PeerBarrier(self.pg, slots=4, wait_ns=self.peer_wait_ns, fail=self._stats[1:2])
         base = 0
+        pbase = 0
+        sbase = 0
         for g in groups:
             g.base = base
+            g.pbase = pbase
             if self.peer:
-                g.flat_param = self.sym_params.view(self.param_dtype, g.total, base * esize)
+                if g.sharded:       # a temporary full copy, only to lay the parameters out
+                    g.flat_param = torch.zeros(g.total, dtype=self.param_dtype, device=self.device)
+                else:
+                    g.flat_param = self.sym_params.view(self.param_dtype, g.total, pbase * esize)
+                    pbase += g.total
                 g.flat_grad = self.sym_grads.view(self.param_dtype, g.total, base * esize)
             else:
                 g.flat_param = torch.zeros(g.total, dtype=self.param_dtype, device=self.device)
                 g.flat_grad = torch.zeros(g.total, dtype=self.param_dtype, device=self.device)
             base += g.total
+            if g.sharded:
+                g.shard_base = sbase
+                g.shard_store = shard_flat[sbase:sbase + g.numel // self.world]
+                sbase += g.numel // self.world
+                if self.peer:
+                    g.ready = torch.zeros(g.numel * 2 // 65536, dtype=torch.int32, device=self.device)
             for p, o in zip(g.params, g.offsets):
                 view = g.flat_param[o:o + p.numel()].view(p.shape)
                 view.copy_(p.data)
@@ -188,6 +286,8 @@ class ShardedDataParallel:
             shard = g.numel // self.world
             lo = self.rank * shard
             g.master = g.flat_param[lo:lo + shard].float()
+            if g.sharded:
+                g.shard_store.copy_(g.flat_param[lo:lo + shard])
             g.exp_avg = torch.zeros(shard, dtype=torch.float32, device=self.device)
             g.exp_avg_sq = torch.zeros(shard, dtype=torch.float32, device=self.device)
             if self.world > 1:
@@ -201,12 +301,27 @@ class ShardedDataParallel:
                     mp.momentum = torch.zeros(n, dtype=torch.float32, device=self.device)
                     mp.grad32 = torch.zeros(_align(n, 8), dtype=torch.float32, device=self.device)
         self.groups = groups
+        if shard_total:
+            # the full copies of the sharded groups were only needed to lay the parameters out: the symmetric parameter
+            # buffer keeps the root group, the blocks' parameters now live in the shards and, while a block runs, in a
+            # pooled buffer
+            for g in groups:
+                if g.sharded:
+                    g.flat_param = None
+                    self._point_params(g, self._pool[0])
+
+    def _own_slice(self, g: ParamGroup) -> torch.Tensor:
+        """This rank's 1/world of the group's bf16 parameters (a slice of the resident flat buffer, the persistent
+        shard, or, inside ``full_parameters()``, a slice of the temporary full copy)."""
+        shard = g.numel // self.world
+        if g.sharded and g.flat_param is None:
+            return g.shard_store
+        return g.flat_param[self.rank * shard:(self.rank + 1) * shard]
 
     def resync_master(self) -> None:
         """Re-derive the fp32 master shards from the current bf16 parameters (after a weight load)."""
         for g in self.groups:
-            shard = g.numel // self.world
-            g.master.copy_(g.flat_param[self.rank * shard:(self.rank + 1) * shard].float())
+            g.master.copy_(self._own_slice(g).float())
             for mp in g.muon:
                 if mp.master is not None:
                     mp.master.copy_(g.flat_param[mp.offset:mp.offset + mp.param.numel()].float())
@@ -232,6 +347,121 @@ class ShardedDataParallel:
                 a, b = max(o, lo), min(o + p.numel(), hi)
                 if a < b:
                     g.master[a - lo:b - lo].copy_(src[a - o:b - o])
+
+    # ---------------------------------------------------------------------------------- sharded weights
+    def _point_params(self, g: ParamGroup, flat: torch.Tensor) -> None:
+        for p, o in zip(g.params, g.offsets):
+            p.data = flat[o:o + p.numel()].view(p.shape)
+
+    def _install_shard_hooks(self, blocks) -> None:
+        by_name = {g.name: g for g in self.groups}
+        inner = getattr(self.model, "model", None)
+        for i, blk in enumerate(blocks or []):
+            g = by_name.get(f"block{i}")
+            if g is None or not g.sharded:
+                continue
+
+            def pre_fwd(module, args, g=g):
+                # first forward, or the recomputation inside backward: the block's first GEMM gathers (fused)
+                self._prepare_group(g, fused=True, module=module)
+
+            def post_fwd(module, args, out, g=g):
+                if not g.in_backward:
+                    self._release_group(g)
+
+            def pre_bwd(module, grad_out, g=g, blk=blk):
+                g.in_backward = True
+                recompute = bool(inner is not None and inner.gradient_checkpointing and inner._checkpoint_layer(blk))
+                if not recompute:           # the backward kernels are the first consumers: gather up front
+                    self._prepare_group(g, fused=False, module=module)
+
+            def post_bwd(module, grad_in, grad_out, g=g):
+                g.in_backward = False
+                self._release_group(g)
+
+            g.fixed_slot = i % 2
+            blk.register_forward_pre_hook(pre_fwd)
+            blk.register_forward_hook(post_fwd)
+            blk.register_full_backward_pre_hook(pre_bwd)
+            blk.register_full_backward_hook(post_bwd)
+
+    def _prepare_group(self, g: ParamGroup, fused: bool, module=None) -> None:
+        """Make the group's parameters addressable in full: take a pooled buffer, point the parameters at it and
+        fill it, either at once (``fused=False``: one gather kernel / all-gather) or, for everything past the small
+        1-D parameters, inside the block's first GEMM (``fused=True``; see ``PendingGather``)."""
+        if g.pool_slot >= 0:
+            return
+        # a block always lands in the same pooled buffer: tensors that autograd saved in the forward (weights are saved
+        # as views) must find the re-gathered values at the same addresses in the backward
+        slot = g.fixed_slot
+        if self._pool_owner[slot] is not None:
+            raise RuntimeError(f"sharded weights: pooled buffer {slot} is still held by {self._pool_owner[slot].name} "
+                               f"when {g.name} needs it (blocks must run one after the other)")
+        self._pool_owner[slot] = g
+        g.pool_slot = slot
+        flat = self._pool[slot][:g.total]
+        self._point_params(g, flat)
+        shard = g.numel // self.world
+        if not self.peer:
+            dist.all_gather_into_tensor(flat[:g.numel], g.shard_store, group=self.pg)      # NCCL / gloo statement
+            return
+        ptrs = self.sym_shards.ptr_array(g.shard_base * 2)
+        attn = getattr(module, "attn", None)
+        if fused and attn is not None and hasattr(attn, "q_proj"):
+            # the 1-D parameters (norm weights ...) are read before the first GEMM: they sit at the head of rank 0's shard
+            if g.head_elems:
+                _native.call("ttcd_peer_add", _native.ptr(flat), _native.i64(self.sym_shards.peer_ptrs[0] + g.shard_base * 2),
+                             _native.i64(g.head_elems), _native.i32(0), _native.stream_ptr())
+            g.epoch += 1
+            g.gather = PendingGather(self, g, flat, ptrs, shard)
+            attn.q_proj.weight._ttcd_gather = g.gather
+            return
+        _native.call("ttcd_peer_gather", _native.ptr(flat), ptrs, _native.i32(self.world), _native.i64(shard), _native.stream_ptr())
+
+    def _release_group(self, g: ParamGroup) -> None:
+        if g.pool_slot < 0:
+            return
+        if g.gather is not None:
+            g.gather.pending = False
+        g.gather = None
+        self._pool_owner[g.pool_slot] = None
+        g.pool_slot = -1
+
+    def full_parameters(self):
+        """Context manager: every sharded group's parameters materialised in full (checkpoint save / load,
+        evaluation).  On exit this rank's slices are written back to its shards and the full copies dropped."""
+        from contextlib import contextmanager
+
+        @contextmanager
+        def ctx():
+            held = []
+            for g in self.groups:
+                if not g.sharded:
+                    continue
+                self._release_group(g)
+                full = torch.empty(g.total, dtype=self.param_dtype, device=self.device)
+                shard = g.numel // self.world
+                if self.peer:
+                    _native.call("ttcd_peer_gather", _native.ptr(full), self.sym_shards.ptr_array(g.shard_base * 2),
+                                 _native.i32(self.world), _native.i64(shard), _native.stream_ptr())
+                else:
+                    dist.all_gather_into_tensor(full[:g.numel], g.shard_store, group=self.pg)
+                g.flat_param = full
+                self._point_params(g, full)
+                held.append(g)
+            try:
+                yield self
+            finally:
+                for g in held:
+                    shard = g.numel // self.world
+                    g.shard_store.copy_(g.flat_param[self.rank * shard:(self.rank + 1) * shard])
+                    g.flat_param = None
+                    self._point_params(g, self._pool[0])
+                if held and self.world > 1:
+                    if self.device.type == "cuda":
+                        torch.cuda.synchronize(self.device)
+                    dist.barrier(group=self.pg)          # every rank's shard is written before anyone gathers again
+        return ctx()
 
     # ---------------------------------------------------------------------------------- reduce-scatter
     def _install_hooks(self):
@@ -413,13 +643,25 @@ class ShardedDataParallel:
         for g in self.groups:
             shard = g.numel // self.world
             lo = self.rank * shard
+            if g.sharded:
+                # sharded weights: the update stays in this rank's shard; the next use gathers it
+                if self.use_native:
+                    from ..ops import cuda
+                    cuda.adamw_step(g.master, g.grad_shard, g.exp_avg, g.exp_avg_sq, g.shard_store, lr=lr, beta1=b1, beta2=b2,
+                                    eps=self.eps, weight_decay=self.weight_decay, step=self.step_count, coef=self._coef,
+                                    skip=self._skip if (self.skip_nan_inf or self.peer) else None)
+                elif not (self.skip_nan_inf and bool(self._skip)):
+                    ref_ops.adamw_step(g.master, g.grad_shard.float() * self._coef, g.exp_avg, g.exp_avg_sq, lr=lr, beta1=b1,
+                                       beta2=b2, eps=self.eps, weight_decay=self.weight_decay, step=self.step_count)
+                    g.shard_store.copy_(g.master)
+                continue
             out_slice = g.flat_param[lo:lo + shard]
             if self.peer:
                 bc1 = 1.0 - b1 ** self.step_count
                 bc2_sqrt = math.sqrt(1.0 - b2 ** self.step_count)
                 _native.call("ttcd_adamw_push", _native.ptr(g.master), _native.ptr(g.grad_shard), _native.ptr(g.exp_avg),
                              _native.ptr(g.exp_avg_sq), self.sym_params.ptr_array(), _native.i32(self.world),
-                             _native.i64(g.base + lo), _native.i64(shard), _native.f32(lr), _native.f32(b1), _native.f32(b2),
+                             _native.i64(g.pbase + lo), _native.i64(shard), _native.f32(lr), _native.f32(b1), _native.f32(b2),
                              _native.f32(self.eps), _native.f32(self.weight_decay), _native.f32(bc1), _native.f32(bc2_sqrt),
                              _native.ptr(self._coef), _native.ptr(self._skip), _native.stream_ptr())
                 continue
@@ -469,7 +711,7 @@ class ShardedDataParallel:
                 if self.peer:
                     n8 = n // 8 * 8
                     _native.call("ttcd_push_cast", _native.ptr(mp.master), self.sym_params.ptr_array(), _native.i32(self.world),
-                                 _native.i64(g.base + mp.offset), _native.i64(n8), _native.stream_ptr())
+                                 _native.i64(g.pbase + mp.offset), _native.i64(n8), _native.stream_ptr())
                     if n8 != n:
                         dst[n8:].copy_(mp.master[n8:])
                 else:
@@ -508,10 +750,11 @@ class ShardedDataParallel:
         for g in self.groups:
             s = state["groups"][g.name]
             g.master.copy_(s["master"]); g.exp_avg.copy_(s["exp_avg"]); g.exp_avg_sq.copy_(s["exp_avg_sq"])
-            shard = g.numel // self.world
-            g.flat_param[self.rank * shard:(self.rank + 1) * shard].copy_(g.master)
+            self._own_slice(g).copy_(g.master)
         if self.world > 1:
             for g in self.groups:
+                if g.sharded:
+                    continue
                 shard = g.numel // self.world
                 dist.all_gather_into_tensor(g.flat_param, g.flat_param[self.rank * shard:(self.rank + 1) * shard].clone(),
                                             group=self.pg)

@@ -172,12 +172,13 @@ class CheckpointManager:
 
     def _model_state(self, dtype: torch.dtype | None = None) -> dict[str, torch.Tensor]:
         """Full-precision model tensors rebuilt from the fp32 master shards (tied weights written twice)."""
-        full = self.engine.sdp.gather_full("master")
         out = {}
-        for name, p in self.engine.model.state_dict().items():
-            src = full.get(p.data_ptr())
-            t = src if src is not None else p.detach().float()
-            out[name] = t.to(dtype) if dtype is not None else t
+        with self.engine.sdp.full_parameters():        # sharded weights: every parameter addressable (and distinct) in full
+            full = self.engine.sdp.gather_full("master")
+            for name, p in self.engine.model.state_dict().items():
+                src = full.get(p.data_ptr())
+                t = src if src is not None else p.detach().float().clone()
+                out[name] = t.to(dtype) if dtype is not None else t
         tp = getattr(self.engine, "tp", None)
         if tp is not None:
             from ..parallel.tensor import gather_named
@@ -265,11 +266,12 @@ class CheckpointManager:
         t0 = time.perf_counter()
         try:
             as_saved: dict[int, torch.Tensor] = {}
-            load_model_weights(self.engine.model, path, self.exclude, loaded=as_saved)
-            self.engine.sdp.resync_master()
-            # checkpoints written by this trainer hold the fp32 masters: take them as they are, so that a resumed
-            # run continues from exactly the weights the interrupted one had (not from their bf16 rounding)
-            self.engine.sdp.load_full_master(as_saved)
+            with self.engine.sdp.full_parameters():
+                load_model_weights(self.engine.model, path, self.exclude, loaded=as_saved)
+                self.engine.sdp.resync_master()
+                # checkpoints written by this trainer hold the fp32 masters: take them as they are, so that a resumed
+                # run continues from exactly the weights the interrupted one had (not from their bf16 rounding)
+                self.engine.sdp.load_full_master(as_saved)
             keys = checkpoint_keys(path)
             if not weights_only and any(k.startswith("optimizer.") for k in keys):
                 self._load_training_state(path, keys)

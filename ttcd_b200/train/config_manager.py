@@ -94,7 +94,9 @@ SPEC: list[tuple] = [
     ("training.enable_cpu_offload", FLAG, False, ""),
     ("training.tensor_parallel_degree", int, 1, ""),
     ("training.disable_loss_parallel", FLAG, False, ""),
-    ("training.fsdp_reshard_after_forward", str, "default", "default | always | never"),
+    ("training.fsdp_reshard_after_forward", str, "default",
+     "default | never: bf16 weights stay resident on every rank (they fit a 180 GB GPU); always: ZeRO-3, a block's weights "
+     "are stored 1/world per rank and gathered inside its first GEMM, for forward and again for backward"),
     ("training.mixed_precision_param", str, "bfloat16", ""),
     ("training.mixed_precision_reduce", str, "float32", ""),
     ("training.compile", FLAG, False, "accepted; this framework has no tracing compiler"),

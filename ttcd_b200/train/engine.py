@@ -27,6 +27,7 @@ class EngineConfig:
     max_norm: float | None = 1.0
     replicate: bool = False                   # DDP-style replicated optimizer state + gradient all-reduce (fallback path)
     replicate_degree: int = 1                 # hybrid sharding: this many shard groups, gradients averaged across them
+    shard_weights: bool = False               # ZeRO-3: block parameters stored 1/world per rank, gathered inside the first GEMM
     activation_offload: bool = False          # saved activations -> pinned host memory on a side stream
     activation_checkpoint: str = "full"       # full | none | everyN (every Nth block) | ttt (TTT blocks only) | op (cheap ops only)
     dtype: torch.dtype = torch.bfloat16
@@ -106,6 +107,10 @@ class TrainEngine:
                         process_group = g
                 self._tp_dp = True
         extra = {}
+        if self.cfg.shard_weights:
+            if self.tp is not None or getattr(self, "cp", None) is not None or self.cfg.replicate:
+                raise NotImplementedError("sharded weights are combined with plain sharded data parallelism only")
+            extra["shard_weights"] = True
         if self.cfg.replicate_degree > 1 and not self.cfg.replicate:
             # hybrid sharding (replicate x shard): rank = r * S + s; a shard group holds the ranks with the same r,
             # a replicate group the ranks with the same s

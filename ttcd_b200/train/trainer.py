@@ -204,6 +204,7 @@ def main(job_config: JobConfig) -> None:
                         muon_momentum=opt.muon_momentum, tensor_parallel=tp, context_parallel=cp,
                         activation_offload=job_config.activation_offload.mode not in ("none", "", None),
                         replicate=(tr.data_parallel_shard_degree == 1 and tr.data_parallel_replicate_degree not in (0, 1)),
+                        shard_weights=tr.fsdp_reshard_after_forward == "always",
                         replicate_degree=(tr.data_parallel_replicate_degree
                                           if tr.data_parallel_shard_degree != 1 and tr.data_parallel_replicate_degree > 1 else 1))
     engine = TrainEngine(model_config, ecfg, device=device)
