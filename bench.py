@@ -61,6 +61,7 @@ def parse_args():
     ap.add_argument("--ref-ac", default="auto", choices=["auto", "none", "full"],
                     help="reference arm: 'auto' runs without activation checkpointing if that fits, else with full")
     ap.add_argument("--no-extra", action="store_true", help="skip the ac_full and context-parallel extras")
+    ap.add_argument("--muon", action="store_true", help="Muon on the 2-D hidden weights, AdamW on the rest")
     ap.add_argument("--worker", default=None, choices=["cp", "zero3"], help=argparse.SUPPRESS)
     return ap.parse_args()
 
@@ -169,7 +170,8 @@ def run_ours(args):
     if args.layers is not None:
         overrides["num_hidden_layers"] = args.layers
     cfg = load_model_config(args.config, **overrides)
-    engine = TrainEngine(cfg, EngineConfig(activation_checkpoint="none" if args.no_ac else args.ac), device=f"cuda:{local}")
+    engine = TrainEngine(cfg, EngineConfig(activation_checkpoint="none" if args.no_ac else args.ac, enable_muon=args.muon),
+                         device=f"cuda:{local}")
     B, S, V = args.batch_per_gpu, args.seq_len, cfg.vocab_size
     n_total = args.warmup + 2 * args.steps
     gen = torch.Generator().manual_seed(1234 + rank)
@@ -224,7 +226,7 @@ def run_ours(args):
             "impl": "ours",
             "config": {"model": Path(args.config).stem, "global_batch": B * world, "seq_len": S,
                        "parallelism": f"sharded-dp{world}", "activation_checkpointing": ac_mode,
-                       "optimizer": "AdamW", "l2": "per-step working set (several GB) exceeds the 126 MB L2",
+                       "optimizer": "Muon+AdamW" if args.muon else "AdamW", "l2": "per-step working set (several GB) exceeds the 126 MB L2",
                        "layers": cfg.num_hidden_layers},
             "clocks": clocks,
             "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e / args.steps, 2),

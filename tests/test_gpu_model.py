@@ -135,3 +135,37 @@ def test_small_query_attention_kernel(Tq, Tk, H, HK, D, W):
     want = ref.attention(q.float(), k.float(), v.float(), W)
     err = (got.float() - want).abs()
     assert err.max() < 2e-2, float(err.max())
+
+
+def _distinct_shapes():
+    import glob
+    import json
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1] / "configs"
+    seen = {}
+    for f in sorted(glob.glob(str(root / "*" / "*.json"))):
+        d = json.loads(Path(f).read_text())
+        hs, nh = d.get("hidden_size"), d.get("num_heads")
+        key = (d["model_type"], hs, nh, d.get("num_kv_heads"), d.get("head_dim"), d.get("intermediate_size"), d.get("hidden_ratio"),
+               bool(d.get("qk_norm")), d.get("window_size") is None)
+        seen.setdefault(key, f)
+    return sorted(seen.values())
+
+
+@pytest.mark.parametrize("path", _distinct_shapes(), ids=lambda p: p.split("/")[-1][:-5])
+def test_every_shipped_shape_runs_one_layer(path):
+    """One block of every distinct (model type, widths, heads) among the shipped configs: forward, backward and an
+    optimizer step on the native path (hidden 4096 takes the wide-row norm kernels, head_dim 80 / 96 the PyTorch
+    attention, 15 / 5 heads the masked tile edges)."""
+    from ttcd_b200.train.engine import load_model_config
+    cfg = load_model_config(path, num_hidden_layers=1, vocab_size=4096, max_position_embeddings=2048)
+    if getattr(cfg, "ttt_layers", None):
+        cfg.ttt_layers = [0]
+        cfg.ttt_chunk = 256
+    if getattr(cfg, "window_size", None):
+        cfg.window_size = min(cfg.window_size, 384)
+    eng = TrainEngine(cfg, EngineConfig(lr=1e-3, activation_checkpoint="none"), device=DEV)
+    ids = torch.randint(0, 4096, (1, 1024), device=DEV)
+    l0 = eng.train_step(ids)
+    l1 = eng.train_step(ids)
+    assert l0 == l0 and l1 == l1 and l1 < l0 + 0.5, (l0, l1)

@@ -745,6 +745,22 @@ def _too_short(q, k) -> bool:
     return q.shape[1] < 128 or k.shape[1] < 128
 
 
+_warned_head_dims: set[int] = set()
+
+
+def _unsupported_head_dim(q) -> bool:
+    """The tensor-core attention kernels are built for head_dim 64 and 128 (every recipe of the reference); other
+    widths (80 and 96 appear in two of its generic transformer configs) run the PyTorch statement, said once."""
+    D = q.shape[-1]
+    if D in (64, 128):
+        return False
+    if D not in _warned_head_dims:
+        _warned_head_dims.add(D)
+        import warnings
+        warnings.warn(f"attention with head_dim {D} runs the PyTorch statement (the native kernels cover 64 and 128)")
+    return True
+
+
 def _packed_args(q, k, cu_seqlens):
     """Packed (varlen) rows are handled inside the kernels: one launch, per-token sequence bounds."""
     if cu_seqlens is None:
@@ -756,6 +772,8 @@ def _packed_args(q, k, cu_seqlens):
 
 def attention(q, k, v, window=None, scale=None, cu_seqlens=None, return_lse=False):
     _check(q, "q")
+    if _unsupported_head_dim(q):
+        return reference.attention(q, k, v, window, scale, cu_seqlens, return_lse)
     if _too_short(q, k):
         if cu_seqlens is None and not return_lse and not torch.is_grad_enabled() and attn_small_q_supported(q, k):
             return attn_small_q(q, k, v, window, scale)
@@ -768,7 +786,7 @@ def attention(q, k, v, window=None, scale=None, cu_seqlens=None, return_lse=Fals
 
 def dual_window_attention(q, k, v, window_teacher, window_student, scale=None, cu_seqlens=None):
     _check(q, "q")
-    if _too_short(q, k):
+    if _too_short(q, k) or _unsupported_head_dim(q):
         return reference.dual_window_attention(q, k, v, window_teacher, window_student, scale, cu_seqlens)
     scale = q.shape[-1] ** -0.5 if scale is None else scale
     seg_start, seg_end = _packed_args(q, k, cu_seqlens)

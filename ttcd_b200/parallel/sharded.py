@@ -695,19 +695,24 @@ class ShardedDataParallel:
         return norm
 
     def _step_muon(self, lr: float, cur) -> None:
-        """Owner-side Muon updates, then publication of the new bf16 weights to every rank."""
-        from ..train.muon import muon_update
+        """Owner-side Muon updates (same-shape matrices orthogonalised as one batch), then publication of the new
+        bf16 weights to every rank."""
+        from ..train.muon import muon_update_many
         coef = self._coef if self.max_norm is not None else None
+        owned = [mp for mp in self.muon_params if mp.owner == self.rank]
+        saved = {}
+        for mp in owned:
+            saved[id(mp)] = mp.grad32
+            mp.grad32 = mp.grad32[:mp.param.numel()]
+        muon_update_many(owned, lr, self.weight_decay, self.muon_momentum, coef,
+                         skip=self._skip if (self.skip_nan_inf or self.peer) else None)
+        for mp in owned:
+            mp.grad32 = saved[id(mp)]
         for mp in self.muon_params:
             g = self.groups[mp.group_index]
             n = mp.param.numel()
             dst = g.flat_param[mp.offset:mp.offset + n]
             if mp.owner == self.rank:
-                saved = mp.grad32
-                mp.grad32 = saved[:n]
-                muon_update(mp, lr, self.weight_decay, self.muon_momentum, coef,
-                            skip=self._skip if (self.skip_nan_inf or self.peer) else None)
-                mp.grad32 = saved
                 if self.peer:
                     n8 = n // 8 * 8
                     _native.call("ttcd_push_cast", _native.ptr(mp.master), self.sym_params.ptr_array(), _native.i32(self.world),

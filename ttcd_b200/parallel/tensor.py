@@ -50,6 +50,7 @@ class TensorParallel:
         self.device = torch.device(device if device is not None else "cpu")
         self.fused = (self.device.type == "cuda" and nv.available()) if fused is None else fused
         self.wait_ns = wait_ns
+        self._warned: set = set()
         self.rs_lag = 32              # gemm_rs schedule: own row blocks trail the pushes by 32 rounds (csrc/gemm_comm.cu::gc_tile)
         self.epoch = 0
         self.calls = 0
@@ -77,8 +78,16 @@ class TensorParallel:
 
     # ------------------------------------------------------------------------------- raw collectives+GEMM
     def _fits(self, m_shard: int, n: int, k: int) -> bool:
-        return (self.fused and m_shard % self.BM == 0 and n % self.BN == 0 and k % 64 == 0 and m_shard <= self.max_rows
-                and max(n, k) <= self.max_feat and (self.BM * k * 2) % 16384 == 0)
+        ok = (self.fused and m_shard % self.BM == 0 and n % self.BN == 0 and k % 64 == 0 and m_shard <= self.max_rows
+              and max(n, k) <= self.max_feat and (self.BM * k * 2) % 16384 == 0)
+        if not ok and self.fused and (m_shard, n, k) not in self._warned:
+            # said once per shape: the layer then runs NCCL + the plain GEMM instead of the fused kernel
+            self._warned.add((m_shard, n, k))
+            import logging
+            logging.getLogger("ttcd_b200").warning(
+                "tensor parallel: shape rows/rank=%d N=%d K=%d does not fit the fused GEMM+collective kernels "
+                "(rows %% 128, N %% 256, K %% 64, buffer sizes): using NCCL + GEMM for it", m_shard, n, k)
+        return ok
 
     def ag_gemm(self, x_shard: torch.Tensor, w: torch.Tensor, w_is_kn: bool = False):
         """``(all_gather_rows(x_shard) @ W^T, gathered)``.  ``w``: [N, K], or [K, N] when ``w_is_kn``."""

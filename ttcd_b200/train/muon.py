@@ -72,17 +72,44 @@ def muon_update(mp: MuonParam, lr: float, weight_decay: float, momentum: float, 
                 nesterov: bool = True, skip: torch.Tensor | None = None) -> torch.Tensor:
     """Owner-side update of one parameter; returns the new fp32 master (in place).  ``skip``: device int
     scalar, non-zero when the step must leave momentum and weights untouched (non-finite gradient norm)."""
-    g = mp.grad32 if coef is None else mp.grad32 * coef
-    new_mom = mp.momentum * momentum + g
-    g = g.add(new_mom, alpha=momentum) if nesterov else new_mom
-    u = orthogonalize(g.view(mp.param.shape)).float().reshape(-1)
-    rows, cols = mp.param.shape[-2], mp.param.shape[-1]      # last two dims also for >2-D parameters (707-716)
-    adj_lr = lr * 0.2 * math.sqrt(max(rows, cols))
-    new_master = (mp.master * (1.0 - lr * weight_decay)).add_(u, alpha=-adj_lr)
-    if skip is not None:
-        keep = skip == 0
-        new_mom = torch.where(keep, new_mom, mp.momentum)
-        new_master = torch.where(keep, new_master, mp.master)
-    mp.momentum.copy_(new_mom)
-    mp.master.copy_(new_master)
+    muon_update_many([mp], lr, weight_decay, momentum, coef, nesterov, skip)
     return mp.master
+
+
+def muon_update_many(params: list[MuonParam], lr: float, weight_decay: float, momentum: float,
+                     coef: torch.Tensor | None, nesterov: bool = True, skip: torch.Tensor | None = None) -> None:
+    """Owner-side update of several parameters.  Parameters of one shape are orthogonalised as ONE batched
+    Newton-Schulz call (15 GEMM launches for the whole group instead of 15 per matrix: the matrices of a 1024-wide
+    model are a handful of tiles each, so per-matrix launches are pure latency); the reference batches the same way
+    for its 3-D case (custom_components/muon_v2.py:68-110)."""
+    if not params:
+        return
+    pre = []                          # (param, momentum after this step, Nesterov-combined gradient)
+    for mp in params:
+        g = mp.grad32 if coef is None else mp.grad32 * coef
+        new_mom = mp.momentum * momentum + g
+        g = g.add(new_mom, alpha=momentum) if nesterov else new_mom
+        pre.append((mp, new_mom, g))
+    by_shape: dict[tuple, list[int]] = {}
+    for i, (mp, _, _) in enumerate(pre):
+        by_shape.setdefault(tuple(mp.param.shape), []).append(i)
+    updates: list[torch.Tensor | None] = [None] * len(pre)
+    for shape, idx in by_shape.items():
+        if len(shape) == 2 and min(shape) >= 64 and len(idx) > 1:
+            stacked = torch.stack([pre[i][2].view(shape) for i in idx])            # [n, rows, cols]
+            u = ops.newton_schulz(stacked).float()
+            for j, i in enumerate(idx):
+                updates[i] = u[j].reshape(-1)
+        else:
+            for i in idx:
+                updates[i] = orthogonalize(pre[i][2].view(shape)).float().reshape(-1)
+    for (mp, new_mom, _), u in zip(pre, updates):
+        rows, cols = mp.param.shape[-2], mp.param.shape[-1]      # last two dims also for >2-D parameters (707-716)
+        adj_lr = lr * 0.2 * math.sqrt(max(rows, cols))
+        new_master = (mp.master * (1.0 - lr * weight_decay)).add_(u, alpha=-adj_lr)
+        if skip is not None:
+            keep = skip == 0
+            new_mom = torch.where(keep, new_mom, mp.momentum)
+            new_master = torch.where(keep, new_master, mp.master)
+        mp.momentum.copy_(new_mom)
+        mp.master.copy_(new_master)
