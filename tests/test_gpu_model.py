@@ -169,3 +169,26 @@ def test_every_shipped_shape_runs_one_layer(path):
     l0 = eng.train_step(ids)
     l1 = eng.train_step(ids)
     assert l0 == l0 and l1 == l1 and l1 < l0 + 0.5, (l0, l1)
+
+
+@pytest.mark.parametrize("family", ["delta_net", "gated_deltanet"])
+def test_recurrent_family_decodes_from_its_state(family):
+    """bf16 on the native path (convolution, norm and GEMM kernels): prefill + token-by-token decoding from the state
+    cache against one forward over the whole row."""
+    from ttcd_b200.models import (DeltaNetConfig, DeltaNetForCausalLM, GatedDeltaNetConfig, GatedDeltaNetForCausalLM,
+                                  RecurrentCache)
+    torch.manual_seed(0)
+    if family == "delta_net":
+        model = DeltaNetForCausalLM(DeltaNetConfig(hidden_size=256, num_hidden_layers=2, num_heads=4, vocab_size=512))
+    else:
+        model = GatedDeltaNetForCausalLM(GatedDeltaNetConfig(hidden_size=256, num_hidden_layers=2, num_heads=2, head_dim=64,
+                                                             vocab_size=512))
+    model = model.to(DEV, torch.bfloat16).eval()
+    ids = torch.randint(0, 512, (2, 300), device=DEV)
+    with torch.no_grad():
+        full = model(input_ids=ids, use_cache=False).logits.float()
+        cache = RecurrentCache()
+        first = model(input_ids=ids[:, :290], past_key_values=cache, use_cache=True).logits
+        steps = [model(input_ids=ids[:, t:t + 1], past_key_values=cache, use_cache=True).logits for t in range(290, 300)]
+    got = torch.cat([first, *steps], dim=1).float()
+    assert _cos(got, full) > 0.999, _cos(got, full)

@@ -1,14 +1,17 @@
 """Model families and their HF Auto* registration.
 
-Importing this package registers ``transformer``, ``ipttt`` and ``ipttcdv9`` with
+Importing this package registers ``transformer``, ``ipttt``, ``ipttcdv9``, ``deltanet_baseline``, ``delta_net`` and
+``gated_deltanet`` with
 ``AutoConfig`` / ``AutoModel`` / ``AutoModelForCausalLM`` (the reference does the same on
 ``import custom_models``: custom_models/ipttcd/__init__.py:17-24, custom_models/ipttt/__init__.py).
 """
 from transformers import AutoConfig, AutoModel, AutoModelForCausalLM
 
-from .configuration import (DeltaNetBaselineConfig, IPTTCDConfig, IPTTCDv8Config, IPTTCDv9Config, IPTTCDv9LowCopyConfig, IPTTTConfig,
+from .configuration import (DeltaNetBaselineConfig, DeltaNetConfig, GatedDeltaNetConfig, IPTTCDConfig, IPTTCDv8Config, IPTTCDv9Config, IPTTCDv9LowCopyConfig, IPTTTConfig,
                             TransformerConfig)
 from .layers import Attention, GatedMLP, RMSNorm, RotaryEmbedding, WindowKVCache
+from .modeling_delta_net import (DeltaNet, DeltaNetBlock, DeltaNetForCausalLM, DeltaNetModel, GatedDeltaNet, GatedDeltaNetBlock,
+                                 GatedDeltaNetForCausalLM, GatedDeltaNetModel, RecurrentCache, ShortConv)
 from .modeling_deltanet_baseline import DeltaNetBaselineBlock, DeltaNetBaselineForCausalLM, DeltaNetBaselineModel
 from .modeling_ipttcdv9 import IPTTCDBlock, IPTTCDForCausalLM, IPTTCDMLP, IPTTCDModel
 from .modeling_ipttt import IPTTTBlock, IPTTTForCausalLM, IPTTTMLP, IPTTTModel
@@ -24,6 +27,8 @@ def register_all() -> None:
         (IPTTTConfig, IPTTTModel, IPTTTForCausalLM),
         (IPTTCDv9Config, IPTTCDModel, IPTTCDForCausalLM),
         (DeltaNetBaselineConfig, DeltaNetBaselineModel, DeltaNetBaselineForCausalLM),
+        (DeltaNetConfig, DeltaNetModel, DeltaNetForCausalLM),
+        (GatedDeltaNetConfig, GatedDeltaNetModel, GatedDeltaNetForCausalLM),
     ):
         AutoConfig.register(cfg.model_type, cfg, exist_ok=True)
         AutoModel.register(cfg, model, exist_ok=True)
@@ -36,9 +41,13 @@ register_all()
 # registering the same ``model_type`` strings with the HF Auto classes later cannot redirect it.
 MODEL_CLASSES = {cfg.model_type: (cfg, causal) for cfg, causal in (
     (TransformerConfig, TransformerForCausalLM), (IPTTTConfig, IPTTTForCausalLM), (IPTTCDv9Config, IPTTCDForCausalLM),
-    (DeltaNetBaselineConfig, DeltaNetBaselineForCausalLM))}
+    (DeltaNetBaselineConfig, DeltaNetBaselineForCausalLM), (DeltaNetConfig, DeltaNetForCausalLM),
+    (GatedDeltaNetConfig, GatedDeltaNetForCausalLM))}
 
 __all__ = [
+    "DeltaNetConfig", "DeltaNetModel", "DeltaNetForCausalLM", "DeltaNetBlock", "DeltaNet",
+    "GatedDeltaNetConfig", "GatedDeltaNetModel", "GatedDeltaNetForCausalLM", "GatedDeltaNetBlock", "GatedDeltaNet",
+    "RecurrentCache", "ShortConv",
     "DeltaNetBaselineConfig", "DeltaNetBaselineModel", "DeltaNetBaselineForCausalLM", "DeltaNetBaselineBlock",
     "TransformerConfig", "IPTTTConfig", "IPTTCDConfig", "IPTTCDv8Config", "IPTTCDv9Config", "IPTTCDv9LowCopyConfig",
     "TransformerModel", "TransformerForCausalLM", "TransformerBlock",

@@ -334,8 +334,93 @@ class DeltaNetBaselineConfig(IPTTCDConfig):
         super().__init__(**kwargs)
 
 
+_RECURRENT_COMMON_FIELDS: tuple[tuple[str, Any], ...] = (
+    ("attn_mode", "chunk"),
+    ("hidden_size", 2048),
+    ("use_short_conv", True),
+    ("conv_size", 4),
+    ("max_position_embeddings", 2048),
+    ("hidden_ratio", 4),
+    ("intermediate_size", None),
+    ("hidden_act", "swish"),
+    ("norm_eps", 1e-6),
+    ("attn", None),
+    ("use_cache", True),
+    ("initializer_range", 0.02),
+    ("fuse_norm", True),
+    ("fuse_swiglu", True),
+    ("fuse_cross_entropy", True),
+    ("fuse_linear_cross_entropy", False),
+    ("use_l2warp", False),
+    ("vocab_size", 32000),
+)
+
+
+class _RecurrentConfig(_TableConfig):
+    """Shared rules of the linear-recurrent families: the optional ``attn`` dict turns the listed layers into softmax
+    attention (hybrid layouts) and must name ``layers`` and ``num_heads``."""
+
+    def __init__(self, **kwargs):  # explicit: keeps HF from generating a dataclass __init__
+        super().__init__(**kwargs)
+
+    def _validate(self) -> None:
+        super()._validate()
+        attn = self.attn
+        if attn is not None:
+            if not isinstance(attn, dict):
+                raise ValueError("attn must be a dictionary")
+            if "layers" not in attn:
+                raise ValueError("Layer indices must be provided to initialize hybrid attention layers")
+            if "num_heads" not in attn:
+                raise ValueError("Number of heads must be provided to initialize hybrid attention layers")
+            attn.setdefault("num_kv_heads", attn["num_heads"])
+            attn.setdefault("qkv_bias", False)
+            attn.setdefault("window_size", None)
+            attn.setdefault("rope_theta", 10000.0)
+
+
+class DeltaNetConfig(_RecurrentConfig):
+    """``delta_net`` (fla/models/delta_net/configuration_delta_net.py:8-110)."""
+
+    model_type = "delta_net"
+    FIELDS = _RECURRENT_COMMON_FIELDS + (
+        ("expand_k", 1.0),
+        ("expand_v", 1.0),
+        ("use_gate", False),
+        ("use_beta", True),
+        ("use_output_norm", True),
+        ("num_heads", 16),
+        ("qk_norm", "l2"),
+        ("qk_activation", "silu"),
+        ("num_hidden_layers", 24),
+    )
+
+    def __init__(self, **kwargs):  # explicit: keeps HF from generating a dataclass __init__
+        super().__init__(**kwargs)
+
+
+class GatedDeltaNetConfig(_RecurrentConfig):
+    """``gated_deltanet`` (fla/models/gated_deltanet/configuration_gated_deltanet.py:8-100)."""
+
+    model_type = "gated_deltanet"
+    FIELDS = _RECURRENT_COMMON_FIELDS + (
+        ("expand_v", 2.0),
+        ("use_gate", True),
+        ("allow_neg_eigval", False),
+        ("head_dim", 256),
+        ("num_heads", 6),
+        ("num_v_heads", None),
+        ("num_hidden_layers", 21),
+    )
+
+    def __init__(self, **kwargs):  # explicit: keeps HF from generating a dataclass __init__
+        super().__init__(**kwargs)
+
+
 __all__ = [
     "DeltaNetBaselineConfig",
+    "DeltaNetConfig",
+    "GatedDeltaNetConfig",
     "TransformerConfig",
     "IPTTTConfig",
     "IPTTCDConfig",

@@ -209,3 +209,14 @@ def newton_schulz(g, coeffs=reference.NS_COEFFS):
     if g.is_cuda and _native.available():
         return _cuda().newton_schulz(g, coeffs)
     return reference.newton_schulz(g, coeffs)
+
+
+def gated_delta_rule(q, k, v, g, beta, *, scale=None, l2norm: bool = True, cu_seqlens=None, initial_state=None,
+                     output_final_state: bool = False, recurrent: bool = False):
+    """(Gated) delta rule over q, k [B,T,H,Dk], v [B,T,H,Dv], log decay g and write strength beta [B,T,H]; ``g`` None is
+    the plain delta rule.  ``recurrent`` takes the token-by-token form (short decode steps), otherwise the chunked
+    form whose matrix products run as batched GEMMs.  Returns (o, final state or None)."""
+    if recurrent and cu_seqlens is None:
+        return reference.gated_delta_rule_recurrent(q, k, v, g, beta, scale, l2norm, initial_state, output_final_state)
+    return reference.gated_delta_rule_chunked(q, k, v, g, beta, scale, l2norm, 64, cu_seqlens, initial_state,
+                                              output_final_state)

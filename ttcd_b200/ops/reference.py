@@ -457,6 +457,85 @@ def delta_rule_chunked(q, k, v, beta, scale=None, l2norm: bool = True, chunk: in
     return o.to(dtype)
 
 
+def gated_delta_rule_recurrent(q, k, v, g, beta, scale=None, l2norm: bool = True, initial_state=None,
+                               output_final_state: bool = False):
+    """Token-by-token gated delta rule (the statement of fla/ops/gated_delta_rule/fused_recurrent.py):
+    S' = exp(g_t) S_{t-1};  u_t = beta_t (v_t - S'^T k_t);  S_t = S' + k_t u_t^T;  o_t = S_t^T (scale q_t).
+    q, k: [B, T, H, Dk]; v: [B, T, H, Dv]; g (log decay, <= 0) and beta: [B, T, H]; ``g`` None means no decay (the
+    plain delta rule).  The state is [B, H, Dk, Dv] in fp32.  Returns (o, final state or None).  The oracle of
+    ``gated_delta_rule_chunked`` and the path single-token decoding takes."""
+    qf, kf, vf, bf = q.float(), k.float(), v.float(), beta.float()
+    if l2norm:
+        qf, kf = F.normalize(qf, dim=-1, eps=1e-6), F.normalize(kf, dim=-1, eps=1e-6)
+    scale = q.shape[-1] ** -0.5 if scale is None else scale
+    B, T, H, D = qf.shape
+    S = qf.new_zeros(B, H, D, vf.shape[-1]) if initial_state is None else initial_state.float()
+    out = []
+    for t in range(T):
+        kt, bt = kf[:, t], bf[:, t].unsqueeze(-1)
+        if g is not None:
+            S = S * g[:, t].float().exp()[..., None, None]
+        pred = torch.einsum("bhkv,bhk->bhv", S, kt)
+        S = S + torch.einsum("bhk,bhv->bhkv", kt, bt * (vf[:, t] - pred))
+        out.append(torch.einsum("bhkv,bhk->bhv", S, qf[:, t] * scale))
+    return torch.stack(out, dim=1).to(q.dtype), (S if output_final_state else None)
+
+
+def gated_delta_rule_chunked(q, k, v, g, beta, scale=None, l2norm: bool = True, chunk: int = 64, cu_seqlens=None,
+                             initial_state=None, output_final_state: bool = False):
+    """Chunk-parallel gated delta rule (the computation of fla/ops/gated_delta_rule/chunk.py and, with ``g`` None, of
+    fla/ops/delta_rule/chunk.py).  With G the running sum of g inside a chunk and S_0 the state entering it, the
+    updates u solve the unit-lower-triangular system (I + L) U = beta V - (beta e^G K) S_0 with
+    L_ij = beta_i e^{G_i - G_j} (k_i . k_j) for j < i; every exponent is a difference G_i - G_j with i >= j, so
+    nothing overflows.  Differentiable through autograd; shapes as in ``gated_delta_rule_recurrent``.  With
+    ``cu_seqlens`` (batch 1) each packed sequence starts from a zero state (``initial_state`` then has one entry per
+    sequence)."""
+    if cu_seqlens is not None:
+        bounds = cu_seqlens.tolist()
+        outs, finals = [], []
+        for i, (a, b) in enumerate(zip(bounds[:-1], bounds[1:])):
+            init = None if initial_state is None else initial_state[i:i + 1]
+            o, s = gated_delta_rule_chunked(q[:, a:b], k[:, a:b], v[:, a:b], None if g is None else g[:, a:b], beta[:, a:b],
+                                            scale, l2norm, chunk, None, init, output_final_state)
+            outs.append(o)
+            finals.append(s)
+        return torch.cat(outs, dim=1), (torch.cat(finals, dim=0) if output_final_state else None)
+    dtype = q.dtype
+    qf, kf, vf, bf = q.float(), k.float(), v.float(), beta.float()
+    if l2norm:
+        qf, kf = F.normalize(qf, dim=-1, eps=1e-6), F.normalize(kf, dim=-1, eps=1e-6)
+    scale = q.shape[-1] ** -0.5 if scale is None else scale
+    B, T, H, D = qf.shape
+    gf = qf.new_zeros(B, T, H) if g is None else g.float()
+    pad = (-T) % chunk
+    if pad:                     # padded steps: beta = 0 (no update) and g = 0 (no decay) leave the state untouched
+        qf, kf, vf = (F.pad(x, (0, 0, 0, 0, 0, pad)) for x in (qf, kf, vf))
+        bf, gf = F.pad(bf, (0, 0, 0, pad)), F.pad(gf, (0, 0, 0, pad))
+    n = (T + pad) // chunk
+    qc, kc, vc = (x.view(B, n, chunk, H, -1).permute(0, 3, 1, 2, 4) for x in (qf * scale, kf, vf))     # [B, H, n, C, D]
+    bc = bf.view(B, n, chunk, H).permute(0, 3, 1, 2).unsqueeze(-1)
+    G = gf.view(B, n, chunk, H).permute(0, 3, 1, 2).cumsum(-1)                                         # [B, H, n, C]
+    tril = torch.ones(chunk, chunk, dtype=torch.bool, device=q.device).tril()
+    decay = (G.unsqueeze(-1) - G.unsqueeze(-2)).masked_fill(~tril, float("-inf")).exp()                # e^{G_i - G_j}, i >= j
+    eg = G.exp().unsqueeze(-1)                                                                         # e^{G_i}
+    to_end = (G[..., -1:] - G).exp().unsqueeze(-1)                                                     # e^{G_C - G_j}
+    kb, vb = kc * bc, vc * bc
+    eye = torch.eye(chunk, device=q.device)
+    lower = torch.tril(kb @ kc.transpose(-1, -2) * decay, -1)
+    t_inv = torch.linalg.solve_triangular(eye + lower, eye.expand_as(lower), upper=False)
+    w, u = t_inv @ (kb * eg), t_inv @ vb
+    qk = (qc @ kc.transpose(-1, -2)) * decay
+    q_in, k_out = qc * eg, kc * to_end
+    S = qf.new_zeros(B, H, D, vf.shape[-1]) if initial_state is None else initial_state.float()
+    outs = []
+    for i in range(n):
+        u_i = u[:, :, i] - w[:, :, i] @ S
+        outs.append(q_in[:, :, i] @ S + qk[:, :, i] @ u_i)
+        S = S * eg[:, :, i, -1:, :] + k_out[:, :, i].transpose(-1, -2) @ u_i
+    o = torch.stack(outs, dim=2).permute(0, 2, 3, 1, 4).reshape(B, n * chunk, H, -1)[:, :T]
+    return o.to(dtype), (S if output_final_state else None)
+
+
 def dual_window_attention_backward_combined(q, k, v, d_o_t, d_o_s, window_teacher, window_student, scale=None):
     """Gradients of ``dual_window_attention`` through ONE softmax (the statement the combined backward kernels
     implement).  Inside the student window P_S = r * P_T with the per-row ratio r = exp(lse_T - lse_S), so the two
