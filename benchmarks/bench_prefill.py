@@ -8,8 +8,9 @@ CUDA events, median of ``--iters`` after ``--warmup``.
         --seq-len 65536 --batch 1 --modes eval_nomask_cache,train_fwd --ablation full --attn-impl fused
 
 * modes: ``eval_mask_cache`` (mask of ones + KV cache + last-position logits), ``eval_nomask_cache``,
-  ``eval_nocache``, ``train_fwd`` (training-mode forward, no grad), ``gen1`` (generate one token),
-  ``eval_ppl_style`` (all logits + 512-token chunked NLL).
+  ``eval_nocache``, ``train_fwd`` (training-mode forward, no grad), ``gen1`` (generate one token), ``gen64`` /
+  ``gen64_eager`` (generate 64 tokens with the captured decode step / the eager loop; with ``gen1`` in the same run a
+  ``decode`` row reports (gen64 - gen1) / 63 as ms per token), ``eval_ppl_style`` (all logits + 512-token chunked NLL).
 * ablations: ``full``, ``no_ttt`` (blocks and MLPs treated as non-TTT: single attention), ``attn_only`` (dual
   attention kept, fast-weight scan off).
 * ``--attn-impl fused|two_pass``: the one-pass dual-window kernel or two single-window calls (what the
@@ -29,7 +30,7 @@ import torch
 ROOT = Path(__file__).resolve().parents[1]
 sys.path.insert(0, str(ROOT))
 
-MODES = ("eval_mask_cache", "eval_nomask_cache", "eval_nocache", "train_fwd", "gen1", "eval_ppl_style")
+MODES = ("eval_mask_cache", "eval_nomask_cache", "eval_nocache", "train_fwd", "gen1", "gen64", "gen64_eager", "eval_ppl_style")
 
 
 def apply_ablation(model, ablation: str) -> None:
@@ -68,6 +69,9 @@ def run_mode(model, input_ids, mode: str, iters: int, warmup: int) -> dict:
         if mode == "gen1":
             model.eval()
             return model.generate(input_ids, max_new_tokens=1, do_sample=False)
+        if mode in ("gen64", "gen64_eager"):
+            model.eval()
+            return model.generate(input_ids, max_new_tokens=64, do_sample=False, use_graph=mode == "gen64")
         if mode == "eval_ppl_style":
             model.eval()
             logits = model(input_ids=input_ids).logits[:, :-1]
@@ -137,6 +141,13 @@ def main(argv=None):
                "L": args.seq_len, "model": Path(args.config).stem, **res}
         print(json.dumps(row), flush=True)
         rows.append(row)
+    by_mode = {r["mode"]: r for r in rows}
+    for mode in ("gen64", "gen64_eager"):
+        if mode in by_mode and "gen1" in by_mode:
+            row = {"bench": "decode", "mode": mode, "B": args.batch, "L": args.seq_len, "model": Path(args.config).stem,
+                   "ms_per_token": round((by_mode[mode]["ms_median"] - by_mode["gen1"]["ms_median"]) / 63, 3)}
+            print(json.dumps(row), flush=True)
+            rows.append(row)
     if args.out:
         Path(args.out).write_text(json.dumps(rows, indent=1))
 

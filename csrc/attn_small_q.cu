@@ -33,6 +33,7 @@ struct SmallQParams {
   const bf16* q; const bf16* k; const bf16* v;
   float* part_o;        // [B, H, Tq, splits, D]
   float* part_ml;       // [B, H, Tq, splits, 2]  (max in log2 units, sum)
+  const int* kv_len;    // optional device word: the number of valid keys (<= Tk); read at launch time
   int B, Tq, Tk, H, HK, splits, window;
   int64_t ldq, ldk, ldv, sq, sk, sv;
   float scale_log2;
@@ -46,7 +47,9 @@ __global__ void __launch_bounds__(SQ_WARPS * 32) attn_small_q_partial_kernel(con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = p.H / p.HK;
   const int key0 = split * SQ_KEYS;
-  const int nkeys = min(SQ_KEYS, p.Tk - key0);
+  // a cache with a device-side fill count: splits past the count stage nothing and report an empty partial
+  const int Tk = p.kv_len != nullptr ? min(max(*p.kv_len, p.Tq), p.Tk) : p.Tk;
+  const int nkeys = min(SQ_KEYS, Tk - key0);
   constexpr int VPR = D / 8;                                     // 16-byte vectors per row
   // ---- stage K and V rows of this split
   for (int i = threadIdx.x; i < nkeys * VPR; i += blockDim.x) {
@@ -62,7 +65,7 @@ __global__ void __launch_bounds__(SQ_WARPS * 32) attn_small_q_partial_kernel(con
   const int npairs = p.Tq * G;
   for (int pair = warp; pair < npairs; pair += SQ_WARPS) {
     const int row = pair / G, h = kvh * G + pair % G;
-    const int qpos = p.Tk - p.Tq + row;
+    const int qpos = Tk - p.Tq + row;
     const int lo_excl = p.window > 0 ? qpos - p.window : -1;
     // the query row -> shared memory as fp32
     const bf16* qrow = p.q + static_cast<int64_t>(b) * p.sq + static_cast<int64_t>(row) * p.ldq + h * D;
@@ -189,10 +192,12 @@ static int launch_small_q(const SmallQParams& p, bf16* out, cudaStream_t stream)
 // q [B, Tq, *] (token stride ldq, batch stride sq, head h at column h*D), k / v [B, Tk, *] likewise with HK heads,
 // 16-byte aligned rows; out contiguous [B, Tq, H, D] bf16.  part_o fp32 [B, H, Tq, splits, D] and part_ml fp32
 // [B, H, Tq, splits, 2] are caller-provided scratch; splits must equal ceil(Tk / 256).  window <= 0: unlimited.
+// kv_len (may be null): a device int holding how many of the Tk key rows are filled, read when the kernel runs, so
+// that a captured launch follows a cache that grows between replays; the causal alignment then counts from it.
 TTCD_EXPORT int ttcd_attn_small_q(const void* q, const void* k, const void* v, void* out, float* part_o, float* part_ml,
                                   int B, int Tq, int Tk, int H, int HK, int D, long long ldq, long long ldk, long long ldv,
                                   long long sq, long long sk, long long sv, int window, float scale, int splits,
-                                  void* stream_ptr) {
+                                  const int* kv_len, void* stream_ptr) {
   using namespace ttcd;
   if (B <= 0 || Tq <= 0 || Tq >= 128 || Tk < Tq || H <= 0 || HK <= 0 || H % HK != 0 || (D != 64 && D != 128))
     return TTCD_ERR_ARG;
@@ -200,7 +205,7 @@ TTCD_EXPORT int ttcd_attn_small_q(const void* q, const void* k, const void* v, v
   if ((reinterpret_cast<uintptr_t>(k) & 15u) || (reinterpret_cast<uintptr_t>(v) & 15u)) return TTCD_ERR_ARG;
   SmallQParams p;
   p.q = static_cast<const bf16*>(q); p.k = static_cast<const bf16*>(k); p.v = static_cast<const bf16*>(v);
-  p.part_o = part_o; p.part_ml = part_ml;
+  p.part_o = part_o; p.part_ml = part_ml; p.kv_len = kv_len;
   p.B = B; p.Tq = Tq; p.Tk = Tk; p.H = H; p.HK = HK; p.splits = splits; p.window = window;
   p.ldq = ldq; p.ldk = ldk; p.ldv = ldv; p.sq = sq; p.sk = sk; p.sv = sv;
   p.scale_log2 = scale * 1.4426950408889634f;

@@ -3,6 +3,7 @@
 #include "common.cuh"
 
 #include <cudaTypedefs.h>
+#include <cstdio>
 #include <mutex>
 
 namespace ttcd {
@@ -21,6 +22,9 @@ static PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
   return fn;
 }
 
+// What the last failed tensor-map encode was asked for (per thread), for the error message of the binding.
+static thread_local char g_tmap_error[320] = "";
+
 int make_tmap_bf16_3d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows, uint64_t batch,
                       uint64_t row_stride_elems, uint64_t batch_stride_elems, uint32_t box_inner,
                       uint32_t box_rows) {
@@ -37,6 +41,12 @@ int make_tmap_bf16_3d(CUtensorMap* map, const void* base, uint64_t inner, uint64
   CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    std::snprintf(g_tmap_error, sizeof(g_tmap_error),
+                  "cuTensorMapEncodeTiled -> %d: base %p dims {%llu, %llu, %llu} strides(bytes) {%llu, %llu} box {%u, %u, 1}",
+                  static_cast<int>(r), base, static_cast<unsigned long long>(dims[0]), static_cast<unsigned long long>(dims[1]),
+                  static_cast<unsigned long long>(dims[2]), static_cast<unsigned long long>(strides[0]),
+                  static_cast<unsigned long long>(strides[1]), box_inner, box_rows);
   return r == CUDA_SUCCESS ? TTCD_OK : TTCD_ERR_TMAP;
 }
 
@@ -53,4 +63,11 @@ int sm_count() {
 }
 
 }  // namespace ttcd
+
+// Copies the description of this thread's last failed tensor-map encode into buf (empty string if none).
+TTCD_EXPORT int ttcd_last_tmap_error(char* buf, int size) {
+  if (buf == nullptr || size <= 0) return TTCD_ERR_ARG;
+  std::snprintf(buf, static_cast<size_t>(size), "%s", ttcd::g_tmap_error);
+  return TTCD_OK;
+}
 

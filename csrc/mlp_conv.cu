@@ -82,6 +82,40 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const bf16* __restrict_
 // ------------------------------------------------------------------------------------------------
 constexpr int CONV_ROWS = 64;
 constexpr int CONV_MAXK = 8;
+constexpr int CONV_BATCH = 8;      // rows whose loads are issued together (memory-level parallelism per thread)
+
+__device__ __forceinline__ void conv_unpack(const uint4& raw, float (&dst)[8]) {
+  const float2 a = unpack_bf16(raw.x), b = unpack_bf16(raw.y), c = unpack_bf16(raw.z), d = unpack_bf16(raw.w);
+  dst[0] = a.x; dst[1] = a.y; dst[2] = b.x; dst[3] = b.y; dst[4] = c.x; dst[5] = c.y; dst[6] = d.x; dst[7] = d.y;
+}
+
+// CONV_BATCH rows starting at ``row`` (rows outside [0, C) read as zero); the loads carry no dependence on one
+// another, so they are all in flight before the first use.
+__device__ __forceinline__ void conv_load_rows(const bf16* __restrict__ col, int row, int C, int D, uint4 (&raw)[CONV_BATCH]) {
+#pragma unroll
+  for (int i = 0; i < CONV_BATCH; ++i) {
+    const int c = row + i;
+    raw[i] = (c >= 0 && c < C) ? __ldg(reinterpret_cast<const uint4*>(col + static_cast<int64_t>(c) * D)) : make_uint4(0, 0, 0, 0);
+  }
+}
+
+template <int K>
+__device__ __forceinline__ void conv_preload(const bf16* __restrict__ col, int row, int C, int D, float (&win)[K][8]) {
+#pragma unroll
+  for (int j = 0; j < K - 1; ++j) {
+    const int c = row + j;
+    const uint4 raw = (c >= 0 && c < C) ? __ldg(reinterpret_cast<const uint4*>(col + static_cast<int64_t>(c) * D)) : make_uint4(0, 0, 0, 0);
+    conv_unpack(raw, win[j]);
+  }
+}
+
+template <int K>
+__device__ __forceinline__ void conv_shift(float (&win)[K][8]) {
+#pragma unroll
+  for (int j = 0; j < K - 1; ++j)
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) win[j][ch] = win[j + 1][ch];
+}
 
 template <int K>
 __global__ void __launch_bounds__(128) dwconv_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
@@ -96,37 +130,25 @@ __global__ void __launch_bounds__(128) dwconv_fwd_kernel(const bf16* __restrict_
 #pragma unroll
     for (int j = 0; j < K; ++j) wv[ch][j] = __bfloat162float(w[(cv + ch) * K + j]);
   float win[K][8];
-  // preload rows c0-left .. c0-left+K-2
+  conv_preload<K>(x + base, c0 - left, C, D, win);          // rows c0-left .. c0-left+K-2
+  for (int r0 = 0; r0 < CONV_ROWS && c0 + r0 < C; r0 += CONV_BATCH) {
+    uint4 raw[CONV_BATCH];
+    conv_load_rows(x + base, c0 + r0 - left + K - 1, C, D, raw);
 #pragma unroll
-  for (int j = 0; j < K - 1; ++j) {
-    const int c = c0 - left + j;
-    if (c >= 0 && c < C) load8(x + base + static_cast<int64_t>(c) * D, win[j]);
-    else
+    for (int i = 0; i < CONV_BATCH; ++i) {
+      const int c = c0 + r0 + i;
+      conv_unpack(raw[i], win[K - 1]);
+      float o[8];
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) win[j][ch] = 0.f;
-  }
-#pragma unroll 4
-  for (int r = 0; r < CONV_ROWS; ++r) {
-    const int c = c0 + r;
-    if (c >= C) break;
-    const int cin = c - left + K - 1;
-    if (cin >= 0 && cin < C) load8(x + base + static_cast<int64_t>(cin) * D, win[K - 1]);
-    else
+      for (int ch = 0; ch < 8; ++ch) {
+        float acc = 0.f;
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) win[K - 1][ch] = 0.f;
-    float o[8];
-#pragma unroll
-    for (int ch = 0; ch < 8; ++ch) {
-      float acc = 0.f;
-#pragma unroll
-      for (int j = 0; j < K; ++j) acc += wv[ch][j] * win[j][ch];
-      o[ch] = acc;
+        for (int j = 0; j < K; ++j) acc += wv[ch][j] * win[j][ch];
+        o[ch] = acc;
+      }
+      if (c < C) store8(y + base + static_cast<int64_t>(c) * D, o);
+      conv_shift<K>(win);
     }
-    store8(y + base + static_cast<int64_t>(c) * D, o);
-#pragma unroll
-    for (int j = 0; j < K - 1; ++j)
-#pragma unroll
-      for (int ch = 0; ch < 8; ++ch) win[j][ch] = win[j + 1][ch];
   }
 }
 
@@ -140,80 +162,60 @@ __global__ void __launch_bounds__(128) dwconv_bwd_kernel(const bf16* __restrict_
   if (cv >= D) return;
   const int c0 = blockIdx.y * CONV_ROWS;
   const int64_t base = static_cast<int64_t>(blockIdx.z) * C * D + cv;
-  float wv[8][K], dwacc[8][K];
-#pragma unroll
-  for (int ch = 0; ch < 8; ++ch)
-#pragma unroll
-    for (int j = 0; j < K; ++j) {
-      wv[ch][j] = __bfloat162float(w[(cv + ch) * K + j]);
-      dwacc[ch][j] = 0.f;
-    }
   // dx pass: window over dy rows c+left-(K-1) .. c+left
   {
+    float wv[8][K];
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch)
+#pragma unroll
+      for (int j = 0; j < K; ++j) wv[ch][j] = __bfloat162float(w[(cv + ch) * K + j]);
     float win[K][8];
+    conv_preload<K>(dy + base, c0 + left - (K - 1), C, D, win);
+    for (int r0 = 0; r0 < CONV_ROWS && c0 + r0 < C; r0 += CONV_BATCH) {
+      uint4 raw[CONV_BATCH];
+      conv_load_rows(dy + base, c0 + r0 + left, C, D, raw);
 #pragma unroll
-    for (int j = 0; j < K - 1; ++j) {
-      const int c = c0 + left - (K - 1) + j;
-      if (c >= 0 && c < C) load8(dy + base + static_cast<int64_t>(c) * D, win[j]);
-      else
+      for (int i = 0; i < CONV_BATCH; ++i) {
+        const int c = c0 + r0 + i;
+        conv_unpack(raw[i], win[K - 1]);
+        float o[8];
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) win[j][ch] = 0.f;
-    }
-#pragma unroll 4
-    for (int r = 0; r < CONV_ROWS; ++r) {
-      const int c = c0 + r;
-      if (c >= C) break;
-      const int cin = c + left;
-      if (cin >= 0 && cin < C) load8(dy + base + static_cast<int64_t>(cin) * D, win[K - 1]);
-      else
+        for (int ch = 0; ch < 8; ++ch) {
+          float acc = 0.f;
+          // win[m] holds dy[c + left - (K-1) + m]; it pairs with tap j = K-1-m
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) win[K - 1][ch] = 0.f;
-      float o[8];
-#pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        float acc = 0.f;
-        // win[m] holds dy[c + left - (K-1) + m]; it pairs with tap j = K-1-m
-#pragma unroll
-        for (int m = 0; m < K; ++m) acc += wv[ch][K - 1 - m] * win[m][ch];
-        o[ch] = acc;
+          for (int m = 0; m < K; ++m) acc += wv[ch][K - 1 - m] * win[m][ch];
+          o[ch] = acc;
+        }
+        if (c < C) store8(dx + base + static_cast<int64_t>(c) * D, o);
+        conv_shift<K>(win);
       }
-      store8(dx + base + static_cast<int64_t>(c) * D, o);
-#pragma unroll
-      for (int j = 0; j < K - 1; ++j)
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch) win[j][ch] = win[j + 1][ch];
     }
   }
-  // dw pass: for output position c, x window rows c-left .. c-left+K-1
+  // dw pass: for output position c, x window rows c-left .. c-left+K-1 (rows of dy past C read as zero: no term)
   if (dw_partial != nullptr) {
+    float dwacc[8][K];
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch)
+#pragma unroll
+      for (int j = 0; j < K; ++j) dwacc[ch][j] = 0.f;
     float win[K][8];
+    conv_preload<K>(x + base, c0 - left, C, D, win);
+    for (int r0 = 0; r0 < CONV_ROWS && c0 + r0 < C; r0 += CONV_BATCH) {
+      uint4 raw[CONV_BATCH], graw[CONV_BATCH];
+      conv_load_rows(x + base, c0 + r0 - left + K - 1, C, D, raw);
+      conv_load_rows(dy + base, c0 + r0, C, D, graw);
 #pragma unroll
-    for (int j = 0; j < K - 1; ++j) {
-      const int c = c0 - left + j;
-      if (c >= 0 && c < C) load8(x + base + static_cast<int64_t>(c) * D, win[j]);
-      else
+      for (int i = 0; i < CONV_BATCH; ++i) {
+        conv_unpack(raw[i], win[K - 1]);
+        float g[8];
+        conv_unpack(graw[i], g);
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) win[j][ch] = 0.f;
-    }
-#pragma unroll 4
-    for (int r = 0; r < CONV_ROWS; ++r) {
-      const int c = c0 + r;
-      if (c >= C) break;
-      const int cin = c - left + K - 1;
-      if (cin >= 0 && cin < C) load8(x + base + static_cast<int64_t>(cin) * D, win[K - 1]);
-      else
+        for (int ch = 0; ch < 8; ++ch)
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) win[K - 1][ch] = 0.f;
-      float g[8];
-      load8(dy + base + static_cast<int64_t>(c) * D, g);
-#pragma unroll
-      for (int ch = 0; ch < 8; ++ch)
-#pragma unroll
-        for (int j = 0; j < K; ++j) dwacc[ch][j] += g[ch] * win[j][ch];
-#pragma unroll
-      for (int j = 0; j < K - 1; ++j)
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch) win[j][ch] = win[j + 1][ch];
+          for (int j = 0; j < K; ++j) dwacc[ch][j] += g[ch] * win[j][ch];
+        conv_shift<K>(win);
+      }
     }
     float* out = dw_partial + (static_cast<int64_t>(blockIdx.z) * gridDim.y + blockIdx.y) * D * K;
 #pragma unroll

@@ -192,3 +192,38 @@ def test_recurrent_family_decodes_from_its_state(family):
         steps = [model(input_ids=ids[:, t:t + 1], past_key_values=cache, use_cache=True).logits for t in range(290, 300)]
     got = torch.cat([first, *steps], dim=1).float()
     assert _cos(got, full) > 0.999, _cos(got, full)
+
+
+def test_graph_decoding_follows_eager_decoding():
+    """The captured decode step (fixed-address ring cache, positions and fill count on the device) against the eager
+    loop, teacher-forced so that one near-tie cannot send the two down different continuations: per-step logits agree;
+    then ``generate`` end to end, and a second prompt through the same capture."""
+    from ttcd_b200.models import decoding
+    from ttcd_b200.models.layers import WindowKVCache
+    torch.manual_seed(0)
+    model = IPTTCDv9ForCausalLM(_config(window_size=256, max_position_embeddings=4096)).to(DEV, torch.bfloat16).eval()
+    prompt, new = 700, 300                                     # the 256-row rings wrap
+    ids = torch.randint(0, 1024, (2, prompt + new), device=DEV)
+    with torch.no_grad():
+        grow, source = WindowKVCache(), WindowKVCache()
+        model(input_ids=ids[:, :prompt], past_key_values=grow, use_cache=True, logits_to_keep=1)
+        model(input_ids=ids[:, :prompt], past_key_values=source, use_cache=True, logits_to_keep=1)
+        dec = decoding.GraphDecoder(model, source, new)
+        worst = 1.0
+        for t in range(prompt, prompt + new):
+            want = model(input_ids=ids[:, t:t + 1], past_key_values=grow, use_cache=True, logits_to_keep=1).logits[:, -1]
+            dec.token.copy_(ids[:, t:t + 1])
+            dec.graph.replay()
+            worst = min(worst, _cos(dec.last_logits, want))
+        assert worst > 0.999, worst
+        launches = _native.launch_count
+        a = model.generate(ids[:, :prompt], max_new_tokens=24)
+        b = model.generate(ids[:, :prompt], max_new_tokens=24, use_graph=False)
+        assert a.shape == b.shape == (2, prompt + 24)
+        assert torch.equal(a[:, :prompt + 2], b[:, :prompt + 2])
+        first = model._graph_decoder
+        c = model.generate(ids[:, 100:100 + prompt], max_new_tokens=24)       # another prompt: the capture is reused
+        assert model._graph_decoder is first and c.shape == (2, prompt + 24)
+        d = model.generate(ids[:, 100:100 + prompt], max_new_tokens=24, use_graph=False)
+        assert torch.equal(c[:, :prompt + 2], d[:, :prompt + 2])
+        assert _native.launch_count > launches

@@ -112,6 +112,10 @@ def call(symbol: str, *args) -> None:
     rc = fn(*args)
     if rc != 0:
         detail = _ERRORS.get(rc, f"cudaError {rc}")
+        if rc == -4 and hasattr(lib, "ttcd_last_tmap_error"):
+            buf = ctypes.create_string_buffer(320)
+            lib.ttcd_last_tmap_error(buf, ctypes.c_int(320))
+            detail += f" ({buf.value.decode(errors='replace')})"
         raise NativeError(f"{symbol} failed: {detail}")
 
 

@@ -286,11 +286,13 @@ class DecoderForCausalLM(DecoderPreTrainedModel):
     @torch.no_grad()
     def generate(self, input_ids: torch.Tensor, max_new_tokens: int = 32, do_sample: bool = False,
                  temperature: float = 1.0, top_k: int | None = None, top_p: float | None = None,
-                 eos_token_id: int | list[int] | None = None, attention_mask=None, **_):
+                 eos_token_id: int | list[int] | None = None, attention_mask=None, use_graph: bool = True, **_):
         """Prefill once (TTT layers run their dual path), then decode token by token from the cache.
 
         Mirrors the reference's behaviour: fast weights are built during prefill only and are not
         carried into single-token decode steps (custom_models/ipttcd/modeling_ipttcdv9.py:794-850).
+        Greedy decoding on the native path replays one captured CUDA graph per token (models/decoding.py);
+        ``use_graph=False`` keeps the eager loop.
         """
         eos = set(eos_token_id if isinstance(eos_token_id, (list, tuple)) else
                   ([eos_token_id] if eos_token_id is not None else []))
@@ -299,6 +301,15 @@ class DecoderForCausalLM(DecoderPreTrainedModel):
                    use_cache=True, logits_to_keep=1)
         tokens = input_ids
         finished = torch.zeros(input_ids.shape[0], dtype=torch.bool, device=input_ids.device)
+        from . import decoding
+        if (use_graph and max_new_tokens > 1 and not self.training and type(cache) is WindowKVCache
+                and decoding.graph_decoding_supported(self, input_ids, attention_mask, do_sample)):
+            # greedy decoding on the native path: the step is captured once and replayed per token
+            first = out.logits[:, -1].float().argmax(-1, keepdim=True)
+            if eos and bool(torch.isin(first.squeeze(1), torch.tensor(sorted(eos), device=first.device)).all()):
+                return torch.cat([tokens, first], dim=1)
+            rest = decoding.decoder_for(self, cache, max_new_tokens - 1).run(first, max_new_tokens - 1, eos)
+            return torch.cat([tokens, first, rest], dim=1)
         for _step in range(max_new_tokens):
             logits = out.logits[:, -1].float()
             if do_sample:

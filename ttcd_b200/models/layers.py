@@ -119,6 +119,83 @@ class WindowKVCache:
             self.layers[i] = (k.index_select(0, beam_idx), v.index_select(0, beam_idx))
 
 
+class StaticWindowCache(WindowKVCache):
+    """Decoding cache at fixed addresses: every layer keeps a ring buffer of ``window`` rows (layers without a window:
+    the tokens seen plus ``max_new_tokens``, rounded up to 1024), the write slot, the fill count and the rotary
+    position live in device tensors that ``advance()`` updates in place.  A decode step through this cache reads no
+    value on the host and allocates nothing that outlives it, so it can be captured once as a CUDA graph and replayed
+    per token.  The token of absolute index ``a`` sits in row ``a % capacity``; attention over a ring needs no mask
+    beyond the fill count, because every row it holds is inside the window (keys carry their rotary phase already).
+    One query token per step; prompts of unequal length (a padding mask) stay on the eager cache."""
+
+    def __init__(self, source: WindowKVCache, windows: dict[int, int | None], max_new_tokens: int):
+        super().__init__()
+        seen = {source.seen[i] for i in source.layers}
+        if len(seen) != 1:
+            raise ValueError("the layers of the source cache have seen different numbers of tokens")
+        self.start = seen.pop()
+        self.max_position = self.start + max_new_tokens          # rotary table rows a decode run may touch
+        first = next(iter(source.layers.values()))[0]
+        dev = first.device
+        self.capacity: dict[int, int] = {}
+        for i, (k, v) in source.layers.items():
+            w = windows.get(i)
+            cap = int(w) if w is not None else -(-(self.start + max_new_tokens) // 1024) * 1024
+            n = k.shape[1]
+            if n > cap:
+                raise ValueError(f"layer {i}: {n} cached rows do not fit a ring of {cap}")
+            rk = k.new_zeros(k.shape[0], cap, *k.shape[2:])
+            rv = v.new_zeros(v.shape[0], cap, *v.shape[2:])
+            rows = torch.arange(self.start - n, self.start, device=dev) % cap
+            rk.index_copy_(1, rows, k)
+            rv.index_copy_(1, rows, v)
+            self.layers[i] = (rk, rv)
+            self.seen[i] = self.start
+            self.capacity[i] = cap
+        self.pos = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.positions = torch.zeros(first.shape[0], 1, dtype=torch.int64, device=dev)
+        self.positions._ttcd_bounded = True                      # never beyond max_position: no host check per step
+        self.slot = {c: torch.zeros(1, dtype=torch.int64, device=dev) for c in set(self.capacity.values())}
+        self.kv_len = {c: torch.zeros(1, dtype=torch.int32, device=dev) for c in set(self.capacity.values())}
+        self.reset(self.start)
+
+    def reset(self, position: int) -> None:
+        """Point the device state at the token of absolute index ``position`` (the next one to be written)."""
+        self.pos.fill_(position)
+        self._derive()
+        for i in self.seen:
+            self.seen[i] = position
+
+    def _derive(self) -> None:
+        self.positions.copy_(self.pos.expand_as(self.positions))
+        for c, slot in self.slot.items():
+            torch.remainder(self.pos, c, out=slot)
+            self.kv_len[c].copy_(torch.clamp(self.pos + 1, max=c))
+
+    def advance(self) -> None:
+        """Device side of moving on by one token (captured with the step)."""
+        self.pos.add_(1)
+        self._derive()
+
+    def host_advance(self, n: int = 1) -> None:
+        """Host mirror of ``advance`` for ``get_seq_length`` (a replayed graph runs no Python)."""
+        for i in self.seen:
+            self.seen[i] += n
+
+    def append(self, k: torch.Tensor, v: torch.Tensor, layer_idx: int):
+        """Write this step's k/v [B,1,HK,D] into the ring; returns (ring k, ring v, fill count incl. this token)."""
+        if k.shape[1] != 1:
+            raise ValueError("the static cache takes one token per step")
+        rk, rv = self.layers[layer_idx]
+        c = self.capacity[layer_idx]
+        rk.index_copy_(1, self.slot[c], k)
+        rv.index_copy_(1, self.slot[c], v)
+        return rk, rv, self.kv_len[c]
+
+    def update(self, k, v, layer_idx, window):
+        raise RuntimeError("StaticWindowCache is written through append()")
+
+
 def _gate_activation(name: str):
     return {"sigmoid": torch.sigmoid, "swish": F.silu, "silu": F.silu, "relu": F.relu}[name]
 
@@ -129,8 +206,9 @@ class Attention(nn.Module):
     def __init__(self, hidden_size, num_heads, num_kv_heads=None, head_dim=None, qkv_bias=False,
                  qk_norm=False, window_size=None, rope_theta=10000.0, max_position_embeddings=None,
                  layer_idx=None, use_output_gate=False, gate_fn="sigmoid", elementwise_affine=True,
-                 norm_eps=1e-5, rope_scaling=None, use_nope=False):
+                 norm_eps=1e-5, rope_scaling=None, use_nope=False, use_l2_softmax=False):
         super().__init__()
+        self.use_l2_softmax = use_l2_softmax
         self.hidden_size = hidden_size
         self.num_heads = num_heads
         self.num_kv_heads = num_heads if num_kv_heads is None else num_kv_heads
@@ -206,6 +284,11 @@ class Attention(nn.Module):
     def forward(self, hidden_states, attention_mask=None, past_key_values: WindowKVCache | None = None,
                 use_cache: bool = False, cu_seqlens=None, positions=None, **_):
         B, T, _ = hidden_states.shape
+        if isinstance(past_key_values, StaticWindowCache):          # one token, nothing read on the host (capturable)
+            cache = past_key_values
+            q, k, v = self.project_qkv(hidden_states, 0, max_seqlen=cache.max_position, positions=cache.positions)
+            k_all, v_all, kv_len = cache.append(k, v, self.layer_idx)
+            return self.finish(ops.decode_attention(q, k_all, v_all, kv_len), hidden_states), cache
         offset = 0
         cp = _cp_state() if past_key_values is None else None
         if cp is not None:
@@ -223,7 +306,11 @@ class Attention(nn.Module):
             k_all, v_all = past_key_values.update(k, v, self.layer_idx, self.window_size)
             if had_content:
                 k, v = k_all, v_all
-        if cp is not None:
+        if self.use_l2_softmax:
+            if cp is not None or (attention_mask is not None and not bool(attention_mask.all())):
+                raise NotImplementedError("use_l2_softmax with context parallelism or a padding mask")
+            o = ops.l2_softmax_attention(q, k, v, cu_seqlens=cu_seqlens)
+        elif cp is not None:
             from ..parallel import context as _context
             o = _context.attention(q, k, v, self.window_size, None, self.layer_idx)
         elif attention_mask is not None and not bool(attention_mask.all()):

@@ -30,6 +30,7 @@ def build_attention(config, layer_idx: int, with_rope_scaling: bool) -> Attentio
         elementwise_affine=config.elementwise_affine,
         norm_eps=config.norm_eps,
         rope_scaling=getattr(config, "rope_scaling", None) if with_rope_scaling else None,
+        use_l2_softmax=bool(getattr(config, "use_l2_softmax", False)),
     )
 
 

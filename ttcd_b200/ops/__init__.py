@@ -123,6 +123,29 @@ def attention(q, k, v, window=None, scale=None, cu_seqlens=None, return_lse: boo
 _DUAL_IMPL = "fused"
 
 
+def l2_softmax_attention(q, k, v, scale=None, cu_seqlens=None):
+    """Causal attention with L2-normalised exponentials (``use_l2_softmax``): PyTorch statement on every device (no
+    shipped config enables it)."""
+    return reference.l2_softmax_attention(q, k, v, scale, cu_seqlens)
+
+
+def decode_attention(q, k, v, kv_len, scale=None):
+    """One decode step over a fixed-capacity cache: q [B,1,H,D] against the first ``kv_len`` rows (a one-element int32
+    device tensor, read on the device) of k, v [B,cap,HK,D], in whatever order they sit (a ring buffer): no positional
+    mask, every filled row is visible.  Nothing here reads ``kv_len`` on the host, so the call can be captured."""
+    if _native.use_native(q) and q.shape[1] == 1 and _cuda().attn_small_q_supported(q, k):
+        return _cuda().attn_small_q(q, k, v, None, scale, kv_len)
+    B, _, H, D = q.shape
+    cap, HK = k.shape[1], k.shape[2]
+    scale = D ** -0.5 if scale is None else scale
+    kf = k.float().repeat_interleave(H // HK, dim=2)
+    vf = v.float().repeat_interleave(H // HK, dim=2)
+    s = torch.einsum("bqhd,bkhd->bhqk", q.float(), kf) * scale
+    hidden = torch.arange(cap, device=q.device) >= kv_len.to(q.device)
+    p = torch.softmax(s.masked_fill(hidden[None, None, None, :], float("-inf")), dim=-1)
+    return torch.einsum("bhqk,bkhd->bqhd", p, vf).to(q.dtype)
+
+
 def set_dual_attention_impl(impl: str) -> str:
     """``fused`` (default: one pass over K/V) or ``two_pass`` (two single-window calls, the reference's
     unpatched behaviour) — an A/B switch for benchmarks.  Returns the previous setting."""

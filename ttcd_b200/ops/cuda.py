@@ -470,10 +470,11 @@ class _QKNormRope(torch.autograd.Function):
         off = 0 if isinstance(offset, torch.Tensor) else int(offset)
         if isinstance(offset, torch.Tensor):
             pos = (torch.arange(T, device=q.device)[None, :] + offset.to(q.device).view(-1, 1)).to(torch.int32).reshape(-1)
-        if cos is not None:
+        if cos is not None and not getattr(positions, "_ttcd_bounded", False):      # (a static cache checked its bound)
             need = (int(pos.max()) if pos is not None else T - 1 + off) + 1
             if cos.shape[0] < need:
                 raise ValueError(f"rotary table has {cos.shape[0]} positions, need {need}")
+        if cos is not None:
             cos, sin = cos.contiguous(), sin.contiguous()
         nv.call("ttcd_qk_norm_rope_fwd", nv.ptr(q), nv.i64(ldq), nv.ptr(k), nv.i64(ldk), nv.ptr(q_out), nv.i64(H * D),
                 nv.ptr(k_out), nv.i64(HK * D), nv.ptr(qwb), nv.ptr(kwb), nv.ptr(cos), nv.ptr(sin), nv.ptr(pos),
@@ -799,9 +800,11 @@ def attn_small_q_supported(q, k) -> bool:
             and k.shape[1] >= q.shape[1] and q.shape[2] % k.shape[2] == 0)
 
 
-def attn_small_q(q, k, v, window=None, scale=None):
+def attn_small_q(q, k, v, window=None, scale=None, kv_len=None):
     """Attention of a few query rows (a decode step or a short continuation) over a key/value cache: bottom-right
-    aligned causal mask, optional window; forward only (split over the keys, merged by a second pass)."""
+    aligned causal mask, optional window; forward only (split over the keys, merged by a second pass).  ``kv_len``
+    (int32 device tensor of one element) says how many of the key rows are filled and is read by the kernel, so a
+    captured launch follows a cache that fills up between replays."""
     B, Tq, H, D = q.shape
     Tk, HK = k.shape[1], k.shape[2]
     scale = D ** -0.5 if scale is None else scale
@@ -814,7 +817,7 @@ def attn_small_q(q, k, v, window=None, scale=None):
     part_ml = torch.empty(B, H, Tq, splits, 2, dtype=torch.float32, device=q.device)
     nv.call("ttcd_attn_small_q", nv.ptr(q), nv.ptr(k), nv.ptr(v), nv.ptr(out), nv.ptr(part_o), nv.ptr(part_ml), nv.i32(B),
             nv.i32(Tq), nv.i32(Tk), nv.i32(H), nv.i32(HK), nv.i32(D), nv.i64(ldq), nv.i64(ldk), nv.i64(ldv), nv.i64(sq),
-            nv.i64(sk), nv.i64(sv), nv.i32(window or 0), nv.f32(scale), nv.i32(splits), nv.stream_ptr())
+            nv.i64(sk), nv.i64(sv), nv.i32(window or 0), nv.f32(scale), nv.i32(splits), nv.ptr(kv_len), nv.stream_ptr())
     return out
 
 

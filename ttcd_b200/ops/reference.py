@@ -173,6 +173,34 @@ def dual_window_attention(q, k, v, window_teacher: int | None, window_student: i
     return o_t, o_s
 
 
+def l2_softmax_attention(q, k, v, scale: float | None = None, cu_seqlens=None, block: int = 1024):
+    """Causal attention whose weights are the exponentials normalised by their L2 norm instead of their sum:
+    p_ij = exp(s_ij - m_i) / sqrt(sum_j exp(2 (s_ij - m_i)))  (fla/ops/attn/parallel.py:71-165 with ``use_l2``; the
+    reference applies no sliding window on this path, fla/layers/attn.py:246-279).  q [B,Tq,H,D], k/v [B,Tk,HK,D],
+    bottom-right aligned when Tq < Tk; query rows are processed ``block`` at a time so that the score matrix stays
+    small.  Differentiable through autograd."""
+    if cu_seqlens is not None:
+        bounds = cu_seqlens.tolist()
+        return torch.cat([l2_softmax_attention(q[:, a:b], k[:, a:b], v[:, a:b], scale, None, block)
+                          for a, b in zip(bounds[:-1], bounds[1:])], dim=1)
+    B, Tq, H, D = q.shape
+    Tk, HK = k.shape[1], k.shape[2]
+    scale = D ** -0.5 if scale is None else scale
+    kf = k.float().repeat_interleave(H // HK, dim=2)
+    vf = v.float().repeat_interleave(H // HK, dim=2)
+    outs = []
+    for r0 in range(0, Tq, block):
+        r1 = min(Tq, r0 + block)
+        hi = Tk - Tq + r1                                            # keys any row of this block may see
+        s = torch.einsum("bqhd,bkhd->bhqk", q[:, r0:r1].float(), kf[:, :hi]) * scale
+        rows = torch.arange(r0, r1, device=q.device)[:, None] + (Tk - Tq)
+        s = s.masked_fill(torch.arange(hi, device=q.device)[None, :] > rows, float("-inf"))
+        e = torch.exp(s - s.amax(dim=-1, keepdim=True))
+        p = e / e.square().sum(-1, keepdim=True).sqrt()
+        outs.append(torch.einsum("bhqk,bkhd->bqhd", p, vf[:, :hi]))
+    return torch.cat(outs, dim=1).to(q.dtype)
+
+
 def lse_merge(o_a, lse_a, o_b, lse_b):
     """Merge two partial softmax results (o[B,T,H,D], lse[B,H,T]) over disjoint key sets."""
     m = torch.maximum(lse_a, lse_b)
