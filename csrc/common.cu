@@ -30,6 +30,14 @@ int make_tmap_bf16_3d(CUtensorMap* map, const void* base, uint64_t inner, uint64
                       uint32_t box_rows) {
   auto encode = get_encode();
   if (encode == nullptr) return TTCD_ERR_TMAP;
+  // The encode is a driver call and wants a current context.  A thread whose first CUDA work is one of these
+  // launches (an autograd worker running a GEMM as the first node of a backward pass) has made no runtime call yet
+  // that would have bound the primary context to it: bind it once per thread.
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    cudaFree(nullptr);
+    context_bound = true;
+  }
   if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (row_stride_elems % 8) != 0) return TTCD_ERR_ARG;
   if (batch > 1 && (batch_stride_elems % 8) != 0) return TTCD_ERR_ARG;
   cuuint64_t dims[3] = {inner, rows, batch == 0 ? 1 : batch};

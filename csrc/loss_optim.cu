@@ -25,18 +25,25 @@ __device__ __forceinline__ float block_reduce(float v, float* scratch, bool is_m
   return out;
 }
 
-// One block per row of logits [rows][ld] (bf16).  Writes loss_row[row] = lse - logit[label] (0 when
-// ignored) and, when write_grad, overwrites the row with (softmax - onehot) * (*grad_scale).
+// One block per row of logits [rows][ld] (bf16).  With eps = label smoothing and zeta = the weight of lse^2:
+//   loss_row[row] = lse - (1 - eps) logit[label] - eps mean(logits) + zeta lse^2      (0 when the label is ignored)
+// and, when write_grad, the row is overwritten with its gradient times (*grad_scale):
+//   softmax (1 + 2 zeta lse) - (1 - eps) onehot - eps / V
+// l2_factor > 0 adds the l2-warp term on EVERY row (ignored ones too, as the reference's fused linear-CE does,
+// fla/modules/fused_linear_cross_entropy.py:250-283): max logit * l2_factor * (*grad_scale) at the arg-max column
+// (the lowest column on ties); the loss value is unchanged by it.
 __global__ void __launch_bounds__(1024) ce_rows_kernel(bf16* __restrict__ logits, const int64_t* __restrict__ labels,
                                                        float* __restrict__ loss_row, float* __restrict__ lse_row,
                                                        const float* __restrict__ grad_scale, int V, int64_t ld,
-                                                       int ignore_index, int write_grad) {
+                                                       int ignore_index, int write_grad, float eps, float zeta,
+                                                       float l2_factor) {
   __shared__ float scratch[33];
   const int64_t row = blockIdx.x;
   bf16* lr = logits + row * ld;
   const int64_t label = labels[row];
   const int nvec = V / 8;
-  float m = -INFINITY, s = 0.f;
+  float m = -INFINITY, s = 0.f, sumx = 0.f;
+  int arg = 0;
   for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
     const uint4 raw = *reinterpret_cast<const uint4*>(lr + i * 8);
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -48,34 +55,50 @@ __global__ void __launch_bounds__(1024) ce_rows_kernel(bf16* __restrict__ logits
       f[2 * k + 1] = t.y;
     }
     float lm = f[0];
+    int la = 0;
 #pragma unroll
-    for (int k = 1; k < 8; ++k) lm = fmaxf(lm, f[k]);
+    for (int k = 1; k < 8; ++k)
+      if (f[k] > lm) { lm = f[k]; la = k; }
     if (lm > m) {
       s *= __expf(m - lm);
       m = lm;
+      arg = i * 8 + la;
     }
 #pragma unroll
-    for (int k = 0; k < 8; ++k) s += __expf(f[k] - m);
+    for (int k = 0; k < 8; ++k) {
+      s += __expf(f[k] - m);
+      sumx += f[k];
+    }
   }
   for (int i = nvec * 8 + threadIdx.x; i < V; i += blockDim.x) {
     const float f = __bfloat162float(lr[i]);
     if (f > m) {
       s *= __expf(m - f);
       m = f;
+      arg = i;
     }
     s += __expf(f - m);
+    sumx += f;
   }
   const float gm = block_reduce(m, scratch, true);
   s = (m == -INFINITY) ? 0.f : s * __expf(m - gm);
   const float gs = block_reduce(s, scratch, false);
   const float lse = gm + __logf(gs);
+  float mean_x = 0.f;
+  if (eps != 0.f) mean_x = block_reduce(sumx, scratch, false) / static_cast<float>(V);
+  int arg_col = -1;
+  if (l2_factor != 0.f && write_grad)         // column indices are below 2^24: exact as floats
+    arg_col = -static_cast<int>(block_reduce(m == gm ? -static_cast<float>(arg) : -INFINITY, scratch, true));
   const bool valid = label != ignore_index && label >= 0 && label < V;
   if (threadIdx.x == 0) {
-    loss_row[row] = valid ? lse - __bfloat162float(lr[label]) : 0.f;
+    loss_row[row] = valid ? lse - (1.f - eps) * __bfloat162float(lr[label]) - eps * mean_x + zeta * lse * lse : 0.f;
     if (lse_row != nullptr) lse_row[row] = lse;
   }
   if (!write_grad) return;
-  const float scale = valid ? *grad_scale : 0.f;
+  const float gsc = *grad_scale;
+  const float scale = valid ? gsc : 0.f;
+  const float pw = 1.f + 2.f * zeta * lse, hot = 1.f - eps, flat = eps / static_cast<float>(V);
+  const float warp_term = gm * l2_factor * gsc;
   __syncthreads();  // label logit read above before the row is overwritten
   for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
     uint4 raw = *reinterpret_cast<const uint4*>(lr + i * 8);
@@ -84,8 +107,8 @@ __global__ void __launch_bounds__(1024) ce_rows_kernel(bf16* __restrict__ logits
     for (int k = 0; k < 4; ++k) {
       float2 t = unpack_bf16(w[k]);
       const int c = i * 8 + 2 * k;
-      t.x = (__expf(t.x - lse) - (c == label ? 1.f : 0.f)) * scale;
-      t.y = (__expf(t.y - lse) - (c + 1 == label ? 1.f : 0.f)) * scale;
+      t.x = (__expf(t.x - lse) * pw - (c == label ? hot : 0.f) - flat) * scale + (c == arg_col ? warp_term : 0.f);
+      t.y = (__expf(t.y - lse) * pw - (c + 1 == label ? hot : 0.f) - flat) * scale + (c + 1 == arg_col ? warp_term : 0.f);
       w[k] = pack_bf16(t.x, t.y);
     }
     raw.x = w[0]; raw.y = w[1]; raw.z = w[2]; raw.w = w[3];
@@ -93,7 +116,7 @@ __global__ void __launch_bounds__(1024) ce_rows_kernel(bf16* __restrict__ logits
   }
   for (int i = nvec * 8 + threadIdx.x; i < V; i += blockDim.x) {
     const float f = __bfloat162float(lr[i]);
-    lr[i] = __float2bfloat16((__expf(f - lse) - (i == label ? 1.f : 0.f)) * scale);
+    lr[i] = __float2bfloat16((__expf(f - lse) * pw - (i == label ? hot : 0.f) - flat) * scale + (i == arg_col ? warp_term : 0.f));
   }
 }
 
@@ -199,11 +222,13 @@ static unsigned flat_grid(long long n) {
 // logits: [rows][ld] bf16 (modified in place when write_grad); labels: int64 [rows].
 TTCD_EXPORT int ttcd_ce_rows(void* logits, const long long* labels, float* loss_row, float* lse_row,
                              const float* grad_scale, long long rows, int V, long long ld, int ignore_index,
-                             int write_grad, void* stream_ptr) {
+                             int write_grad, float label_smoothing, float lse_square_scale, float l2_factor,
+                             void* stream_ptr) {
   if (rows <= 0 || V <= 0 || ld % 8 != 0 || (write_grad && grad_scale == nullptr)) return TTCD_ERR_ARG;
+  if (label_smoothing < 0.f || label_smoothing >= 1.f || V >= (1 << 24)) return TTCD_ERR_ARG;
   ce_rows_kernel<<<static_cast<unsigned>(rows), 1024, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
       static_cast<bf16*>(logits), reinterpret_cast<const int64_t*>(labels), loss_row, lse_row, grad_scale, V, ld,
-      ignore_index, write_grad);
+      ignore_index, write_grad, label_smoothing, lse_square_scale, l2_factor);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -58,20 +58,18 @@ def load_tokenizer(path: str):
 
 
 @torch.no_grad()
-def greedy_decode(model, input_ids: torch.Tensor, max_new_tokens: int, eos_ids: set[int] | None = None) -> list[int]:
-    """Batch-1 greedy decoding: one prefill with the cache, then one token per step."""
-    out = model(input_ids=input_ids, use_cache=True, logits_to_keep=1)
-    cache = out.past_key_values
+def greedy_decode(model, input_ids: torch.Tensor, max_new_tokens: int, eos_ids: set[int] | None = None,
+                  use_graph: bool = True) -> list[int]:
+    """Batch-1 greedy decoding through the model's own ``generate`` (one prefill with the cache, then one token per
+    step: a replayed CUDA graph on the native path unless ``use_graph`` is off); the tokens before the first
+    end-of-sequence token are returned."""
+    tokens = model.generate(input_ids, max_new_tokens=max_new_tokens, do_sample=False,
+                            eos_token_id=sorted(eos_ids) if eos_ids else None, use_graph=use_graph)
     produced: list[int] = []
-    nxt = out.logits[:, -1].argmax(-1, keepdim=True)
-    for _ in range(max_new_tokens):
-        tok = int(nxt)
+    for tok in tokens[0, input_ids.shape[1]:].tolist():
         if eos_ids and tok in eos_ids:
             break
         produced.append(tok)
-        out = model(input_ids=nxt, past_key_values=cache, use_cache=True, logits_to_keep=1)
-        cache = out.past_key_values
-        nxt = out.logits[:, -1].argmax(-1, keepdim=True)
     return produced
 
 

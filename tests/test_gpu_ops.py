@@ -213,6 +213,42 @@ def test_linear_cross_entropy():
     _close(w.grad, wf.grad, 3e-5, 5e-2, "lce dw")
 
 
+@pytest.mark.parametrize("smoothing,z", [(0.1, 0.0), (0.0, 1e-3), (0.05, 2e-4)])
+def test_cross_entropy_label_smoothing_and_z_loss(smoothing, z):
+    V = 4096 + 24                                   # a ragged tail after the vector loop
+    logits = (torch.randn(200, V, device=DEV) * 3).to(BF).requires_grad_()
+    labels = torch.randint(0, V, (200,), device=DEV)
+    labels[::5] = -100
+    loss = ops.cross_entropy(logits, labels, label_smoothing=smoothing, z_loss=z)
+    loss.backward()
+    lf = logits.detach().float().requires_grad_()
+    lr = ref.cross_entropy(lf, labels, label_smoothing=smoothing, z_loss=z)
+    lr.backward()
+    assert abs(loss.item() - lr.item()) < 2e-3 * max(1.0, abs(lr.item())), (loss.item(), lr.item())
+    _close(logits.grad, lf.grad, 2e-5, 2e-2, "dlogits")
+
+
+def test_linear_cross_entropy_with_l2_warp():
+    """The l2-warp term (max logit * 1e-4 / valid tokens at each row's arg-max) is added inside the row kernel."""
+    N, Hd, V = 600, 256, 4096
+    h = (torch.randn(N, Hd, device=DEV) * 0.5).to(BF).requires_grad_()
+    w = (torch.randn(V, Hd, device=DEV) * 0.1).to(BF).requires_grad_()
+    labels = torch.randint(0, V, (N,), device=DEV)
+    labels[:50] = -100
+    penalty = 20.0                                  # large enough to stand out from bf16 rounding of the CE part
+    plain = ops.linear_cross_entropy(h, labels, w, num_chunks=3)
+    g_plain = torch.autograd.grad(plain, [h, w])
+    loss = ops.linear_cross_entropy(h, labels, w, num_chunks=3, l2_penalty=penalty)
+    loss.backward()
+    assert abs(loss.item() - plain.item()) < 1e-6                          # the term touches gradients only
+    hf, wf = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    lr = ref.linear_cross_entropy(hf, labels, wf, l2_penalty=penalty)
+    lr.backward()
+    assert (h.grad - g_plain[0]).abs().max() > 1e-4, "the penalty changed nothing"
+    _close(h.grad, hf.grad, 1e-4, 5e-2, "lce+l2warp dh")
+    _close(w.grad, wf.grad, 1e-4, 5e-2, "lce+l2warp dw")
+
+
 def test_adamw_and_sumsq():
     from ttcd_b200.ops import cuda
     n = 100_003

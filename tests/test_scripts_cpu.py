@@ -4,6 +4,7 @@ import subprocess
 import sys
 from pathlib import Path
 
+import pytest
 import torch
 
 ROOT = Path(__file__).resolve().parents[1]
@@ -193,3 +194,44 @@ def test_checkpoint_bench_runs_both_attention_implementations(tmp_path):
         ops.set_dual_attention_impl("fused")
     assert len(a["predictions"]) == 2 and a["predictions"] == b["predictions"]
     assert a["median_prefill_ms"] > 0 and "decode_ms_per_token" in a
+
+
+def test_ab_harness_reports_agreement_of_two_arms(tmp_path, monkeypatch):
+    """scripts/eval_ab.py on a tiny random model: the task suite (prediction identity), NLL per arm and the KL pass
+    between the two dual-attention implementations, written to one report."""
+    import eval_ab as ab
+    from ttcd_b200.models import IPTTCDv9Config, IPTTCDForCausalLM
+
+    class Tok:
+        eos_token_id = None
+
+        def __call__(self, text, return_tensors=None, add_special_tokens=False):
+            from types import SimpleNamespace
+            return SimpleNamespace(input_ids=torch.tensor([[(ord(c) * 7) % 61 for c in text]]))
+
+        def decode(self, ids, skip_special_tokens=True):
+            return " ".join(str(i) for i in ids)
+
+    torch.manual_seed(0)
+    model = IPTTCDForCausalLM(IPTTCDv9Config(hidden_size=32, num_hidden_layers=2, num_heads=4, num_kv_heads=2, head_dim=8,
+                                             intermediate_size=64, vocab_size=64, window_size=24, window_size_student=8,
+                                             ttt_mode=True, ttt_chunk=8, ttt_layers=[1], fuse_cross_entropy=False,
+                                             fuse_linear_cross_entropy=False, max_position_embeddings=256)).eval()
+    monkeypatch.setattr(ab, "load_model", lambda args: model)
+    monkeypatch.setattr(ab, "load_tokenizer", lambda path: Tok())
+    d = tmp_path / "ctx64" / "niah_single_1"
+    d.mkdir(parents=True)
+    (d / "validation.jsonl").write_text("\n".join(
+        json.dumps({"input": "abcdefgh" * (4 + i), "answer_prefix": " ans", "outputs": ["1"]}) for i in range(3)))
+    out = tmp_path / "ab.json"
+    rep = ab.main(["--tokenizer", "none", "--device", "cpu", "--data_dir", str(tmp_path), "--tasks", "niah_single_1",
+                   "--ctx_lens", "64", "--max_samples", "2", "--max_new_tokens", "4", "--seq_len", "48", "--ppl_docs", "3",
+                   "--kl_docs", "2", "--output", str(out)])
+    saved = json.loads(out.read_text())
+    assert saved["arm_a"] == {"attn": "two_pass", "decode": "eager"} and saved["arm_b"] == {"attn": "fused", "decode": "graph"}
+    assert saved["identical_predictions"] == [2, 2] and saved["tasks"]["niah_single_1@64"]["n"] == 2
+    dist = saved["distribution"]
+    assert dist["docs"] == 3 and dist["kl_tokens"] == 2 * 48 and dist["kl_max"] < 1e-6 and dist["top1_flip_rate"] == 0.0
+    assert abs(dist["nll_diff"]) < 1e-5 and rep["arms_agree"] is True
+    with pytest.raises(SystemExit):
+        ab.parse_arm("attn=flash")

@@ -14,7 +14,8 @@ from .modeling_delta_net import (DeltaNet, DeltaNetBlock, DeltaNetForCausalLM, D
                                  GatedDeltaNetForCausalLM, GatedDeltaNetModel, RecurrentCache, ShortConv)
 from .modeling_deltanet_baseline import DeltaNetBaselineBlock, DeltaNetBaselineForCausalLM, DeltaNetBaselineModel
 from .modeling_ipttcdv9 import IPTTCDBlock, IPTTCDForCausalLM, IPTTCDMLP, IPTTCDModel
-from .modeling_ipttt import IPTTTBlock, IPTTTForCausalLM, IPTTTMLP, IPTTTModel
+from .modeling_ipttt import FastWeightCache, IPTTTBlock, IPTTTForCausalLM, IPTTTMLP, IPTTTModel
+from .modeling_ipttt_llama import IPTTTLlamaForCausalLM, TTTDynamicCache, ipttt_config_from_llama
 from .modeling_transformer import TransformerBlock, TransformerForCausalLM, TransformerModel
 
 IPTTCDv9Model = IPTTCDModel
@@ -51,7 +52,8 @@ __all__ = [
     "DeltaNetBaselineConfig", "DeltaNetBaselineModel", "DeltaNetBaselineForCausalLM", "DeltaNetBaselineBlock",
     "TransformerConfig", "IPTTTConfig", "IPTTCDConfig", "IPTTCDv8Config", "IPTTCDv9Config", "IPTTCDv9LowCopyConfig",
     "TransformerModel", "TransformerForCausalLM", "TransformerBlock",
-    "IPTTTModel", "IPTTTForCausalLM", "IPTTTBlock", "IPTTTMLP",
+    "IPTTTModel", "IPTTTForCausalLM", "IPTTTBlock", "IPTTTMLP", "FastWeightCache",
+    "IPTTTLlamaForCausalLM", "TTTDynamicCache", "ipttt_config_from_llama",
     "IPTTCDModel", "IPTTCDForCausalLM", "IPTTCDBlock", "IPTTCDMLP", "IPTTCDv9Model", "IPTTCDv9ForCausalLM",
     "Attention", "GatedMLP", "RMSNorm", "RotaryEmbedding", "WindowKVCache", "register_all",
 ]

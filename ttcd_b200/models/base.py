@@ -32,14 +32,16 @@ class FusedLinearCrossEntropyLoss(nn.Module):
 
     ignore_index = IGNORE_INDEX
 
-    def __init__(self, num_chunks: int = 8, use_l2warp: bool = False):
+    def __init__(self, num_chunks: int = 8, use_l2warp: bool = False, l2_penalty_factor: float = 1e-4):
         super().__init__()
         self.num_chunks = num_chunks
         self.use_l2warp = use_l2warp
+        self.l2_penalty_factor = l2_penalty_factor
 
     def forward(self, hidden, labels, weight, bias=None):
         return ops.linear_cross_entropy(hidden.reshape(-1, hidden.shape[-1]), labels.reshape(-1), weight, bias,
-                                        self.ignore_index, self.num_chunks)
+                                        self.ignore_index, self.num_chunks,
+                                        self.l2_penalty_factor if self.use_l2warp else 0.0)
 
 
 class FusedCrossEntropyLoss(nn.Module):
@@ -286,7 +288,8 @@ class DecoderForCausalLM(DecoderPreTrainedModel):
     @torch.no_grad()
     def generate(self, input_ids: torch.Tensor, max_new_tokens: int = 32, do_sample: bool = False,
                  temperature: float = 1.0, top_k: int | None = None, top_p: float | None = None,
-                 eos_token_id: int | list[int] | None = None, attention_mask=None, use_graph: bool = True, **_):
+                 eos_token_id: int | list[int] | None = None, attention_mask=None, use_graph: bool = True,
+                 past_key_values=None, **_):
         """Prefill once (TTT layers run their dual path), then decode token by token from the cache.
 
         Mirrors the reference's behaviour: fast weights are built during prefill only and are not
@@ -296,7 +299,7 @@ class DecoderForCausalLM(DecoderPreTrainedModel):
         """
         eos = set(eos_token_id if isinstance(eos_token_id, (list, tuple)) else
                   ([eos_token_id] if eos_token_id is not None else []))
-        cache = getattr(self.model, "cache_class", WindowKVCache)()
+        cache = past_key_values if past_key_values is not None else getattr(self.model, "cache_class", WindowKVCache)()
         out = self(input_ids=input_ids, attention_mask=attention_mask, past_key_values=cache,
                    use_cache=True, logits_to_keep=1)
         tokens = input_ids

@@ -185,7 +185,9 @@ class IPTTTConfig(_TableConfig):
         _check_ttt_common(self)
         if self.ttt_proj_init not in {"diagonal", "diagonal_gaussian", "zero"}:
             raise ValueError("`ttt_proj_init` must be one of {'diagonal', 'diagonal_gaussian', 'zero'}.")
-        if self.ttt_target not in {"hidden", "embedding"}:
+        # "layer_input" (the residual stream entering the block) is what the HF-Llama inference port of the reference
+        # feeds its fast weights (custom_models/ipttt/inference.py:783-816); the training model knows the other two
+        if self.ttt_target not in {"hidden", "embedding", "layer_input"}:
             raise ValueError("`ttt_target` must be one of {'hidden', 'embedding'}.")
         if self.ttt_conv_kernel_size <= 0 or self.ttt_conv_kernel_size % 2 == 0:
             raise ValueError("`ttt_conv_kernel_size` must be a positive odd integer.")

@@ -42,7 +42,7 @@ class RMSNorm(nn.Module):
 
 
 class RotaryEmbedding(nn.Module):
-    """NeoX-style rotary tables with optional YaRN rescaling (mscale baked into cos/sin)."""
+    """NeoX-style rotary tables with optional YaRN (mscale baked into cos/sin) or Llama-3 frequency rescaling."""
 
     def __init__(self, dim: int, base: float = 10000.0, rope_scaling: dict | None = None):
         super().__init__()
@@ -53,9 +53,17 @@ class RotaryEmbedding(nn.Module):
         kind = None if rope_scaling is None else (rope_scaling.get("type") or rope_scaling.get("rope_type"))
         if kind in (None, "default"):      # transformers >= 5 writes {"rope_type": "default"} for plain RoPE
             rope_scaling = None
-        if rope_scaling is not None:
+        self.llama3 = None
+        if rope_scaling is not None and kind == "llama3":
+            self.llama3 = dict(
+                factor=float(rope_scaling.get("factor", 1.0)),
+                original_max_position=int(rope_scaling["original_max_position_embeddings"]),
+                low_freq_factor=float(rope_scaling.get("low_freq_factor", 1.0)),
+                high_freq_factor=float(rope_scaling.get("high_freq_factor", 4.0)),
+            )
+        elif rope_scaling is not None:
             if kind != "yarn":
-                raise NotImplementedError(f"rope_scaling type {kind!r} is not supported (only 'yarn')")
+                raise NotImplementedError(f"rope_scaling type {kind!r} is not supported (only 'yarn' and 'llama3')")
             factor = float(rope_scaling.get("factor", 1.0))
             self.yarn = dict(
                 factor=factor,
@@ -71,6 +79,8 @@ class RotaryEmbedding(nn.Module):
     def inv_freq(self, device=None) -> torch.Tensor:
         if self.yarn is not None and self.yarn["factor"] > 1.0:
             return ref_ops.yarn_inv_freq(self.dim, self.base, device=device, **self.yarn)
+        if self.llama3 is not None:
+            return ref_ops.llama3_inv_freq(self.dim, self.base, device=device, **self.llama3)
         return 1.0 / (self.base ** (torch.arange(0, self.dim, 2, device=device, dtype=torch.float32) / self.dim))
 
     def tables(self, seqlen: int, device, dtype):

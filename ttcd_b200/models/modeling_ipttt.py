@@ -153,14 +153,15 @@ class IPTTTBlock(nn.Module):
 
     def forward(self, hidden_states, attention_mask=None, past_key_values=None, use_cache=False,
                 ttt_target_states=None, **kwargs):
-        residual = hidden_states
+        residual = layer_input = hidden_states
         hidden_states = self.attn_norm(hidden_states)
         hidden_states, _ = self.attn(hidden_states, attention_mask=attention_mask,
                                      past_key_values=past_key_values, use_cache=use_cache, **kwargs)
         hidden_states, residual = self.mlp_norm(hidden_states, residual, True)
         target = None
         if self.is_ttt_layer:
-            target = ttt_target_states if self.config.ttt_target == "embedding" else hidden_states
+            kind = self.config.ttt_target
+            target = ttt_target_states if kind == "embedding" else (layer_input if kind == "layer_input" else hidden_states)
         if self.is_ttt_layer and isinstance(past_key_values, FastWeightCache) and not self.training:
             return residual + self._online_mlp(hidden_states, target, past_key_values)
         hidden_states = self.mlp(hidden_states, t=target)

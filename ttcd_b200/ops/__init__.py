@@ -217,15 +217,18 @@ def ttt_scan(z_out, z_tgt, z_hat, beta, w_down, w_update_t, *, lr, update_every,
 # -- losses ------------------------------------------------------------------------------------
 
 def cross_entropy(logits, labels, ignore_index: int = -100, label_smoothing: float = 0.0, z_loss: float = 0.0):
-    if _native.use_native(logits) and label_smoothing == 0.0 and z_loss == 0.0:
-        return _cuda().cross_entropy(logits, labels, ignore_index)
+    if _native.use_native(logits) and logits.dim() == 2 and logits.shape[-1] % 8 == 0:
+        return _cuda().cross_entropy(logits, labels, ignore_index, label_smoothing, z_loss)
     return reference.cross_entropy(logits, labels, ignore_index, label_smoothing, z_loss)
 
 
-def linear_cross_entropy(hidden, labels, weight, bias=None, ignore_index: int = -100, num_chunks: int = 8):
+def linear_cross_entropy(hidden, labels, weight, bias=None, ignore_index: int = -100, num_chunks: int = 8,
+                         l2_penalty: float = 0.0):
+    """CE(hidden @ weight^T) without the full logits; ``l2_penalty`` > 0 adds the l2-warp gradient term (max logit
+    * l2_penalty / valid tokens at each row's arg-max column) inside the same pass."""
     if _native.use_native(hidden) and bias is None:
-        return _cuda().linear_cross_entropy(hidden, labels, weight, ignore_index, num_chunks)
-    return reference.linear_cross_entropy(hidden, labels, weight, bias, ignore_index)
+        return _cuda().linear_cross_entropy(hidden, labels, weight, ignore_index, num_chunks, l2_penalty)
+    return reference.linear_cross_entropy(hidden, labels, weight, bias, ignore_index, l2_penalty)
 
 
 def newton_schulz(g, coeffs=reference.NS_COEFFS):

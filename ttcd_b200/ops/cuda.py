@@ -834,12 +834,12 @@ def lse_merge(o_a, lse_a, o_b, lse_b):
 # losses
 # =============================================================================================
 
-def _ce_rows(logits2, labels, inv_total, ignore_index, write_grad):
+def _ce_rows(logits2, labels, inv_total, ignore_index, write_grad, smoothing=0.0, z_scale=0.0, l2_factor=0.0):
     rows, V = logits2.shape
     loss_rows = torch.empty(rows, dtype=torch.float32, device=logits2.device)
     nv.call("ttcd_ce_rows", nv.ptr(logits2), nv.ptr(labels), nv.ptr(loss_rows), nv.ptr(None), nv.ptr(inv_total),
             nv.i64(rows), nv.i32(V), nv.i64(logits2.stride(0)), nv.i32(ignore_index), nv.i32(1 if write_grad else 0),
-            nv.stream_ptr())
+            nv.f32(smoothing), nv.f32(z_scale), nv.f32(l2_factor), nv.stream_ptr())
     return loss_rows
 
 
@@ -847,14 +847,14 @@ class _CrossEntropy(torch.autograd.Function):
     """Mean CE over valid rows; the gradient is computed in the forward, in place on a copy."""
 
     @staticmethod
-    def forward(ctx, logits, labels, ignore_index):
+    def forward(ctx, logits, labels, ignore_index, smoothing=0.0, z_scale=0.0):
         lg = logits.contiguous().clone() if logits.requires_grad else logits.contiguous()
         if lg.stride(0) % 8:
             raise ValueError("vocab size must be a multiple of 8 for the CE kernel")
         labels = labels.contiguous().to(torch.int64)
         total = labels.ne(ignore_index).sum().clamp_min(1).to(torch.float32)
         inv_total = (1.0 / total).reshape(1)
-        loss_rows = _ce_rows(lg, labels, inv_total, ignore_index, logits.requires_grad)
+        loss_rows = _ce_rows(lg, labels, inv_total, ignore_index, logits.requires_grad, smoothing, z_scale)
         if logits.requires_grad:
             ctx.save_for_backward(lg)
         return (loss_rows.sum() * inv_total).reshape(())
@@ -862,11 +862,11 @@ class _CrossEntropy(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         (dlogits,) = ctx.saved_tensors
-        return dlogits * g.to(dlogits.dtype), None, None
+        return dlogits * g.to(dlogits.dtype), None, None, None, None
 
 
-def cross_entropy(logits, labels, ignore_index=-100):
-    return _CrossEntropy.apply(logits, labels, int(ignore_index))
+def cross_entropy(logits, labels, ignore_index=-100, label_smoothing=0.0, z_loss=0.0):
+    return _CrossEntropy.apply(logits, labels, int(ignore_index), float(label_smoothing), float(z_loss))
 
 
 class _LinearCrossEntropy(torch.autograd.Function):
@@ -874,7 +874,7 @@ class _LinearCrossEntropy(torch.autograd.Function):
     dx and dW GEMMs, so the [tokens, vocab] logits never exist at once and there is no host sync."""
 
     @staticmethod
-    def forward(ctx, hidden, labels, weight, ignore_index, num_chunks):
+    def forward(ctx, hidden, labels, weight, ignore_index, num_chunks, l2_factor=0.0):
         N, Hd = hidden.shape
         V = weight.shape[0]
         hidden = hidden.contiguous()
@@ -888,12 +888,16 @@ class _LinearCrossEntropy(torch.autograd.Function):
         dx = torch.empty_like(hidden) if need_grad else None
         dw = torch.zeros(V, Hd, dtype=torch.float32, device=hidden.device) if need_grad else None
         loss = torch.zeros((), dtype=torch.float32, device=hidden.device)
-        logits = torch.empty(min(chunk, N), V, dtype=_BF16, device=hidden.device)
-        for s in range(0, N, chunk):
-            e = min(s + chunk, N)
+        logits = torch.empty(min(chunk + 127, N), V, dtype=_BF16, device=hidden.device)
+        bounds, s = [], 0
+        while s < N:                       # a tail shorter than one 128-row tile joins the chunk before it
+            e = N if N - (s + chunk) < 128 else s + chunk
+            bounds.append((s, e))
+            s = e
+        for s, e in bounds:
             lg = logits[: e - s]
             gemm(hidden[s:e], w.transpose(0, 1), out=lg.view(1, e - s, V))
-            loss_rows = _ce_rows(lg, labels[s:e], inv_total, ignore_index, need_grad)
+            loss_rows = _ce_rows(lg, labels[s:e], inv_total, ignore_index, need_grad, 0.0, 0.0, l2_factor)
             loss = loss + loss_rows.sum()
             if need_grad:
                 gemm(lg, w, out=dx[s:e].view(1, e - s, Hd))
@@ -906,12 +910,14 @@ class _LinearCrossEntropy(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         dx, dw = ctx.saved_tensors
-        return dx * g.to(dx.dtype), None, dw * g.to(dw.dtype), None, None
+        return dx * g.to(dx.dtype), None, dw * g.to(dw.dtype), None, None, None
 
 
-def linear_cross_entropy(hidden, labels, weight, ignore_index=-100, num_chunks=8):
+def linear_cross_entropy(hidden, labels, weight, ignore_index=-100, num_chunks=8, l2_penalty=0.0):
     _check(hidden, "hidden")
-    return _LinearCrossEntropy.apply(hidden, labels, weight, int(ignore_index), int(num_chunks))
+    if hidden.shape[0] < 128 or hidden.shape[1] < 64 or weight.shape[0] < 128:       # below one GEMM tile
+        return reference.linear_cross_entropy(hidden, labels, weight, None, ignore_index, l2_penalty)
+    return _LinearCrossEntropy.apply(hidden, labels, weight, int(ignore_index), int(num_chunks), float(l2_penalty))
 
 
 # =============================================================================================

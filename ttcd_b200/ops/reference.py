@@ -83,6 +83,21 @@ def yarn_inv_freq(head_dim: int, base: float, factor: float, original_max_positi
     return inv_freq * (1.0 - ramp) + (inv_freq / factor) * ramp
 
 
+def llama3_inv_freq(head_dim: int, base: float, factor: float, original_max_position: int,
+                    low_freq_factor: float = 1.0, high_freq_factor: float = 4.0, device=None) -> torch.Tensor:
+    """Llama-3 rotary scaling: wavelengths longer than original/low_freq_factor are slowed by ``factor``, those
+    shorter than original/high_freq_factor are kept, the band between is blended linearly in original/wavelength."""
+    inv_freq = 1.0 / (base ** (torch.arange(0, head_dim, 2, device=device, dtype=torch.float32) / head_dim))
+    wavelen = 2.0 * math.pi / inv_freq
+    low_wavelen = original_max_position / low_freq_factor
+    high_wavelen = original_max_position / high_freq_factor
+    smooth = ((original_max_position / wavelen - low_freq_factor) / (high_freq_factor - low_freq_factor)).clamp(0.0, 1.0)
+    blended = (1.0 - smooth) * inv_freq / factor + smooth * inv_freq
+    out = torch.where(wavelen > low_wavelen, inv_freq / factor, inv_freq)
+    middle = (wavelen <= low_wavelen) & (wavelen >= high_wavelen)
+    return torch.where(middle, blended, out)
+
+
 def yarn_mscale(factor: float, mscale: float = 1.0) -> float:
     if factor <= 1.0:
         return 1.0
@@ -366,10 +381,34 @@ def cross_entropy(logits, labels, ignore_index: int = -100, label_smoothing: flo
     return loss / valid.sum().clamp_min(1)
 
 
-def linear_cross_entropy(hidden, labels, weight, bias=None, ignore_index: int = -100):
-    """CE(hidden @ weight^T + bias, labels) with the logits GEMM in the activation dtype."""
+class _L2WarpRows(torch.autograd.Function):
+    """Identity on the loss; adds max logit * factor at every row's arg-max column to the gradient of the logits
+    (the l2-warp term of fla/modules/fused_linear_cross_entropy.py:250-283; every row, ignored labels included)."""
+
+    @staticmethod
+    def forward(ctx, loss, logits, factor):
+        ctx.save_for_backward(logits)
+        ctx.factor = factor
+        return loss.view_as(loss)
+
+    @staticmethod
+    def backward(ctx, grad):
+        (logits,) = ctx.saved_tensors
+        mx, idx = logits.max(-1, keepdim=True)
+        g = torch.zeros_like(logits).scatter_(-1, idx, mx * ctx.factor)
+        return grad, g * grad, None
+
+
+def linear_cross_entropy(hidden, labels, weight, bias=None, ignore_index: int = -100, l2_penalty: float = 0.0):
+    """CE(hidden @ weight^T + bias, labels) with the logits GEMM in the activation dtype; ``l2_penalty`` > 0 adds the
+    l2-warp gradient term scaled by 1 / (number of valid labels)."""
     logits = F.linear(hidden, weight.to(hidden.dtype), None if bias is None else bias.to(hidden.dtype))
-    return cross_entropy(logits.view(-1, logits.shape[-1]), labels.reshape(-1), ignore_index)
+    logits = logits.view(-1, logits.shape[-1])
+    loss = cross_entropy(logits, labels.reshape(-1), ignore_index)
+    if l2_penalty:
+        total = labels.ne(ignore_index).sum().clamp_min(1)
+        loss = _L2WarpRows.apply(loss, logits, l2_penalty / total)
+    return loss
 
 
 def l2_warp_grad(logits, loss_scale: float = 1e-4):
