@@ -52,6 +52,13 @@ def run(args, metric, ClockSampler, timed_region, dist_env):
     # declares the same tie as a list.  Setting the attribute changes no computation and is needed
     # to construct the tied-embedding recipe config at all on this image.
     compat = []
+    # transformers >= 5 fills `rope_scaling` with {"rope_type": "default", ...} for plain RoPE; upstream's attention
+    # layer (written against 4.57, where the field stays None) refuses every type but "yarn".  Plain RoPE is what the
+    # config asks for either way, so the field is put back to None (no computation changes).
+    scaling = getattr(cfg, "rope_scaling", None)
+    if isinstance(scaling, dict) and (scaling.get("rope_type") or scaling.get("type")) == "default":
+        cfg.rope_scaling = None
+        compat.append("config.rope_scaling {'rope_type': 'default'} -> None (transformers 5.x)")
     if getattr(cfg, "tie_word_embeddings", False):
         cls = AutoModelForCausalLM._model_mapping[type(cfg)]
         for klass in cls.__mro__:

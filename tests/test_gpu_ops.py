@@ -242,7 +242,12 @@ def test_linear_cross_entropy_with_l2_warp():
     loss.backward()
     assert abs(loss.item() - plain.item()) < 1e-6                          # the term touches gradients only
     hf, wf = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
-    lr = ref.linear_cross_entropy(hf, labels, wf, l2_penalty=penalty)
+    # the arg-max column is taken from the bf16 logits the kernel sees (an fp32 product breaks near-ties differently)
+    seen = ops.linear(h.detach(), w.detach()).float()
+    mx, idx = seen.max(-1, keepdim=True)
+    lg = hf @ wf.t()
+    total = labels.ne(-100).sum()
+    lr = ref.cross_entropy(lg, labels) + (lg.gather(-1, idx) * (mx * penalty / total)).sum()
     lr.backward()
     assert (h.grad - g_plain[0]).abs().max() > 1e-4, "the penalty changed nothing"
     _close(h.grad, hf.grad, 1e-4, 5e-2, "lce+l2warp dh")
