@@ -125,7 +125,8 @@ def test_hybrid_sharding_2x2_matches_one_process():
 # ------------------------------------------------------------------------------------- flags
 @pytest.mark.parametrize("flag", ["--training.enable_cpu_offload", "--optimizer.early_step_in_backward", "--training.compile",
                                   "--fault_tolerance.enable", "--float8.enable_fsdp_float8_all_gather",
-                                  "--memory_estimation.enabled", "--experimental.enable_compiled_autograd"])
+                                  "--memory_estimation.enabled", "--experimental.enable_compiled_autograd",
+                                  "--optimizer.use_distributed_muon"])
 def test_flags_without_machinery_are_refused(flag):
     with pytest.raises(NotImplementedError):
         JobConfig().parse_args([flag])

@@ -131,14 +131,17 @@ class ShardedDataParallel:
                  eps: float = 1e-8, weight_decay: float = 0.1, max_norm: float | None = 1.0,
                  param_dtype: torch.dtype = torch.bfloat16, overlap: bool = True, comm: str | None = None,
                  muon: bool = False, muon_momentum: float = 0.95, muon_filter=None, peer_wait_ns: int = 0,
-                 replicate_group: dist.ProcessGroup | None = None, shard_weights: bool = False):
+                 replicate_group: dist.ProcessGroup | None = None, shard_weights: bool = False, tensor_parallel=None):
         """``comm``: 'peer' = fused peer-memory kernels over NVLink (default on CUDA with the native
         library), 'nccl' = the NCCL reduce-scatter / all-gather baseline (also TTCD_COMM=nccl).
         ``peer_wait_ns``: budget of one peer-flag wait (0: the library default of 10 s).
         ``replicate_group``: hybrid sharding (the reference's HSDP mesh, flame/models/parallelize_fla.py:75-78):
         ``process_group`` shards the optimizer state, and the ranks of ``replicate_group`` (one per shard group,
-        holding the same shard) average their reduced gradient shards with an all-reduce before the update."""
+        holding the same shard) average their reduced gradient shards with an all-reduce before the update.
+        ``tensor_parallel``: the tensor-parallel state (``group``, ``rank``, ``world``) when the model's weights are
+        1/tp slices; Muon then orthogonalises the whole matrices (train/muon.py)."""
         import os
+        self.tensor_parallel = tensor_parallel
         self.shard_weights = bool(shard_weights)
         self.replicate_pg = replicate_group
         self.replicate_world = dist.get_world_size(replicate_group) if replicate_group is not None else 1
@@ -225,6 +228,8 @@ class ShardedDataParallel:
             for p, n in chosen:                      # Muon region: whole parameters, owned by one rank each
                 g.offsets.append(off)
                 mp = MuonParam(global_names[id(p)], p, gi, off)
+                spec = getattr(p, "_tp_shard", None)
+                mp.tp_dim = None if spec is None else int(spec[0])
                 g.muon.append(mp)
                 self.muon_params.append(mp)
                 off += _align(p.numel(), 8)
@@ -568,8 +573,14 @@ class ShardedDataParallel:
             lo = self.rank * shard if self.world > 1 else 0
             hi = lo + shard
             grad = self._local_grad(g)
+            muon = {id(mp.param): mp for mp in g.muon}
             for p, off in zip(g.params, g.offsets):
                 if id(p) not in wanted:
+                    continue
+                if id(p) in muon:                       # whole parameter at its owner, nothing elsewhere
+                    mp = muon[id(p)]
+                    if mp.owner == self.rank and mp.grad32 is not None:
+                        out.append(mp.grad32[:p.numel()])
                     continue
                 a, b = max(off, lo), min(off + p.numel(), hi)
                 if a < b:
@@ -705,7 +716,7 @@ class ShardedDataParallel:
             saved[id(mp)] = mp.grad32
             mp.grad32 = mp.grad32[:mp.param.numel()]
         muon_update_many(owned, lr, self.weight_decay, self.muon_momentum, coef,
-                         skip=self._skip if (self.skip_nan_inf or self.peer) else None)
+                         skip=self._skip if (self.skip_nan_inf or self.peer) else None, tp=self.tensor_parallel)
         for mp in owned:
             mp.grad32 = saved[id(mp)]
         for mp in self.muon_params:

@@ -240,6 +240,9 @@ class JobConfig:
         "float8.force_recompute_fp8_weight_in_bwd": "float8 training is not built",
         "float8.recipe_name": "float8 training is not built",
         "model.converters": "model converters (float8) are not built",
+        "optimizer.use_distributed_muon": "every Muon matrix is orthogonalised once, by its owner rank (the reference's "
+                                          "default 'parallel' mode); the all-gather-and-recompute-everywhere variant is not built "
+                                          "for data parallelism (tensor-parallel weight slices ARE gathered that way)",
     }
 
     def _refuse_unsupported(self) -> None:

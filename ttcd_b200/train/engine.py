@@ -94,8 +94,6 @@ class TrainEngine:
         self.tp = getattr(self, "tp", None)
         self._tp_dp = False
         if self.tp is not None:
-            if self.cfg.enable_muon:
-                raise NotImplementedError("Muon needs whole matrices; it is not available with tensor parallelism")
             world, rank = dist.get_world_size(), dist.get_rank()
             process_group = False           # every rank optimises its own weight shards
             if self.tp.world != world:
@@ -107,6 +105,8 @@ class TrainEngine:
                         process_group = g
                 self._tp_dp = True
         extra = {}
+        if self.tp is not None and self.cfg.enable_muon:
+            extra["tensor_parallel"] = self.tp          # Muon gathers the weight slices into whole matrices
         if self.cfg.shard_weights:
             if self.tp is not None or getattr(self, "cp", None) is not None or self.cfg.replicate:
                 raise NotImplementedError("sharded weights are combined with plain sharded data parallelism only")

@@ -48,6 +48,7 @@ class MuonParam:
     master: torch.Tensor | None = None      # fp32, owner only
     momentum: torch.Tensor | None = None    # fp32, owner only
     grad32: torch.Tensor | None = None      # fp32 reduced gradient, owner only
+    tp_dim: int | None = None               # tensor parallelism: the dimension along which ``param`` is a 1/tp slice
 
 
 def assign_owners(params: list[MuonParam], world: int) -> None:
@@ -77,11 +78,17 @@ def muon_update(mp: MuonParam, lr: float, weight_decay: float, momentum: float, 
 
 
 def muon_update_many(params: list[MuonParam], lr: float, weight_decay: float, momentum: float,
-                     coef: torch.Tensor | None, nesterov: bool = True, skip: torch.Tensor | None = None) -> None:
+                     coef: torch.Tensor | None, nesterov: bool = True, skip: torch.Tensor | None = None, tp=None) -> None:
     """Owner-side update of several parameters.  Parameters of one shape are orthogonalised as ONE batched
     Newton-Schulz call (15 GEMM launches for the whole group instead of 15 per matrix: the matrices of a 1024-wide
     model are a handful of tiles each, so per-matrix launches are pure latency); the reference batches the same way
-    for its 3-D case (custom_components/muon_v2.py:68-110)."""
+    for its 3-D case (custom_components/muon_v2.py:68-110).
+
+    ``tp`` (an object with ``group``, ``rank``, ``world``): under tensor parallelism a weight is a slice of its matrix
+    along ``mp.tp_dim``.  Momentum is element-wise and stays on the slice; for the orthogonalisation the slices of
+    the group's ranks are gathered into the whole matrix (every rank of the group then runs the same Newton-Schulz
+    and keeps its slice of the result), and the update's scale uses the whole matrix's dimensions.  All ranks of a
+    tensor-parallel group hold the same parameters in the same order, so they issue the same gathers."""
     if not params:
         return
     pre = []                          # (param, momentum after this step, Nesterov-combined gradient)
@@ -90,21 +97,45 @@ def muon_update_many(params: list[MuonParam], lr: float, weight_decay: float, mo
         new_mom = mp.momentum * momentum + g
         g = g.add(new_mom, alpha=momentum) if nesterov else new_mom
         pre.append((mp, new_mom, g))
+
+    def gathers(mp) -> bool:            # a slice of the matrix itself (not of a leading batch dimension)
+        return tp is not None and tp.world > 1 and mp.tp_dim is not None and mp.tp_dim >= mp.param.dim() - 2
+
+    def whole(x: torch.Tensor, dim: int) -> torch.Tensor:
+        parts = [torch.empty_like(x) for _ in range(tp.world)]
+        dist.all_gather(parts, x.contiguous(), group=tp.group)
+        return torch.cat(parts, dim=dim)
+
+    def mine(x: torch.Tensor, dim: int) -> torch.Tensor:
+        per = x.shape[dim] // tp.world
+        return x.narrow(dim, tp.rank * per, per)
+
     by_shape: dict[tuple, list[int]] = {}
     for i, (mp, _, _) in enumerate(pre):
-        by_shape.setdefault(tuple(mp.param.shape), []).append(i)
+        by_shape.setdefault((tuple(mp.param.shape), mp.tp_dim if gathers(mp) else None), []).append(i)
     updates: list[torch.Tensor | None] = [None] * len(pre)
-    for shape, idx in by_shape.items():
-        if len(shape) == 2 and min(shape) >= 64 and len(idx) > 1:
+    for (shape, dim), idx in by_shape.items():
+        full_min = min(s_ * (tp.world if dim == k else 1) for k, s_ in enumerate(shape[-2:], start=len(shape) - 2)) \
+            if dim is not None else min(shape[-2:])
+        if len(shape) == 2 and full_min >= 64 and (len(idx) > 1 or dim is not None):
             stacked = torch.stack([pre[i][2].view(shape) for i in idx])            # [n, rows, cols]
-            u = ops.newton_schulz(stacked).float()
+            if dim is not None:
+                u = mine(ops.newton_schulz(whole(stacked, dim + 1)).float(), dim + 1)
+            else:
+                u = ops.newton_schulz(stacked).float()
             for j, i in enumerate(idx):
                 updates[i] = u[j].reshape(-1)
         else:
             for i in idx:
-                updates[i] = orthogonalize(pre[i][2].view(shape)).float().reshape(-1)
+                g = pre[i][2].view(shape)
+                if dim is not None:
+                    updates[i] = mine(orthogonalize(whole(g, dim)).float(), dim).reshape(-1)
+                else:
+                    updates[i] = orthogonalize(g).float().reshape(-1)
     for (mp, new_mom, _), u in zip(pre, updates):
         rows, cols = mp.param.shape[-2], mp.param.shape[-1]      # last two dims also for >2-D parameters (707-716)
+        if gathers(mp):
+            rows, cols = (rows * tp.world, cols) if mp.tp_dim == mp.param.dim() - 2 else (rows, cols * tp.world)
         adj_lr = lr * 0.2 * math.sqrt(max(rows, cols))
         new_master = (mp.master * (1.0 - lr * weight_decay)).add_(u, alpha=-adj_lr)
         if skip is not None:
