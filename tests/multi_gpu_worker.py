@@ -221,6 +221,9 @@ def main():
     if what in ("all", "cp"):
         from tests.multi_gpu_cp import check_context_parallel
         check_context_parallel()
+    if what in ("all", "layouts"):
+        from tests.multi_gpu_misc import check_all
+        check_all()
     torch.cuda.synchronize()
     assert _native.device_status() == 0
     dist.barrier()

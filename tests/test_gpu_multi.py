@@ -80,3 +80,11 @@ def test_gradient_accumulation_reduces_once_on_gpus():
 @pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
 def test_sharded_weights_gathered_inside_the_first_gemm():
     _launch("zero3", 2)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
+@pytest.mark.timeout(900)
+def test_replicated_pipeline_vocab_parallel_and_hybrid_layouts_on_gpus():
+    """Replicated data parallelism, vocabulary-parallel cross-entropy and a two-stage pipeline on 2 GPUs; with 4 or
+    more GPUs also hybrid sharding (2 replicas x 2 shards)."""
+    _launch("layouts", 4 if _ngpu() >= 4 else 2)
