@@ -5,13 +5,15 @@ write) between timed iterations, and is reported with the achieved fraction of t
 in MEASURED_PEAKS.json (cuBLAS bf16 burst throughput and copy bandwidth).  Library baselines
 (cuBLAS via torch.matmul, flash-attn 2) are timed the same way when importable.
 
-    python benchmarks/bench_kernels.py [--what gemm,attn,conv,attn_bwd,misc,ref] [--seq 65536] [--batch 1]
+    python benchmarks/bench_kernels.py [--what gemm,attn,conv,attn_bwd,misc,ref,ref_misc] [--seq 65536] [--batch 1]
 
 ``--what ref`` times the reference project's own kernels on this GPU next to this library's: its fused dual-window
 Triton kernel (profiling/fused_dual_attn.py:244-272), its LSE-combination variant on flash-attn 2
 (profiling/lse_dual_attn.py:16-39), two flash-attn calls, and its Triton chunked depthwise conv
 (profiling/fused_conv.py:51-61) against the cuDNN path.  They are imported, unmodified, from the reference checkout
 (``TTCD_REFERENCE_ROOT``, a ``reference`` directory beside this repository, or ``baseline/_ref``).
+``--what ref_misc`` does the same for its fla Triton add+RMSNorm, rotary, SwiGLU and fused linear-cross-entropy kernels
+(fla/modules/{layernorm,rotary,activations,fused_linear_cross_entropy}.py).
 """
 from __future__ import annotations
 
@@ -327,6 +329,79 @@ def bench_reference(seqs, batches, wt=8192, ws=4096):
             torch.cuda.empty_cache()
 
 
+def bench_reference_misc():
+    """The reference's element-wise and loss kernels (fla Triton: add+RMSNorm, rotary, SwiGLU, fused linear
+    cross-entropy), forward + backward on this GPU beside this library's, flagship shapes."""
+    root = _reference_profiling()
+    if root is None:
+        emit(bench="reference_misc", error="reference checkout not found")
+        return
+    from ttcd_b200 import ops
+    from ttcd_b200.ops import reference as ref
+    try:
+        from fla.modules import FusedLinearCrossEntropyLoss, RMSNorm, RotaryEmbedding
+        from fla.modules.activations import swiglu as fla_swiglu
+    except Exception as exc:
+        emit(bench="reference_misc", error=f"{type(exc).__name__}: {exc}"[:200])
+        return
+    torch.manual_seed(0)
+    T, d = 65536, 1024
+
+    def guarded(row, key, fn, **kw):
+        try:
+            row[key] = round(timeit(fn, **kw), 4)
+        except Exception as exc:
+            row[key.replace("_ms", "_error")] = f"{type(exc).__name__}: {exc}"[:160]
+
+    # --- add + RMSNorm (prenorm: returns the normalised rows and the new residual)
+    x = torch.randn(1, T, d, device="cuda").to(BF).requires_grad_()
+    res = torch.randn(1, T, d, device="cuda").to(BF).requires_grad_()
+    w = torch.ones(d, device="cuda", dtype=BF).requires_grad_()
+    g1, g2 = torch.randn(1, T, d, device="cuda").to(BF), torch.randn(1, T, d, device="cuda").to(BF)
+    norm = RMSNorm(d, eps=1e-6).to("cuda", BF)
+    row = dict(bench="reference_add_rmsnorm_fwd_bwd", shape=[T, d])
+    guarded(row, "ours_ms", lambda: torch.autograd.grad(ops.rmsnorm(x, w, 1e-6, residual=res, prenorm=True), [x, res, w], [g1, g2]))
+    guarded(row, "ref_triton_ms", lambda: torch.autograd.grad(norm(x, res, True), [x, res, norm.weight], [g1, g2]))
+    emit(**row)
+    # --- SwiGLU
+    a = torch.randn(T, 3072, device="cuda").to(BF).requires_grad_()
+    b = torch.randn(T, 3072, device="cuda").to(BF).requires_grad_()
+    g = torch.randn(T, 3072, device="cuda").to(BF)
+    row = dict(bench="reference_swiglu_fwd_bwd", shape=[T, 3072])
+    guarded(row, "ours_ms", lambda: torch.autograd.grad(ops.swiglu(a, b), [a, b], g))
+    guarded(row, "ref_triton_ms", lambda: torch.autograd.grad(fla_swiglu(a, b), [a, b], g))
+    emit(**row)
+    del a, b, g
+    # --- rotary on q [1, T, 16, 128] and k [1, T, 8, 128] (this library fuses the per-head q/k RMSNorm into the same pass)
+    q = torch.randn(1, T, 16, 128, device="cuda").to(BF).requires_grad_()
+    k = torch.randn(1, T, 8, 128, device="cuda").to(BF).requires_grad_()
+    gq, gk = torch.randn_like(q), torch.randn_like(k)
+    cos, sin = ref.rope_tables(128, 1e6, T, device="cuda", dtype=BF)
+    qw = torch.ones(128, device="cuda", dtype=BF).requires_grad_()
+    kw = torch.ones(128, device="cuda", dtype=BF).requires_grad_()
+    rot = RotaryEmbedding(128, base=1e6).to("cuda")
+    qn, kn = RMSNorm(128, eps=1e-6).to("cuda", BF), RMSNorm(128, eps=1e-6).to("cuda", BF)
+    row = dict(bench="reference_qknorm_rope_fwd_bwd", shape=[T, 16, 8, 128])
+    guarded(row, "ours_fused_norm_rope_ms", lambda: torch.autograd.grad(ops.qkv_norm_rope(q, k, qw, kw, 1e-6, cos, sin), [q, k], [gq, gk]))
+    guarded(row, "ref_triton_rope_only_ms", lambda: torch.autograd.grad(rot(q, k, seqlen_offset=0, max_seqlen=T), [q, k], [gq, gk]))
+    guarded(row, "ref_triton_norm_then_rope_ms",
+            lambda: torch.autograd.grad(rot(qn(q), kn(k), seqlen_offset=0, max_seqlen=T), [q, k], [gq, gk]))
+    emit(**row)
+    del q, k, gq, gk
+    torch.cuda.empty_cache()
+    # --- fused linear cross-entropy, 65536 x 1024 -> 151936
+    vocab = 151936
+    hid = (torch.randn(T, d, device="cuda") * 0.5).to(BF).requires_grad_()
+    wl = (torch.randn(vocab, d, device="cuda") * 0.02).to(BF).requires_grad_()
+    labels = torch.randint(0, vocab, (T,), device="cuda")
+    crit = FusedLinearCrossEntropyLoss(num_chunks=8)
+    row = dict(bench="reference_linear_cross_entropy_fwd_bwd", tokens=T, hidden=d, vocab=vocab)
+    guarded(row, "ours_ms", lambda: torch.autograd.grad(ops.linear_cross_entropy(hid, labels, wl), [hid, wl]), iters=3)
+    guarded(row, "ref_triton_ms", lambda: torch.autograd.grad(crit(hid.unsqueeze(0), labels.unsqueeze(0), wl, None), [hid, wl]),
+            iters=3, warmup=1)
+    emit(**row)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--what", default="gemm,attn,conv")
@@ -347,6 +422,8 @@ def main():
         bench_conv()
     if "misc" in what:
         bench_misc()
+    if "ref_misc" in what:
+        bench_reference_misc()
     if "ref" in what:
         bench_reference(seqs, batches)
     st = _native.device_status()

@@ -28,6 +28,8 @@ struct GemmParams {
   const bf16* row_scale;     // optional [batch*M]
   int a_bcast, b_bcast;      // operand shared by every batch entry (its tensor map has batch 1)
   int m_fastest;             // raster order inside a batch entry: consecutive tiles walk M (the B panel is the big one)
+  float2* lse_part;          // optional [batch*M][tiles_n]: per row and column tile (max, sum of exp(x - max)) of the
+                             // bf16-rounded outputs, for a log-sum-exp over the row without another pass (bf16 out only)
 };
 
 template <int BN, int STAGES>
@@ -193,6 +195,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         // (full 128-byte lines, clipped at the matrix edges by the tensor map); two staging buffers per warp.
         uint8_t* stage = smem + S::EPI_OFFSET + quarter * 8192;
         int chunk = 0;
+        const bool want_lse = p.lse_part != nullptr;
+        float run_m = -INFINITY, run_s = 0.f;
 #pragma unroll 1
         for (int c = 0; c < BN; c += 64, ++chunk) {
           uint32_t v0[32], v1[32];
@@ -228,6 +232,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
             o.z = pack_bf16(f[4], f[5]);
             o.w = pack_bf16(f[6], f[7]);
             *reinterpret_cast<uint4*>(buf + sw128_offset(lane, j >> 3)) = o;
+            if (want_lse) {
+              // running (max, sum) over this thread's row, on the values as the consumer will read them (bf16)
+              const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+              float r[8];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 t = unpack_bf16(ow[e]);
+                r[2 * e] = col + j + 2 * e < p.N ? t.x : -INFINITY;
+                r[2 * e + 1] = col + j + 2 * e + 1 < p.N ? t.y : -INFINITY;
+              }
+              float mx = r[0];
+#pragma unroll
+              for (int e = 1; e < 8; ++e) mx = fmaxf(mx, r[e]);
+              if (mx > run_m) {
+                run_s *= __expf(run_m - mx);
+                run_m = mx;
+              }
+              if (run_m != -INFINITY) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) run_s += __expf(r[e] - run_m);
+              }
+            }
           }
           fence_proxy_async_smem();
           __syncwarp();
@@ -236,6 +262,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
             tma_store_commit();
           }
         }
+        if (want_lse && row_ok) p.lse_part[(b * p.M + row) * p.tiles_n + n0 / BN] = make_float2(run_m, run_s);
       } else {
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
@@ -330,13 +357,14 @@ TTCD_DEFINE_STATUS_READER(gemm)
 // a: [batch][M][K] (a_mn = 0, row stride lda) or [batch][K][M] (a_mn = 1).  b likewise with N.
 // c / c_in: [batch][M][N], row stride ldc, bf16 or fp32 (out_fp32).  Strides in elements.
 // c_in may alias c.  row_scale: optional bf16 [batch*M].
-TTCD_EXPORT int ttcd_gemm_bf16(const void* a, const void* b, void* c, const void* c_in, const void* row_scale,
-                               long long M, long long N, long long K, long long batch, long long lda,
-                               long long ldb, long long ldc, long long stride_a, long long stride_b,
-                               long long stride_c, int a_mn, int b_mn, int out_fp32, float alpha, float beta,
-                               void* stream_ptr) {
+static int gemm_bf16_impl(const void* a, const void* b, void* c, const void* c_in, const void* row_scale,
+                         long long M, long long N, long long K, long long batch, long long lda,
+                         long long ldb, long long ldc, long long stride_a, long long stride_b,
+                         long long stride_c, int a_mn, int b_mn, int out_fp32, float alpha, float beta,
+                         float* lse_part, void* stream_ptr) {
   using namespace ttcd;
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return TTCD_ERR_ARG;
+  if (lse_part != nullptr && (out_fp32 || (reinterpret_cast<uintptr_t>(lse_part) & 7u))) return TTCD_ERR_ARG;
   const int elem_c = out_fp32 ? 4 : 2;
   if ((reinterpret_cast<uintptr_t>(c) & 15u) || (ldc * elem_c) % 16 != 0 || (stride_c * elem_c) % 16 != 0)
     return TTCD_ERR_ARG;
@@ -367,6 +395,7 @@ TTCD_EXPORT int ttcd_gemm_bf16(const void* a, const void* b, void* c, const void
   // the operand panel that is re-streamed once per step of the outer tile loop should be the smaller one (it then
   // lives in the 126 MB L2): walk M fastest when the B panel (N x K) is the larger
   p.m_fastest = N > M ? 1 : 0;
+  p.lse_part = reinterpret_cast<float2*>(lse_part);
   CUtensorMap tc = ta;      // fp32 outputs are written with plain stores and never touch this map
   if (!out_fp32) {
     rc = make_tmap_bf16_3d(&tc, c, N, M, batch, ldc, stride_c, 64, 32);
@@ -374,4 +403,25 @@ TTCD_EXPORT int ttcd_gemm_bf16(const void* a, const void* b, void* c, const void
   }
   if (BN == 256) return dispatch_major<256, 4>(ta, tb, tc, c, c_in, p, a_mn, b_mn, out_fp32, stream);
   return dispatch_major<128, 6>(ta, tb, tc, c, c_in, p, a_mn, b_mn, out_fp32, stream);
+}
+
+TTCD_EXPORT int ttcd_gemm_bf16(const void* a, const void* b, void* c, const void* c_in, const void* row_scale,
+                               long long M, long long N, long long K, long long batch, long long lda,
+                               long long ldb, long long ldc, long long stride_a, long long stride_b,
+                               long long stride_c, int a_mn, int b_mn, int out_fp32, float alpha, float beta,
+                               void* stream_ptr) {
+  return gemm_bf16_impl(a, b, c, c_in, row_scale, M, N, K, batch, lda, ldb, ldc, stride_a, stride_b, stride_c, a_mn, b_mn,
+                        out_fp32, alpha, beta, nullptr, stream_ptr);
+}
+
+// Same GEMM (bf16 output) that also leaves, per output row and column tile, the pair (max, sum of exp(x - max)) of the
+// row's values in that tile, taken on the bf16-rounded outputs: lse_part is fp32 [batch*M][tiles_n][2] with
+// tiles_n = ceil(N / 256) (N >= 256) or ceil(N / 128).  A consumer merges the tiles_n pairs of a row into its
+// log-sum-exp without reading the row (the cross-entropy row kernel does).
+TTCD_EXPORT int ttcd_gemm_bf16_lse(const void* a, const void* b, void* c, long long M, long long N, long long K,
+                                   long long lda, long long ldb, long long ldc, int a_mn, int b_mn, float alpha,
+                                   float* lse_part, void* stream_ptr) {
+  if (lse_part == nullptr) return TTCD_ERR_ARG;
+  return gemm_bf16_impl(a, b, c, nullptr, nullptr, M, N, K, 1, lda, ldb, ldc, 0, 0, M * ldc, a_mn, b_mn, 0, alpha, 0.f,
+                        lse_part, stream_ptr);
 }

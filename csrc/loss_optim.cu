@@ -36,7 +36,7 @@ __global__ void __launch_bounds__(1024) ce_rows_kernel(bf16* __restrict__ logits
                                                        float* __restrict__ loss_row, float* __restrict__ lse_row,
                                                        const float* __restrict__ grad_scale, int V, int64_t ld,
                                                        int ignore_index, int write_grad, float eps, float zeta,
-                                                       float l2_factor) {
+                                                       float l2_factor, const float2* __restrict__ lse_part, int n_parts) {
   __shared__ float scratch[33];
   const int64_t row = blockIdx.x;
   bf16* lr = logits + row * ld;
@@ -44,7 +44,19 @@ __global__ void __launch_bounds__(1024) ce_rows_kernel(bf16* __restrict__ logits
   const int nvec = V / 8;
   float m = -INFINITY, s = 0.f, sumx = 0.f;
   int arg = 0;
-  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+  // the producing GEMM left (max, sum) per column tile of this row: merge them instead of reading the row
+  const bool have_parts = lse_part != nullptr;
+  if (have_parts) {
+    for (int i = threadIdx.x; i < n_parts; i += blockDim.x) {
+      const float2 t = lse_part[row * n_parts + i];
+      if (t.x > m) {
+        s *= __expf(m - t.x);
+        m = t.x;
+      }
+      if (t.x != -INFINITY) s += t.y * __expf(t.x - m);
+    }
+  }
+  for (int i = threadIdx.x; i < (have_parts ? 0 : nvec); i += blockDim.x) {
     const uint4 raw = *reinterpret_cast<const uint4*>(lr + i * 8);
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
     float f[8];
@@ -70,7 +82,7 @@ __global__ void __launch_bounds__(1024) ce_rows_kernel(bf16* __restrict__ logits
       sumx += f[k];
     }
   }
-  for (int i = nvec * 8 + threadIdx.x; i < V; i += blockDim.x) {
+  for (int i = nvec * 8 + threadIdx.x; i < (have_parts ? 0 : V); i += blockDim.x) {
     const float f = __bfloat162float(lr[i]);
     if (f > m) {
       s *= __expf(m - f);
@@ -220,15 +232,19 @@ static unsigned flat_grid(long long n) {
 }
 
 // logits: [rows][ld] bf16 (modified in place when write_grad); labels: int64 [rows].
+// lse_part (may be null): fp32 [rows][n_parts][2] left by ttcd_gemm_bf16_lse for these logits; the first pass over the
+// row is then skipped (not with label smoothing or the l2-warp term, which need the row's mean / arg-max).
 TTCD_EXPORT int ttcd_ce_rows(void* logits, const long long* labels, float* loss_row, float* lse_row,
                              const float* grad_scale, long long rows, int V, long long ld, int ignore_index,
                              int write_grad, float label_smoothing, float lse_square_scale, float l2_factor,
-                             void* stream_ptr) {
+                             const float* lse_part, int n_parts, void* stream_ptr) {
   if (rows <= 0 || V <= 0 || ld % 8 != 0 || (write_grad && grad_scale == nullptr)) return TTCD_ERR_ARG;
   if (label_smoothing < 0.f || label_smoothing >= 1.f || V >= (1 << 24)) return TTCD_ERR_ARG;
+  if (lse_part != nullptr && (n_parts <= 0 || label_smoothing != 0.f || l2_factor != 0.f)) return TTCD_ERR_ARG;
   ce_rows_kernel<<<static_cast<unsigned>(rows), 1024, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
       static_cast<bf16*>(logits), reinterpret_cast<const int64_t*>(labels), loss_row, lse_row, grad_scale, V, ld,
-      ignore_index, write_grad, label_smoothing, lse_square_scale, l2_factor);
+      ignore_index, write_grad, label_smoothing, lse_square_scale, l2_factor, reinterpret_cast<const float2*>(lse_part),
+      n_parts);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -46,9 +46,10 @@ def check_tensor_parallel():
     tp.close()
 
 
-def check_tp_model():
+def check_tp_model(muon: bool = False):
     """IP-TTCD under tensor+sequence parallelism (fused kernels where the shapes allow) vs the same model on
-    one GPU: loss, gradient norm and weights after one optimizer step."""
+    one GPU: loss, gradient norm and weights after one optimizer step (AdamW, or with ``muon`` Muon on the hidden
+    matrices: the ranks gather their weight slices into whole matrices for the Newton-Schulz step)."""
     from ttcd_b200.models import IPTTCDv9Config
     from ttcd_b200.parallel import tensor as tpmod
     from ttcd_b200.train.engine import EngineConfig, TrainEngine
@@ -59,14 +60,16 @@ def check_tp_model():
                          ttt_layers=[1], ttt_update_every=4, qk_norm=True, tie_word_embeddings=False, fuse_cross_entropy=False,
                          fuse_linear_cross_entropy=True, ttt_teacher_conv_init="identity", ttt_normalize_student_features=False)
     ids = torch.randint(0, cfg.vocab_size, (1, 1024), generator=torch.Generator().manual_seed(5)).cuda()
-    ref = TrainEngine(cfg, EngineConfig(lr=1e-3, seed=7, activation_checkpoint="none"), device=dev, process_group=False)
+    ref = TrainEngine(cfg, EngineConfig(lr=1e-3, seed=7, activation_checkpoint="none", enable_muon=muon), device=dev,
+                      process_group=False)
     ref.sdp.zero_grad()
     ref_loss = float(ref.forward_backward(ids))
     ref_norm = float(ref.sdp.step(1e-3))
     ref_after = {n: p.detach().float().clone() for n, p in ref.model.named_parameters()}
     del ref
-    eng = TrainEngine(cfg, EngineConfig(lr=1e-3, seed=7, activation_checkpoint="none", tensor_parallel=world), device=dev)
-    assert eng.tp is not None and eng.tp.fused
+    eng = TrainEngine(cfg, EngineConfig(lr=1e-3, seed=7, activation_checkpoint="none", tensor_parallel=world,
+                                        enable_muon=muon), device=dev)
+    assert eng.tp is not None and eng.tp.fused and bool(eng.sdp.muon_params) == muon
     eng.sdp.zero_grad()
     loss = float(eng.forward_backward(ids))
     norm = float(eng.sdp.step(1e-3))

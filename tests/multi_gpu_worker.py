@@ -212,6 +212,7 @@ def main():
         from tests.multi_gpu_tp import check_tensor_parallel, check_tp_model
         check_tensor_parallel()
         check_tp_model()
+        check_tp_model(muon=True)
     if what in ("all", "zero3"):
         check_sharded_weights()
     if what in ("all", "late_rank"):

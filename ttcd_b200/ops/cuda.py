@@ -834,13 +834,28 @@ def lse_merge(o_a, lse_a, o_b, lse_b):
 # losses
 # =============================================================================================
 
-def _ce_rows(logits2, labels, inv_total, ignore_index, write_grad, smoothing=0.0, z_scale=0.0, l2_factor=0.0):
+def _ce_rows(logits2, labels, inv_total, ignore_index, write_grad, smoothing=0.0, z_scale=0.0, l2_factor=0.0, lse_part=None):
+    """``lse_part`` [rows, tiles, 2] (from ``_logits_with_lse``): the kernel merges it instead of a first pass over the row."""
     rows, V = logits2.shape
     loss_rows = torch.empty(rows, dtype=torch.float32, device=logits2.device)
     nv.call("ttcd_ce_rows", nv.ptr(logits2), nv.ptr(labels), nv.ptr(loss_rows), nv.ptr(None), nv.ptr(inv_total),
             nv.i64(rows), nv.i32(V), nv.i64(logits2.stride(0)), nv.i32(ignore_index), nv.i32(1 if write_grad else 0),
-            nv.f32(smoothing), nv.f32(z_scale), nv.f32(l2_factor), nv.stream_ptr())
+            nv.f32(smoothing), nv.f32(z_scale), nv.f32(l2_factor), nv.ptr(lse_part),
+            nv.i32(0 if lse_part is None else lse_part.shape[1]), nv.stream_ptr())
     return loss_rows
+
+
+def _logits_with_lse(hidden2, w, out):
+    """out[rows, V] = hidden2 @ w^T (bf16) and, from the GEMM's epilogue, the (max, sum of exp) of every row per column
+    tile: fp32 [rows, tiles, 2].  hidden2 [rows, K] and w [V, K] row-major."""
+    rows, K = hidden2.shape
+    V = w.shape[0]
+    tiles = -(-V // (256 if V >= 256 else 128))
+    parts = torch.empty(rows, tiles, 2, dtype=torch.float32, device=hidden2.device)
+    nv.call("ttcd_gemm_bf16_lse", nv.ptr(hidden2), nv.ptr(w), nv.ptr(out), nv.i64(rows), nv.i64(V), nv.i64(K),
+            nv.i64(hidden2.stride(0)), nv.i64(w.stride(0)), nv.i64(out.stride(0)), nv.i32(0), nv.i32(0), nv.f32(1.0),
+            nv.ptr(parts), nv.stream_ptr())
+    return parts
 
 
 class _CrossEntropy(torch.autograd.Function):
@@ -869,6 +884,26 @@ def cross_entropy(logits, labels, ignore_index=-100, label_smoothing=0.0, z_loss
     return _CrossEntropy.apply(logits, labels, int(ignore_index), float(label_smoothing), float(z_loss))
 
 
+def _lce_chunk_rows(n_rows: int, hidden: int, num_chunks: int, sms: int = 148) -> int:
+    """Rows per chunk of the chunked lm_head pass: about ``n_rows / num_chunks``, moved (by up to a quarter either way)
+    to the multiple of 128 whose dx GEMM ([rows, vocab] x [vocab, hidden]: rows/128 x hidden/256 output tiles, the only
+    one of the three GEMMs with few tiles) fills whole waves of the persistent kernel's CTAs; 8192 rows x 1024 would be
+    256 tiles = 1.73 waves, 9472 rows are 296 tiles = 2 waves."""
+    target = max(1, -(-n_rows // max(1, num_chunks)) // 128)
+    total = -(-n_rows // 128)
+    if target >= total:
+        return total * 128
+    n_tiles = max(1, -(-hidden // 256))
+    best, best_key = target, None
+    for m in range(max(1, target - target // 4), min(total, target + target // 4) + 1):
+        tiles = m * n_tiles
+        eff = tiles / (-(-tiles // sms) * sms)
+        key = (round(eff, 2), -abs(m - target))
+        if best_key is None or key > best_key:
+            best, best_key = m, key
+    return best * 128
+
+
 class _LinearCrossEntropy(torch.autograd.Function):
     """CE(hidden @ W^T) in token chunks: logits GEMM -> row kernel (LSE + in-place dlogits) ->
     dx and dW GEMMs, so the [tokens, vocab] logits never exist at once and there is no host sync."""
@@ -883,12 +918,14 @@ class _LinearCrossEntropy(torch.autograd.Function):
         total = labels.ne(ignore_index).sum().clamp_min(1).to(torch.float32)
         inv_total = (1.0 / total).reshape(1)
         need_grad = hidden.requires_grad or weight.requires_grad
-        chunk = max(128, -(-N // max(1, num_chunks)))
-        chunk = ((chunk + 127) // 128) * 128
+        chunk = _lce_chunk_rows(N, Hd, num_chunks)
         dx = torch.empty_like(hidden) if need_grad else None
         dw = torch.zeros(V, Hd, dtype=torch.float32, device=hidden.device) if need_grad else None
         loss = torch.zeros((), dtype=torch.float32, device=hidden.device)
         logits = torch.empty(min(chunk + 127, N), V, dtype=_BF16, device=hidden.device)
+        # the row statistics come out of the logits GEMM's epilogue (the l2-warp term needs the arg-max: row pass)
+        fuse_lse = (l2_factor == 0.0 and nv.has("ttcd_gemm_bf16_lse") and w.is_contiguous() and Hd % 8 == 0
+                    and hidden.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
         bounds, s = [], 0
         while s < N:                       # a tail shorter than one 128-row tile joins the chunk before it
             e = N if N - (s + chunk) < 128 else s + chunk
@@ -896,8 +933,12 @@ class _LinearCrossEntropy(torch.autograd.Function):
             s = e
         for s, e in bounds:
             lg = logits[: e - s]
-            gemm(hidden[s:e], w.transpose(0, 1), out=lg.view(1, e - s, V))
-            loss_rows = _ce_rows(lg, labels[s:e], inv_total, ignore_index, need_grad, 0.0, 0.0, l2_factor)
+            parts = None
+            if fuse_lse:
+                parts = _logits_with_lse(hidden[s:e], w, lg)
+            else:
+                gemm(hidden[s:e], w.transpose(0, 1), out=lg.view(1, e - s, V))
+            loss_rows = _ce_rows(lg, labels[s:e], inv_total, ignore_index, need_grad, 0.0, 0.0, l2_factor, parts)
             loss = loss + loss_rows.sum()
             if need_grad:
                 gemm(lg, w, out=dx[s:e].view(1, e - s, Hd))
