@@ -213,8 +213,12 @@ def run_ours(args):
                 ac_full = {"error": f"{type(exc).__name__}: {exc}"[:200]}
             engine.set_activation_checkpointing(ac_mode)
         if world > 1:
+            # the children build their own engines on the same GPUs: give this one's memory back first
             del dev, host, e2e_host
-            engine.sdp.zero_grad()
+            engine.close()
+            del engine
+            import gc
+            gc.collect()
             torch.cuda.empty_cache()
             extra["cp"] = run_children(args, rank, world, "cp", 23)
             extra["zero3"] = run_children(args, rank, world, "zero3", 41)

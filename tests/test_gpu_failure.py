@@ -105,3 +105,22 @@ def test_expired_peer_wait_makes_the_optimizer_kernel_leave_the_weights_alone():
     nv.call("ttcd_adamw_push", *args(torch.zeros(1, dtype=torch.int32, device="cuda")))
     torch.cuda.synchronize()
     assert not torch.equal(p32, before[0]) and torch.equal(flat[0], flat[1]) and not torch.equal(flat[0], before[3])
+
+
+def test_check_every_call_mode_names_the_launch_whose_wait_ran_out(monkeypatch):
+    """The debugging mode (TTCD_CHECK_EVERY_CALL=1) synchronises after each launch and reads the status words, so an
+    expired wait is reported by the call that contained it; healthy launches pass through it unchanged."""
+    from ttcd_b200 import _native as nv
+    from ttcd_b200.ops import cuda
+    nv.load(required=True)
+    nv.device_status()
+    monkeypatch.setattr(nv, "_CHECK_EVERY_CALL", True)
+    x = torch.randn(256, 256, device="cuda").bfloat16()
+    torch.testing.assert_close(cuda.gemm(x, x).float(), x.float() @ x.float(), rtol=2e-2, atol=0.5)     # healthy
+    mine = torch.zeros(256, dtype=torch.int32, device="cuda")
+    ghost = torch.zeros(256, dtype=torch.int32, device="cuda")
+    with pytest.raises(nv.NativeError, match="ttcd_comm_barrier.*status 501"):
+        nv.call("ttcd_comm_barrier", _i64s([mine.data_ptr(), ghost.data_ptr()]), nv.i32(0), nv.i32(2), nv.i32(0), nv.i32(1),
+                nv.i64(100_000_000), nv.ptr(None), nv.stream_ptr())
+    assert nv.device_status() == 0                                         # the mode consumed the code
+    torch.testing.assert_close(cuda.gemm(x, x).float(), x.float() @ x.float(), rtol=2e-2, atol=0.5)     # still usable

@@ -117,6 +117,28 @@ def call(symbol: str, *args) -> None:
             lib.ttcd_last_tmap_error(buf, ctypes.c_int(320))
             detail += f" ({buf.value.decode(errors='replace')})"
         raise NativeError(f"{symbol} failed: {detail}")
+    if _CHECK_EVERY_CALL and _MULTI_KERNEL.get(symbol, 1) > 0:
+        _check_after(symbol)
+
+
+# TTCD_CHECK_EVERY_CALL=1: debugging aid for locating a misbehaving launch.  After every kernel call the device is
+# synchronised, so an asynchronous CUDA error surfaces at the call that caused it instead of at some later
+# synchronisation, and the status words of the bounded waits are read, so an expired wait is attributed to its kernel.
+# Serialises everything (no overlap, no graph capture): never a setting for timing runs.
+_CHECK_EVERY_CALL = os.environ.get("TTCD_CHECK_EVERY_CALL", "0") == "1"
+
+
+def _check_after(symbol: str) -> None:
+    import torch
+    if torch.cuda.is_current_stream_capturing():
+        return
+    try:
+        torch.cuda.synchronize()
+    except RuntimeError as exc:
+        raise NativeError(f"{symbol}: the device reported an error after this launch: {exc}") from exc
+    code = device_status(reset=True)
+    if code:
+        raise NativeError(f"{symbol}: a bounded device wait ran out in this launch (status {code})")
 
 
 def i32(v) -> ctypes.c_int:

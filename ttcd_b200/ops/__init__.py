@@ -8,6 +8,8 @@ raises instead of silently falling back.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.nn.functional as F
 
@@ -237,6 +239,11 @@ def newton_schulz(g, coeffs=reference.NS_COEFFS):
     return reference.newton_schulz(g, coeffs)
 
 
+# chunk length of the (gated) delta rule: the chunk-to-chunk loop is sequential (T / chunk small launches per layer), the
+# work inside a chunk is one batched triangular solve and a few batched GEMMs that grow with the chunk
+_DELTA_CHUNK = int(os.environ.get("TTCD_DELTA_CHUNK", "64"))
+
+
 def gated_delta_rule(q, k, v, g, beta, *, scale=None, l2norm: bool = True, cu_seqlens=None, initial_state=None,
                      output_final_state: bool = False, recurrent: bool = False):
     """(Gated) delta rule over q, k [B,T,H,Dk], v [B,T,H,Dv], log decay g and write strength beta [B,T,H]; ``g`` None is
@@ -244,5 +251,5 @@ def gated_delta_rule(q, k, v, g, beta, *, scale=None, l2norm: bool = True, cu_se
     form whose matrix products run as batched GEMMs.  Returns (o, final state or None)."""
     if recurrent and cu_seqlens is None:
         return reference.gated_delta_rule_recurrent(q, k, v, g, beta, scale, l2norm, initial_state, output_final_state)
-    return reference.gated_delta_rule_chunked(q, k, v, g, beta, scale, l2norm, 64, cu_seqlens, initial_state,
+    return reference.gated_delta_rule_chunked(q, k, v, g, beta, scale, l2norm, _DELTA_CHUNK, cu_seqlens, initial_state,
                                               output_final_state)

@@ -736,6 +736,32 @@ class ShardedDataParallel:
                 src = dist.get_global_rank(self.pg, mp.owner) if self.pg is not None else mp.owner
                 dist.broadcast(dst, src=src, group=self.pg)
 
+    def close(self) -> None:
+        """Give the device memory back: the symmetric buffers (peer mappings first, then this rank's allocation, after
+        every rank has stopped using them), the optimizer state and the pooled weight buffers.  The model's parameters
+        and gradients are views of those buffers, so the model is unusable afterwards."""
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=self.pg)
+        for p in self.model.parameters():
+            p.grad = None
+            p.data = torch.empty(0, dtype=p.dtype, device=p.device)
+        for buf in (self.sym_params, self.sym_grads, getattr(self, "sym_shards", None),
+                    None if self.barrier is None else self.barrier.buf):
+            if buf is not None:
+                buf.close()
+        self.sym_params = self.sym_grads = self.sym_shards = self.barrier = None
+        self._pool = []
+        for g in self.groups:
+            g.master = g.exp_avg = g.exp_avg_sq = g.flat_param = g.flat_grad = g.shard_store = None
+            g.grad_shard = g.grad_full32 = None
+        for mp in self.muon_params:
+            mp.master = mp.momentum = mp.grad32 = None
+        self.groups, self.muon_params = [], []
+        if self.device.type == "cuda":
+            torch.cuda.empty_cache()
+
     def check_health(self) -> None:
         """Raise if a bounded device-side wait ran out since the last check (a peer was later than the wait budget,
         or a kernel's own pipeline stalled).  Synchronises the device: call it where the host already waits (a

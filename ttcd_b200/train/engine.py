@@ -280,6 +280,15 @@ class TrainEngine:
         self.last_loss = loss
         return float(loss.item()) if return_loss_on_host else loss
 
+    def close(self) -> None:
+        """Release the device memory of the runtime (flat buffers, optimizer state, peer mappings); the engine and its
+        model cannot be used afterwards."""
+        for part in (getattr(self, "tp", None), getattr(self, "cp", None)):
+            if part is not None and hasattr(part, "close"):
+                part.close()
+        if hasattr(self.sdp, "close"):
+            self.sdp.close()
+
     @property
     def grad_norm(self):
         return self.sdp.last_grad_norm
