@@ -227,3 +227,26 @@ def test_graph_decoding_follows_eager_decoding():
         d = model.generate(ids[:, 100:100 + prompt], max_new_tokens=24, use_graph=False)
         assert torch.equal(c[:, :prompt + 2], d[:, :prompt + 2])
         assert _native.launch_count > launches
+
+
+@pytest.mark.parametrize("gated", [False, True])
+def test_delta_rule_on_the_gpu_matches_the_token_by_token_statement(gated):
+    """The chunked rule on CUDA (TF32 products, prefix scan over chunks, 256-token chunks) against the fp32 recurrence
+    evaluated on the CPU: outputs, final state and gradients."""
+    from ttcd_b200 import ops
+    from ttcd_b200.ops import reference as ref
+    gen = torch.Generator().manual_seed(3)
+    B, T, H, D, Dv = 2, 1300, 3, 64, 128
+    q, k = torch.randn(B, T, H, D, generator=gen), torch.randn(B, T, H, D, generator=gen)
+    v = torch.randn(B, T, H, Dv, generator=gen)
+    beta = torch.rand(B, T, H, generator=gen)
+    g = -torch.rand(B, T, H, generator=gen) * 0.2 if gated else None
+    cpu = [t.clone().requires_grad_() for t in (q, k, v, beta)]
+    o_ref, s_ref = ref.gated_delta_rule_recurrent(cpu[0], cpu[1], cpu[2], g, cpu[3], output_final_state=True)
+    (o_ref.square().sum() + s_ref.sum()).backward()
+    dev = [t.clone().to(DEV).requires_grad_() for t in (q, k, v, beta)]
+    o, s = ops.gated_delta_rule(dev[0], dev[1], dev[2], None if g is None else g.to(DEV), dev[3], output_final_state=True)
+    (o.square().sum() + s.sum()).backward()
+    assert _cos(o.cpu(), o_ref) > 0.9999 and _cos(s.cpu(), s_ref) > 0.9999
+    for a, b, name in zip(dev, cpu, ("q", "k", "v", "beta")):
+        assert _cos(a.grad.cpu(), b.grad) > 0.999, (name, _cos(a.grad.cpu(), b.grad))

@@ -239,17 +239,26 @@ def newton_schulz(g, coeffs=reference.NS_COEFFS):
     return reference.newton_schulz(g, coeffs)
 
 
-# chunk length of the (gated) delta rule: the chunk-to-chunk loop is sequential (T / chunk small launches per layer), the
-# work inside a chunk is one batched triangular solve and a few batched GEMMs that grow with the chunk
-_DELTA_CHUNK = int(os.environ.get("TTCD_DELTA_CHUNK", "64"))
+# chunk length of the (gated) delta rule (0: 256 for sequences of 1024 tokens and more, else 64).  The work inside a chunk
+# is one batched triangular solve and a few batched GEMMs; the chain over chunks is a prefix scan of D x D maps, whose
+# intermediates shrink with the number of chunks.
+_DELTA_CHUNK = int(os.environ.get("TTCD_DELTA_CHUNK", "0"))
 
 
 def gated_delta_rule(q, k, v, g, beta, *, scale=None, l2norm: bool = True, cu_seqlens=None, initial_state=None,
                      output_final_state: bool = False, recurrent: bool = False):
     """(Gated) delta rule over q, k [B,T,H,Dk], v [B,T,H,Dv], log decay g and write strength beta [B,T,H]; ``g`` None is
     the plain delta rule.  ``recurrent`` takes the token-by-token form (short decode steps), otherwise the chunked
-    form whose matrix products run as batched GEMMs.  Returns (o, final state or None)."""
+    form whose matrix products run as batched GEMMs.  Returns (o, final state or None).
+
+    When gradients are needed the chunked form runs under activation recomputation: autograd keeps q, k, v, g, beta and
+    rebuilds the fp32 intermediates (per-chunk triangular factors, the scan's D x D maps) in backward; kept, they are
+    several GB per layer at 64K tokens per step."""
     if recurrent and cu_seqlens is None:
         return reference.gated_delta_rule_recurrent(q, k, v, g, beta, scale, l2norm, initial_state, output_final_state)
-    return reference.gated_delta_rule_chunked(q, k, v, g, beta, scale, l2norm, _DELTA_CHUNK, cu_seqlens, initial_state,
-                                              output_final_state)
+    chunk = _DELTA_CHUNK or (256 if q.shape[1] >= 1024 else 64)
+    args = (q, k, v, g, beta, scale, l2norm, chunk, cu_seqlens, initial_state, output_final_state)
+    if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, g, beta)):
+        from torch.utils.checkpoint import checkpoint
+        return checkpoint(reference.gated_delta_rule_chunked, *args, use_reentrant=False)
+    return reference.gated_delta_rule_chunked(*args)

@@ -548,13 +548,51 @@ def gated_delta_rule_recurrent(q, k, v, g, beta, scale=None, l2norm: bool = True
     return torch.stack(out, dim=1).to(q.dtype), (S if output_final_state else None)
 
 
+class _full_fp32:
+    """Inside the block fp32 products stay fp32 (the triangular solve of the chunk factors)."""
+
+    def __enter__(self):
+        self.prev = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = False
+        return self
+
+    def __exit__(self, *exc):
+        torch.backends.cuda.matmul.allow_tf32 = self.prev
+
+
+class _tf32_matmuls:
+    """On CUDA, let fp32 matrix products use the tensor cores' TF32 mode inside the block (10-bit mantissa operands,
+    fp32 accumulation: finer than the bf16 operands the reference's Triton kernels multiply); restores the setting."""
+
+    def __init__(self, enabled: bool):
+        self.enabled = enabled
+
+    def __enter__(self):
+        if self.enabled:
+            self.prev = torch.backends.cuda.matmul.allow_tf32
+            torch.backends.cuda.matmul.allow_tf32 = True
+        return self
+
+    def __exit__(self, *exc):
+        if self.enabled:
+            torch.backends.cuda.matmul.allow_tf32 = self.prev
+
+
 def gated_delta_rule_chunked(q, k, v, g, beta, scale=None, l2norm: bool = True, chunk: int = 64, cu_seqlens=None,
-                             initial_state=None, output_final_state: bool = False):
+                             initial_state=None, output_final_state: bool = False, scan: bool = True):
+    with _tf32_matmuls(q.is_cuda):
+        return _gated_delta_rule_chunked(q, k, v, g, beta, scale, l2norm, chunk, cu_seqlens, initial_state,
+                                         output_final_state, scan)
+
+
+def _gated_delta_rule_chunked(q, k, v, g, beta, scale=None, l2norm: bool = True, chunk: int = 64, cu_seqlens=None,
+                              initial_state=None, output_final_state: bool = False, scan: bool = True):
     """Chunk-parallel gated delta rule (the computation of fla/ops/gated_delta_rule/chunk.py and, with ``g`` None, of
     fla/ops/delta_rule/chunk.py).  With G the running sum of g inside a chunk and S_0 the state entering it, the
     updates u solve the unit-lower-triangular system (I + L) U = beta V - (beta e^G K) S_0 with
     L_ij = beta_i e^{G_i - G_j} (k_i . k_j) for j < i; every exponent is a difference G_i - G_j with i >= j, so
-    nothing overflows.  Differentiable through autograd; shapes as in ``gated_delta_rule_recurrent``.  With
+    nothing overflows.  The chunk-to-chunk chain is affine in the state and is composed by a prefix scan (``scan``; the
+    plain loop over chunks otherwise).  Differentiable through autograd; shapes as in ``gated_delta_rule_recurrent``.  With
     ``cu_seqlens`` (batch 1) each packed sequence starts from a zero state (``initial_state`` then has one entry per
     sequence)."""
     if cu_seqlens is not None:
@@ -563,7 +601,7 @@ def gated_delta_rule_chunked(q, k, v, g, beta, scale=None, l2norm: bool = True, 
         for i, (a, b) in enumerate(zip(bounds[:-1], bounds[1:])):
             init = None if initial_state is None else initial_state[i:i + 1]
             o, s = gated_delta_rule_chunked(q[:, a:b], k[:, a:b], v[:, a:b], None if g is None else g[:, a:b], beta[:, a:b],
-                                            scale, l2norm, chunk, None, init, output_final_state)
+                                            scale, l2norm, chunk, None, init, output_final_state, scan)
             outs.append(o)
             finals.append(s)
         return torch.cat(outs, dim=1), (torch.cat(finals, dim=0) if output_final_state else None)
@@ -589,17 +627,39 @@ def gated_delta_rule_chunked(q, k, v, g, beta, scale=None, l2norm: bool = True, 
     kb, vb = kc * bc, vc * bc
     eye = torch.eye(chunk, device=q.device)
     lower = torch.tril(kb @ kc.transpose(-1, -2) * decay, -1)
-    t_inv = torch.linalg.solve_triangular(eye + lower, eye.expand_as(lower), upper=False)
+    with _tf32_matmuls(False) if not q.is_cuda else _full_fp32():
+        t_inv = torch.linalg.solve_triangular(eye + lower, eye.expand_as(lower), upper=False)
     w, u = t_inv @ (kb * eg), t_inv @ vb
     qk = (qc @ kc.transpose(-1, -2)) * decay
     q_in, k_out = qc * eg, kc * to_end
-    S = qf.new_zeros(B, H, D, vf.shape[-1]) if initial_state is None else initial_state.float()
-    outs = []
-    for i in range(n):
-        u_i = u[:, :, i] - w[:, :, i] @ S
-        outs.append(q_in[:, :, i] @ S + qk[:, :, i] @ u_i)
-        S = S * eg[:, :, i, -1:, :] + k_out[:, :, i].transpose(-1, -2) @ u_i
-    o = torch.stack(outs, dim=2).permute(0, 2, 3, 1, 4).reshape(B, n * chunk, H, -1)[:, :T]
+    S0 = qf.new_zeros(B, H, D, vf.shape[-1]) if initial_state is None else initial_state.float()
+    if n > 4 and scan and D <= 128:        # (for wider heads the D x D x D products of the scan cost more than the loop)
+        # The state entering chunk i+1 is linear in the one entering chunk i:  S_{i+1} = M_i S_i + N_i  with
+        # M_i = e^{G_C} I - k_out_i^T w_i  (D x D) and N_i = k_out_i^T u_i.  The chain over the n chunks is a prefix
+        # composition of these affine maps, done in log2(n) rounds of batched products instead of n dependent steps.
+        kt = k_out.transpose(-1, -2)                                             # [B, H, n, D, C]
+        M = torch.diag_embed(eg[:, :, :, -1, :].expand(B, H, n, D)) - kt @ w     # [B, H, n, D, D]
+        N = kt @ u                                                               # [B, H, n, D, Dv]
+        d = 1
+        while d < n:                                                             # inclusive prefix: (M, N)_i := map_i o ... o map_0
+            M_lo, N_lo = M[:, :, :-d], N[:, :, :-d]
+            N = torch.cat([N[:, :, :d], M[:, :, d:] @ N_lo + N[:, :, d:]], dim=2)
+            M = torch.cat([M[:, :, :d], M[:, :, d:] @ M_lo], dim=2)
+            d *= 2
+        after = M @ S0.unsqueeze(2) + N                                          # state after chunk i
+        states = torch.cat([S0.unsqueeze(2), after[:, :, :-1]], dim=2)           # state entering chunk i
+        u_all = u - w @ states
+        o = q_in @ states + qk @ u_all
+        S = after[:, :, -1]
+    else:
+        S = S0
+        outs = []
+        for i in range(n):
+            u_i = u[:, :, i] - w[:, :, i] @ S
+            outs.append(q_in[:, :, i] @ S + qk[:, :, i] @ u_i)
+            S = S * eg[:, :, i, -1:, :] + k_out[:, :, i].transpose(-1, -2) @ u_i
+        o = torch.stack(outs, dim=2)
+    o = o.permute(0, 2, 3, 1, 4).reshape(B, n * chunk, H, -1)[:, :T]
     return o.to(dtype), (S if output_final_state else None)
 
 
