@@ -3,13 +3,15 @@ import torch
 import torch.distributed as dist
 
 
-def check_context_parallel():
+def check_context_parallel(window=512):
+    """``window`` 512: the K/V halo path.  None: a full-attention teacher, which takes the head-parallel path (one
+    all-to-all gives every rank all tokens of its share of the heads)."""
     from ttcd_b200.models import IPTTCDv9Config
     from ttcd_b200.parallel import context
     from ttcd_b200.train.engine import EngineConfig, TrainEngine
     rank, world = dist.get_rank(), dist.get_world_size()
     cfg = IPTTCDv9Config(hidden_size=256, num_hidden_layers=2, num_heads=4, num_kv_heads=2, head_dim=64, intermediate_size=768,
-                         vocab_size=4096, window_size=512, max_position_embeddings=8192, ttt_mode=True, ttt_chunk=256,
+                         vocab_size=4096, window_size=window, max_position_embeddings=8192, ttt_mode=True, ttt_chunk=256,
                          ttt_layers=[1], ttt_update_every=2, qk_norm=True, tie_word_embeddings=True, fuse_cross_entropy=False,
                          fuse_linear_cross_entropy=True, ttt_teacher_conv_init="identity", ttt_normalize_student_features=False)
     S = 1024 * world
@@ -47,4 +49,4 @@ def check_context_parallel():
     assert worst[0] < 6e-2, f"context-parallel gradient mismatch: {worst}"
     context.shutdown()
     if rank == 0:
-        print(f"context parallel ok: loss {float(loss):.4f} vs {ref_loss:.4f}, worst relative grad error {worst[0]:.3g} ({worst[1]})")
+        print(f"context parallel (window {window}) ok: loss {float(loss):.4f} vs {ref_loss:.4f}, worst relative grad error {worst[0]:.3g} ({worst[1]})")

@@ -222,6 +222,7 @@ def main():
     if what in ("all", "cp"):
         from tests.multi_gpu_cp import check_context_parallel
         check_context_parallel()
+        check_context_parallel(window=None)
     if what in ("all", "layouts"):
         from tests.multi_gpu_misc import check_all
         check_all()

@@ -23,12 +23,12 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, ids, ref_loss, ref_grads, q):
+def _worker(rank, world, port, ids, ref_loss, ref_grads, q, window=48):
     try:
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
         dist.init_process_group("gloo", rank=rank, world_size=world)
         from ttcd_b200.train.engine import EngineConfig, TrainEngine
-        cfg = IPTTCDv9Config(**KW)
+        cfg = IPTTCDv9Config(**dict(KW, window_size=window))
         eng = TrainEngine(cfg, EngineConfig(dtype=torch.float32, lr=0.0, seed=3, activation_checkpoint="none",
                                             context_parallel=world, max_norm=None), device="cpu")
         with torch.no_grad():
@@ -52,11 +52,14 @@ def _worker(rank, world, port, ids, ref_loss, ref_grads, q):
 
 
 @pytest.mark.timeout(300)
-def test_context_parallel_matches_single_process():
+@pytest.mark.parametrize("window", [48, None, 100])
+def test_context_parallel_matches_single_process(window):
+    """window 48: the K/V halo path.  None (full-attention teacher) and 100 (longer than the 64-token shard): the
+    head-parallel path, where one all-to-all gives each rank all tokens of half the heads."""
     torch.manual_seed(0)
     ids = torch.randint(0, 256, (2, 128))
     from ttcd_b200.train.engine import EngineConfig, TrainEngine
-    eng = TrainEngine(IPTTCDv9Config(**KW), EngineConfig(dtype=torch.float32, lr=0.0, seed=3, activation_checkpoint="none",
+    eng = TrainEngine(IPTTCDv9Config(**dict(KW, window_size=window)), EngineConfig(dtype=torch.float32, lr=0.0, seed=3, activation_checkpoint="none",
                                                          max_norm=None), device="cpu")
     with torch.no_grad():
         for n, p in eng.model.named_parameters():
@@ -68,7 +71,7 @@ def test_context_parallel_matches_single_process():
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, ids, ref_loss, ref_grads, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, ids, ref_loss, ref_grads, q, window)) for r in range(2)]
     for p in procs:
         p.start()
     results = [q.get(timeout=240) for _ in procs]

@@ -1,4 +1,5 @@
-"""Context parallelism for sliding-window models: contiguous sequence shards + a one-sided K/V halo.
+"""Context parallelism: contiguous sequence shards + a one-sided K/V halo for sliding-window layers, head-parallel
+(all-to-all) attention where a halo does not do (full-attention teachers, windows longer than a shard).
 
 Rank r of a context-parallel group holds tokens [r*S_l, (r+1)*S_l).  Because every layer is windowed,
 the only remote data attention needs is the tail of the PREVIOUS rank's K/V (the last ``w_T - 1`` keys,
@@ -50,8 +51,16 @@ class ContextParallel:
         self.barrier = PeerBarrier(group, slots=4) if (torch.cuda.is_available() and nv.available()) else None
         self.layers: dict[int, _LayerBuffers] = {}
         self._sum_bufs: dict = {}
+
+    @staticmethod
+    def by_heads(s_local: int, window: int | None, tiles: bool) -> bool:
+        """Whether attention runs head-parallel (all-to-all) instead of with a halo: a full-attention layer needs every
+        earlier rank's keys, and a window longer than the shard needs more than the previous rank's (``tiles``: the
+        kernels take the halo in whole 128-key blocks)."""
         if window is None:
-            raise NotImplementedError("context parallelism needs a sliding-window teacher (window_size set)")
+            return True
+        need = (window - 1 + 127) // 128 * 128 if tiles else window - 1
+        return need > s_local
 
     def halo_len(self, s_local: int) -> int:
         if self.rank == 0:
@@ -247,8 +256,69 @@ def _gathered_kv(k, v, cp):
     return _GatherPrefix.apply(k, cp), _GatherPrefix.apply(v, cp)
 
 
+def _all_to_all(out: torch.Tensor, inp: torch.Tensor, group) -> None:
+    """out[i] = the block that rank i addressed to this rank (inp[j] goes to rank j); blocks along dim 0."""
+    if dist.get_backend(group) == "gloo":            # no all-to-all there: gather everything, keep this rank's column
+        parts = [torch.empty_like(inp) for _ in range(dist.get_world_size(group))]
+        dist.all_gather(parts, inp, group=group)
+        me = dist.get_rank(group)
+        for i, part in enumerate(parts):
+            out[i].copy_(part[me])
+        return
+    dist.all_to_all_single(out, inp, group=group)
+
+
+class _SeqToHeads(torch.autograd.Function):
+    """[B, S_l, H, D] (this rank's tokens, all heads) -> [B, S_l * size, H / size, D] (all tokens, this rank's heads),
+    and back in backward.  ``inverse`` swaps the two directions."""
+
+    @staticmethod
+    def forward(ctx, x, cp, inverse: bool):
+        ctx.cp, ctx.inverse = cp, inverse
+        return _SeqToHeads._run(x, cp, inverse)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _SeqToHeads._run(g, ctx.cp, not ctx.inverse), None, None
+
+    @staticmethod
+    def _run(x, cp, inverse):
+        n = cp.size
+        if not inverse:
+            B, S, H, D = x.shape
+            h = H // n
+            inp = x.reshape(B, S, n, h, D).permute(2, 0, 1, 3, 4).contiguous()        # [to rank, B, S_l, h, D]
+            out = torch.empty_like(inp)
+            _all_to_all(out, inp, cp.group)                                          # [from rank, B, S_l, h, D]
+            return out.permute(1, 0, 2, 3, 4).reshape(B, n * S, h, D)
+        B, T, h, D = x.shape
+        S = T // n
+        inp = x.reshape(B, n, S, h, D).permute(1, 0, 2, 3, 4).contiguous()            # [to rank (its tokens), B, S_l, h, D]
+        out = torch.empty_like(inp)
+        _all_to_all(out, inp, cp.group)                                              # [from rank (its heads), B, S_l, h, D]
+        return out.permute(1, 2, 0, 3, 4).reshape(B, S, n * h, D)
+
+
+def _attention_by_heads(q, k, v, window_t, window_s, scale, dual, cp):
+    """Head-parallel attention: one all-to-all turns the token shards of all heads into all tokens of H / size heads,
+    the single-GPU kernels (any window, dual or not) run on those heads, a second all-to-all returns the outputs to
+    the token shards.  Used when a halo does not do: full-attention teachers, windows longer than a shard."""
+    from .. import ops
+    if q.shape[2] % cp.size or k.shape[2] % cp.size:
+        raise NotImplementedError(
+            f"head-parallel attention needs the head counts ({q.shape[2]} query, {k.shape[2]} key/value) to divide by the "
+            f"context-parallel degree {cp.size}")
+    qh, kh, vh = (_SeqToHeads.apply(t, cp, False) for t in (q, k, v))
+    if dual:
+        o_t, o_s = ops.dual_window_attention(qh, kh, vh, window_t, window_s, scale)
+        return _SeqToHeads.apply(o_t, cp, True), _SeqToHeads.apply(o_s, cp, True)
+    return _SeqToHeads.apply(ops.attention(qh, kh, vh, window=window_t, scale=scale), cp, True)
+
+
 def attention(q, k, v, window, scale, layer_idx):
     cp = _ACTIVE
+    if cp.by_heads(q.shape[1], window, nv.use_native(q)):
+        return _attention_by_heads(q, k, v, window, window, scale, False, cp)
     if not nv.use_native(q):
         from ..ops import reference
         k_all, v_all = _gathered_kv(k, v, cp)
@@ -260,6 +330,8 @@ def attention(q, k, v, window, scale, layer_idx):
 
 def dual_window_attention(q, k, v, window_t, window_s, scale, layer_idx):
     cp = _ACTIVE
+    if cp.by_heads(q.shape[1], window_t, nv.use_native(q)):
+        return _attention_by_heads(q, k, v, window_t, window_s, scale, True, cp)
     if not nv.use_native(q):
         from ..ops import reference
         k_all, v_all = _gathered_kv(k, v, cp)
