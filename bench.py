@@ -54,7 +54,7 @@ def parse_args():
     ap.add_argument("--seq-len", type=int, default=65536)
     ap.add_argument("--batch-per-gpu", type=int, default=1)
     ap.add_argument("--layers", type=int, default=None, help="debug only: override num_hidden_layers (invalidates the number)")
-    ap.add_argument("--ac", default="none", choices=["none", "full", "ttt"],
+    ap.add_argument("--ac", default="none", choices=["none", "full", "ttt", "op"],
                     help="activation checkpointing of this framework's arm; 'none' keeps the activations of one "
                          "64K-token step resident, which fits the 180 GB of a B200 (the reference recipe needs 'full')")
     ap.add_argument("--no-ac", action="store_true", help="same as --ac none (kept for older command lines)")
@@ -193,6 +193,7 @@ def run_ours(args):
     ms_e2e = timed_region(torch, dist, world, lambda i: losses.append(engine.train_step(e2e_host[i])), args.steps)
     clocks = sampler.stop() if sampler else {}
     status = _native.device_status()
+    peak_gib = round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)
 
     tokens = B * S * world * args.steps
     value = tokens / (ms_dev / 1e3)
@@ -236,7 +237,7 @@ def run_ours(args):
             "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e / args.steps, 2),
                     "h2d_bytes_per_step": B * S * 8, "d2h_bytes_per_step": 4},
             "gpu_launches": launches, "final_loss": losses[-1] if losses else None, "device_status": status,
-            "ac_full": ac_full, "extra": extra,
+            "peak_mem_gib": peak_gib, "ac_full": ac_full, "extra": extra,
         }), flush=True)
     if world > 1:
         dist.destroy_process_group()
