@@ -88,3 +88,36 @@ def test_replicated_pipeline_vocab_parallel_and_hybrid_layouts_on_gpus():
     """Replicated data parallelism, vocabulary-parallel cross-entropy and a two-stage pipeline on 2 GPUs; with 4 or
     more GPUs also hybrid sharding (2 replicas x 2 shards)."""
     _launch("layouts", 4 if _ngpu() >= 4 else 2)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
+@pytest.mark.timeout(900)
+def test_trainer_entry_point_on_two_gpus_saves_and_resumes(tmp_path):
+    """``python -m flame.train`` under torchrun on 2 GPUs (native kernels, fused peer-memory data parallelism, synthetic
+    data): 4 steps with a checkpoint at 2 and 4, then a second launch that resumes at 4 and trains to 6."""
+    import json
+    cfg = dict(model_type="ipttcdv9", hidden_size=256, num_hidden_layers=2, num_heads=4, num_kv_heads=2, head_dim=64,
+               intermediate_size=768, vocab_size=4096, window_size=256, max_position_embeddings=2048, ttt_mode=True,
+               ttt_chunk=128, ttt_layers=[1], ttt_update_every=4, qk_norm=True, tie_word_embeddings=True,
+               fuse_cross_entropy=False, fuse_linear_cross_entropy=True)
+    (tmp_path / "model.json").write_text(json.dumps(cfg))
+
+    def run(steps: int) -> str:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+               "--master-port", str(_free_port()), "-m", "flame.train", "--job.dump_folder", str(tmp_path / "run"),
+               "--model.config", str(tmp_path / "model.json"), "--training.dataset", "synthetic", "--training.seq_len", "1024",
+               "--training.batch_size", "1", "--training.steps", str(steps), "--optimizer.lr", "1e-3",
+               "--lr_scheduler.warmup_steps", "2", "--checkpoint.enable_checkpoint", "--checkpoint.interval", "2",
+               "--metrics.log_freq", "1", "--training.seed", "3"]
+        res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, PYTHONPATH=str(ROOT)),
+                             cwd=str(ROOT))
+        out = res.stdout + res.stderr
+        assert res.returncode == 0, out[-4000:]
+        return out
+
+    first = run(4)
+    ckpt = tmp_path / "run" / "checkpoint"
+    assert (ckpt / "step-2" / ".metadata").is_file() and (ckpt / "step-4" / ".metadata").is_file(), first[-2000:]
+    second = run(6)
+    assert (ckpt / "step-6" / ".metadata").is_file(), second[-2000:]
+    assert "step-4" in second or "step 4" in second.lower() or "resum" in second.lower() or "load" in second.lower(), second[-2000:]
