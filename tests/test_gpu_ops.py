@@ -272,6 +272,30 @@ def test_gemm_epilogue_row_statistics(rows, K, V):
     torch.testing.assert_close(lse, torch.logsumexp(out.float(), dim=-1), rtol=1e-5, atol=1e-4)
 
 
+@pytest.mark.parametrize("BH,n,D,Dv", [(3, 5, 32, 32), (2, 7, 128, 64), (2, 3, 256, 96), (5, 1, 64, 128)])
+def test_delta_chain_kernels_match_the_loop(BH, n, D, Dv):
+    """The chunk-to-chunk chain of the delta rule (one launch per direction) against the same recurrence written as
+    a PyTorch loop: corrected values, the state entering every chunk, the final state, and all five gradients."""
+    from ttcd_b200.ops import delta_chain as dc
+    gen = torch.Generator().manual_seed(BH * 100 + D)
+    mk = lambda *sh, sc=0.2: (torch.randn(*sh, generator=gen) * sc).to(DEV).requires_grad_()  # noqa: E731
+    w, u, kt, s0 = mk(BH, n, 64, D, sc=0.1), mk(BH, n, 64, Dv), mk(BH, n, 64, D, sc=0.1), mk(BH, D, Dv)
+    gamma = torch.rand(BH, n, generator=gen).to(DEV).requires_grad_()
+    assert dc._native_ok(w, u)
+    outs = dc.delta_chain(w, u, kt, gamma, s0)
+    want = dc._fwd_torch(*(t.detach() for t in (w, u, kt, gamma, s0)))
+    for a, b, name in zip(outs, want, ("vn", "states", "final")):
+        torch.testing.assert_close(a, b, rtol=1e-4, atol=1e-4, msg=lambda m, name=name: f"{name}: {m}")
+    gs = [torch.randn_like(o) for o in outs]
+    got = torch.autograd.grad(outs, [w, u, kt, gamma, s0], gs)
+    d_vn_tot, ds_next, d_s0 = dc._bwd_torch(w.detach(), kt.detach(), gamma.detach(), *gs)
+    states = want[1]
+    ref = [-(d_vn_tot @ states.transpose(-1, -2)), d_vn_tot, want[0] @ ds_next.transpose(-1, -2),
+           (states * ds_next).sum(dim=(-1, -2)), d_s0]
+    for a, b, name in zip(got, ref, ("dw", "du", "dkt", "dgamma", "ds0")):
+        torch.testing.assert_close(a, b, rtol=2e-4, atol=2e-4, msg=lambda m, name=name: f"{name}: {m}")
+
+
 def test_adamw_and_sumsq():
     from ttcd_b200.ops import cuda
     n = 100_003

@@ -256,8 +256,14 @@ def gated_delta_rule(q, k, v, g, beta, *, scale=None, l2norm: bool = True, cu_se
     several GB per layer at 64K tokens per step."""
     if recurrent and cu_seqlens is None:
         return reference.gated_delta_rule_recurrent(q, k, v, g, beta, scale, l2norm, initial_state, output_final_state)
-    chunk = _DELTA_CHUNK or (256 if q.shape[1] >= 1024 else 64)
-    args = (q, k, v, g, beta, scale, l2norm, chunk, cu_seqlens, initial_state, output_final_state)
+    # on the GPU the chain over chunks is one kernel per direction (64-row chunks, small per-chunk tensors); elsewhere
+    # fewer, longer chunks keep the number of dependent steps down
+    chain = q.is_cuda and _native.available() and _native.has("ttcd_delta_chain_fwd") \
+        and q.shape[-1] in (32, 64, 128, 256) and v.shape[-1] % 32 == 0
+    chunk = _DELTA_CHUNK or (64 if chain else (256 if q.shape[1] >= 1024 else 64))
+    if chunk != 64:
+        chain = False
+    args = (q, k, v, g, beta, scale, l2norm, chunk, cu_seqlens, initial_state, output_final_state, True, chain)
     if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, g, beta)):
         from torch.utils.checkpoint import checkpoint
         return checkpoint(reference.gated_delta_rule_chunked, *args, use_reentrant=False)

@@ -579,20 +579,21 @@ class _tf32_matmuls:
 
 
 def gated_delta_rule_chunked(q, k, v, g, beta, scale=None, l2norm: bool = True, chunk: int = 64, cu_seqlens=None,
-                             initial_state=None, output_final_state: bool = False, scan: bool = True):
+                             initial_state=None, output_final_state: bool = False, scan: bool = True, chain: bool = False):
     with _tf32_matmuls(q.is_cuda):
         return _gated_delta_rule_chunked(q, k, v, g, beta, scale, l2norm, chunk, cu_seqlens, initial_state,
-                                         output_final_state, scan)
+                                         output_final_state, scan, chain)
 
 
 def _gated_delta_rule_chunked(q, k, v, g, beta, scale=None, l2norm: bool = True, chunk: int = 64, cu_seqlens=None,
-                              initial_state=None, output_final_state: bool = False, scan: bool = True):
+                              initial_state=None, output_final_state: bool = False, scan: bool = True, chain: bool = False):
     """Chunk-parallel gated delta rule (the computation of fla/ops/gated_delta_rule/chunk.py and, with ``g`` None, of
     fla/ops/delta_rule/chunk.py).  With G the running sum of g inside a chunk and S_0 the state entering it, the
     updates u solve the unit-lower-triangular system (I + L) U = beta V - (beta e^G K) S_0 with
     L_ij = beta_i e^{G_i - G_j} (k_i . k_j) for j < i; every exponent is a difference G_i - G_j with i >= j, so
-    nothing overflows.  The chunk-to-chunk chain is affine in the state and is composed by a prefix scan (``scan``; the
-    plain loop over chunks otherwise).  Differentiable through autograd; shapes as in ``gated_delta_rule_recurrent``.  With
+    nothing overflows.  The chunk-to-chunk chain is one op with a hand-written backward (``chain``: ops/delta_chain.py,
+    a CUDA kernel per direction), or, being affine in the state, a prefix scan of D x D maps (``scan``), or the plain
+    loop over chunks.  Differentiable through autograd; shapes as in ``gated_delta_rule_recurrent``.  With
     ``cu_seqlens`` (batch 1) each packed sequence starts from a zero state (``initial_state`` then has one entry per
     sequence)."""
     if cu_seqlens is not None:
@@ -601,7 +602,7 @@ def _gated_delta_rule_chunked(q, k, v, g, beta, scale=None, l2norm: bool = True,
         for i, (a, b) in enumerate(zip(bounds[:-1], bounds[1:])):
             init = None if initial_state is None else initial_state[i:i + 1]
             o, s = gated_delta_rule_chunked(q[:, a:b], k[:, a:b], v[:, a:b], None if g is None else g[:, a:b], beta[:, a:b],
-                                            scale, l2norm, chunk, None, init, output_final_state, scan)
+                                            scale, l2norm, chunk, None, init, output_final_state, scan, chain)
             outs.append(o)
             finals.append(s)
         return torch.cat(outs, dim=1), (torch.cat(finals, dim=0) if output_final_state else None)
@@ -633,7 +634,15 @@ def _gated_delta_rule_chunked(q, k, v, g, beta, scale=None, l2norm: bool = True,
     qk = (qc @ kc.transpose(-1, -2)) * decay
     q_in, k_out = qc * eg, kc * to_end
     S0 = qf.new_zeros(B, H, D, vf.shape[-1]) if initial_state is None else initial_state.float()
-    if n > 4 and scan and D <= 128:        # (for wider heads the D x D x D products of the scan cost more than the loop)
+    if chain:
+        # the chain over chunks as ONE op (a CUDA kernel per direction on the GPU): ops/delta_chain.py
+        from .delta_chain import delta_chain
+        Dv = vf.shape[-1]
+        flat = lambda t: t.reshape(B * H, n, *t.shape[3:])  # noqa: E731
+        vn, states, S = delta_chain(flat(w), flat(u), flat(k_out), eg[:, :, :, -1, 0].reshape(B * H, n), S0.reshape(B * H, D, Dv))
+        vn, states, S = vn.view(B, H, n, chunk, Dv), states.view(B, H, n, D, Dv), S.view(B, H, D, Dv)
+        o = q_in @ states + qk @ vn
+    elif n > 4 and scan and D <= 128:        # (for wider heads the D x D x D products of the scan cost more than the loop)
         # The state entering chunk i+1 is linear in the one entering chunk i:  S_{i+1} = M_i S_i + N_i  with
         # M_i = e^{G_C} I - k_out_i^T w_i  (D x D) and N_i = k_out_i^T u_i.  The chain over the n chunks is a prefix
         # composition of these affine maps, done in log2(n) rounds of batched products instead of n dependent steps.
