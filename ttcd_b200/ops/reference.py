@@ -618,7 +618,8 @@ def _gated_delta_rule_chunked(q, k, v, g, beta, scale=None, l2norm: bool = True,
         qf, kf, vf = (F.pad(x, (0, 0, 0, 0, 0, pad)) for x in (qf, kf, vf))
         bf, gf = F.pad(bf, (0, 0, 0, pad)), F.pad(gf, (0, 0, 0, pad))
     n = (T + pad) // chunk
-    qc, kc, vc = (x.view(B, n, chunk, H, -1).permute(0, 3, 1, 2, 4) for x in (qf * scale, kf, vf))     # [B, H, n, C, D]
+    # [B, H, n, C, D], made contiguous once (every batched product would otherwise copy its strided operand)
+    qc, kc, vc = (x.view(B, n, chunk, H, -1).permute(0, 3, 1, 2, 4).contiguous() for x in (qf * scale, kf, vf))
     bc = bf.view(B, n, chunk, H).permute(0, 3, 1, 2).unsqueeze(-1)
     G = gf.view(B, n, chunk, H).permute(0, 3, 1, 2).cumsum(-1)                                         # [B, H, n, C]
     tril = torch.ones(chunk, chunk, dtype=torch.bool, device=q.device).tril()
