@@ -252,8 +252,8 @@ def gated_delta_rule(q, k, v, g, beta, *, scale=None, l2norm: bool = True, cu_se
     form whose matrix products run as batched GEMMs.  Returns (o, final state or None).
 
     When gradients are needed the chunked form runs under activation recomputation: autograd keeps q, k, v, g, beta and
-    rebuilds the fp32 intermediates (per-chunk triangular factors, the scan's D x D maps) in backward; kept, they are
-    several GB per layer at 64K tokens per step."""
+    rebuilds the fp32 intermediates (per-chunk triangular factors, WY products, chunk states) in backward; kept, they
+    are several GB per layer at 64K tokens per step."""
     if recurrent and cu_seqlens is None:
         return reference.gated_delta_rule_recurrent(q, k, v, g, beta, scale, l2norm, initial_state, output_final_state)
     # on the GPU the chain over chunks is one kernel per direction (64-row chunks, small per-chunk tensors); elsewhere
@@ -264,7 +264,15 @@ def gated_delta_rule(q, k, v, g, beta, *, scale=None, l2norm: bool = True, cu_se
     if chunk != 64:
         chain = False
     args = (q, k, v, g, beta, scale, l2norm, chunk, cu_seqlens, initial_state, output_final_state, True, chain)
-    if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, g, beta)):
+    needs_grad = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, g, beta))
+    if needs_grad and not _keep_delta_intermediates(q, v, chunk):
         from torch.utils.checkpoint import checkpoint
         return checkpoint(reference.gated_delta_rule_chunked, *args, use_reentrant=False)
     return reference.gated_delta_rule_chunked(*args)
+
+
+def _keep_delta_intermediates(q, v, chunk: int) -> bool:
+    """Whether a call of the chunked rule keeps its fp32 intermediates for backward instead of recomputing them.
+    Recomputation is the default: kept, the intermediates of a 24-layer model at 16 x 4096 tokens come to ~140 GB (for a
+    5 % shorter step on `delta_net` 340M, and more than 180 GB on `gated_deltanet`).  ``TTCD_DELTA_KEEP=1`` keeps them."""
+    return q.is_cuda and os.environ.get("TTCD_DELTA_KEEP", "0") == "1"
