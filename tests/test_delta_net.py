@@ -195,3 +195,29 @@ def test_chain_op_backward_matches_autograd():
     g_got = torch.autograd.grad(got, [w, u, kt, gamma, s0], gs)
     for a, b in zip(got + g_got, want + g_want):
         torch.testing.assert_close(a, b, rtol=1e-10, atol=1e-10)
+
+
+@pytest.mark.parametrize("gated,l2norm", [(False, True), (True, True), (True, False)])
+def test_fused_op_statement_matches_the_recurrence(gated, l2norm):
+    """The one-op form of the chunked rule (hand-written backward through the chunk-local part, the chain and the output
+    products; its PyTorch statement, which is also the oracle of the CUDA kernels) against the token-by-token rule:
+    outputs, final state and the gradients of q, k, v, g, beta and the initial state, on a ragged length."""
+    from ttcd_b200.ops.delta_fused import gated_delta_rule_fused
+    q, k, v, g, beta = (t.double() for t in _rule_inputs())
+    if not l2norm:
+        k = torch.nn.functional.normalize(k, dim=-1)
+    if not gated:
+        g = None
+    s0 = torch.randn(2, 3, 16, 24, dtype=torch.float64) * 0.1
+    leaves = [None if t is None else t.clone().requires_grad_() for t in (q, k, v, g, beta, s0)]
+    twins = [None if t is None else t.clone().requires_grad_() for t in (q, k, v, g, beta, s0)]
+    o_r, s_r = R.gated_delta_rule_recurrent(*leaves[:5], None, l2norm, leaves[5], True)
+    o_f, s_f = gated_delta_rule_fused(*twins[:5], None, l2norm, twins[5], True)
+    go, gs = torch.randn_like(o_r), torch.randn_like(s_r)
+    ((o_r * go).sum() + (s_r * gs).sum()).backward()
+    ((o_f * go).sum() + (s_f * gs).sum()).backward()
+    torch.testing.assert_close(o_f, o_r.double(), rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(s_f, s_r.double(), rtol=1e-4, atol=1e-5)
+    for a, b, name in zip(twins, leaves, ("q", "k", "v", "g", "beta", "s0")):
+        if a is not None:
+            torch.testing.assert_close(a.grad, b.grad.double(), rtol=1e-3, atol=1e-4, msg=lambda m, name=name: f"d{name}: {m}")

@@ -29,6 +29,11 @@ def _close(got, want, atol, rtol, name=""):
     assert bad == 0.0, f"{name}: max err {err.max().item():.4g}, {bad * 100:.3f}% outside tol, ref max {want.abs().max().item():.4g}"
 
 
+def _cos(a, b):
+    a, b = a.double().flatten(), b.double().flatten()
+    return float(torch.dot(a, b) / (a.norm() * b.norm()).clamp_min(1e-30))
+
+
 # ------------------------------------------------------------------------------------------- GEMM
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 256, 128), (384, 320, 192), (1000, 1160, 1032), (4096, 1024, 1024)])
@@ -294,6 +299,68 @@ def test_delta_chain_kernels_match_the_loop(BH, n, D, Dv):
            (states * ds_next).sum(dim=(-1, -2)), d_s0]
     for a, b, name in zip(got, ref, ("dw", "du", "dkt", "dgamma", "ds0")):
         torch.testing.assert_close(a, b, rtol=2e-4, atol=2e-4, msg=lambda m, name=name: f"{name}: {m}")
+
+
+def _delta_inputs(B, T, H, D, Dv, gated, l2norm, dtype, seed):
+    gen = torch.Generator().manual_seed(seed)
+    q, k = torch.randn(B, T, H, D, generator=gen), torch.randn(B, T, H, D, generator=gen)
+    if not l2norm:                       # callers that switch the normalisation off pass unit keys
+        k = torch.nn.functional.normalize(k, dim=-1)
+    v = torch.randn(B, T, H, Dv, generator=gen)
+    beta = torch.rand(B, T, H, generator=gen)
+    g = -torch.rand(B, T, H, generator=gen) * 0.3 if gated else None
+    q, k, v = (t.to(DEV).to(dtype) for t in (q, k, v))
+    return q, k, v, beta.to(DEV), None if g is None else g.to(DEV)
+
+
+@pytest.mark.parametrize("D,Dv,gated,l2norm,dtype", [(64, 64, True, True, torch.float32), (128, 128, False, True, BF),
+                                                      (256, 128, True, False, torch.float32), (128, 192, True, True, BF)])
+def test_delta_prep_kernels_match_their_statement(D, Dv, gated, l2norm, dtype):
+    """The chunk-local kernels of the delta rule (WY factors, scaled keys / queries, intra-chunk scores; and the
+    gradients of q, k, v, beta, g from the gradients of those) against the same formulas in float64, on a ragged
+    length (the last chunk has 8 of 64 rows)."""
+    from ttcd_b200.ops import delta_fused as df
+    B, T, H = 2, 200, 3
+    q, k, v, beta, g = _delta_inputs(B, T, H, D, Dv, gated, l2norm, dtype, seed=D + Dv)
+    scale = D ** -0.5
+    assert df.native_ok(q, v)
+    dbl = lambda t: None if t is None else t.double()  # noqa: E731
+    got = df._prep_fwd(q, k, v, beta, g, scale, l2norm)
+    want = df._prep_fwd_torch(dbl(q), dbl(k), dbl(v), dbl(beta), dbl(g), scale, l2norm)
+    for a, b, name in zip(got, want, ("w", "u", "kt", "q_in", "qk", "gamma")):
+        torch.testing.assert_close(a.double(), b, rtol=1e-4, atol=1e-5, msg=lambda m, name=name: f"{name}: {m}")
+    gen = torch.Generator().manual_seed(7)
+    grads = [torch.randn(o.shape, generator=gen).to(DEV) for o in got]
+    got_b = df._prep_bwd(q, k, v, beta, g, scale, l2norm, *grads)
+    want_b = df._prep_bwd_torch(dbl(q), dbl(k), dbl(v), dbl(beta), dbl(g), scale, l2norm, *(t.double() for t in grads))
+    for a, b, name in zip(got_b, want_b, ("dq", "dk", "dv", "dbeta", "dg")):
+        if b is None:
+            assert a is None
+            continue
+        tol = float(b.abs().max()) * 2e-5
+        torch.testing.assert_close(a.double(), b, rtol=1e-4, atol=tol, msg=lambda m, name=name: f"{name}: {m}")
+
+
+@pytest.mark.parametrize("gated,keep", [(True, "1"), (False, "0")])
+def test_fused_delta_rule_matches_its_cpu_statement(gated, keep, monkeypatch):
+    """The whole op on CUDA (kernels + batched products, intermediates kept or rebuilt in backward) against the same op in
+    float64 on the CPU: outputs, final state and the gradients of q, k, v, g, beta and the initial state."""
+    from ttcd_b200.ops import delta_fused as df
+    monkeypatch.setenv("TTCD_DELTA_KEEP", keep)
+    B, T, H, D, Dv = 2, 333, 2, 128, 128
+    q, k, v, beta, g = _delta_inputs(B, T, H, D, Dv, gated, True, torch.float32, seed=11)
+    s0 = (torch.randn(B, H, D, Dv, generator=torch.Generator().manual_seed(5)) * 0.1).to(DEV)
+    dev = [None if t is None else t.clone().requires_grad_() for t in (q, k, v, g, beta, s0)]
+    cpu = [None if t is None else t.detach().double().cpu().requires_grad_() for t in (q, k, v, g, beta, s0)]
+    o, s = df.gated_delta_rule_fused(*dev[:5], None, True, dev[5], True)
+    o_ref, s_ref = df.gated_delta_rule_fused(*cpu[:5], None, True, cpu[5], True)
+    go, gs = torch.randn_like(o_ref), torch.randn_like(s_ref)
+    ((o_ref * go).sum() + (s_ref * gs).sum()).backward()
+    ((o * go.to(DEV).float()).sum() + (s * gs.to(DEV).float()).sum()).backward()
+    assert _cos(o.cpu().double(), o_ref) > 0.99999 and _cos(s.cpu().double(), s_ref) > 0.99999
+    for a, b, name in zip(dev, cpu, ("q", "k", "v", "g", "beta", "s0")):
+        if a is not None:
+            assert _cos(a.grad.cpu().double(), b.grad) > 0.9999, (name, _cos(a.grad.cpu().double(), b.grad))
 
 
 def test_adamw_and_sumsq():

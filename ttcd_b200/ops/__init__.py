@@ -14,7 +14,7 @@ import torch
 import torch.nn.functional as F
 
 from .. import _native
-from . import reference
+from . import delta_fused, reference
 
 __all__ = [
     "rmsnorm", "rmsnorm_dual", "qkv_norm_rope", "rope", "swiglu", "swiglu_packed", "linear", "matmul",
@@ -243,6 +243,7 @@ def newton_schulz(g, coeffs=reference.NS_COEFFS):
 # is one batched triangular solve and a few batched GEMMs; the chain over chunks is a prefix scan of D x D maps, whose
 # intermediates shrink with the number of chunks.
 _DELTA_CHUNK = int(os.environ.get("TTCD_DELTA_CHUNK", "0"))
+_DELTA_FUSED = os.environ.get("TTCD_DELTA_FUSED", "1") != "0"
 
 
 def gated_delta_rule(q, k, v, g, beta, *, scale=None, l2norm: bool = True, cu_seqlens=None, initial_state=None,
@@ -256,6 +257,19 @@ def gated_delta_rule(q, k, v, g, beta, *, scale=None, l2norm: bool = True, cu_se
     are several GB per layer at 64K tokens per step."""
     if recurrent and cu_seqlens is None:
         return reference.gated_delta_rule_recurrent(q, k, v, g, beta, scale, l2norm, initial_state, output_final_state)
+    if _DELTA_FUSED and not _DELTA_CHUNK and delta_fused.native_ok(q, v):
+        # one op with a hand-written backward: chunk-local kernels, the chain kernels, batched products in between
+        if cu_seqlens is None:
+            return delta_fused.gated_delta_rule_fused(q, k, v, g, beta, scale, l2norm, initial_state, output_final_state)
+        bounds = cu_seqlens.tolist()
+        outs, finals = [], []
+        for i, (a, b) in enumerate(zip(bounds[:-1], bounds[1:])):      # every packed sequence starts from its own state
+            o, s = delta_fused.gated_delta_rule_fused(q[:, a:b], k[:, a:b], v[:, a:b], None if g is None else g[:, a:b],
+                                                      beta[:, a:b], scale, l2norm,
+                                                      None if initial_state is None else initial_state[i:i + 1], output_final_state)
+            outs.append(o)
+            finals.append(s)
+        return torch.cat(outs, dim=1), (torch.cat(finals, dim=0) if output_final_state else None)
     # on the GPU the chain over chunks is one kernel per direction (64-row chunks, small per-chunk tensors); elsewhere
     # fewer, longer chunks keep the number of dependent steps down
     chain = q.is_cuda and _native.available() and _native.has("ttcd_delta_chain_fwd") \
