@@ -1,7 +1,8 @@
 // The chunk-local part of the (gated) delta rule, forward and backward, one CTA per (batch, head, 64-token chunk)
-// (sm_100a; fp32 FMA work on 64 x 64 tiles in shared memory: the products of a chunk are 64 x 64 x D, the point of the
-// kernels is to replace some forty element-wise / batched-GEMM / triangular-solve launches over fp32 [B,H,T,D]
-// tensors by one pass that reads q, k, v once).
+// (sm_100a; the 64 x 64 x 64 products run on the tensor cores as TF32 mma.sync tiles with fp32 accumulation, out of
+// fp32 tiles in shared memory; the triangular inverse and all element-wise work stay fp32.  The products of a chunk are
+// too small for a tcgen05 pipeline; the point of the kernels is to replace some forty element-wise / batched-GEMM /
+// triangular-solve launches over fp32 [B,H,T,D] tensors by one pass that reads q, k, v once).
 //
 // With q, k the (optionally L2-normalised, q also scaled) rows of the chunk, beta the write strengths, G the running
 // sum of the log decays g inside the chunk (G = 0 without a gate), dec_ij = e^{G_i - G_j} for i >= j:
@@ -28,12 +29,14 @@
 namespace ttcd {
 
 constexpr int DP_C = 64;                  // rows of a chunk
-constexpr int DP_LD = 68;                 // row stride (floats) of a 64 x 64 tile: 16-byte rows, rows 4 banks apart
-constexpr int DP_TILE = DP_C * DP_LD;
+constexpr int DP_LDA = 68;                // row stride (floats) of a tile read as the A operand, or row-wise as B (X Y^T)
+constexpr int DP_LDB = 72;                // row stride of a tile read column-wise as the B operand (M X)
+constexpr int DP_TILE_A = DP_C * DP_LDA;
+constexpr int DP_TILE_B = DP_C * DP_LDB;
 constexpr int DP_THREADS = 256;
-constexpr int DP_VEC = 12 * DP_C;         // per-row vectors
-constexpr int DP_SMEM_FWD = (5 * DP_TILE + DP_VEC) * 4;
-constexpr int DP_SMEM_BWD = (6 * DP_TILE + DP_VEC) * 4;
+constexpr int DP_VEC = 8 * DP_C + 8 * 2 * DP_C;     // 8 per-row vectors + 8 pairs of partial row sums
+constexpr int DP_SMEM_FWD = (3 * DP_TILE_A + 2 * DP_TILE_B + DP_VEC) * 4;
+constexpr int DP_SMEM_BWD = (3 * DP_TILE_A + 3 * DP_TILE_B + DP_VEC) * 4;
 
 struct DeltaPrepParams {
   const void* q; const void* k; const void* v;      // [B, T, H, D | Dv], bf16 or fp32 (in_bf16)
@@ -45,38 +48,58 @@ struct DeltaPrepParams {
   float *dq, *dk, *dv, *dbeta, *dg;                 // backward outputs, token layout [B, T, H, *] fp32
 };
 
-// ---- 64 x 64 x 64 products; thread (ty, tx) of the 16 x 16 grid owns rows ty + 16 a -----------------------------
-// acc[a][b] += sum_d X[ty + 16 a][d] Y[tx + 16 b][d]     (X Y^T: the thread's columns are tx + 16 b)
-__device__ __forceinline__ void mm_nt(float (&acc)[4][4], const float* X, const float* Y, int ty, int tx) {
+// ---- 64 x 64 x 64 products as TF32 m16n8k8 tiles -----------------------------------------------------------------
+// Warp (wr, wc) of the 4 x 2 warp grid owns rows 16 wr .. +15 and columns 32 wc .. +31 (four n-tiles of 8); lane
+// (g = lane / 4, c = lane % 4) holds, of n-tile t, the elements (r0, j), (r0, j + 1), (r1, j), (r1, j + 1) with
+// r0 = 16 wr + g, r1 = r0 + 8, j = 32 wc + 8 t + 2 c  ->  acc[t][0..3].
+struct Own {
+  int r0, r1, wr, wc, g, c;
+  __device__ Own() {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    wr = warp >> 1; wc = warp & 1; g = lane >> 2; c = lane & 3;
+    r0 = 16 * wr + g; r1 = r0 + 8;
+  }
+  __device__ __forceinline__ int col(int t) const { return 32 * wc + 8 * t + 2 * c; }
+};
+__device__ __forceinline__ uint32_t tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void load_a(uint32_t (&a)[4], const float* X, const Own& o, int k0) {
+  a[0] = tf32(X[o.r0 * DP_LDA + k0 + o.c]);
+  a[1] = tf32(X[o.r1 * DP_LDA + k0 + o.c]);
+  a[2] = tf32(X[o.r0 * DP_LDA + k0 + o.c + 4]);
+  a[3] = tf32(X[o.r1 * DP_LDA + k0 + o.c + 4]);
+}
+// acc += X Y^T:  acc(i, j) += sum_d X[i][d] Y[j][d]      (both tiles with row stride DP_LDA)
+__device__ __forceinline__ void mm_nt(float (&acc)[4][4], const float* X, const float* Y, const Own& o) {
 #pragma unroll 2
-  for (int d = 0; d < DP_C; d += 4) {
-    float4 x[4], y[4];
+  for (int k0 = 0; k0 < DP_C; k0 += 8) {
+    uint32_t a[4];
+    load_a(a, X, o, k0);
 #pragma unroll
-    for (int a = 0; a < 4; ++a) x[a] = *reinterpret_cast<const float4*>(X + (ty + 16 * a) * DP_LD + d);
-#pragma unroll
-    for (int b = 0; b < 4; ++b) y[b] = *reinterpret_cast<const float4*>(Y + (tx + 16 * b) * DP_LD + d);
-#pragma unroll
-    for (int a = 0; a < 4; ++a)
-#pragma unroll
-      for (int b = 0; b < 4; ++b)
-        acc[a][b] = fmaf(x[a].x, y[b].x, fmaf(x[a].y, y[b].y, fmaf(x[a].z, y[b].z, fmaf(x[a].w, y[b].w, acc[a][b]))));
+    for (int t = 0; t < 4; ++t) {
+      const float* y = Y + (32 * o.wc + 8 * t + o.g) * DP_LDA + k0 + o.c;
+      mma_tf32(acc[t], a, tf32(y[0]), tf32(y[4]));
+    }
   }
 }
-// acc[a][b] += sum_j M[ty + 16 a][j] X[j][4 tx + b]      (M X: the thread's columns are 4 tx + b)
-__device__ __forceinline__ void mm_nn(float (&acc)[4][4], const float* M, const float* X, int ty, int tx) {
+// acc += M X:    acc(i, j) += sum_k M[i][k] X[k][j]      (M with row stride DP_LDA, X with DP_LDB)
+__device__ __forceinline__ void mm_nn(float (&acc)[4][4], const float* M, const float* X, const Own& o) {
 #pragma unroll 2
-  for (int j = 0; j < DP_C; j += 4) {
-    float4 m[4], x[4];
+  for (int k0 = 0; k0 < DP_C; k0 += 8) {
+    uint32_t a[4];
+    load_a(a, M, o, k0);
 #pragma unroll
-    for (int a = 0; a < 4; ++a) m[a] = *reinterpret_cast<const float4*>(M + (ty + 16 * a) * DP_LD + j);
-#pragma unroll
-    for (int jj = 0; jj < 4; ++jj) x[jj] = *reinterpret_cast<const float4*>(X + (j + jj) * DP_LD + 4 * tx);
-#pragma unroll
-    for (int a = 0; a < 4; ++a) {
-      acc[a][0] = fmaf(m[a].x, x[0].x, fmaf(m[a].y, x[1].x, fmaf(m[a].z, x[2].x, fmaf(m[a].w, x[3].x, acc[a][0]))));
-      acc[a][1] = fmaf(m[a].x, x[0].y, fmaf(m[a].y, x[1].y, fmaf(m[a].z, x[2].y, fmaf(m[a].w, x[3].y, acc[a][1]))));
-      acc[a][2] = fmaf(m[a].x, x[0].z, fmaf(m[a].y, x[1].z, fmaf(m[a].z, x[2].z, fmaf(m[a].w, x[3].z, acc[a][2]))));
-      acc[a][3] = fmaf(m[a].x, x[0].w, fmaf(m[a].y, x[1].w, fmaf(m[a].z, x[2].w, fmaf(m[a].w, x[3].w, acc[a][3]))));
+    for (int t = 0; t < 4; ++t) {
+      const float* x = X + (k0 + o.c) * DP_LDB + 32 * o.wc + 8 * t + o.g;
+      mma_tf32(acc[t], a, tf32(x[0]), tf32(x[4 * DP_LDB]));
     }
   }
 }
@@ -86,13 +109,17 @@ __device__ __forceinline__ void zero(float (&acc)[4][4]) {
 #pragma unroll
     for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
 }
-// sum over the 16 threads (tx) that share a row; every one of them gets the total
-__device__ __forceinline__ float row_sum16(float v) {
-  v += __shfl_xor_sync(0xffffffffu, v, 8);
-  v += __shfl_xor_sync(0xffffffffu, v, 4);
-  v += __shfl_xor_sync(0xffffffffu, v, 2);
+// sum over the four lanes (c) that share the rows r0, r1 of a warp; every one of them gets the total
+__device__ __forceinline__ float quad_sum(float v) {
   v += __shfl_xor_sync(0xffffffffu, v, 1);
+  v += __shfl_xor_sync(0xffffffffu, v, 2);
   return v;
+}
+// a thread's sums over its columns of rows r0 / r1 -> the warp-column's slot of a pair of partial row sums
+__device__ __forceinline__ void put_row_partials(float* pair, const Own& o, float s0, float s1) {
+  s0 = quad_sum(s0);
+  s1 = quad_sum(s1);
+  if (o.c == 0) { pair[o.wc * DP_C + o.r0] = s0; pair[o.wc * DP_C + o.r1] = s1; }
 }
 
 // ---- tile loads: 64 rows x 64 columns -> shared memory, times a per-row factor ----------------------------------
@@ -107,34 +134,36 @@ __device__ __forceinline__ float4 load4(const void* base, int64_t elem, bool bf)
   return *reinterpret_cast<const float4*>(static_cast<const float*>(base) + elem);
 }
 // token layout [.., T, H, width]: row r of the chunk is token t0 + r (zero beyond `rows`)
-__device__ __forceinline__ void load_tokens(float* dst, const void* src, bool bf, int64_t elem0, int64_t row_stride, int rows,
-                                            const float* mul) {
+__device__ __forceinline__ void load_tokens(float* dst, int ld, const void* src, bool bf, int64_t elem0, int64_t row_stride,
+                                            int rows, const float* mul) {
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
     const int f = threadIdx.x + DP_THREADS * e, r = f >> 4, c4 = (f & 15) * 4;
     float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
     if (r < rows) x = load4(src, elem0 + r * row_stride + c4, bf);
     const float m = mul != nullptr ? mul[r] : 1.f;
-    *reinterpret_cast<float4*>(dst + r * DP_LD + c4) = make_float4(x.x * m, x.y * m, x.z * m, x.w * m);
+    *reinterpret_cast<float4*>(dst + r * ld + c4) = make_float4(x.x * m, x.y * m, x.z * m, x.w * m);
   }
 }
 // chunk layout [.., 64, width] fp32 (all 64 rows exist)
-__device__ __forceinline__ void load_chunk(float* dst, const float* src, int width, const float* mul) {
+__device__ __forceinline__ void load_chunk(float* dst, int ld, const float* src, int width) {
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
     const int f = threadIdx.x + DP_THREADS * e, r = f >> 4, c4 = (f & 15) * 4;
-    const float4 x = *reinterpret_cast<const float4*>(src + static_cast<int64_t>(r) * width + c4);
-    const float m = mul != nullptr ? mul[r] : 1.f;
-    *reinterpret_cast<float4*>(dst + r * DP_LD + c4) = make_float4(x.x * m, x.y * m, x.z * m, x.w * m);
+    *reinterpret_cast<float4*>(dst + r * ld + c4) = *reinterpret_cast<const float4*>(src + static_cast<int64_t>(r) * width + c4);
   }
 }
 
-// per-row vectors in shared memory
+// per-row vectors and pairs of partial row sums (one half per warp column) in shared memory
 struct DeltaVec {
-  float *beta, *G, *eg, *to_end, *rq, *rk, *v0, *v1, *v2, *v3, *v4, *v5;
+  float *beta, *G, *eg, *to_end, *rq, *rk, *m0, *m1;
+  float* pair[8];
   __device__ explicit DeltaVec(float* p)
-      : beta(p), G(p + 64), eg(p + 128), to_end(p + 192), rq(p + 256), rk(p + 320), v0(p + 384), v1(p + 448),
-        v2(p + 512), v3(p + 576), v4(p + 640), v5(p + 704) {}
+      : beta(p), G(p + 64), eg(p + 128), to_end(p + 192), rq(p + 256), rk(p + 320), m0(p + 384), m1(p + 448) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) pair[i] = p + 512 + 128 * i;
+  }
+  __device__ __forceinline__ float total(int i, int row) const { return pair[i][row] + pair[i][DP_C + row]; }
 };
 
 struct ChunkCoord {
@@ -151,7 +180,7 @@ __device__ __forceinline__ void chunk_rows(const DeltaPrepParams& p, const Chunk
     const bool ok = tid < cc.rows;
     const int64_t at = (cc.tok0 + tid) * p.H + cc.h;
     vec.beta[tid] = ok ? p.beta[at] : 0.f;
-    vec.v0[tid] = (ok && p.g != nullptr) ? p.g[at] : 0.f;
+    vec.m0[tid] = (ok && p.g != nullptr) ? p.g[at] : 0.f;
   }
   // row norms: warp w takes rows 8 w .. 8 w + 7
   for (int rr = 0; rr < 8; ++rr) {
@@ -178,7 +207,7 @@ __device__ __forceinline__ void chunk_rows(const DeltaPrepParams& p, const Chunk
   __syncthreads();
   if (tid < DP_C) {
     float s = 0.f;
-    for (int j = 0; j <= tid; ++j) s += vec.v0[j];
+    for (int j = 0; j <= tid; ++j) s += vec.m0[j];
     vec.G[tid] = s;
   }
   __syncthreads();
@@ -189,36 +218,36 @@ __device__ __forceinline__ void chunk_rows(const DeltaPrepParams& p, const Chunk
   __syncthreads();
 }
 
-// A = k k^T and QK = q k^T over all D (thread-owned elements [ty + 16 a][tx + 16 b]); S0, S1: two scratch tiles
+// A = k k^T and QK = q k^T over all D (in the threads' accumulator layout); S0, S1: two scratch tiles
 __device__ __forceinline__ void chunk_grams(const DeltaPrepParams& p, const ChunkCoord& cc, const DeltaVec& vec, float* S0,
-                                            float* S1, float (&A)[4][4], float (&QK)[4][4], int ty, int tx) {
+                                            float* S1, float (&A)[4][4], float (&QK)[4][4], const Own& o) {
   zero(A);
   zero(QK);
   const int64_t row_stride = static_cast<int64_t>(p.H) * p.D;
   const int64_t elem0 = (cc.tok0 * p.H + cc.h) * p.D;
   for (int s = 0; s < p.D; s += DP_C) {
-    load_tokens(S0, p.k, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rk);
-    load_tokens(S1, p.q, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rq);
+    load_tokens(S0, DP_LDA, p.k, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rk);
+    load_tokens(S1, DP_LDA, p.q, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rq);
     __syncthreads();
-    mm_nt(A, S0, S0, ty, tx);
-    mm_nt(QK, S1, S0, ty, tx);
+    mm_nt(A, S0, S0, o);
+    mm_nt(QK, S1, S0, o);
     __syncthreads();
   }
 }
 
 // T = (I + L)^-1 by forward substitution, column by column: column c belongs to the four lanes 4 c .. 4 c + 3 of one
-// warp, which split the sum over earlier rows.  Writes T (Tm) and, if asked, its transpose (TTm).
+// warp, which split the sum over earlier rows.  Writes T (Tm) and, if asked, its transpose (TTm).  fp32 throughout.
 __device__ __forceinline__ void chunk_inverse(const float* Lm, float* Tm, float* TTm) {
   const int c = threadIdx.x >> 2, part = threadIdx.x & 3;
   for (int i = 0; i < DP_C; ++i) {
     float s = 0.f;
-    for (int j = c + part; j < i; j += 4) s = fmaf(Lm[i * DP_LD + j], Tm[j * DP_LD + c], s);
+    for (int j = c + part; j < i; j += 4) s = fmaf(Lm[i * DP_LDA + j], Tm[j * DP_LDA + c], s);
     s += __shfl_xor_sync(0xffffffffu, s, 1);
     s += __shfl_xor_sync(0xffffffffu, s, 2);
     if (part == 0) {
       const float t = i == c ? 1.f : (i > c ? -s : 0.f);
-      Tm[i * DP_LD + c] = t;
-      if (TTm != nullptr) TTm[c * DP_LD + i] = t;
+      Tm[i * DP_LDA + c] = t;
+      if (TTm != nullptr) TTm[c * DP_LDA + i] = t;
     }
     __syncwarp();
   }
@@ -241,26 +270,27 @@ __device__ __forceinline__ ChunkCoord chunk_coord(const DeltaPrepParams& p) {
 __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_fwd_kernel(const DeltaPrepParams p) {
   extern __shared__ __align__(16) float dp_smem[];
   float* Lm = dp_smem;                   // L, then T with the columns scaled for w
-  float* Tm = Lm + DP_TILE;
-  float* Tu = Tm + DP_TILE;              // T with the columns scaled for u
-  float* S0 = Tu + DP_TILE;
-  float* S1 = S0 + DP_TILE;
-  const DeltaVec vec(dp_smem + 5 * DP_TILE);
-  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  float* Tm = Lm + DP_TILE_A;
+  float* Tu = Tm + DP_TILE_A;            // T with the columns scaled for u
+  float* S0 = Tu + DP_TILE_A;
+  float* S1 = S0 + DP_TILE_B;
+  const DeltaVec vec(S1 + DP_TILE_B);
+  const int tid = threadIdx.x;
+  const Own o;
   const ChunkCoord cc = chunk_coord(p);
 
   chunk_rows(p, cc, vec);
   float A[4][4], QK[4][4];
-  chunk_grams(p, cc, vec, S0, S1, A, QK, ty, tx);
+  chunk_grams(p, cc, vec, S0, S1, A, QK, o);
   // L (strictly lower) into shared memory, qk = lower(dec QK) into S1 for a coalesced copy out
 #pragma unroll
-  for (int a = 0; a < 4; ++a)
+  for (int t = 0; t < 4; ++t)
 #pragma unroll
-    for (int b = 0; b < 4; ++b) {
-      const int i = ty + 16 * a, j = tx + 16 * b;
+    for (int e = 0; e < 4; ++e) {
+      const int i = e < 2 ? o.r0 : o.r1, j = o.col(t) + (e & 1);
       const float dec = i >= j ? expf(vec.G[i] - vec.G[j]) : 0.f;
-      Lm[i * DP_LD + j] = i > j ? vec.beta[i] * dec * A[a][b] : 0.f;
-      S1[i * DP_LD + j] = dec * QK[a][b];
+      Lm[i * DP_LDA + j] = i > j ? vec.beta[i] * dec * A[t][e] : 0.f;
+      S1[i * DP_LDB + j] = dec * QK[t][e];
     }
   __syncthreads();
   {
@@ -268,7 +298,7 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_fwd_kernel(const Del
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int f = tid + DP_THREADS * e, r = f >> 4, c4 = (f & 15) * 4;
-      *reinterpret_cast<float4*>(out + r * DP_C + c4) = *reinterpret_cast<const float4*>(S1 + r * DP_LD + c4);
+      *reinterpret_cast<float4*>(out + r * DP_C + c4) = *reinterpret_cast<const float4*>(S1 + r * DP_LDB + c4);
     }
     if (tid == 0) p.gamma[cc.chunk] = vec.eg[DP_C - 1];
   }
@@ -278,24 +308,24 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_fwd_kernel(const Del
 #pragma unroll
   for (int e = 0; e < 16; ++e) {
     const int f = tid + DP_THREADS * e, i = f >> 6, j = f & 63;
-    const float t = Tm[i * DP_LD + j];
-    Lm[i * DP_LD + j] = t * vec.beta[j] * vec.eg[j];
-    Tu[i * DP_LD + j] = t * vec.beta[j];
+    const float t = Tm[i * DP_LDA + j];
+    Lm[i * DP_LDA + j] = t * vec.beta[j] * vec.eg[j];
+    Tu[i * DP_LDA + j] = t * vec.beta[j];
   }
   __syncthreads();
   const float* Tw = Lm;
   const int64_t row_stride = static_cast<int64_t>(p.H) * p.D;
   const int64_t elem0 = (cc.tok0 * p.H + cc.h) * p.D;
   for (int s = 0; s < p.D; s += DP_C) {
-    load_tokens(S0, p.k, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rk);
-    load_tokens(S1, p.q, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rq);
+    load_tokens(S0, DP_LDB, p.k, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rk);
+    load_tokens(S1, DP_LDB, p.q, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rq);
     __syncthreads();
     // kt = e^{G_last - G} k, q_in = e^G q (element-wise, in the loaders' layout)
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int f = tid + DP_THREADS * e, r = f >> 4, c4 = (f & 15) * 4;
-      const float4 kk = *reinterpret_cast<const float4*>(S0 + r * DP_LD + c4);
-      const float4 qq = *reinterpret_cast<const float4*>(S1 + r * DP_LD + c4);
+      const float4 kk = *reinterpret_cast<const float4*>(S0 + r * DP_LDB + c4);
+      const float4 qq = *reinterpret_cast<const float4*>(S1 + r * DP_LDB + c4);
       const float te = vec.to_end[r], eg = vec.eg[r];
       const int64_t at = (cc.chunk * DP_C + r) * p.D + s + c4;
       *reinterpret_cast<float4*>(p.kt + at) = make_float4(kk.x * te, kk.y * te, kk.z * te, kk.w * te);
@@ -303,25 +333,27 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_fwd_kernel(const Del
     }
     float acc[4][4];
     zero(acc);
-    mm_nn(acc, Tw, S0, ty, tx);
+    mm_nn(acc, Tw, S0, o);
 #pragma unroll
-    for (int a = 0; a < 4; ++a)
-      *reinterpret_cast<float4*>(p.w + (cc.chunk * DP_C + ty + 16 * a) * p.D + s + 4 * tx) =
-          make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
+    for (int t = 0; t < 4; ++t) {
+      *reinterpret_cast<float2*>(p.w + (cc.chunk * DP_C + o.r0) * p.D + s + o.col(t)) = make_float2(acc[t][0], acc[t][1]);
+      *reinterpret_cast<float2*>(p.w + (cc.chunk * DP_C + o.r1) * p.D + s + o.col(t)) = make_float2(acc[t][2], acc[t][3]);
+    }
     __syncthreads();
   }
   const int64_t vrow_stride = static_cast<int64_t>(p.H) * p.Dv;
   const int64_t velem0 = (cc.tok0 * p.H + cc.h) * p.Dv;
   for (int s = 0; s < p.Dv; s += DP_C) {
-    load_tokens(S0, p.v, p.in_bf16, velem0 + s, vrow_stride, cc.rows, nullptr);
+    load_tokens(S0, DP_LDB, p.v, p.in_bf16, velem0 + s, vrow_stride, cc.rows, nullptr);
     __syncthreads();
     float acc[4][4];
     zero(acc);
-    mm_nn(acc, Tu, S0, ty, tx);
+    mm_nn(acc, Tu, S0, o);
 #pragma unroll
-    for (int a = 0; a < 4; ++a)
-      *reinterpret_cast<float4*>(p.u + (cc.chunk * DP_C + ty + 16 * a) * p.Dv + s + 4 * tx) =
-          make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
+    for (int t = 0; t < 4; ++t) {
+      *reinterpret_cast<float2*>(p.u + (cc.chunk * DP_C + o.r0) * p.Dv + s + o.col(t)) = make_float2(acc[t][0], acc[t][1]);
+      *reinterpret_cast<float2*>(p.u + (cc.chunk * DP_C + o.r1) * p.Dv + s + o.col(t)) = make_float2(acc[t][2], acc[t][3]);
+    }
     __syncthreads();
   }
 }
@@ -329,31 +361,35 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_fwd_kernel(const Del
 // =====================================================================================================
 // backward
 // =====================================================================================================
+// pairs of partial row sums
+enum { PR_E = 0, PR_B = 1, PR_RK1 = 2, PR_RQ1 = 3, PR_RT1 = 4, PR_DOTQ = 5, PR_DOTK = 6, PR_VB = 7 };
+
 __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_bwd_kernel(const DeltaPrepParams p) {
   extern __shared__ __align__(16) float dp_smem[];
-  float* t0 = dp_smem;                   // L -> d_T -> M1 + M1^T
-  float* t1 = t0 + DP_TILE;              // T -> M2^T
-  float* t2 = t1 + DP_TILE;              // T^T
-  float* t3 = t2 + DP_TILE;              // T^T d_T -> M2
-  float* S0 = t3 + DP_TILE;
-  float* S1 = S0 + DP_TILE;
-  const DeltaVec vec(dp_smem + 6 * DP_TILE);
-  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  float* t0 = dp_smem;                   // L -> d_T (read column-wise) -> M1 + M1^T
+  float* t1 = t0 + DP_TILE_B;            // T -> M2^T
+  float* t2 = t1 + DP_TILE_A;            // T^T
+  float* t3 = t2 + DP_TILE_A;            // T^T d_T -> M2
+  float* S0 = t3 + DP_TILE_A;
+  float* S1 = S0 + DP_TILE_B;
+  const DeltaVec vec(S1 + DP_TILE_B);
+  const int tid = threadIdx.x;
+  const Own o;
   const ChunkCoord cc = chunk_coord(p);
   const int64_t row_stride = static_cast<int64_t>(p.H) * p.D, vrow_stride = static_cast<int64_t>(p.H) * p.Dv;
   const int64_t elem0 = (cc.tok0 * p.H + cc.h) * p.D, velem0 = (cc.tok0 * p.H + cc.h) * p.Dv;
 
   chunk_rows(p, cc, vec);
   float A[4][4], QK[4][4];
-  chunk_grams(p, cc, vec, S0, S1, A, QK, ty, tx);
+  chunk_grams(p, cc, vec, S0, S1, A, QK, o);
 #pragma unroll
-  for (int a = 0; a < 4; ++a)
+  for (int t = 0; t < 4; ++t)
 #pragma unroll
-    for (int b = 0; b < 4; ++b) {
-      const int i = ty + 16 * a, j = tx + 16 * b;
-      t0[i * DP_LD + j] = i > j ? vec.beta[i] * expf(vec.G[i] - vec.G[j]) * A[a][b] : 0.f;
+    for (int e = 0; e < 4; ++e) {
+      const int i = e < 2 ? o.r0 : o.r1, j = o.col(t) + (e & 1);
+      t0[i * DP_LDA + j] = i > j ? vec.beta[i] * expf(vec.G[i] - vec.G[j]) * A[t][e] : 0.f;
     }
-  if (tid < DP_C) { vec.v1[tid] = vec.beta[tid] * vec.eg[tid] * vec.rk[tid]; vec.v2[tid] = vec.beta[tid]; }
+  if (tid < DP_C) { vec.m0[tid] = vec.beta[tid] * vec.eg[tid] * vec.rk[tid]; vec.m1[tid] = vec.beta[tid]; }
   __syncthreads();
   chunk_inverse(t0, t1, t2);
   __syncthreads();
@@ -362,166 +398,174 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_bwd_kernel(const Del
   float acc[4][4];
   zero(acc);
   for (int s = 0; s < p.D; s += DP_C) {
-    load_chunk(S0, p.d_w + cc.chunk * DP_C * p.D + s, p.D, nullptr);
-    load_tokens(S1, p.k, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.v1);
+    load_chunk(S0, DP_LDA, p.d_w + cc.chunk * DP_C * p.D + s, p.D);
+    load_tokens(S1, DP_LDA, p.k, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.m0);
     __syncthreads();
-    mm_nt(acc, S0, S1, ty, tx);
+    mm_nt(acc, S0, S1, o);
     __syncthreads();
   }
   for (int s = 0; s < p.Dv; s += DP_C) {
-    load_chunk(S0, p.d_u + cc.chunk * DP_C * p.Dv + s, p.Dv, nullptr);
-    load_tokens(S1, p.v, p.in_bf16, velem0 + s, vrow_stride, cc.rows, vec.v2);
+    load_chunk(S0, DP_LDA, p.d_u + cc.chunk * DP_C * p.Dv + s, p.Dv);
+    load_tokens(S1, DP_LDA, p.v, p.in_bf16, velem0 + s, vrow_stride, cc.rows, vec.m1);
     __syncthreads();
-    mm_nt(acc, S0, S1, ty, tx);
+    mm_nt(acc, S0, S1, o);
     __syncthreads();
   }
 #pragma unroll
-  for (int a = 0; a < 4; ++a)
-#pragma unroll
-    for (int b = 0; b < 4; ++b) t0[(ty + 16 * a) * DP_LD + tx + 16 * b] = acc[a][b];
+  for (int t = 0; t < 4; ++t) {
+    *reinterpret_cast<float2*>(t0 + o.r0 * DP_LDB + o.col(t)) = make_float2(acc[t][0], acc[t][1]);
+    *reinterpret_cast<float2*>(t0 + o.r1 * DP_LDB + o.col(t)) = make_float2(acc[t][2], acc[t][3]);
+  }
   __syncthreads();
   // ---- d_L = -strict_lower(T^T d_T T^T)
   zero(acc);
-  mm_nn(acc, t2, t0, ty, tx);                                   // X1 = T^T d_T   (columns 4 tx + b)
+  mm_nn(acc, t2, t0, o);                                        // X1 = T^T d_T
 #pragma unroll
-  for (int a = 0; a < 4; ++a)
-    *reinterpret_cast<float4*>(t3 + (ty + 16 * a) * DP_LD + 4 * tx) = make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
+  for (int t = 0; t < 4; ++t) {
+    *reinterpret_cast<float2*>(t3 + o.r0 * DP_LDA + o.col(t)) = make_float2(acc[t][0], acc[t][1]);
+    *reinterpret_cast<float2*>(t3 + o.r1 * DP_LDA + o.col(t)) = make_float2(acc[t][2], acc[t][3]);
+  }
   __syncthreads();
   zero(acc);
-  mm_nt(acc, t3, t1, ty, tx);                                   // X1 T^T        (columns tx + 16 b)
+  mm_nt(acc, t3, t1, o);                                        // X1 T^T
   __syncthreads();                                              // t0 (d_T), t1 (T), t3 (X1) are free from here
   // ---- element-wise on the owned elements: M1 (+ its transpose) -> t0, M2 -> t3, M2^T -> t1; row / column sums
   {
     const float* dqk = p.d_qk + cc.chunk * DP_C * DP_C;
-    float e_col[4] = {0.f, 0.f, 0.f, 0.f};
+    float e_row[2] = {0.f, 0.f}, b_row[2] = {0.f, 0.f};
 #pragma unroll
-    for (int a = 0; a < 4; ++a) {
-      const int i = ty + 16 * a;
-      float e_row = 0.f, b_row = 0.f;
+    for (int t = 0; t < 4; ++t) {
+      float e_col[2] = {0.f, 0.f};
 #pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        const int j = tx + 16 * b;
+      for (int e = 0; e < 4; ++e) {
+        const int i = e < 2 ? o.r0 : o.r1, j = o.col(t) + (e & 1);
         const float dec = i >= j ? expf(vec.G[i] - vec.G[j]) : 0.f;
-        const float dl = i > j ? -acc[a][b] : 0.f;
+        const float dl = i > j ? -acc[t][e] : 0.f;
         const float m1 = dl * vec.beta[i] * dec;
         const float m2 = dqk[i * DP_C + j] * dec;
-        const float e = m1 * A[a][b] + m2 * QK[a][b];          // d_L L + M2 QK
-        e_row += e;
-        e_col[b] += e;
-        b_row += dl * dec * A[a][b];
-        if (i > j) { t0[i * DP_LD + j] = m1; t0[j * DP_LD + i] = m1; }
-        if (i == j) t0[i * DP_LD + j] = 0.f;
-        t3[i * DP_LD + j] = m2;
-        t1[j * DP_LD + i] = m2;
+        const float ee = m1 * A[t][e] + m2 * QK[t][e];         // d_L L + M2 QK
+        e_row[e >> 1] += ee;
+        e_col[e & 1] += ee;
+        b_row[e >> 1] += dl * dec * A[t][e];
+        if (i > j) { t0[i * DP_LDA + j] = m1; t0[j * DP_LDA + i] = m1; }
+        if (i == j) t0[i * DP_LDA + j] = 0.f;
+        t3[i * DP_LDA + j] = m2;
+        t1[j * DP_LDA + i] = m2;
       }
-      e_row = row_sum16(e_row);
-      b_row = row_sum16(b_row);
-      if (tx == 0) { vec.v3[i] = e_row; vec.v4[i] = b_row; }
-    }
-    // column sums of E: partials per ty in S0, then 64 threads add the 16 partials
+      // column sums of E over the warp's 16 rows -> S0[wr][j], added up by 64 threads below
 #pragma unroll
-    for (int b = 0; b < 4; ++b) S0[ty * DP_LD + tx + 16 * b] = e_col[b];
+      for (int h = 0; h < 2; ++h) {
+        float v = e_col[h];
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        v += __shfl_xor_sync(0xffffffffu, v, 8);
+        v += __shfl_xor_sync(0xffffffffu, v, 16);
+        if (o.g == 0) S0[o.wr * DP_LDB + o.col(t) + h] = v;
+      }
+    }
+    put_row_partials(vec.pair[PR_E], o, e_row[0], e_row[1]);
+    put_row_partials(vec.pair[PR_B], o, b_row[0], b_row[1]);
   }
   __syncthreads();
   if (tid < DP_C) {
     float s = 0.f;
-    for (int y = 0; y < 16; ++y) s += S0[y * DP_LD + tid];
-    vec.v3[tid] -= s;                                           // dG so far: row sum - column sum of E
+    for (int y = 0; y < 4; ++y) s += S0[y * DP_LDB + tid];
+    vec.m0[tid] = vec.total(PR_E, tid) - s;                     // dG so far: row sum - column sum of E
   }
   __syncthreads();
 
   // ---- per D slice: dq, dk (with respect to the normalised rows), kept in the outputs until the row dots are known
-  float rk1[4] = {0.f, 0.f, 0.f, 0.f}, rq1[4] = {0.f, 0.f, 0.f, 0.f}, rt1[4] = {0.f, 0.f, 0.f, 0.f};
-  float dotq[4] = {0.f, 0.f, 0.f, 0.f}, dotk[4] = {0.f, 0.f, 0.f, 0.f};
+  float rk1[2] = {0.f, 0.f}, rq1[2] = {0.f, 0.f}, rt1[2] = {0.f, 0.f}, dotq[2] = {0.f, 0.f}, dotk[2] = {0.f, 0.f};
   for (int s = 0; s < p.D; s += DP_C) {
-    load_tokens(S0, p.k, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rk);
-    load_tokens(S1, p.q, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rq);
+    load_tokens(S0, DP_LDB, p.k, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rk);
+    load_tokens(S1, DP_LDB, p.q, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rq);
     __syncthreads();
     float adq[4][4], adk[4][4];
     zero(adq);
     zero(adk);
-    mm_nn(adq, t3, S0, ty, tx);                                 // M2 k
-    mm_nn(adk, t0, S0, ty, tx);                                 // (M1 + M1^T) k
-    mm_nn(adk, t1, S1, ty, tx);                                 // M2^T q
+    mm_nn(adq, t3, S0, o);                                      // M2 k
+    mm_nn(adk, t0, S0, o);                                      // (M1 + M1^T) k
+    mm_nn(adk, t1, S1, o);                                      // M2^T q
 #pragma unroll
-    for (int a = 0; a < 4; ++a) {
-      const int i = ty + 16 * a;
-      const float4 dqi = *reinterpret_cast<const float4*>(p.d_qin + (cc.chunk * DP_C + i) * p.D + s + 4 * tx);
-      const float4 qq = *reinterpret_cast<const float4*>(S1 + i * DP_LD + 4 * tx);
-      const float eg = vec.eg[i];
-      adq[a][0] = fmaf(dqi.x, eg, adq[a][0]); adq[a][1] = fmaf(dqi.y, eg, adq[a][1]);
-      adq[a][2] = fmaf(dqi.z, eg, adq[a][2]); adq[a][3] = fmaf(dqi.w, eg, adq[a][3]);
-      rq1[a] += dqi.x * qq.x + dqi.y * qq.y + dqi.z * qq.z + dqi.w * qq.w;
-      dotq[a] += adq[a][0] * qq.x + adq[a][1] * qq.y + adq[a][2] * qq.z + adq[a][3] * qq.w;
-      if (i < cc.rows)
-        *reinterpret_cast<float4*>(p.dq + elem0 + i * row_stride + s + 4 * tx) = make_float4(adq[a][0], adq[a][1], adq[a][2], adq[a][3]);
-    }
+    for (int t = 0; t < 4; ++t)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int i = h ? o.r1 : o.r0, j = o.col(t);
+        const float2 dqi = *reinterpret_cast<const float2*>(p.d_qin + (cc.chunk * DP_C + i) * p.D + s + j);
+        const float2 qq = *reinterpret_cast<const float2*>(S1 + i * DP_LDB + j);
+        const float eg = vec.eg[i];
+        const float x0 = fmaf(dqi.x, eg, adq[t][2 * h]), x1 = fmaf(dqi.y, eg, adq[t][2 * h + 1]);
+        rq1[h] += dqi.x * qq.x + dqi.y * qq.y;
+        dotq[h] += x0 * qq.x + x1 * qq.y;
+        if (i < cc.rows) *reinterpret_cast<float2*>(p.dq + elem0 + i * row_stride + s + j) = make_float2(x0, x1);
+      }
     __syncthreads();
-    load_chunk(S1, p.d_w + cc.chunk * DP_C * p.D + s, p.D, nullptr);
+    load_chunk(S1, DP_LDB, p.d_w + cc.chunk * DP_C * p.D + s, p.D);
     __syncthreads();
     zero(adq);
-    mm_nn(adq, t2, S1, ty, tx);                                 // d_kbg = T^T d_w
+    mm_nn(adq, t2, S1, o);                                      // d_kbg = T^T d_w
 #pragma unroll
-    for (int a = 0; a < 4; ++a) {
-      const int i = ty + 16 * a;
-      const float4 dkt = *reinterpret_cast<const float4*>(p.d_kt + (cc.chunk * DP_C + i) * p.D + s + 4 * tx);
-      const float4 kk = *reinterpret_cast<const float4*>(S0 + i * DP_LD + 4 * tx);
-      const float be = vec.beta[i] * vec.eg[i], te = vec.to_end[i];
-      rk1[a] += adq[a][0] * kk.x + adq[a][1] * kk.y + adq[a][2] * kk.z + adq[a][3] * kk.w;
-      rt1[a] += dkt.x * kk.x + dkt.y * kk.y + dkt.z * kk.z + dkt.w * kk.w;
-      adk[a][0] += adq[a][0] * be + dkt.x * te; adk[a][1] += adq[a][1] * be + dkt.y * te;
-      adk[a][2] += adq[a][2] * be + dkt.z * te; adk[a][3] += adq[a][3] * be + dkt.w * te;
-      dotk[a] += adk[a][0] * kk.x + adk[a][1] * kk.y + adk[a][2] * kk.z + adk[a][3] * kk.w;
-      if (i < cc.rows)
-        *reinterpret_cast<float4*>(p.dk + elem0 + i * row_stride + s + 4 * tx) = make_float4(adk[a][0], adk[a][1], adk[a][2], adk[a][3]);
-    }
+    for (int t = 0; t < 4; ++t)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int i = h ? o.r1 : o.r0, j = o.col(t);
+        const float2 dkt = *reinterpret_cast<const float2*>(p.d_kt + (cc.chunk * DP_C + i) * p.D + s + j);
+        const float2 kk = *reinterpret_cast<const float2*>(S0 + i * DP_LDB + j);
+        const float be = vec.beta[i] * vec.eg[i], te = vec.to_end[i];
+        const float d0 = adq[t][2 * h], d1 = adq[t][2 * h + 1];
+        rk1[h] += d0 * kk.x + d1 * kk.y;
+        rt1[h] += dkt.x * kk.x + dkt.y * kk.y;
+        const float x0 = adk[t][2 * h] + d0 * be + dkt.x * te, x1 = adk[t][2 * h + 1] + d1 * be + dkt.y * te;
+        dotk[h] += x0 * kk.x + x1 * kk.y;
+        if (i < cc.rows) *reinterpret_cast<float2*>(p.dk + elem0 + i * row_stride + s + j) = make_float2(x0, x1);
+      }
     __syncthreads();
   }
   // ---- per Dv slice: dv = beta T^T d_u
-  float rvb[4] = {0.f, 0.f, 0.f, 0.f};
+  float rvb[2] = {0.f, 0.f};
   for (int s = 0; s < p.Dv; s += DP_C) {
-    load_chunk(S0, p.d_u + cc.chunk * DP_C * p.Dv + s, p.Dv, nullptr);
-    load_tokens(S1, p.v, p.in_bf16, velem0 + s, vrow_stride, cc.rows, nullptr);
+    load_chunk(S0, DP_LDB, p.d_u + cc.chunk * DP_C * p.Dv + s, p.Dv);
+    load_tokens(S1, DP_LDB, p.v, p.in_bf16, velem0 + s, vrow_stride, cc.rows, nullptr);
     __syncthreads();
     zero(acc);
-    mm_nn(acc, t2, S0, ty, tx);
+    mm_nn(acc, t2, S0, o);
 #pragma unroll
-    for (int a = 0; a < 4; ++a) {
-      const int i = ty + 16 * a;
-      const float4 vv = *reinterpret_cast<const float4*>(S1 + i * DP_LD + 4 * tx);
-      const float be = vec.beta[i];
-      rvb[a] += acc[a][0] * vv.x + acc[a][1] * vv.y + acc[a][2] * vv.z + acc[a][3] * vv.w;
-      if (i < cc.rows)
-        *reinterpret_cast<float4*>(p.dv + velem0 + i * vrow_stride + s + 4 * tx) =
-            make_float4(acc[a][0] * be, acc[a][1] * be, acc[a][2] * be, acc[a][3] * be);
-    }
+    for (int t = 0; t < 4; ++t)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int i = h ? o.r1 : o.r0, j = o.col(t);
+        const float2 vv = *reinterpret_cast<const float2*>(S1 + i * DP_LDB + j);
+        const float be = vec.beta[i];
+        rvb[h] += acc[t][2 * h] * vv.x + acc[t][2 * h + 1] * vv.y;
+        if (i < cc.rows)
+          *reinterpret_cast<float2*>(p.dv + velem0 + i * vrow_stride + s + j) = make_float2(acc[t][2 * h] * be, acc[t][2 * h + 1] * be);
+      }
     __syncthreads();
   }
-  // ---- row sums across the 16 threads of a row -> per-row vectors (v0: dot_q, v1: dot_k, v2: d_kt.k e^{..})
-#pragma unroll
-  for (int a = 0; a < 4; ++a) {
-    const int i = ty + 16 * a;
-    const float s_rk1 = row_sum16(rk1[a]), s_rq1 = row_sum16(rq1[a]), s_rt1 = row_sum16(rt1[a]);
-    const float s_dq = row_sum16(dotq[a]), s_dk = row_sum16(dotk[a]), s_vb = row_sum16(rvb[a]);
-    if (tx == 0) {
-      const float eg = vec.eg[i], r_kt = s_rt1 * vec.to_end[i];
-      vec.v0[i] = s_dq;
-      vec.v1[i] = s_dk;
-      vec.v2[i] = r_kt;
-      vec.v4[i] += eg * s_rk1 + s_vb;                                           // dbeta
-      vec.v3[i] += vec.beta[i] * eg * s_rk1 + eg * s_rq1 - r_kt;                // dG
-    }
+  put_row_partials(vec.pair[PR_RK1], o, rk1[0], rk1[1]);
+  put_row_partials(vec.pair[PR_RQ1], o, rq1[0], rq1[1]);
+  put_row_partials(vec.pair[PR_RT1], o, rt1[0], rt1[1]);
+  put_row_partials(vec.pair[PR_DOTQ], o, dotq[0], dotq[1]);
+  put_row_partials(vec.pair[PR_DOTK], o, dotk[0], dotk[1]);
+  put_row_partials(vec.pair[PR_VB], o, rvb[0], rvb[1]);
+  __syncthreads();
+  // ---- per-row results: dbeta, dG (m0), the d_kt term of every row (m1)
+  float dbeta_i = 0.f;
+  if (tid < DP_C) {
+    const float eg = vec.eg[tid], s_rk1 = vec.total(PR_RK1, tid);
+    const float r_kt = vec.total(PR_RT1, tid) * vec.to_end[tid];
+    dbeta_i = vec.total(PR_B, tid) + eg * s_rk1 + vec.total(PR_VB, tid);
+    vec.m0[tid] += vec.beta[tid] * eg * s_rk1 + eg * vec.total(PR_RQ1, tid) - r_kt;
+    vec.m1[tid] = r_kt;
   }
   __syncthreads();
   if (tid < DP_C) {
     // dG_last also collects every row's d_kt term and gamma's gradient; dg = reverse running sum of dG
-    float tail = p.d_gamma[cc.chunk] * vec.eg[DP_C - 1];
-    for (int j = 0; j < DP_C; ++j) tail += vec.v2[j];
-    float s = tail;
-    for (int j = DP_C - 1; j >= tid; --j) s += vec.v3[j];
+    float s = p.d_gamma[cc.chunk] * vec.eg[DP_C - 1];
+    for (int j = 0; j < DP_C; ++j) s += vec.m1[j];
+    for (int j = DP_C - 1; j >= tid; --j) s += vec.m0[j];
     if (tid < cc.rows) {
       const int64_t at = (cc.tok0 + tid) * p.H + cc.h;
-      p.dbeta[at] = vec.v4[tid];
+      p.dbeta[at] = dbeta_i;
       if (p.dg != nullptr) p.dg[at] = s;
     }
   }
@@ -537,7 +581,7 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_bwd_kernel(const Del
       const float4 qr = load4(p.q, at, p.in_bf16), kr = load4(p.k, at, p.in_bf16);
       float4 gq = *reinterpret_cast<const float4*>(p.dq + at), gk = *reinterpret_cast<const float4*>(p.dk + at);
       const float rq = vec.rq[r], rk = vec.rk[r];
-      const float cq = vec.v0[r] * inv_s2 * rq, ck = vec.v1[r] * k_on * rk;    // (dot / scale^2) * (q_s / q),  dot * (k_n / k)
+      const float cq = vec.total(PR_DOTQ, r) * inv_s2 * rq, ck = vec.total(PR_DOTK, r) * k_on * rk;
       gq = make_float4(rq * (gq.x - cq * qr.x), rq * (gq.y - cq * qr.y), rq * (gq.z - cq * qr.z), rq * (gq.w - cq * qr.w));
       gk = make_float4(rk * (gk.x - ck * kr.x), rk * (gk.y - ck * kr.y), rk * (gk.z - ck * kr.z), rk * (gk.w - ck * kr.w));
       *reinterpret_cast<float4*>(p.dq + at) = gq;

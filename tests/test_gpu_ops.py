@@ -327,8 +327,10 @@ def test_delta_prep_kernels_match_their_statement(D, Dv, gated, l2norm, dtype):
     dbl = lambda t: None if t is None else t.double()  # noqa: E731
     got = df._prep_fwd(q, k, v, beta, g, scale, l2norm)
     want = df._prep_fwd_torch(dbl(q), dbl(k), dbl(v), dbl(beta), dbl(g), scale, l2norm)
+    # the 64 x 64 x 64 products run with TF32 operands (10-bit mantissa): errors relative to the largest entry
     for a, b, name in zip(got, want, ("w", "u", "kt", "q_in", "qk", "gamma")):
-        torch.testing.assert_close(a.double(), b, rtol=1e-4, atol=1e-5, msg=lambda m, name=name: f"{name}: {m}")
+        tol = float(b.abs().max()) * (1e-5 if name in ("kt", "q_in", "gamma") else 2e-3)
+        torch.testing.assert_close(a.double(), b, rtol=0, atol=tol, msg=lambda m, name=name: f"{name}: {m}")
     gen = torch.Generator().manual_seed(7)
     grads = [torch.randn(o.shape, generator=gen).to(DEV) for o in got]
     got_b = df._prep_bwd(q, k, v, beta, g, scale, l2norm, *grads)
@@ -337,8 +339,9 @@ def test_delta_prep_kernels_match_their_statement(D, Dv, gated, l2norm, dtype):
         if b is None:
             assert a is None
             continue
-        tol = float(b.abs().max()) * 2e-5
-        torch.testing.assert_close(a.double(), b, rtol=1e-4, atol=tol, msg=lambda m, name=name: f"{name}: {m}")
+        tol = float(b.abs().max()) * 4e-3
+        torch.testing.assert_close(a.double(), b, rtol=0, atol=tol, msg=lambda m, name=name: f"{name}: {m}")
+        assert _cos(a, b) > 0.99999, (name, _cos(a, b))
 
 
 @pytest.mark.parametrize("gated,keep", [(True, "1"), (False, "0")])
