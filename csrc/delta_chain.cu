@@ -1,5 +1,6 @@
-// The chunk-to-chunk chain of the (gated) delta rule (sm_100a; plain fp32 FMA work, no tensor cores: the products are
-// 64 x D x 32 per chunk and column slice, the point of the kernel is to run the n dependent steps in ONE launch).
+// The chunk-to-chunk chain of the (gated) delta rule (sm_100a; the two products of a step, 64 x D x 32 each, run on the
+// tensor cores as TF32 mma.sync tiles with fp32 accumulation: they are far too small for a tcgen05 pipeline; the point
+// of the kernel is to run the n dependent steps in ONE launch with the state resident in registers).
 //
 // For one (batch, head) pair, S [D, Dv] the running state and i the chunk index:
 //
@@ -10,9 +11,9 @@
 //
 // (the role of chunk_gated_delta_rule_fwd_h / chunk_gated_delta_rule_bwd_dhu in fla/ops/common/chunk_delta_h.py).
 // The columns of S never mix, so a CTA owns 32 of them for the whole sequence: grid (Dv / 32, batch * heads).  Per
-// chunk the CTA stages a_i and b_i [64, D] in shared memory; thread (warp, lane) owns column `lane`, rows
-// warp + 8 r of y and rows warp * (D / 8) + r of S (kept in registers across chunks, mirrored in shared memory for
-// the other warps).  No waits on other CTAs or on asynchronous copies: nothing here can spin.
+// chunk the CTA stages a_i and b_i [64, D] in shared memory.  S [D, 32] lives in the accumulator registers of the
+// second product (D / 32 m16n8 tiles per warp) across chunks and is mirrored in shared memory as the B operand of the
+// first.  No waits on other CTAs or on asynchronous copies: nothing here can spin.
 #include "common.cuh"
 
 namespace ttcd {
@@ -20,6 +21,7 @@ namespace ttcd {
 constexpr int DC_C = 64;         // rows of a chunk
 constexpr int DC_COLS = 32;      // state columns per CTA
 constexpr int DC_THREADS = 256;  // 8 warps
+constexpr int DC_LDS = 40;       // row stride of the [*, 32] tiles read column-wise as B operands (8 banks apart)
 
 struct DeltaChainParams {
   const float* a; const float* b; const float* gamma; const float* x; const float* add; const float* s_init;
@@ -29,28 +31,54 @@ struct DeltaChainParams {
   int reverse;
 };
 
-template <int R>                 // R = D / 8: rows of S owned by one thread
+__device__ __forceinline__ uint32_t dc_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ void dc_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int D>
 __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChainParams p) {
-  constexpr int D = R * 8;
+  constexpr int LDA = D + 4;                 // a_i rows read as the A operand (rows 4 banks apart)
+  constexpr int LDB = D + 8;                 // b_i rows read as the A operand of b^T (rows 8 banks apart)
+  constexpr int TPW = D / 32;                // m16n8 tiles of S per warp: tile id = warp * TPW + x -> (id / 4, id % 4)
+  constexpr int NT = TPW >= 4 ? 4 : TPW;     // ... of which NT share an m-tile
+  constexpr int MT = TPW / NT;
   extern __shared__ __align__(16) float dc_smem[];
-  float* As = dc_smem;                       // [64][D]
-  float* Bs = As + DC_C * D;                 // [64][D]
-  float* Ss = Bs + DC_C * D;                 // [D][32]
-  float* Ys = Ss + D * DC_COLS;              // [64][32]
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* As = dc_smem;                       // [64][LDA]
+  float* Bs = As + DC_C * LDA;               // [64][LDB]
+  float* Ss = Bs + DC_C * LDB;               // [D][40]
+  float* Ys = Ss + D * DC_LDS;               // [64][40]   sign_b * y
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, c = lane & 3;
   const int col0 = blockIdx.x * DC_COLS;
   const int64_t bh = blockIdx.y;
   const int Dv = p.Dv;
   const float* a_base = p.a + bh * p.n * DC_C * D;
   const float* b_base = p.b + bh * p.n * DC_C * D;
-  const float* x_base = p.x + bh * p.n * DC_C * Dv + col0 + lane;
-  float* y_base = p.y + bh * p.n * DC_C * Dv + col0 + lane;
-  float* st_base = p.states + bh * p.n * D * Dv + col0 + lane;
-  const float* add_base = p.add != nullptr ? p.add + bh * p.n * D * Dv + col0 + lane : nullptr;
+  const float* x_base = p.x + bh * p.n * DC_C * Dv + col0;
+  float* y_base = p.y + bh * p.n * DC_C * Dv + col0;
+  float* st_base = p.states + bh * p.n * D * Dv + col0;
+  const float* add_base = p.add != nullptr ? p.add + bh * p.n * D * Dv + col0 : nullptr;
+  // the warp's tiles of S: m-tile mt0 + m (rows 16 (mt0 + m) + g, + 8), n-tiles nt0 .. nt0 + NT - 1 (columns 8 nt + 2 c, + 1)
+  const int mt0 = (warp * TPW) >> 2, nt0 = (warp * TPW) & 3;
+  // the warp's two tiles of y: m-tile warp / 2, n-tiles 2 (warp % 2), + 1
+  const int ymt = warp >> 1, ynt0 = 2 * (warp & 1);
 
-  float s[R];                                // S[warp * R + r][lane]
+  float s[MT][NT][4];
 #pragma unroll
-  for (int r = 0; r < R; ++r) s[r] = p.s_init[(bh * D + warp * R + r) * Dv + col0 + lane];
+  for (int m = 0; m < MT; ++m)
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      const int row = 16 * (mt0 + m) + g, col = 8 * (nt0 + t) + 2 * c;
+      const float2 lo = *reinterpret_cast<const float2*>(p.s_init + (bh * D + row) * Dv + col0 + col);
+      const float2 hi = *reinterpret_cast<const float2*>(p.s_init + (bh * D + row + 8) * Dv + col0 + col);
+      s[m][t][0] = lo.x; s[m][t][1] = lo.y; s[m][t][2] = hi.x; s[m][t][3] = hi.y;
+    }
 
   for (int step = 0; step < p.n; ++step) {
     const int i = p.reverse ? p.n - 1 - step : step;
@@ -58,71 +86,94 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChai
     const float4* ga = reinterpret_cast<const float4*>(a_base + static_cast<int64_t>(i) * DC_C * D);
     const float4* gb = reinterpret_cast<const float4*>(b_base + static_cast<int64_t>(i) * DC_C * D);
     for (int v = threadIdx.x; v < DC_C * D / 4; v += DC_THREADS) {
-      reinterpret_cast<float4*>(As)[v] = __ldg(ga + v);
-      reinterpret_cast<float4*>(Bs)[v] = __ldg(gb + v);
+      const int row = v / (D / 4), c4 = (v % (D / 4)) * 4;
+      *reinterpret_cast<float4*>(As + row * LDA + c4) = __ldg(ga + v);
+      *reinterpret_cast<float4*>(Bs + row * LDB + c4) = __ldg(gb + v);
     }
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      Ss[(warp * R + r) * DC_COLS + lane] = s[r];
-      st_base[(static_cast<int64_t>(i) * D + warp * R + r) * Dv] = s[r];
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        const int row = 16 * (mt0 + m) + g, col = 8 * (nt0 + t) + 2 * c;
+        const float2 lo = make_float2(s[m][t][0], s[m][t][1]), hi = make_float2(s[m][t][2], s[m][t][3]);
+        *reinterpret_cast<float2*>(Ss + row * DC_LDS + col) = lo;
+        *reinterpret_cast<float2*>(Ss + (row + 8) * DC_LDS + col) = hi;
+        *reinterpret_cast<float2*>(st_base + (static_cast<int64_t>(i) * D + row) * Dv + col) = lo;
+        *reinterpret_cast<float2*>(st_base + (static_cast<int64_t>(i) * D + row + 8) * Dv + col) = hi;
+      }
+    __syncthreads();
+    // ---- y = x + sign_a * (a S): the warp's two 16 x 8 tiles
+    {
+      float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      const float* arow = As + (16 * ymt + g) * LDA + c;
+#pragma unroll 4
+      for (int k0 = 0; k0 < D; k0 += 8) {
+        uint32_t a[4];
+        a[0] = dc_tf32(arow[k0]); a[1] = dc_tf32(arow[8 * LDA + k0]);
+        a[2] = dc_tf32(arow[k0 + 4]); a[3] = dc_tf32(arow[8 * LDA + k0 + 4]);
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          const float* sb = Ss + (k0 + c) * DC_LDS + 8 * (ynt0 + t) + g;
+          dc_mma(acc[t], a, dc_tf32(sb[0]), dc_tf32(sb[4 * DC_LDS]));
+        }
+      }
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int row = 16 * ymt + g + 8 * h, col = 8 * (ynt0 + t) + 2 * c;
+          const int64_t off = (static_cast<int64_t>(i) * DC_C + row) * Dv + col;
+          const float2 xv = *reinterpret_cast<const float2*>(x_base + off);
+          const float2 yv = make_float2(xv.x + p.sign_a * acc[t][2 * h], xv.y + p.sign_a * acc[t][2 * h + 1]);
+          *reinterpret_cast<float2*>(y_base + off) = yv;
+          *reinterpret_cast<float2*>(Ys + row * DC_LDS + col) = make_float2(p.sign_b * yv.x, p.sign_b * yv.y);
+        }
     }
     __syncthreads();
-    // ---- y rows warp + 8 q:  y = x + sign_a * (a S)
-    float acc[8];
-#pragma unroll
-    for (int q = 0; q < 8; ++q) acc[q] = 0.f;
-    for (int d = 0; d < D; d += 4) {
-      const float s0 = Ss[(d + 0) * DC_COLS + lane], s1 = Ss[(d + 1) * DC_COLS + lane];
-      const float s2 = Ss[(d + 2) * DC_COLS + lane], s3 = Ss[(d + 3) * DC_COLS + lane];
-#pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        const float4 av = *reinterpret_cast<const float4*>(As + (warp + 8 * q) * D + d);     // same address across the warp
-        acc[q] = fmaf(av.x, s0, fmaf(av.y, s1, fmaf(av.z, s2, fmaf(av.w, s3, acc[q]))));
-      }
-    }
-#pragma unroll
-    for (int q = 0; q < 8; ++q) {
-      const int c = warp + 8 * q;
-      const int64_t off = (static_cast<int64_t>(i) * DC_C + c) * Dv;
-      const float yv = x_base[off] + p.sign_a * acc[q];
-      y_base[off] = yv;
-      Ys[c * DC_COLS + lane] = yv;
-    }
-    __syncthreads();
-    // ---- S rows warp * R + r:  S = gamma S + add + sign_b * (b^T y)
-    float upd[R];
-#pragma unroll
-    for (int r = 0; r < R; ++r) upd[r] = 0.f;
-    for (int c = 0; c < DC_C; ++c) {
-      const float yv = Ys[c * DC_COLS + lane];
-      const float* brow = Bs + c * D + warp * R;
-#pragma unroll
-      for (int r = 0; r < R; r += 4) {
-        const float4 bv = *reinterpret_cast<const float4*>(brow + r);
-        upd[r] = fmaf(bv.x, yv, upd[r]);
-        upd[r + 1] = fmaf(bv.y, yv, upd[r + 1]);
-        upd[r + 2] = fmaf(bv.z, yv, upd[r + 2]);
-        upd[r + 3] = fmaf(bv.w, yv, upd[r + 3]);
-      }
-    }
+    // ---- S = gamma S + add + sign_b * (b^T y), accumulated in place
     const float gm = p.gamma[bh * p.n + i];
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      float v = gm * s[r] + p.sign_b * upd[r];
-      if (add_base != nullptr) v += add_base[(static_cast<int64_t>(i) * D + warp * R + r) * Dv];
-      s[r] = v;
+    for (int m = 0; m < MT; ++m) {
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        const int row = 16 * (mt0 + m) + g, col = 8 * (nt0 + t) + 2 * c;
+        float2 lo = make_float2(0.f, 0.f), hi = make_float2(0.f, 0.f);
+        if (add_base != nullptr) {
+          lo = *reinterpret_cast<const float2*>(add_base + (static_cast<int64_t>(i) * D + row) * Dv + col);
+          hi = *reinterpret_cast<const float2*>(add_base + (static_cast<int64_t>(i) * D + row + 8) * Dv + col);
+        }
+        s[m][t][0] = fmaf(gm, s[m][t][0], lo.x); s[m][t][1] = fmaf(gm, s[m][t][1], lo.y);
+        s[m][t][2] = fmaf(gm, s[m][t][2], hi.x); s[m][t][3] = fmaf(gm, s[m][t][3], hi.y);
+      }
+      const float* bcol = Bs + c * LDB + 16 * (mt0 + m) + g;             // b^T as the A operand: A[d][k] = b[k][d]
+#pragma unroll 4
+      for (int k0 = 0; k0 < DC_C; k0 += 8) {
+        uint32_t a[4];
+        a[0] = dc_tf32(bcol[k0 * LDB]); a[1] = dc_tf32(bcol[k0 * LDB + 8]);
+        a[2] = dc_tf32(bcol[(k0 + 4) * LDB]); a[3] = dc_tf32(bcol[(k0 + 4) * LDB + 8]);
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          const float* yb = Ys + (k0 + c) * DC_LDS + 8 * (nt0 + t) + g;
+          dc_mma(s[m][t], a, dc_tf32(yb[0]), dc_tf32(yb[4 * DC_LDS]));
+        }
+      }
     }
     __syncthreads();                           // As / Bs / Ss / Ys are rewritten by the next step
   }
 #pragma unroll
-  for (int r = 0; r < R; ++r) p.s_last[(bh * D + warp * R + r) * Dv + col0 + lane] = s[r];
+  for (int m = 0; m < MT; ++m)
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      const int row = 16 * (mt0 + m) + g, col = 8 * (nt0 + t) + 2 * c;
+      *reinterpret_cast<float2*>(p.s_last + (bh * D + row) * Dv + col0 + col) = make_float2(s[m][t][0], s[m][t][1]);
+      *reinterpret_cast<float2*>(p.s_last + (bh * D + row + 8) * Dv + col0 + col) = make_float2(s[m][t][2], s[m][t][3]);
+    }
 }
 
-template <int R>
+template <int D>
 static int launch_delta_chain(const DeltaChainParams& p, int BH, cudaStream_t stream) {
-  constexpr int D = R * 8;
-  constexpr int smem = (2 * DC_C * D + D * DC_COLS + DC_C * DC_COLS) * static_cast<int>(sizeof(float));
-  auto kern = delta_chain_kernel<R>;
+  constexpr int smem = (DC_C * (D + 4) + DC_C * (D + 8) + D * DC_LDS + DC_C * DC_LDS) * static_cast<int>(sizeof(float));
+  auto kern = delta_chain_kernel<D>;
   static bool configured = false;
   if (!configured) {
     TTCD_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -135,10 +186,10 @@ static int launch_delta_chain(const DeltaChainParams& p, int BH, cudaStream_t st
 static int delta_chain_dispatch(const DeltaChainParams& p, int BH, cudaStream_t stream) {
   if (BH <= 0 || p.n <= 0 || p.Dv <= 0 || p.Dv % DC_COLS != 0 || BH > 65535) return TTCD_ERR_ARG;
   switch (p.D) {
-    case 32: return launch_delta_chain<4>(p, BH, stream);
-    case 64: return launch_delta_chain<8>(p, BH, stream);
-    case 128: return launch_delta_chain<16>(p, BH, stream);
-    case 256: return launch_delta_chain<32>(p, BH, stream);
+    case 32: return launch_delta_chain<32>(p, BH, stream);
+    case 64: return launch_delta_chain<64>(p, BH, stream);
+    case 128: return launch_delta_chain<128>(p, BH, stream);
+    case 256: return launch_delta_chain<256>(p, BH, stream);
     default: return TTCD_ERR_ARG;
   }
 }

@@ -199,7 +199,9 @@ class _FusedDeltaRule(torch.autograd.Function):
         ctx.save_for_backward(q, k, v, g32, beta32, s0_32, *kept)
         ctx.scale, ctx.l2norm, ctx.has_kept = scale, l2norm, bool(kept)
         ctx.dtypes = (beta.dtype, None if g is None else g.dtype, None if s0 is None else s0.dtype)
-        return _from_chunks(o, B, T).to(q.dtype).contiguous(), final.view(B, H, D, Dv)
+        out = torch.empty(B, T, H, Dv, dtype=q.dtype, device=q.device)
+        out.copy_(_from_chunks(o, B, T))                            # one pass: layout change and cast
+        return out, final.view(B, H, D, Dv)
 
     @staticmethod
     def backward(ctx, d_o, d_final):
@@ -211,7 +213,12 @@ class _FusedDeltaRule(torch.autograd.Function):
         else:
             w, kt, q_in, qk, gamma, vn, states, _ = _stages_1_2(q, k, v, g32, beta32, s0_32, ctx.scale, ctx.l2norm)
         n = w.shape[1]
-        do_c = _flat(_to_chunks(d_o, n).contiguous()) if d_o is not None else _flat(torch.zeros_like(vn))
+        if d_o is None:
+            do_c = _flat(torch.zeros_like(vn))
+        else:                                                       # one pass: cast and layout change (rows beyond T: zero)
+            do_c = vn.new_empty(B, H, n * C, Dv) if n * C == T else vn.new_zeros(B, H, n * C, Dv)
+            do_c[:, :, :T].copy_(d_o.transpose(1, 2))
+            do_c = do_c.view(-1, C, Dv)
         d_final = torch.zeros_like(s0_32) if d_final is None else _f(d_final).reshape(B * H, D, Dv)
         with _tf32_matmuls(q.is_cuda):
             # output stage: o = q_in S + qk vn
@@ -223,7 +230,7 @@ class _FusedDeltaRule(torch.autograd.Function):
             # the chain, in reverse
             d_u, ds_next, d_s0 = dc._bwd(w, kt, gamma, d_vn, d_states, d_final)
             del d_vn, d_states
-            d_w = torch.bmm(_flat(d_u), _flat(states).transpose(1, 2)).neg_().view_as(w)
+            d_w = torch.baddbmm(d_u.new_zeros(1, 1, 1), _flat(d_u), _flat(states).transpose(1, 2), beta=0, alpha=-1).view_as(w)
             d_kt = torch.bmm(_flat(vn), _flat(ds_next).transpose(1, 2)).view_as(kt)
         # sum(states * ds_next) per chunk, in slices so that the product never exists at full size
         d_gamma = torch.cat([(a * b).sum(dim=(-1, -2)) for a, b in zip(states.split(8), ds_next.split(8))])
