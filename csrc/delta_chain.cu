@@ -29,6 +29,9 @@ struct DeltaChainParams {
   int n, D, Dv;
   float sign_a, sign_b;          // y = x + sign_a a S;  S = gamma S + add + sign_b b^T y
   int reverse;
+  // optional: per chunk, the sum over this CTA's columns of dot_with[i] * (S entering the step)  ->  dot_out[bh][i][blockIdx.x]
+  // (the reverse chain uses it for the gradient of gamma: dot_with = the forward states)
+  const float* dot_with; float* dot_out;
 };
 
 __device__ __forceinline__ uint32_t dc_tf32(float x) {
@@ -54,6 +57,7 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChai
   float* Bs = As + DC_C * LDA;               // [64][LDB]
   float* Ss = Bs + DC_C * LDB;               // [D][40]
   float* Ys = Ss + D * DC_LDS;               // [64][40]   sign_b * y
+  float* red = Ys + DC_C * DC_LDS;           // [8] per-warp partial sums of the optional dot product
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, c = lane & 3;
   const int col0 = blockIdx.x * DC_COLS;
   const int64_t bh = blockIdx.y;
@@ -64,6 +68,7 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChai
   float* y_base = p.y + bh * p.n * DC_C * Dv + col0;
   float* st_base = p.states + bh * p.n * D * Dv + col0;
   const float* add_base = p.add != nullptr ? p.add + bh * p.n * D * Dv + col0 : nullptr;
+  const float* dot_base = p.dot_with != nullptr ? p.dot_with + bh * p.n * D * Dv + col0 : nullptr;
   // the warp's tiles of S: m-tile mt0 + m (rows 16 (mt0 + m) + g, + 8), n-tiles nt0 .. nt0 + NT - 1 (columns 8 nt + 2 c, + 1)
   const int mt0 = (warp * TPW) >> 2, nt0 = (warp * TPW) & 3;
   // the warp's two tiles of y: m-tile warp / 2, n-tiles 2 (warp % 2), + 1
@@ -101,7 +106,28 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChai
         *reinterpret_cast<float2*>(st_base + (static_cast<int64_t>(i) * D + row) * Dv + col) = lo;
         *reinterpret_cast<float2*>(st_base + (static_cast<int64_t>(i) * D + row + 8) * Dv + col) = hi;
       }
+    if (dot_base != nullptr) {
+      float part = 0.f;
+#pragma unroll
+      for (int m = 0; m < MT; ++m)
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          const int row = 16 * (mt0 + m) + g, col = 8 * (nt0 + t) + 2 * c;
+          const float2 lo = *reinterpret_cast<const float2*>(dot_base + (static_cast<int64_t>(i) * D + row) * Dv + col);
+          const float2 hi = *reinterpret_cast<const float2*>(dot_base + (static_cast<int64_t>(i) * D + row + 8) * Dv + col);
+          part += s[m][t][0] * lo.x + s[m][t][1] * lo.y + s[m][t][2] * hi.x + s[m][t][3] * hi.y;
+        }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+      if (lane == 0) red[warp] = part;
+    }
     __syncthreads();
+    if (dot_base != nullptr && threadIdx.x == 0) {
+      float tot = 0.f;
+#pragma unroll
+      for (int wv = 0; wv < DC_THREADS / 32; ++wv) tot += red[wv];
+      p.dot_out[(bh * p.n + i) * gridDim.x + blockIdx.x] = tot;
+    }
     // ---- y = x + sign_a * (a S): the warp's two 16 x 8 tiles
     {
       float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -172,7 +198,7 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChai
 
 template <int D>
 static int launch_delta_chain(const DeltaChainParams& p, int BH, cudaStream_t stream) {
-  constexpr int smem = (DC_C * (D + 4) + DC_C * (D + 8) + D * DC_LDS + DC_C * DC_LDS) * static_cast<int>(sizeof(float));
+  constexpr int smem = (DC_C * (D + 4) + DC_C * (D + 8) + D * DC_LDS + DC_C * DC_LDS + 8) * static_cast<int>(sizeof(float));
   auto kern = delta_chain_kernel<D>;
   static bool configured = false;
   if (!configured) {
@@ -205,17 +231,22 @@ TTCD_EXPORT int ttcd_delta_chain_fwd(const float* w, const float* u, const float
   p.a = w; p.b = kt; p.gamma = gamma; p.x = u; p.add = nullptr; p.s_init = s0;
   p.y = vn; p.states = states; p.s_last = s_final;
   p.n = n; p.D = D; p.Dv = Dv; p.sign_a = -1.f; p.sign_b = 1.f; p.reverse = 0;
+  p.dot_with = nullptr; p.dot_out = nullptr;
   return ttcd::delta_chain_dispatch(p, BH, static_cast<cudaStream_t>(stream_ptr));
 }
 
 // Reverse chain: d_vn, d_states, d_final are the gradients arriving at vn, states and the final state; writes the total
-// gradient of vn (d_vn_tot), the gradient of the state LEAVING each chunk (ds_next [BH][n][D][Dv]) and of s0.
+// gradient of vn (d_vn_tot), the gradient of the state LEAVING each chunk (ds_next [BH][n][D][Dv]) and of s0.  With
+// `states` (the forward states) it also writes d_gamma_parts [BH][n][Dv / 32]: per chunk and 32-column slice, the sum of
+// states * ds_next (the gradient of the chunk's decay is their sum over the slices).
 TTCD_EXPORT int ttcd_delta_chain_bwd(const float* w, const float* kt, const float* gamma, const float* d_vn,
                                      const float* d_states, const float* d_final, float* d_vn_tot, float* ds_next,
-                                     float* d_s0, int BH, int n, int D, int Dv, void* stream_ptr) {
+                                     float* d_s0, const float* states, float* d_gamma_parts, int BH, int n, int D, int Dv,
+                                     void* stream_ptr) {
   ttcd::DeltaChainParams p;
   p.a = kt; p.b = w; p.gamma = gamma; p.x = d_vn; p.add = d_states; p.s_init = d_final;
   p.y = d_vn_tot; p.states = ds_next; p.s_last = d_s0;
   p.n = n; p.D = D; p.Dv = Dv; p.sign_a = 1.f; p.sign_b = -1.f; p.reverse = 1;
+  p.dot_with = d_gamma_parts != nullptr ? states : nullptr; p.dot_out = d_gamma_parts;
   return ttcd::delta_chain_dispatch(p, BH, static_cast<cudaStream_t>(stream_ptr));
 }

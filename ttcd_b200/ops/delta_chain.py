@@ -33,7 +33,7 @@ def _fwd_torch(w, u, kt, gamma, s0):
     return vn, states, S
 
 
-def _bwd_torch(w, kt, gamma, d_vn, d_states, d_final):
+def _bwd_torch(w, kt, gamma, d_vn, d_states, d_final, states=None):
     BH, n, C, D = w.shape
     dS = d_final.clone()
     d_vn_tot = torch.empty_like(d_vn)
@@ -42,7 +42,9 @@ def _bwd_torch(w, kt, gamma, d_vn, d_states, d_final):
         dS_next[:, i] = dS
         d_vn_tot[:, i] = d_vn[:, i] + kt[:, i] @ dS
         dS = gamma[:, i, None, None] * dS + d_states[:, i] - w[:, i].transpose(-1, -2) @ d_vn_tot[:, i]
-    return d_vn_tot, dS_next, dS
+    if states is None:
+        return d_vn_tot, dS_next, dS
+    return d_vn_tot, dS_next, dS, (states * dS_next).sum(dim=(-1, -2))
 
 
 def _native_ok(w, u) -> bool:
@@ -65,19 +67,24 @@ def _fwd(w, u, kt, gamma, s0):
     return vn, states, final
 
 
-def _bwd(w, kt, gamma, d_vn, d_states, d_final):
+def _bwd(w, kt, gamma, d_vn, d_states, d_final, states=None):
+    """The reverse chain; with ``states`` (the forward states) also the gradient of gamma, sum(states * dS_next) per chunk."""
     if not _native_ok(w, d_vn):
-        return _bwd_torch(w, kt, gamma, d_vn, d_states, d_final)
+        return _bwd_torch(w, kt, gamma, d_vn, d_states, d_final, states)
     BH, n, C, D = w.shape
     Dv = d_vn.shape[-1]
     w, kt, gamma, d_vn, d_states, d_final = (t.contiguous() for t in (w, kt, gamma, d_vn, d_states, d_final))
     d_vn_tot = torch.empty_like(d_vn)
     dS_next = torch.empty_like(d_states)
     d_s0 = torch.empty_like(d_final)
+    parts = None if states is None else torch.empty(BH, n, Dv // 32, dtype=torch.float32, device=w.device)
     # the reverse chain is the forward chain with the roles of w and kt exchanged (and transposed uses)
     nv.call("ttcd_delta_chain_bwd", nv.ptr(w), nv.ptr(kt), nv.ptr(gamma), nv.ptr(d_vn), nv.ptr(d_states), nv.ptr(d_final),
-            nv.ptr(d_vn_tot), nv.ptr(dS_next), nv.ptr(d_s0), nv.i32(BH), nv.i32(n), nv.i32(D), nv.i32(Dv), nv.stream_ptr())
-    return d_vn_tot, dS_next, d_s0
+            nv.ptr(d_vn_tot), nv.ptr(dS_next), nv.ptr(d_s0), nv.ptr(None if states is None else states.contiguous()),
+            nv.ptr(parts), nv.i32(BH), nv.i32(n), nv.i32(D), nv.i32(Dv), nv.stream_ptr())
+    if states is None:
+        return d_vn_tot, dS_next, d_s0
+    return d_vn_tot, dS_next, d_s0, parts.sum(-1)
 
 
 class _DeltaChain(torch.autograd.Function):
@@ -93,11 +100,10 @@ class _DeltaChain(torch.autograd.Function):
         zeros = lambda t, like: torch.zeros_like(like) if t is None else t  # noqa: E731
         d_vn, d_states = zeros(d_vn, vn), zeros(d_states, states)
         d_final = zeros(d_final, states[:, 0])
-        d_vn_tot, dS_next, d_s0 = _bwd(w, kt, gamma, d_vn, d_states, d_final)
+        d_vn_tot, dS_next, d_s0, d_gamma = _bwd(w, kt, gamma, d_vn, d_states, d_final, states)      # d_gamma [BH, n]
         d_u = d_vn_tot
         d_w = -(d_vn_tot @ states.transpose(-1, -2))                      # [BH, n, C, D]
         d_kt = vn @ dS_next.transpose(-1, -2)                             # [BH, n, C, D]
-        d_gamma = (states * dS_next).sum(dim=(-1, -2))                    # [BH, n]
         return d_w, d_u, d_kt, d_gamma, d_s0
 
 

@@ -19,6 +19,7 @@ stage (``_prep_fwd_torch`` / ``_prep_bwd_torch`` are also the oracle of the kern
 from __future__ import annotations
 
 import os
+import weakref
 
 import torch
 import torch.nn.functional as F
@@ -157,18 +158,39 @@ def _prep_bwd(q, k, v, beta, g, scale, l2norm, d_w, d_u, d_kt, d_qin, d_qk, d_ga
 
 
 # ------------------------------------------------------------------------------------------------ the op
-def _keep_intermediates(q: torch.Tensor, nbytes: int) -> bool:
-    """Keep the fp32 intermediates of a call for backward?  ``TTCD_DELTA_KEEP`` = 1 / 0 forces the answer; otherwise
-    they are kept while that leaves 60 % of the device memory free (blocks the allocator holds but does not use count
-    as free), so that a deep model keeps them on as many layers as fit and rebuilds them on the rest."""
+_KEEP_BUDGET = float(os.environ.get("TTCD_DELTA_KEEP_FRACTION", "0.2"))
+_kept_bytes = 0          # bytes of kept intermediates whose backward has not run yet
+
+
+def _release(nbytes: int) -> None:
+    global _kept_bytes
+    _kept_bytes -= nbytes
+
+
+def _keep_intermediates(ctx, q: torch.Tensor, nbytes: int) -> bool:
+    """Keep the fp32 intermediates of a call for backward?  ``TTCD_DELTA_KEEP`` = 1 / 0 forces the answer.  Otherwise
+    they are kept while all kept sets that still wait for their backward stay within a fifth of the device memory
+    (``TTCD_DELTA_KEEP_FRACTION``), so that a deep model keeps them on as many layers as that allows and rebuilds them
+    on the rest), and nothing is kept once the process has come within a fifth of the device memory at its peak: a model
+    whose other activations fill the device rebuilds everywhere from its second step on."""
+    global _kept_bytes
+    if not any(ctx.needs_input_grad):
+        return False
     mode = os.environ.get("TTCD_DELTA_KEEP", "auto")
     if mode in ("0", "1"):
         return mode == "1"
     if not q.is_cuda:
         return True
-    free, total = torch.cuda.mem_get_info(q.device)
-    free += torch.cuda.memory_reserved(q.device) - torch.cuda.memory_allocated(q.device)
-    return free - nbytes > 0.6 * total
+    total = torch.cuda.get_device_properties(q.device).total_memory
+    if _kept_bytes + nbytes > _KEEP_BUDGET * total:
+        return False
+    if torch.cuda.max_memory_allocated(q.device) + nbytes > 0.8 * total:      # an earlier step already came close to the limit
+        return False
+    if torch.cuda.memory_allocated(q.device) + nbytes > 0.5 * total:          # this step's forward is already that large
+        return False
+    _kept_bytes += nbytes
+    weakref.finalize(ctx, _release, nbytes)          # backward done or graph dropped: the set is gone either way
+    return True
 
 
 def _stages_1_2(q, k, v, g, beta, s0, scale, l2norm):
@@ -194,7 +216,7 @@ class _FusedDeltaRule(torch.autograd.Function):
         with _tf32_matmuls(q.is_cuda):
             o = torch.baddbmm(torch.bmm(_flat(q_in), _flat(states)), _flat(qk), _flat(vn)).view(B * H, -1, C, Dv)
         kept = (w, kt, q_in, qk, gamma, vn, states)
-        if not _keep_intermediates(q, sum(t.numel() * 4 for t in kept)):
+        if not _keep_intermediates(ctx, q, sum(t.numel() * 4 for t in kept)):
             kept = ()
         ctx.save_for_backward(q, k, v, g32, beta32, s0_32, *kept)
         ctx.scale, ctx.l2norm, ctx.has_kept = scale, l2norm, bool(kept)
@@ -228,12 +250,10 @@ class _FusedDeltaRule(torch.autograd.Function):
             d_states = torch.bmm(_flat(q_in).transpose(1, 2), do_c).view_as(states)
             del do_c
             # the chain, in reverse
-            d_u, ds_next, d_s0 = dc._bwd(w, kt, gamma, d_vn, d_states, d_final)
+            d_u, ds_next, d_s0, d_gamma = dc._bwd(w, kt, gamma, d_vn, d_states, d_final, states)
             del d_vn, d_states
             d_w = torch.baddbmm(d_u.new_zeros(1, 1, 1), _flat(d_u), _flat(states).transpose(1, 2), beta=0, alpha=-1).view_as(w)
             d_kt = torch.bmm(_flat(vn), _flat(ds_next).transpose(1, 2)).view_as(kt)
-        # sum(states * ds_next) per chunk, in slices so that the product never exists at full size
-        d_gamma = torch.cat([(a * b).sum(dim=(-1, -2)) for a, b in zip(states.split(8), ds_next.split(8))])
         del ds_next
         dq, dk, dv, dbeta, dg = _prep_bwd(q, k, v, beta32, g32, ctx.scale, ctx.l2norm, d_w, d_u, d_kt, d_qin, d_qk, d_gamma)
         beta_dtype, g_dtype, s0_dtype = ctx.dtypes
