@@ -590,6 +590,36 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_bwd_kernel(const Del
   }
 }
 
+// ---- layout changes between token rows [B, T, H, W] and chunk rows [B*H, n*64, W] (fp32), one 16-byte group per thread
+__global__ void __launch_bounds__(256) delta_rows_kernel(const void* src, void* dst, int T, int H, int n, int W, int64_t groups,
+                                                         int to_tokens, int token_bf16) {
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= groups) return;
+  const int wq = W / 4;
+  const int c4 = static_cast<int>(idx % wq) * 4;
+  const int64_t row = idx / wq;                                  // chunk row: (b * H + h) * n * 64 + t
+  const int t = static_cast<int>(row % (static_cast<int64_t>(n) * DP_C));
+  const int64_t bh = row / (static_cast<int64_t>(n) * DP_C);
+  const int64_t tok = ((bh / H) * T + t) * H + bh % H;           // token row: (b * T + t) * H + h
+  if (to_tokens) {
+    if (t >= T) return;
+    const float4 x = *reinterpret_cast<const float4*>(static_cast<const float*>(src) + row * W + c4);
+    if (token_bf16) {
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(x.x, x.y), hi = __floats2bfloat162_rn(x.z, x.w);
+      uint2 raw;
+      raw.x = *reinterpret_cast<const uint32_t*>(&lo);
+      raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(static_cast<bf16*>(dst) + tok * W + c4) = raw;
+    } else {
+      *reinterpret_cast<float4*>(static_cast<float*>(dst) + tok * W + c4) = x;
+    }
+  } else {
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (t < T) x = load4(src, tok * W + c4, token_bf16 != 0);
+    *reinterpret_cast<float4*>(static_cast<float*>(dst) + row * W + c4) = x;
+  }
+}
+
 static int delta_prep_check(const DeltaPrepParams& p, int BH) {
   if (BH <= 0 || BH > 65535 || p.T <= 0 || p.H <= 0 || BH % p.H != 0 || p.n != (p.T + DP_C - 1) / DP_C) return TTCD_ERR_ARG;
   if (p.D < DP_C || p.D % DP_C != 0 || p.Dv < DP_C || p.Dv % DP_C != 0) return TTCD_ERR_ARG;
@@ -641,5 +671,19 @@ TTCD_EXPORT int ttcd_delta_prep_bwd(const void* q, const void* k, const void* v,
     configured = true;
   }
   ttcd::delta_prep_bwd_kernel<<<dim3(p.n, B * H), ttcd::DP_THREADS, ttcd::DP_SMEM_BWD, static_cast<cudaStream_t>(stream_ptr)>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Chunk rows [B*H, n*64, W] fp32 -> token rows [B, T, H, W] (bf16 or fp32; rows beyond T are dropped), or the reverse
+// (rows beyond T zero).  W a multiple of 4; both buffers 16-byte aligned.
+TTCD_EXPORT int ttcd_delta_rows(const void* src, void* dst, int B, int T, int H, int W, int to_tokens, int token_bf16,
+                                void* stream_ptr) {
+  if (B <= 0 || T <= 0 || H <= 0 || W <= 0 || W % 4 != 0) return TTCD_ERR_ARG;
+  const int n = (T + ttcd::DP_C - 1) / ttcd::DP_C;
+  const int64_t groups = static_cast<int64_t>(B) * H * n * ttcd::DP_C * (W / 4);
+  const int64_t blocks = (groups + 255) / 256;
+  if (blocks > 0x7fffffffLL) return TTCD_ERR_SIZE;
+  ttcd::delta_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
+      src, dst, T, H, n, W, groups, to_tokens, token_bf16);
   return static_cast<int>(cudaGetLastError());
 }

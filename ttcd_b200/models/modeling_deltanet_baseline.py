@@ -13,7 +13,6 @@ import torch
 import torch.nn as nn
 
 from .. import ops
-from ..ops import reference as ref_ops
 from .base import DecoderForCausalLM, DecoderModel
 from .configuration import DeltaNetBaselineConfig
 from .layers import GatedMLP, RMSNorm
@@ -53,7 +52,7 @@ class DeltaNetBaselineBlock(nn.Module):
             k = ops.linear(dn_in, self.dn_k_proj.weight).view(shape)
             v = ops.linear(dn_in, self.dn_v_proj.weight).view(shape)
             beta = torch.sigmoid(torch.nn.functional.linear(dn_in, self.dn_b_proj.weight))
-            o = ref_ops.delta_rule_chunked(q, k, v, beta, cu_seqlens=kwargs.get("cu_seqlens"))
+            o, _ = ops.gated_delta_rule(q, k, v, None, beta, cu_seqlens=kwargs.get("cu_seqlens"))
             attn_out = ops.linear(o.reshape(b, t, -1), self.dn_o_proj.weight)
         hidden_states, residual = self.mlp_norm(attn_out, residual, True)
         return residual + self.mlp(hidden_states)

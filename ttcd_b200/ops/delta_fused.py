@@ -157,6 +157,34 @@ def _prep_bwd(q, k, v, beta, g, scale, l2norm, d_w, d_u, d_kt, d_qin, d_qk, d_ga
     return dq, dk, dv, dbeta, dg
 
 
+def _rows_to_tokens(x: torch.Tensor, B: int, T: int, dtype: torch.dtype) -> torch.Tensor:
+    """Chunk layout [B*H, n, 64, W] -> token layout [B, T, H, W] in ``dtype``: one pass (layout change and cast)."""
+    BH, n, _, W = x.shape
+    out = torch.empty(B, T, BH // B, W, dtype=dtype, device=x.device)
+    if x.is_cuda and nv.available() and nv.has("ttcd_delta_rows") and x.dtype == torch.float32 \
+            and dtype in (torch.bfloat16, torch.float32) and W % 4 == 0:
+        nv.call("ttcd_delta_rows", nv.ptr(x.contiguous()), nv.ptr(out), nv.i32(B), nv.i32(T), nv.i32(BH // B), nv.i32(W),
+                nv.i32(1), nv.i32(int(dtype == torch.bfloat16)), nv.stream_ptr())
+    else:
+        out.copy_(_from_chunks(x, B, T))
+    return out
+
+
+def _rows_to_chunks(x: torch.Tensor, n: int, dtype: torch.dtype) -> torch.Tensor:
+    """Token layout [B, T, H, W] -> chunk layout [B*H, n, 64, W] in ``dtype`` (fp32 on the GPU), rows beyond T zero."""
+    B, T, H, W = x.shape
+    if x.is_cuda and nv.available() and nv.has("ttcd_delta_rows") and dtype == torch.float32 \
+            and x.dtype in (torch.bfloat16, torch.float32) and W % 4 == 0:
+        x = _aligned(x)
+        out = torch.empty(B * H, n, C, W, dtype=dtype, device=x.device)
+        nv.call("ttcd_delta_rows", nv.ptr(x), nv.ptr(out), nv.i32(B), nv.i32(T), nv.i32(H), nv.i32(W), nv.i32(0),
+                nv.i32(int(x.dtype == torch.bfloat16)), nv.stream_ptr())
+        return out
+    out = x.new_zeros(B, H, n * C, W, dtype=dtype)
+    out[:, :, :T].copy_(x.transpose(1, 2))
+    return out.view(B * H, n, C, W)
+
+
 # ------------------------------------------------------------------------------------------------ the op
 _KEEP_BUDGET = float(os.environ.get("TTCD_DELTA_KEEP_FRACTION", "0.2"))
 _kept_bytes = 0          # bytes of kept intermediates whose backward has not run yet
@@ -221,9 +249,7 @@ class _FusedDeltaRule(torch.autograd.Function):
         ctx.save_for_backward(q, k, v, g32, beta32, s0_32, *kept)
         ctx.scale, ctx.l2norm, ctx.has_kept = scale, l2norm, bool(kept)
         ctx.dtypes = (beta.dtype, None if g is None else g.dtype, None if s0 is None else s0.dtype)
-        out = torch.empty(B, T, H, Dv, dtype=q.dtype, device=q.device)
-        out.copy_(_from_chunks(o, B, T))                            # one pass: layout change and cast
-        return out, final.view(B, H, D, Dv)
+        return _rows_to_tokens(o, B, T, q.dtype), final.view(B, H, D, Dv)
 
     @staticmethod
     def backward(ctx, d_o, d_final):
@@ -235,12 +261,7 @@ class _FusedDeltaRule(torch.autograd.Function):
         else:
             w, kt, q_in, qk, gamma, vn, states, _ = _stages_1_2(q, k, v, g32, beta32, s0_32, ctx.scale, ctx.l2norm)
         n = w.shape[1]
-        if d_o is None:
-            do_c = _flat(torch.zeros_like(vn))
-        else:                                                       # one pass: cast and layout change (rows beyond T: zero)
-            do_c = vn.new_empty(B, H, n * C, Dv) if n * C == T else vn.new_zeros(B, H, n * C, Dv)
-            do_c[:, :, :T].copy_(d_o.transpose(1, 2))
-            do_c = do_c.view(-1, C, Dv)
+        do_c = _flat(torch.zeros_like(vn)) if d_o is None else _flat(_rows_to_chunks(d_o, n, vn.dtype))
         d_final = torch.zeros_like(s0_32) if d_final is None else _f(d_final).reshape(B * H, D, Dv)
         with _tf32_matmuls(q.is_cuda):
             # output stage: o = q_in S + qk vn
