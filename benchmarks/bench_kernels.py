@@ -5,7 +5,7 @@ write) between timed iterations, and is reported with the achieved fraction of t
 in MEASURED_PEAKS.json (cuBLAS bf16 burst throughput and copy bandwidth).  Library baselines
 (cuBLAS via torch.matmul, flash-attn 2) are timed the same way when importable.
 
-    python benchmarks/bench_kernels.py [--what gemm,attn,conv,attn_bwd,misc,ref,ref_misc] [--seq 65536] [--batch 1]
+    python benchmarks/bench_kernels.py [--what gemm,attn,conv,attn_bwd,misc,delta,ref,ref_misc] [--seq 65536] [--batch 1]
 
 ``--what ref`` times the reference project's own kernels on this GPU next to this library's: its fused dual-window
 Triton kernel (profiling/fused_dual_attn.py:244-272), its LSE-combination variant on flash-attn 2
@@ -14,6 +14,11 @@ Triton kernel (profiling/fused_dual_attn.py:244-272), its LSE-combination varian
 (``TTCD_REFERENCE_ROOT``, a ``reference`` directory beside this repository, or ``baseline/_ref``).
 ``--what ref_misc`` does the same for its fla Triton add+RMSNorm, rotary, SwiGLU and fused linear-cross-entropy kernels
 (fla/modules/{layernorm,rotary,activations,fused_linear_cross_entropy}.py).
+``--what delta`` times the stages of the chunked delta rule (chunk-local kernels, chain kernels, the whole op forward +
+backward) at the 340M shapes of the two delta families, 4096-token sequences, ``--batch`` sequences (16 in the model
+benchmarks), beside the PyTorch statement of the rule and, when the reference checkout is importable, its Triton
+``chunk_delta_rule`` / ``chunk_gated_delta_rule`` (fla/ops/delta_rule/chunk.py, fla/ops/gated_delta_rule/chunk.py);
+``--what delta_stages`` times the kernels only (the small case for a profiler capture).
 """
 from __future__ import annotations
 
@@ -402,6 +407,71 @@ def bench_reference_misc():
     emit(**row)
 
 
+def bench_delta(batch: int, stages_only: bool = False):
+    """Stages of the chunked (gated) delta rule at the 340M shapes of the two families, T = 4096 per sequence."""
+    import os
+    from ttcd_b200 import ops
+    from ttcd_b200.ops import delta_chain as dc, delta_fused as df, reference as ref
+    T = 4096
+    for name, H, D, Dv, gated in (("delta_net_340M", 8, 128, 128, False), ("gated_deltanet_340M", 6, 256, 512, True)):
+        torch.manual_seed(0)
+        q, k = (torch.randn(batch, T, H, D, device="cuda").to(BF).requires_grad_() for _ in range(2))
+        v = torch.randn(batch, T, H, Dv, device="cuda").to(BF).requires_grad_()
+        beta = torch.rand(batch, T, H, device="cuda").requires_grad_()
+        g = (-torch.rand(batch, T, H, device="cuda") * 0.1).requires_grad_() if gated else None
+        leaves = [t for t in (q, k, v, g, beta) if t is not None]
+        scale = D ** -0.5
+        if not df.native_ok(q, v):
+            emit(bench="delta", model=name, error="kernels do not take this shape")
+            continue
+        row = dict(bench="delta_rule", model=name, shape=[batch, T, H, D, Dv], gated=gated)
+        with torch.no_grad():
+            qd, kd, vd, bd = q.detach(), k.detach(), v.detach(), beta.detach()
+            gd = None if g is None else g.detach()
+            w, u, kt, q_in, qk, gamma = df._prep_fwd(qd, kd, vd, bd, gd, scale, True)
+            s0 = torch.zeros(batch * H, D, Dv, device="cuda")
+            vn, states, _ = dc._fwd(w, u, kt, gamma, s0)
+            grads = [torch.randn_like(t) for t in (w, u, kt, q_in, qk, gamma)]
+            d_states = torch.randn_like(states) * 0.01
+            row["prep_fwd_ms"] = round(timeit(lambda: df._prep_fwd(qd, kd, vd, bd, gd, scale, True)), 4)
+            row["chain_fwd_ms"] = round(timeit(lambda: dc._fwd(w, u, kt, gamma, s0)), 4)
+            row["prep_bwd_ms"] = round(timeit(lambda: df._prep_bwd(qd, kd, vd, bd, gd, scale, True, *grads)), 4)
+            row["chain_bwd_ms"] = round(timeit(lambda: dc._bwd(w, kt, gamma, grads[1], d_states, s0, states)), 4)
+            del w, u, kt, q_in, qk, gamma, vn, states, grads, d_states
+        if stages_only:
+            emit(**row)
+            continue
+        go = torch.randn(batch, T, H, Dv, device="cuda").to(BF)
+
+        def whole(fn):
+            o = fn()
+            torch.autograd.grad(o, leaves, go)
+
+        row["op_fwd_bwd_ms"] = round(timeit(lambda: whole(lambda: ops.gated_delta_rule(q, k, v, g, beta)[0]), iters=5), 4)
+        try:
+            from torch.utils.checkpoint import checkpoint
+            row["pytorch_statement_fwd_bwd_ms"] = round(timeit(lambda: whole(lambda: checkpoint(
+                ref.gated_delta_rule_chunked, q, k, v, g, beta, None, True, 64, None, None, False, True, True,
+                use_reentrant=False)[0]), iters=3, warmup=1), 4)
+        except Exception as exc:
+            row["pytorch_statement_error"] = f"{type(exc).__name__}: {exc}"[:160]
+        torch.cuda.empty_cache()
+        if _reference_profiling() is not None:
+            try:
+                if gated:
+                    from fla.ops.gated_delta_rule import chunk_gated_delta_rule as fla_rule
+                    call = lambda: fla_rule(q, k, v, g, beta.to(BF), use_qk_l2norm_in_kernel=True)[0]  # noqa: E731
+                else:
+                    from fla.ops.delta_rule import chunk_delta_rule as fla_rule
+                    call = lambda: fla_rule(q, k, v, beta.to(BF), use_qk_l2norm_in_kernel=True)[0]  # noqa: E731
+                row["ref_triton_fwd_bwd_ms"] = round(timeit(lambda: whole(call), iters=5), 4)
+            except Exception as exc:
+                row["ref_triton_error"] = f"{type(exc).__name__}: {exc}"[:160]
+        emit(**row)
+        del q, k, v, beta, g, go, leaves
+        torch.cuda.empty_cache()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--what", default="gemm,attn,conv")
@@ -422,6 +492,8 @@ def main():
         bench_conv()
     if "misc" in what:
         bench_misc()
+    if "delta" in what or "delta_stages" in what:
+        bench_delta(batches[0], stages_only="delta" not in what)
     if "ref_misc" in what:
         bench_reference_misc()
     if "ref" in what:
