@@ -10,8 +10,9 @@
 //            a = kt, b = w, x = d_vn (from downstream), add = d_states (from downstream), y = total d_vn
 //
 // (the role of chunk_gated_delta_rule_fwd_h / chunk_gated_delta_rule_bwd_dhu in fla/ops/common/chunk_delta_h.py).
-// The columns of S never mix, so a CTA owns 32 of them for the whole sequence: grid (Dv / 32, batch * heads).  Per
-// chunk the CTA stages a_i and b_i [64, D] in shared memory.  S [D, 32] lives in the accumulator registers of the
+// The columns of S never mix, so a CTA owns 32 of them (64 for D = 256, where a_i and b_i are large and every column
+// slice re-reads them) for the whole sequence: grid (Dv / columns, batch * heads).  Per chunk the CTA stages a_i and
+// b_i [64, D] in shared memory with asynchronous 16-byte copies that overlap the publication of S.  S [D, 32] lives in the accumulator registers of the
 // second product (D / 32 m16n8 tiles per warp) across chunks and is mirrored in shared memory as the B operand of the
 // first.  No waits on other CTAs or on asynchronous copies: nothing here can spin.
 #include "common.cuh"
@@ -19,9 +20,7 @@
 namespace ttcd {
 
 constexpr int DC_C = 64;         // rows of a chunk
-constexpr int DC_COLS = 32;      // state columns per CTA
 constexpr int DC_THREADS = 256;  // 8 warps
-constexpr int DC_LDS = 40;       // row stride of the [*, 32] tiles read column-wise as B operands (8 banks apart)
 
 struct DeltaChainParams {
   const float* a; const float* b; const float* gamma; const float* x; const float* add; const float* s_init;
@@ -39,19 +38,28 @@ __device__ __forceinline__ uint32_t dc_tf32(float x) {
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
   return r;
 }
+__device__ __forceinline__ void dc_cp_async16(float* dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void dc_cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
 __device__ __forceinline__ void dc_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <int D>
+template <int D, int DC_COLS>
 __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChainParams p) {
   constexpr int LDA = D + 4;                 // a_i rows read as the A operand (rows 4 banks apart)
   constexpr int LDB = D + 8;                 // b_i rows read as the A operand of b^T (rows 8 banks apart)
-  constexpr int TPW = D / 32;                // m16n8 tiles of S per warp: tile id = warp * TPW + x -> (id / 4, id % 4)
-  constexpr int NT = TPW >= 4 ? 4 : TPW;     // ... of which NT share an m-tile
+  constexpr int DC_LDS = DC_COLS + 8;        // rows of the [*, columns] tiles read column-wise as B operands (8 banks apart)
+  constexpr int NTM = DC_COLS / 8;           // n-tiles per m-tile of S
+  constexpr int TPW = (D / 16) * NTM / 8;    // m16n8 tiles of S per warp: tile id = warp * TPW + x -> (id / NTM, id % NTM)
+  constexpr int NT = TPW >= NTM ? NTM : TPW; // ... of which NT share an m-tile
   constexpr int MT = TPW / NT;
+  constexpr int YT = DC_COLS / 16;           // n-tiles of y per warp
   extern __shared__ __align__(16) float dc_smem[];
   float* As = dc_smem;                       // [64][LDA]
   float* Bs = As + DC_C * LDA;               // [64][LDB]
@@ -70,9 +78,9 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChai
   const float* add_base = p.add != nullptr ? p.add + bh * p.n * D * Dv + col0 : nullptr;
   const float* dot_base = p.dot_with != nullptr ? p.dot_with + bh * p.n * D * Dv + col0 : nullptr;
   // the warp's tiles of S: m-tile mt0 + m (rows 16 (mt0 + m) + g, + 8), n-tiles nt0 .. nt0 + NT - 1 (columns 8 nt + 2 c, + 1)
-  const int mt0 = (warp * TPW) >> 2, nt0 = (warp * TPW) & 3;
-  // the warp's two tiles of y: m-tile warp / 2, n-tiles 2 (warp % 2), + 1
-  const int ymt = warp >> 1, ynt0 = 2 * (warp & 1);
+  const int mt0 = (warp * TPW) / NTM, nt0 = (warp * TPW) % NTM;
+  // the warp's YT tiles of y: m-tile warp / 2, n-tiles YT (warp % 2) ..
+  const int ymt = warp >> 1, ynt0 = YT * (warp & 1);
 
   float s[MT][NT][4];
 #pragma unroll
@@ -92,8 +100,8 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChai
     const float4* gb = reinterpret_cast<const float4*>(b_base + static_cast<int64_t>(i) * DC_C * D);
     for (int v = threadIdx.x; v < DC_C * D / 4; v += DC_THREADS) {
       const int row = v / (D / 4), c4 = (v % (D / 4)) * 4;
-      *reinterpret_cast<float4*>(As + row * LDA + c4) = __ldg(ga + v);
-      *reinterpret_cast<float4*>(Bs + row * LDB + c4) = __ldg(gb + v);
+      dc_cp_async16(As + row * LDA + c4, ga + v);
+      dc_cp_async16(Bs + row * LDB + c4, gb + v);
     }
 #pragma unroll
     for (int m = 0; m < MT; ++m)
@@ -101,8 +109,8 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChai
       for (int t = 0; t < NT; ++t) {
         const int row = 16 * (mt0 + m) + g, col = 8 * (nt0 + t) + 2 * c;
         const float2 lo = make_float2(s[m][t][0], s[m][t][1]), hi = make_float2(s[m][t][2], s[m][t][3]);
-        *reinterpret_cast<float2*>(Ss + row * DC_LDS + col) = lo;
-        *reinterpret_cast<float2*>(Ss + (row + 8) * DC_LDS + col) = hi;
+        *reinterpret_cast<uint2*>(Ss + row * DC_LDS + col) = make_uint2(dc_tf32(lo.x), dc_tf32(lo.y));      // B operand, rounded once
+        *reinterpret_cast<uint2*>(Ss + (row + 8) * DC_LDS + col) = make_uint2(dc_tf32(hi.x), dc_tf32(hi.y));
         *reinterpret_cast<float2*>(st_base + (static_cast<int64_t>(i) * D + row) * Dv + col) = lo;
         *reinterpret_cast<float2*>(st_base + (static_cast<int64_t>(i) * D + row + 8) * Dv + col) = hi;
       }
@@ -121,30 +129,34 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChai
       for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
       if (lane == 0) red[warp] = part;
     }
+    dc_cp_async_wait_all();
     __syncthreads();
     if (dot_base != nullptr && threadIdx.x == 0) {
       float tot = 0.f;
 #pragma unroll
       for (int wv = 0; wv < DC_THREADS / 32; ++wv) tot += red[wv];
-      p.dot_out[(bh * p.n + i) * gridDim.x + blockIdx.x] = tot;
+      p.dot_out[(bh * p.n + i) * (Dv / 32) + blockIdx.x] = tot;        // rows of Dv / 32 slots (zero-filled by the caller)
     }
-    // ---- y = x + sign_a * (a S): the warp's two 16 x 8 tiles
+    // ---- y = x + sign_a * (a S): the warp's YT 16 x 8 tiles
     {
-      float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      float acc[YT][4];
+#pragma unroll
+      for (int t = 0; t < YT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
       const float* arow = As + (16 * ymt + g) * LDA + c;
+      const uint32_t* sb0 = reinterpret_cast<const uint32_t*>(Ss) + c * DC_LDS + 8 * ynt0 + g;
 #pragma unroll 4
       for (int k0 = 0; k0 < D; k0 += 8) {
         uint32_t a[4];
         a[0] = dc_tf32(arow[k0]); a[1] = dc_tf32(arow[8 * LDA + k0]);
         a[2] = dc_tf32(arow[k0 + 4]); a[3] = dc_tf32(arow[8 * LDA + k0 + 4]);
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          const float* sb = Ss + (k0 + c) * DC_LDS + 8 * (ynt0 + t) + g;
-          dc_mma(acc[t], a, dc_tf32(sb[0]), dc_tf32(sb[4 * DC_LDS]));
+        for (int t = 0; t < YT; ++t) {
+          const uint32_t* sb = sb0 + k0 * DC_LDS + 8 * t;
+          dc_mma(acc[t], a, sb[0], sb[4 * DC_LDS]);
         }
       }
 #pragma unroll
-      for (int t = 0; t < 2; ++t)
+      for (int t = 0; t < YT; ++t)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int row = 16 * ymt + g + 8 * h, col = 8 * (ynt0 + t) + 2 * c;
@@ -152,7 +164,7 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChai
           const float2 xv = *reinterpret_cast<const float2*>(x_base + off);
           const float2 yv = make_float2(xv.x + p.sign_a * acc[t][2 * h], xv.y + p.sign_a * acc[t][2 * h + 1]);
           *reinterpret_cast<float2*>(y_base + off) = yv;
-          *reinterpret_cast<float2*>(Ys + row * DC_LDS + col) = make_float2(p.sign_b * yv.x, p.sign_b * yv.y);
+          *reinterpret_cast<uint2*>(Ys + row * DC_LDS + col) = make_uint2(dc_tf32(p.sign_b * yv.x), dc_tf32(p.sign_b * yv.y));
         }
     }
     __syncthreads();
@@ -179,8 +191,8 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChai
         a[2] = dc_tf32(bcol[(k0 + 4) * LDB]); a[3] = dc_tf32(bcol[(k0 + 4) * LDB + 8]);
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
-          const float* yb = Ys + (k0 + c) * DC_LDS + 8 * (nt0 + t) + g;
-          dc_mma(s[m][t], a, dc_tf32(yb[0]), dc_tf32(yb[4 * DC_LDS]));
+          const uint32_t* yb = reinterpret_cast<const uint32_t*>(Ys) + (k0 + c) * DC_LDS + 8 * (nt0 + t) + g;
+          dc_mma(s[m][t], a, yb[0], yb[4 * DC_LDS]);
         }
       }
     }
@@ -196,26 +208,26 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChai
     }
 }
 
-template <int D>
+template <int D, int COLS>
 static int launch_delta_chain(const DeltaChainParams& p, int BH, cudaStream_t stream) {
-  constexpr int smem = (DC_C * (D + 4) + DC_C * (D + 8) + D * DC_LDS + DC_C * DC_LDS + 8) * static_cast<int>(sizeof(float));
-  auto kern = delta_chain_kernel<D>;
+  constexpr int smem = (DC_C * (D + 4) + DC_C * (D + 8) + D * (COLS + 8) + DC_C * (COLS + 8) + 8) * static_cast<int>(sizeof(float));
+  auto kern = delta_chain_kernel<D, COLS>;
   static bool configured = false;
   if (!configured) {
     TTCD_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  kern<<<dim3(p.Dv / DC_COLS, BH), DC_THREADS, smem, stream>>>(p);
+  kern<<<dim3(p.Dv / COLS, BH), DC_THREADS, smem, stream>>>(p);
   return static_cast<int>(cudaGetLastError());
 }
 
 static int delta_chain_dispatch(const DeltaChainParams& p, int BH, cudaStream_t stream) {
-  if (BH <= 0 || p.n <= 0 || p.Dv <= 0 || p.Dv % DC_COLS != 0 || BH > 65535) return TTCD_ERR_ARG;
+  if (BH <= 0 || p.n <= 0 || p.Dv <= 0 || p.Dv % 32 != 0 || BH > 65535) return TTCD_ERR_ARG;
   switch (p.D) {
-    case 32: return launch_delta_chain<32>(p, BH, stream);
-    case 64: return launch_delta_chain<64>(p, BH, stream);
-    case 128: return launch_delta_chain<128>(p, BH, stream);
-    case 256: return launch_delta_chain<256>(p, BH, stream);
+    case 32: return launch_delta_chain<32, 32>(p, BH, stream);
+    case 64: return launch_delta_chain<64, 32>(p, BH, stream);
+    case 128: return launch_delta_chain<128, 32>(p, BH, stream);
+    case 256: return p.Dv % 64 == 0 ? launch_delta_chain<256, 64>(p, BH, stream) : launch_delta_chain<256, 32>(p, BH, stream);
     default: return TTCD_ERR_ARG;
   }
 }
@@ -237,8 +249,8 @@ TTCD_EXPORT int ttcd_delta_chain_fwd(const float* w, const float* u, const float
 
 // Reverse chain: d_vn, d_states, d_final are the gradients arriving at vn, states and the final state; writes the total
 // gradient of vn (d_vn_tot), the gradient of the state LEAVING each chunk (ds_next [BH][n][D][Dv]) and of s0.  With
-// `states` (the forward states) it also writes d_gamma_parts [BH][n][Dv / 32]: per chunk and 32-column slice, the sum of
-// states * ds_next (the gradient of the chunk's decay is their sum over the slices).
+// `states` (the forward states) it also writes d_gamma_parts [BH][n][Dv / 32] (zero-filled by the caller): per chunk and
+// column slice of a CTA, the sum of states * ds_next (the gradient of the chunk's decay is the sum over a row).
 TTCD_EXPORT int ttcd_delta_chain_bwd(const float* w, const float* kt, const float* gamma, const float* d_vn,
                                      const float* d_states, const float* d_final, float* d_vn_tot, float* ds_next,
                                      float* d_s0, const float* states, float* d_gamma_parts, int BH, int n, int D, int Dv,

@@ -77,7 +77,9 @@ __device__ __forceinline__ void load_a(uint32_t (&a)[4], const float* X, const O
   a[2] = tf32(X[o.r0 * DP_LDA + k0 + o.c + 4]);
   a[3] = tf32(X[o.r1 * DP_LDA + k0 + o.c + 4]);
 }
+// B operands that were rounded to TF32 when their tile was written (ROUNDED_B) are fed as they are.
 // acc += X Y^T:  acc(i, j) += sum_d X[i][d] Y[j][d]      (both tiles with row stride DP_LDA)
+template <bool ROUNDED_B>
 __device__ __forceinline__ void mm_nt(float (&acc)[4][4], const float* X, const float* Y, const Own& o) {
 #pragma unroll 2
   for (int k0 = 0; k0 < DP_C; k0 += 8) {
@@ -86,11 +88,13 @@ __device__ __forceinline__ void mm_nt(float (&acc)[4][4], const float* X, const 
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
       const float* y = Y + (32 * o.wc + 8 * t + o.g) * DP_LDA + k0 + o.c;
-      mma_tf32(acc[t], a, tf32(y[0]), tf32(y[4]));
+      if (ROUNDED_B) mma_tf32(acc[t], a, __float_as_uint(y[0]), __float_as_uint(y[4]));
+      else mma_tf32(acc[t], a, tf32(y[0]), tf32(y[4]));
     }
   }
 }
 // acc += M X:    acc(i, j) += sum_k M[i][k] X[k][j]      (M with row stride DP_LDA, X with DP_LDB)
+template <bool ROUNDED_B>
 __device__ __forceinline__ void mm_nn(float (&acc)[4][4], const float* M, const float* X, const Own& o) {
 #pragma unroll 2
   for (int k0 = 0; k0 < DP_C; k0 += 8) {
@@ -99,7 +103,8 @@ __device__ __forceinline__ void mm_nn(float (&acc)[4][4], const float* M, const 
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
       const float* x = X + (k0 + o.c) * DP_LDB + 32 * o.wc + 8 * t + o.g;
-      mma_tf32(acc[t], a, tf32(x[0]), tf32(x[4 * DP_LDB]));
+      if (ROUNDED_B) mma_tf32(acc[t], a, __float_as_uint(x[0]), __float_as_uint(x[4 * DP_LDB]));
+      else mma_tf32(acc[t], a, tf32(x[0]), tf32(x[4 * DP_LDB]));
     }
   }
 }
@@ -134,6 +139,11 @@ __device__ __forceinline__ float4 load4(const void* base, int64_t elem, bool bf)
   return *reinterpret_cast<const float4*>(static_cast<const float*>(base) + elem);
 }
 // token layout [.., T, H, width]: row r of the chunk is token t0 + r (zero beyond `rows`)
+__device__ __forceinline__ float4 round4(float4 x) {
+  return make_float4(__uint_as_float(tf32(x.x)), __uint_as_float(tf32(x.y)), __uint_as_float(tf32(x.z)), __uint_as_float(tf32(x.w)));
+}
+// ROUND: the tile is stored rounded to TF32 (it is only multiplied, as an operand of the products)
+template <bool ROUND>
 __device__ __forceinline__ void load_tokens(float* dst, int ld, const void* src, bool bf, int64_t elem0, int64_t row_stride,
                                             int rows, const float* mul) {
 #pragma unroll
@@ -142,15 +152,16 @@ __device__ __forceinline__ void load_tokens(float* dst, int ld, const void* src,
     float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
     if (r < rows) x = load4(src, elem0 + r * row_stride + c4, bf);
     const float m = mul != nullptr ? mul[r] : 1.f;
-    *reinterpret_cast<float4*>(dst + r * ld + c4) = make_float4(x.x * m, x.y * m, x.z * m, x.w * m);
+    x = make_float4(x.x * m, x.y * m, x.z * m, x.w * m);
+    *reinterpret_cast<float4*>(dst + r * ld + c4) = ROUND ? round4(x) : x;
   }
 }
-// chunk layout [.., 64, width] fp32 (all 64 rows exist)
+// chunk layout [.., 64, width] fp32 (all 64 rows exist), stored rounded to TF32
 __device__ __forceinline__ void load_chunk(float* dst, int ld, const float* src, int width) {
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
     const int f = threadIdx.x + DP_THREADS * e, r = f >> 4, c4 = (f & 15) * 4;
-    *reinterpret_cast<float4*>(dst + r * ld + c4) = *reinterpret_cast<const float4*>(src + static_cast<int64_t>(r) * width + c4);
+    *reinterpret_cast<float4*>(dst + r * ld + c4) = round4(*reinterpret_cast<const float4*>(src + static_cast<int64_t>(r) * width + c4));
   }
 }
 
@@ -226,11 +237,11 @@ __device__ __forceinline__ void chunk_grams(const DeltaPrepParams& p, const Chun
   const int64_t row_stride = static_cast<int64_t>(p.H) * p.D;
   const int64_t elem0 = (cc.tok0 * p.H + cc.h) * p.D;
   for (int s = 0; s < p.D; s += DP_C) {
-    load_tokens(S0, DP_LDA, p.k, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rk);
-    load_tokens(S1, DP_LDA, p.q, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rq);
+    load_tokens<true>(S0, DP_LDA, p.k, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rk);
+    load_tokens<true>(S1, DP_LDA, p.q, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rq);
     __syncthreads();
-    mm_nt(A, S0, S0, o);
-    mm_nt(QK, S1, S0, o);
+    mm_nt<true>(A, S0, S0, o);
+    mm_nt<true>(QK, S1, S0, o);
     __syncthreads();
   }
 }
@@ -317,8 +328,8 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_fwd_kernel(const Del
   const int64_t row_stride = static_cast<int64_t>(p.H) * p.D;
   const int64_t elem0 = (cc.tok0 * p.H + cc.h) * p.D;
   for (int s = 0; s < p.D; s += DP_C) {
-    load_tokens(S0, DP_LDB, p.k, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rk);
-    load_tokens(S1, DP_LDB, p.q, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rq);
+    load_tokens<false>(S0, DP_LDB, p.k, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rk);     // exact: kt, q_in are written from these
+    load_tokens<false>(S1, DP_LDB, p.q, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rq);
     __syncthreads();
     // kt = e^{G_last - G} k, q_in = e^G q (element-wise, in the loaders' layout)
 #pragma unroll
@@ -333,7 +344,7 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_fwd_kernel(const Del
     }
     float acc[4][4];
     zero(acc);
-    mm_nn(acc, Tw, S0, o);
+    mm_nn<false>(acc, Tw, S0, o);
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
       *reinterpret_cast<float2*>(p.w + (cc.chunk * DP_C + o.r0) * p.D + s + o.col(t)) = make_float2(acc[t][0], acc[t][1]);
@@ -344,11 +355,11 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_fwd_kernel(const Del
   const int64_t vrow_stride = static_cast<int64_t>(p.H) * p.Dv;
   const int64_t velem0 = (cc.tok0 * p.H + cc.h) * p.Dv;
   for (int s = 0; s < p.Dv; s += DP_C) {
-    load_tokens(S0, DP_LDB, p.v, p.in_bf16, velem0 + s, vrow_stride, cc.rows, nullptr);
+    load_tokens<true>(S0, DP_LDB, p.v, p.in_bf16, velem0 + s, vrow_stride, cc.rows, nullptr);
     __syncthreads();
     float acc[4][4];
     zero(acc);
-    mm_nn(acc, Tu, S0, o);
+    mm_nn<true>(acc, Tu, S0, o);
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
       *reinterpret_cast<float2*>(p.u + (cc.chunk * DP_C + o.r0) * p.Dv + s + o.col(t)) = make_float2(acc[t][0], acc[t][1]);
@@ -399,27 +410,27 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_bwd_kernel(const Del
   zero(acc);
   for (int s = 0; s < p.D; s += DP_C) {
     load_chunk(S0, DP_LDA, p.d_w + cc.chunk * DP_C * p.D + s, p.D);
-    load_tokens(S1, DP_LDA, p.k, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.m0);
+    load_tokens<true>(S1, DP_LDA, p.k, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.m0);
     __syncthreads();
-    mm_nt(acc, S0, S1, o);
+    mm_nt<true>(acc, S0, S1, o);
     __syncthreads();
   }
   for (int s = 0; s < p.Dv; s += DP_C) {
     load_chunk(S0, DP_LDA, p.d_u + cc.chunk * DP_C * p.Dv + s, p.Dv);
-    load_tokens(S1, DP_LDA, p.v, p.in_bf16, velem0 + s, vrow_stride, cc.rows, vec.m1);
+    load_tokens<true>(S1, DP_LDA, p.v, p.in_bf16, velem0 + s, vrow_stride, cc.rows, vec.m1);
     __syncthreads();
-    mm_nt(acc, S0, S1, o);
+    mm_nt<true>(acc, S0, S1, o);
     __syncthreads();
   }
 #pragma unroll
   for (int t = 0; t < 4; ++t) {
-    *reinterpret_cast<float2*>(t0 + o.r0 * DP_LDB + o.col(t)) = make_float2(acc[t][0], acc[t][1]);
-    *reinterpret_cast<float2*>(t0 + o.r1 * DP_LDB + o.col(t)) = make_float2(acc[t][2], acc[t][3]);
+    *reinterpret_cast<uint2*>(t0 + o.r0 * DP_LDB + o.col(t)) = make_uint2(tf32(acc[t][0]), tf32(acc[t][1]));     // B operand below
+    *reinterpret_cast<uint2*>(t0 + o.r1 * DP_LDB + o.col(t)) = make_uint2(tf32(acc[t][2]), tf32(acc[t][3]));
   }
   __syncthreads();
   // ---- d_L = -strict_lower(T^T d_T T^T)
   zero(acc);
-  mm_nn(acc, t2, t0, o);                                        // X1 = T^T d_T
+  mm_nn<true>(acc, t2, t0, o);                                  // X1 = T^T d_T
 #pragma unroll
   for (int t = 0; t < 4; ++t) {
     *reinterpret_cast<float2*>(t3 + o.r0 * DP_LDA + o.col(t)) = make_float2(acc[t][0], acc[t][1]);
@@ -427,7 +438,7 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_bwd_kernel(const Del
   }
   __syncthreads();
   zero(acc);
-  mm_nt(acc, t3, t1, o);                                        // X1 T^T
+  mm_nt<false>(acc, t3, t1, o);                                 // X1 T^T  (T is kept exact)
   __syncthreads();                                              // t0 (d_T), t1 (T), t3 (X1) are free from here
   // ---- element-wise on the owned elements: M1 (+ its transpose) -> t0, M2 -> t3, M2^T -> t1; row / column sums
   {
@@ -476,15 +487,15 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_bwd_kernel(const Del
   // ---- per D slice: dq, dk (with respect to the normalised rows), kept in the outputs until the row dots are known
   float rk1[2] = {0.f, 0.f}, rq1[2] = {0.f, 0.f}, rt1[2] = {0.f, 0.f}, dotq[2] = {0.f, 0.f}, dotk[2] = {0.f, 0.f};
   for (int s = 0; s < p.D; s += DP_C) {
-    load_tokens(S0, DP_LDB, p.k, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rk);
-    load_tokens(S1, DP_LDB, p.q, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rq);
+    load_tokens<true>(S0, DP_LDB, p.k, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rk);
+    load_tokens<true>(S1, DP_LDB, p.q, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rq);
     __syncthreads();
     float adq[4][4], adk[4][4];
     zero(adq);
     zero(adk);
-    mm_nn(adq, t3, S0, o);                                      // M2 k
-    mm_nn(adk, t0, S0, o);                                      // (M1 + M1^T) k
-    mm_nn(adk, t1, S1, o);                                      // M2^T q
+    mm_nn<true>(adq, t3, S0, o);                                // M2 k
+    mm_nn<true>(adk, t0, S0, o);                                // (M1 + M1^T) k
+    mm_nn<true>(adk, t1, S1, o);                                // M2^T q
 #pragma unroll
     for (int t = 0; t < 4; ++t)
 #pragma unroll
@@ -502,7 +513,7 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_bwd_kernel(const Del
     load_chunk(S1, DP_LDB, p.d_w + cc.chunk * DP_C * p.D + s, p.D);
     __syncthreads();
     zero(adq);
-    mm_nn(adq, t2, S1, o);                                      // d_kbg = T^T d_w
+    mm_nn<true>(adq, t2, S1, o);                                // d_kbg = T^T d_w
 #pragma unroll
     for (int t = 0; t < 4; ++t)
 #pragma unroll
@@ -524,10 +535,10 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_bwd_kernel(const Del
   float rvb[2] = {0.f, 0.f};
   for (int s = 0; s < p.Dv; s += DP_C) {
     load_chunk(S0, DP_LDB, p.d_u + cc.chunk * DP_C * p.Dv + s, p.Dv);
-    load_tokens(S1, DP_LDB, p.v, p.in_bf16, velem0 + s, vrow_stride, cc.rows, nullptr);
+    load_tokens<true>(S1, DP_LDB, p.v, p.in_bf16, velem0 + s, vrow_stride, cc.rows, nullptr);
     __syncthreads();
     zero(acc);
-    mm_nn(acc, t2, S0, o);
+    mm_nn<true>(acc, t2, S0, o);
 #pragma unroll
     for (int t = 0; t < 4; ++t)
 #pragma unroll

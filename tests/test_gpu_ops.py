@@ -277,7 +277,7 @@ def test_gemm_epilogue_row_statistics(rows, K, V):
     torch.testing.assert_close(lse, torch.logsumexp(out.float(), dim=-1), rtol=1e-5, atol=1e-4)
 
 
-@pytest.mark.parametrize("BH,n,D,Dv", [(3, 5, 32, 32), (2, 7, 128, 64), (2, 3, 256, 96), (5, 1, 64, 128)])
+@pytest.mark.parametrize("BH,n,D,Dv", [(3, 5, 32, 32), (2, 7, 128, 64), (2, 3, 256, 96), (5, 1, 64, 128), (2, 4, 256, 128)])
 def test_delta_chain_kernels_match_the_loop(BH, n, D, Dv):
     """The chunk-to-chunk chain of the delta rule (one launch per direction) against the same recurrence written as
     a PyTorch loop: corrected values, the state entering every chunk, the final state, and all five gradients."""

@@ -77,7 +77,7 @@ def _bwd(w, kt, gamma, d_vn, d_states, d_final, states=None):
     d_vn_tot = torch.empty_like(d_vn)
     dS_next = torch.empty_like(d_states)
     d_s0 = torch.empty_like(d_final)
-    parts = None if states is None else torch.empty(BH, n, Dv // 32, dtype=torch.float32, device=w.device)
+    parts = None if states is None else torch.zeros(BH, n, Dv // 32, dtype=torch.float32, device=w.device)
     # the reverse chain is the forward chain with the roles of w and kt exchanged (and transposed uses)
     nv.call("ttcd_delta_chain_bwd", nv.ptr(w), nv.ptr(kt), nv.ptr(gamma), nv.ptr(d_vn), nv.ptr(d_states), nv.ptr(d_final),
             nv.ptr(d_vn_tot), nv.ptr(dS_next), nv.ptr(d_s0), nv.ptr(None if states is None else states.contiguous()),
