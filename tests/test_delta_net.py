@@ -221,3 +221,41 @@ def test_fused_op_statement_matches_the_recurrence(gated, l2norm):
     for a, b, name in zip(twins, leaves, ("q", "k", "v", "g", "beta", "s0")):
         if a is not None:
             torch.testing.assert_close(a.grad, b.grad.double(), rtol=1e-3, atol=1e-4, msg=lambda m, name=name: f"d{name}: {m}")
+
+
+def test_kept_intermediates_stay_within_their_budget(monkeypatch):
+    """The keep-or-rebuild decision of the fused op: sets are kept while the ones still waiting for their backward fit the
+    budget, the count falls when a call's graph goes away, and a process that has already peaked near the device's
+    capacity keeps nothing."""
+    import gc
+    from ttcd_b200.ops import delta_fused as df
+
+    class Ctx:
+        needs_input_grad = (True,)
+
+    class FakeQ:
+        is_cuda, device = True, "cuda:0"
+
+    class Props:
+        total_memory = 1000
+
+    peak = {"v": 0}
+    monkeypatch.setattr(df.torch.cuda, "get_device_properties", lambda d: Props)
+    monkeypatch.setattr(df.torch.cuda, "max_memory_allocated", lambda d: peak["v"])
+    monkeypatch.setattr(df.torch.cuda, "memory_allocated", lambda d: 0)
+    monkeypatch.setattr(df, "_kept_bytes", 0)
+    monkeypatch.delenv("TTCD_DELTA_KEEP", raising=False)
+    a, b, c = Ctx(), Ctx(), Ctx()
+    assert df._keep_intermediates(a, FakeQ, 90) and df._keep_intermediates(b, FakeQ, 90)
+    assert not df._keep_intermediates(c, FakeQ, 90)            # 270 > a fifth of 1000
+    del a
+    gc.collect()
+    assert df._kept_bytes == 90 and df._keep_intermediates(c, FakeQ, 90)
+    peak["v"] = 750
+    assert not df._keep_intermediates(Ctx(), FakeQ, 60)         # 750 + 60 > 80 % of 1000
+    no_grad = Ctx()
+    no_grad.needs_input_grad = (False,)
+    peak["v"] = 0
+    assert not df._keep_intermediates(no_grad, FakeQ, 1)
+    monkeypatch.setenv("TTCD_DELTA_KEEP", "1")
+    assert df._keep_intermediates(Ctx(), FakeQ, 10_000)

@@ -250,11 +250,12 @@ def gated_delta_rule(q, k, v, g, beta, *, scale=None, l2norm: bool = True, cu_se
                      output_final_state: bool = False, recurrent: bool = False):
     """(Gated) delta rule over q, k [B,T,H,Dk], v [B,T,H,Dv], log decay g and write strength beta [B,T,H]; ``g`` None is
     the plain delta rule.  ``recurrent`` takes the token-by-token form (short decode steps), otherwise the chunked
-    form whose matrix products run as batched GEMMs.  Returns (o, final state or None).
+    form.  Returns (o, final state or None).
 
-    When gradients are needed the chunked form runs under activation recomputation: autograd keeps q, k, v, g, beta and
-    rebuilds the fp32 intermediates (per-chunk triangular factors, WY products, chunk states) in backward; kept, they
-    are several GB per layer at 64K tokens per step."""
+    On the GPU, for head sizes the kernels take, the chunked form is one op with a hand-written backward
+    (``ops/delta_fused.py``: chunk-local kernels, chain kernels, batched products; its fp32 intermediates are kept for
+    backward within a memory budget and rebuilt beyond it).  Elsewhere it is the PyTorch statement under activation
+    recomputation: autograd keeps q, k, v, g, beta and rebuilds the per-chunk factors and states in backward."""
     if recurrent and cu_seqlens is None:
         return reference.gated_delta_rule_recurrent(q, k, v, g, beta, scale, l2norm, initial_state, output_final_state)
     if _DELTA_FUSED and not _DELTA_CHUNK and delta_fused.native_ok(q, v):
