@@ -125,12 +125,21 @@ def test_hybrid_sharding_2x2_matches_one_process():
 # ------------------------------------------------------------------------------------- flags
 @pytest.mark.parametrize("flag", ["--training.enable_cpu_offload", "--optimizer.early_step_in_backward", "--training.compile",
                                   "--fault_tolerance.enable", "--float8.enable_fsdp_float8_all_gather",
-                                  "--memory_estimation.enabled", "--experimental.enable_compiled_autograd",
-                                  "--optimizer.use_distributed_muon"])
+                                  "--memory_estimation.enabled", "--experimental.enable_compiled_autograd"])
 def test_flags_without_machinery_are_refused(flag):
     with pytest.raises(NotImplementedError):
         JobConfig().parse_args([flag])
     JobConfig().parse_args([])          # the defaults parse
+
+
+def test_flag_for_another_schedule_of_the_same_update_is_accepted_with_a_note():
+    cfg = JobConfig()
+    cfg.parse_args(["--optimizer.use_distributed_muon"])
+    notes = cfg.equivalent_flag_notes()
+    assert len(notes) == 1 and "use_distributed_muon" in notes[0] and "owner" in notes[0]
+    plain = JobConfig()
+    plain.parse_args([])
+    assert plain.equivalent_flag_notes() == []
 
 
 # ------------------------------------------------------------------------------------- op-level recompute policy

@@ -240,10 +240,24 @@ class JobConfig:
         "float8.force_recompute_fp8_weight_in_bwd": "float8 training is not built",
         "float8.recipe_name": "float8 training is not built",
         "model.converters": "model converters (float8) are not built",
-        "optimizer.use_distributed_muon": "every Muon matrix is orthogonalised once, by its owner rank (the reference's "
-                                          "default 'parallel' mode); the all-gather-and-recompute-everywhere variant is not built "
-                                          "for data parallelism (tensor-parallel weight slices ARE gathered that way)",
     }
+
+    # Flags that pick, in the reference, another schedule of a computation this framework does one way; accepted (the
+    # result is the same), with a note for the log.
+    EQUIVALENT = {
+        "optimizer.use_distributed_muon": "every Muon matrix is orthogonalised once, by its owner rank, and the update is "
+                                          "published to the others (the reference's variant gathers the whole gradient on "
+                                          "every rank and repeats the Newton-Schulz iteration there: same update)",
+    }
+
+    def equivalent_flag_notes(self) -> list[str]:
+        """One line per accepted flag of ``EQUIVALENT`` that is set, for the trainer's start-up log."""
+        notes = []
+        for key, why in self.EQUIVALENT.items():
+            section, name = key.split(".", 1)
+            if getattr(getattr(self, section), name) not in (False, None, [], ""):
+                notes.append(f"--{key}: {why}")
+        return notes
 
     def _refuse_unsupported(self) -> None:
         for key, why in self.UNSUPPORTED.items():

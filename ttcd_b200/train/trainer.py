@@ -158,6 +158,8 @@ def main(job_config: JobConfig) -> None:
     tr = job_config.training
     if job_config.job.print_args and rank == 0:
         logger.info(json.dumps(job_config.to_dict(), indent=2, default=str))
+    for note in job_config.equivalent_flag_notes():
+        logger.info(f"accepted as equivalent: {note}")
     if job_config.experimental.pipeline_parallel_degree > 1:
         raise NotImplementedError("pipeline parallelism is not supported for these models")
     if job_config.experimental.custom_model_path:
