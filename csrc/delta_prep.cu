@@ -138,30 +138,65 @@ __device__ __forceinline__ float4 load4(const void* base, int64_t elem, bool bf)
   }
   return *reinterpret_cast<const float4*>(static_cast<const float*>(base) + elem);
 }
-// token layout [.., T, H, width]: row r of the chunk is token t0 + r (zero beyond `rows`)
+// A tile travels in two halves so that its global loads can be in flight while the previous tile is multiplied:
+// fetch_* issues the loads into registers, store_* (after the barrier that frees the shared-memory tile) converts,
+// scales and writes them.
+struct RawTile { uint4 w[4]; };
 __device__ __forceinline__ float4 round4(float4 x) {
   return make_float4(__uint_as_float(tf32(x.x)), __uint_as_float(tf32(x.y)), __uint_as_float(tf32(x.z)), __uint_as_float(tf32(x.w)));
 }
-// ROUND: the tile is stored rounded to TF32 (it is only multiplied, as an operand of the products)
-template <bool ROUND>
-__device__ __forceinline__ void load_tokens(float* dst, int ld, const void* src, bool bf, int64_t elem0, int64_t row_stride,
-                                            int rows, const float* mul) {
+// token layout [.., T, H, width]: row r of the chunk is token t0 + r (zero beyond `rows`)
+__device__ __forceinline__ void fetch_tokens(RawTile& t, const void* src, bool bf, int64_t elem0, int64_t row_stride, int rows) {
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
     const int f = threadIdx.x + DP_THREADS * e, r = f >> 4, c4 = (f & 15) * 4;
-    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (r < rows) x = load4(src, elem0 + r * row_stride + c4, bf);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < rows) {
+      if (bf) {
+        const uint2 h = *reinterpret_cast<const uint2*>(static_cast<const bf16*>(src) + elem0 + r * row_stride + c4);
+        v.x = h.x; v.y = h.y;
+      } else {
+        v = *reinterpret_cast<const uint4*>(static_cast<const float*>(src) + elem0 + r * row_stride + c4);
+      }
+    }
+    t.w[e] = v;
+  }
+}
+// ROUND: the tile is stored rounded to TF32 (it is only multiplied, as an operand of the products)
+template <bool ROUND>
+__device__ __forceinline__ void store_tokens(float* dst, int ld, const RawTile& t, bool bf, const float* mul) {
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const int f = threadIdx.x + DP_THREADS * e, r = f >> 4, c4 = (f & 15) * 4;
+    const uint4 v = t.w[e];
+    float4 x;
+    if (bf) {
+      const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&v.x);
+      const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&v.y);
+      x = make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+    } else {
+      x = make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
+    }
     const float m = mul != nullptr ? mul[r] : 1.f;
     x = make_float4(x.x * m, x.y * m, x.z * m, x.w * m);
     *reinterpret_cast<float4*>(dst + r * ld + c4) = ROUND ? round4(x) : x;
   }
 }
 // chunk layout [.., 64, width] fp32 (all 64 rows exist), stored rounded to TF32
-__device__ __forceinline__ void load_chunk(float* dst, int ld, const float* src, int width) {
+__device__ __forceinline__ void fetch_chunk(RawTile& t, const float* src, int width) {
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
     const int f = threadIdx.x + DP_THREADS * e, r = f >> 4, c4 = (f & 15) * 4;
-    *reinterpret_cast<float4*>(dst + r * ld + c4) = round4(*reinterpret_cast<const float4*>(src + static_cast<int64_t>(r) * width + c4));
+    t.w[e] = *reinterpret_cast<const uint4*>(src + static_cast<int64_t>(r) * width + c4);
+  }
+}
+__device__ __forceinline__ void store_chunk(float* dst, int ld, const RawTile& t) {
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const int f = threadIdx.x + DP_THREADS * e, r = f >> 4, c4 = (f & 15) * 4;
+    const uint4 v = t.w[e];
+    *reinterpret_cast<float4*>(dst + r * ld + c4) =
+        round4(make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w)));
   }
 }
 
@@ -236,10 +271,17 @@ __device__ __forceinline__ void chunk_grams(const DeltaPrepParams& p, const Chun
   zero(QK);
   const int64_t row_stride = static_cast<int64_t>(p.H) * p.D;
   const int64_t elem0 = (cc.tok0 * p.H + cc.h) * p.D;
+  RawTile rk, rq;
+  fetch_tokens(rk, p.k, p.in_bf16, elem0, row_stride, cc.rows);
+  fetch_tokens(rq, p.q, p.in_bf16, elem0, row_stride, cc.rows);
   for (int s = 0; s < p.D; s += DP_C) {
-    load_tokens<true>(S0, DP_LDA, p.k, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rk);
-    load_tokens<true>(S1, DP_LDA, p.q, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rq);
+    store_tokens<true>(S0, DP_LDA, rk, p.in_bf16, vec.rk);
+    store_tokens<true>(S1, DP_LDA, rq, p.in_bf16, vec.rq);
     __syncthreads();
+    if (s + DP_C < p.D) {
+      fetch_tokens(rk, p.k, p.in_bf16, elem0 + s + DP_C, row_stride, cc.rows);
+      fetch_tokens(rq, p.q, p.in_bf16, elem0 + s + DP_C, row_stride, cc.rows);
+    }
     mm_nt<true>(A, S0, S0, o);
     mm_nt<true>(QK, S1, S0, o);
     __syncthreads();
@@ -293,6 +335,11 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_fwd_kernel(const Del
   chunk_rows(p, cc, vec);
   float A[4][4], QK[4][4];
   chunk_grams(p, cc, vec, S0, S1, A, QK, o);
+  const int64_t row_stride = static_cast<int64_t>(p.H) * p.D, vrow_stride = static_cast<int64_t>(p.H) * p.Dv;
+  const int64_t elem0 = (cc.tok0 * p.H + cc.h) * p.D, velem0 = (cc.tok0 * p.H + cc.h) * p.Dv;
+  RawTile ra, rb;                        // the next tiles, in flight while the current ones are worked on
+  fetch_tokens(ra, p.k, p.in_bf16, elem0, row_stride, cc.rows);
+  fetch_tokens(rb, p.q, p.in_bf16, elem0, row_stride, cc.rows);
   // L (strictly lower) into shared memory, qk = lower(dec QK) into S1 for a coalesced copy out
 #pragma unroll
   for (int t = 0; t < 4; ++t)
@@ -325,12 +372,16 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_fwd_kernel(const Del
   }
   __syncthreads();
   const float* Tw = Lm;
-  const int64_t row_stride = static_cast<int64_t>(p.H) * p.D;
-  const int64_t elem0 = (cc.tok0 * p.H + cc.h) * p.D;
   for (int s = 0; s < p.D; s += DP_C) {
-    load_tokens<false>(S0, DP_LDB, p.k, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rk);     // exact: kt, q_in are written from these
-    load_tokens<false>(S1, DP_LDB, p.q, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rq);
+    store_tokens<false>(S0, DP_LDB, ra, p.in_bf16, vec.rk);     // exact: kt, q_in are written from these
+    store_tokens<false>(S1, DP_LDB, rb, p.in_bf16, vec.rq);
     __syncthreads();
+    if (s + DP_C < p.D) {
+      fetch_tokens(ra, p.k, p.in_bf16, elem0 + s + DP_C, row_stride, cc.rows);
+      fetch_tokens(rb, p.q, p.in_bf16, elem0 + s + DP_C, row_stride, cc.rows);
+    } else {
+      fetch_tokens(ra, p.v, p.in_bf16, velem0, vrow_stride, cc.rows);
+    }
     // kt = e^{G_last - G} k, q_in = e^G q (element-wise, in the loaders' layout)
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
@@ -352,11 +403,10 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_fwd_kernel(const Del
     }
     __syncthreads();
   }
-  const int64_t vrow_stride = static_cast<int64_t>(p.H) * p.Dv;
-  const int64_t velem0 = (cc.tok0 * p.H + cc.h) * p.Dv;
   for (int s = 0; s < p.Dv; s += DP_C) {
-    load_tokens<true>(S0, DP_LDB, p.v, p.in_bf16, velem0 + s, vrow_stride, cc.rows, nullptr);
+    store_tokens<true>(S0, DP_LDB, ra, p.in_bf16, nullptr);
     __syncthreads();
+    if (s + DP_C < p.Dv) fetch_tokens(ra, p.v, p.in_bf16, velem0 + s + DP_C, vrow_stride, cc.rows);
     float acc[4][4];
     zero(acc);
     mm_nn<true>(acc, Tu, S0, o);
@@ -401,6 +451,19 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_bwd_kernel(const Del
       t0[i * DP_LDA + j] = i > j ? vec.beta[i] * expf(vec.G[i] - vec.G[j]) * A[t][e] : 0.f;
     }
   if (tid < DP_C) { vec.m0[tid] = vec.beta[tid] * vec.eg[tid] * vec.rk[tid]; vec.m1[tid] = vec.beta[tid]; }
+  RawTile ra, rb;                        // the next tiles, in flight while the current ones are worked on
+  const int nd = p.D / DP_C, nv = p.Dv / DP_C;
+  // tile pair `it` of the d_T sum: (d_w, beta e^G k) slices first, then (d_u, beta v) slices
+  auto fetch_dT = [&](int it) {
+    if (it < nd) {
+      fetch_chunk(ra, p.d_w + cc.chunk * DP_C * p.D + it * DP_C, p.D);
+      fetch_tokens(rb, p.k, p.in_bf16, elem0 + it * DP_C, row_stride, cc.rows);
+    } else {
+      fetch_chunk(ra, p.d_u + cc.chunk * DP_C * p.Dv + (it - nd) * DP_C, p.Dv);
+      fetch_tokens(rb, p.v, p.in_bf16, velem0 + (it - nd) * DP_C, vrow_stride, cc.rows);
+    }
+  };
+  fetch_dT(0);
   __syncthreads();
   chunk_inverse(t0, t1, t2);
   __syncthreads();
@@ -408,17 +471,16 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_bwd_kernel(const Del
   // ---- d_T = d_w (beta e^G k)^T + d_u (beta v)^T
   float acc[4][4];
   zero(acc);
-  for (int s = 0; s < p.D; s += DP_C) {
-    load_chunk(S0, DP_LDA, p.d_w + cc.chunk * DP_C * p.D + s, p.D);
-    load_tokens<true>(S1, DP_LDA, p.k, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.m0);
+  for (int it = 0; it < nd + nv; ++it) {
+    store_chunk(S0, DP_LDA, ra);
+    store_tokens<true>(S1, DP_LDA, rb, p.in_bf16, it < nd ? vec.m0 : vec.m1);
     __syncthreads();
-    mm_nt<true>(acc, S0, S1, o);
-    __syncthreads();
-  }
-  for (int s = 0; s < p.Dv; s += DP_C) {
-    load_chunk(S0, DP_LDA, p.d_u + cc.chunk * DP_C * p.Dv + s, p.Dv);
-    load_tokens<true>(S1, DP_LDA, p.v, p.in_bf16, velem0 + s, vrow_stride, cc.rows, vec.m1);
-    __syncthreads();
+    if (it + 1 < nd + nv) {
+      fetch_dT(it + 1);
+    } else {                             // the first tiles of the dq / dk loop, in flight over the d_L phase
+      fetch_tokens(ra, p.k, p.in_bf16, elem0, row_stride, cc.rows);
+      fetch_tokens(rb, p.q, p.in_bf16, elem0, row_stride, cc.rows);
+    }
     mm_nt<true>(acc, S0, S1, o);
     __syncthreads();
   }
@@ -486,10 +548,12 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_bwd_kernel(const Del
 
   // ---- per D slice: dq, dk (with respect to the normalised rows), kept in the outputs until the row dots are known
   float rk1[2] = {0.f, 0.f}, rq1[2] = {0.f, 0.f}, rt1[2] = {0.f, 0.f}, dotq[2] = {0.f, 0.f}, dotk[2] = {0.f, 0.f};
+  RawTile rc;
   for (int s = 0; s < p.D; s += DP_C) {
-    load_tokens<true>(S0, DP_LDB, p.k, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rk);
-    load_tokens<true>(S1, DP_LDB, p.q, p.in_bf16, elem0 + s, row_stride, cc.rows, vec.rq);
+    store_tokens<true>(S0, DP_LDB, ra, p.in_bf16, vec.rk);
+    store_tokens<true>(S1, DP_LDB, rb, p.in_bf16, vec.rq);
     __syncthreads();
+    fetch_chunk(rc, p.d_w + cc.chunk * DP_C * p.D + s, p.D);     // needed after the first epilogue
     float adq[4][4], adk[4][4];
     zero(adq);
     zero(adk);
@@ -510,8 +574,15 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_bwd_kernel(const Del
         if (i < cc.rows) *reinterpret_cast<float2*>(p.dq + elem0 + i * row_stride + s + j) = make_float2(x0, x1);
       }
     __syncthreads();
-    load_chunk(S1, DP_LDB, p.d_w + cc.chunk * DP_C * p.D + s, p.D);
+    store_chunk(S1, DP_LDB, rc);
     __syncthreads();
+    if (s + DP_C < p.D) {
+      fetch_tokens(ra, p.k, p.in_bf16, elem0 + s + DP_C, row_stride, cc.rows);
+      fetch_tokens(rb, p.q, p.in_bf16, elem0 + s + DP_C, row_stride, cc.rows);
+    } else {                             // the first tiles of the dv loop
+      fetch_chunk(ra, p.d_u + cc.chunk * DP_C * p.Dv, p.Dv);
+      fetch_tokens(rb, p.v, p.in_bf16, velem0, vrow_stride, cc.rows);
+    }
     zero(adq);
     mm_nn<true>(adq, t2, S1, o);                                // d_kbg = T^T d_w
 #pragma unroll
@@ -534,9 +605,13 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_bwd_kernel(const Del
   // ---- per Dv slice: dv = beta T^T d_u
   float rvb[2] = {0.f, 0.f};
   for (int s = 0; s < p.Dv; s += DP_C) {
-    load_chunk(S0, DP_LDB, p.d_u + cc.chunk * DP_C * p.Dv + s, p.Dv);
-    load_tokens<true>(S1, DP_LDB, p.v, p.in_bf16, velem0 + s, vrow_stride, cc.rows, nullptr);
+    store_chunk(S0, DP_LDB, ra);
+    store_tokens<true>(S1, DP_LDB, rb, p.in_bf16, nullptr);
     __syncthreads();
+    if (s + DP_C < p.Dv) {
+      fetch_chunk(ra, p.d_u + cc.chunk * DP_C * p.Dv + s + DP_C, p.Dv);
+      fetch_tokens(rb, p.v, p.in_bf16, velem0 + s + DP_C, vrow_stride, cc.rows);
+    }
     zero(acc);
     mm_nn<true>(acc, t2, S0, o);
 #pragma unroll
