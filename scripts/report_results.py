@@ -1,5 +1,5 @@
-"""Tables (markdown on stdout, optional CSV) and, when matplotlib is installed, figures from the JSON files the
-evaluation and benchmark scripts write.  One sub-command per result kind:
+"""Tables (markdown on stdout, optional CSV) and figures (matplotlib when it is installed, plain SVG line charts
+otherwise) from the JSON files the evaluation and benchmark scripts write.  One sub-command per result kind:
 
     python scripts/report_results.py niah --inputs base=eval/niah_base.json ttcd=eval/niah_ttcd.json [--fig out.png]
     python scripts/report_results.py token-ppl --inputs base=eval/ppl_base.json ttcd=eval/ppl_ttcd.json [--fig out.png]
@@ -14,7 +14,7 @@ evaluation and benchmark scripts write.  One sub-command per result kind:
 * ``prefill``: median milliseconds per (model, mode, sequence length) of ``benchmarks/bench_prefill.py --out`` files
   (reference profiling/summarize.py:10-44).
 
-Figures are skipped with a note when matplotlib cannot be imported; the tables never need it.
+Without matplotlib a figure is written as ``<name>.svg`` by a small built-in SVG writer; the tables never need either.
 """
 from __future__ import annotations
 
@@ -42,7 +42,80 @@ def _table(header: list[str], rows: list[list]) -> str:
     return "\n".join(lines)
 
 
+class _SvgAxes:
+    """The few ``Axes`` calls the figures below make, drawn as a plain SVG file (line charts with markers, a legend,
+    linear or log-2 x axis): the fallback when matplotlib cannot be imported."""
+    COLORS = ["#1f77b4", "#d62728", "#2ca02c", "#ff7f0e", "#9467bd", "#8c564b", "#17becf", "#7f7f7f"]
+
+    def __init__(self):
+        self.series, self.xlog, self.xlabel, self.ylabel = [], False, "", ""
+
+    def plot(self, x, y, marker=None, label=None, **_):
+        pts = [(float(a), float(b)) for a, b in zip(x, y) if a is not None and b is not None]
+        self.series.append((pts, bool(marker), label or f"series {len(self.series) + 1}"))
+        return []
+
+    def set_xscale(self, kind, base=2, **_):
+        self.xlog = kind == "log"
+
+    def set_xlabel(self, text):
+        self.xlabel = text
+
+    def set_ylabel(self, text):
+        self.ylabel = text
+
+    def grid(self, *_, **__):
+        pass
+
+    def legend(self, *_, **__):
+        pass
+
+    def save(self, path: Path, width=800, height=450) -> None:
+        left, right, top, bottom = 70, 20, 20, 55
+        fx = (lambda v: math.log2(v)) if self.xlog else (lambda v: v)
+        pts = [(fx(a), b) for s_, _m, _l in self.series for a, b in s_ if not self.xlog or a > 0]
+        if not pts:
+            pts = [(0.0, 0.0), (1.0, 1.0)]
+        x0, x1 = min(p[0] for p in pts), max(p[0] for p in pts)
+        y0, y1 = min(p[1] for p in pts), max(p[1] for p in pts)
+        x1, y1 = (x1 if x1 > x0 else x0 + 1.0), (y1 if y1 > y0 else y0 + 1.0)
+        pad = 0.05 * (y1 - y0)
+        y0, y1 = y0 - pad, y1 + pad
+        sx = lambda v: left + (fx(v) - x0) / (x1 - x0) * (width - left - right)  # noqa: E731
+        sy = lambda v: height - bottom - (v - y0) / (y1 - y0) * (height - top - bottom)  # noqa: E731
+        out = [f'<svg xmlns="http://www.w3.org/2000/svg" width="{width}" height="{height}" font-family="sans-serif" font-size="12">',
+               f'<rect width="{width}" height="{height}" fill="white"/>']
+        for i in range(6):                                           # horizontal grid lines and y tick labels
+            v = y0 + (y1 - y0) * i / 5
+            out.append(f'<line x1="{left}" y1="{sy(v):.1f}" x2="{width - right}" y2="{sy(v):.1f}" stroke="#dddddd"/>')
+            out.append(f'<text x="{left - 6}" y="{sy(v) + 4:.1f}" text-anchor="end">{v:.3g}</text>')
+        ticks = sorted({a for s_, _m, _l in self.series for a, _b in s_}) if self.xlog else [x0 + (x1 - x0) * i / 5 for i in range(6)]
+        for v in ticks[:: max(1, len(ticks) // 10)]:
+            if self.xlog and v <= 0:
+                continue
+            out.append(f'<line x1="{sx(v):.1f}" y1="{top}" x2="{sx(v):.1f}" y2="{height - bottom}" stroke="#eeeeee"/>')
+            out.append(f'<text x="{sx(v):.1f}" y="{height - bottom + 16}" text-anchor="middle">{v:.6g}</text>')
+        out.append(f'<rect x="{left}" y="{top}" width="{width - left - right}" height="{height - top - bottom}" fill="none" stroke="black"/>')
+        for k, (series, marker, label) in enumerate(self.series):
+            color = self.COLORS[k % len(self.COLORS)]
+            series = [(a, b) for a, b in series if not self.xlog or a > 0]
+            if series:
+                path_pts = " ".join(f"{sx(a):.1f},{sy(b):.1f}" for a, b in series)
+                out.append(f'<polyline points="{path_pts}" fill="none" stroke="{color}" stroke-width="1.6"/>')
+                if marker:
+                    out += [f'<circle cx="{sx(a):.1f}" cy="{sy(b):.1f}" r="3" fill="{color}"/>' for a, b in series]
+            out.append(f'<rect x="{left + 10}" y="{top + 8 + 16 * k}" width="12" height="3" fill="{color}"/>')
+            out.append(f'<text x="{left + 28}" y="{top + 14 + 16 * k}">{label}</text>')
+        out.append(f'<text x="{(left + width - right) / 2:.0f}" y="{height - 12}" text-anchor="middle">{self.xlabel}</text>')
+        out.append(f'<text x="16" y="{(top + height - bottom) / 2:.0f}" text-anchor="middle" '
+                   f'transform="rotate(-90 16 {(top + height - bottom) / 2:.0f})">{self.ylabel}</text>')
+        out.append("</svg>")
+        path.parent.mkdir(parents=True, exist_ok=True)
+        path.write_text("\n".join(out))
+
+
 def _figure(path: str | None, draw) -> None:
+    """``draw(ax)`` into ``path`` with matplotlib, or, where it is not installed, as an SVG file beside it."""
     if not path:
         return
     try:
@@ -50,7 +123,11 @@ def _figure(path: str | None, draw) -> None:
         matplotlib.use("Agg")
         import matplotlib.pyplot as plt
     except ImportError:
-        print(f"(matplotlib is not installed: {path} not written)")
+        ax = _SvgAxes()
+        draw(ax)
+        target = Path(path).with_suffix(".svg")
+        ax.save(target)
+        print(f"(matplotlib is not installed: wrote {target} instead)")
         return
     fig, ax = plt.subplots(figsize=(8, 4.5), constrained_layout=True)
     draw(ax)

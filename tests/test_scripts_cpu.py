@@ -152,6 +152,18 @@ def test_final_block_eval_manifest_and_merges(tmp_path):
     assert "niah_single_1" in text and by_task["average"]["m"][4096] == 80.0
     rr.main(["final-block", "--input", str(tmp_path / "ab" / "fixed_final_block_doc_ppl.json")])
     rr.main(["token-ppl", "--inputs", f"x={tmp_path / 's.json'}"])
+    # figures: matplotlib where it is installed, else the built-in SVG writer (same name, .svg)
+    rr.main(["final-block", "--input", str(tmp_path / "ab" / "fixed_final_block_doc_ppl.json"), "--fig", str(tmp_path / "fig" / "ffb.png")])
+    written = list((tmp_path / "fig").glob("ffb.*"))
+    assert len(written) == 1
+    if written[0].suffix == ".svg":
+        svg = written[0].read_text()
+        assert svg.startswith("<svg") and svg.count("<polyline") == 2 and "perplexity of the final block" in svg
+    ax = rr._SvgAxes()
+    ax.plot([1024, 2048, 4096], [3.0, 2.5, 2.25], marker="o", label="m")
+    ax.set_xscale("log", base=2)
+    ax.save(tmp_path / "fig" / "direct.svg")
+    assert (tmp_path / "fig" / "direct.svg").read_text().count("<circle") == 3
 
 
 def test_verify_configs_reports_every_config():
