@@ -4,7 +4,7 @@ otherwise) from the JSON files the evaluation and benchmark scripts write.  One 
     python scripts/report_results.py niah --inputs base=eval/niah_base.json ttcd=eval/niah_ttcd.json [--fig out.png]
     python scripts/report_results.py token-ppl --inputs base=eval/ppl_base.json ttcd=eval/ppl_ttcd.json [--fig out.png]
     python scripts/report_results.py final-block --input eval/ffb_all/fixed_final_block_doc_ppl.json [--fig out.png]
-    python scripts/report_results.py prefill --inputs 'results/*.json'
+    python scripts/report_results.py prefill --inputs 'results/*.json' [--fig out.png]
 
 * ``niah``: accuracy per task and context length of ``eval_ruler.py`` / ``eval_niah.py`` outputs, one block per task
   with one row per model (the figure of the reference's scripts/plot_niah.py as a table).
@@ -12,7 +12,7 @@ otherwise) from the JSON files the evaluation and benchmark scripts write.  One 
   (reference scripts/plot_token_ppl.py plots the same curves).
 * ``final-block``: perplexity of the fixed final block per context length and model.
 * ``prefill``: median milliseconds per (model, mode, sequence length) of ``benchmarks/bench_prefill.py --out`` files
-  (reference profiling/summarize.py:10-44).
+  (reference profiling/summarize.py:10-44; the figure is the role of its profiling/plot_sweep.py / plot_bsz.py curves).
 
 Without matplotlib a figure is written as ``<name>.svg`` by a small built-in SVG writer; the tables never need either.
 """
@@ -174,6 +174,7 @@ def main(argv=None):
     p.add_argument("--input", required=True)
     p.add_argument("--fig", default=None)
     p = sub.add_parser("prefill")
+    p.add_argument("--fig", default=None)
     p.add_argument("--inputs", nargs="+", required=True, help="files or globs written by bench_prefill.py --out")
     args = ap.parse_args(argv)
 
@@ -236,6 +237,15 @@ def main(argv=None):
             print(f"\n**{mode}** (median ms)\n")
             print(_table(["model"] + [f"L={L}" for L in lens],
                          [[label] + [v.get(L) for L in lens] for (m, label), v in sorted(cells.items()) if m == mode]))
+
+        def draw(ax):            # one curve per (mode, model): median ms against the prompt length
+            for (mode, label), v in sorted(cells.items()):
+                xs = sorted(v)
+                ax.plot(xs, [v[L] for L in xs], marker="o", label=f"{label} / {mode}")
+            ax.set_xscale("log", base=2)
+            ax.set_xlabel("prompt length")
+            ax.set_ylabel("median ms")
+        _figure(getattr(args, "fig", None), draw)
 
 
 if __name__ == "__main__":
