@@ -223,10 +223,10 @@ def test_fused_op_statement_matches_the_recurrence(gated, l2norm):
             torch.testing.assert_close(a.grad, b.grad.double(), rtol=1e-3, atol=1e-4, msg=lambda m, name=name: f"d{name}: {m}")
 
 
-def test_kept_intermediates_stay_within_their_budget(monkeypatch):
-    """The keep-or-rebuild decision of the fused op: sets are kept while the ones still waiting for their backward fit the
-    budget, the count falls when a call's graph goes away, and a process that has already peaked near the device's
-    capacity keeps nothing."""
+def test_kept_intermediates_stay_within_their_share_of_memory(monkeypatch):
+    """The keep-or-rebuild decision of the fused op: sets are kept while the ones still waiting for their backward fit
+    the allowed share of the device memory, the count falls when a call's graph goes away, and a process that has
+    already peaked near the device's capacity keeps nothing."""
     import gc
     from ttcd_b200.ops import delta_fused as df
 

@@ -186,7 +186,7 @@ def _rows_to_chunks(x: torch.Tensor, n: int, dtype: torch.dtype) -> torch.Tensor
 
 
 # ------------------------------------------------------------------------------------------------ the op
-_KEEP_BUDGET = float(os.environ.get("TTCD_DELTA_KEEP_FRACTION", "0.2"))
+_KEEP_FRACTION = float(os.environ.get("TTCD_DELTA_KEEP_FRACTION", "0.2"))
 _kept_bytes = 0          # bytes of kept intermediates whose backward has not run yet
 
 
@@ -210,7 +210,7 @@ def _keep_intermediates(ctx, q: torch.Tensor, nbytes: int) -> bool:
     if not q.is_cuda:
         return True
     total = torch.cuda.get_device_properties(q.device).total_memory
-    if _kept_bytes + nbytes > _KEEP_BUDGET * total:
+    if _kept_bytes + nbytes > _KEEP_FRACTION * total:
         return False
     if torch.cuda.max_memory_allocated(q.device) + nbytes > 0.8 * total:      # an earlier step already came close to the limit
         return False
