@@ -23,7 +23,8 @@ constexpr int DC_C = 64;         // rows of a chunk
 constexpr int DC_THREADS = 256;  // 8 warps
 
 struct DeltaChainParams {
-  const float* a; const float* b; const float* gamma; const float* x; const float* add; const float* s_init;
+  const bf16* a; const bf16* b;   // bf16: exact TF32 operands after a 16-bit shift, half the staging traffic
+  const float* gamma; const float* x; const float* add; const float* s_init;
   float* y; float* states; float* s_last;
   int n, D, Dv;
   float sign_a, sign_b;          // y = x + sign_a a S;  S = gamma S + add + sign_b b^T y
@@ -38,7 +39,10 @@ __device__ __forceinline__ uint32_t dc_tf32(float x) {
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
   return r;
 }
-__device__ __forceinline__ void dc_cp_async16(float* dst_smem, const void* src) {
+__device__ __forceinline__ uint32_t dc_bf16_bits(const bf16* p) {   // a bf16 value as a TF32 operand
+  return static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(p)) << 16;
+}
+__device__ __forceinline__ void dc_cp_async16(void* dst_smem, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
 }
 __device__ __forceinline__ void dc_cp_async_wait_all() {
@@ -52,8 +56,7 @@ __device__ __forceinline__ void dc_mma(float (&d)[4], const uint32_t (&a)[4], ui
 
 template <int D, int DC_COLS>
 __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChainParams p) {
-  constexpr int LDA = D + 4;                 // a_i rows read as the A operand (rows 4 banks apart)
-  constexpr int LDB = D + 8;                 // b_i rows read as the A operand of b^T (rows 8 banks apart)
+  constexpr int LDT = D + 8;                 // bf16 row stride of the a_i / b_i tiles: rows 4 banks apart, 16-byte rows
   constexpr int DC_LDS = DC_COLS + 8;        // rows of the [*, columns] tiles read column-wise as B operands (8 banks apart)
   constexpr int NTM = DC_COLS / 8;           // n-tiles per m-tile of S
   constexpr int TPW = (D / 16) * NTM / 8;    // m16n8 tiles of S per warp: tile id = warp * TPW + x -> (id / NTM, id % NTM)
@@ -61,17 +64,17 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChai
   constexpr int MT = TPW / NT;
   constexpr int YT = DC_COLS / 16;           // n-tiles of y per warp
   extern __shared__ __align__(16) float dc_smem[];
-  float* As = dc_smem;                       // [64][LDA]
-  float* Bs = As + DC_C * LDA;               // [64][LDB]
-  float* Ss = Bs + DC_C * LDB;               // [D][40]
+  bf16* As = reinterpret_cast<bf16*>(dc_smem);              // [64][LDT]
+  bf16* Bs = As + DC_C * LDT;                               // [64][LDT]
+  float* Ss = reinterpret_cast<float*>(Bs + DC_C * LDT);    // [D][columns + 8], rounded to TF32
   float* Ys = Ss + D * DC_LDS;               // [64][40]   sign_b * y
   float* red = Ys + DC_C * DC_LDS;           // [8] per-warp partial sums of the optional dot product
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, c = lane & 3;
   const int col0 = blockIdx.x * DC_COLS;
   const int64_t bh = blockIdx.y;
   const int Dv = p.Dv;
-  const float* a_base = p.a + bh * p.n * DC_C * D;
-  const float* b_base = p.b + bh * p.n * DC_C * D;
+  const bf16* a_base = p.a + bh * p.n * DC_C * D;
+  const bf16* b_base = p.b + bh * p.n * DC_C * D;
   const float* x_base = p.x + bh * p.n * DC_C * Dv + col0;
   float* y_base = p.y + bh * p.n * DC_C * Dv + col0;
   float* st_base = p.states + bh * p.n * D * Dv + col0;
@@ -96,12 +99,12 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChai
   for (int step = 0; step < p.n; ++step) {
     const int i = p.reverse ? p.n - 1 - step : step;
     // ---- stage a_i, b_i; publish S (to shared memory for the y products, to global memory as states[i])
-    const float4* ga = reinterpret_cast<const float4*>(a_base + static_cast<int64_t>(i) * DC_C * D);
-    const float4* gb = reinterpret_cast<const float4*>(b_base + static_cast<int64_t>(i) * DC_C * D);
-    for (int v = threadIdx.x; v < DC_C * D / 4; v += DC_THREADS) {
-      const int row = v / (D / 4), c4 = (v % (D / 4)) * 4;
-      dc_cp_async16(As + row * LDA + c4, ga + v);
-      dc_cp_async16(Bs + row * LDB + c4, gb + v);
+    const uint4* ga = reinterpret_cast<const uint4*>(a_base + static_cast<int64_t>(i) * DC_C * D);
+    const uint4* gb = reinterpret_cast<const uint4*>(b_base + static_cast<int64_t>(i) * DC_C * D);
+    for (int v = threadIdx.x; v < DC_C * D / 8; v += DC_THREADS) {
+      const int row = v / (D / 8), c8 = (v % (D / 8)) * 8;
+      dc_cp_async16(As + row * LDT + c8, ga + v);
+      dc_cp_async16(Bs + row * LDT + c8, gb + v);
     }
 #pragma unroll
     for (int m = 0; m < MT; ++m)
@@ -142,13 +145,13 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChai
       float acc[YT][4];
 #pragma unroll
       for (int t = 0; t < YT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
-      const float* arow = As + (16 * ymt + g) * LDA + c;
+      const bf16* arow = As + (16 * ymt + g) * LDT + c;
       const uint32_t* sb0 = reinterpret_cast<const uint32_t*>(Ss) + c * DC_LDS + 8 * ynt0 + g;
 #pragma unroll 4
       for (int k0 = 0; k0 < D; k0 += 8) {
         uint32_t a[4];
-        a[0] = dc_tf32(arow[k0]); a[1] = dc_tf32(arow[8 * LDA + k0]);
-        a[2] = dc_tf32(arow[k0 + 4]); a[3] = dc_tf32(arow[8 * LDA + k0 + 4]);
+        a[0] = dc_bf16_bits(arow + k0); a[1] = dc_bf16_bits(arow + 8 * LDT + k0);
+        a[2] = dc_bf16_bits(arow + k0 + 4); a[3] = dc_bf16_bits(arow + 8 * LDT + k0 + 4);
 #pragma unroll
         for (int t = 0; t < YT; ++t) {
           const uint32_t* sb = sb0 + k0 * DC_LDS + 8 * t;
@@ -183,12 +186,12 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChai
         s[m][t][0] = fmaf(gm, s[m][t][0], lo.x); s[m][t][1] = fmaf(gm, s[m][t][1], lo.y);
         s[m][t][2] = fmaf(gm, s[m][t][2], hi.x); s[m][t][3] = fmaf(gm, s[m][t][3], hi.y);
       }
-      const float* bcol = Bs + c * LDB + 16 * (mt0 + m) + g;             // b^T as the A operand: A[d][k] = b[k][d]
+      const bf16* bcol = Bs + c * LDT + 16 * (mt0 + m) + g;              // b^T as the A operand: A[d][k] = b[k][d]
 #pragma unroll 4
       for (int k0 = 0; k0 < DC_C; k0 += 8) {
         uint32_t a[4];
-        a[0] = dc_tf32(bcol[k0 * LDB]); a[1] = dc_tf32(bcol[k0 * LDB + 8]);
-        a[2] = dc_tf32(bcol[(k0 + 4) * LDB]); a[3] = dc_tf32(bcol[(k0 + 4) * LDB + 8]);
+        a[0] = dc_bf16_bits(bcol + k0 * LDT); a[1] = dc_bf16_bits(bcol + k0 * LDT + 8);
+        a[2] = dc_bf16_bits(bcol + (k0 + 4) * LDT); a[3] = dc_bf16_bits(bcol + (k0 + 4) * LDT + 8);
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
           const uint32_t* yb = reinterpret_cast<const uint32_t*>(Ys) + (k0 + c) * DC_LDS + 8 * (nt0 + t) + g;
@@ -210,7 +213,8 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChai
 
 template <int D, int COLS>
 static int launch_delta_chain(const DeltaChainParams& p, int BH, cudaStream_t stream) {
-  constexpr int smem = (DC_C * (D + 4) + DC_C * (D + 8) + D * (COLS + 8) + DC_C * (COLS + 8) + 8) * static_cast<int>(sizeof(float));
+  constexpr int smem = 2 * DC_C * (D + 8) * static_cast<int>(sizeof(bf16)) +
+                       (D * (COLS + 8) + DC_C * (COLS + 8) + 8) * static_cast<int>(sizeof(float));
   auto kern = delta_chain_kernel<D, COLS>;
   static bool configured = false;
   if (!configured) {
@@ -234,9 +238,9 @@ static int delta_chain_dispatch(const DeltaChainParams& p, int BH, cudaStream_t 
 
 }  // namespace ttcd
 
-// All tensors fp32, contiguous: w, kt [BH][n][64][D]; u, vn [BH][n][64][Dv]; gamma [BH][n]; s0, s_final [BH][D][Dv];
+// Contiguous tensors: w, kt [BH][n][64][D] bf16; fp32: u, vn [BH][n][64][Dv]; gamma [BH][n]; s0, s_final [BH][D][Dv];
 // states [BH][n][D][Dv] (the state entering each chunk).  D in {32, 64, 128, 256}, Dv a multiple of 32.
-TTCD_EXPORT int ttcd_delta_chain_fwd(const float* w, const float* u, const float* kt, const float* gamma, const float* s0,
+TTCD_EXPORT int ttcd_delta_chain_fwd(const bf16* w, const float* u, const bf16* kt, const float* gamma, const float* s0,
                                      float* vn, float* states, float* s_final, int BH, int n, int D, int Dv,
                                      void* stream_ptr) {
   ttcd::DeltaChainParams p;
@@ -251,7 +255,7 @@ TTCD_EXPORT int ttcd_delta_chain_fwd(const float* w, const float* u, const float
 // gradient of vn (d_vn_tot), the gradient of the state LEAVING each chunk (ds_next [BH][n][D][Dv]) and of s0.  With
 // `states` (the forward states) it also writes d_gamma_parts [BH][n][Dv / 32] (zero-filled by the caller): per chunk and
 // column slice of a CTA, the sum of states * ds_next (the gradient of the chunk's decay is the sum over a row).
-TTCD_EXPORT int ttcd_delta_chain_bwd(const float* w, const float* kt, const float* gamma, const float* d_vn,
+TTCD_EXPORT int ttcd_delta_chain_bwd(const bf16* w, const bf16* kt, const float* gamma, const float* d_vn,
                                      const float* d_states, const float* d_final, float* d_vn_tot, float* ds_next,
                                      float* d_s0, const float* states, float* d_gamma_parts, int BH, int n, int D, int Dv,
                                      void* stream_ptr) {

@@ -43,7 +43,8 @@ struct DeltaPrepParams {
   const float* beta; const float* g;                // [B, T, H]; g null: no gate
   int T, H, D, Dv, n;                               // n = chunks per sequence
   float scale; int l2norm; int in_bf16;
-  float *w, *u, *kt, *q_in, *qk, *gamma;            // forward outputs, chunk layout [B*H, n, 64, *]
+  bf16 *w, *kt;                                     // forward outputs, chunk layout [B*H, n, 64, *]: the chain's tile operands in bf16,
+  float *u, *q_in, *qk, *gamma;                     // the rest fp32
   const float *d_w, *d_u, *d_kt, *d_qin, *d_qk, *d_gamma;
   float *dq, *dk, *dv, *dbeta, *dg;                 // backward outputs, token layout [B, T, H, *] fp32
 };
@@ -390,7 +391,8 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_fwd_kernel(const Del
       const float4 qq = *reinterpret_cast<const float4*>(S1 + r * DP_LDB + c4);
       const float te = vec.to_end[r], eg = vec.eg[r];
       const int64_t at = (cc.chunk * DP_C + r) * p.D + s + c4;
-      *reinterpret_cast<float4*>(p.kt + at) = make_float4(kk.x * te, kk.y * te, kk.z * te, kk.w * te);
+      const __nv_bfloat162 k01 = __floats2bfloat162_rn(kk.x * te, kk.y * te), k23 = __floats2bfloat162_rn(kk.z * te, kk.w * te);
+      *reinterpret_cast<uint2*>(p.kt + at) = make_uint2(*reinterpret_cast<const uint32_t*>(&k01), *reinterpret_cast<const uint32_t*>(&k23));
       *reinterpret_cast<float4*>(p.q_in + at) = make_float4(qq.x * eg, qq.y * eg, qq.z * eg, qq.w * eg);
     }
     float acc[4][4];
@@ -398,8 +400,8 @@ __global__ void __launch_bounds__(DP_THREADS, 2) delta_prep_fwd_kernel(const Del
     mm_nn<false>(acc, Tw, S0, o);
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
-      *reinterpret_cast<float2*>(p.w + (cc.chunk * DP_C + o.r0) * p.D + s + o.col(t)) = make_float2(acc[t][0], acc[t][1]);
-      *reinterpret_cast<float2*>(p.w + (cc.chunk * DP_C + o.r1) * p.D + s + o.col(t)) = make_float2(acc[t][2], acc[t][3]);
+      *reinterpret_cast<__nv_bfloat162*>(p.w + (cc.chunk * DP_C + o.r0) * p.D + s + o.col(t)) = __floats2bfloat162_rn(acc[t][0], acc[t][1]);
+      *reinterpret_cast<__nv_bfloat162*>(p.w + (cc.chunk * DP_C + o.r1) * p.D + s + o.col(t)) = __floats2bfloat162_rn(acc[t][2], acc[t][3]);
     }
     __syncthreads();
   }
@@ -715,10 +717,10 @@ static int delta_prep_check(const DeltaPrepParams& p, int BH) {
 }  // namespace ttcd
 
 // q, k [B, T, H, D], v [B, T, H, Dv] contiguous, bf16 (in_bf16 = 1) or fp32; beta, g [B, T, H] fp32 (g may be null).
-// Outputs fp32 in chunk layout, n = ceil(T / 64) chunks per (batch, head): w, kt, q_in [B*H, n, 64, D]; u [B*H, n, 64, Dv];
-// qk [B*H, n, 64, 64]; gamma [B*H, n].  Rows beyond T act as beta = 0, g = 0.  D, Dv multiples of 64.
-TTCD_EXPORT int ttcd_delta_prep_fwd(const void* q, const void* k, const void* v, const float* beta, const float* g, float* w,
-                                    float* u, float* kt, float* q_in, float* qk, float* gamma, int B, int T, int H, int D,
+// Outputs in chunk layout, n = ceil(T / 64) chunks per (batch, head): w, kt [B*H, n, 64, D] bf16 (the chain kernel's tile
+// operands); fp32: q_in [B*H, n, 64, D], u [B*H, n, 64, Dv], qk [B*H, n, 64, 64], gamma [B*H, n].  Rows beyond T act as beta = 0, g = 0.  D, Dv multiples of 64.
+TTCD_EXPORT int ttcd_delta_prep_fwd(const void* q, const void* k, const void* v, const float* beta, const float* g, bf16* w,
+                                    float* u, bf16* kt, float* q_in, float* qk, float* gamma, int B, int T, int H, int D,
                                     int Dv, float scale, int l2norm, int in_bf16, void* stream_ptr) {
   ttcd::DeltaPrepParams p = {};
   p.q = q; p.k = k; p.v = v; p.beta = beta; p.g = g;

@@ -284,7 +284,9 @@ def test_delta_chain_kernels_match_the_loop(BH, n, D, Dv):
     from ttcd_b200.ops import delta_chain as dc
     gen = torch.Generator().manual_seed(BH * 100 + D)
     mk = lambda *sh, sc=0.2: (torch.randn(*sh, generator=gen) * sc).to(DEV).requires_grad_()  # noqa: E731
-    w, u, kt, s0 = mk(BH, n, 64, D, sc=0.1), mk(BH, n, 64, Dv), mk(BH, n, 64, D, sc=0.1), mk(BH, D, Dv)
+    mk16 = lambda *sh, sc: (torch.randn(*sh, generator=gen) * sc).bfloat16().float().to(DEV).requires_grad_()  # noqa: E731
+    # w and kt are multiplied as bf16 by the kernels: values that bf16 holds exactly, so that the loop sees the same numbers
+    w, u, kt, s0 = mk16(BH, n, 64, D, sc=0.1), mk(BH, n, 64, Dv), mk16(BH, n, 64, D, sc=0.1), mk(BH, D, Dv)
     gamma = torch.rand(BH, n, generator=gen).to(DEV).requires_grad_()
     assert dc._native_ok(w, u)
     outs = dc.delta_chain(w, u, kt, gamma, s0)
@@ -332,7 +334,7 @@ def test_delta_prep_kernels_match_their_statement(D, Dv, gated, l2norm, dtype):
     want = df._prep_fwd_torch(dbl(q), dbl(k), dbl(v), dbl(beta), dbl(g), scale, l2norm)
     # the 64 x 64 x 64 products run with TF32 operands (10-bit mantissa): errors relative to the largest entry
     for a, b, name in zip(got, want, ("w", "u", "kt", "q_in", "qk", "gamma")):
-        tol = float(b.abs().max()) * (1e-5 if name in ("kt", "q_in", "gamma") else 2e-3)
+        tol = float(b.abs().max()) * {"q_in": 1e-5, "gamma": 1e-5, "kt": 4e-3, "w": 5e-3}.get(name, 2e-3)    # w, kt are stored as bf16
         torch.testing.assert_close(a.double(), b, rtol=0, atol=tol, msg=lambda m, name=name: f"{name}: {m}")
     gen = torch.Generator().manual_seed(7)
     grads = [torch.randn(o.shape, generator=gen).to(DEV) for o in got]

@@ -22,6 +22,7 @@ from .. import _native as nv
 
 
 def _fwd_torch(w, u, kt, gamma, s0):
+    w, kt = w.to(u.dtype), kt.to(u.dtype)
     BH, n, C, D = w.shape
     S = s0.clone()
     vn = torch.empty_like(u)
@@ -34,6 +35,7 @@ def _fwd_torch(w, u, kt, gamma, s0):
 
 
 def _bwd_torch(w, kt, gamma, d_vn, d_states, d_final, states=None):
+    w, kt = w.to(d_vn.dtype), kt.to(d_vn.dtype)
     BH, n, C, D = w.shape
     dS = d_final.clone()
     d_vn_tot = torch.empty_like(d_vn)
@@ -49,8 +51,13 @@ def _bwd_torch(w, kt, gamma, d_vn, d_states, d_final, states=None):
 
 def _native_ok(w, u) -> bool:
     D, Dv = w.shape[-1], u.shape[-1]
-    return (w.is_cuda and nv.available() and nv.has("ttcd_delta_chain_fwd") and w.dtype == torch.float32
-            and D in (32, 64, 128, 256) and Dv % 32 == 0 and w.shape[2] == 64)
+    return (w.is_cuda and nv.available() and nv.has("ttcd_delta_chain_fwd") and w.dtype in (torch.float32, torch.bfloat16)
+            and u.dtype == torch.float32 and D in (32, 64, 128, 256) and Dv % 32 == 0 and w.shape[2] == 64)
+
+
+def _tiles(t: torch.Tensor) -> torch.Tensor:
+    """w / kt as the kernels take them: contiguous bf16 (exact TF32 operands, half the staging traffic)."""
+    return t.to(torch.bfloat16).contiguous()
 
 
 def _fwd(w, u, kt, gamma, s0):
@@ -58,7 +65,8 @@ def _fwd(w, u, kt, gamma, s0):
         return _fwd_torch(w, u, kt, gamma, s0)
     BH, n, C, D = w.shape
     Dv = u.shape[-1]
-    w, u, kt, gamma, s0 = (t.contiguous() for t in (w, u, kt, gamma, s0))
+    w, kt = _tiles(w), _tiles(kt)
+    u, gamma, s0 = (t.contiguous() for t in (u, gamma, s0))
     vn = torch.empty_like(u)
     states = torch.empty(BH, n, D, Dv, dtype=torch.float32, device=w.device)
     final = torch.empty(BH, D, Dv, dtype=torch.float32, device=w.device)
@@ -73,7 +81,8 @@ def _bwd(w, kt, gamma, d_vn, d_states, d_final, states=None):
         return _bwd_torch(w, kt, gamma, d_vn, d_states, d_final, states)
     BH, n, C, D = w.shape
     Dv = d_vn.shape[-1]
-    w, kt, gamma, d_vn, d_states, d_final = (t.contiguous() for t in (w, kt, gamma, d_vn, d_states, d_final))
+    w, kt = _tiles(w), _tiles(kt)
+    gamma, d_vn, d_states, d_final = (t.contiguous() for t in (gamma, d_vn, d_states, d_final))
     d_vn_tot = torch.empty_like(d_vn)
     dS_next = torch.empty_like(d_states)
     d_s0 = torch.empty_like(d_final)
@@ -108,6 +117,6 @@ class _DeltaChain(torch.autograd.Function):
 
 
 def delta_chain(w, u, kt, gamma, s0):
-    """w, kt [BH, n, C, D]; u [BH, n, C, Dv]; gamma [BH, n]; s0 [BH, D, Dv] (fp32).  Returns (vn [BH, n, C, Dv], the state
+    """w, kt [BH, n, C, D] (the CUDA kernels multiply them as bf16); u [BH, n, C, Dv]; gamma [BH, n]; s0 [BH, D, Dv] (fp32).  Returns (vn [BH, n, C, Dv], the state
     entering every chunk [BH, n, D, Dv], the final state [BH, D, Dv])."""
     return _DeltaChain.apply(w, u, kt, gamma, s0)

@@ -133,7 +133,8 @@ def _prep_fwd(q, k, v, beta, g, scale, l2norm):
     B, T, H, D = q.shape
     Dv, n, dev = v.shape[-1], -(-T // C), q.device
     new = lambda *s: torch.empty(*s, dtype=torch.float32, device=dev)  # noqa: E731
-    w, kt, q_in, u = new(B * H, n, C, D), new(B * H, n, C, D), new(B * H, n, C, D), new(B * H, n, C, Dv)
+    w, kt = (torch.empty(B * H, n, C, D, dtype=torch.bfloat16, device=dev) for _ in range(2))     # the chain's tile operands
+    q_in, u = new(B * H, n, C, D), new(B * H, n, C, Dv)
     qk, gamma = new(B * H, n, C, C), new(B * H, n)
     nv.call("ttcd_delta_prep_fwd", nv.ptr(q), nv.ptr(k), nv.ptr(v), nv.ptr(beta), nv.ptr(g), nv.ptr(w), nv.ptr(u), nv.ptr(kt),
             nv.ptr(q_in), nv.ptr(qk), nv.ptr(gamma), nv.i32(B), nv.i32(T), nv.i32(H), nv.i32(D), nv.i32(Dv), nv.f32(scale),
@@ -244,7 +245,7 @@ class _FusedDeltaRule(torch.autograd.Function):
         with _tf32_matmuls(q.is_cuda):
             o = torch.baddbmm(torch.bmm(_flat(q_in), _flat(states)), _flat(qk), _flat(vn)).view(B * H, -1, C, Dv)
         kept = (w, kt, q_in, qk, gamma, vn, states)
-        if not _keep_intermediates(ctx, q, sum(t.numel() * 4 for t in kept)):
+        if not _keep_intermediates(ctx, q, sum(t.numel() * t.element_size() for t in kept)):
             kept = ()
         ctx.save_for_backward(q, k, v, g32, beta32, s0_32, *kept)
         ctx.scale, ctx.l2norm, ctx.has_kept = scale, l2norm, bool(kept)
@@ -273,8 +274,8 @@ class _FusedDeltaRule(torch.autograd.Function):
             # the chain, in reverse
             d_u, ds_next, d_s0, d_gamma = dc._bwd(w, kt, gamma, d_vn, d_states, d_final, states)
             del d_vn, d_states
-            d_w = torch.baddbmm(d_u.new_zeros(1, 1, 1), _flat(d_u), _flat(states).transpose(1, 2), beta=0, alpha=-1).view_as(w)
-            d_kt = torch.bmm(_flat(vn), _flat(ds_next).transpose(1, 2)).view_as(kt)
+            d_w = torch.baddbmm(d_u.new_zeros(1, 1, 1), _flat(d_u), _flat(states).transpose(1, 2), beta=0, alpha=-1).view(w.shape)
+            d_kt = torch.bmm(_flat(vn), _flat(ds_next).transpose(1, 2)).view(kt.shape)
         del ds_next
         dq, dk, dv, dbeta, dg = _prep_bwd(q, k, v, beta32, g32, ctx.scale, ctx.l2norm, d_w, d_u, d_kt, d_qin, d_qk, d_gamma)
         beta_dtype, g_dtype, s0_dtype = ctx.dtypes
