@@ -12,9 +12,13 @@
 // (the role of chunk_gated_delta_rule_fwd_h / chunk_gated_delta_rule_bwd_dhu in fla/ops/common/chunk_delta_h.py).
 // The columns of S never mix, so a CTA owns 32 of them (64 for D = 256, where a_i and b_i are large and every column
 // slice re-reads them) for the whole sequence: grid (Dv / columns, batch * heads).  Per chunk the CTA stages a_i and
-// b_i [64, D] in shared memory with asynchronous 16-byte copies that overlap the publication of S.  S [D, 32] lives in the accumulator registers of the
-// second product (D / 32 m16n8 tiles per warp) across chunks and is mirrored in shared memory as the B operand of the
-// first.  No waits on other CTAs or on asynchronous copies: nothing here can spin.
+// b_i [64, D] (bf16) in shared memory with asynchronous 16-byte copies that overlap the publication of S.  S [D, columns]
+// lives in the accumulator registers of the second product (D / 32 m16n8 tiles per warp) across chunks, in fp32, and is
+// mirrored in shared memory, rounded to bf16, as the B operand of the first; y is rounded the same way for the second.
+// Every operand of a product is thus a bf16 value (an exact TF32 operand after a 16-bit shift; the precision the
+// reference's Triton kernels multiply at), the sums and the state stay fp32, and two CTAs fit an SM at every D.
+// The only asynchronous copies are the CTA's own cp.async groups (waited for with wait_group); nothing here waits on
+// another CTA, so nothing can spin.
 #include "common.cuh"
 
 namespace ttcd {
@@ -34,11 +38,6 @@ struct DeltaChainParams {
   const float* dot_with; float* dot_out;
 };
 
-__device__ __forceinline__ uint32_t dc_tf32(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-  return r;
-}
 __device__ __forceinline__ uint32_t dc_bf16_bits(const bf16* p) {   // a bf16 value as a TF32 operand
   return static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(p)) << 16;
 }
@@ -55,9 +54,9 @@ __device__ __forceinline__ void dc_mma(float (&d)[4], const uint32_t (&a)[4], ui
 }
 
 template <int D, int DC_COLS>
-__global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChainParams p) {
+__global__ void __launch_bounds__(DC_THREADS, 2) delta_chain_kernel(const DeltaChainParams p) {
   constexpr int LDT = D + 8;                 // bf16 row stride of the a_i / b_i tiles: rows 4 banks apart, 16-byte rows
-  constexpr int DC_LDS = DC_COLS + 8;        // rows of the [*, columns] tiles read column-wise as B operands (8 banks apart)
+  constexpr int DC_LDS = DC_COLS + 8;        // bf16 row stride of the [*, columns] tiles read column-wise as B operands
   constexpr int NTM = DC_COLS / 8;           // n-tiles per m-tile of S
   constexpr int TPW = (D / 16) * NTM / 8;    // m16n8 tiles of S per warp: tile id = warp * TPW + x -> (id / NTM, id % NTM)
   constexpr int NT = TPW >= NTM ? NTM : TPW; // ... of which NT share an m-tile
@@ -66,9 +65,9 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChai
   extern __shared__ __align__(16) float dc_smem[];
   bf16* As = reinterpret_cast<bf16*>(dc_smem);              // [64][LDT]
   bf16* Bs = As + DC_C * LDT;                               // [64][LDT]
-  float* Ss = reinterpret_cast<float*>(Bs + DC_C * LDT);    // [D][columns + 8], rounded to TF32
-  float* Ys = Ss + D * DC_LDS;               // [64][40]   sign_b * y
-  float* red = Ys + DC_C * DC_LDS;           // [8] per-warp partial sums of the optional dot product
+  bf16* Ss = Bs + DC_C * LDT;                               // [D][columns + 8]   S as the B operand of a S
+  bf16* Ys = Ss + D * DC_LDS;                               // [64][columns + 8]  sign_b * y as the B operand of b^T y
+  float* red = reinterpret_cast<float*>(Ys + DC_C * DC_LDS);    // [8] per-warp partial sums of the optional dot product
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, c = lane & 3;
   const int col0 = blockIdx.x * DC_COLS;
   const int64_t bh = blockIdx.y;
@@ -112,8 +111,8 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChai
       for (int t = 0; t < NT; ++t) {
         const int row = 16 * (mt0 + m) + g, col = 8 * (nt0 + t) + 2 * c;
         const float2 lo = make_float2(s[m][t][0], s[m][t][1]), hi = make_float2(s[m][t][2], s[m][t][3]);
-        *reinterpret_cast<uint2*>(Ss + row * DC_LDS + col) = make_uint2(dc_tf32(lo.x), dc_tf32(lo.y));      // B operand, rounded once
-        *reinterpret_cast<uint2*>(Ss + (row + 8) * DC_LDS + col) = make_uint2(dc_tf32(hi.x), dc_tf32(hi.y));
+        *reinterpret_cast<__nv_bfloat162*>(Ss + row * DC_LDS + col) = __floats2bfloat162_rn(lo.x, lo.y);      // B operand, rounded once
+        *reinterpret_cast<__nv_bfloat162*>(Ss + (row + 8) * DC_LDS + col) = __floats2bfloat162_rn(hi.x, hi.y);
         *reinterpret_cast<float2*>(st_base + (static_cast<int64_t>(i) * D + row) * Dv + col) = lo;
         *reinterpret_cast<float2*>(st_base + (static_cast<int64_t>(i) * D + row + 8) * Dv + col) = hi;
       }
@@ -146,7 +145,7 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChai
 #pragma unroll
       for (int t = 0; t < YT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
       const bf16* arow = As + (16 * ymt + g) * LDT + c;
-      const uint32_t* sb0 = reinterpret_cast<const uint32_t*>(Ss) + c * DC_LDS + 8 * ynt0 + g;
+      const bf16* sb0 = Ss + c * DC_LDS + 8 * ynt0 + g;
 #pragma unroll 4
       for (int k0 = 0; k0 < D; k0 += 8) {
         uint32_t a[4];
@@ -154,8 +153,8 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChai
         a[2] = dc_bf16_bits(arow + k0 + 4); a[3] = dc_bf16_bits(arow + 8 * LDT + k0 + 4);
 #pragma unroll
         for (int t = 0; t < YT; ++t) {
-          const uint32_t* sb = sb0 + k0 * DC_LDS + 8 * t;
-          dc_mma(acc[t], a, sb[0], sb[4 * DC_LDS]);
+          const bf16* sb = sb0 + k0 * DC_LDS + 8 * t;
+          dc_mma(acc[t], a, dc_bf16_bits(sb), dc_bf16_bits(sb + 4 * DC_LDS));
         }
       }
 #pragma unroll
@@ -167,7 +166,7 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChai
           const float2 xv = *reinterpret_cast<const float2*>(x_base + off);
           const float2 yv = make_float2(xv.x + p.sign_a * acc[t][2 * h], xv.y + p.sign_a * acc[t][2 * h + 1]);
           *reinterpret_cast<float2*>(y_base + off) = yv;
-          *reinterpret_cast<uint2*>(Ys + row * DC_LDS + col) = make_uint2(dc_tf32(p.sign_b * yv.x), dc_tf32(p.sign_b * yv.y));
+          *reinterpret_cast<__nv_bfloat162*>(Ys + row * DC_LDS + col) = __floats2bfloat162_rn(p.sign_b * yv.x, p.sign_b * yv.y);
         }
     }
     __syncthreads();
@@ -194,8 +193,8 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChai
         a[2] = dc_bf16_bits(bcol + (k0 + 4) * LDT); a[3] = dc_bf16_bits(bcol + (k0 + 4) * LDT + 8);
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
-          const uint32_t* yb = reinterpret_cast<const uint32_t*>(Ys) + (k0 + c) * DC_LDS + 8 * (nt0 + t) + g;
-          dc_mma(s[m][t], a, yb[0], yb[4 * DC_LDS]);
+          const bf16* yb = Ys + (k0 + c) * DC_LDS + 8 * (nt0 + t) + g;
+          dc_mma(s[m][t], a, dc_bf16_bits(yb), dc_bf16_bits(yb + 4 * DC_LDS));
         }
       }
     }
@@ -213,8 +212,8 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chain_kernel(const DeltaChai
 
 template <int D, int COLS>
 static int launch_delta_chain(const DeltaChainParams& p, int BH, cudaStream_t stream) {
-  constexpr int smem = 2 * DC_C * (D + 8) * static_cast<int>(sizeof(bf16)) +
-                       (D * (COLS + 8) + DC_C * (COLS + 8) + 8) * static_cast<int>(sizeof(float));
+  constexpr int smem = (2 * DC_C * (D + 8) + D * (COLS + 8) + DC_C * (COLS + 8)) * static_cast<int>(sizeof(bf16)) +
+                       8 * static_cast<int>(sizeof(float));
   auto kern = delta_chain_kernel<D, COLS>;
   static bool configured = false;
   if (!configured) {

@@ -291,10 +291,10 @@ def test_delta_chain_kernels_match_the_loop(BH, n, D, Dv):
     assert dc._native_ok(w, u)
     outs = dc.delta_chain(w, u, kt, gamma, s0)
     want = dc._fwd_torch(*(t.detach() for t in (w, u, kt, gamma, s0)))
-    # the products run with TF32 operands (10-bit mantissa): errors relative to the largest entry
+    # the running state and the corrected values enter the products rounded to bf16: errors relative to the largest entry
     for a, b, name in zip(outs, want, ("vn", "states", "final")):
-        torch.testing.assert_close(a, b, rtol=0, atol=3e-3 * float(b.abs().max()), msg=lambda m, name=name: f"{name}: {m}")
-        assert _cos(a, b) > 0.99999, name
+        torch.testing.assert_close(a, b, rtol=0, atol=8e-3 * float(b.abs().max()), msg=lambda m, name=name: f"{name}: {m}")
+        assert _cos(a, b) > 0.9999, name
     gs = [torch.randn_like(o) for o in outs]
     got = torch.autograd.grad(outs, [w, u, kt, gamma, s0], gs)
     d_vn_tot, ds_next, d_s0 = dc._bwd_torch(w.detach(), kt.detach(), gamma.detach(), *gs)
@@ -302,8 +302,8 @@ def test_delta_chain_kernels_match_the_loop(BH, n, D, Dv):
     ref = [-(d_vn_tot @ states.transpose(-1, -2)), d_vn_tot, want[0] @ ds_next.transpose(-1, -2),
            (states * ds_next).sum(dim=(-1, -2)), d_s0]
     for a, b, name in zip(got, ref, ("dw", "du", "dkt", "dgamma", "ds0")):
-        torch.testing.assert_close(a, b, rtol=0, atol=3e-3 * float(b.abs().max()), msg=lambda m, name=name: f"{name}: {m}")
-        assert _cos(a, b) > 0.99999, name
+        torch.testing.assert_close(a, b, rtol=0, atol=8e-3 * float(b.abs().max()), msg=lambda m, name=name: f"{name}: {m}")
+        assert _cos(a, b) > 0.9999, name
 
 
 def _delta_inputs(B, T, H, D, Dv, gated, l2norm, dtype, seed):
