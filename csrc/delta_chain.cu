@@ -54,7 +54,7 @@ __device__ __forceinline__ void dc_mma(float (&d)[4], const uint32_t (&a)[4], ui
 }
 
 template <int D, int DC_COLS>
-__global__ void __launch_bounds__(DC_THREADS, 2) delta_chain_kernel(const DeltaChainParams p) {
+__global__ void __launch_bounds__(DC_THREADS, (D <= 128 ? 4 : 2)) delta_chain_kernel(const DeltaChainParams p) {
   constexpr int LDT = D + 8;                 // bf16 row stride of the a_i / b_i tiles: rows 4 banks apart, 16-byte rows
   constexpr int DC_LDS = DC_COLS + 8;        // bf16 row stride of the [*, columns] tiles read column-wise as B operands
   constexpr int NTM = DC_COLS / 8;           // n-tiles per m-tile of S
