@@ -231,8 +231,9 @@ def test_graph_decoding_follows_eager_decoding():
 
 @pytest.mark.parametrize("gated", [False, True])
 def test_delta_rule_on_the_gpu_matches_the_token_by_token_statement(gated):
-    """The chunked rule on CUDA (TF32 products, prefix scan over chunks, 256-token chunks) against the fp32 recurrence
-    evaluated on the CPU: outputs, final state and gradients."""
+    """The chunked rule on CUDA (the one-op form: chunk-local kernels, chain kernels, batched products; bf16 / TF32
+    operands with fp32 sums) against the fp32 recurrence evaluated on the CPU: outputs, final state and gradients, on a
+    length that is not a multiple of the chunk."""
     from ttcd_b200 import ops
     from ttcd_b200.ops import reference as ref
     gen = torch.Generator().manual_seed(3)
