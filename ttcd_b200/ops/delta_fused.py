@@ -1,6 +1,7 @@
 """The chunked (gated) delta rule as ONE differentiable op with a hand-written backward.
 
-Three stages per call, chunks of 64 tokens, everything between them in chunk layout [B*H, n, 64, *] fp32:
+Three stages per call, chunks of 64 tokens, everything between them in chunk layout [B*H, n, 64, *] (fp32, except the
+chain kernels' tile operands ``w`` and ``kt``, which the GPU path stores as bf16):
 
 1. chunk-local (csrc/delta_prep.cu, one CTA per chunk): row normalisation, decay sums, the unit-lower-triangular
    inverse and the WY factors ``w, u``, the end-scaled keys ``kt``, the decayed queries ``q_in``, the intra-chunk
@@ -9,8 +10,9 @@ Three stages per call, chunks of 64 tokens, everything between them in chunk lay
 3. the outputs ``o_i = q_in_i S_i + qk_i vn_i`` (two batched products).
 
 Backward runs the three stages in reverse: four batched products for the output stage, the reverse chain, three
-more for the chain's operands, and one kernel for the chunk-local part.  The fp32 intermediates are kept for
-backward while device memory is plentiful and rebuilt from q, k, v, g, beta otherwise (stages 1 and 2 again).
+more for the chain's operands, and one kernel for the chunk-local part.  The intermediates are kept for backward
+within a share of the device memory and rebuilt from q, k, v, g, beta beyond it (stages 1 and 2 again).  On the GPU
+every operand of a kernel product is a bf16 or TF32 value and every sum is fp32.
 
 This is the computation of fla/ops/gated_delta_rule/chunk.py (``chunk_gated_delta_rule``) and, with ``g`` None, of
 fla/ops/delta_rule/chunk.py (``chunk_delta_rule``).  Off the GPU the same op runs its PyTorch statement of every
